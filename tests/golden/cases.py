@@ -1,0 +1,99 @@
+"""Seeded inputs of the golden cases, shared by the fixture writer and the tests."""
+
+from __future__ import annotations
+
+import torch
+
+from aklr_b200 import workloads as wl
+
+ROUTE_SHAPE = wl.MoEConfig("route256", 128, 128, 256, 8, "sigmoid")
+
+
+def tiny_layer():
+    cfg, seed, tokens = wl.CONFIGS["tiny"], 1234, 64
+    hidden, _, _ = wl.router_inputs(cfg, tokens, seed)
+    w1, s1, w2, s2 = wl.expert_weights(cfg, seed)
+    return cfg, dict(
+        hidden_states=hidden, router_weight=wl.router_weight(cfg, seed), w1=w1, w1_scale=s1, w2=w2, w2_scale=s2
+    )
+
+
+def ds_small_layer():
+    cfg, seed, tokens = wl.CONFIGS["deepseek_small"], 4321, 48
+    hidden, _, bias = wl.router_inputs(cfg, tokens, seed)
+    # x40 spreads the logits so the sigmoid scores are not all near 0.5
+    rw = (wl.router_weight(cfg, seed) * 40).to(torch.bfloat16)
+    w1, s1, w2, s2 = wl.expert_weights(cfg, seed)
+    return cfg, dict(
+        hidden_states=hidden,
+        router_weight=rw,
+        correction_bias=bias,
+        w1=w1,
+        w1_scale=s1,
+        w2=w2,
+        w2_scale=s2,
+        routed_scaling_factor=cfg.routed_scaling_factor,
+    )
+
+
+def route_ds():
+    _, logits, bias = wl.router_inputs(ROUTE_SHAPE, 192, 77)
+    return logits, bias
+
+
+def route_tied():
+    """Heavy ties: logits take 5 distinct values."""
+    g = torch.Generator().manual_seed(5)
+    return (torch.randint(0, 5, (64, 256), generator=g).float() * 0.5 - 1.0).to(torch.bfloat16)
+
+
+def route_qwen3():
+    cfg = wl.CONFIGS["qwen3"]
+    _, logits, _ = wl.router_inputs(cfg, 160, 99)
+    return cfg, logits
+
+
+def bgt():
+    _, logits, bias = wl.router_inputs(ROUTE_SHAPE, 96, 78)
+    return logits, bias
+
+
+def quant_x():
+    x = wl.normal(31, "quant.x", (24, 512), 1.0, dtype=torch.bfloat16)
+    x[3] = 0  # an all-zero row: the amax floor
+    x[5, :128] *= 1e-30
+    return x
+
+
+def mx_case(seed: int, tokens: int = 12, hidden: int = 128, inter: int = 64, experts: int = 6, topk: int = 2):
+    """Random MXFP4 expert weights (random nibbles, e8m0 exponents 118..123) + routing."""
+    g = torch.Generator().manual_seed(seed)
+    x = (torch.randn(tokens, hidden, generator=g)).to(torch.bfloat16)
+    w1 = torch.randint(0, 256, (experts, 2 * inter, hidden // 2), generator=g, dtype=torch.uint8)
+    w2 = torch.randint(0, 256, (experts, hidden, inter // 2), generator=g, dtype=torch.uint8)
+    s1 = torch.randint(118, 124, (experts, 2 * inter, hidden // 32), generator=g, dtype=torch.uint8)
+    s2 = torch.randint(118, 124, (experts, hidden, inter // 32), generator=g, dtype=torch.uint8)
+    ids = torch.stack([torch.randperm(experts, generator=g)[:topk] for _ in range(tokens)]).to(torch.int32)
+    wts = torch.rand(tokens, topk, generator=g)
+    return dict(hidden_states=x, w1=w1, w1_scale=s1, w2=w2, w2_scale=s2, topk_ids=ids, topk_weights=wts)
+
+
+def mega_group():
+    """Two ranks, 3 experts each: global expert e = local e % 3 of rank e // 3."""
+    base = mx_case(7)
+    group = []
+    for r in range(2):
+        mine = mx_case(100 + r)
+        group.append(
+            dict(
+                hidden_states=mine["hidden_states"],
+                topk_ids=mine["topk_ids"],
+                topk_weights=mine["topk_weights"],
+                w1=base["w1"][3 * r : 3 * r + 3],
+                w1_scale=base["w1_scale"][3 * r : 3 * r + 3],
+                w2=base["w2"][3 * r : 3 * r + 3],
+                w2_scale=base["w2_scale"][3 * r : 3 * r + 3],
+                swiglu_limit=10.0,
+            )
+        )
+    return base, group
