@@ -1,0 +1,433 @@
+// extern "C" surface of libaklr_b200.so: argument checks, workspace layout, TMA descriptors and
+// the launch sequence of one fused-MoE layer.  No allocation, no synchronisation (except
+// aklr_moe_read_status, whose purpose is to read a result back), no state between calls.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/aklr_b200.h"
+#include "common.cuh"
+#include "kernels.h"
+
+namespace {
+
+thread_local char g_error[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list args;
+  va_start(args, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, args);
+  va_end(args);
+  return code;
+}
+
+int cuda_fail(cudaError_t err, const char* what) {
+  return fail(AKLR_ERR_CUDA, "%s: %s", what, cudaGetErrorString(err));
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &result) != cudaSuccess ||
+        result != cudaDriverEntryPointSuccess)
+      sym = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(sym);
+  }();
+  return fn;
+}
+
+// 2-D map over a row-major byte matrix [rows, cols]; box = box_rows x 128 bytes, SWIZZLE_128B.
+int make_map_u8(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (!encode) return fail(AKLR_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  if (reinterpret_cast<uintptr_t>(base) % 16 != 0 || cols % 16 != 0)
+    return fail(AKLR_ERR_BAD_ARGUMENT, "TMA operand must be 16-byte aligned with a 16-byte multiple row pitch");
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols};
+  const cuuint32_t box[2] = {128, box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(AKLR_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return AKLR_OK;
+}
+
+int sm_count() {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+  return n;
+}
+
+int check_device() {
+  int dev = 0, major = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return fail(AKLR_ERR_NO_DEVICE, "no CUDA device is current");
+  cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+  if (major != 10) return fail(AKLR_ERR_NO_DEVICE, "this library holds sm_100a code only; device has capability %d.x", major);
+  return AKLR_OK;
+}
+
+int pick_block_m(const aklr_moe_config& c) {
+  if (c.block_m) return c.block_m;
+  const double avg = static_cast<double>(c.n_tokens) * c.topk / (c.n_routed > 0 ? c.n_routed : 1);
+  int bm = 16;
+  while (bm < 128 && bm < avg * 1.5) bm *= 2;
+  return bm;
+}
+
+int check_config(const aklr_moe_config& c) {
+  if (c.n_tokens < 0 || c.hidden < 128 || c.inter < 128 || c.hidden % 128 || c.inter % 128)
+    return fail(AKLR_ERR_UNSUPPORTED_SHAPE, "hidden (%d) and inter (%d) must be positive multiples of 128", c.hidden, c.inter);
+  if (c.n_routed < 1 || c.n_routed > 1024 || c.n_shared < 0 || c.topk < 1 || c.topk + c.n_shared > 32 || c.topk > c.n_routed)
+    return fail(AKLR_ERR_UNSUPPORTED_SHAPE, "n_routed=%d topk=%d n_shared=%d is outside 1..1024 experts, <=32 routes", c.n_routed, c.topk, c.n_shared);
+  if (c.block_m != 0 && c.block_m != 16 && c.block_m != 32 && c.block_m != 64 && c.block_m != 128)
+    return fail(AKLR_ERR_BAD_ARGUMENT, "block_m must be 0, 16, 32, 64 or 128");
+  if (static_cast<int64_t>(c.n_tokens) * (c.topk + c.n_shared) > (1ll << 30))
+    return fail(AKLR_ERR_TOO_LARGE, "too many routes");
+  return AKLR_OK;
+}
+
+int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+void layout_of(const aklr_moe_config& c, aklr_moe_workspace_layout* l) {
+  const int64_t routes_per_token = c.topk + c.n_shared;
+  const int64_t routes = static_cast<int64_t>(c.n_tokens) * routes_per_token;
+  const int64_t experts = c.n_routed + c.n_shared;
+  const int bm = pick_block_m(c);
+  int64_t max_blocks = aklr::align_max_blocks(routes, experts, bm);
+  if (max_blocks < 1) max_blocks = 1;
+  const int64_t cap = max_blocks * bm;
+  const int64_t chunks = (routes + 1023) / 1024;
+  int64_t at = 0;
+  auto take = [&](int64_t bytes, int64_t align) {
+    at = align_up(at, align);
+    const int64_t here = at;
+    at += bytes;
+    return here;
+  };
+  l->status = take(16, 256);
+  l->num_blocks = take(16, 16);
+  l->topk_ids = take(routes * 4, 256);
+  l->topk_weights = take(routes * 4, 256);
+  l->sorted_ids = take(cap * 4, 256);
+  l->block_expert = take(max_blocks * 4, 256);
+  l->counts = take(experts * 4, 256);
+  l->chunk_hist = take((chunks > 0 ? chunks : 1) * experts * 4, 256);
+  l->xq = take(cap * c.hidden, 1024);
+  l->xs = take(cap * (c.hidden / 128) * 4, 256);
+  l->hq = take(cap * c.inter, 1024);
+  l->hs = take(cap * (c.inter / 128) * 4, 256);
+  l->rows = take(routes * c.hidden * 2, 1024);
+  l->total_bytes = align_up(at, 256);
+  l->block_m = bm;
+  l->max_blocks = static_cast<int32_t>(max_blocks);
+  l->capacity = static_cast<int32_t>(cap);
+  l->n_experts = static_cast<int32_t>(experts);
+}
+
+// Everything after the routing table exists: sort, quantise, two grouped GEMMs, combine.
+int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, const void* hidden_states,
+                const int32_t* topk_ids, const float* topk_weights, const int32_t* expert_map,
+                int n_experts_global, const void* w1, const float* w1_scale, const void* w2,
+                const float* w2_scale, void* out, uint8_t* ws, cudaStream_t stream) {
+  using namespace aklr;
+  const int routes_per_token = c.topk + c.n_shared;
+  const int routes = c.n_tokens * routes_per_token;
+  const int experts = c.n_routed + c.n_shared;
+  int32_t* status = reinterpret_cast<int32_t*>(ws + l.status);
+  int32_t* num_blocks = reinterpret_cast<int32_t*>(ws + l.num_blocks);
+  int32_t* sorted_ids = reinterpret_cast<int32_t*>(ws + l.sorted_ids);
+  int32_t* block_expert = reinterpret_cast<int32_t*>(ws + l.block_expert);
+
+  AlignParams ap{};
+  ap.topk_ids = topk_ids;
+  ap.expert_map = expert_map;
+  ap.sorted_ids = sorted_ids;
+  ap.block_expert = block_expert;
+  ap.counts = reinterpret_cast<int32_t*>(ws + l.counts);
+  ap.num_blocks = num_blocks;
+  ap.chunk_hist = reinterpret_cast<int32_t*>(ws + l.chunk_hist);
+  ap.n_routes = routes;
+  ap.n_experts = experts;
+  ap.n_experts_global = n_experts_global;
+  ap.block_m = l.block_m;
+  int rc = launch_align(ap, stream);
+  if (rc) return fail(rc, "moe_align launch failed");
+
+  GatherQuantParams qp{};
+  qp.x = hidden_states;
+  qp.sorted_ids = sorted_ids;
+  qp.num_rows = num_blocks + 1;
+  qp.q = ws + l.xq;
+  qp.scales = reinterpret_cast<float*>(ws + l.xs);
+  qp.n_rows = l.capacity;
+  qp.hidden = c.hidden;
+  qp.routes_per_token = routes_per_token;
+  rc = launch_gather_quant_fp8(qp, stream);
+  if (rc) return fail(rc, "activation quant launch failed");
+
+  const int sms = sm_count();
+  GroupedGemmParams g1{};
+  rc = make_map_u8(&g1.map_w, w1, static_cast<uint64_t>(experts) * 2 * c.inter, c.hidden, 128);
+  if (rc) return rc;
+  rc = make_map_u8(&g1.map_x, ws + l.xq, l.capacity, c.hidden, l.block_m);
+  if (rc) return rc;
+  g1.w_scale = w1_scale;
+  g1.x_scale = reinterpret_cast<const float*>(ws + l.xs);
+  g1.sorted_ids = sorted_ids;
+  g1.block_expert = block_expert;
+  g1.num_blocks = num_blocks;
+  g1.out_q = ws + l.hq;
+  g1.out_scale = reinterpret_cast<float*>(ws + l.hs);
+  g1.status = status;
+  g1.k = c.hidden;
+  g1.out_dim = c.inter;
+  g1.rows_per_expert = 2 * c.inter;
+  g1.block_m = l.block_m;
+  g1.max_blocks = l.max_blocks;
+  g1.stages = grouped_gemm_pick_stages(true, l.block_m, c.hidden);
+  if (g1.stages < 2) return fail(AKLR_ERR_UNSUPPORTED_SHAPE, "hidden=%d needs more shared memory than one SM has", c.hidden);
+  rc = launch_grouped_gemm_gate_up(g1, sms, stream);
+  if (rc) return fail(rc, "gate_up grouped GEMM launch failed");
+
+  GroupedGemmParams g2{};
+  rc = make_map_u8(&g2.map_w, w2, static_cast<uint64_t>(experts) * c.hidden, c.inter, 128);
+  if (rc) return rc;
+  rc = make_map_u8(&g2.map_x, ws + l.hq, l.capacity, c.inter, l.block_m);
+  if (rc) return rc;
+  g2.w_scale = w2_scale;
+  g2.x_scale = reinterpret_cast<const float*>(ws + l.hs);
+  g2.sorted_ids = sorted_ids;
+  g2.block_expert = block_expert;
+  g2.num_blocks = num_blocks;
+  g2.topk_weights = topk_weights;
+  g2.out_rows = ws + l.rows;
+  g2.status = status;
+  g2.k = c.inter;
+  g2.out_dim = c.hidden;
+  g2.rows_per_expert = c.hidden;
+  g2.block_m = l.block_m;
+  g2.max_blocks = l.max_blocks;
+  g2.stages = grouped_gemm_pick_stages(false, l.block_m, c.inter);
+  if (g2.stages < 2) return fail(AKLR_ERR_UNSUPPORTED_SHAPE, "inter=%d needs more shared memory than one SM has", c.inter);
+  rc = launch_grouped_gemm_down(g2, sms, stream);
+  if (rc) return fail(rc, "down grouped GEMM launch failed");
+
+  CombineParams cp{};
+  cp.rows = ws + l.rows;
+  cp.topk_ids = topk_ids;
+  cp.expert_map = expert_map;
+  cp.out = out;
+  cp.n_tokens = c.n_tokens;
+  cp.hidden = c.hidden;
+  cp.routes_per_token = routes_per_token;
+  cp.n_experts_global = n_experts_global;
+  rc = launch_combine(cp, stream);
+  if (rc) return fail(rc, "combine launch failed");
+  return AKLR_OK;
+}
+
+int prepare(const aklr_moe_config* cfg, aklr_moe_workspace_layout* l, void* workspace, size_t workspace_bytes,
+            cudaStream_t stream) {
+  if (!cfg) return fail(AKLR_ERR_BAD_ARGUMENT, "cfg is NULL");
+  int rc = check_config(*cfg);
+  if (rc) return rc;
+  rc = check_device();
+  if (rc) return rc;
+  layout_of(*cfg, l);
+  if (!workspace || workspace_bytes < static_cast<size_t>(l->total_bytes))
+    return fail(AKLR_ERR_WORKSPACE_TOO_SMALL, "workspace holds %zu bytes, the call needs %lld", workspace_bytes,
+                static_cast<long long>(l->total_bytes));
+  if (reinterpret_cast<uintptr_t>(workspace) % 1024 != 0)
+    return fail(AKLR_ERR_BAD_ARGUMENT, "workspace must be 1024-byte aligned");
+  const cudaError_t err = cudaMemsetAsync(static_cast<uint8_t*>(workspace) + l->status, 0, 32, stream);
+  if (err != cudaSuccess) return cuda_fail(err, "clearing the status words");
+  return AKLR_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int aklr_abi_version(void) { return AKLR_B200_ABI_VERSION; }
+
+const char* aklr_status_string(int code) {
+  switch (code) {
+    case AKLR_OK: return "ok";
+    case AKLR_ERR_BAD_ARGUMENT: return "bad argument";
+    case AKLR_ERR_WORKSPACE_TOO_SMALL: return "workspace too small";
+    case AKLR_ERR_CUDA: return "CUDA runtime or driver error";
+    case AKLR_ERR_UNSUPPORTED_SHAPE: return "unsupported shape";
+    case AKLR_ERR_NO_DEVICE: return "no sm_100 device";
+    case AKLR_ERR_KERNEL_WAIT_TIMEOUT: return "a device-side wait gave up";
+    case AKLR_ERR_TOO_LARGE: return "problem too large";
+    default: return "unknown status";
+  }
+}
+
+const char* aklr_last_error(void) { return g_error; }
+
+int aklr_moe_fp8_workspace(const aklr_moe_config* cfg, aklr_moe_workspace_layout* layout) {
+  if (!cfg || !layout) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
+  const int rc = check_config(*cfg);
+  if (rc) return rc;
+  layout_of(*cfg, layout);
+  return AKLR_OK;
+}
+
+int aklr_moe_fp8_forward(const aklr_moe_config* cfg, const void* hidden_states, const void* logits,
+                         const void* bias, const float* sigmoid_table, const void* w1, const float* w1_scale,
+                         const void* w2, const float* w2_scale, void* out, void* workspace,
+                         size_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  aklr_moe_workspace_layout l;
+  int rc = prepare(cfg, &l, workspace, workspace_bytes, stream);
+  if (rc) return rc;
+  if (!hidden_states || !logits || !w1 || !w1_scale || !w2 || !w2_scale || !out)
+    return fail(AKLR_ERR_BAD_ARGUMENT, "NULL tensor argument");
+  if (cfg->n_tokens == 0) return AKLR_OK;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  int32_t* ids = reinterpret_cast<int32_t*>(ws + l.topk_ids);
+  float* weights = reinterpret_cast<float*>(ws + l.topk_weights);
+  rc = aklr_moe_route(cfg, logits, bias, sigmoid_table, ids, weights, stream_);
+  if (rc) return rc;
+  return run_experts(*cfg, l, hidden_states, ids, weights, nullptr, cfg->n_routed + cfg->n_shared, w1, w1_scale, w2,
+                     w2_scale, out, ws, stream);
+}
+
+int aklr_moe_fp8_experts(const aklr_moe_config* cfg, const void* hidden_states, const int32_t* topk_ids,
+                         const float* topk_weights, const int32_t* expert_map, const void* w1,
+                         const float* w1_scale, const void* w2, const float* w2_scale, void* out,
+                         void* workspace, size_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  aklr_moe_workspace_layout l;
+  int rc = prepare(cfg, &l, workspace, workspace_bytes, stream);
+  if (rc) return rc;
+  if (!hidden_states || !topk_ids || !topk_weights || !w1 || !w1_scale || !w2 || !w2_scale || !out)
+    return fail(AKLR_ERR_BAD_ARGUMENT, "NULL tensor argument");
+  if (cfg->n_tokens == 0) return AKLR_OK;
+  const int local = cfg->n_routed + cfg->n_shared;
+  const int global = expert_map ? cfg->n_experts_global : local;
+  if (expert_map && global < 1) return fail(AKLR_ERR_BAD_ARGUMENT, "n_experts_global must be set with an expert map");
+  return run_experts(*cfg, l, hidden_states, topk_ids, topk_weights, expert_map, global, w1, w1_scale, w2, w2_scale,
+                     out, static_cast<uint8_t*>(workspace), stream);
+}
+
+int aklr_moe_route(const aklr_moe_config* cfg, const void* logits, const void* bias, const float* sigmoid_table,
+                   int32_t* topk_ids, float* topk_weights, void* stream) {
+  if (!cfg || !logits || !topk_ids || !topk_weights) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
+  int rc = check_device();
+  if (rc) return rc;
+  aklr::RouteParams p{};
+  p.logits = logits;
+  p.bias = bias;
+  p.sigmoid_table = sigmoid_table;
+  p.topk_ids = topk_ids;
+  p.topk_weights = topk_weights;
+  p.n_tokens = cfg->n_tokens;
+  p.n_routed = cfg->n_routed;
+  p.n_shared = cfg->n_shared;
+  p.topk = cfg->topk;
+  p.scoring = cfg->scoring;
+  p.num_expert_group = cfg->num_expert_group < 1 ? 1 : cfg->num_expert_group;
+  p.topk_group = cfg->topk_group < 1 ? 1 : cfg->topk_group;
+  p.renormalize = cfg->renormalize;
+  p.logits_are_bf16 = cfg->logits_dtype == AKLR_DTYPE_BF16;
+  p.bias_is_bf16 = cfg->bias_dtype == AKLR_DTYPE_BF16;
+  p.routed_scaling_factor = cfg->routed_scaling_factor;
+  rc = aklr::launch_route(p, static_cast<cudaStream_t>(stream));
+  if (rc) return fail(rc, "routing: %s", aklr_status_string(rc));
+  return AKLR_OK;
+}
+
+int aklr_moe_align(const int32_t* topk_ids, const int32_t* expert_map, int32_t n_routes, int32_t n_experts,
+                   int32_t n_experts_global, int32_t block_m, int32_t* sorted_ids, int32_t* block_expert,
+                   int32_t* counts, int32_t* num_blocks, int32_t* chunk_scratch, void* stream) {
+  if (!topk_ids || !sorted_ids || !block_expert || !counts || !num_blocks || !chunk_scratch)
+    return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
+  int rc = check_device();
+  if (rc) return rc;
+  aklr::AlignParams p{};
+  p.topk_ids = topk_ids;
+  p.expert_map = expert_map;
+  p.sorted_ids = sorted_ids;
+  p.block_expert = block_expert;
+  p.counts = counts;
+  p.num_blocks = num_blocks;
+  p.chunk_hist = chunk_scratch;
+  p.n_routes = n_routes;
+  p.n_experts = n_experts;
+  p.n_experts_global = expert_map ? n_experts_global : n_experts;
+  p.block_m = block_m;
+  rc = aklr::launch_align(p, static_cast<cudaStream_t>(stream));
+  if (rc) return fail(rc, "moe_align: %s", aklr_status_string(rc));
+  return AKLR_OK;
+}
+
+int64_t aklr_moe_align_max_blocks(int64_t n_routes, int64_t n_experts, int64_t block_m) {
+  return aklr::align_max_blocks(n_routes, n_experts, block_m);
+}
+
+int aklr_router_gemm_bf16(const void* x, const void* w, void* logits, int32_t n_tokens, int32_t hidden,
+                          int32_t n_routed, void* stream) {
+  if (!x || !w || !logits) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
+  int rc = check_device();
+  if (rc) return rc;
+  rc = aklr::launch_router_gemm(x, w, logits, n_tokens, hidden, n_routed, static_cast<cudaStream_t>(stream));
+  if (rc) return fail(rc, "router GEMM: %s", aklr_status_string(rc));
+  return AKLR_OK;
+}
+
+int aklr_per_group_quant_fp8(const void* x, void* q, float* scales, int32_t rows, int32_t hidden, void* stream) {
+  if (!x || !q || !scales) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
+  int rc = check_device();
+  if (rc) return rc;
+  rc = aklr::launch_per_group_quant_fp8(x, static_cast<uint8_t*>(q), scales, rows, hidden,
+                                        static_cast<cudaStream_t>(stream));
+  if (rc) return fail(rc, "per_group_quant_fp8: %s", aklr_status_string(rc));
+  return AKLR_OK;
+}
+
+int aklr_per_group_quant_mxfp8(const void* x, void* q, uint8_t* scales, int32_t rows, int32_t hidden,
+                               void* stream) {
+  if (!x || !q || !scales) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
+  int rc = check_device();
+  if (rc) return rc;
+  rc = aklr::launch_per_group_quant_mxfp8(x, static_cast<uint8_t*>(q), scales, rows, hidden,
+                                          static_cast<cudaStream_t>(stream));
+  if (rc) return fail(rc, "per_group_quant_mxfp8: %s", aklr_status_string(rc));
+  return AKLR_OK;
+}
+
+int aklr_moe_act_quant_fp8(const void* x, void* q, float* scales, int32_t rows, int32_t hidden, void* stream) {
+  if (!x || !q || !scales) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
+  int rc = check_device();
+  if (rc) return rc;
+  aklr::GatherQuantParams p{};
+  p.x = x;
+  p.q = static_cast<uint8_t*>(q);
+  p.scales = scales;
+  p.n_rows = rows;
+  p.hidden = hidden;
+  p.routes_per_token = 1;
+  rc = aklr::launch_gather_quant_fp8(p, static_cast<cudaStream_t>(stream));
+  if (rc) return fail(rc, "activation quant: %s", aklr_status_string(rc));
+  return AKLR_OK;
+}
+
+int aklr_moe_read_status(const void* workspace, int32_t* host_status, void* stream_) {
+  if (!workspace || !host_status) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  cudaError_t err = cudaMemcpyAsync(host_status, workspace, 8, cudaMemcpyDeviceToHost, stream);
+  if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
+  if (err != cudaSuccess) return cuda_fail(err, "reading the status words");
+  return host_status[0] == 0 ? AKLR_OK : fail(host_status[0], "device wait gave up at location %d", host_status[1]);
+}
+
+}  // extern "C"

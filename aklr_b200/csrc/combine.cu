@@ -1,0 +1,117 @@
+// Top-k weighted combine (unpermute) and the router projection, sm_100a.
+//
+// combine: out[t] = bf16( sum over the token's routes of its per-route row ), summed in float32
+// in slot order; the rows already carry the route weight (the down projection applies it).
+// Routes to experts this rank does not hold add nothing, as in the reference's expert_mask /
+// expert_offset statements (aklr/ops/fused_moe/reference.py:78-84).  HBM-bound: 16-byte loads.
+//
+// router: logits = bf16( x @ W^T ) with float32 accumulation, the rounding point of the
+// reference's _router_logits (aklr/plugins/sglang/models/qwen3_moe/reference.py:24-31).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace aklr {
+
+__global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
+  const int vec_per_row = p.hidden >> 3;  // 8 bf16 per 16-byte vector
+  const int64_t total = static_cast<int64_t>(p.n_tokens) * vec_per_row;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int token = static_cast<int>(i / vec_per_row);
+    const int v = static_cast<int>(i - static_cast<int64_t>(token) * vec_per_row);
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int s = 0; s < p.routes_per_token; ++s) {
+      const int route = token * p.routes_per_token + s;
+      int e = p.topk_ids[route];
+      if (e < 0 || e >= p.n_experts_global) continue;
+      if (p.expert_map && p.expert_map[e] < 0) continue;
+      const uint4 raw = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.rows) +
+                                                        static_cast<size_t>(route) * p.hidden + v * 8);
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        acc[2 * q] += __uint_as_float(w[q] << 16);
+        acc[2 * q + 1] += __uint_as_float(w[q] & 0xFFFF0000u);
+      }
+    }
+    uint4 packed;
+    uint32_t* o = reinterpret_cast<uint32_t*>(&packed);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const __nv_bfloat162 two = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+      o[q] = *reinterpret_cast<const uint32_t*>(&two);
+    }
+    *reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + static_cast<size_t>(token) * p.hidden + v * 8) = packed;
+  }
+}
+
+int launch_combine(const CombineParams& p, cudaStream_t stream) {
+  if (p.hidden % 8 != 0) return AKLR_ERR_UNSUPPORTED_SHAPE;
+  if (p.n_tokens == 0) return AKLR_OK;
+  const int64_t total = static_cast<int64_t>(p.n_tokens) * (p.hidden / 8);
+  const int64_t blocks = (total + 255) / 256;
+  const int grid = static_cast<int>(blocks < 148 * 8 ? blocks : 148 * 8);
+  combine_kernel<<<grid, 256, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+}
+
+// One warp per (token, 8 experts): lanes stride the hidden dimension with 16-byte loads.
+constexpr int kRouterExperts = 8;
+__global__ void __launch_bounds__(256)
+router_gemm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w, uint16_t* __restrict__ logits,
+                   int n_tokens, int hidden, int n_routed) {
+  const int lane = threadIdx.x & 31;
+  const int groups = (n_routed + kRouterExperts - 1) / kRouterExperts;
+  const int64_t item = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= static_cast<int64_t>(n_tokens) * groups) return;
+  const int token = static_cast<int>(item / groups);
+  const int e0 = static_cast<int>(item - static_cast<int64_t>(token) * groups) * kRouterExperts;
+  float acc[kRouterExperts];
+#pragma unroll
+  for (int j = 0; j < kRouterExperts; ++j) acc[j] = 0.0f;
+  for (int h = lane * 8; h < hidden; h += 256) {
+    const uint4 xr = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(token) * hidden + h);
+    const uint32_t xw[4] = {xr.x, xr.y, xr.z, xr.w};
+#pragma unroll
+    for (int j = 0; j < kRouterExperts; ++j) {
+      if (e0 + j < n_routed) {
+        const uint4 wr = *reinterpret_cast<const uint4*>(w + static_cast<size_t>(e0 + j) * hidden + h);
+        const uint32_t ww[4] = {wr.x, wr.y, wr.z, wr.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          acc[j] = fmaf(__uint_as_float(xw[q] << 16), __uint_as_float(ww[q] << 16), acc[j]);
+          acc[j] = fmaf(__uint_as_float(xw[q] & 0xFFFF0000u), __uint_as_float(ww[q] & 0xFFFF0000u), acc[j]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kRouterExperts; ++j) {
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) acc[j] += __shfl_xor_sync(0xFFFFFFFFu, acc[j], off);
+  }
+  if (lane < kRouterExperts && e0 + lane < n_routed) {
+    float v = acc[0];
+#pragma unroll
+    for (int j = 1; j < kRouterExperts; ++j)
+      if (lane == j) v = acc[j];
+    const __nv_bfloat16 r = __float2bfloat16_rn(v);
+    logits[static_cast<size_t>(token) * n_routed + e0 + lane] = *reinterpret_cast<const uint16_t*>(&r);
+  }
+}
+
+int launch_router_gemm(const void* x, const void* w, void* logits, int n_tokens, int hidden, int n_routed,
+                       cudaStream_t stream) {
+  if (hidden % 8 != 0) return AKLR_ERR_UNSUPPORTED_SHAPE;
+  if (n_tokens == 0) return AKLR_OK;
+  const int groups = (n_routed + kRouterExperts - 1) / kRouterExperts;
+  const int64_t items = static_cast<int64_t>(n_tokens) * groups;
+  const int64_t blocks = (items + 7) / 8;
+  if (blocks > 0x7FFFFFFF) return AKLR_ERR_TOO_LARGE;
+  router_gemm_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
+      static_cast<const uint16_t*>(x), static_cast<const uint16_t*>(w), static_cast<uint16_t*>(logits), n_tokens,
+      hidden, n_routed);
+  return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+}
+
+}  // namespace aklr

@@ -1,0 +1,343 @@
+// Grouped FP8 GEMMs of the fused-MoE layer on tcgen05 (sm_100a): gate_up (+ SiLU*mul + 1x128
+// FP8 requant) and down (+ route weight), both with 128x128 weight block scales and 1x128
+// activation scales applied in float32 exactly where the reference's dequantised matmul has them
+// (aklr/plugins/sglang/models/deepseek_v2/reference.py:146-183,
+//  aklr/plugins/sglang/models/qwen3_moe/reference.py:57-88).
+//
+// Orientation ("swap-AB"): the WEIGHT tile is the MMA's M side (128 output channels = 128 TMEM
+// lanes), the block's tokens are the N side (block_m = 16..128 columns).  A decode batch with a
+// handful of rows per expert therefore streams each weight byte from HBM exactly once and spends
+// tensor work only on 16 token columns, and a weight block scale is one scalar per (tile, K-block)
+// while the activation scale varies along the columns.
+//
+// Per K-block of 128 the MMA warp issues 4 (x2 for gate and up) tcgen05.mma of K=32 into one of
+// two TMEM partial buffers; the epilogue warps drain the partial with tcgen05.ld and fold it into
+// float32 register accumulators times (weight scale x activation scale) -- the tensor core has no
+// 128-granular float scale input.  Persistent CTAs (one per SM) walk the (block, channel-tile)
+// list; TMA (SWIZZLE_128B) feeds a ring of shared-memory stages.  No cluster, no multicast.
+//
+// Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..9
+// epilogue (TMEM lane quarter = warp % 4, column half = (warp-2)/4).
+#include <cfloat>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace aklr {
+
+constexpr int kGemmThreads = 320;
+constexpr int kEpiThreads = 256;
+constexpr int kWTileBytes = 128 * 128;  // 128 channels x 128 K bytes
+
+struct GemmSmemLayout {
+  int stage_bytes, misc_bytes, total_bytes;
+  int off_misc, off_rid, off_wmax, off_bars;
+};
+
+__host__ __device__ inline GemmSmemLayout gemm_layout(bool gate_up, int block_m, int k, int stages) {
+  GemmSmemLayout l;
+  const int kb = k / 128;
+  l.stage_bytes = (gate_up ? 2 : 1) * kWTileBytes + block_m * 128;
+  const int scale_bytes = kb * block_m * 4;
+  const int out_bytes = block_m * 128 * (gate_up ? 1 : 2);
+  l.misc_bytes = ((scale_bytes > out_bytes ? scale_bytes : out_bytes) + 127) & ~127;
+  l.off_misc = stages * l.stage_bytes;
+  l.off_rid = l.off_misc + l.misc_bytes;       // int[block_m]
+  l.off_wmax = l.off_rid + block_m * 4;        // float[4][block_m]
+  l.off_bars = l.off_wmax + 4 * block_m * 4;   // barriers, tmem ptr, abort flag
+  l.total_bytes = l.off_bars + (2 * stages + 4) * 8 + 16;
+  return l;
+}
+
+size_t grouped_gemm_smem_bytes(bool gate_up, int block_m, int k, int stages) {
+  return static_cast<size_t>(gemm_layout(gate_up, block_m, k, stages).total_bytes) + 1024;  // alignment slack
+}
+
+int grouped_gemm_pick_stages(bool gate_up, int block_m, int k) {
+  for (int s = 8; s >= 2; --s)
+    if (grouped_gemm_smem_bytes(gate_up, block_m, k, s) <= 227 * 1024) return s;
+  return 0;
+}
+
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ bool epi_bar_any(int flag) {
+  uint32_t any;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.or.pred p, 1, 256, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(any)
+      : "r"(flag)
+      : "memory");
+  return any != 0;
+}
+
+template <int BM, bool GATE_UP>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
+  constexpr int NH = BM / 2;                        // columns per epilogue warp
+  constexpr int CH = NH >= 16 ? 16 : 8;             // columns per tcgen05.ld
+  constexpr int BUF_COLS = (GATE_UP ? 2 : 1) * BM;  // TMEM columns of one partial buffer
+  constexpr int TMEM_COLS = 2 * BUF_COLS < 32 ? 32 : 2 * BUF_COLS;
+  constexpr uint32_t IDESC = umma_idesc_e4m3(BM);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int KB = p.k >> 7;
+  const int S = p.stages;
+  const GemmSmemLayout L = gemm_layout(GATE_UP, BM, p.k, S);
+  float* sx = reinterpret_cast<float*>(smem + L.off_misc);  // [KB][BM] activation scales ...
+  uint8_t* out_tile = smem + L.off_misc;                    // ... aliased by the output tile
+  int* rid_s = reinterpret_cast<int*>(smem + L.off_rid);
+  float* wmax = reinterpret_cast<float*>(smem + L.off_wmax);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.off_bars);
+  uint64_t* empty = full + S;
+  uint64_t* tmem_full = empty + S;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int nb = *p.num_blocks;
+  if (nb > p.max_blocks) nb = p.max_blocks;
+  const int tiles_per_block = p.out_dim >> 7;
+  const int total_tiles = nb * tiles_per_block;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], kEpiThreads / 32);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&p.map_w);
+    tma_prefetch_desc(&p.map_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_ptr, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer ------------------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int j = t / nb, b = t - j * nb;
+        const int e = p.block_expert[b];
+        const int w_row = e * p.rows_per_expert + j * 128;
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
+          uint8_t* st = smem + s * L.stage_bytes;
+          mbar_expect_tx(&full[s], L.stage_bytes);
+          tma_load_2d(st, &p.map_w, &full[s], kb * 128, w_row);
+          if (GATE_UP) tma_load_2d(st + kWTileBytes, &p.map_w, &full[s], kb * 128, w_row + p.out_dim);
+          tma_load_2d(st + (GATE_UP ? 2 : 1) * kWTileBytes, &p.map_x, &full[s], kb * 128, b * BM);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer --------------------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          const int buf = it & 1;
+          const uint32_t bph = (it >> 1) & 1;
+          if (!mbar_wait(&full[s], ph, abort_flag, p.status, 2)) { ok = false; break; }
+          if (!mbar_wait(&tmem_empty[buf], bph ^ 1, abort_flag, p.status, 3)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a0 = smem_u32(smem + s * L.stage_bytes);
+          const uint64_t da0 = umma_desc_sw128(a0);
+          const uint64_t da1 = umma_desc_sw128(a0 + kWTileBytes);
+          const uint64_t db = umma_desc_sw128(a0 + (GATE_UP ? 2 : 1) * kWTileBytes);
+          const uint32_t d = tmem_base + buf * BUF_COLS;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {  // 32 K bytes per MMA: the descriptor start moves 32 B
+            umma_f8f6f4(d, da0 + 2 * k, db + 2 * k, IDESC, k > 0);
+            if (GATE_UP) umma_f8f6f4(d + BM, da1 + 2 * k, db + 2 * k, IDESC, k > 0);
+          }
+          tc_commit(&empty[s]);         // the stage is free once these MMAs have read it
+          tc_commit(&tmem_full[buf]);   // and the partial is complete
+        }
+      }
+    }
+  } else {
+    // ------------------------------- epilogue warps ----------------------------------------
+    const int ew = warp - 2;
+    const int quarter = warp & 3;            // TMEM lanes this warp may read
+    const int half = ew >> 2;                // which half of the columns
+    const int et = threadIdx.x - 64;         // 0..255
+    const int chan = quarter * 32 + lane;    // output channel inside the tile = TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const int IB = p.out_dim >> 7;           // gate_up: 128-blocks of the intermediate size
+    uint32_t it = 0;
+    bool bad = false;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      if (epi_bar_any(*abort_flag)) break;   // also fences the aliased smem against the last tile
+      const int j = t / nb, b = t - j * nb;
+      const int e = p.block_expert[b];
+      for (int i = et; i < BM * KB; i += kEpiThreads) {
+        const int n = i / KB, kb = i - n * KB;
+        sx[kb * BM + n] = p.x_scale[static_cast<size_t>(b * BM + n) * KB + kb];
+      }
+      if (et < BM) rid_s[et] = p.sorted_ids[b * BM + et];
+      epi_bar_sync();
+
+      float acc0[NH], acc1[GATE_UP ? NH : 1];
+#pragma unroll
+      for (int i = 0; i < NH; ++i) acc0[i] = 0.0f;
+      if (GATE_UP) {
+#pragma unroll
+        for (int i = 0; i < NH; ++i) acc1[i] = 0.0f;
+      }
+      const float* ws0 = p.w_scale + (static_cast<size_t>(e) * (p.rows_per_expert >> 7) + j) * KB;
+      const float* ws1 = ws0 + static_cast<size_t>(IB) * KB;  // the up rows' blocks (gate_up only)
+
+      for (int kb = 0; kb < KB; ++kb, ++it) {
+        const int buf = it & 1;
+        const uint32_t bph = (it >> 1) & 1;
+        if (!mbar_wait(&tmem_full[buf], bph, abort_flag, p.status, 4)) bad = true;
+        tc_fence_after_sync();
+        const float sw0 = __ldg(ws0 + kb);
+        const float sw1 = GATE_UP ? __ldg(ws1 + kb) : 0.0f;
+        const float* sxk = sx + kb * BM + half * NH;
+        const uint32_t t0 = tmem_base + lane_addr + buf * BUF_COLS + half * NH;
+#pragma unroll
+        for (int c = 0; c < NH; c += CH) {
+          uint32_t r0[CH], r1[CH];
+          if (CH == 16) {
+            AKLR_TMEM_LD_16(t0 + c, r0);
+            if (GATE_UP) AKLR_TMEM_LD_16(t0 + BM + c, r1);
+          } else {
+            AKLR_TMEM_LD_8(t0 + c, r0);
+            if (GATE_UP) AKLR_TMEM_LD_8(t0 + BM + c, r1);
+          }
+          tc_wait_ld();
+          if (c + CH >= NH) {  // last chunk read: hand the buffer back to the MMA warp
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+          }
+#pragma unroll
+          for (int i = 0; i < CH; i += 4) {
+            const float4 s4 = *reinterpret_cast<const float4*>(sxk + c + i);
+            const float s[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              acc0[c + i + q] = fmaf(__uint_as_float(r0[i + q]), s[q] * sw0, acc0[c + i + q]);
+              if (GATE_UP) acc1[c + i + q] = fmaf(__uint_as_float(r1[i + q]), s[q] * sw1, acc1[c + i + q]);
+            }
+          }
+        }
+      }
+
+      epi_bar_sync();  // every warp is done with the activation scales: the region becomes the out tile
+      if (GATE_UP) {
+        // h = silu(gate) * up, rounded to bf16; then 1 x 128 requant over this tile's 128 channels
+#pragma unroll
+        for (int i = 0; i < NH; ++i) {
+          const float g = acc0[i];
+          const float h = __fdiv_rn(g, 1.0f + __expf(-g)) * acc1[i];
+          acc0[i] = __bfloat162float(__float2bfloat16_rn(h));
+          const float m = warp_max_nonneg(fabsf(acc0[i]));
+          if (lane == 0) wmax[quarter * BM + half * NH + i] = m;
+        }
+        epi_bar_sync();
+#pragma unroll
+        for (int i = 0; i < NH; ++i) {
+          const int n = half * NH + i;
+          const float m = fmaxf(fmaxf(wmax[n], wmax[BM + n]), fmaxf(wmax[2 * BM + n], wmax[3 * BM + n]));
+          const float scale = fmaxf(__fdiv_rn(m, 448.0f), FLT_MIN);
+          out_tile[n * 128 + chan] = static_cast<uint8_t>(
+              __nv_cvt_float_to_fp8(__fdiv_rn(acc0[i], scale), __NV_SATFINITE, __NV_E4M3));
+          if (chan == 0 && rid_s[n] >= 0 && !bad)
+            p.out_scale[static_cast<size_t>(b * BM + n) * IB + j] = scale;
+        }
+        epi_bar_sync();
+        for (int i = et; i < BM * 8; i += kEpiThreads) {  // 16 bytes per thread, 8 per row
+          const int n = i >> 3, seg = i & 7;
+          if (rid_s[n] >= 0 && !bad)
+            *reinterpret_cast<uint4*>(p.out_q + static_cast<size_t>(b * BM + n) * p.out_dim + j * 128 + seg * 16) =
+                *reinterpret_cast<const uint4*>(out_tile + n * 128 + seg * 16);
+        }
+      } else {
+        __nv_bfloat16* out16 = reinterpret_cast<__nv_bfloat16*>(out_tile);
+#pragma unroll
+        for (int i = 0; i < NH; ++i) {
+          const int n = half * NH + i;
+          const int rid = rid_s[n];
+          const float w = rid >= 0 ? __ldg(p.topk_weights + rid) : 0.0f;
+          out16[n * 128 + chan] = __float2bfloat16_rn(acc0[i] * w);
+        }
+        epi_bar_sync();
+        for (int i = et; i < BM * 16; i += kEpiThreads) {  // 16 bytes per thread, 16 per row
+          const int n = i >> 4, seg = i & 15;
+          const int rid = rid_s[n];
+          if (rid >= 0 && !bad)
+            *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out_rows) +
+                                      (static_cast<size_t>(rid) * p.out_dim + j * 128) * 2 + seg * 16) =
+                *reinterpret_cast<const uint4*>(out_tile + n * 256 + seg * 16);
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {  // a wait gave up: let copies in flight land before shared memory is released
+    const uint64_t start = global_timer_ns();
+    while (global_timer_ns() - start < 200000ull) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <bool GATE_UP>
+static int launch_grouped(const GroupedGemmParams& p, int sm_count, cudaStream_t stream) {
+  if (p.k % 128 != 0 || p.out_dim % 128 != 0 || p.max_blocks < 1) return AKLR_ERR_UNSUPPORTED_SHAPE;
+  if (p.stages < 2) return AKLR_ERR_UNSUPPORTED_SHAPE;
+  const size_t smem = grouped_gemm_smem_bytes(GATE_UP, p.block_m, p.k, p.stages);
+  if (smem > 227 * 1024) return AKLR_ERR_UNSUPPORTED_SHAPE;
+  const long long tiles = static_cast<long long>(p.max_blocks) * (p.out_dim / 128);
+  const int grid = static_cast<int>(tiles < sm_count ? tiles : sm_count);
+  auto run = [&](auto kernel) {
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (err != cudaSuccess) return AKLR_ERR_CUDA;
+    kernel<<<grid, kGemmThreads, smem, stream>>>(p);
+    return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+  };
+  switch (p.block_m) {
+    case 16: return run(grouped_gemm_kernel<16, GATE_UP>);
+    case 32: return run(grouped_gemm_kernel<32, GATE_UP>);
+    case 64: return run(grouped_gemm_kernel<64, GATE_UP>);
+    case 128: return run(grouped_gemm_kernel<128, GATE_UP>);
+    default: return AKLR_ERR_UNSUPPORTED_SHAPE;
+  }
+}
+
+int launch_grouped_gemm_gate_up(const GroupedGemmParams& p, int sm_count, cudaStream_t stream) {
+  return launch_grouped<true>(p, sm_count, stream);
+}
+int launch_grouped_gemm_down(const GroupedGemmParams& p, int sm_count, cudaStream_t stream) {
+  return launch_grouped<false>(p, sm_count, stream);
+}
+
+}  // namespace aklr

@@ -1,0 +1,97 @@
+// Internal launch interface between the kernel files and the C ABI (abi.cu).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define AKLR_SCORING_SOFTMAX 0
+#define AKLR_SCORING_SIGMOID 1
+
+namespace aklr {
+
+struct RouteParams {
+  const void* logits;          // [n_tokens, n_routed] bf16 or f32
+  const void* bias;            // [n_routed] bf16 or f32, or null
+  const float* sigmoid_table;  // 65536 floats indexed by bf16 bits, or null
+  int32_t* topk_ids;           // [n_tokens, topk + n_shared]
+  float* topk_weights;         // [n_tokens, topk + n_shared]
+  int n_tokens, n_routed, n_shared, topk;
+  int scoring, num_expert_group, topk_group, renormalize;
+  int logits_are_bf16, bias_is_bf16;
+  float routed_scaling_factor;
+};
+int launch_route(const RouteParams& p, cudaStream_t stream);
+
+struct AlignParams {
+  const int32_t* topk_ids;    // [n_routes] global expert ids (negative: dropped)
+  const int32_t* expert_map;  // [n_experts_global] -> local id or -1, or null (identity)
+  int32_t* sorted_ids;        // [capacity] route ids, -1 in padding
+  int32_t* block_expert;      // [max_blocks]
+  int32_t* counts;            // [n_experts]
+  int32_t* num_blocks;        // [2]: blocks used, rows used (= blocks * block_m)
+  int32_t* chunk_hist;        // [ceil(n_routes/1024) * n_experts] scratch
+  int n_routes, n_experts, n_experts_global, block_m;
+};
+int launch_align(const AlignParams& p, cudaStream_t stream);
+
+// rows of the sorted table an align call can use at most
+inline int64_t align_max_blocks(int64_t n_routes, int64_t n_experts, int64_t block_m) {
+  const int64_t nonempty = n_routes < n_experts ? n_routes : n_experts;
+  return n_routes / block_m + nonempty;
+}
+
+struct GatherQuantParams {
+  const void* x;              // [n_tokens, hidden] bf16
+  const int32_t* sorted_ids;  // [capacity] or null: row r reads token r
+  const int32_t* num_rows;    // device count of rows in use (null: n_rows)
+  uint8_t* q;                 // [rows, hidden] e4m3
+  float* scales;              // [rows, hidden/128]
+  int n_rows, hidden, routes_per_token;
+};
+int launch_gather_quant_fp8(const GatherQuantParams& p, cudaStream_t stream);
+
+// standalone quant ops
+int launch_per_group_quant_fp8(const void* x_bf16, uint8_t* q, float* scales_group_major, int rows, int hidden,
+                               cudaStream_t stream);
+int launch_per_group_quant_mxfp8(const void* x_bf16, uint8_t* q, uint8_t* scales_e8m0, int rows, int hidden,
+                                 cudaStream_t stream);
+
+struct GroupedGemmParams {
+  CUtensorMap map_w;   // weights flattened to [experts*rows_per_expert, k], box 128 x 128
+  CUtensorMap map_x;   // activations [capacity, k] e4m3, box block_m x 128
+  const float* w_scale;        // [experts, rows_per_expert/128, k/128]
+  const float* x_scale;        // [capacity, k/128]
+  const int32_t* sorted_ids;   // [capacity]
+  const int32_t* block_expert; // [max_blocks]
+  const int32_t* num_blocks;   // device count
+  const float* topk_weights;   // [n_routes] (down projection only)
+  uint8_t* out_q;              // gate_up: [capacity, inter] e4m3
+  float* out_scale;            // gate_up: [capacity, inter/128]
+  void* out_rows;              // down: [n_routes, hidden] bf16 per-route contributions
+  int32_t* status;             // [2] error word + location
+  int k;                       // reduction length (hidden for gate_up, inter for down)
+  int out_dim;                 // inter (gate_up) or hidden (down)
+  int rows_per_expert;         // 2*inter (gate_up) or hidden (down)
+  int block_m;                 // tokens per block: 16, 32, 64 or 128
+  int max_blocks;              // upper bound used to size the tile loop
+  int stages;
+};
+int launch_grouped_gemm_gate_up(const GroupedGemmParams& p, int sm_count, cudaStream_t stream);
+int launch_grouped_gemm_down(const GroupedGemmParams& p, int sm_count, cudaStream_t stream);
+size_t grouped_gemm_smem_bytes(bool gate_up, int block_m, int k, int stages);
+int grouped_gemm_pick_stages(bool gate_up, int block_m, int k);
+
+struct CombineParams {
+  const void* rows;          // [n_tokens * routes_per_token, hidden] bf16
+  const int32_t* topk_ids;   // [n_tokens, routes_per_token] global ids
+  const int32_t* expert_map; // null or global -> local (-1: not here, the route adds nothing)
+  void* out;                 // [n_tokens, hidden] bf16
+  int n_tokens, hidden, routes_per_token, n_experts_global;
+};
+int launch_combine(const CombineParams& p, cudaStream_t stream);
+
+int launch_router_gemm(const void* x_bf16, const void* w_bf16, void* logits_bf16, int n_tokens, int hidden,
+                       int n_routed, cudaStream_t stream);
+
+}  // namespace aklr

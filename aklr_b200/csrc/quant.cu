@@ -1,0 +1,159 @@
+// Per-token-group FP8 activation quantisation, sm_100a.  All three kernels are HBM-bound
+// element-wise passes: 16-byte loads (8 bf16 per lane), shuffle reductions inside the lanes of
+// one group, 8-byte stores.
+//
+//  * gather_quant_fp8: the MoE layer's scheme -- scale = max(amax/448, FLT_MIN), code =
+//    e4m3(x / scale), both true divisions, as the reference's _fp8_input does
+//    (aklr/plugins/sglang/models/qwen3_moe/reference.py:44-54); rows are gathered through the
+//    sorted route table so the grouped GEMM reads expert-contiguous rows.
+//  * per_group_quant_fp8: the standalone op -- scale = max(amax,1e-10)*(1/448), code =
+//    e4m3(clamp(x * (1/scale))), scales stored group-major (aklr/ops/quant/reference.py:9-28).
+//  * per_group_quant_mxfp8: 1 x 32 groups, power-of-two scale rounded up, e8m0 exponent bytes
+//    (aklr/ops/quant/reference.py:31-48).
+#include <cfloat>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace aklr {
+
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&v)[8]) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+
+__device__ __forceinline__ float amax8(const float (&v)[8]) {
+  float m = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[i]));
+  return m;
+}
+
+__device__ __forceinline__ uint2 pack8_e4m3(const float (&v)[8]) {
+  uint2 out;
+  out.x = cvt_e4m3x2(v[0], v[1]) | (static_cast<uint32_t>(cvt_e4m3x2(v[2], v[3])) << 16);
+  out.y = cvt_e4m3x2(v[4], v[5]) | (static_cast<uint32_t>(cvt_e4m3x2(v[6], v[7])) << 16);
+  return out;
+}
+
+// One half-warp (16 lanes x 8 values) per 1 x 128 group.
+__global__ void __launch_bounds__(256) gather_quant_fp8_kernel(GatherQuantParams p) {
+  const int groups_per_row = p.hidden >> 7;
+  const int n_rows = p.num_rows ? min(*p.num_rows, p.n_rows) : p.n_rows;
+  const int64_t total = static_cast<int64_t>(n_rows) * groups_per_row;
+  const int sub = threadIdx.x & 15;
+  const uint32_t group_mask = 0xFFFFu << (threadIdx.x & 16);  // the lanes of this half-warp
+  const int64_t half_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 4;
+  for (int64_t g = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4; g < total;
+       g += half_warps) {
+    const int row = static_cast<int>(g / groups_per_row);
+    const int grp = static_cast<int>(g - static_cast<int64_t>(row) * groups_per_row);
+    int token = row;
+    if (p.sorted_ids) {
+      const int rid = p.sorted_ids[row];
+      token = rid < 0 ? -1 : rid / p.routes_per_token;
+    }
+    if (token < 0) continue;  // padding rows are never read back
+    const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.x) +
+                                                      static_cast<size_t>(token) * p.hidden + grp * 128 + sub * 8);
+    float v[8];
+    unpack8(raw, v);
+    float m = amax8(v);
+#pragma unroll
+    for (int off = 8; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(group_mask, m, off, 16));
+    const float scale = fmaxf(__fdiv_rn(m, 448.0f), FLT_MIN);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __fdiv_rn(v[i], scale);
+    *reinterpret_cast<uint2*>(p.q + static_cast<size_t>(row) * p.hidden + grp * 128 + sub * 8) = pack8_e4m3(v);
+    if (sub == 0) p.scales[static_cast<size_t>(row) * groups_per_row + grp] = scale;
+  }
+}
+
+int launch_gather_quant_fp8(const GatherQuantParams& p, cudaStream_t stream) {
+  if (p.hidden % 128 != 0) return AKLR_ERR_UNSUPPORTED_SHAPE;
+  if (p.n_rows == 0) return AKLR_OK;
+  const int64_t groups = static_cast<int64_t>(p.n_rows) * (p.hidden / 128);
+  const int64_t blocks = (groups * 16 + 255) / 256;
+  const int grid = static_cast<int>(blocks < 148 * 16 ? blocks : 148 * 16);
+  gather_quant_fp8_kernel<<<grid, 256, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+}
+
+__global__ void __launch_bounds__(256)
+per_group_quant_fp8_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ q,
+                           float* __restrict__ scales, int rows, int hidden) {
+  const int groups_per_row = hidden >> 7;
+  const int64_t total = static_cast<int64_t>(rows) * groups_per_row;
+  const int sub = threadIdx.x & 15;
+  const uint32_t group_mask = 0xFFFFu << (threadIdx.x & 16);  // the lanes of this half-warp
+  const int64_t half_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 4;
+  for (int64_t g = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4; g < total;
+       g += half_warps) {
+    const int row = static_cast<int>(g / groups_per_row);
+    const int grp = static_cast<int>(g - static_cast<int64_t>(row) * groups_per_row);
+    const size_t at = static_cast<size_t>(row) * hidden + grp * 128 + sub * 8;
+    float v[8];
+    unpack8(*reinterpret_cast<const uint4*>(x + at), v);
+    float m = amax8(v);
+#pragma unroll
+    for (int off = 8; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(group_mask, m, off, 16));
+    const float scale = __fmul_rn(fmaxf(m, 1e-10f), 1.0f / 448.0f);
+    const float recip = __fdiv_rn(1.0f, scale);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = fminf(fmaxf(__fmul_rn(v[i], recip), -448.0f), 448.0f);
+    *reinterpret_cast<uint2*>(q + at) = pack8_e4m3(v);
+    if (sub == 0) scales[static_cast<size_t>(grp) * rows + row] = scale;
+  }
+}
+
+int launch_per_group_quant_fp8(const void* x, uint8_t* q, float* scales, int rows, int hidden,
+                               cudaStream_t stream) {
+  if (hidden % 128 != 0) return AKLR_ERR_UNSUPPORTED_SHAPE;
+  if (rows == 0) return AKLR_OK;
+  const int64_t groups = static_cast<int64_t>(rows) * (hidden / 128);
+  const int64_t blocks = (groups * 16 + 255) / 256;
+  const int grid = static_cast<int>(blocks < 148 * 16 ? blocks : 148 * 16);
+  per_group_quant_fp8_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), q, scales, rows, hidden);
+  return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+}
+
+// Four lanes x 8 values per 1 x 32 group.
+__global__ void __launch_bounds__(256)
+per_group_quant_mxfp8_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ q,
+                             uint8_t* __restrict__ scales, int64_t elements) {
+  const int64_t slots = elements >> 3;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const uint32_t group_mask = 0xFu << (threadIdx.x & 28);  // the four lanes of this group
+  // the four lanes of a group run the same number of iterations: slots is a multiple of 4
+  for (int64_t slot = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; slot < slots; slot += stride) {
+    float v[8];
+    unpack8(*reinterpret_cast<const uint4*>(x + slot * 8), v);
+    float m = amax8(v);
+    m = fmaxf(m, __shfl_xor_sync(group_mask, m, 2, 4));
+    m = fmaxf(m, __shfl_xor_sync(group_mask, m, 1, 4));
+    const uint32_t raw = __float_as_uint(__fmul_rn(fmaxf(m, 1e-10f), 1.0f / 448.0f));
+    const uint32_t exponent = (raw >> 23) + ((raw & 0x7FFFFFu) != 0u ? 1u : 0u);
+    const float scale = __uint_as_float(exponent << 23);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = fminf(fmaxf(__fdiv_rn(v[i], scale), -448.0f), 448.0f);
+    *reinterpret_cast<uint2*>(q + slot * 8) = pack8_e4m3(v);
+    if ((slot & 3) == 0) scales[slot >> 2] = static_cast<uint8_t>(exponent);
+  }
+}
+
+int launch_per_group_quant_mxfp8(const void* x, uint8_t* q, uint8_t* scales, int rows, int hidden,
+                                 cudaStream_t stream) {
+  if (hidden % 32 != 0) return AKLR_ERR_UNSUPPORTED_SHAPE;
+  if (rows == 0) return AKLR_OK;
+  const int64_t elements = static_cast<int64_t>(rows) * hidden;
+  const int64_t blocks = (elements / 8 + 255) / 256;
+  const int grid = static_cast<int>(blocks < 148 * 16 ? blocks : 148 * 16);
+  per_group_quant_mxfp8_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), q, scales, elements);
+  return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+}
+
+}  // namespace aklr

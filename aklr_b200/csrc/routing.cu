@@ -1,0 +1,354 @@
+// Top-k routing and the moe_align token sort, sm_100a.
+//
+// Routing: one warp per token.  Each expert's ranking value becomes a 64-bit key
+// (order-preserving image of the float in the high word, ~expert in the low word), so a warp
+// arg-max of keys picks the largest value and, among equals, the lowest expert id -- the order
+// the reference's stable descending sort defines
+// (aklr/plugins/sglang/models/deepseek_v2/reference.py:114-143,
+//  aklr/plugins/sglang/models/qwen3_moe/reference.py:34-41, aklr/ops/topk/reference.py:17-35).
+//
+// Sort: a stable counting sort of routes (token*K + slot) by expert, each expert's run padded
+// with -1 to a multiple of block_m, plus a block -> expert table.  The reference defines no order
+// here (its kernels use atomics); this one is deterministic.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace aklr {
+
+__device__ __forceinline__ uint32_t ordered_bits(float v) {
+  v += 0.0f;  // -0 -> +0, so equal values have equal images
+  const uint32_t u = __float_as_uint(v);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+struct Key {
+  uint32_t hi, lo;
+};
+__device__ __forceinline__ bool key_greater(Key a, Key b) { return a.hi > b.hi || (a.hi == b.hi && a.lo > b.lo); }
+
+// warp-wide max of 64-bit keys given as two words (all lanes take part)
+__device__ __forceinline__ Key warp_max_key(Key k) {
+  const uint32_t hi = __reduce_max_sync(0xFFFFFFFFu, k.hi);
+  const uint32_t lo = __reduce_max_sync(0xFFFFFFFFu, k.hi == hi ? k.lo : 0u);
+  return Key{hi, lo};
+}
+
+__device__ __forceinline__ float sigmoid_exact(float x) { return __fdiv_rn(1.0f, 1.0f + expf(-x)); }
+
+// VPT: values per lane; expert e = i*32 + lane sits in register i.
+template <int VPT>
+__global__ void __launch_bounds__(256) route_kernel(RouteParams p) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int token = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  if (token >= p.n_tokens) return;
+  const int E = p.n_routed;
+  const int ktot = p.topk + p.n_shared;
+
+  float score[VPT];   // what weighs the expert (softmax: the logit; sigmoid: the score)
+  uint32_t rank[VPT]; // ordered image of what ranks it; 0 = not a candidate
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int e = i * 32 + lane;
+    score[i] = 0.0f;
+    rank[i] = 0u;
+    if (e < E) {
+      float logit;
+      uint32_t bits16 = 0;
+      if (p.logits_are_bf16) {
+        bits16 = reinterpret_cast<const uint16_t*>(p.logits)[static_cast<size_t>(token) * E + e];
+        logit = bf16_bits_to_float(bits16);
+      } else {
+        logit = reinterpret_cast<const float*>(p.logits)[static_cast<size_t>(token) * E + e];
+      }
+      if (p.scoring == AKLR_SCORING_SIGMOID) {
+        const float s = (p.logits_are_bf16 && p.sigmoid_table) ? p.sigmoid_table[bits16] : sigmoid_exact(logit);
+        float b = 0.0f;
+        if (p.bias) b = p.bias_is_bf16 ? bf16_bits_to_float(reinterpret_cast<const uint16_t*>(p.bias)[e])
+                                       : reinterpret_cast<const float*>(p.bias)[e];
+        score[i] = s;
+        rank[i] = ordered_bits(s + b);
+      } else {
+        score[i] = logit;
+        rank[i] = ordered_bits(logit);
+      }
+    }
+  }
+
+  // ---- grouped routing: keep the topk_group groups whose two best biased scores sum highest ----
+  if (p.num_expert_group > 1 && p.topk_group < p.num_expert_group) {
+    const int G = p.num_expert_group;
+    const int gs = E / G;
+    float my_group_score = 0.0f;  // lane g holds group g's score
+    for (int g = 0; g < G; ++g) {
+      Key best{0u, 0u};
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int e = i * 32 + lane;
+        const Key k{(e < E && e / gs == g) ? rank[i] : 0u, ~static_cast<uint32_t>(e)};
+        if (key_greater(k, best)) best = k;
+      }
+      const Key first = warp_max_key(best);
+      Key second_local{0u, 0u};
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int e = i * 32 + lane;
+        const Key k{(e < E && e / gs == g) ? rank[i] : 0u, ~static_cast<uint32_t>(e)};
+        const bool is_first = (k.hi == first.hi && k.lo == first.lo);
+        if (!is_first && key_greater(k, second_local)) second_local = k;
+      }
+      const Key second = warp_max_key(second_local);
+      // recover the floats from their ordered images
+      auto value_of = [](uint32_t o) {
+        const uint32_t u = (o & 0x80000000u) ? (o & 0x7FFFFFFFu) : ~o;
+        return __uint_as_float(u);
+      };
+      const float sum = value_of(first.hi) + value_of(second.hi);
+      if (lane == g) my_group_score = sum;
+    }
+    uint32_t kept_mask = 0u;
+    Key gk{lane < G ? ordered_bits(my_group_score) : 0u, ~static_cast<uint32_t>(lane)};
+    for (int j = 0; j < p.topk_group; ++j) {
+      const Key top = warp_max_key(gk);
+      const int g = static_cast<int>(~top.lo);
+      kept_mask |= 1u << g;
+      if (lane == g) gk.hi = 0u;
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int e = i * 32 + lane;
+      if (e < E && !((kept_mask >> (e / gs)) & 1u)) rank[i] = 0u;
+    }
+  }
+
+  // ---- top-k by key; lane j keeps the j-th pick ----
+  int my_id = -1;
+  float my_score = 0.0f;
+  for (int j = 0; j < p.topk; ++j) {
+    Key best{0u, 0u};
+    float best_score = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const Key k{rank[i], ~static_cast<uint32_t>(i * 32 + lane)};
+      if (key_greater(k, best)) {
+        best = k;
+        best_score = score[i];
+      }
+    }
+    const Key top = warp_max_key(best);
+    const int e = static_cast<int>(~top.lo);
+    const bool mine = (best.hi == top.hi && best.lo == top.lo);
+    const float s = __shfl_sync(0xFFFFFFFFu, best_score, __ffs(__ballot_sync(0xFFFFFFFFu, mine)) - 1);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+      if (mine && i * 32 + lane == e) rank[i] = 0u;
+    if (lane == j) {
+      my_id = e;
+      my_score = s;
+    }
+  }
+
+  // ---- weights ----
+  float w = 0.0f;
+  if (p.scoring == AKLR_SCORING_SIGMOID) {
+    float total = 0.0f;
+    for (int j = 0; j < p.topk; ++j) total += __shfl_sync(0xFFFFFFFFu, my_score, j);
+    w = p.renormalize ? __fdiv_rn(my_score, total) : my_score;
+    w *= p.routed_scaling_factor;
+  } else {
+    // softmax over the chosen logits (lane 0 holds the largest)
+    const float top_logit = __shfl_sync(0xFFFFFFFFu, my_score, 0);
+    const float ex = lane < p.topk ? expf(my_score - top_logit) : 0.0f;
+    float total = 0.0f;
+    for (int j = 0; j < p.topk; ++j) total += __shfl_sync(0xFFFFFFFFu, ex, j);
+    w = __fdiv_rn(ex, total);
+  }
+  if (lane < p.topk) {
+    p.topk_ids[static_cast<size_t>(token) * ktot + lane] = my_id;
+    p.topk_weights[static_cast<size_t>(token) * ktot + lane] = w;
+  } else if (lane < ktot) {  // shared experts: the slots after the routed ones, at weight 1
+    p.topk_ids[static_cast<size_t>(token) * ktot + lane] = E + (lane - p.topk);
+    p.topk_weights[static_cast<size_t>(token) * ktot + lane] = 1.0f;
+  }
+}
+
+int launch_route(const RouteParams& p, cudaStream_t stream) {
+  if (p.n_tokens == 0) return AKLR_OK;
+  if (p.n_routed < 1 || p.n_routed > 1024 || p.topk < 1 || p.topk + p.n_shared > 32 || p.topk > p.n_routed)
+    return AKLR_ERR_UNSUPPORTED_SHAPE;
+  if (p.num_expert_group > 1) {
+    if (p.num_expert_group > 32 || p.n_routed % p.num_expert_group != 0 ||
+        p.n_routed / p.num_expert_group < 2 || p.topk_group > p.num_expert_group || p.topk_group < 1 ||
+        p.topk > p.topk_group * (p.n_routed / p.num_expert_group))
+      return AKLR_ERR_UNSUPPORTED_SHAPE;
+  }
+  const int threads = 256, warps = threads / 32;
+  const int blocks = (p.n_tokens + warps - 1) / warps;
+  const int vpt = (p.n_routed + 31) / 32;
+  if (vpt <= 1) route_kernel<1><<<blocks, threads, 0, stream>>>(p);
+  else if (vpt <= 2) route_kernel<2><<<blocks, threads, 0, stream>>>(p);
+  else if (vpt <= 4) route_kernel<4><<<blocks, threads, 0, stream>>>(p);
+  else if (vpt <= 8) route_kernel<8><<<blocks, threads, 0, stream>>>(p);
+  else if (vpt <= 16) route_kernel<16><<<blocks, threads, 0, stream>>>(p);
+  else route_kernel<32><<<blocks, threads, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+}
+
+// =============================================================================================
+// moe_align: stable counting sort of routes by expert with per-expert padding
+// =============================================================================================
+constexpr int kSortChunk = 1024;  // routes per CTA, one per thread
+
+__device__ __forceinline__ int local_expert(const AlignParams& p, int route) {
+  int e = p.topk_ids[route];
+  if (e < 0 || e >= p.n_experts_global) return -1;
+  if (p.expert_map) e = p.expert_map[e];
+  return (e >= 0 && e < p.n_experts) ? e : -1;
+}
+
+// Pass 1: histogram of each 1024-route chunk -> chunk_hist[chunk][expert]
+__global__ void __launch_bounds__(kSortChunk) align_count_kernel(AlignParams p) {
+  extern __shared__ int hist[];
+  for (int e = threadIdx.x; e < p.n_experts; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  const int route = blockIdx.x * kSortChunk + threadIdx.x;
+  if (route < p.n_routes) {
+    const int e = local_expert(p, route);
+    if (e >= 0) atomicAdd(&hist[e], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < p.n_experts; e += blockDim.x)
+    p.chunk_hist[static_cast<size_t>(blockIdx.x) * p.n_experts + e] = hist[e];
+}
+
+// Shared by the scan kernel and the one-CTA path: from per-expert totals in smem ``total`` compute
+// padded bases, the block table, counts, the pad fill.  ``base`` receives each expert's first row.
+__device__ void plan_blocks(const AlignParams& p, const int* total, int* base, int* scratch) {
+  // serial-in-chunks exclusive scan over experts of padded block counts (n_experts <= 1025)
+  const int tid = threadIdx.x, nt = blockDim.x;
+  const int per = (p.n_experts + nt - 1) / nt;
+  int local_sum = 0;
+  for (int i = 0; i < per; ++i) {
+    const int e = tid * per + i;
+    if (e < p.n_experts) local_sum += (total[e] + p.block_m - 1) / p.block_m;
+  }
+  scratch[tid] = local_sum;
+  __syncthreads();
+  // Hillis-Steele inclusive scan over nt partial sums
+  for (int off = 1; off < nt; off <<= 1) {
+    const int v = tid >= off ? scratch[tid - off] : 0;
+    __syncthreads();
+    scratch[tid] += v;
+    __syncthreads();
+  }
+  int running = scratch[tid] - local_sum;  // blocks before this thread's experts
+  if (tid == nt - 1) {
+    p.num_blocks[0] = scratch[tid];
+    p.num_blocks[1] = scratch[tid] * p.block_m;
+  }
+  for (int i = 0; i < per; ++i) {
+    const int e = tid * per + i;
+    if (e < p.n_experts) {
+      const int c = total[e];
+      const int nb = (c + p.block_m - 1) / p.block_m;
+      base[e] = running * p.block_m;
+      p.counts[e] = c;
+      for (int b = 0; b < nb; ++b) p.block_expert[running + b] = e;
+      for (int r = c; r < nb * p.block_m; ++r) p.sorted_ids[running * p.block_m + r] = -1;
+      running += nb;
+    }
+  }
+  __syncthreads();
+}
+
+// Stable placement of one chunk: thread t holds route chunk_start + t.  ``cursor[e]`` is the next
+// free row of expert e for this chunk (smem, updated in warp order so the order stays stable).
+__device__ void place_chunk(const AlignParams& p, int route, int* cursor) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int e = route < p.n_routes ? local_expert(p, route) : -1;
+  const uint32_t active = __ballot_sync(0xFFFFFFFFu, e >= 0);
+  uint32_t same = 0;
+  if (e >= 0) same = __match_any_sync(active, e);
+  const int rank_in_warp = __popc(same & ((1u << lane) - 1u));
+  const bool leader = e >= 0 && rank_in_warp == 0;
+  int start = 0;
+  for (int w = 0; w < (blockDim.x >> 5); ++w) {
+    if (warp == w && leader) {
+      start = cursor[e];
+      cursor[e] = start + __popc(same);
+    }
+    __syncthreads();
+  }
+  if (e >= 0) {
+    start = __shfl_sync(same, start, __ffs(same) - 1);
+    p.sorted_ids[start + rank_in_warp] = route;
+  }
+}
+
+// Pass 2 (one CTA): per-expert totals, per-chunk offsets, block table.
+__global__ void __launch_bounds__(1024) align_scan_kernel(AlignParams p, int n_chunks) {
+  extern __shared__ int sm[];
+  int* total = sm;                  // [n_experts]
+  int* base = sm + p.n_experts;     // [n_experts]
+  int* scratch = base + p.n_experts;  // [blockDim]
+  for (int e = threadIdx.x; e < p.n_experts; e += blockDim.x) {
+    int run = 0;
+    for (int c = 0; c < n_chunks; ++c) {
+      const size_t at = static_cast<size_t>(c) * p.n_experts + e;
+      const int h = p.chunk_hist[at];
+      p.chunk_hist[at] = run;  // exclusive offset of chunk c inside expert e
+      run += h;
+    }
+    total[e] = run;
+  }
+  __syncthreads();
+  plan_blocks(p, total, base, scratch);
+  for (int e = threadIdx.x; e < p.n_experts; e += blockDim.x)
+    for (int c = 0; c < n_chunks; ++c) p.chunk_hist[static_cast<size_t>(c) * p.n_experts + e] += base[e];
+}
+
+// Pass 3: scatter each chunk
+__global__ void __launch_bounds__(kSortChunk) align_scatter_kernel(AlignParams p) {
+  extern __shared__ int cursor[];
+  for (int e = threadIdx.x; e < p.n_experts; e += blockDim.x)
+    cursor[e] = p.chunk_hist[static_cast<size_t>(blockIdx.x) * p.n_experts + e];
+  __syncthreads();
+  place_chunk(p, blockIdx.x * kSortChunk + threadIdx.x, cursor);
+}
+
+// All three passes in one CTA, for up to kSmallRoutes routes (decode batches).
+constexpr int kSmallRoutes = 4096;
+__global__ void __launch_bounds__(kSortChunk) align_small_kernel(AlignParams p) {
+  extern __shared__ int sm[];
+  int* total = sm;
+  int* base = sm + p.n_experts;
+  int* scratch = base + p.n_experts;
+  for (int e = threadIdx.x; e < p.n_experts; e += blockDim.x) total[e] = 0;
+  __syncthreads();
+  for (int r = threadIdx.x; r < p.n_routes; r += blockDim.x) {
+    const int e = local_expert(p, r);
+    if (e >= 0) atomicAdd(&total[e], 1);
+  }
+  __syncthreads();
+  plan_blocks(p, total, base, scratch);
+  for (int start = 0; start < p.n_routes; start += kSortChunk) {
+    place_chunk(p, start + threadIdx.x, base);
+    __syncthreads();
+  }
+}
+
+int launch_align(const AlignParams& p, cudaStream_t stream) {
+  if (p.n_experts < 1 || p.n_experts > 2048 || p.block_m < 1) return AKLR_ERR_UNSUPPORTED_SHAPE;
+  const size_t smem = (2 * static_cast<size_t>(p.n_experts) + 1024) * sizeof(int);
+  if (p.n_routes <= kSmallRoutes) {
+    align_small_kernel<<<1, kSortChunk, smem, stream>>>(p);
+  } else {
+    const int chunks = (p.n_routes + kSortChunk - 1) / kSortChunk;
+    align_count_kernel<<<chunks, kSortChunk, p.n_experts * sizeof(int), stream>>>(p);
+    align_scan_kernel<<<1, 1024, smem, stream>>>(p, chunks);
+    align_scatter_kernel<<<chunks, kSortChunk, p.n_experts * sizeof(int), stream>>>(p);
+  }
+  return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+}
+
+}  // namespace aklr

@@ -1,0 +1,152 @@
+/* C ABI of the B200 (sm_100a) fused-MoE library, libaklr_b200.so.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as void*: a
+ * cudaStream_t), launches on that stream, never synchronises, never allocates device memory and
+ * keeps no state between calls: scratch comes from the caller as one workspace buffer whose size
+ * the matching *_workspace_bytes function gives.  Return value: 0, or a negative AKLR_ERR_* code
+ * (aklr_status_string names it).  Nothing here falls back to a CPU path.
+ *
+ * Each function cites the reference interface it stands in for (paths inside the reference
+ * project).  The reference's kernels are Python `run(*, <tensors>, out)` callables served by its
+ * dispatch registry (aklr/ops/README.md:183-251); its native-extension precedent registers
+ * `run(Tensor..., Tensor(a!) out) -> ()` (aklr/ops/README.md:269-279).  A binding passes
+ * tensor.data_ptr() values to the functions below.
+ */
+#ifndef AKLR_B200_H
+#define AKLR_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AKLR_B200_ABI_VERSION 1
+
+#define AKLR_OK 0
+#define AKLR_ERR_BAD_ARGUMENT -1
+#define AKLR_ERR_WORKSPACE_TOO_SMALL -2
+#define AKLR_ERR_CUDA -3
+#define AKLR_ERR_UNSUPPORTED_SHAPE -4
+#define AKLR_ERR_NO_DEVICE -5
+#define AKLR_ERR_KERNEL_WAIT_TIMEOUT -6
+#define AKLR_ERR_TOO_LARGE -7
+
+#define AKLR_SCORING_SOFTMAX 0
+#define AKLR_SCORING_SIGMOID 1
+#define AKLR_DTYPE_BF16 0
+#define AKLR_DTYPE_F32 1
+
+/* One fused-MoE layer call.  Expert slots in w1/w2: the n_routed routed experts, then n_shared
+ * shared experts every token visits at weight 1 (aklr/plugins/sglang/models/deepseek_v2/
+ * reference.py:80-88).  Routes per token = topk + n_shared. */
+typedef struct aklr_moe_config {
+  int32_t n_tokens;
+  int32_t hidden;            /* model dim, multiple of 128 */
+  int32_t inter;             /* expert intermediate dim, multiple of 128 */
+  int32_t n_routed;          /* router columns, <= 1024 */
+  int32_t n_shared;          /* shared experts appended after the routed ones */
+  int32_t topk;
+  int32_t scoring;           /* AKLR_SCORING_* */
+  int32_t num_expert_group;  /* 1 = ungrouped */
+  int32_t topk_group;
+  int32_t renormalize;       /* sigmoid scoring only; softmax always renormalises over the chosen */
+  float routed_scaling_factor;
+  int32_t logits_dtype;      /* AKLR_DTYPE_* of router logits */
+  int32_t bias_dtype;        /* AKLR_DTYPE_* of correction_bias */
+  int32_t block_m;           /* tokens per expert block: 16/32/64/128, 0 = library picks */
+  int32_t n_experts_global;  /* experts-only entry with an expert map: ids range over this; else 0 */
+} aklr_moe_config;
+
+/* Byte offsets of the intermediates inside the workspace (for tests and debuggers). */
+typedef struct aklr_moe_workspace_layout {
+  int64_t total_bytes;
+  int64_t status;        /* int32[2]: first failed device wait (0 = none), its location */
+  int64_t topk_ids;      /* int32 [n_tokens, routes] */
+  int64_t topk_weights;  /* float [n_tokens, routes] */
+  int64_t sorted_ids;    /* int32 [capacity] route ids grouped by expert, -1 = padding */
+  int64_t block_expert;  /* int32 [max_blocks] */
+  int64_t counts;        /* int32 [experts] routes per expert */
+  int64_t num_blocks;    /* int32 [2] blocks in use, rows in use */
+  int64_t chunk_hist;    /* int32 sort scratch */
+  int64_t xq;            /* e4m3 [capacity, hidden] */
+  int64_t xs;            /* float [capacity, hidden/128] */
+  int64_t hq;            /* e4m3 [capacity, inter] */
+  int64_t hs;            /* float [capacity, inter/128] */
+  int64_t rows;          /* bf16 [n_tokens*routes, hidden] weighted per-route outputs */
+  int32_t block_m;
+  int32_t max_blocks;
+  int32_t capacity;      /* max_blocks * block_m */
+  int32_t n_experts;     /* expert slots sorted over */
+} aklr_moe_workspace_layout;
+
+int aklr_abi_version(void);
+const char* aklr_status_string(int code);
+/* Message of the last failing call on this thread ("" if none). */
+const char* aklr_last_error(void);
+
+/* Workspace of aklr_moe_fp8_forward / aklr_moe_fp8_experts for this config. */
+int aklr_moe_fp8_workspace(const aklr_moe_config* cfg, aklr_moe_workspace_layout* layout);
+
+/* Whole layer from router logits: routing, sort, quant, gate_up, down, combine.
+ * Stands in for the kernels behind `deepseek_v2_fp8_moe` / `qwen3_moe_fp8_moe`
+ * (aklr/plugins/sglang/models/deepseek_v2/api.py:35-50, .../qwen3_moe/api.py:14-23; arithmetic:
+ * .../deepseek_v2/reference.py:163-183, .../qwen3_moe/reference.py:64-88) after the router GEMM.
+ *   hidden_states bf16 [T,H]; logits [T,n_routed]; bias [n_routed] or NULL;
+ *   sigmoid_table float[65536] on the device indexed by bf16 bits, or NULL (computed in-kernel);
+ *   w1 e4m3 [E,2I,H] gate rows then up rows; w1_scale float [E,2I/128,H/128];
+ *   w2 e4m3 [E,H,I]; w2_scale float [E,H/128,I/128]; out bf16 [T,H]. */
+int aklr_moe_fp8_forward(const aklr_moe_config* cfg, const void* hidden_states, const void* logits,
+                         const void* bias, const float* sigmoid_table, const void* w1, const float* w1_scale,
+                         const void* w2, const float* w2_scale, void* out, void* workspace,
+                         size_t workspace_bytes, void* stream);
+
+/* Experts only, routing given: stands in for the kernels behind `fused_moe` with FP8 128x128
+ * weights (aklr/ops/fused_moe/api.py:17-44; expert_mask semantics
+ * aklr/ops/fused_moe/reference.py:78-84).  topk_ids int32 [T, topk + n_shared] hold ids in
+ * [0, n_experts_global); expert_map int32 [n_experts_global] maps them to this rank's slot or -1
+ * (NULL: identity).  topk_weights float [T, topk + n_shared]. */
+int aklr_moe_fp8_experts(const aklr_moe_config* cfg, const void* hidden_states, const int32_t* topk_ids,
+                         const float* topk_weights, const int32_t* expert_map, const void* w1,
+                         const float* w1_scale, const void* w2, const float* w2_scale, void* out,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
+/* Routing alone: `biased_grouped_topk` (aklr/ops/topk/api.py:12-22, reference.py:17-35) and the
+ * routing halves of the two layer ops.  Writes topk_ids int32 / topk_weights float
+ * [T, topk + n_shared]. */
+int aklr_moe_route(const aklr_moe_config* cfg, const void* logits, const void* bias, const float* sigmoid_table,
+                   int32_t* topk_ids, float* topk_weights, void* stream);
+
+/* moe_align: stable sort of routes by expert, padded per expert to block_m.  The reference has no
+ * function for it (its kernels sort inside, e.g. deepseek_v2 kernel e5adae63cb11d836,
+ * kernel.py:276-361).  chunk_scratch: int32 [ceil(n_routes/1024) * n_experts]. */
+int aklr_moe_align(const int32_t* topk_ids, const int32_t* expert_map, int32_t n_routes, int32_t n_experts,
+                   int32_t n_experts_global, int32_t block_m, int32_t* sorted_ids, int32_t* block_expert,
+                   int32_t* counts, int32_t* num_blocks, int32_t* chunk_scratch, void* stream);
+int64_t aklr_moe_align_max_blocks(int64_t n_routes, int64_t n_experts, int64_t block_m);
+
+/* logits bf16 [T,E] = bf16(x [T,H] @ w [E,H]^T): `_router_logits`
+ * (aklr/plugins/sglang/models/qwen3_moe/reference.py:24-31). */
+int aklr_router_gemm_bf16(const void* x, const void* w, void* logits, int32_t n_tokens, int32_t hidden,
+                          int32_t n_routed, void* stream);
+
+/* `per_group_quant_fp8` (aklr/ops/quant/api.py:8-9, reference.py:9-28): x bf16 [T,H] ->
+ * q e4m3 [T,H], scales float [H/128, T] (group-major). */
+int aklr_per_group_quant_fp8(const void* x, void* q, float* scales, int32_t rows, int32_t hidden, void* stream);
+/* `per_group_quant_mxfp8` (aklr/ops/quant/api.py:12-13, reference.py:31-48): q e4m3 [T,H],
+ * scales e8m0 bytes [T, H/32]. */
+int aklr_per_group_quant_mxfp8(const void* x, void* q, uint8_t* scales, int32_t rows, int32_t hidden,
+                               void* stream);
+/* The layer's own activation quantiser (division form, row-major scales [T,H/128]):
+ * `_fp8_input` (aklr/plugins/sglang/models/qwen3_moe/reference.py:44-54). */
+int aklr_moe_act_quant_fp8(const void* x, void* q, float* scales, int32_t rows, int32_t hidden, void* stream);
+
+/* Copies the workspace's status words to host_status[2] and waits for the stream: 0 = every
+ * device-side wait completed. */
+int aklr_moe_read_status(const void* workspace, int32_t* host_status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AKLR_B200_H */

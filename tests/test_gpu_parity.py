@@ -1,0 +1,370 @@
+"""GPU parity: the CUDA path (through the C ABI) against the CPU oracle and the golden fixtures.
+
+Gates: routing ids, per-expert counts and sorted order bit-exact; routing weights abs/rel 1e-4;
+FP8 codes and scales of the activation quantiser bit-exact; layer output max relative error
+<= 2e-2 (per row, relative to the row's largest reference magnitude), cosine >= 0.9995 and whole-
+output SQNR >= 30 dB against the float32 oracle rounded to bf16.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from aklr_b200 import workloads as wl
+from oracle import moe_oracle as orc
+from tests.golden import cases
+
+pytestmark = pytest.mark.gpu
+
+WEIGHT_TOL = 1e-4
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def t(a) -> torch.Tensor:
+    return torch.from_numpy(np.asarray(a))
+
+
+def routing_of(cfg: wl.MoEConfig):
+    from aklr_b200.moe import Routing
+
+    return Routing(
+        topk=cfg.topk,
+        scoring=cfg.scoring,
+        n_shared=cfg.n_shared,
+        num_expert_group=cfg.num_expert_group,
+        topk_group=cfg.topk_group,
+        renormalize=cfg.renormalize,
+        routed_scaling_factor=cfg.routed_scaling_factor,
+    )
+
+
+def assert_routing(ids, weights, ref_ids, ref_weights):
+    assert torch.equal(ids.cpu().long(), ref_ids.long()), "routing ids differ from the oracle"
+    torch.testing.assert_close(weights.cpu(), ref_weights.float(), atol=WEIGHT_TOL, rtol=WEIGHT_TOL)
+
+
+# ------------------------------------------------------------------------------------------------
+# routing
+# ------------------------------------------------------------------------------------------------
+def test_grouped_sigmoid_routing_matches_golden(golden):
+    from aklr_b200.moe import Routing, route
+
+    logits, bias = cases.route_ds()
+    r = Routing(topk=8, scoring="sigmoid", num_expert_group=8, topk_group=4, renormalize=True, routed_scaling_factor=2.5)
+    ids, w = route(logits.to(dev()), bias.to(dev()), r)
+    assert_routing(ids, w, t(golden["route_ds.ids"]), t(golden["route_ds.weights"]))
+    r = Routing(topk=8, scoring="sigmoid", num_expert_group=8, topk_group=4, renormalize=False, routed_scaling_factor=1.0)
+    ids, w = route(logits.to(dev()), bias.to(dev()), r)
+    assert_routing(ids, w, t(golden["route_ds_norenorm.ids"]), t(golden["route_ds_norenorm.weights"]))
+
+
+def test_tied_logits_route_to_the_lower_expert(golden):
+    from aklr_b200.moe import Routing, route
+
+    tied = cases.route_tied()
+    r = Routing(topk=8, scoring="sigmoid", num_expert_group=8, topk_group=4, renormalize=True, routed_scaling_factor=2.5)
+    ids, w = route(tied.to(dev()), torch.zeros(256, dtype=torch.bfloat16, device=dev()), r)
+    assert_routing(ids, w, t(golden["route_tied.ids"]), t(golden["route_tied.weights"]))
+    ids, w = route(tied[:, :128].contiguous().to(dev()), None, Routing(topk=8))
+    assert_routing(ids, w, t(golden["route_tied_softmax.ids"]), t(golden["route_tied_softmax.weights"]))
+    # the reference's known answer (tests/ops/test_reference.py:91-108): 1024 experts, float32 logits
+    logits = torch.zeros(1, 1024)
+    logits[0, [583, 571, 368, 31]] = 1.0
+    r = Routing(topk=3, scoring="sigmoid", renormalize=False)
+    ids, _ = route(logits.to(dev()), torch.zeros(1024, device=dev()), r)
+    assert ids.cpu().tolist() == [[31, 368, 571]]
+
+
+def test_softmax_routing_matches_golden(golden):
+    from aklr_b200.moe import Routing, route
+
+    cfg, logits = cases.route_qwen3()
+    ids, w = route(logits.to(dev()), None, Routing(topk=cfg.topk))
+    assert_routing(ids, w, t(golden["route_qwen3.ids"]), t(golden["route_qwen3.weights"]))
+
+
+def test_standalone_biased_grouped_topk_matches_golden(golden):
+    from aklr_b200.moe import Routing, route
+
+    logits, bias = cases.bgt()
+    r = Routing(topk=8, scoring="sigmoid", renormalize=True, routed_scaling_factor=2.5)
+    ids, w = route(logits.to(dev()), bias.to(dev()), r)
+    assert_routing(ids, w, t(golden["bgt.ids"]), t(golden["bgt.weights"]))
+
+
+@pytest.mark.parametrize("n_tokens", [1, 2, 3, 31, 33, 127, 129, 1000])
+@pytest.mark.parametrize("name", ["deepseek_v3", "qwen3", "mixtral"])
+def test_routing_matches_oracle_on_ragged_batches(name, n_tokens):
+    from aklr_b200.moe import route
+
+    cfg = wl.CONFIGS[name]
+    _, logits, bias = wl.router_inputs(cfg, n_tokens, seed=n_tokens)
+    if cfg.scoring == "sigmoid":
+        ref_ids, ref_w = orc.grouped_sigmoid_topk(
+            logits.float(), bias.float(), cfg.topk, cfg.num_expert_group, cfg.topk_group, True, cfg.routed_scaling_factor
+        )
+        ref_ids, ref_w = orc.with_shared_slot(ref_ids, ref_w, cfg.n_routed)
+    else:
+        ref_ids, ref_w = orc.softmax_topk(logits.float(), cfg.topk)
+    ids, w = route(logits.to(dev()), None if bias is None else bias.to(dev()), routing_of(cfg))
+    assert_routing(ids, w, ref_ids, ref_w)
+
+
+# ------------------------------------------------------------------------------------------------
+# sort
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize(
+    "n_tokens,n_experts,k,block_m",
+    [(1, 257, 9, 16), (7, 8, 2, 16), (64, 8, 2, 32), (256, 257, 9, 16), (455, 257, 9, 32), (456, 128, 8, 64), (3000, 257, 9, 128), (20000, 64, 6, 128)],
+)
+def test_moe_align_matches_oracle(n_tokens, n_experts, k, block_m):
+    from aklr_b200.moe import moe_align
+
+    g = torch.Generator().manual_seed(n_tokens)
+    ids = torch.stack([torch.randperm(n_experts, generator=g)[:k] for _ in range(n_tokens)]).to(torch.int32)
+    sorted_ids, block_expert, counts, nb = moe_align(ids.to(dev()), n_experts, block_m)
+    ref_sorted, ref_blocks, ref_counts = orc.moe_align(ids, n_experts, block_m)
+    assert torch.equal(counts.cpu().long(), ref_counts)
+    assert nb == ref_blocks.numel()
+    assert torch.equal(block_expert.cpu(), ref_blocks)
+    assert torch.equal(sorted_ids.cpu(), ref_sorted)
+
+
+def test_moe_align_with_an_expert_map_drops_other_ranks_routes():
+    from aklr_b200.moe import moe_align
+
+    g = torch.Generator().manual_seed(3)
+    ids = torch.stack([torch.randperm(32, generator=g)[:4] for _ in range(300)]).to(torch.int32)
+    expert_map = torch.full((32,), -1, dtype=torch.int32)
+    expert_map[8:16] = torch.arange(8, dtype=torch.int32)  # this rank holds global experts 8..15
+    sorted_ids, block_expert, counts, nb = moe_align(ids.to(dev()), 8, 16, expert_map.to(dev()))
+    local = torch.where((ids >= 8) & (ids < 16), ids - 8, -1)
+    ref_sorted, ref_blocks, ref_counts = orc.moe_align(local, 8, 16)
+    assert torch.equal(counts.cpu().long(), ref_counts)
+    assert torch.equal(block_expert.cpu(), ref_blocks)
+    assert torch.equal(sorted_ids.cpu(), ref_sorted)
+
+
+# ------------------------------------------------------------------------------------------------
+# quantisers
+# ------------------------------------------------------------------------------------------------
+def test_activation_quant_is_bit_exact():
+    from aklr_b200.moe import act_quant_fp8
+
+    x = wl.normal(5, "x", (67, 1024), 1.0, dtype=torch.bfloat16)
+    x[3] = 0
+    x[5, :128] *= 1e-30
+    x[7] *= 300.0
+    q, s = act_quant_fp8(x.to(dev()))
+    ref_q, ref_s = orc.fp8_group_quant(x.float())
+    assert torch.equal(s.cpu(), ref_s)
+    assert torch.equal(q.cpu().view(torch.uint8), ref_q.view(torch.uint8))
+
+
+def test_standalone_quant_ops_match_golden(golden):
+    from aklr_b200.moe import per_group_quant_fp8, per_group_quant_mxfp8
+
+    x = cases.quant_x().to(dev())
+    q, s = per_group_quant_fp8(x)
+    assert torch.equal(q.cpu().float(), t(golden["quant_fp8.q"]))
+    assert torch.equal(s.cpu(), t(golden["quant_fp8.s"]))
+    q, s = per_group_quant_mxfp8(x)
+    assert torch.equal(q.cpu().float(), t(golden["quant_mxfp8.q"]))
+    assert torch.equal(s.cpu(), t(golden["quant_mxfp8.s"]))
+
+
+def test_router_gemm_rounds_like_the_oracle():
+    from aklr_b200.moe import router_logits
+
+    cfg, a = cases.tiny_layer()
+    got = router_logits(a["hidden_states"].to(dev()), a["router_weight"].to(dev())).cpu().float()
+    ref = orc.router_logits(a["hidden_states"], a["router_weight"])
+    # float32 sums in another order may land one bf16 step away
+    step = ref.abs().clamp_min(1e-3) * 2.0**-7
+    assert ((got - ref).abs() <= step).all()
+    assert (got == ref).float().mean() > 0.97
+
+
+# ------------------------------------------------------------------------------------------------
+# whole layer
+# ------------------------------------------------------------------------------------------------
+def run_layer(cfg, args, logits, block_m):
+    from aklr_b200.moe import fused_moe_fp8
+
+    d = dev()
+    bias = args.get("correction_bias")
+    out, ws = fused_moe_fp8(
+        args["hidden_states"].to(d),
+        logits.to(torch.bfloat16).to(d),
+        None if bias is None else bias.to(d),
+        args["w1"].to(d),
+        args["w1_scale"].to(d),
+        args["w2"].to(d),
+        args["w2_scale"].to(d),
+        routing_of(cfg),
+        block_m=block_m,
+        return_workspace=True,
+    )
+    ws.check_status()
+    return out, ws
+
+
+def check_intermediates(cfg, args, ws, ref_ids):
+    """Sorted order, counts, first quantisation bit-exact; second quantisation nearly so."""
+    ids = ws.topk_ids().cpu()
+    assert torch.equal(ids.long(), ref_ids)
+    ref_sorted, ref_blocks, ref_counts = orc.moe_align(ids, cfg.n_experts, ws.layout.block_m)
+    assert torch.equal(ws.counts().cpu().long(), ref_counts)
+    assert torch.equal(ws.block_expert().cpu(), ref_blocks)
+    assert torch.equal(ws.sorted_ids().cpu(), ref_sorted)
+    xq, xs = ws.xq()
+    rows = (ref_sorted >= 0).nonzero().flatten()
+    tokens = ref_sorted[rows].long() // cfg.routes_per_token
+    ref_q, ref_s = orc.fp8_group_quant(args["hidden_states"].float())
+    assert torch.equal(xs.cpu()[rows], ref_s[tokens])
+    assert torch.equal(xq.cpu().view(torch.uint8)[rows], ref_q.view(torch.uint8)[tokens])
+
+
+@pytest.mark.parametrize("block_m", [16, 32, 64, 128, 0])
+def test_tiny_layer_matches_golden(golden, block_m):
+    cfg, a = cases.tiny_layer()
+    out, ws = run_layer(cfg, a, t(golden["tiny.logits"]), block_m)
+    check_intermediates(cfg, a, ws, t(golden["tiny.ids"]))
+    gates = orc.output_gates(out.cpu(), t(golden["tiny.out"]))
+    assert orc.gates_pass(gates), gates
+
+
+@pytest.mark.parametrize("block_m", [16, 64, 0])
+def test_deepseek_small_layer_matches_golden(golden, block_m):
+    cfg, a = cases.ds_small_layer()
+    out, ws = run_layer(cfg, a, t(golden["ds_small.logits"]), block_m)
+    check_intermediates(cfg, a, ws, t(golden["ds_small.ids"]))
+    gates = orc.output_gates(out.cpu(), t(golden["ds_small.out"]))
+    assert orc.gates_pass(gates), gates
+
+
+def test_layer_from_hidden_states_through_the_router_gemm(golden):
+    """Router GEMM on the device: ids may differ from the oracle's only where two logits are
+    one bf16 step apart; the output still has to pass the float gates."""
+    from aklr_b200.moe import fused_moe_fp8, router_logits
+
+    cfg, a = cases.tiny_layer()
+    d = dev()
+    logits = router_logits(a["hidden_states"].to(d), a["router_weight"].to(d))
+    out = fused_moe_fp8(
+        a["hidden_states"].to(d), logits, None, a["w1"].to(d), a["w1_scale"].to(d), a["w2"].to(d), a["w2_scale"].to(d), routing_of(cfg)
+    )
+    ref = orc.qwen3_moe_fp8_moe(
+        a["hidden_states"], a["router_weight"], a["w1"], a["w1_scale"], a["w2"], a["w2_scale"], cfg.topk, logits=logits.cpu().float()
+    )
+    gates = orc.output_gates(out.cpu(), ref)
+    assert orc.gates_pass(gates), gates
+
+
+@pytest.mark.parametrize("n_tokens", [1, 2, 3, 31, 33, 129])
+def test_ragged_token_counts(n_tokens):
+    cfg = wl.CONFIGS["deepseek_small"]
+    hidden, logits, bias = wl.router_inputs(cfg, n_tokens, seed=100 + n_tokens)
+    w1, s1, w2, s2 = wl.expert_weights(cfg, seed=9)
+    a = dict(hidden_states=hidden, correction_bias=bias, w1=w1, w1_scale=s1, w2=w2, w2_scale=s2)
+    out, ws = run_layer(cfg, a, logits, 0)
+    ref = orc.deepseek_v2_fp8_moe(
+        hidden, None, bias, w1, s1, w2, s2, cfg.topk, cfg.num_expert_group, cfg.topk_group, True, 2.5, logits=logits.float()
+    )
+    gates = orc.output_gates(out.cpu(), ref)
+    assert orc.gates_pass(gates), gates
+
+
+def test_empty_batch_is_a_no_op():
+    from aklr_b200.moe import fused_moe_fp8
+
+    cfg = wl.CONFIGS["tiny"]
+    w1, s1, w2, s2 = wl.expert_weights(cfg, seed=9)
+    d = dev()
+    out = fused_moe_fp8(
+        torch.empty((0, cfg.hidden), dtype=torch.bfloat16, device=d),
+        torch.empty((0, cfg.n_routed), dtype=torch.bfloat16, device=d),
+        None, w1.to(d), s1.to(d), w2.to(d), s2.to(d), routing_of(cfg),
+    )
+    assert out.shape == (0, cfg.hidden)
+
+
+def test_qwen3_shaped_layer_with_skewed_routing():
+    cfg = wl.CONFIGS["qwen3"]
+    n_tokens = 256
+    hidden, logits, _ = wl.router_inputs(cfg, n_tokens, seed=21)
+    w1, s1, w2, s2 = wl.expert_weights(cfg, seed=22)
+    a = dict(hidden_states=hidden, w1=w1, w1_scale=s1, w2=w2, w2_scale=s2)
+    out, ws = run_layer(cfg, a, logits, 0)
+    ref_ids, _ = orc.softmax_topk(logits.float(), cfg.topk)
+    check_intermediates(cfg, a, ws, ref_ids)
+    ref = orc.qwen3_moe_fp8_moe(hidden, None, w1, s1, w2, s2, cfg.topk, logits=logits.float())
+    gates = orc.output_gates(out.cpu(), ref)
+    assert orc.gates_pass(gates), gates
+
+
+def test_experts_only_entry_with_an_expert_map():
+    """One rank's share under replicated-token expert parallelism: routes to experts the rank
+    does not hold add nothing (aklr/ops/fused_moe/reference.py:78-84)."""
+    from aklr_b200.moe import fused_experts_fp8
+
+    cfg = wl.CONFIGS["tiny"]
+    hidden, logits, _ = wl.router_inputs(cfg, 40, seed=31)
+    w1, s1, w2, s2 = wl.expert_weights(cfg, seed=32)
+    ids, weights = orc.softmax_topk(logits.float(), cfg.topk)
+    d = dev()
+    lo, hi = 2, 6  # this rank holds global experts 2..5
+    expert_map = torch.full((cfg.n_routed,), -1, dtype=torch.int32)
+    expert_map[lo:hi] = torch.arange(hi - lo, dtype=torch.int32)
+    out = fused_experts_fp8(
+        hidden.to(d), ids.to(torch.int32).to(d), weights.to(d), w1[lo:hi].to(d), s1[lo:hi].to(d), w2[lo:hi].to(d), s2[lo:hi].to(d),
+        expert_map=expert_map.to(d),
+    )
+    local = torch.where((ids >= lo) & (ids < hi), ids - lo, -1)
+    ref = orc.fp8_experts(hidden, local, weights, w1[lo:hi], s1[lo:hi], w2[lo:hi], s2[lo:hi])
+    gates = orc.output_gates(out.cpu(), ref)
+    assert orc.gates_pass(gates), gates
+
+
+class _LazyExperts:
+    """Indexable like a weight tensor on the host, fetching one expert from the device at a time."""
+
+    def __init__(self, device_tensor):
+        self.t = device_tensor
+
+    def __getitem__(self, e):
+        return self.t[e].cpu()
+
+
+@pytest.mark.parametrize("n_tokens", [64, 4096])
+def test_deepseek_v3_full_width_on_sampled_tokens(n_tokens):
+    """Full DeepSeek-V3 widths (11 GB of expert weights drawn on the device).  A token's output
+    depends on that token alone, so the oracle checks a sample of tokens exactly as it would
+    check all of them; ids and counts are checked for the whole batch."""
+    from aklr_b200.moe import fused_moe_fp8
+
+    cfg = wl.CONFIGS["deepseek_v3"]
+    d = dev()
+    w1, s1, w2, s2 = wl.expert_weights(cfg, seed=41, device=d, experts_per_chunk=4)
+    hidden, logits, bias = wl.router_inputs(cfg, n_tokens, seed=42)
+    out, ws = fused_moe_fp8(hidden.to(d), logits.to(d), bias.to(d), w1, s1, w2, s2, routing_of(cfg), return_workspace=True)
+    ws.check_status()
+    ref_ids, ref_w = orc.grouped_sigmoid_topk(logits.float(), bias.float(), 8, 8, 4, True, 2.5)
+    ref_ids, ref_w = orc.with_shared_slot(ref_ids, ref_w, cfg.n_routed)
+    assert torch.equal(ws.topk_ids().cpu().long(), ref_ids)
+    assert torch.equal(ws.counts().cpu().long(), torch.bincount(ref_ids.flatten(), minlength=cfg.n_experts))
+    sample = torch.tensor([0, n_tokens // 3, n_tokens - 1])
+    ref = orc.fp8_experts(
+        hidden[sample], ref_ids[sample], ref_w[sample], _LazyExperts(w1), _LazyExperts(s1), _LazyExperts(w2), _LazyExperts(s2)
+    )
+    gates = orc.output_gates(out[sample.to(d)].cpu(), ref)
+    assert orc.gates_pass(gates), gates
+    # permuting the tokens permutes the output rows bit for bit
+    perm = torch.randperm(n_tokens, generator=torch.Generator().manual_seed(1))
+    out2 = fused_moe_fp8(hidden[perm].to(d), logits[perm].to(d), bias.to(d), w1, s1, w2, s2, routing_of(cfg))
+    assert torch.equal(out2.cpu(), out.cpu()[perm])
