@@ -67,6 +67,9 @@ SIGNATURES = {
     "aklr_per_group_quant_mxfp8": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_void_p]),
     "aklr_moe_act_quant_fp8": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_void_p]),
     "aklr_moe_read_status": (c_int32, [c_void_p, POINTER(c_int32), c_void_p]),
+    "aklr_kernel_launch_count": (c_int64, []),
+    "aklr_profile_begin": (c_int32, [c_int32]),
+    "aklr_profile_read": (c_int32, [c_int32, POINTER(c_float)]),
 }
 
 _lib = None

@@ -4,6 +4,8 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <atomic>
+#include <vector>
 
 #include "../../include/aklr_b200.h"
 #include "common.cuh"
@@ -12,6 +14,24 @@
 namespace {
 
 thread_local char g_error[512] = "";
+
+// ---- optional stage timing: a ring of CUDA events the caller switches on for a measurement ----
+constexpr int kStages = 6;  // route, sort, quant, gate_up, down, combine
+struct StageProfile {
+  std::vector<cudaEvent_t> events;  // (kStages + 1) per recorded call
+  int capacity = 0, used = 0;
+  bool on = false;
+};
+StageProfile g_profile;
+std::atomic<long long> g_launches{0};
+
+void profile_mark(cudaStream_t stream, int slot, int stage) {
+  if (g_profile.on && slot >= 0) cudaEventRecord(g_profile.events[slot * (kStages + 1) + stage], stream);
+}
+int profile_slot() {
+  if (!g_profile.on || g_profile.used >= g_profile.capacity) return -1;
+  return g_profile.used++;
+}
 
 int fail(int code, const char* fmt, ...) {
   va_list args;
@@ -135,7 +155,7 @@ void layout_of(const aklr_moe_config& c, aklr_moe_workspace_layout* l) {
 int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, const void* hidden_states,
                 const int32_t* topk_ids, const float* topk_weights, const int32_t* expert_map,
                 int n_experts_global, const void* w1, const float* w1_scale, const void* w2,
-                const float* w2_scale, void* out, uint8_t* ws, cudaStream_t stream) {
+                const float* w2_scale, void* out, uint8_t* ws, cudaStream_t stream, int slot) {
   using namespace aklr;
   const int routes_per_token = c.topk + c.n_shared;
   const int routes = c.n_tokens * routes_per_token;
@@ -159,6 +179,8 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   ap.block_m = l.block_m;
   int rc = launch_align(ap, stream);
   if (rc) return fail(rc, "moe_align launch failed");
+  g_launches += routes <= 4096 ? 1 : 3;
+  profile_mark(stream, slot, 2);
 
   GatherQuantParams qp{};
   qp.x = hidden_states;
@@ -171,6 +193,8 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   qp.routes_per_token = routes_per_token;
   rc = launch_gather_quant_fp8(qp, stream);
   if (rc) return fail(rc, "activation quant launch failed");
+  g_launches += 1;
+  profile_mark(stream, slot, 3);
 
   const int sms = sm_count();
   GroupedGemmParams g1{};
@@ -195,6 +219,8 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   if (g1.stages < 2) return fail(AKLR_ERR_UNSUPPORTED_SHAPE, "hidden=%d needs more shared memory than one SM has", c.hidden);
   rc = launch_grouped_gemm_gate_up(g1, sms, stream);
   if (rc) return fail(rc, "gate_up grouped GEMM launch failed");
+  g_launches += 1;
+  profile_mark(stream, slot, 4);
 
   GroupedGemmParams g2{};
   rc = make_map_u8(&g2.map_w, w2, static_cast<uint64_t>(experts) * c.hidden, c.inter, 128);
@@ -218,6 +244,8 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   if (g2.stages < 2) return fail(AKLR_ERR_UNSUPPORTED_SHAPE, "inter=%d needs more shared memory than one SM has", c.inter);
   rc = launch_grouped_gemm_down(g2, sms, stream);
   if (rc) return fail(rc, "down grouped GEMM launch failed");
+  g_launches += 1;
+  profile_mark(stream, slot, 5);
 
   CombineParams cp{};
   cp.rows = ws + l.rows;
@@ -230,6 +258,8 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   cp.n_experts_global = n_experts_global;
   rc = launch_combine(cp, stream);
   if (rc) return fail(rc, "combine launch failed");
+  g_launches += 1;
+  profile_mark(stream, slot, 6);
   return AKLR_OK;
 }
 
@@ -289,16 +319,19 @@ int aklr_moe_fp8_forward(const aklr_moe_config* cfg, const void* hidden_states, 
   aklr_moe_workspace_layout l;
   int rc = prepare(cfg, &l, workspace, workspace_bytes, stream);
   if (rc) return rc;
+  if (cfg->n_tokens == 0) return AKLR_OK;  // nothing to do; empty tensors may have NULL pointers
   if (!hidden_states || !logits || !w1 || !w1_scale || !w2 || !w2_scale || !out)
     return fail(AKLR_ERR_BAD_ARGUMENT, "NULL tensor argument");
-  if (cfg->n_tokens == 0) return AKLR_OK;
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   int32_t* ids = reinterpret_cast<int32_t*>(ws + l.topk_ids);
   float* weights = reinterpret_cast<float*>(ws + l.topk_weights);
+  const int slot = profile_slot();
+  profile_mark(stream, slot, 0);
   rc = aklr_moe_route(cfg, logits, bias, sigmoid_table, ids, weights, stream_);
   if (rc) return rc;
+  profile_mark(stream, slot, 1);
   return run_experts(*cfg, l, hidden_states, ids, weights, nullptr, cfg->n_routed + cfg->n_shared, w1, w1_scale, w2,
-                     w2_scale, out, ws, stream);
+                     w2_scale, out, ws, stream, slot);
 }
 
 int aklr_moe_fp8_experts(const aklr_moe_config* cfg, const void* hidden_states, const int32_t* topk_ids,
@@ -309,14 +342,17 @@ int aklr_moe_fp8_experts(const aklr_moe_config* cfg, const void* hidden_states, 
   aklr_moe_workspace_layout l;
   int rc = prepare(cfg, &l, workspace, workspace_bytes, stream);
   if (rc) return rc;
+  if (cfg->n_tokens == 0) return AKLR_OK;
   if (!hidden_states || !topk_ids || !topk_weights || !w1 || !w1_scale || !w2 || !w2_scale || !out)
     return fail(AKLR_ERR_BAD_ARGUMENT, "NULL tensor argument");
-  if (cfg->n_tokens == 0) return AKLR_OK;
   const int local = cfg->n_routed + cfg->n_shared;
   const int global = expert_map ? cfg->n_experts_global : local;
   if (expert_map && global < 1) return fail(AKLR_ERR_BAD_ARGUMENT, "n_experts_global must be set with an expert map");
+  const int slot = profile_slot();
+  profile_mark(stream, slot, 0);
+  profile_mark(stream, slot, 1);
   return run_experts(*cfg, l, hidden_states, topk_ids, topk_weights, expert_map, global, w1, w1_scale, w2, w2_scale,
-                     out, static_cast<uint8_t*>(workspace), stream);
+                     out, static_cast<uint8_t*>(workspace), stream, slot);
 }
 
 int aklr_moe_route(const aklr_moe_config* cfg, const void* logits, const void* bias, const float* sigmoid_table,
@@ -343,6 +379,7 @@ int aklr_moe_route(const aklr_moe_config* cfg, const void* logits, const void* b
   p.routed_scaling_factor = cfg->routed_scaling_factor;
   rc = aklr::launch_route(p, static_cast<cudaStream_t>(stream));
   if (rc) return fail(rc, "routing: %s", aklr_status_string(rc));
+  g_launches += p.n_tokens > 0;
   return AKLR_OK;
 }
 
@@ -367,6 +404,7 @@ int aklr_moe_align(const int32_t* topk_ids, const int32_t* expert_map, int32_t n
   p.block_m = block_m;
   rc = aklr::launch_align(p, static_cast<cudaStream_t>(stream));
   if (rc) return fail(rc, "moe_align: %s", aklr_status_string(rc));
+  g_launches += n_routes <= 4096 ? 1 : 3;
   return AKLR_OK;
 }
 
@@ -381,6 +419,7 @@ int aklr_router_gemm_bf16(const void* x, const void* w, void* logits, int32_t n_
   if (rc) return rc;
   rc = aklr::launch_router_gemm(x, w, logits, n_tokens, hidden, n_routed, static_cast<cudaStream_t>(stream));
   if (rc) return fail(rc, "router GEMM: %s", aklr_status_string(rc));
+  g_launches += 1;
   return AKLR_OK;
 }
 
@@ -391,6 +430,7 @@ int aklr_per_group_quant_fp8(const void* x, void* q, float* scales, int32_t rows
   rc = aklr::launch_per_group_quant_fp8(x, static_cast<uint8_t*>(q), scales, rows, hidden,
                                         static_cast<cudaStream_t>(stream));
   if (rc) return fail(rc, "per_group_quant_fp8: %s", aklr_status_string(rc));
+  g_launches += 1;
   return AKLR_OK;
 }
 
@@ -402,6 +442,7 @@ int aklr_per_group_quant_mxfp8(const void* x, void* q, uint8_t* scales, int32_t 
   rc = aklr::launch_per_group_quant_mxfp8(x, static_cast<uint8_t*>(q), scales, rows, hidden,
                                           static_cast<cudaStream_t>(stream));
   if (rc) return fail(rc, "per_group_quant_mxfp8: %s", aklr_status_string(rc));
+  g_launches += 1;
   return AKLR_OK;
 }
 
@@ -418,6 +459,7 @@ int aklr_moe_act_quant_fp8(const void* x, void* q, float* scales, int32_t rows, 
   p.routes_per_token = 1;
   rc = aklr::launch_gather_quant_fp8(p, static_cast<cudaStream_t>(stream));
   if (rc) return fail(rc, "activation quant: %s", aklr_status_string(rc));
+  g_launches += 1;
   return AKLR_OK;
 }
 
@@ -428,6 +470,33 @@ int aklr_moe_read_status(const void* workspace, int32_t* host_status, void* stre
   if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
   if (err != cudaSuccess) return cuda_fail(err, "reading the status words");
   return host_status[0] == 0 ? AKLR_OK : fail(host_status[0], "device wait gave up at location %d", host_status[1]);
+}
+
+int64_t aklr_kernel_launch_count(void) { return g_launches.load(); }
+
+int aklr_profile_begin(int32_t max_calls) {
+  for (cudaEvent_t e : g_profile.events) cudaEventDestroy(e);
+  g_profile.events.clear();
+  g_profile.capacity = g_profile.used = 0;
+  g_profile.on = false;
+  if (max_calls <= 0) return AKLR_OK;
+  g_profile.events.resize(static_cast<size_t>(max_calls) * (kStages + 1));
+  for (cudaEvent_t& e : g_profile.events) {
+    const cudaError_t err = cudaEventCreate(&e);
+    if (err != cudaSuccess) return cuda_fail(err, "creating profile events");
+  }
+  g_profile.capacity = max_calls;
+  g_profile.on = true;
+  return AKLR_OK;
+}
+
+int aklr_profile_read(int32_t call, float* stage_ms) {
+  if (!stage_ms || call < 0 || call >= g_profile.used) return fail(AKLR_ERR_BAD_ARGUMENT, "no such recorded call");
+  cudaEvent_t* ev = &g_profile.events[static_cast<size_t>(call) * (kStages + 1)];
+  cudaError_t err = cudaEventSynchronize(ev[kStages]);
+  for (int i = 0; i < kStages && err == cudaSuccess; ++i) err = cudaEventElapsedTime(&stage_ms[i], ev[i], ev[i + 1]);
+  if (err != cudaSuccess) return cuda_fail(err, "reading profile events");
+  return AKLR_OK;
 }
 
 }  // extern "C"

@@ -1,0 +1,542 @@
+"""The fused-MoE ops with the reference's api signatures, served by the sm_100a kernels.
+
+    from aklr_b200 import ops
+    ops.init()                                   # once per process, on the GPU rank's device
+    out = ops.deepseek_v2_fp8_moe(hidden_states=..., router_weight=..., ...)
+    if isinstance(out, ops.FallbackReason): ...  # run the engine's own code
+
+Signatures follow aklr/plugins/sglang/models/deepseek_v2/api.py:35-50,
+aklr/plugins/sglang/models/qwen3_moe/api.py:14-23, aklr/ops/fused_moe/api.py:17-44,
+aklr/ops/topk/api.py:12-22 and aklr/ops/quant/api.py:8-13 parameter for parameter.
+"""
+
+from __future__ import annotations
+
+import math
+from collections.abc import Mapping
+from typing import Any
+
+import torch
+
+from aklr_b200 import moe
+from aklr_b200.core.dispatch import (
+    DispatcherRegistry,
+    FallbackReason,
+    LoadError,
+    OpContract,
+    Param,
+    api,
+    overlaps,
+    tensor_ok,
+)
+
+__all__ = [
+    "FallbackReason",
+    "LoadError",
+    "biased_grouped_topk",
+    "deepseek_v2_fp8_moe",
+    "fused_moe",
+    "init",
+    "per_group_quant_fp8",
+    "per_group_quant_mxfp8",
+    "qwen3_moe_fp8_moe",
+]
+
+FP8 = torch.float8_e4m3fn
+BF16 = torch.bfloat16
+MAX_TOKENS = 65536
+
+
+def init() -> None:
+    """Start the runtime once per process (probe the device, load the library, open the ops)."""
+    DispatcherRegistry.default().init_once()
+
+
+def _attr_name(value: Any) -> Any:
+    """An enum-like attr by its lower-case name, so engine enums match strings (the reference's
+    attr_value, aklr/core/contract/spec/_points.py:45-59)."""
+    name = getattr(value, "name", None)
+    return name.lower() if isinstance(name, str) else (value.lower() if isinstance(value, str) else value)
+
+
+def _fp8_weights_key(call: Mapping[str, Any], hidden: int, device) -> tuple | None:
+    """(experts, inter) when w1/w2 and their 128 x 128 block scales are well formed, row-major."""
+    w1, w2, s1, s2 = call["w1"], call["w2"], call["w1_scale"], call["w2_scale"]
+    if not (tensor_ok(w1, FP8, 3, device) and tensor_ok(w2, FP8, 3, device)):
+        return None
+    if not (tensor_ok(s1, torch.float32, 3, device) and tensor_ok(s2, torch.float32, 3, device)):
+        return None
+    # the aiter-shuffled layout (16 x 16 tiles) is another layout variant, not served here
+    if getattr(w1, "is_shuffled", False) or getattr(w2, "is_shuffled", False):
+        return None
+    e, two_i, h = w1.shape
+    inter = two_i // 2
+    if h != hidden or two_i % 256 or hidden % 128 or not (128 <= inter <= 16384 and 128 <= hidden <= 16384):
+        return None
+    if tuple(w2.shape) != (e, hidden, inter):
+        return None
+    if tuple(s1.shape) != (e, two_i // 128, hidden // 128) or tuple(s2.shape) != (e, hidden // 128, inter // 128):
+        return None
+    return e, inter
+
+
+# --------------------------------------------------------------------------------------------------
+# deepseek_v2_fp8_moe@1.0  (aklr/plugins/sglang/models/deepseek_v2/contract.py:188-320)
+# --------------------------------------------------------------------------------------------------
+def _deepseek_key(call):
+    x, rw, bias = call["hidden_states"], call["router_weight"], call["correction_bias"]
+    if not tensor_ok(x, BF16, 2):
+        return None
+    device = x.device
+    n_tokens, hidden = x.shape
+    if not (1 <= n_tokens <= MAX_TOKENS):
+        return None
+    if not tensor_ok(rw, BF16, 2, device) or rw.shape[1] != hidden:
+        return None
+    n_routed = rw.shape[0]
+    if not tensor_ok(bias, BF16, 1, device) or bias.shape[0] != n_routed:
+        return None
+    weights = _fp8_weights_key(call, hidden, device)
+    if weights is None or weights[0] != n_routed + 1 or not (1 <= n_routed <= 1024):
+        return None
+    topk, groups, topk_group = call["topk"], call["num_expert_group"], call["topk_group"]
+    if not all(isinstance(v, int) and not isinstance(v, bool) for v in (topk, groups, topk_group)):
+        return None
+    if _attr_name(call["scoring_func"]) != "sigmoid" or not isinstance(call["renormalize"], bool):
+        return None
+    factor = call["routed_scaling_factor"]
+    if not isinstance(factor, (int, float)) or not math.isfinite(factor) or factor <= 0:
+        return None
+    if (
+        groups < 1
+        or groups > 32
+        or n_routed % groups
+        or (groups > 1 and n_routed // groups < 2)
+        or not (1 <= topk_group <= groups)
+        or not (1 <= topk <= min(31, topk_group * (n_routed // groups)))
+    ):
+        return None
+    return ("row_major", hidden, n_routed, weights[1], topk, groups, topk_group, call["renormalize"], float(factor))
+
+
+def _layer_alloc(call, key):
+    return torch.empty_like(call["hidden_states"])
+
+
+def _deepseek_run(call, out):
+    x = call["hidden_states"]
+    logits = moe.router_logits(x, call["router_weight"])
+    routing = moe.Routing(
+        topk=call["topk"],
+        scoring="sigmoid",
+        n_shared=1,
+        num_expert_group=call["num_expert_group"],
+        topk_group=call["topk_group"],
+        renormalize=call["renormalize"],
+        routed_scaling_factor=float(call["routed_scaling_factor"]),
+    )
+    moe.fused_moe_fp8(
+        x, logits, call["correction_bias"], call["w1"], call["w1_scale"], call["w2"], call["w2_scale"], routing, out=out
+    )
+
+
+DEEPSEEK_V2_FP8_MOE = OpContract(
+    contract_id="deepseek_v2_fp8_moe@1.0",
+    description=(
+        "sglang's DeepseekV2MoE on one rank with fp8 experts at a scale per 128 x 128 block and the "
+        "shared expert in their last slot: router logits in bf16, sigmoid scores + correction bias, "
+        "grouped top-k, renormalised unbiased scores x routed_scaling_factor, shared expert at "
+        "weight 1; each expert down(silu(gate(x)) * up(x)) with both linears' inputs in bf16 then "
+        "fp8 per 1 x 128 at amax/448."
+    ),
+    params=[
+        Param("hidden_states"),
+        Param("router_weight"),
+        Param("correction_bias"),
+        Param("w1"),
+        Param("w1_scale"),
+        Param("w2"),
+        Param("w2_scale"),
+        Param("topk"),
+        Param("num_expert_group"),
+        Param("topk_group"),
+        Param("renormalize"),
+        Param("scoring_func"),
+        Param("routed_scaling_factor"),
+    ],
+    outputs=["out"],
+    key=_deepseek_key,
+    alloc=_layer_alloc,
+    run=_deepseek_run,
+)
+
+
+@api(DEEPSEEK_V2_FP8_MOE)
+def deepseek_v2_fp8_moe(
+    hidden_states,
+    router_weight,
+    correction_bias,
+    w1,
+    w1_scale,
+    w2,
+    w2_scale,
+    topk,
+    num_expert_group,
+    topk_group,
+    renormalize,
+    scoring_func,
+    routed_scaling_factor,
+): ...
+
+
+# --------------------------------------------------------------------------------------------------
+# qwen3_moe_fp8_moe@1.0  (aklr/plugins/sglang/models/qwen3_moe/contract.py:61-146; topk 2 added
+# for the Mixtral-shaped configuration)
+# --------------------------------------------------------------------------------------------------
+def _qwen3_key(call):
+    x, rw = call["hidden_states"], call["router_weight"]
+    if not tensor_ok(x, BF16, 2):
+        return None
+    device = x.device
+    n_tokens, hidden = x.shape
+    if not (1 <= n_tokens <= MAX_TOKENS) or not tensor_ok(rw, BF16, 2, device) or rw.shape[1] != hidden:
+        return None
+    n_routed = rw.shape[0]
+    weights = _fp8_weights_key(call, hidden, device)
+    if weights is None or weights[0] != n_routed or not (1 <= n_routed <= 1024):
+        return None
+    topk = call["topk"]
+    if not isinstance(topk, int) or isinstance(topk, bool) or not (1 <= topk <= min(32, n_routed)):
+        return None
+    return ("row_major", hidden, n_routed, weights[1], topk)
+
+
+def _qwen3_run(call, out):
+    x = call["hidden_states"]
+    logits = moe.router_logits(x, call["router_weight"])
+    moe.fused_moe_fp8(
+        x, logits, None, call["w1"], call["w1_scale"], call["w2"], call["w2_scale"], moe.Routing(topk=call["topk"]), out=out
+    )
+
+
+QWEN3_MOE_FP8_MOE = OpContract(
+    contract_id="qwen3_moe_fp8_moe@1.0",
+    description=(
+        "sglang's Qwen3MoeSparseMoeBlock on one rank with fp8 experts at a scale per 128 x 128 block: "
+        "bf16 router logits, top-k by logit (ties to the lower id), softmax over the chosen, experts as "
+        "in deepseek_v2_fp8_moe."
+    ),
+    params=[
+        Param("hidden_states"),
+        Param("router_weight"),
+        Param("w1"),
+        Param("w1_scale"),
+        Param("w2"),
+        Param("w2_scale"),
+        Param("topk", 8),
+    ],
+    outputs=["out"],
+    key=_qwen3_key,
+    alloc=_layer_alloc,
+    run=_qwen3_run,
+)
+
+
+@api(QWEN3_MOE_FP8_MOE)
+def qwen3_moe_fp8_moe(
+    hidden_states,
+    router_weight,
+    w1,
+    w1_scale,
+    w2,
+    w2_scale,
+    topk=8,
+): ...
+
+
+# --------------------------------------------------------------------------------------------------
+# fused_moe@1.0 -- experts only, routing given (aklr/ops/fused_moe/contract.py:75-300).  The
+# reference's Points are MXFP4 (quant_type per_1x32); this build serves the FP8 block-scaled
+# format, quant_type "per_128x128" (the aiter enum name sglang passes for it,
+# aklr/plugins/sglang/models/deepseek_v2/baseline.py:159).
+# --------------------------------------------------------------------------------------------------
+def _fused_moe_key(call):
+    x = call["hidden_states"]
+    if not tensor_ok(x, BF16, 2):
+        return None
+    device = x.device
+    n_tokens, hidden = x.shape
+    if not (1 <= n_tokens <= MAX_TOKENS):
+        return None
+    if _attr_name(call["quant_type"]) != "per_128x128" or _attr_name(call["activation"]) not in ("silu", None):
+        return None
+    if call["w1_scale"] is None or call["w2_scale"] is None:
+        return None
+    weights = _fp8_weights_key(call, hidden, device)
+    if weights is None:
+        return None
+    unsupported = ("a1_scale", "a2_scale", "bias1", "bias2", "swiglu_limit", "beta", "linear_beta", "num_local_tokens")
+    if any(call[name] is not None for name in unsupported) or call["doweight_stage1"]:
+        return None
+    if call["gate_mode"] not in (None, "separated") or call["out_dtype"] not in (None, BF16):
+        return None
+    ids, wts = call["topk_ids"], call["topk_weights"]
+    if not tensor_ok(ids, torch.int32, 2, device) or not tensor_ok(wts, torch.float32, 2, device):
+        return None
+    if ids.shape != wts.shape or ids.shape[0] != n_tokens or not (1 <= ids.shape[1] <= 32):
+        return None
+    mask = call["expert_mask"]
+    global_experts = weights[0]
+    if mask is not None:
+        if not tensor_ok(mask, torch.int32, 1, device):
+            return None
+        global_experts = mask.shape[0]
+    out = call["out"]
+    if out is not None:
+        if not tensor_ok(out, BF16, 2, device) or out.shape != x.shape:
+            return None
+        if any(isinstance(v, torch.Tensor) and overlaps(out, v) for k, v in call.items() if k != "out"):
+            return None
+    return ("row_major", hidden, weights[0], weights[1], ids.shape[1], global_experts, mask is not None)
+
+
+def _fused_moe_alloc(call, key):
+    return call["out"] if call["out"] is not None else torch.empty_like(call["hidden_states"])
+
+
+def _fused_moe_run(call, out):
+    mask = call["expert_mask"]
+    expert_map = None
+    if mask is not None:  # a global id to its slot in w1, -1 off this rank (fused_moe/reference.py:78-84)
+        expert_map = torch.where(mask == 1, torch.cumsum(mask, 0, dtype=torch.int32) - 1, -1).to(torch.int32)
+    moe.fused_experts_fp8(
+        call["hidden_states"],
+        call["topk_ids"],
+        call["topk_weights"],
+        call["w1"],
+        call["w1_scale"],
+        call["w2"],
+        call["w2_scale"],
+        expert_map=expert_map,
+        out=out,
+    )
+
+
+FUSED_MOE = OpContract(
+    contract_id="fused_moe@1.0",
+    description="Each token through its top-k experts given the routing, weighted, summed (FP8 128 x 128 experts).",
+    params=[
+        Param("hidden_states"),
+        Param("w1"),
+        Param("w2"),
+        Param("topk_weights"),
+        Param("topk_ids"),
+        Param("expert_mask", None),
+        Param("activation", None),
+        Param("quant_type", None),
+        Param("doweight_stage1", False),
+        Param("w1_scale", None),
+        Param("w2_scale", None),
+        Param("a1_scale", None),
+        Param("a2_scale", None),
+        Param("bias1", None),
+        Param("bias2", None),
+        Param("swiglu_limit", None),
+        Param("beta", None),
+        Param("linear_beta", None),
+        Param("gate_mode", None),
+        Param("out_dtype", None),
+        Param("num_local_tokens", None),
+        Param("act_quant", 4),
+        Param("out", None),
+    ],
+    outputs=["out"],
+    key=_fused_moe_key,
+    alloc=_fused_moe_alloc,
+    run=_fused_moe_run,
+)
+
+
+@api(FUSED_MOE)
+def fused_moe(
+    hidden_states,
+    w1,
+    w2,
+    topk_weights,
+    topk_ids,
+    expert_mask=None,
+    activation=None,
+    quant_type=None,
+    doweight_stage1=False,
+    w1_scale=None,
+    w2_scale=None,
+    a1_scale=None,
+    a2_scale=None,
+    bias1=None,
+    bias2=None,
+    swiglu_limit=None,
+    beta=None,
+    linear_beta=None,
+    gate_mode=None,
+    out_dtype=None,
+    num_local_tokens=None,
+    act_quant=4,
+    out=None,
+): ...
+
+
+# --------------------------------------------------------------------------------------------------
+# biased_grouped_topk@1.0 (aklr/ops/topk/contract.py:36-109); group dropping is also served
+# --------------------------------------------------------------------------------------------------
+def _topk_key(call):
+    logits, bias = call["router_logits"], call["correction_bias"]
+    if not tensor_ok(logits, (BF16, torch.float32), 2):
+        return None
+    device = logits.device
+    n_tokens, n_experts = logits.shape
+    if not (1 <= n_tokens <= MAX_TOKENS and 1 <= n_experts <= 1024):
+        return None
+    if not tensor_ok(bias, (BF16, torch.float32), 1, device) or bias.shape[0] != n_experts:
+        return None
+    wts, ids = call["topk_weights"], call["topk_ids"]
+    if not tensor_ok(wts, torch.float32, 2, device) or not tensor_ok(ids, torch.int32, 2, device):
+        return None
+    if wts.shape != ids.shape or wts.shape[0] != n_tokens or not (1 <= wts.shape[1] <= 32):
+        return None
+    if overlaps(wts, logits) or overlaps(ids, logits) or overlaps(wts, ids):
+        return None
+    groups, topk_group, topk = call["num_expert_group"], call["topk_group"], wts.shape[1]
+    if not (isinstance(groups, int) and isinstance(topk_group, int) and isinstance(call["renormalize"], bool)):
+        return None
+    if groups < 1 or groups > 32 or n_experts % groups or not (1 <= topk_group <= groups):
+        return None
+    if groups > 1 and topk_group < groups and n_experts // groups < 2:
+        return None
+    if topk > topk_group * (n_experts // groups):
+        return None
+    factor = call["routed_scaling_factor"]
+    if not isinstance(factor, (int, float)) or not math.isfinite(factor):
+        return None
+    return (str(logits.dtype), str(bias.dtype), n_experts, topk, groups, topk_group, call["renormalize"])
+
+
+def _topk_alloc(call, key):
+    return call["topk_weights"], call["topk_ids"]
+
+
+def _topk_run(call, outputs):
+    routing = moe.Routing(
+        topk=call["topk_weights"].shape[1],
+        scoring="sigmoid",
+        num_expert_group=call["num_expert_group"],
+        topk_group=call["topk_group"],
+        renormalize=call["renormalize"],
+        routed_scaling_factor=float(call["routed_scaling_factor"]),
+    )
+    moe.route(call["router_logits"], call["correction_bias"], routing, call["topk_ids"], call["topk_weights"])
+
+
+BIASED_GROUPED_TOPK = OpContract(
+    contract_id="biased_grouped_topk@1.0",
+    description="Each token's top-k experts by sigmoid score + bias (ties to the lower expert), weighted by the unbiased scores.",
+    params=[
+        Param("router_logits"),
+        Param("correction_bias"),
+        Param("topk_weights"),
+        Param("topk_ids"),
+        Param("num_expert_group"),
+        Param("topk_group"),
+        Param("renormalize"),
+        Param("routed_scaling_factor", 1.0),
+    ],
+    outputs=["topk_weights", "topk_ids"],
+    key=_topk_key,
+    alloc=_topk_alloc,
+    run=_topk_run,
+)
+
+
+@api(BIASED_GROUPED_TOPK)
+def biased_grouped_topk(
+    router_logits,
+    correction_bias,
+    topk_weights,
+    topk_ids,
+    num_expert_group,
+    topk_group,
+    renormalize,
+    routed_scaling_factor=1.0,
+): ...
+
+
+# --------------------------------------------------------------------------------------------------
+# per_group_quant_fp8@1.0 / per_group_quant_mxfp8@1.0 (aklr/ops/quant/contract.py:17-76)
+# --------------------------------------------------------------------------------------------------
+def _quant_key(group: int, max_hidden: int):
+    def key(call):
+        x = call["x"]
+        if not tensor_ok(x, BF16, 2):
+            return None
+        rows, hidden = x.shape
+        if not (1 <= rows <= 131072) or hidden % group or not (group <= hidden <= max_hidden):
+            return None
+        return (hidden,)
+
+    return key
+
+
+def _quant_fp8_alloc(call, key):
+    x = call["x"]
+    rows, hidden = x.shape
+    return (
+        torch.empty((rows, hidden), dtype=FP8, device=x.device),
+        torch.empty((hidden // 128, rows), dtype=torch.float32, device=x.device),
+    )
+
+
+def _quant_mxfp8_alloc(call, key):
+    x = call["x"]
+    rows, hidden = x.shape
+    return (
+        torch.empty((rows, hidden), dtype=FP8, device=x.device),
+        torch.empty((rows, hidden // 32), dtype=torch.uint8, device=x.device),
+    )
+
+
+PER_GROUP_QUANT_FP8 = OpContract(
+    contract_id="per_group_quant_fp8@1.0",
+    description="Groups of 128 bf16 values to e4m3 with group-major float32 scales amax*(1/448).",
+    params=[Param("x")],
+    outputs=["quantized", "scales"],
+    key=_quant_key(128, 21504),
+    alloc=_quant_fp8_alloc,
+    run=lambda call, outs: moe.per_group_quant_fp8(call["x"], outs[0], outs[1]),
+)
+
+PER_GROUP_QUANT_MXFP8 = OpContract(
+    contract_id="per_group_quant_mxfp8@1.0",
+    description="Groups of 32 bf16 values to e4m3 with row-major e8m0 scales rounded up to a power of two.",
+    params=[Param("x")],
+    outputs=["quantized", "scales"],
+    key=_quant_key(32, 21504),
+    alloc=_quant_mxfp8_alloc,
+    run=lambda call, outs: moe.per_group_quant_mxfp8(call["x"], outs[0], outs[1]),
+)
+
+
+@api(PER_GROUP_QUANT_FP8)
+def per_group_quant_fp8(x): ...
+
+
+@api(PER_GROUP_QUANT_MXFP8)
+def per_group_quant_mxfp8(x): ...
+
+
+CONTRACTS = (
+    DEEPSEEK_V2_FP8_MOE,
+    QWEN3_MOE_FP8_MOE,
+    FUSED_MOE,
+    BIASED_GROUPED_TOPK,
+    PER_GROUP_QUANT_FP8,
+    PER_GROUP_QUANT_MXFP8,
+)

@@ -111,20 +111,26 @@ def quantize_block_fp8(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     return codes, scale.reshape(*lead, rb, cb).contiguous()
 
 
-def expert_weights(cfg: MoEConfig, seed: int, device="cpu", experts_per_chunk: int = 8):
-    """(w1 e4m3 [E,2I,H], w1_scale f32 [E,2I/128,H/128], w2 e4m3 [E,H,I], w2_scale): N(0,0.02)
-    quantised per 128 x 128 block; drawn ``experts_per_chunk`` experts at a time."""
-    e_total, h, i = cfg.n_experts, cfg.hidden, cfg.inter
-    w1 = torch.empty((e_total, 2 * i, h), dtype=FP8, device=device)
-    w2 = torch.empty((e_total, h, i), dtype=FP8, device=device)
-    s1 = torch.empty((e_total, 2 * i // BLOCK, h // BLOCK), dtype=torch.float32, device=device)
-    s2 = torch.empty((e_total, h // BLOCK, i // BLOCK), dtype=torch.float32, device=device)
-    for lo in range(0, e_total, experts_per_chunk):
-        hi = min(e_total, lo + experts_per_chunk)
-        q, s = quantize_block_fp8(normal(seed, f"w1.{lo}", (hi - lo, 2 * i, h), 0.02, device))
-        w1[lo:hi], s1[lo:hi] = q, s
-        q, s = quantize_block_fp8(normal(seed, f"w2.{lo}", (hi - lo, h, i), 0.02, device))
-        w2[lo:hi], s2[lo:hi] = q, s
+def one_expert_weights(cfg: MoEConfig, seed: int, expert: int, device="cpu"):
+    """(w1 e4m3 [2I,H], w1_scale, w2 e4m3 [H,I], w2_scale) of one expert: N(0,0.02) quantised per
+    128 x 128 block.  Each expert has its own seed, so any subset can be drawn alone."""
+    h, i = cfg.hidden, cfg.inter
+    w1, s1 = quantize_block_fp8(normal(seed, f"w1.{expert}", (2 * i, h), 0.02, device))
+    w2, s2 = quantize_block_fp8(normal(seed, f"w2.{expert}", (h, i), 0.02, device))
+    return w1, s1, w2, s2
+
+
+def expert_weights(cfg: MoEConfig, seed: int, device="cpu", experts=None):
+    """(w1 e4m3 [E,2I,H], w1_scale f32 [E,2I/128,H/128], w2 e4m3 [E,H,I], w2_scale) for the expert
+    slots ``experts`` (default: all, the shared ones last)."""
+    ids = list(range(cfg.n_experts)) if experts is None else list(experts)
+    h, i = cfg.hidden, cfg.inter
+    w1 = torch.empty((len(ids), 2 * i, h), dtype=FP8, device=device)
+    w2 = torch.empty((len(ids), h, i), dtype=FP8, device=device)
+    s1 = torch.empty((len(ids), 2 * i // BLOCK, h // BLOCK), dtype=torch.float32, device=device)
+    s2 = torch.empty((len(ids), h // BLOCK, i // BLOCK), dtype=torch.float32, device=device)
+    for slot, e in enumerate(ids):
+        w1[slot], s1[slot], w2[slot], s2[slot] = one_expert_weights(cfg, seed, e, device)
     return w1, s1, w2, s2
 
 
@@ -176,6 +182,7 @@ __all__ = [
     "expert_weights",
     "expected_distinct_experts",
     "normal",
+    "one_expert_weights",
     "quantize_block_fp8",
     "roofline_work",
     "router_inputs",

@@ -146,6 +146,16 @@ int aklr_moe_act_quant_fp8(const void* x, void* q, float* scales, int32_t rows, 
  * device-side wait completed. */
 int aklr_moe_read_status(const void* workspace, int32_t* host_status, void* stream);
 
+/* Measurement aids (no counterpart in the reference, which times with rocprofiler:
+ * aklr/core/utils/testing.py:171-252).  aklr_kernel_launch_count: kernels this library has
+ * launched in this process.  aklr_profile_begin(n): record CUDA events around the six stages
+ * (route, sort, quant, gate_up, down, combine) of the next n layer calls of this process;
+ * n = 0 switches it off.  aklr_profile_read(call, ms[6]) waits for that call and gives its
+ * stage durations in milliseconds. */
+int64_t aklr_kernel_launch_count(void);
+int aklr_profile_begin(int32_t max_calls);
+int aklr_profile_read(int32_t call, float* stage_ms);
+
 #ifdef __cplusplus
 }
 #endif

@@ -350,7 +350,7 @@ def test_deepseek_v3_full_width_on_sampled_tokens(n_tokens):
 
     cfg = wl.CONFIGS["deepseek_v3"]
     d = dev()
-    w1, s1, w2, s2 = wl.expert_weights(cfg, seed=41, device=d, experts_per_chunk=4)
+    w1, s1, w2, s2 = wl.expert_weights(cfg, seed=41, device=d)
     hidden, logits, bias = wl.router_inputs(cfg, n_tokens, seed=42)
     out, ws = fused_moe_fp8(hidden.to(d), logits.to(d), bias.to(d), w1, s1, w2, s2, routing_of(cfg), return_workspace=True)
     ws.check_status()
