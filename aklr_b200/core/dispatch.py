@@ -127,6 +127,10 @@ def overlaps(a: torch.Tensor, b: torch.Tensor) -> bool:
     return a0 < b0 + b.numel() * b.element_size() and b0 < a0 + a.numel() * a.element_size()
 
 
+def _is_capturing() -> bool:
+    return torch.cuda.is_available() and torch.cuda.is_current_stream_capturing()
+
+
 class Trace:
     """AKLR_TRACE: logs each distinct dispatch (op, key, outcome) once, as the reference's
     tracer does (aklr/core/runtime/dispatch/_trace.py:36-100)."""
@@ -138,12 +142,13 @@ class Trace:
         self._lock = threading.Lock()
 
     def op(self, contract: OpContract, key, outcome) -> None:
-        item = ("op", contract.contract_id, key, outcome if isinstance(outcome, FallbackReason) else "served")
+        what = outcome.value if isinstance(outcome, FallbackReason) else "served"
+        item = ("op", contract.contract_id, key, what)
         with self._lock:
             if item in self._seen:
                 return
             self._seen.add(item)
-        _TRACE_OP.info("%s %s -> %s", contract.contract_id, key, item[3] if isinstance(item[3], str) else item[3].value)
+        _TRACE_OP.info("%s %s -> %s", contract.contract_id, key, what)
 
     def plugin(self, engine: str, target: str, route: str, fallback) -> None:
         item = ("plugin", engine, target, fallback)
@@ -204,7 +209,7 @@ class KernelDispatcher:
         key = self.contract.key(call)
         if key is None:
             return None, FallbackReason.OUT_OF_CONTRACT
-        if key not in self.warmed_keys and torch.cuda.is_current_stream_capturing():
+        if key not in self.warmed_keys and _is_capturing():
             # a Point first seen inside a graph capture would do its first-call set-up there
             return key, FallbackReason.NOT_WARMED
         return key, None

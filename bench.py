@@ -234,9 +234,16 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--sweep", action="store_true", help="also time decode/prefill token counts (extra keys)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling captures)")
+    ap.add_argument("--routed-experts", type=int, default=0, help="shrink the layer to this many routed experts (profiling captures only)")
+    ap.add_argument("--block-m", type=int, default=0, help="force the tokens-per-block of the grouped GEMMs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     cfg = wl.CONFIGS["deepseek_v3"]
+    if args.routed_experts:
+        import dataclasses
+
+        cfg = dataclasses.replace(cfg, name=f"deepseek_v3_{args.routed_experts}e", n_routed=args.routed_experts)
 
     if args.impl == "reference":
         run_reference_arm(args, cfg)
@@ -280,11 +287,11 @@ def main() -> None:
         batches.append((hidden, logits))
     bias = wl.router_inputs(cfg, 1, SEED + 1, device)[2]
     out = torch.empty((T, cfg.hidden), dtype=torch.bfloat16, device=device)
-    ws = Workspace(_config(T, cfg.hidden, cfg.inter, cfg.n_routed, routing, batches[0][1], bias), device)
+    ws = Workspace(_config(T, cfg.hidden, cfg.inter, cfg.n_routed, routing, batches[0][1], bias, args.block_m), device)
 
     def step(i):
         hidden, logits = batches[i % n_batches]
-        fused_moe_fp8(hidden, logits, bias, w1, s1, w2, s2, routing, out=out, workspace=ws)
+        fused_moe_fp8(hidden, logits, bias, w1, s1, w2, s2, routing, out=out, workspace=ws, block_m=args.block_m)
 
     for i in range(args.warmup):
         step(i)
@@ -354,51 +361,53 @@ def main() -> None:
         },
     }
 
-    # ---- end to end through the op API from pinned host buffers --------------------------------
-    host_hidden = [b[0].cpu().pin_memory() for b in batches]
-    host_out = torch.empty((T, cfg.hidden), dtype=torch.bfloat16).pin_memory()
-    dev_hidden = torch.empty_like(batches[0][0])
-    ops.init()
+    e2e = None
+    if not args.no_e2e:
+        # ---- end to end through the op API from pinned host buffers --------------------------------
+        host_hidden = [b[0].cpu().pin_memory() for b in batches]
+        host_out = torch.empty((T, cfg.hidden), dtype=torch.bfloat16).pin_memory()
+        dev_hidden = torch.empty_like(batches[0][0])
+        ops.init()
 
-    def e2e_step(i):
-        dev_hidden.copy_(host_hidden[i % n_batches], non_blocking=True)
-        result = ops.deepseek_v2_fp8_moe(
-            hidden_states=dev_hidden,
-            router_weight=router_w,
-            correction_bias=bias,
-            w1=w1,
-            w1_scale=s1,
-            w2=w2,
-            w2_scale=s2,
-            topk=cfg.topk,
-            num_expert_group=cfg.num_expert_group,
-            topk_group=cfg.topk_group,
-            renormalize=cfg.renormalize,
-            scoring_func="sigmoid",
-            routed_scaling_factor=cfg.routed_scaling_factor,
-        )
-        if not isinstance(result, torch.Tensor):
-            raise SystemExit(f"the op fell back: {result}")
-        host_out.copy_(result, non_blocking=True)
+        def e2e_step(i):
+            dev_hidden.copy_(host_hidden[i % n_batches], non_blocking=True)
+            result = ops.deepseek_v2_fp8_moe(
+                hidden_states=dev_hidden,
+                router_weight=router_w,
+                correction_bias=bias,
+                w1=w1,
+                w1_scale=s1,
+                w2=w2,
+                w2_scale=s2,
+                topk=cfg.topk,
+                num_expert_group=cfg.num_expert_group,
+                topk_group=cfg.topk_group,
+                renormalize=cfg.renormalize,
+                scoring_func="sigmoid",
+                routed_scaling_factor=cfg.routed_scaling_factor,
+            )
+            if not isinstance(result, torch.Tensor):
+                raise SystemExit(f"the op fell back: {result}")
+            host_out.copy_(result, non_blocking=True)
 
-    for i in range(args.warmup):
-        e2e_step(i)
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        e2e_step(i)
-    e1.record()
-    torch.cuda.synchronize()
-    e2e_ms = e0.elapsed_time(e1) / args.steps
-    e2e = {
-        "value": T / (e2e_ms * 1e-3),
-        "unit": UNIT,
-        "ms_per_step": e2e_ms,
-        "h2d_bytes_per_step": T * cfg.hidden * 2,
-        "d2h_bytes_per_step": T * cfg.hidden * 2,
-        "api": "aklr_b200.ops.deepseek_v2_fp8_moe (router GEMM included)",
-    }
+        for i in range(args.warmup):
+            e2e_step(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            e2e_step(i)
+        e1.record()
+        torch.cuda.synchronize()
+        e2e_ms = e0.elapsed_time(e1) / args.steps
+        e2e = {
+            "value": T / (e2e_ms * 1e-3),
+            "unit": UNIT,
+            "ms_per_step": e2e_ms,
+            "h2d_bytes_per_step": T * cfg.hidden * 2,
+            "d2h_bytes_per_step": T * cfg.hidden * 2,
+            "api": "aklr_b200.ops.deepseek_v2_fp8_moe (router GEMM included)",
+        }
 
     sweep = None
     if args.sweep:
