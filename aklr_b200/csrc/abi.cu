@@ -191,6 +191,7 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   qp.n_rows = l.capacity;
   qp.hidden = c.hidden;
   qp.routes_per_token = routes_per_token;
+  qp.block_m = l.block_m;
   rc = launch_gather_quant_fp8(qp, stream);
   if (rc) return fail(rc, "activation quant launch failed");
   g_launches += 1;

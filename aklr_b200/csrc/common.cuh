@@ -1,6 +1,6 @@
 // Shared device helpers for the sm_100a fused-MoE kernels: error codes, bounded mbarrier
 // waits, TMA / tcgen05 PTX wrappers.  Every wait in this library is bounded: after
-// AKLR_WAIT_LIMIT_NS it gives up, records where in a status word the host can read, and the
+// AKLR_WAIT_LIMIT_CYCLES it gives up, records where in a status word the host can read, and the
 // kernel drains and returns instead of hanging the device.
 #pragma once
 
@@ -20,8 +20,8 @@
 #define AKLR_ERR_KERNEL_WAIT_TIMEOUT -6
 #define AKLR_ERR_TOO_LARGE -7
 
-#ifndef AKLR_WAIT_LIMIT_NS
-#define AKLR_WAIT_LIMIT_NS 2000000000ull  // 2 s
+#ifndef AKLR_WAIT_LIMIT_CYCLES
+#define AKLR_WAIT_LIMIT_CYCLES 4000000000ll  // about 2 s of SM clock
 #endif
 
 namespace aklr {
@@ -64,21 +64,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait.  Returns false when the limit ran out or another thread of the CTA already
 // gave up (``*abort_flag`` != 0); the first to give up records ``where`` in status[0..1].
+// The loop polls mbarrier.try_wait (which itself suspends the thread for a short hardware-defined
+// time) and looks at the SM's cycle counter only every 1024 polls: reading %globaltimer or
+// sleeping here costs microseconds of wake-up latency per pipeline hand-off.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int where) {
-  for (int i = 0; i < 64; ++i)
+  long long start = 0;
+  for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t start = global_timer_ns();
-  while (true) {
-    for (int i = 0; i < 32; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (global_timer_ns() - start > AKLR_WAIT_LIMIT_NS) {
-      *abort_flag = 1;
-      if (atomicCAS(status, 0, AKLR_ERR_KERNEL_WAIT_TIMEOUT) == 0) status[1] = where;
-      return false;
+    if ((spin & 1023u) == 0u) {
+      if (*abort_flag) return false;
+      const long long now = clock64();
+      if (start == 0) start = now;
+      if (now - start > AKLR_WAIT_LIMIT_CYCLES) {
+        *abort_flag = 1;
+        if (atomicCAS(status, 0, AKLR_ERR_KERNEL_WAIT_TIMEOUT) == 0) status[1] = where;
+        return false;
+      }
     }
-    __nanosleep(64);
   }
 }
 

@@ -25,26 +25,45 @@
 
 namespace aklr {
 
+#ifdef AKLR_GEMM_TIMING
+// Development aid (never compiled into the shipped library): CTA 0 accumulates cycle counts per
+// pipeline role.  [0] producer wait-empty, [1] mma wait-full, [2] mma wait-tmem-empty, [3] mma issue,
+// [4] epi wait-tmem-full, [5] epi ld+fma, [6] epi tile set-up, [7] epi final, [8] K-blocks, [9] total
+__device__ long long g_gemm_timing[2][16];
+#define TIMING_ADD(slot, expr)                                   \
+  do {                                                           \
+    const long long t_begin_ = clock64();                        \
+    expr;                                                        \
+    if (blockIdx.x == 0) tacc[slot] += clock64() - t_begin_;     \
+  } while (0)
+#else
+#define TIMING_ADD(slot, expr) \
+  do {                         \
+    expr;                      \
+  } while (0)
+#endif
+
 constexpr int kGemmThreads = 320;
 constexpr int kEpiThreads = 256;
 constexpr int kWTileBytes = 128 * 128;  // 128 channels x 128 K bytes
 
 struct GemmSmemLayout {
   int stage_bytes, misc_bytes, total_bytes;
-  int off_misc, off_rid, off_wmax, off_bars;
+  int off_misc, off_rid, off_wmax, off_wscale, off_bars;
 };
 
 __host__ __device__ inline GemmSmemLayout gemm_layout(bool gate_up, int block_m, int k, int stages) {
   GemmSmemLayout l;
   const int kb = k / 128;
   l.stage_bytes = (gate_up ? 2 : 1) * kWTileBytes + block_m * 128;
-  const int scale_bytes = kb * block_m * 4;
+  const int scale_bytes = (gate_up ? 2 : 1) * kb * block_m * 4;  // combined scale table(s)
   const int out_bytes = block_m * 128 * (gate_up ? 1 : 2);
   l.misc_bytes = ((scale_bytes > out_bytes ? scale_bytes : out_bytes) + 127) & ~127;
   l.off_misc = stages * l.stage_bytes;
   l.off_rid = l.off_misc + l.misc_bytes;       // int[block_m]
   l.off_wmax = l.off_rid + block_m * 4;        // float[4][block_m]
-  l.off_bars = l.off_wmax + 4 * block_m * 4;   // barriers, tmem ptr, abort flag
+  l.off_wscale = l.off_wmax + 4 * block_m * 4; // float[block_m]: per-column requant inverse / route weight
+  l.off_bars = (l.off_wscale + block_m * 4 + 15) & ~15;  // barriers, tmem ptr, abort flag
   l.total_bytes = l.off_bars + (2 * stages + 4) * 8 + 16;
   return l;
 }
@@ -77,7 +96,7 @@ template <int BM, bool GATE_UP>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
   constexpr int NH = BM / 2;                        // columns per epilogue warp
-  constexpr int CH = NH >= 16 ? 16 : 8;             // columns per tcgen05.ld
+  constexpr int CH = (NH >= 16 && !(GATE_UP && BM == 128)) ? 16 : 8;  // columns per tcgen05.ld (register budget)
   constexpr int BUF_COLS = (GATE_UP ? 2 : 1) * BM;  // TMEM columns of one partial buffer
   constexpr int TMEM_COLS = 2 * BUF_COLS < 32 ? 32 : 2 * BUF_COLS;
   constexpr uint32_t IDESC = umma_idesc_e4m3(BM);
@@ -87,10 +106,11 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
   const int KB = p.k >> 7;
   const int S = p.stages;
   const GemmSmemLayout L = gemm_layout(GATE_UP, BM, p.k, S);
-  float* sx = reinterpret_cast<float*>(smem + L.off_misc);  // [KB][BM] activation scales ...
-  uint8_t* out_tile = smem + L.off_misc;                    // ... aliased by the output tile
+  float* ftab = reinterpret_cast<float*>(smem + L.off_misc);  // [tiles][KB][BM] combined scales ...
+  uint8_t* out_tile = smem + L.off_misc;                      // ... aliased by the output tile
   int* rid_s = reinterpret_cast<int*>(smem + L.off_rid);
   float* wmax = reinterpret_cast<float*>(smem + L.off_wmax);
+  float* colscale = reinterpret_cast<float*>(smem + L.off_wscale);  // [BM]
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.off_bars);
   uint64_t* empty = full + S;
   uint64_t* tmem_full = empty + S;
@@ -132,6 +152,10 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+#ifdef AKLR_GEMM_TIMING
+      long long tacc[16] = {0};
+      const long long t_role = clock64();
+#endif
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const int j = t / nb, b = t - j * nb;
         const int e = p.block_expert[b];
@@ -139,7 +163,9 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
-          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
+          bool got;
+          TIMING_ADD(0, got = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1));
+          if (!got) { ok = false; break; }
           uint8_t* st = smem + s * L.stage_bytes;
           mbar_expect_tx(&full[s], L.stage_bytes);
           tma_load_2d(st, &p.map_w, &full[s], kb * 128, w_row);
@@ -147,20 +173,36 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
           tma_load_2d(st + (GATE_UP ? 2 : 1) * kWTileBytes, &p.map_x, &full[s], kb * 128, b * BM);
         }
       }
+#ifdef AKLR_GEMM_TIMING
+      if (blockIdx.x == 0) {
+        g_gemm_timing[GATE_UP][0] = tacc[0];
+        g_gemm_timing[GATE_UP][8] = it;
+        g_gemm_timing[GATE_UP][9] = clock64() - t_role;
+      }
+#endif
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer --------------------------------------------
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+#ifdef AKLR_GEMM_TIMING
+      long long tacc[16] = {0};
+#endif
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
           const int buf = it & 1;
           const uint32_t bph = (it >> 1) & 1;
-          if (!mbar_wait(&full[s], ph, abort_flag, p.status, 2)) { ok = false; break; }
-          if (!mbar_wait(&tmem_empty[buf], bph ^ 1, abort_flag, p.status, 3)) { ok = false; break; }
+          bool got;
+          TIMING_ADD(1, got = mbar_wait(&full[s], ph, abort_flag, p.status, 2));
+          if (!got) { ok = false; break; }
+          TIMING_ADD(2, got = mbar_wait(&tmem_empty[buf], bph ^ 1, abort_flag, p.status, 3));
+          if (!got) { ok = false; break; }
+#ifdef AKLR_GEMM_TIMING
+          const long long t_issue = clock64();
+#endif
           tc_fence_after_sync();
           const uint32_t a0 = smem_u32(smem + s * L.stage_bytes);
           const uint64_t da0 = umma_desc_sw128(a0);
@@ -174,8 +216,15 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
           }
           tc_commit(&empty[s]);         // the stage is free once these MMAs have read it
           tc_commit(&tmem_full[buf]);   // and the partial is complete
+#ifdef AKLR_GEMM_TIMING
+          tacc[3] += clock64() - t_issue;
+#endif
         }
       }
+#ifdef AKLR_GEMM_TIMING
+      if (blockIdx.x == 0)
+        for (int i = 1; i <= 3; ++i) g_gemm_timing[GATE_UP][i] = tacc[i];
+#endif
     }
   } else {
     // ------------------------------- epilogue warps ----------------------------------------
@@ -186,88 +235,135 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
     const int chan = quarter * 32 + lane;    // output channel inside the tile = TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const int IB = p.out_dim >> 7;           // gate_up: 128-blocks of the intermediate size
+    constexpr int TILES = GATE_UP ? 2 : 1;
+    constexpr int CPT = NH / CH;             // chunks per accumulator tile
+    constexpr int NC = TILES * CPT;          // chunks per K-block
     uint32_t it = 0;
     bool bad = false;
+#ifdef AKLR_GEMM_TIMING
+    long long tacc[16] = {0};
+    long long t_mark = clock64();
+#endif
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+#ifdef AKLR_GEMM_TIMING
+      tacc[7] += clock64() - t_mark;
+      t_mark = clock64();
+#endif
       if (epi_bar_any(*abort_flag)) break;   // also fences the aliased smem against the last tile
       const int j = t / nb, b = t - j * nb;
       const int e = p.block_expert[b];
-      for (int i = et; i < BM * KB; i += kEpiThreads) {
-        const int n = i / KB, kb = i - n * KB;
-        sx[kb * BM + n] = p.x_scale[static_cast<size_t>(b * BM + n) * KB + kb];
-      }
-      if (et < BM) rid_s[et] = p.sorted_ids[b * BM + et];
-      epi_bar_sync();
-
-      float acc0[NH], acc1[GATE_UP ? NH : 1];
+      // Combined scale table of the tile, ftab[tile][kb][n] = activation scale x weight block
+      // scale, so the K loop is one shared-memory float4 per four columns and one FMA per element.
+      {
+        const float* ws0 = p.w_scale + (static_cast<size_t>(e) * (p.rows_per_expert >> 7) + j) * KB;
+        const float* xs = p.x_scale + static_cast<size_t>(b) * KB * BM;  // [kb][n] of this block
+        constexpr int kBatch = 4;  // loads of a batch are issued together: one L2 round trip, not four
+        for (int base = et; base < BM * KB; base += kEpiThreads * kBatch) {
+          float s[kBatch], w0[kBatch], w1[kBatch];
 #pragma unroll
-      for (int i = 0; i < NH; ++i) acc0[i] = 0.0f;
-      if (GATE_UP) {
-#pragma unroll
-        for (int i = 0; i < NH; ++i) acc1[i] = 0.0f;
-      }
-      const float* ws0 = p.w_scale + (static_cast<size_t>(e) * (p.rows_per_expert >> 7) + j) * KB;
-      const float* ws1 = ws0 + static_cast<size_t>(IB) * KB;  // the up rows' blocks (gate_up only)
-
-      for (int kb = 0; kb < KB; ++kb, ++it) {
-        const int buf = it & 1;
-        const uint32_t bph = (it >> 1) & 1;
-        if (!mbar_wait(&tmem_full[buf], bph, abort_flag, p.status, 4)) bad = true;
-        tc_fence_after_sync();
-        const float sw0 = __ldg(ws0 + kb);
-        const float sw1 = GATE_UP ? __ldg(ws1 + kb) : 0.0f;
-        const float* sxk = sx + kb * BM + half * NH;
-        const uint32_t t0 = tmem_base + lane_addr + buf * BUF_COLS + half * NH;
-#pragma unroll
-        for (int c = 0; c < NH; c += CH) {
-          uint32_t r0[CH], r1[CH];
-          if (CH == 16) {
-            AKLR_TMEM_LD_16(t0 + c, r0);
-            if (GATE_UP) AKLR_TMEM_LD_16(t0 + BM + c, r1);
-          } else {
-            AKLR_TMEM_LD_8(t0 + c, r0);
-            if (GATE_UP) AKLR_TMEM_LD_8(t0 + BM + c, r1);
-          }
-          tc_wait_ld();
-          if (c + CH >= NH) {  // last chunk read: hand the buffer back to the MMA warp
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+          for (int u = 0; u < kBatch; ++u) {
+            const int i = base + u * kEpiThreads;
+            const bool in = i < BM * KB;
+            const int kb = in ? i / BM : 0;
+            s[u] = in ? __ldg(xs + i) : 0.0f;
+            w0[u] = __ldg(ws0 + kb);
+            w1[u] = GATE_UP ? __ldg(ws0 + static_cast<size_t>(IB) * KB + kb) : 0.0f;
           }
 #pragma unroll
-          for (int i = 0; i < CH; i += 4) {
-            const float4 s4 = *reinterpret_cast<const float4*>(sxk + c + i);
-            const float s[4] = {s4.x, s4.y, s4.z, s4.w};
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              acc0[c + i + q] = fmaf(__uint_as_float(r0[i + q]), s[q] * sw0, acc0[c + i + q]);
-              if (GATE_UP) acc1[c + i + q] = fmaf(__uint_as_float(r1[i + q]), s[q] * sw1, acc1[c + i + q]);
+          for (int u = 0; u < kBatch; ++u) {
+            const int i = base + u * kEpiThreads;
+            if (i < BM * KB) {
+              ftab[i] = s[u] * w0[u];
+              if (GATE_UP) ftab[BM * KB + i] = s[u] * w1[u];
             }
           }
         }
       }
+      if (et < BM) {
+        const int rid = p.sorted_ids[b * BM + et];
+        rid_s[et] = rid;
+        if (!GATE_UP) colscale[et] = rid >= 0 ? p.topk_weights[rid] : 0.0f;
+      }
+      epi_bar_sync();
 
-      epi_bar_sync();  // every warp is done with the activation scales: the region becomes the out tile
+#ifdef AKLR_GEMM_TIMING
+      tacc[6] += clock64() - t_mark;
+#endif
+      float acc[TILES][NH];
+#pragma unroll
+      for (int a = 0; a < TILES; ++a)
+#pragma unroll
+        for (int i = 0; i < NH; ++i) acc[a][i] = 0.0f;
+
+      for (int kb = 0; kb < KB; ++kb, ++it) {
+        const int buf = it & 1;
+        const uint32_t bph = (it >> 1) & 1;
+        bool got;
+        TIMING_ADD(4, got = mbar_wait(&tmem_full[buf], bph, abort_flag, p.status, 4));
+        if (!got) bad = true;
+        tc_fence_after_sync();
+#ifdef AKLR_GEMM_TIMING
+        const long long t_work = clock64();
+#endif
+        const float* fk = ftab + kb * BM + half * NH;
+        const uint32_t t0 = tmem_base + lane_addr + buf * BUF_COLS + half * NH;
+        // software pipeline: the load of chunk k+1 is in flight while chunk k is folded in
+        uint32_t r[2][CH];
+        if (CH == 16) AKLR_TMEM_LD_16(t0, r[0]); else AKLR_TMEM_LD_8(t0, r[0]);
+#pragma unroll
+        for (int k = 0; k < NC; ++k) {
+          tc_wait_ld();
+          if (k + 1 < NC) {
+            const uint32_t at = t0 + ((k + 1) / CPT) * BM + ((k + 1) % CPT) * CH;
+            if (CH == 16) AKLR_TMEM_LD_16(at, r[(k + 1) & 1]); else AKLR_TMEM_LD_8(at, r[(k + 1) & 1]);
+          } else {  // everything is read: hand the buffer back to the MMA warp
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+          }
+          const int a = k / CPT, c = (k % CPT) * CH;
+          const float* f = fk + a * (BM * KB) + c;
+#pragma unroll
+          for (int i = 0; i < CH; i += 4) {
+            const float4 f4 = *reinterpret_cast<const float4*>(f + i);
+            acc[a][c + i + 0] = fmaf(__uint_as_float(r[k & 1][i + 0]), f4.x, acc[a][c + i + 0]);
+            acc[a][c + i + 1] = fmaf(__uint_as_float(r[k & 1][i + 1]), f4.y, acc[a][c + i + 1]);
+            acc[a][c + i + 2] = fmaf(__uint_as_float(r[k & 1][i + 2]), f4.z, acc[a][c + i + 2]);
+            acc[a][c + i + 3] = fmaf(__uint_as_float(r[k & 1][i + 3]), f4.w, acc[a][c + i + 3]);
+          }
+        }
+#ifdef AKLR_GEMM_TIMING
+        tacc[5] += clock64() - t_work;
+#endif
+      }
+#ifdef AKLR_GEMM_TIMING
+      t_mark = clock64();
+#endif
+
+      epi_bar_sync();  // every warp is done with the scale table: the region becomes the out tile
       if (GATE_UP) {
         // h = silu(gate) * up, rounded to bf16; then 1 x 128 requant over this tile's 128 channels
 #pragma unroll
         for (int i = 0; i < NH; ++i) {
-          const float g = acc0[i];
-          const float h = __fdiv_rn(g, 1.0f + __expf(-g)) * acc1[i];
-          acc0[i] = __bfloat162float(__float2bfloat16_rn(h));
-          const float m = warp_max_nonneg(fabsf(acc0[i]));
+          const float g = acc[0][i];
+          const float h = __fdividef(g, 1.0f + __expf(-g)) * acc[TILES - 1][i];
+          acc[0][i] = __bfloat162float(__float2bfloat16_rn(h));
+          const float m = warp_max_nonneg(fabsf(acc[0][i]));
           if (lane == 0) wmax[quarter * BM + half * NH + i] = m;
+        }
+        epi_bar_sync();
+        if (et < BM) {  // one thread per token column: its scale, stored for the down projection
+          const float m = fmaxf(fmaxf(wmax[et], wmax[BM + et]), fmaxf(wmax[2 * BM + et], wmax[3 * BM + et]));
+          const float scale = fmaxf(__fdiv_rn(m, 448.0f), FLT_MIN);
+          colscale[et] = __fdiv_rn(1.0f, scale);
+          if (rid_s[et] >= 0 && !bad) p.out_scale[(static_cast<size_t>(b) * IB + j) * BM + et] = scale;
         }
         epi_bar_sync();
 #pragma unroll
         for (int i = 0; i < NH; ++i) {
           const int n = half * NH + i;
-          const float m = fmaxf(fmaxf(wmax[n], wmax[BM + n]), fmaxf(wmax[2 * BM + n], wmax[3 * BM + n]));
-          const float scale = fmaxf(__fdiv_rn(m, 448.0f), FLT_MIN);
           out_tile[n * 128 + chan] = static_cast<uint8_t>(
-              __nv_cvt_float_to_fp8(__fdiv_rn(acc0[i], scale), __NV_SATFINITE, __NV_E4M3));
-          if (chan == 0 && rid_s[n] >= 0 && !bad)
-            p.out_scale[static_cast<size_t>(b * BM + n) * IB + j] = scale;
+              __nv_cvt_float_to_fp8(acc[0][i] * colscale[n], __NV_SATFINITE, __NV_E4M3));
         }
         epi_bar_sync();
         for (int i = et; i < BM * 8; i += kEpiThreads) {  // 16 bytes per thread, 8 per row
@@ -281,9 +377,7 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
 #pragma unroll
         for (int i = 0; i < NH; ++i) {
           const int n = half * NH + i;
-          const int rid = rid_s[n];
-          const float w = rid >= 0 ? __ldg(p.topk_weights + rid) : 0.0f;
-          out16[n * 128 + chan] = __float2bfloat16_rn(acc0[i] * w);
+          out16[n * 128 + chan] = __float2bfloat16_rn(acc[0][i] * colscale[n]);
         }
         epi_bar_sync();
         for (int i = et; i < BM * 16; i += kEpiThreads) {  // 16 bytes per thread, 16 per row
@@ -296,6 +390,10 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
         }
       }
     }
+#ifdef AKLR_GEMM_TIMING
+    if (blockIdx.x == 0 && warp == 2 && lane == 0)
+      for (int i = 4; i <= 7; ++i) g_gemm_timing[GATE_UP][i] = tacc[i];
+#endif
   }
 
   tc_fence_before_sync();
@@ -332,6 +430,12 @@ static int launch_grouped(const GroupedGemmParams& p, int sm_count, cudaStream_t
     default: return AKLR_ERR_UNSUPPORTED_SHAPE;
   }
 }
+
+#ifdef AKLR_GEMM_TIMING
+extern "C" int aklr_debug_read_gemm_timing(long long* host32) {
+  return cudaMemcpyFromSymbol(host32, g_gemm_timing, sizeof(g_gemm_timing)) == cudaSuccess ? 0 : -3;
+}
+#endif
 
 int launch_grouped_gemm_gate_up(const GroupedGemmParams& p, int sm_count, cudaStream_t stream) {
   return launch_grouped<true>(p, sm_count, stream);

@@ -46,8 +46,8 @@ struct GatherQuantParams {
   const int32_t* sorted_ids;  // [capacity] or null: row r reads token r
   const int32_t* num_rows;    // device count of rows in use (null: n_rows)
   uint8_t* q;                 // [rows, hidden] e4m3
-  float* scales;              // [rows, hidden/128]
-  int n_rows, hidden, routes_per_token;
+  float* scales;              // block_m == 0: [rows, hidden/128]; else [rows/block_m, hidden/128, block_m]
+  int n_rows, hidden, routes_per_token, block_m;
 };
 int launch_gather_quant_fp8(const GatherQuantParams& p, cudaStream_t stream);
 
@@ -61,13 +61,13 @@ struct GroupedGemmParams {
   CUtensorMap map_w;   // weights flattened to [experts*rows_per_expert, k], box 128 x 128
   CUtensorMap map_x;   // activations [capacity, k] e4m3, box block_m x 128
   const float* w_scale;        // [experts, rows_per_expert/128, k/128]
-  const float* x_scale;        // [capacity, k/128]
+  const float* x_scale;        // [max_blocks, k/128, block_m]
   const int32_t* sorted_ids;   // [capacity]
   const int32_t* block_expert; // [max_blocks]
   const int32_t* num_blocks;   // device count
   const float* topk_weights;   // [n_routes] (down projection only)
   uint8_t* out_q;              // gate_up: [capacity, inter] e4m3
-  float* out_scale;            // gate_up: [capacity, inter/128]
+  float* out_scale;            // gate_up: [max_blocks, inter/128, block_m]
   void* out_rows;              // down: [n_routes, hidden] bf16 per-route contributions
   int32_t* status;             // [2] error word + location
   int k;                       // reduction length (hidden for gate_up, inter for down)

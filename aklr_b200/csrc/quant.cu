@@ -69,7 +69,12 @@ __global__ void __launch_bounds__(256) gather_quant_fp8_kernel(GatherQuantParams
 #pragma unroll
     for (int i = 0; i < 8; ++i) v[i] = __fdiv_rn(v[i], scale);
     *reinterpret_cast<uint2*>(p.q + static_cast<size_t>(row) * p.hidden + grp * 128 + sub * 8) = pack8_e4m3(v);
-    if (sub == 0) p.scales[static_cast<size_t>(row) * groups_per_row + grp] = scale;
+    if (sub == 0) {
+      if (p.block_m > 0)  // [block][group][row in block]: what the grouped GEMM stages per tile
+        p.scales[(static_cast<size_t>(row / p.block_m) * groups_per_row + grp) * p.block_m + row % p.block_m] = scale;
+      else
+        p.scales[static_cast<size_t>(row) * groups_per_row + grp] = scale;
+    }
   }
 }
 

@@ -144,19 +144,19 @@ class Workspace:
     def block_expert(self) -> torch.Tensor:
         return self._view(self.layout.block_expert, self.num_blocks(), torch.int32)
 
+    def _row_scales(self, offset: int, groups: int) -> torch.Tensor:
+        """Scales stored [block, group, row-in-block], returned as [row, group]."""
+        blocks, bm = self.layout.max_blocks, self.layout.block_m
+        stored = self._view(offset, blocks * groups * bm, torch.float32).view(blocks, groups, bm)
+        return stored.permute(0, 2, 1).reshape(blocks * bm, groups)
+
     def xq(self) -> tuple[torch.Tensor, torch.Tensor]:
         rows, h = self.layout.capacity, self.cfg.hidden
-        return (
-            self._view(self.layout.xq, rows * h, FP8).view(rows, h),
-            self._view(self.layout.xs, rows * (h // 128), torch.float32).view(rows, h // 128),
-        )
+        return self._view(self.layout.xq, rows * h, FP8).view(rows, h), self._row_scales(self.layout.xs, h // 128)
 
     def hq(self) -> tuple[torch.Tensor, torch.Tensor]:
         rows, i = self.layout.capacity, self.cfg.inter
-        return (
-            self._view(self.layout.hq, rows * i, FP8).view(rows, i),
-            self._view(self.layout.hs, rows * (i // 128), torch.float32).view(rows, i // 128),
-        )
+        return self._view(self.layout.hq, rows * i, FP8).view(rows, i), self._row_scales(self.layout.hs, i // 128)
 
     def route_rows(self) -> torch.Tensor:
         n = self.cfg.n_tokens * self.routes_per_token

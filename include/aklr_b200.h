@@ -71,9 +71,9 @@ typedef struct aklr_moe_workspace_layout {
   int64_t num_blocks;    /* int32 [2] blocks in use, rows in use */
   int64_t chunk_hist;    /* int32 sort scratch */
   int64_t xq;            /* e4m3 [capacity, hidden] */
-  int64_t xs;            /* float [capacity, hidden/128] */
+  int64_t xs;            /* float [max_blocks, hidden/128, block_m] */
   int64_t hq;            /* e4m3 [capacity, inter] */
-  int64_t hs;            /* float [capacity, inter/128] */
+  int64_t hs;            /* float [max_blocks, inter/128, block_m] */
   int64_t rows;          /* bf16 [n_tokens*routes, hidden] weighted per-route outputs */
   int32_t block_m;
   int32_t max_blocks;
