@@ -62,6 +62,9 @@ SIGNATURES = {
     "aklr_moe_route": (c_int32, [POINTER(MoeConfig)] + [c_void_p] * 5 + [c_void_p]),
     "aklr_moe_align": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32] + [c_void_p] * 5 + [c_void_p]),
     "aklr_moe_align_max_blocks": (c_int64, [c_int64, c_int64, c_int64]),
+    "aklr_moe_align_noalloc": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32] + [c_void_p] * 4 + [c_void_p]),
+    "aklr_moe_align_noalloc_max_scratch_ints": (c_int32, []),
+    "aklr_moe_align_noalloc_last_error": (c_char_p, []),
     "aklr_router_gemm_bf16": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p]),
     "aklr_per_group_quant_fp8": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_void_p]),
     "aklr_per_group_quant_mxfp8": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_void_p]),

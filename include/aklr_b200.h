@@ -126,6 +126,19 @@ int aklr_moe_align(const int32_t* topk_ids, const int32_t* expert_map, int32_t n
                    int32_t* counts, int32_t* num_blocks, int32_t* chunk_scratch, void* stream);
 int64_t aklr_moe_align_max_blocks(int64_t n_routes, int64_t n_experts, int64_t block_m);
 
+/* moe_align without a scratch argument.  It has no counterpart in the reference.  For callers
+ * that cannot allocate device memory where they sort (a frozen memory pool, a hook handed only the
+ * engine's tensors, a binding with no allocator): the histogram scratch is a 1 MiB array inside
+ * the library, held by every GPU that loads it.  Limit: ceil(n_routes/1024) * n_experts <=
+ * aklr_moe_align_noalloc_max_scratch_ints() (262144), else AKLR_ERR_TOO_LARGE.  The first call on
+ * a device resolves the array's address (make it before any stream capture); calls on one device
+ * share the array, so calls whose kernels overlap on the GPU race.  Outputs as aklr_moe_align. */
+int aklr_moe_align_noalloc(const int32_t* topk_ids, const int32_t* expert_map, int32_t n_routes,
+                           int32_t n_experts, int32_t n_experts_global, int32_t block_m, int32_t* sorted_ids,
+                           int32_t* block_expert, int32_t* counts, int32_t* num_blocks, void* stream);
+int32_t aklr_moe_align_noalloc_max_scratch_ints(void);
+const char* aklr_moe_align_noalloc_last_error(void);
+
 /* logits bf16 [T,E] = bf16(x [T,H] @ w [E,H]^T): `_router_logits`
  * (aklr/plugins/sglang/models/qwen3_moe/reference.py:24-31). */
 int aklr_router_gemm_bf16(const void* x, const void* w, void* logits, int32_t n_tokens, int32_t hidden,
