@@ -155,7 +155,10 @@ void layout_of(const aklr_moe_config& c, aklr_moe_workspace_layout* l) {
 int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, const void* hidden_states,
                 const int32_t* topk_ids, const float* topk_weights, const int32_t* expert_map,
                 int n_experts_global, const void* w1, const float* w1_scale, const void* w2,
-                const float* w2_scale, void* out, uint8_t* ws, cudaStream_t stream, int slot) {
+                const float* w2_scale, void* out, uint8_t* ws, cudaStream_t stream, int slot,
+                const uint8_t* q_in = nullptr, const float* scales_in = nullptr, void* rows_out = nullptr) {
+  // q_in/scales_in: the rows arrive already quantised (expert-parallel receive side);
+  // rows_out: write the weighted per-route rows there and skip the combine.
   using namespace aklr;
   const int routes_per_token = c.topk + c.n_shared;
   const int routes = c.n_tokens * routes_per_token;
@@ -192,7 +195,9 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   qp.hidden = c.hidden;
   qp.routes_per_token = routes_per_token;
   qp.block_m = l.block_m;
-  rc = launch_gather_quant_fp8(qp, stream);
+  qp.q_in = q_in;
+  qp.scales_in = scales_in;
+  rc = q_in ? launch_gather_rows_fp8(qp, stream) : launch_gather_quant_fp8(qp, stream);
   if (rc) return fail(rc, "activation quant launch failed");
   g_launches += 1;
   profile_mark(stream, slot, 3);
@@ -234,7 +239,7 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   g2.block_expert = block_expert;
   g2.num_blocks = num_blocks;
   g2.topk_weights = topk_weights;
-  g2.out_rows = ws + l.rows;
+  g2.out_rows = rows_out ? rows_out : ws + l.rows;
   g2.status = status;
   g2.k = c.inter;
   g2.out_dim = c.hidden;
@@ -248,6 +253,10 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   g_launches += 1;
   profile_mark(stream, slot, 5);
 
+  if (rows_out) {
+    profile_mark(stream, slot, 6);
+    return AKLR_OK;
+  }
   CombineParams cp{};
   cp.rows = ws + l.rows;
   cp.topk_ids = topk_ids;
@@ -354,6 +363,72 @@ int aklr_moe_fp8_experts(const aklr_moe_config* cfg, const void* hidden_states, 
   profile_mark(stream, slot, 1);
   return run_experts(*cfg, l, hidden_states, topk_ids, topk_weights, expert_map, global, w1, w1_scale, w2, w2_scale,
                      out, static_cast<uint8_t*>(workspace), stream, slot);
+}
+
+int aklr_moe_fp8_experts_prequant(const aklr_moe_config* cfg, const void* rows_q, const float* rows_scale,
+                                  const int32_t* expert_ids, const float* weights, const void* w1,
+                                  const float* w1_scale, const void* w2, const float* w2_scale, void* out_rows,
+                                  void* workspace, size_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  aklr_moe_workspace_layout l;
+  if (cfg && (cfg->topk != 1 || cfg->n_shared != 0)) return fail(AKLR_ERR_BAD_ARGUMENT, "prequantised rows carry one route each: topk 1, n_shared 0");
+  int rc = prepare(cfg, &l, workspace, workspace_bytes, stream);
+  if (rc) return rc;
+  if (cfg->n_tokens == 0) return AKLR_OK;
+  if (!rows_q || !rows_scale || !expert_ids || !weights || !w1 || !w1_scale || !w2 || !w2_scale || !out_rows)
+    return fail(AKLR_ERR_BAD_ARGUMENT, "NULL tensor argument");
+  const int slot = profile_slot();
+  profile_mark(stream, slot, 0);
+  profile_mark(stream, slot, 1);
+  return run_experts(*cfg, l, nullptr, expert_ids, weights, nullptr, cfg->n_routed, w1, w1_scale, w2, w2_scale, nullptr,
+                     static_cast<uint8_t*>(workspace), stream, slot, static_cast<const uint8_t*>(rows_q), rows_scale,
+                     out_rows);
+}
+
+int aklr_ep_dispatch_meta(const int32_t* sorted_ids, const int32_t* topk_ids, const float* topk_weights,
+                          int32_t n_send, int32_t n_routes, int32_t experts_per_rank, int32_t* send_expert,
+                          float* send_weight, int32_t* position_of_route, void* stream) {
+  if (!sorted_ids || !topk_ids || !topk_weights || !send_expert || !send_weight || !position_of_route || experts_per_rank < 1)
+    return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
+  int rc = check_device();
+  if (rc) return rc;
+  aklr::EpMetaParams p{sorted_ids, topk_ids, topk_weights, send_expert, send_weight, position_of_route,
+                       n_send, n_routes, experts_per_rank};
+  rc = aklr::launch_ep_meta(p, static_cast<cudaStream_t>(stream));
+  if (rc) return fail(rc, "ep dispatch meta: %s", aklr_status_string(rc));
+  g_launches += n_send > 0;
+  return AKLR_OK;
+}
+
+int aklr_ep_gather_quant(const void* hidden_states, const int32_t* sorted_ids, int32_t n_send, int32_t hidden,
+                         int32_t routes_per_token, void* rows_q, float* rows_scale, void* stream) {
+  if (!hidden_states || !sorted_ids || !rows_q || !rows_scale) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
+  int rc = check_device();
+  if (rc) return rc;
+  aklr::GatherQuantParams p{};
+  p.x = hidden_states;
+  p.sorted_ids = sorted_ids;
+  p.q = static_cast<uint8_t*>(rows_q);
+  p.scales = rows_scale;
+  p.n_rows = n_send;
+  p.hidden = hidden;
+  p.routes_per_token = routes_per_token;
+  rc = aklr::launch_gather_quant_fp8(p, static_cast<cudaStream_t>(stream));
+  if (rc) return fail(rc, "ep gather quant: %s", aklr_status_string(rc));
+  g_launches += n_send > 0;
+  return AKLR_OK;
+}
+
+int aklr_ep_combine(const void* rows, const int32_t* position_of_route, const void* shared_rows, void* out,
+                    int32_t n_tokens, int32_t topk, int32_t hidden, void* stream) {
+  if (!position_of_route || !out) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
+  int rc = check_device();
+  if (rc) return rc;
+  aklr::EpCombineParams p{rows, position_of_route, shared_rows, out, n_tokens, topk, hidden};
+  rc = aklr::launch_ep_combine(p, static_cast<cudaStream_t>(stream));
+  if (rc) return fail(rc, "ep combine: %s", aklr_status_string(rc));
+  g_launches += n_tokens > 0;
+  return AKLR_OK;
 }
 
 int aklr_moe_route(const aklr_moe_config* cfg, const void* logits, const void* bias, const float* sigmoid_table,

@@ -43,6 +43,8 @@ inline int64_t align_max_blocks(int64_t n_routes, int64_t n_experts, int64_t blo
 
 struct GatherQuantParams {
   const void* x;              // [n_tokens, hidden] bf16
+  const uint8_t* q_in;        // gather_rows only: [n_tokens, hidden] e4m3 quantised by the sender
+  const float* scales_in;     // gather_rows only: [n_tokens, hidden/128]
   const int32_t* sorted_ids;  // [capacity] or null: row r reads token r
   const int32_t* num_rows;    // device count of rows in use (null: n_rows)
   uint8_t* q;                 // [rows, hidden] e4m3
@@ -50,6 +52,7 @@ struct GatherQuantParams {
   int n_rows, hidden, routes_per_token, block_m;
 };
 int launch_gather_quant_fp8(const GatherQuantParams& p, cudaStream_t stream);
+int launch_gather_rows_fp8(const GatherQuantParams& p, cudaStream_t stream);
 
 // standalone quant ops
 int launch_per_group_quant_fp8(const void* x_bf16, uint8_t* q, float* scales_group_major, int rows, int hidden,
@@ -90,6 +93,27 @@ struct CombineParams {
   int n_tokens, hidden, routes_per_token, n_experts_global;
 };
 int launch_combine(const CombineParams& p, cudaStream_t stream);
+
+// ---- expert parallelism: sender-side packing and home-side combine --------------------------
+struct EpMetaParams {
+  const int32_t* sorted_ids;    // [n_send] routes ordered by destination rank (moe_align, block_m 1)
+  const int32_t* topk_ids;      // [n_routes] global expert ids
+  const float* topk_weights;    // [n_routes]
+  int32_t* send_expert;         // [n_send] expert id local to the destination rank
+  float* send_weight;           // [n_send]
+  int32_t* position_of_route;   // [n_routes] where the route sits in the send order (-1: not sent)
+  int n_send, n_routes, experts_per_rank;
+};
+int launch_ep_meta(const EpMetaParams& p, cudaStream_t stream);
+
+struct EpCombineParams {
+  const void* rows;                  // [n_send, hidden] bf16, weighted, in send order
+  const int32_t* position_of_route;  // [n_tokens * topk]
+  const void* shared_rows;           // [n_tokens, hidden] bf16 or null
+  void* out;                         // [n_tokens, hidden] bf16
+  int n_tokens, topk, hidden;
+};
+int launch_ep_combine(const EpCombineParams& p, cudaStream_t stream);
 
 int launch_router_gemm(const void* x_bf16, const void* w_bf16, void* logits_bf16, int n_tokens, int hidden,
                        int n_routed, cudaStream_t stream);

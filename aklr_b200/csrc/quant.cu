@@ -78,6 +78,40 @@ __global__ void __launch_bounds__(256) gather_quant_fp8_kernel(GatherQuantParams
   }
 }
 
+// Rows already quantised elsewhere (the sender of an expert-parallel dispatch): copy row rid's codes
+// and scales into the expert-sorted table.  One 16-byte vector per thread.
+__global__ void __launch_bounds__(256) gather_rows_fp8_kernel(GatherQuantParams p) {
+  const int vec_per_row = p.hidden >> 4;
+  const int groups_per_row = p.hidden >> 7;
+  const int n_rows = p.num_rows ? min(*p.num_rows, p.n_rows) : p.n_rows;
+  const int64_t total = static_cast<int64_t>(n_rows) * vec_per_row;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int row = static_cast<int>(i / vec_per_row);
+    const int v = static_cast<int>(i - static_cast<int64_t>(row) * vec_per_row);
+    const int rid = p.sorted_ids[row];
+    if (rid < 0) continue;
+    const int src = rid / p.routes_per_token;
+    *reinterpret_cast<uint4*>(p.q + static_cast<size_t>(row) * p.hidden + v * 16) =
+        *reinterpret_cast<const uint4*>(p.q_in + static_cast<size_t>(src) * p.hidden + v * 16);
+    if ((v & 7) == 0) {  // the thread holding the first 16 bytes of a 128-group moves its scale
+      const int grp = v >> 3;
+      p.scales[(static_cast<size_t>(row / p.block_m) * groups_per_row + grp) * p.block_m + row % p.block_m] =
+          p.scales_in[static_cast<size_t>(src) * groups_per_row + grp];
+    }
+  }
+}
+
+int launch_gather_rows_fp8(const GatherQuantParams& p, cudaStream_t stream) {
+  if (p.hidden % 128 != 0 || p.block_m < 1) return AKLR_ERR_UNSUPPORTED_SHAPE;
+  if (p.n_rows == 0) return AKLR_OK;
+  const int64_t total = static_cast<int64_t>(p.n_rows) * (p.hidden / 16);
+  const int64_t blocks = (total + 255) / 256;
+  const int grid = static_cast<int>(blocks < 148 * 16 ? blocks : 148 * 16);
+  gather_rows_fp8_kernel<<<grid, 256, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+}
+
 int launch_gather_quant_fp8(const GatherQuantParams& p, cudaStream_t stream) {
   if (p.hidden % 128 != 0) return AKLR_ERR_UNSUPPORTED_SHAPE;
   if (p.n_rows == 0) return AKLR_OK;

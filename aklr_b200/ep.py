@@ -1,0 +1,376 @@
+"""Expert parallelism for the FP8 fused-MoE layer: tokens stay on their home rank, experts are
+sharded, NCCL all-to-alls carry routes out (FP8 rows + scales) and weighted bf16 rows back.
+
+Ownership is the reference's (aklr/ops/mega_moe/contract.py:42-51, reference.py:25,38): with
+``n_local`` routed experts per rank, global expert ``e`` is local expert ``e % n_local`` of rank
+``e // n_local``.  Shared experts are replicated and applied to a rank's own tokens on a side
+stream while the dispatch is in flight.  No kernel waits on another rank: every exchange is a
+host-ordered collective whose payload lands in local HBM before a kernel reads it.
+
+One step of one rank is three phases, so that a test can drive several ranks in one process:
+
+    state = layer.prepare(hidden, logits, bias)          # route, order by rank, quantise, pack
+    received = comm.exchange(state.send, state.send_counts)
+    rows = layer.compute(received)                       # local experts over the rows received
+    back = comm.exchange_back(rows, ...)
+    out = layer.finish(state, back)                      # weighted sum at home + shared experts
+
+``ExpertParallelMoE.forward`` runs them over ``torch.distributed``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import dataclasses
+
+import torch
+
+from aklr_b200 import _lib
+from aklr_b200.moe import FP8, Routing, Workspace, _config, _ptr, _stream, fused_experts_fp8, route
+
+
+@dataclasses.dataclass
+class Packed:
+    """What one rank sends: rows ordered by destination rank."""
+
+    rows_q: torch.Tensor      # uint8 view of e4m3 [n_send, H]
+    rows_scale: torch.Tensor  # float32 [n_send, H/128]
+    meta: torch.Tensor        # int32 [n_send, 2]: expert id on the destination, weight bits
+    counts: torch.Tensor      # int32 [world] rows per destination (device)
+
+
+@dataclasses.dataclass
+class StepState:
+    send: Packed
+    position_of_route: torch.Tensor
+    shared_rows: torch.Tensor | None
+    shared_done: torch.cuda.Event | None
+    n_tokens: int
+
+
+class CudaKernels:
+    """The device side of the phases: libaklr_b200.so through the C ABI."""
+
+    def route(self, logits, bias, routing):
+        return route(logits, bias, routing)
+
+    def order_by_rank(self, ids, n_local, world):
+        """(routes sorted by destination rank int32 [R], rows per rank int32 [world])."""
+        lib = _lib.load()
+        device = ids.device
+        n_routes = ids.numel()
+        n_experts = n_local * world
+        rank_of = (torch.arange(n_experts, dtype=torch.int32, device=device) // n_local).contiguous()
+        sorted_ids = torch.empty(n_routes + world, dtype=torch.int32, device=device)
+        block_rank = torch.empty(n_routes + world, dtype=torch.int32, device=device)
+        counts = torch.empty(world, dtype=torch.int32, device=device)
+        num_blocks = torch.empty(2, dtype=torch.int32, device=device)
+        scratch = torch.empty(max(1, (n_routes + 1023) // 1024) * world, dtype=torch.int32, device=device)
+        _lib.check(
+            lib.aklr_moe_align(
+                _ptr(ids), _ptr(rank_of), n_routes, world, n_experts, 1, _ptr(sorted_ids), _ptr(block_rank),
+                _ptr(counts), _ptr(num_blocks), _ptr(scratch), _stream(),
+            )
+        )
+        return sorted_ids[:n_routes], counts
+
+    def pack(self, hidden, ids, weights, sorted_ids, n_local):
+        lib = _lib.load()
+        device = hidden.device
+        n_send, h = sorted_ids.numel(), hidden.shape[1]
+        rows_q = torch.empty((n_send, h), dtype=torch.uint8, device=device)
+        rows_scale = torch.empty((n_send, h // 128), dtype=torch.float32, device=device)
+        meta = torch.empty((2, n_send), dtype=torch.int32, device=device)
+        position = torch.full((ids.numel(),), -1, dtype=torch.int32, device=device)
+        _lib.check(lib.aklr_ep_gather_quant(_ptr(hidden), _ptr(sorted_ids), n_send, h, ids.shape[1], _ptr(rows_q), _ptr(rows_scale), _stream()))
+        _lib.check(
+            lib.aklr_ep_dispatch_meta(
+                _ptr(sorted_ids), _ptr(ids), _ptr(weights), n_send, ids.numel(), n_local, meta[0].data_ptr(),
+                meta[1].data_ptr(), _ptr(position), _stream(),
+            )
+        )
+        return rows_q, rows_scale, meta.t().contiguous(), position
+
+    def experts(self, rows_q, rows_scale, expert_ids, weights, w1, s1, w2, s2):
+        """Weighted bf16 rows [n, H] of rows that arrive quantised, one route each."""
+        device = rows_q.device
+        n, h = rows_q.shape
+        out = torch.empty((n, h), dtype=torch.bfloat16, device=device)
+        if n == 0:
+            return out
+        e, two_i, _ = w1.shape
+        cfg = _config(n, h, two_i // 2, e, Routing(topk=1))
+        ws = Workspace(cfg, device)
+        _lib.check(
+            _lib.load().aklr_moe_fp8_experts_prequant(
+                ctypes.byref(cfg), _ptr(rows_q), _ptr(rows_scale), _ptr(expert_ids), _ptr(weights), _ptr(w1),
+                _ptr(s1), _ptr(w2), _ptr(s2), _ptr(out), ws.base.data_ptr(), ws.layout.total_bytes, _stream(),
+            )
+        )
+        return out
+
+    def shared(self, hidden, w1, s1, w2, s2):
+        """Sum of the shared experts on the rank's own tokens (each at weight 1), bf16 [T, H]."""
+        n_tokens, n_shared = hidden.shape[0], w1.shape[0]
+        ids = torch.arange(n_shared, dtype=torch.int32, device=hidden.device).repeat(n_tokens, 1).contiguous()
+        ones = torch.ones((n_tokens, n_shared), dtype=torch.float32, device=hidden.device)
+        return fused_experts_fp8(hidden, ids, ones, w1, s1, w2, s2)
+
+    def combine(self, rows, position, shared_rows, n_tokens, topk, hidden):
+        out = torch.empty((n_tokens, hidden), dtype=torch.bfloat16, device=position.device)
+        _lib.check(_lib.load().aklr_ep_combine(_ptr(rows), _ptr(position), _ptr(shared_rows), _ptr(out), n_tokens, topk, hidden, _stream()))
+        return out
+
+    def side_stream(self, device):
+        return torch.cuda.Stream(device=device)
+
+
+class ExpertParallelMoE:
+    """One rank's share of an expert-parallel FP8 MoE layer.
+
+    ``w1``/``w2`` (+ scales) hold this rank's ``n_local`` routed experts followed by the layer's
+    shared experts (replicated).  ``routing`` describes the whole layer (global expert count =
+    ``n_local * world``)."""
+
+    def __init__(self, routing: Routing, w1, w1_scale, w2, w2_scale, rank: int, world: int, kernels=None):
+        self.routing = dataclasses.replace(routing, n_shared=0)
+        self.n_shared = routing.n_shared
+        self.n_local = w1.shape[0] - self.n_shared
+        if self.n_local < 1:
+            raise ValueError("w1 must hold at least one routed expert before the shared ones")
+        self.rank, self.world = rank, world
+        self.kernels = kernels or CudaKernels()
+        split = self.n_local
+        self.routed = (w1[:split], w1_scale[:split], w2[:split], w2_scale[:split])
+        self.shared = (w1[split:], w1_scale[split:], w2[split:], w2_scale[split:]) if self.n_shared else None
+        self._side = None
+
+    # ---- phase 1: on the home rank --------------------------------------------------------------
+    def prepare(self, hidden: torch.Tensor, logits: torch.Tensor, bias: torch.Tensor | None) -> StepState:
+        k = self.kernels
+        if logits.shape[1] != self.n_local * self.world:
+            raise ValueError(f"router has {logits.shape[1]} experts, the group holds {self.n_local * self.world}")
+        shared_rows = shared_done = None
+        if self.shared is not None:  # overlaps the dispatch: own tokens through the replicated shared experts
+            if hidden.is_cuda:
+                if self._side is None:
+                    self._side = k.side_stream(hidden.device)
+                self._side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(self._side):
+                    shared_rows = k.shared(hidden, *self.shared)
+                    shared_done = torch.cuda.Event()
+                    shared_done.record(self._side)
+                hidden.record_stream(self._side)
+            else:
+                shared_rows = k.shared(hidden, *self.shared)
+        ids, weights = k.route(logits, bias, self.routing)
+        sorted_ids, counts = k.order_by_rank(ids, self.n_local, self.world)
+        rows_q, rows_scale, meta, position = k.pack(hidden, ids, weights, sorted_ids, self.n_local)
+        return StepState(Packed(rows_q, rows_scale, meta, counts), position, shared_rows, shared_done, hidden.shape[0])
+
+    # ---- phase 2: on the rank that holds the experts ---------------------------------------------
+    def compute(self, received: Packed) -> torch.Tensor:
+        expert_ids = received.meta[:, 0].contiguous()
+        weights = received.meta[:, 1].contiguous().view(torch.float32)
+        rows_q = received.rows_q
+        if rows_q.dtype != FP8 and rows_q.is_cuda:
+            rows_q = rows_q.view(FP8)
+        return self.kernels.experts(rows_q, received.rows_scale, expert_ids, weights, *self.routed)
+
+    # ---- phase 3: back home ------------------------------------------------------------------------
+    def finish(self, state: StepState, back_rows: torch.Tensor) -> torch.Tensor:
+        if state.shared_done is not None:
+            torch.cuda.current_stream().wait_event(state.shared_done)
+        hidden = back_rows.shape[1]
+        return self.kernels.combine(back_rows, state.position_of_route, state.shared_rows, state.n_tokens, self.routing.topk, hidden)
+
+    # ---- all three over torch.distributed ------------------------------------------------------------
+    def forward(self, hidden, logits, bias, group=None) -> torch.Tensor:
+        import torch.distributed as dist
+
+        state = self.prepare(hidden, logits, bias)
+        send = state.send
+        recv_counts_dev = torch.empty_like(send.counts)
+        dist.all_to_all_single(recv_counts_dev, send.counts, group=group)
+        both = torch.stack([send.counts, recv_counts_dev]).cpu()  # the one host read of the step
+        send_counts, recv_counts = both[0].tolist(), both[1].tolist()
+        received = exchange(send, send_counts, recv_counts, group)
+        rows = self.compute(received)
+        back = torch.empty((sum(send_counts), rows.shape[1]), dtype=rows.dtype, device=rows.device)
+        dist.all_to_all_single(back, rows, output_split_sizes=send_counts, input_split_sizes=recv_counts, group=group)
+        return self.finish(state, back)
+
+
+def exchange(send: Packed, send_counts, recv_counts, group=None) -> Packed:
+    """The dispatch all-to-all: rows, scales and metadata, split by destination rank."""
+    import torch.distributed as dist
+
+    n_recv = sum(recv_counts)
+
+    def a2a(t: torch.Tensor) -> torch.Tensor:
+        out = torch.empty((n_recv, *t.shape[1:]), dtype=t.dtype, device=t.device)
+        dist.all_to_all_single(out, t, output_split_sizes=recv_counts, input_split_sizes=send_counts, group=group)
+        return out
+
+    return Packed(a2a(send.rows_q), a2a(send.rows_scale), a2a(send.meta), torch.tensor(recv_counts, dtype=torch.int32))
+
+
+def exchange_in_process(sends: list[Packed]) -> tuple[list[Packed], list[list[int]]]:
+    """The same data movement among ranks that live in one process (tests, single-GPU emulation).
+    Returns what each rank receives and each rank's send counts."""
+    world = len(sends)
+    counts = [s.counts.cpu().tolist() for s in sends]
+    starts = [[sum(c[:d]) for d in range(world)] for c in counts]
+    received = []
+    for dst in range(world):
+        def gather(field):
+            parts = [getattr(sends[src], field)[starts[src][dst] : starts[src][dst] + counts[src][dst]] for src in range(world)]
+            return torch.cat(parts)
+
+        recv_counts = torch.tensor([counts[src][dst] for src in range(world)], dtype=torch.int32)
+        received.append(Packed(gather("rows_q"), gather("rows_scale"), gather("meta"), recv_counts))
+    return received, counts
+
+
+def exchange_back_in_process(rows_per_rank: list[torch.Tensor], counts: list[list[int]]) -> list[torch.Tensor]:
+    """Rows computed on each rank returned to the ranks that sent them, in their send order."""
+    world = len(rows_per_rank)
+    back = []
+    for home in range(world):
+        parts = []
+        for holder in range(world):
+            start = sum(counts[src][holder] for src in range(home))
+            parts.append(rows_per_rank[holder][start : start + counts[home][holder]])
+        back.append(torch.cat(parts))
+    return back
+
+
+def run_in_process(layers: list[ExpertParallelMoE], inputs: list[tuple]) -> list[torch.Tensor]:
+    """All ranks' steps in one process: phase by phase, never two ranks' kernels waiting on each other."""
+    states = [layer.prepare(*inp) for layer, inp in zip(layers, inputs)]
+    received, counts = exchange_in_process([s.send for s in states])
+    rows = [layer.compute(r) for layer, r in zip(layers, received)]
+    back = exchange_back_in_process(rows, counts)
+    return [layer.finish(s, b) for layer, s, b in zip(layers, states, back)]
+
+
+def bench_ep(args, cfg, rank, world, device, clock_sampler, workload_config, metric, unit, measured_peak_hbm):
+    """The N-GPU leg of bench.py: every rank holds n_routed/N routed experts + the shared expert
+    and ``args.tokens`` tokens of its own (weak scaling).  Rank 0 prints the JSON line."""
+    import json
+
+    import torch.distributed as dist
+
+    from aklr_b200 import workloads as wl
+
+    seed = 2024
+    if cfg.n_routed % world:
+        raise SystemExit(f"{cfg.n_routed} routed experts do not split over {world} ranks")
+    n_local = cfg.n_routed // world
+    mine = list(range(rank * n_local, (rank + 1) * n_local)) + list(range(cfg.n_routed, cfg.n_experts))
+    w1, s1, w2, s2 = wl.expert_weights(cfg, seed, device, experts=mine)
+    routing = Routing(cfg.topk, cfg.scoring, cfg.n_shared, cfg.num_expert_group, cfg.topk_group, cfg.renormalize, cfg.routed_scaling_factor)
+    layer = ExpertParallelMoE(routing, w1, s1, w2, s2, rank, world)
+    bias = wl.router_inputs(cfg, 1, seed + 1, device)[2]
+    n_batches, tokens = 4, args.tokens
+    batches = [wl.router_inputs(cfg, tokens, seed + 1 + 97 * rank + b, device)[:2] for b in range(n_batches)]
+    lib = _lib.load()
+
+    def step(i):
+        hidden, logits = batches[i % n_batches]
+        return layer.forward(hidden, logits, bias)
+
+    def timed(fn, steps):
+        dist.barrier()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(steps):
+            fn(i)
+        stop.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        ms = torch.tensor([start.elapsed_time(stop)], device=device)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)  # the slowest rank's device time
+        return float(ms) / steps
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    lib.aklr_profile_begin(2 * args.steps)
+    launches0 = lib.aklr_kernel_launch_count()
+    sampler = clock_sampler(device.index) if rank == 0 else None
+    ms_per_step = timed(lambda i: step(args.warmup + i), args.steps)
+    clocks = sampler.stop() if sampler else None
+    launches = lib.aklr_kernel_launch_count() - launches0
+    # stage times of the routed-expert calls (every second recorded call; the other is the shared expert)
+    stage_ms = [0.0] * 6
+    buf = (ctypes.c_float * 6)()
+    for i in range(args.steps):
+        _lib.check(lib.aklr_profile_read(2 * i + 1, buf))
+        for j in range(6):
+            stage_ms[j] += buf[j] / args.steps
+    lib.aklr_profile_begin(0)
+
+    # end to end from pinned host buffers: H2D of activations and logits, D2H of the output
+    host = [(h.cpu().pin_memory(), lg.cpu().pin_memory()) for h, lg in batches]
+    dev_hidden, dev_logits = torch.empty_like(batches[0][0]), torch.empty_like(batches[0][1])
+    host_out = torch.empty((tokens, cfg.hidden), dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step(i):
+        dev_hidden.copy_(host[i % n_batches][0], non_blocking=True)
+        dev_logits.copy_(host[i % n_batches][1], non_blocking=True)
+        host_out.copy_(layer.forward(dev_hidden, dev_logits, bias), non_blocking=True)
+
+    for i in range(args.warmup):
+        e2e_step(i)
+    e2e_ms = timed(e2e_step, args.steps)
+
+    if rank != 0:
+        return
+    h, inter = cfg.hidden, cfg.inter
+    routes_local = tokens * cfg.topk  # expected rows received per rank under uniform routing
+    gate_up_bytes = n_local * (2 * inter * h + 4 * (2 * inter // 128) * (h // 128)) + routes_local * (h + 4 * (h // 128) + inter)
+    peak, peak_kind = measured_peak_hbm()
+    achieved = gate_up_bytes / (stage_ms[3] * 1e-3) / 1e9 if stage_ms[3] > 0 else 0.0
+    line = {
+        "metric": metric,
+        "value": world * tokens / (ms_per_step * 1e-3),
+        "unit": unit,
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": ms_per_step,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "fp8_e4m3",
+        "data": "synthetic",
+        "config": workload_config(cfg, args),
+        "clocks": clocks,
+        "e2e": {
+            "value": world * tokens / (e2e_ms * 1e-3),
+            "unit": unit,
+            "ms_per_step": e2e_ms,
+            "h2d_bytes_per_step": tokens * (cfg.hidden + cfg.n_routed) * 2,
+            "d2h_bytes_per_step": tokens * cfg.hidden * 2,
+            "api": "aklr_b200.ep.ExpertParallelMoE.forward (from router logits), per rank",
+        },
+        "gpu_launches": int(launches),
+        "roofline": {
+            "kernel": "grouped_gemm_kernel<gate_up> over the rows a rank receives (rank 0)",
+            "bound": "hbm",
+            "achieved": achieved,
+            "peak": peak,
+            "peak_kind": f"of {peak_kind}",
+            "unit": "GB/s",
+            "frac": achieved / peak,
+            "traffic": None,
+            "algorithmic_bytes_per_launch": gate_up_bytes,
+            "ms_per_launch": stage_ms[3],
+            "stage_ms": dict(zip(["route", "sort", "quant", "gate_up", "down", "combine"], stage_ms)),
+            "note": "all local experts assumed hit; rows = tokens*topk (uniform routing expectation)",
+        },
+        "cpu_baseline": None,
+    }
+    print(json.dumps(line), flush=True)

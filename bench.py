@@ -271,6 +271,7 @@ def main() -> None:
         from aklr_b200.ep import bench_ep
 
         bench_ep(args, cfg, rank, world, device, ClockSampler, workload_config, METRIC, UNIT, measured_peak_hbm)
+        dist.destroy_process_group()
         return
 
     from aklr_b200 import ops

@@ -112,6 +112,31 @@ int aklr_moe_fp8_experts(const aklr_moe_config* cfg, const void* hidden_states, 
                          const float* w1_scale, const void* w2, const float* w2_scale, void* out,
                          void* workspace, size_t workspace_bytes, void* stream);
 
+/* Expert parallelism (the reference's `mega_moe` contract: every rank holds n_local experts, global
+ * expert e is local e % n_local of rank e / n_local; aklr/ops/mega_moe/contract.py:42-51,
+ * reference.py:25,38).  The host code orders routes by destination rank with aklr_moe_align
+ * (block_m 1, an expert map global expert -> rank), then:
+ *   aklr_ep_gather_quant    FP8 rows + row-major scales [n_send, H/128] of the routes in send order;
+ *   aklr_ep_dispatch_meta   per sent route its expert id on the destination and its weight, and
+ *                           the inverse map route -> send position (-1 must be pre-filled);
+ *   (NCCL all-to-all of rows, scales, expert ids, weights -- issued by the caller)
+ *   aklr_moe_fp8_experts_prequant  on the receiver: experts over rows that arrive quantised, one
+ *                           route per row (cfg: n_tokens = rows, topk 1, n_shared 0, n_routed =
+ *                           local expert slots); writes weighted bf16 rows [rows, H], no combine;
+ *   (NCCL all-to-all of the bf16 rows back)
+ *   aklr_ep_combine         out[t] = bf16(sum_k rows[position(t,k)] + shared_rows[t]). */
+int aklr_ep_gather_quant(const void* hidden_states, const int32_t* sorted_ids, int32_t n_send, int32_t hidden,
+                         int32_t routes_per_token, void* rows_q, float* rows_scale, void* stream);
+int aklr_ep_dispatch_meta(const int32_t* sorted_ids, const int32_t* topk_ids, const float* topk_weights,
+                          int32_t n_send, int32_t n_routes, int32_t experts_per_rank, int32_t* send_expert,
+                          float* send_weight, int32_t* position_of_route, void* stream);
+int aklr_moe_fp8_experts_prequant(const aklr_moe_config* cfg, const void* rows_q, const float* rows_scale,
+                                  const int32_t* expert_ids, const float* weights, const void* w1,
+                                  const float* w1_scale, const void* w2, const float* w2_scale, void* out_rows,
+                                  void* workspace, size_t workspace_bytes, void* stream);
+int aklr_ep_combine(const void* rows, const int32_t* position_of_route, const void* shared_rows, void* out,
+                    int32_t n_tokens, int32_t topk, int32_t hidden, void* stream);
+
 /* Routing alone: `biased_grouped_topk` (aklr/ops/topk/api.py:12-22, reference.py:17-35) and the
  * routing halves of the two layer ops.  Writes topk_ids int32 / topk_weights float
  * [T, topk + n_shared]. */

@@ -1,0 +1,49 @@
+"""Expert parallelism on the device: several ranks emulated phase by phase in one process on one
+GPU (no kernel ever waits on another rank), against the single-GPU layer and the CPU oracle."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from aklr_b200 import workloads as wl
+from oracle import moe_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def routing_of(cfg):
+    from aklr_b200.moe import Routing
+
+    return Routing(cfg.topk, cfg.scoring, cfg.n_shared, cfg.num_expert_group, cfg.topk_group, cfg.renormalize, cfg.routed_scaling_factor)
+
+
+@pytest.mark.parametrize("world,tokens", [(2, (33, 7)), (4, (16, 1, 40, 5)), (8, (3,) * 8)])
+def test_emulated_ranks_match_single_gpu_and_oracle(world, tokens):
+    from aklr_b200.ep import ExpertParallelMoE, run_in_process
+    from aklr_b200.moe import fused_moe_fp8
+
+    cfg = wl.CONFIGS["deepseek_small"]  # 64 routed experts + 1 shared
+    d = torch.device("cuda:0")
+    w1, s1, w2, s2 = (t.to(d) for t in wl.expert_weights(cfg, seed=70))
+    bias = wl.router_inputs(cfg, 1, seed=71)[2].to(d)
+    n_local = cfg.n_routed // world
+    layers, inputs = [], []
+    for r in range(world):
+        mine = list(range(r * n_local, (r + 1) * n_local)) + [cfg.n_routed]
+        layers.append(ExpertParallelMoE(routing_of(cfg), w1[mine].contiguous(), s1[mine].contiguous(), w2[mine].contiguous(), s2[mine].contiguous(), r, world))
+        hidden, logits, _ = wl.router_inputs(cfg, tokens[r], seed=80 + r)
+        inputs.append((hidden.to(d), logits.to(d), bias))
+    outs = run_in_process(layers, inputs)
+    torch.cuda.synchronize()
+    for r in range(world):
+        hidden, logits, _ = inputs[r]
+        single = fused_moe_fp8(hidden, logits, bias, w1, s1, w2, s2, routing_of(cfg))
+        ref = orc.deepseek_v2_fp8_moe(
+            hidden.cpu(), None, bias.cpu(), w1.cpu(), s1.cpu(), w2.cpu(), s2.cpu(), cfg.topk, cfg.num_expert_group,
+            cfg.topk_group, True, cfg.routed_scaling_factor, logits=logits.cpu().float(),
+        )
+        gates = orc.output_gates(outs[r].cpu(), ref)
+        assert orc.gates_pass(gates), (r, gates)
+        # same kernels, same per-token arithmetic, same summation order: the same bits
+        assert torch.equal(outs[r], single), f"rank {r} differs from the single-GPU layer"
