@@ -327,7 +327,7 @@ def bench_ep(args, cfg, rank, world, device, clock_sampler, workload_config, met
     e2e_ms = timed(e2e_step, args.steps)
 
     if rank != 0:
-        return
+        return None
     h, inter = cfg.hidden, cfg.inter
     routes_local = tokens * cfg.topk  # expected rows received per rank under uniform routing
     gate_up_bytes = n_local * (2 * inter * h + 4 * (2 * inter // 128) * (h // 128)) + routes_local * (h + 4 * (h // 128) + inter)
@@ -373,4 +373,4 @@ def bench_ep(args, cfg, rank, world, device, clock_sampler, workload_config, met
         },
         "cpu_baseline": None,
     }
-    print(json.dumps(line), flush=True)
+    return json.dumps(line)

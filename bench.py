@@ -256,9 +256,14 @@ def main() -> None:
         raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    saved_stdout = None
     if world > 1:
         import torch.distributed as dist
 
+        # NCCL may print a version banner on stdout at its first collective: keep stdout for the JSON line
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
         dist.init_process_group("nccl", device_id=device)
 
     from aklr_b200 import _lib
@@ -270,8 +275,12 @@ def main() -> None:
     if world > 1:
         from aklr_b200.ep import bench_ep
 
-        bench_ep(args, cfg, rank, world, device, ClockSampler, workload_config, METRIC, UNIT, measured_peak_hbm)
+        line = bench_ep(args, cfg, rank, world, device, ClockSampler, workload_config, METRIC, UNIT, measured_peak_hbm)
         dist.destroy_process_group()
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
+        if line is not None:
+            print(line, flush=True)
         return
 
     from aklr_b200 import ops
