@@ -24,6 +24,8 @@ struct StageProfile {
 };
 StageProfile g_profile;
 std::atomic<long long> g_launches{0};
+// Tests set this to run full blocks through the weight-major kernel too (aklr_debug_force_weight_major).
+std::atomic<bool> g_force_swap_ab{false};
 
 void profile_mark(cudaStream_t stream, int slot, int stage) {
   if (g_profile.on && slot >= 0) cudaEventRecord(g_profile.events[slot * (kStages + 1) + stage], stream);
@@ -221,15 +223,17 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   g1.rows_per_expert = 2 * c.inter;
   g1.block_m = l.block_m;
   g1.max_blocks = l.max_blocks;
-  g1.stages = grouped_gemm_pick_stages(true, l.block_m, c.hidden);
+  const bool tm1 = grouped_gemm_is_token_major(true, l.block_m, c.inter) && !g_force_swap_ab;
+  g1.stages = tm1 ? grouped_gemm_prefill_pick_stages(c.hidden) : grouped_gemm_pick_stages(true, l.block_m, c.hidden);
   if (g1.stages < 2) return fail(AKLR_ERR_UNSUPPORTED_SHAPE, "hidden=%d needs more shared memory than one SM has", c.hidden);
-  rc = launch_grouped_gemm_gate_up(g1, sms, stream);
+  rc = tm1 ? launch_grouped_gemm_prefill(g1, true, sms, stream) : launch_grouped_gemm_gate_up(g1, sms, stream);
   if (rc) return fail(rc, "gate_up grouped GEMM launch failed");
   g_launches += 1;
   profile_mark(stream, slot, 4);
 
   GroupedGemmParams g2{};
-  rc = make_map_u8(&g2.map_w, w2, static_cast<uint64_t>(experts) * c.hidden, c.inter, 128);
+  const bool tm2 = grouped_gemm_is_token_major(false, l.block_m, c.hidden) && !g_force_swap_ab;
+  rc = make_map_u8(&g2.map_w, w2, static_cast<uint64_t>(experts) * c.hidden, c.inter, tm2 ? 256 : 128);
   if (rc) return rc;
   rc = make_map_u8(&g2.map_x, ws + l.hq, l.capacity, c.inter, l.block_m);
   if (rc) return rc;
@@ -246,9 +250,9 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   g2.rows_per_expert = c.hidden;
   g2.block_m = l.block_m;
   g2.max_blocks = l.max_blocks;
-  g2.stages = grouped_gemm_pick_stages(false, l.block_m, c.inter);
+  g2.stages = tm2 ? grouped_gemm_prefill_pick_stages(c.inter) : grouped_gemm_pick_stages(false, l.block_m, c.inter);
   if (g2.stages < 2) return fail(AKLR_ERR_UNSUPPORTED_SHAPE, "inter=%d needs more shared memory than one SM has", c.inter);
-  rc = launch_grouped_gemm_down(g2, sms, stream);
+  rc = tm2 ? launch_grouped_gemm_prefill(g2, false, sms, stream) : launch_grouped_gemm_down(g2, sms, stream);
   if (rc) return fail(rc, "down grouped GEMM launch failed");
   g_launches += 1;
   profile_mark(stream, slot, 5);
@@ -549,6 +553,11 @@ int aklr_moe_read_status(const void* workspace, int32_t* host_status, void* stre
 }
 
 int64_t aklr_kernel_launch_count(void) { return g_launches.load(); }
+
+int aklr_debug_force_weight_major(int32_t on) {
+  g_force_swap_ab = on != 0;
+  return AKLR_OK;
+}
 
 int aklr_profile_begin(int32_t max_calls) {
   for (cudaEvent_t e : g_profile.events) cudaEventDestroy(e);

@@ -191,6 +191,9 @@ int aklr_moe_read_status(const void* workspace, int32_t* host_status, void* stre
  * n = 0 switches it off.  aklr_profile_read(call, ms[6]) waits for that call and gives its
  * stage durations in milliseconds. */
 int64_t aklr_kernel_launch_count(void);
+/* Test aid: non-zero makes full 128-token blocks use the weight-major grouped GEMM (the decode
+ * kernel) instead of the token-major one, so both can be checked on the same inputs. */
+int aklr_debug_force_weight_major(int32_t on);
 int aklr_profile_begin(int32_t max_calls);
 int aklr_profile_read(int32_t call, float* stage_ms);
 

@@ -368,3 +368,24 @@ def test_deepseek_v3_full_width_on_sampled_tokens(n_tokens):
     perm = torch.randperm(n_tokens, generator=torch.Generator().manual_seed(1))
     out2 = fused_moe_fp8(hidden[perm].to(d), logits[perm].to(d), bias.to(d), w1, s1, w2, s2, routing_of(cfg))
     assert torch.equal(out2.cpu(), out.cpu()[perm])
+
+
+def test_token_major_and_weight_major_kernels_agree(golden):
+    """Full 128-token blocks run the token-major grouped GEMM; forcing the weight-major one on the
+    same inputs must pass the same gates and agree closely."""
+    from aklr_b200 import _lib
+
+    cfg, a = cases.ds_small_layer()
+    lib = _lib.load()
+    out_tm, ws = run_layer(cfg, a, t(golden["ds_small.logits"]), 128)
+    check_intermediates(cfg, a, ws, t(golden["ds_small.ids"]))
+    lib.aklr_debug_force_weight_major(1)
+    try:
+        out_wm, _ = run_layer(cfg, a, t(golden["ds_small.logits"]), 128)
+    finally:
+        lib.aklr_debug_force_weight_major(0)
+    for out in (out_tm, out_wm):
+        gates = orc.output_gates(out.cpu(), t(golden["ds_small.out"]))
+        assert orc.gates_pass(gates), gates
+    close = orc.output_gates(out_tm.cpu(), out_wm.cpu().float())
+    assert close["sqnr_db"] > 45.0, close
