@@ -157,7 +157,7 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
       const long long t_role = clock64();
 #endif
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const int j = t / nb, b = t - j * nb;
+        const int b = t / tiles_per_block, j = t - b * tiles_per_block;
         const int e = p.block_expert[b];
         const int w_row = e * p.rows_per_expert + j * 128;
         for (int kb = 0; kb < KB; ++kb, ++it) {
@@ -250,7 +250,7 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
       t_mark = clock64();
 #endif
       if (epi_bar_any(*abort_flag)) break;   // also fences the aliased smem against the last tile
-      const int j = t / nb, b = t - j * nb;
+      const int b = t / tiles_per_block, j = t - b * tiles_per_block;
       const int e = p.block_expert[b];
       // Combined scale table of the tile, ftab[tile][kb][n] = activation scale x weight block
       // scale, so the K loop is one shared-memory float4 per four columns and one FMA per element.

@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
       uint32_t it = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const int j = t / nb, b = t - j * nb;
+        const int b = t / tiles_per_block, j = t - b * tiles_per_block;
         const int e = p.block_expert[b];
         const int w_row = e * p.rows_per_expert + (GATE_UP ? j * 128 : j * 256);
         for (int kb = 0; kb < KB; ++kb, ++it) {
@@ -270,7 +270,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
       t_mark = clock64();
 #endif
       if (epi_any(*abort_flag)) break;
-      const int j = t / nb, b = t - j * nb;
+      const int b = t / tiles_per_block, j = t - b * tiles_per_block;
       const int e = p.block_expert[b];
       {
         const float* xs = p.x_scale + static_cast<size_t>(b) * KB * kBM;
