@@ -19,6 +19,9 @@
 // Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..9
 // epilogue (TMEM lane quarter = warp % 4, column half = (warp-2)/4).
 #include <cfloat>
+#include <map>
+#include <mutex>
+#include <utility>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -408,6 +411,21 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
   }
 }
 
+int ensure_max_dynamic_smem(const void* kernel) {
+  static std::mutex lock;
+  static std::map<std::pair<const void*, int>, bool> granted;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return AKLR_ERR_CUDA;
+  std::lock_guard<std::mutex> guard(lock);
+  bool& done = granted[{kernel, dev}];
+  if (!done) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
+      return AKLR_ERR_CUDA;
+    done = true;
+  }
+  return AKLR_OK;
+}
+
 template <bool GATE_UP>
 static int launch_grouped(const GroupedGemmParams& p, int sm_count, cudaStream_t stream) {
   if (p.k % 128 != 0 || p.out_dim % 128 != 0 || p.max_blocks < 1) return AKLR_ERR_UNSUPPORTED_SHAPE;
@@ -417,8 +435,7 @@ static int launch_grouped(const GroupedGemmParams& p, int sm_count, cudaStream_t
   const long long tiles = static_cast<long long>(p.max_blocks) * (p.out_dim / 128);
   const int grid = static_cast<int>(tiles < sm_count ? tiles : sm_count);
   auto run = [&](auto kernel) {
-    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (err != cudaSuccess) return AKLR_ERR_CUDA;
+    if (ensure_max_dynamic_smem(reinterpret_cast<const void*>(kernel)) != AKLR_OK) return AKLR_ERR_CUDA;
     kernel<<<grid, kGemmThreads, smem, stream>>>(p);
     return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
   };

@@ -453,8 +453,7 @@ int launch_grouped_gemm_prefill(const GroupedGemmParams& p, bool gate_up, int sm
   const long long tiles = static_cast<long long>(p.max_blocks) * (gate_up ? p.out_dim / 128 : p.out_dim / 256);
   const int grid = static_cast<int>(tiles < sm_count ? tiles : sm_count);
   auto run = [&](auto kernel) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
-      return AKLR_ERR_CUDA;
+    if (ensure_max_dynamic_smem(reinterpret_cast<const void*>(kernel)) != AKLR_OK) return AKLR_ERR_CUDA;
     kernel<<<grid, kThreads, smem, stream>>>(p);
     return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
   };

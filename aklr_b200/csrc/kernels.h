@@ -120,6 +120,9 @@ struct EpCombineParams {
 };
 int launch_ep_combine(const EpCombineParams& p, cudaStream_t stream);
 
+// Opt a kernel in to the full 227 KB of dynamic shared memory, once per (kernel, device).
+int ensure_max_dynamic_smem(const void* kernel);
+
 int launch_router_gemm(const void* x_bf16, const void* w_bf16, void* logits_bf16, int n_tokens, int hidden,
                        int n_routed, cudaStream_t stream);
 

@@ -389,3 +389,31 @@ def test_token_major_and_weight_major_kernels_agree(golden):
         assert orc.gates_pass(gates), gates
     close = orc.output_gates(out_tm.cpu(), out_wm.cpu().float())
     assert close["sqnr_db"] > 45.0, close
+
+
+def test_layer_call_is_cuda_graph_capturable():
+    """No allocation, synchronisation or host read inside the call: it can be captured once a shape
+    has run eagerly, and a replay on new input values gives what the eager call gives."""
+    from aklr_b200.moe import Workspace, _config, fused_moe_fp8
+
+    cfg = wl.CONFIGS["deepseek_small"]
+    d = dev()
+    w1, s1, w2, s2 = (x.to(d) for x in wl.expert_weights(cfg, seed=9))
+    hidden, logits, bias = (x.to(d) for x in wl.router_inputs(cfg, 24, seed=1))
+    routing = routing_of(cfg)
+    ws = Workspace(_config(24, cfg.hidden, cfg.inter, cfg.n_routed, routing, logits, bias), d)
+    out = torch.empty_like(hidden)
+    fused_moe_fp8(hidden, logits, bias, w1, s1, w2, s2, routing, out=out, workspace=ws)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fused_moe_fp8(hidden, logits, bias, w1, s1, w2, s2, routing, out=out, workspace=ws)
+    hidden2, logits2, _ = (x.to(d) for x in wl.router_inputs(cfg, 24, seed=2))
+    hidden.copy_(hidden2)
+    logits.copy_(logits2)
+    graph.replay()
+    torch.cuda.synchronize()
+    replayed = out.clone()
+    eager = fused_moe_fp8(hidden2, logits2, bias, w1, s1, w2, s2, routing)
+    assert torch.equal(replayed, eager)
+    ws.check_status()
