@@ -80,6 +80,24 @@ int make_map_u8(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols
   return AKLR_OK;
 }
 
+// Packed e2m1 matrix [rows, cols elements]: the TMA unpacks 16 nibbles (8 bytes) to 16 bytes in shared
+// memory, the layout the mixed f8f6f4 MMA reads.  Box = box_rows x 128 elements, SWIZZLE_128B.
+int make_map_fp4(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (!encode) return fail(AKLR_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  if (reinterpret_cast<uintptr_t>(base) % 32 != 0 || (cols / 2) % 32 != 0)
+    return fail(AKLR_ERR_BAD_ARGUMENT, "packed fp4 TMA operand must be 32-byte aligned with a 32-byte multiple row pitch");
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols / 2};
+  const cuuint32_t box[2] = {128, box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, const_cast<void*>(base), dims, strides, box,
+                            elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(AKLR_ERR_CUDA, "cuTensorMapEncodeTiled (packed fp4) failed with CUresult %d", (int)r);
+  return AKLR_OK;
+}
+
 int sm_count() {
   int dev = 0, n = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return 0;
@@ -277,6 +295,111 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   return AKLR_OK;
 }
 
+// MXFP4 experts after the routing table exists: sort, MXFP8 quant, two block-scaled GEMMs, combine.
+int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, const void* hidden_states,
+                   const int32_t* topk_ids, const float* topk_weights, const int32_t* expert_map,
+                   int n_experts_global, const void* w1, const uint8_t* w1_scale, const void* w2,
+                   const uint8_t* w2_scale, float swiglu_limit, void* out, uint8_t* ws, cudaStream_t stream) {
+  using namespace aklr;
+  const int routes_per_token = c.topk + c.n_shared;
+  const int routes = c.n_tokens * routes_per_token;
+  const int experts = c.n_routed + c.n_shared;
+  int32_t* status = reinterpret_cast<int32_t*>(ws + l.status);
+  int32_t* num_blocks = reinterpret_cast<int32_t*>(ws + l.num_blocks);
+  int32_t* sorted_ids = reinterpret_cast<int32_t*>(ws + l.sorted_ids);
+  int32_t* block_expert = reinterpret_cast<int32_t*>(ws + l.block_expert);
+
+  AlignParams ap{};
+  ap.topk_ids = topk_ids;
+  ap.expert_map = expert_map;
+  ap.sorted_ids = sorted_ids;
+  ap.block_expert = block_expert;
+  ap.counts = reinterpret_cast<int32_t*>(ws + l.counts);
+  ap.num_blocks = num_blocks;
+  ap.chunk_hist = reinterpret_cast<int32_t*>(ws + l.chunk_hist);
+  ap.n_routes = routes;
+  ap.n_experts = experts;
+  ap.n_experts_global = n_experts_global;
+  ap.block_m = 128;
+  int rc = launch_align(ap, stream);
+  if (rc) return fail(rc, "moe_align launch failed");
+  g_launches += routes <= 4096 ? 1 : 3;
+
+  MxQuantParams qp{};
+  qp.x = hidden_states;
+  qp.sorted_ids = sorted_ids;
+  qp.num_rows = num_blocks + 1;
+  qp.q = ws + l.xq;
+  qp.scales = ws + l.xs;
+  qp.n_rows = l.capacity;
+  qp.hidden = c.hidden;
+  qp.routes_per_token = routes_per_token;
+  rc = launch_gather_quant_mxfp8(qp, stream);
+  if (rc) return fail(rc, "MXFP8 activation quant launch failed");
+  g_launches += 1;
+
+  const int sms = sm_count();
+  const int stages = grouped_gemm_mx_pick_stages();
+  MxGemmParams g1{};
+  rc = make_map_fp4(&g1.map_w, w1, static_cast<uint64_t>(experts) * 2 * c.inter, c.hidden, 128);
+  if (rc) return rc;
+  rc = make_map_u8(&g1.map_x, ws + l.xq, l.capacity, c.hidden, 128);
+  if (rc) return rc;
+  g1.w_scale = w1_scale;
+  g1.x_scale = ws + l.xs;
+  g1.sorted_ids = sorted_ids;
+  g1.block_expert = block_expert;
+  g1.num_blocks = num_blocks;
+  g1.out_q = ws + l.hq;
+  g1.out_scale = ws + l.hs;
+  g1.status = status;
+  g1.swiglu_limit = swiglu_limit;
+  g1.k = c.hidden;
+  g1.out_dim = c.inter;
+  g1.rows_per_expert = 2 * c.inter;
+  g1.max_blocks = l.max_blocks;
+  g1.stages = stages;
+  rc = launch_grouped_gemm_mx(g1, true, sms, stream);
+  if (rc) return fail(rc, "MX gate_up grouped GEMM launch failed");
+  g_launches += 1;
+
+  MxGemmParams g2{};
+  rc = make_map_fp4(&g2.map_w, w2, static_cast<uint64_t>(experts) * c.hidden, c.inter, 256);
+  if (rc) return rc;
+  rc = make_map_u8(&g2.map_x, ws + l.hq, l.capacity, c.inter, 128);
+  if (rc) return rc;
+  g2.w_scale = w2_scale;
+  g2.x_scale = ws + l.hs;
+  g2.sorted_ids = sorted_ids;
+  g2.block_expert = block_expert;
+  g2.num_blocks = num_blocks;
+  g2.topk_weights = topk_weights;
+  g2.out_rows = ws + l.rows;
+  g2.status = status;
+  g2.k = c.inter;
+  g2.out_dim = c.hidden;
+  g2.rows_per_expert = c.hidden;
+  g2.max_blocks = l.max_blocks;
+  g2.stages = stages;
+  rc = launch_grouped_gemm_mx(g2, false, sms, stream);
+  if (rc) return fail(rc, "MX down grouped GEMM launch failed");
+  g_launches += 1;
+
+  CombineParams cp{};
+  cp.rows = ws + l.rows;
+  cp.topk_ids = topk_ids;
+  cp.expert_map = expert_map;
+  cp.out = out;
+  cp.n_tokens = c.n_tokens;
+  cp.hidden = c.hidden;
+  cp.routes_per_token = routes_per_token;
+  cp.n_experts_global = n_experts_global;
+  rc = launch_combine(cp, stream);
+  if (rc) return fail(rc, "combine launch failed");
+  g_launches += 1;
+  return AKLR_OK;
+}
+
 int prepare(const aklr_moe_config* cfg, aklr_moe_workspace_layout* l, void* workspace, size_t workspace_bytes,
             cudaStream_t stream) {
   if (!cfg) return fail(AKLR_ERR_BAD_ARGUMENT, "cfg is NULL");
@@ -387,6 +510,50 @@ int aklr_moe_fp8_experts_prequant(const aklr_moe_config* cfg, const void* rows_q
   return run_experts(*cfg, l, nullptr, expert_ids, weights, nullptr, cfg->n_routed, w1, w1_scale, w2, w2_scale, nullptr,
                      static_cast<uint8_t*>(workspace), stream, slot, static_cast<const uint8_t*>(rows_q), rows_scale,
                      out_rows);
+}
+
+int aklr_moe_mxfp4_experts(const aklr_moe_config* cfg, const void* hidden_states, const int32_t* topk_ids,
+                           const float* topk_weights, const int32_t* expert_map, const void* w1,
+                           const uint8_t* w1_scale, const void* w2, const uint8_t* w2_scale, float swiglu_limit,
+                           void* out, void* workspace, size_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!cfg) return fail(AKLR_ERR_BAD_ARGUMENT, "cfg is NULL");
+  if (cfg->block_m != 128) return fail(AKLR_ERR_BAD_ARGUMENT, "the MXFP4 path works on 128-token blocks: set block_m = 128");
+  if (cfg->hidden % 256 != 0) return fail(AKLR_ERR_UNSUPPORTED_SHAPE, "the MXFP4 path needs hidden %% 256 == 0 (got %d)", cfg->hidden);
+  aklr_moe_workspace_layout l;
+  int rc = prepare(cfg, &l, workspace, workspace_bytes, stream);
+  if (rc) return rc;
+  if (cfg->n_tokens == 0) return AKLR_OK;
+  if (!hidden_states || !topk_ids || !topk_weights || !w1 || !w1_scale || !w2 || !w2_scale || !out)
+    return fail(AKLR_ERR_BAD_ARGUMENT, "NULL tensor argument");
+  const int local = cfg->n_routed + cfg->n_shared;
+  const int global = expert_map ? cfg->n_experts_global : local;
+  if (expert_map && global < 1) return fail(AKLR_ERR_BAD_ARGUMENT, "n_experts_global must be set with an expert map");
+  return run_mx_experts(*cfg, l, hidden_states, topk_ids, topk_weights, expert_map, global, w1, w1_scale, w2, w2_scale,
+                        swiglu_limit, out, static_cast<uint8_t*>(workspace), stream);
+}
+
+int aklr_moe_mxfp4_forward(const aklr_moe_config* cfg, const void* hidden_states, const void* logits,
+                           const void* bias, const float* sigmoid_table, const void* w1, const uint8_t* w1_scale,
+                           const void* w2, const uint8_t* w2_scale, float swiglu_limit, void* out, void* workspace,
+                           size_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!cfg) return fail(AKLR_ERR_BAD_ARGUMENT, "cfg is NULL");
+  if (cfg->block_m != 128) return fail(AKLR_ERR_BAD_ARGUMENT, "the MXFP4 path works on 128-token blocks: set block_m = 128");
+  if (cfg->hidden % 256 != 0) return fail(AKLR_ERR_UNSUPPORTED_SHAPE, "the MXFP4 path needs hidden %% 256 == 0 (got %d)", cfg->hidden);
+  aklr_moe_workspace_layout l;
+  int rc = prepare(cfg, &l, workspace, workspace_bytes, stream);
+  if (rc) return rc;
+  if (cfg->n_tokens == 0) return AKLR_OK;
+  if (!hidden_states || !logits || !w1 || !w1_scale || !w2 || !w2_scale || !out)
+    return fail(AKLR_ERR_BAD_ARGUMENT, "NULL tensor argument");
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  int32_t* ids = reinterpret_cast<int32_t*>(ws + l.topk_ids);
+  float* weights = reinterpret_cast<float*>(ws + l.topk_weights);
+  rc = aklr_moe_route(cfg, logits, bias, sigmoid_table, ids, weights, stream_);
+  if (rc) return rc;
+  return run_mx_experts(*cfg, l, hidden_states, ids, weights, nullptr, cfg->n_routed + cfg->n_shared, w1, w1_scale, w2,
+                        w2_scale, swiglu_limit, out, ws, stream);
 }
 
 int aklr_ep_dispatch_meta(const int32_t* sorted_ids, const int32_t* topk_ids, const float* topk_weights,

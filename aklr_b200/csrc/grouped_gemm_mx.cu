@@ -1,0 +1,411 @@
+// Grouped GEMMs of the MXFP4-weight / MXFP8-activation MoE layer on tcgen05 block-scaled MMA
+// (sm_100a): `tcgen05.mma.kind::mxf8f6f4.block_scale`, e4m3 activations x e2m1 weights, one ue8m0
+// scale per 32 K elements on both operands, applied inside the tensor core.  Arithmetic of
+// aklr/ops/fused_moe/reference.py:40-127 (act_quant 8) and aklr/ops/mega_moe/reference.py:18-48:
+// gate_up -> (optional clamp) -> SiLU*mul -> bf16 round -> MXFP8 requant per 1 x 32 -> down -> route
+// weight.
+//
+// Because the scales go through the MMA, a tile's whole K reduction accumulates in TMEM and is read
+// out once -- there is no per-K-block fold as in the FP8 128x128 path.
+//
+// Token-major tiles (128 tokens = TMEM lanes, 256 weight rows = columns; gate rows j*128.. then up
+// rows I + j*128.. for gate_up, 256 output channels for down).  Operands:
+//   * activations: e4m3 rows, TMA SWIZZLE_128B, 128 K bytes per K-block;
+//   * weights: packed e2m1 in HBM (64 bytes per 128 K elements), loaded by a TMA map of type
+//     16U4_ALIGN16B, which unpacks them in shared memory to the padded 128-byte rows the mixed
+//     f8f6f4 MMA reads -- HBM traffic is 4 bits per weight;
+//   * scale factors: copied shared memory -> TMEM by tcgen05.cp (32x128b.warpx4) per K-block; a
+//     32-bit TMEM column holds the 4 scale bytes of a row's four K=32 steps, rows r in lane r % 32,
+//     column r / 32.  Activation scales are produced in that order by the quantising kernels; weight
+//     scales stay row-major in HBM ([rows, K/32] bytes, as the checkpoint stores them) and the idle
+//     epilogue warps re-order one 32-bit word per row per K-block into the stage.
+//
+// Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..9 stage
+// scale factors during the K loop and run the epilogue.  Persistent CTAs, bounded waits, no cluster,
+// no multicast.
+#include <cfloat>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace aklr {
+
+namespace {
+
+constexpr int kThreads = 320;
+constexpr int kEpi = 256;
+constexpr int kBM = 128;
+constexpr int kBN = 256;
+constexpr int kABytes = kBM * 128;
+constexpr int kBBytes = kBN * 128;          // unpacked: one byte per e2m1 element in shared memory
+constexpr int kSfaBytes = 512;              // 128 rows x 4 K-steps
+constexpr int kStageBytes = kABytes + kBBytes + 2048;  // operands + scale factors (padded to 2 KB)
+constexpr int kSfaCol = 256, kSfbCol = 260;  // TMEM columns after the 256 accumulator columns
+
+struct MxLayout {
+  int off_rid, off_wgt, off_bars, total;
+};
+
+__host__ __device__ inline MxLayout mx_layout(int stages) {
+  MxLayout l;
+  l.off_rid = stages * kStageBytes;
+  l.off_wgt = l.off_rid + kBM * 4;
+  l.off_bars = l.off_wgt + kBM * 4;
+  l.total = l.off_bars + (3 * stages + 2) * 8 + 16;
+  return l;
+}
+
+__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ bool epi_any(int flag) {
+  uint32_t any;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.or.pred p, 1, 256, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(any)
+      : "r"(flag)
+      : "memory");
+  return any != 0;
+}
+
+// kind::mxf8f6f4 block-scaled instruction descriptor: A e4m3, B e2m1, both K-major, ue8m0 scales,
+// M = 128; sf_id picks which byte of the 32-bit scale column this K=32 step uses.
+__device__ __forceinline__ uint32_t mx_idesc(int n, int sf_id) {
+  return (static_cast<uint32_t>(sf_id) << 4) | (0u << 7) | (5u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (1u << 23) | (static_cast<uint32_t>(128 >> 4) << 24) | (static_cast<uint32_t>(sf_id) << 29);
+}
+
+__device__ __forceinline__ void umma_mx(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                        uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+      : "memory");
+}
+
+// 32 rows x 16 bytes, rows contiguous: no swizzle, 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t sf_desc(uint32_t smem_addr) {
+  return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) | (8ull << 32) | (1ull << 46);
+}
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// ue8m0 exponent of the smallest power of two >= amax / 448 (frexp rule of the reference's _mxfp8):
+// returns the unbiased exponent in [-126, 127]; amax == 0 gives 0 (scale 1).
+__device__ __forceinline__ int mxfp8_exponent(float amax) {
+  if (amax == 0.0f) return 0;
+  const uint32_t bits = __float_as_uint(__fdiv_rn(amax, 448.0f));
+  int e = static_cast<int>(bits >> 23) - 127 + ((bits & 0x7FFFFFu) != 0u ? 1 : 0);
+  return e < -126 ? -126 : (e > 127 ? 127 : e);
+}
+
+template <bool GATE_UP>
+__global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __grid_constant__ MxGemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int KB = p.k >> 7;
+  const int S = p.stages;
+  const MxLayout L = mx_layout(S);
+  int* rid_s = reinterpret_cast<int*>(smem + L.off_rid);
+  float* wgt_s = reinterpret_cast<float*>(smem + L.off_wgt);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.off_bars);
+  uint64_t* empty = full + S;
+  uint64_t* sf_full = empty + S;
+  uint64_t* acc_full = sf_full + S;
+  uint64_t* acc_empty = acc_full + 1;
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(acc_empty + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int nb = *p.num_blocks;
+  if (nb > p.max_blocks) nb = p.max_blocks;
+  const int tiles_per_block = GATE_UP ? (p.out_dim >> 7) : (p.out_dim >> 8);
+  const int total_tiles = nb * tiles_per_block;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+      mbar_init(&sf_full[s], kEpi / 32);
+    }
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, kEpi / 32);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&p.map_w);
+    tma_prefetch_desc(&p.map_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_ptr, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer ------------------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int b = t / tiles_per_block, j = t - b * tiles_per_block;
+        const int e = p.block_expert[b];
+        const int w_row = e * p.rows_per_expert + (GATE_UP ? j * 128 : j * 256);
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 21)) { ok = false; break; }
+          uint8_t* st = smem + s * kStageBytes;
+          // the transaction count of the unpacking fp4 load is its packed size (what crosses from
+          // global memory), not the padded bytes it writes: expecting the padded size never completes
+          mbar_expect_tx(&full[s], kABytes + kBBytes / 2);
+          tma_load_2d(st, &p.map_x, &full[s], kb * 128, b * kBM);
+          if (GATE_UP) {
+            tma_load_2d(st + kABytes, &p.map_w, &full[s], kb * 128, w_row);
+            tma_load_2d(st + kABytes + kBBytes / 2, &p.map_w, &full[s], kb * 128, w_row + p.out_dim);
+          } else {
+            tma_load_2d(st + kABytes, &p.map_w, &full[s], kb * 128, w_row);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer --------------------------------------------
+    if (lane == 0) {
+      uint32_t it = 0, tile_no = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_no) {
+        // the single accumulator must have been read out by the previous tile's epilogue
+        if (!mbar_wait(acc_empty, (tile_no & 1) ^ 1, abort_flag, p.status, 22)) break;
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          if (!mbar_wait(&full[s], ph, abort_flag, p.status, 23)) { ok = false; break; }
+          if (!mbar_wait(&sf_full[s], ph, abort_flag, p.status, 24)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a0 = smem_u32(smem + s * kStageBytes);
+          const uint32_t sf0 = a0 + kABytes + kBBytes;
+          tmem_cp_32x128b_warpx4(tmem_base + kSfaCol, sf_desc(sf0));
+          tmem_cp_32x128b_warpx4(tmem_base + kSfbCol, sf_desc(sf0 + kSfaBytes));
+          tmem_cp_32x128b_warpx4(tmem_base + kSfbCol + 4, sf_desc(sf0 + kSfaBytes + 512));
+          const uint64_t da = umma_desc_sw128(a0);
+          const uint64_t db = umma_desc_sw128(a0 + kABytes);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_mx(tmem_base, da + 2 * k, db + 2 * k, mx_idesc(kBN, k), tmem_base + kSfaCol, tmem_base + kSfbCol,
+                    (kb > 0 || k > 0) ? 1u : 0u);
+          tc_commit(&empty[s]);
+        }
+        if (ok) tc_commit(acc_full);
+      }
+    }
+  } else {
+    // ------------------- scale-factor staging during the K loop, then the epilogue -------------
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int et = threadIdx.x - 64;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const int KS = p.k >> 5;  // scale bytes per weight row
+    uint32_t it = 0, tile_no = 0;
+    bool bad = false;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_no) {
+      if (epi_any(*abort_flag)) break;
+      const int b = t / tiles_per_block, j = t - b * tiles_per_block;
+      const int e = p.block_expert[b];
+      if (et < kBM) {
+        const int rid = p.sorted_ids[b * kBM + et];
+        rid_s[et] = rid;
+        if (!GATE_UP) wgt_s[et] = rid >= 0 ? p.topk_weights[rid] : 0.0f;
+      }
+      epi_sync();  // the epilogue reads other threads' entries
+      // this thread's weight row of the tile (256 rows, one per staging thread)
+      const int wrow = GATE_UP ? (et < 128 ? j * 128 + et : p.out_dim + j * 128 + (et - 128)) : j * 256 + et;
+      const uint8_t* wsf = p.w_scale + (static_cast<size_t>(e) * p.rows_per_expert + wrow) * KS;
+      const uint8_t* xsf = p.x_scale + static_cast<size_t>(b) * KB * kSfaBytes;
+      for (int kb = 0; kb < KB; ++kb, ++it) {
+        const int s = it % S;
+        const uint32_t ph = (it / S) & 1;
+        if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 25)) bad = true;
+        uint8_t* sf = smem + s * kStageBytes + kABytes + kBBytes;
+        if (et < 32) *reinterpret_cast<uint4*>(sf + et * 16) = __ldg(reinterpret_cast<const uint4*>(xsf + kb * kSfaBytes) + et);
+        const int r = et & 127;
+        *reinterpret_cast<uint32_t*>(sf + kSfaBytes + (et >> 7) * 512 + (r & 31) * 16 + (r >> 5) * 4) =
+            __ldg(reinterpret_cast<const uint32_t*>(wsf + kb * 4));
+        fence_proxy_async_smem();  // tcgen05.cp reads these bytes through the async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sf_full[s]);
+      }
+
+      // ---- epilogue: the whole K reduction is in TMEM ----
+      if (!mbar_wait(acc_full, tile_no & 1, abort_flag, p.status, 26)) bad = true;
+      tc_fence_after_sync();
+      float acc[128];
+      {
+        const uint32_t t0 = tmem_base + lane_addr + (GATE_UP ? half * 64 : half * 128);
+#pragma unroll
+        for (int c = 0; c < 128; c += 16) {
+          uint32_t r[16];
+          const uint32_t at = GATE_UP ? (c < 64 ? t0 + c : t0 + 128 + (c - 64)) : t0 + c;
+          AKLR_TMEM_LD_16(at, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) acc[c + i] = __uint_as_float(r[i]);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty);
+
+      const int rid = rid_s[row];
+      if (GATE_UP) {
+        const int IB = p.out_dim >> 7;
+        // two 1 x 32 groups of this thread's 64 h channels
+        uint32_t packed[16];
+        uint32_t scale_bytes = 0;
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+          float m = 0.0f;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float gate = acc[g * 32 + i], up = acc[64 + g * 32 + i];
+            if (p.swiglu_limit > 0.0f) {
+              gate = fminf(gate, p.swiglu_limit);
+              up = fminf(fmaxf(up, -p.swiglu_limit), p.swiglu_limit);
+            }
+            const float h = __fdividef(gate, 1.0f + __expf(-gate)) * up;
+            acc[g * 32 + i] = __bfloat162float(__float2bfloat16_rn(h));
+            m = fmaxf(m, fabsf(acc[g * 32 + i]));
+          }
+          const int ex = mxfp8_exponent(m);
+          const float inv = __uint_as_float(static_cast<uint32_t>(127 - ex) << 23);  // 2^-ex, exact
+          scale_bytes |= static_cast<uint32_t>(ex + 127) << (8 * g);
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            packed[g * 8 + i / 4] = cvt_e4m3x2(acc[g * 32 + i] * inv, acc[g * 32 + i + 1] * inv) |
+                                    (static_cast<uint32_t>(cvt_e4m3x2(acc[g * 32 + i + 2] * inv, acc[g * 32 + i + 3] * inv)) << 16);
+        }
+        if (rid >= 0 && !bad) {
+          uint8_t* dst = p.out_q + static_cast<size_t>(b * kBM + row) * p.out_dim + j * 128 + half * 64;
+#pragma unroll
+          for (int v = 0; v < 4; ++v)
+            *reinterpret_cast<uint4*>(dst + v * 16) = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+          // scale bytes in the order the down projection's tcgen05.cp wants them
+          *reinterpret_cast<uint16_t*>(p.out_scale + (static_cast<size_t>(b) * IB + j) * kSfaBytes + (row & 31) * 16 +
+                                       (row >> 5) * 4 + half * 2) = static_cast<uint16_t>(scale_bytes);
+        }
+      } else if (rid >= 0 && !bad) {
+        const float w = wgt_s[row];
+        uint8_t* dst = static_cast<uint8_t*>(p.out_rows) + (static_cast<size_t>(rid) * p.out_dim + j * 256 + half * 128) * 2;
+#pragma unroll
+        for (int v = 0; v < 16; ++v) {
+          uint32_t o[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const __nv_bfloat162 two = __floats2bfloat162_rn(acc[v * 8 + 2 * q] * w, acc[v * 8 + 2 * q + 1] * w);
+            o[q] = *reinterpret_cast<const uint32_t*>(&two);
+          }
+          *reinterpret_cast<uint4*>(dst + v * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t start = global_timer_ns();
+    while (global_timer_ns() - start < 200000ull) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// Four lanes x 8 values per 1 x 32 group: rows
+// gathered through the sorted route table, e4m3 codes row-major, scale bytes in tcgen05.cp order.
+__global__ void __launch_bounds__(256) gather_quant_mxfp8_kernel(MxQuantParams p) {
+  const int groups_per_row = p.hidden >> 5;
+  const int n_rows = p.num_rows ? min(*p.num_rows, p.n_rows) : p.n_rows;
+  const int64_t total = static_cast<int64_t>(n_rows) * groups_per_row;
+  const int sub = threadIdx.x & 3;
+  const uint32_t group_mask = 0xFu << (threadIdx.x & 28);
+  const int64_t quads = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 2;
+  const int KB = p.hidden >> 7;
+  for (int64_t g = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 2; g < total; g += quads) {
+    const int row = static_cast<int>(g / groups_per_row);
+    const int grp = static_cast<int>(g - static_cast<int64_t>(row) * groups_per_row);
+    const int rid = p.sorted_ids[row];
+    if (rid < 0) continue;
+    const int token = rid / p.routes_per_token;
+    const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.x) +
+                                                      static_cast<size_t>(token) * p.hidden + grp * 32 + sub * 8);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    float v[8];
+    float m = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+      m = fmaxf(m, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
+    }
+    m = fmaxf(m, __shfl_xor_sync(group_mask, m, 2, 4));
+    m = fmaxf(m, __shfl_xor_sync(group_mask, m, 1, 4));
+    const int ex = mxfp8_exponent(m);
+    const float inv = __uint_as_float(static_cast<uint32_t>(127 - ex) << 23);
+    uint2 out;
+    out.x = cvt_e4m3x2(v[0] * inv, v[1] * inv) | (static_cast<uint32_t>(cvt_e4m3x2(v[2] * inv, v[3] * inv)) << 16);
+    out.y = cvt_e4m3x2(v[4] * inv, v[5] * inv) | (static_cast<uint32_t>(cvt_e4m3x2(v[6] * inv, v[7] * inv)) << 16);
+    *reinterpret_cast<uint2*>(p.q + static_cast<size_t>(row) * p.hidden + grp * 32 + sub * 8) = out;
+    if (sub == 0) {
+      const int b = row >> 7, r = row & 127, kb = grp >> 2, ks = grp & 3;
+      p.scales[(static_cast<size_t>(b) * KB + kb) * kSfaBytes + (r & 31) * 16 + (r >> 5) * 4 + ks] =
+          static_cast<uint8_t>(ex + 127);
+    }
+  }
+}
+
+}  // namespace
+
+int launch_gather_quant_mxfp8(const MxQuantParams& p, cudaStream_t stream) {
+  if (p.hidden % 128 != 0) return AKLR_ERR_UNSUPPORTED_SHAPE;
+  if (p.n_rows == 0) return AKLR_OK;
+  const int64_t groups = static_cast<int64_t>(p.n_rows) * (p.hidden / 32);
+  const int64_t blocks = (groups * 4 + 255) / 256;
+  const int grid = static_cast<int>(blocks < 148 * 16 ? blocks : 148 * 16);
+  gather_quant_mxfp8_kernel<<<grid, 256, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+}
+
+int grouped_gemm_mx_pick_stages() {
+  for (int s = 4; s >= 2; --s)
+    if (mx_layout(s).total + 1024 <= 227 * 1024) return s;
+  return 0;
+}
+
+int launch_grouped_gemm_mx(const MxGemmParams& p, bool gate_up, int sm_count, cudaStream_t stream) {
+  if (p.k % 128 != 0 || p.max_blocks < 1 || p.stages < 2) return AKLR_ERR_UNSUPPORTED_SHAPE;
+  if (gate_up ? (p.out_dim % 128 != 0) : (p.out_dim % 256 != 0)) return AKLR_ERR_UNSUPPORTED_SHAPE;
+  const size_t smem = static_cast<size_t>(mx_layout(p.stages).total) + 1024;
+  if (smem > 227 * 1024) return AKLR_ERR_UNSUPPORTED_SHAPE;
+  const long long tiles = static_cast<long long>(p.max_blocks) * (gate_up ? p.out_dim / 128 : p.out_dim / 256);
+  const int grid = static_cast<int>(tiles < sm_count ? tiles : sm_count);
+  auto run = [&](auto kernel) {
+    if (ensure_max_dynamic_smem(reinterpret_cast<const void*>(kernel)) != AKLR_OK) return AKLR_ERR_CUDA;
+    kernel<<<grid, kThreads, smem, stream>>>(p);
+    return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+  };
+  return gate_up ? run(grouped_gemm_mx_kernel<true>) : run(grouped_gemm_mx_kernel<false>);
+}
+
+}  // namespace aklr

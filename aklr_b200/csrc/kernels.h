@@ -90,6 +90,36 @@ int launch_grouped_gemm_prefill(const GroupedGemmParams& p, bool gate_up, int sm
 size_t grouped_gemm_smem_bytes(bool gate_up, int block_m, int k, int stages);
 int grouped_gemm_pick_stages(bool gate_up, int block_m, int k);
 
+// ---- MXFP4 weights / MXFP8 activations (grouped_gemm_mx.cu), always 128-token blocks ----------
+struct MxQuantParams {
+  const void* x;              // [n_tokens, hidden] bf16
+  const int32_t* sorted_ids;  // [capacity]
+  const int32_t* num_rows;    // device count of rows in use
+  uint8_t* q;                 // [capacity, hidden] e4m3
+  uint8_t* scales;            // [capacity/128, hidden/128, 512] e8m0 bytes in tcgen05.cp order
+  int n_rows, hidden, routes_per_token;
+};
+int launch_gather_quant_mxfp8(const MxQuantParams& p, cudaStream_t stream);
+
+struct MxGemmParams {
+  CUtensorMap map_w;           // packed e2m1 weights [experts*rows_per_expert, k], 16U4_ALIGN16B, box 128 x 128|256
+  CUtensorMap map_x;           // e4m3 activations [capacity, k], box 128 x 128
+  const uint8_t* w_scale;      // e8m0 [experts, rows_per_expert, k/32]
+  const uint8_t* x_scale;      // e8m0 [max_blocks, k/128, 512]
+  const int32_t* sorted_ids;
+  const int32_t* block_expert;
+  const int32_t* num_blocks;
+  const float* topk_weights;   // down only
+  uint8_t* out_q;              // gate_up: [capacity, inter] e4m3
+  uint8_t* out_scale;          // gate_up: [max_blocks, inter/128, 512]
+  void* out_rows;              // down: [n_routes, hidden] bf16
+  int32_t* status;
+  float swiglu_limit;          // > 0: clamp gate above and up on both sides before the activation
+  int k, out_dim, rows_per_expert, max_blocks, stages;
+};
+int grouped_gemm_mx_pick_stages();
+int launch_grouped_gemm_mx(const MxGemmParams& p, bool gate_up, int sm_count, cudaStream_t stream);
+
 struct CombineParams {
   const void* rows;          // [n_tokens * routes_per_token, hidden] bf16
   const int32_t* topk_ids;   // [n_tokens, routes_per_token] global ids

@@ -267,6 +267,88 @@ def fused_experts_fp8(
     return (out, ws) if return_workspace else out
 
 
+def _check_mx_weights(hidden_states, w1, w1_scale, w2, w2_scale):
+    e, two_i, half_h = w1.shape
+    h, inter = half_h * 2, two_i // 2
+    if hidden_states.dtype != torch.bfloat16 or hidden_states.shape[-1] != h:
+        raise ValueError("hidden_states must be bfloat16 [tokens, hidden] matching w1's unpacked last dim")
+    for t in (w1, w1_scale, w2, w2_scale):
+        if t.dtype != torch.uint8:
+            raise ValueError("MXFP4 weights (packed e2m1) and their e8m0 scales are uint8 tensors")
+    if tuple(w2.shape) != (e, h, inter // 2) or tuple(w1_scale.shape) != (e, two_i, h // 32) or tuple(w2_scale.shape) != (e, h, inter // 32):
+        raise ValueError("expected w1 [E,2I,H/2], w1_scale [E,2I,H/32], w2 [E,H,I/2], w2_scale [E,H,I/32]")
+    return e, inter, h
+
+
+def fused_experts_mxfp4(
+    hidden_states: torch.Tensor,
+    topk_ids: torch.Tensor,
+    topk_weights: torch.Tensor,
+    w1: torch.Tensor,
+    w1_scale: torch.Tensor,
+    w2: torch.Tensor,
+    w2_scale: torch.Tensor,
+    expert_map: torch.Tensor | None = None,
+    swiglu_limit: float | None = None,
+    out: torch.Tensor | None = None,
+    return_workspace: bool = False,
+):
+    """MXFP4-weight experts with MXFP8 activations, routing given (block-scaled tcgen05 MMA)."""
+    device = _need_cuda(hidden_states, topk_ids, topk_weights, w1, w1_scale, w2, w2_scale, expert_map, out)
+    e, inter, h = _check_mx_weights(hidden_states, w1, w1_scale, w2, w2_scale)
+    if topk_ids.dtype != torch.int32 or topk_weights.dtype != torch.float32 or topk_ids.shape != topk_weights.shape:
+        raise ValueError("topk_ids int32 and topk_weights float32 must share the shape [tokens, routes]")
+    n_tokens, routes = topk_ids.shape
+    n_global = 0 if expert_map is None else expert_map.numel()
+    cfg = _config(n_tokens, h, inter, e, Routing(topk=routes), None, None, 128, n_global)
+    ws = Workspace(cfg, device)
+    if out is None:
+        out = torch.empty_like(hidden_states)
+    _lib.check(
+        _lib.load().aklr_moe_mxfp4_experts(
+            ctypes.byref(cfg), _ptr(hidden_states), _ptr(topk_ids), _ptr(topk_weights), _ptr(expert_map), _ptr(w1),
+            _ptr(w1_scale), _ptr(w2), _ptr(w2_scale), float(swiglu_limit or 0.0), _ptr(out), ws.base.data_ptr(),
+            ws.layout.total_bytes, _stream(),
+        )
+    )
+    return (out, ws) if return_workspace else out
+
+
+def fused_moe_mxfp4(
+    hidden_states: torch.Tensor,
+    logits: torch.Tensor,
+    bias: torch.Tensor | None,
+    w1: torch.Tensor,
+    w1_scale: torch.Tensor,
+    w2: torch.Tensor,
+    w2_scale: torch.Tensor,
+    routing: Routing,
+    swiglu_limit: float | None = None,
+    out: torch.Tensor | None = None,
+    workspace: Workspace | None = None,
+    return_workspace: bool = False,
+):
+    """The whole MXFP4 layer from router logits (the routing of ``fused_moe_fp8``)."""
+    device = _need_cuda(hidden_states, logits, bias, w1, w1_scale, w2, w2_scale, out)
+    e, inter, h = _check_mx_weights(hidden_states, w1, w1_scale, w2, w2_scale)
+    n_tokens, n_routed = logits.shape
+    if n_routed + routing.n_shared != e or hidden_states.shape[0] != n_tokens:
+        raise ValueError("w1 must hold the routed experts followed by the shared ones")
+    cfg = _config(n_tokens, h, inter, n_routed, routing, logits, bias, 128)
+    ws = workspace or Workspace(cfg, device)
+    if out is None:
+        out = torch.empty_like(hidden_states)
+    table = sigmoid_table(device) if routing.scoring == "sigmoid" and logits.dtype == torch.bfloat16 else None
+    _lib.check(
+        _lib.load().aklr_moe_mxfp4_forward(
+            ctypes.byref(cfg), _ptr(hidden_states), _ptr(logits), _ptr(bias), _ptr(table), _ptr(w1), _ptr(w1_scale),
+            _ptr(w2), _ptr(w2_scale), float(swiglu_limit or 0.0), _ptr(out), ws.base.data_ptr(), ws.layout.total_bytes,
+            _stream(),
+        )
+    )
+    return (out, ws) if return_workspace else out
+
+
 def route(logits: torch.Tensor, bias: torch.Tensor | None, routing: Routing, topk_ids=None, topk_weights=None):
     """(topk_ids int32, topk_weights float32), both [tokens, topk + n_shared]."""
     device = _need_cuda(logits, bias, topk_ids, topk_weights)

@@ -111,6 +111,45 @@ def quantize_block_fp8(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     return codes, scale.reshape(*lead, rb, cb).contiguous()
 
 
+E2M1_GRID = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+
+def quantize_mxfp4(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """float32 [..., rows, cols] -> (packed e2m1 uint8 [..., rows, cols/2], low nibble first;
+    e8m0 scale bytes uint8 [..., rows, cols/32]).  Per 1 x 32 block the scale is the power of two
+    that puts amax in (3, 6]; codes are the nearest grid value, ties to the even code."""
+    grid = torch.tensor(E2M1_GRID, dtype=torch.float32, device=w.device)
+    blocks = w.unflatten(-1, (-1, 32))
+    amax = blocks.abs().amax(dim=-1, keepdim=True).clamp_min(1e-10)
+    mantissa, exponent = torch.frexp(amax)
+    exponent = (exponent - 3 + (mantissa > 0.75).int()).clamp(-127, 127)
+    scaled = blocks / torch.exp2(exponent.float())
+    m = scaled.abs()
+    lo = torch.bucketize(m, grid, right=True) - 1
+    hi = (lo + 1).clamp_max(7)
+    below, above = m - grid[lo], grid[hi] - m
+    up = (above < below) | ((above == below) & (hi % 2 == 0))
+    code = torch.where(up, hi, lo) | ((scaled < 0).long() << 3)
+    code = code.flatten(-2).to(torch.uint8)
+    packed = code[..., 0::2] | (code[..., 1::2] << 4)
+    return packed.contiguous(), (exponent.squeeze(-1) + 127).to(torch.uint8).contiguous()
+
+
+def mx_expert_weights(cfg: MoEConfig, seed: int, device="cpu", experts=None):
+    """(w1 e2m1x2 uint8 [E,2I,H/2], w1_scale e8m0 uint8 [E,2I,H/32], w2 [E,H,I/2], w2_scale [E,H,I/32]):
+    N(0,0.02) quantised to MXFP4, each expert from its own seed."""
+    ids = list(range(cfg.n_experts)) if experts is None else list(experts)
+    h, i = cfg.hidden, cfg.inter
+    w1 = torch.empty((len(ids), 2 * i, h // 2), dtype=torch.uint8, device=device)
+    s1 = torch.empty((len(ids), 2 * i, h // 32), dtype=torch.uint8, device=device)
+    w2 = torch.empty((len(ids), h, i // 2), dtype=torch.uint8, device=device)
+    s2 = torch.empty((len(ids), h, i // 32), dtype=torch.uint8, device=device)
+    for slot, e in enumerate(ids):
+        w1[slot], s1[slot] = quantize_mxfp4(normal(seed, f"w1.{e}", (2 * i, h), 0.02, device))
+        w2[slot], s2[slot] = quantize_mxfp4(normal(seed, f"w2.{e}", (h, i), 0.02, device))
+    return w1, s1, w2, s2
+
+
 def one_expert_weights(cfg: MoEConfig, seed: int, expert: int, device="cpu"):
     """(w1 e4m3 [2I,H], w1_scale, w2 e4m3 [H,I], w2_scale) of one expert: N(0,0.02) quantised per
     128 x 128 block.  Each expert has its own seed, so any subset can be drawn alone."""
@@ -181,8 +220,10 @@ __all__ = [
     "MoEConfig",
     "expert_weights",
     "expected_distinct_experts",
+    "mx_expert_weights",
     "normal",
     "one_expert_weights",
+    "quantize_mxfp4",
     "quantize_block_fp8",
     "roofline_work",
     "router_inputs",

@@ -112,6 +112,23 @@ int aklr_moe_fp8_experts(const aklr_moe_config* cfg, const void* hidden_states, 
                          const float* w1_scale, const void* w2, const float* w2_scale, void* out,
                          void* workspace, size_t workspace_bytes, void* stream);
 
+/* MXFP4 experts with MXFP8 activations: the kernels behind `fused_moe` at quant_type per_1x32 with
+ * act_quant 8 (aklr/ops/fused_moe/api.py:17-44, reference.py:40-127) and the local compute of
+ * `mega_moe` (aklr/ops/mega_moe/reference.py:18-48).  w1 packed e2m1 [E, 2I, H/2] (low nibble
+ * first), w1_scale e8m0 bytes [E, 2I, H/32]; w2 [E, H, I/2], w2_scale [E, H, I/32]; activations
+ * are quantised per 1 x 32 to e4m3 at the smallest power-of-two scale >= amax/448, the gated
+ * product is rounded to bf16 and quantised the same way.  swiglu_limit > 0 clamps gate (above) and
+ * up (both sides) before the activation; <= 0: no clamp.  cfg->block_m must be 128, hidden % 256 == 0.
+ * aklr_moe_mxfp4_forward routes from logits first (the DeepSeek routing of aklr_moe_fp8_forward). */
+int aklr_moe_mxfp4_experts(const aklr_moe_config* cfg, const void* hidden_states, const int32_t* topk_ids,
+                           const float* topk_weights, const int32_t* expert_map, const void* w1,
+                           const uint8_t* w1_scale, const void* w2, const uint8_t* w2_scale, float swiglu_limit,
+                           void* out, void* workspace, size_t workspace_bytes, void* stream);
+int aklr_moe_mxfp4_forward(const aklr_moe_config* cfg, const void* hidden_states, const void* logits,
+                           const void* bias, const float* sigmoid_table, const void* w1, const uint8_t* w1_scale,
+                           const void* w2, const uint8_t* w2_scale, float swiglu_limit, void* out, void* workspace,
+                           size_t workspace_bytes, void* stream);
+
 /* Expert parallelism (the reference's `mega_moe` contract: every rank holds n_local experts, global
  * expert e is local e % n_local of rank e / n_local; aklr/ops/mega_moe/contract.py:42-51,
  * reference.py:25,38).  The host code orders routes by destination rank with aklr_moe_align
