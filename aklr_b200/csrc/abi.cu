@@ -299,7 +299,8 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
 int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, const void* hidden_states,
                    const int32_t* topk_ids, const float* topk_weights, const int32_t* expert_map,
                    int n_experts_global, const void* w1, const uint8_t* w1_scale, const void* w2,
-                   const uint8_t* w2_scale, float swiglu_limit, void* out, uint8_t* ws, cudaStream_t stream) {
+                   const uint8_t* w2_scale, float swiglu_limit, void* out, uint8_t* ws, cudaStream_t stream,
+                   const uint8_t* q_in = nullptr, const uint8_t* scales_in = nullptr, void* rows_out = nullptr) {
   using namespace aklr;
   const int routes_per_token = c.topk + c.n_shared;
   const int routes = c.n_tokens * routes_per_token;
@@ -334,6 +335,8 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   qp.n_rows = l.capacity;
   qp.hidden = c.hidden;
   qp.routes_per_token = routes_per_token;
+  qp.q_in = q_in;
+  qp.scales_in = scales_in;
   rc = launch_gather_quant_mxfp8(qp, stream);
   if (rc) return fail(rc, "MXFP8 activation quant launch failed");
   g_launches += 1;
@@ -374,7 +377,7 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   g2.block_expert = block_expert;
   g2.num_blocks = num_blocks;
   g2.topk_weights = topk_weights;
-  g2.out_rows = ws + l.rows;
+  g2.out_rows = rows_out ? rows_out : ws + l.rows;
   g2.status = status;
   g2.k = c.inter;
   g2.out_dim = c.hidden;
@@ -384,6 +387,7 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   rc = launch_grouped_gemm_mx(g2, false, sms, stream);
   if (rc) return fail(rc, "MX down grouped GEMM launch failed");
   g_launches += 1;
+  if (rows_out) return AKLR_OK;
 
   CombineParams cp{};
   cp.rows = ws + l.rows;
@@ -554,6 +558,47 @@ int aklr_moe_mxfp4_forward(const aklr_moe_config* cfg, const void* hidden_states
   if (rc) return rc;
   return run_mx_experts(*cfg, l, hidden_states, ids, weights, nullptr, cfg->n_routed + cfg->n_shared, w1, w1_scale, w2,
                         w2_scale, swiglu_limit, out, ws, stream);
+}
+
+int aklr_moe_mxfp4_experts_prequant(const aklr_moe_config* cfg, const void* rows_q, const uint8_t* rows_scale,
+                                    const int32_t* expert_ids, const float* weights, const void* w1,
+                                    const uint8_t* w1_scale, const void* w2, const uint8_t* w2_scale,
+                                    float swiglu_limit, void* out_rows, void* workspace, size_t workspace_bytes,
+                                    void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!cfg) return fail(AKLR_ERR_BAD_ARGUMENT, "cfg is NULL");
+  if (cfg->topk != 1 || cfg->n_shared != 0 || cfg->block_m != 128)
+    return fail(AKLR_ERR_BAD_ARGUMENT, "prequantised rows carry one route each: topk 1, n_shared 0, block_m 128");
+  if (cfg->hidden % 256 != 0) return fail(AKLR_ERR_UNSUPPORTED_SHAPE, "the MXFP4 path needs hidden %% 256 == 0");
+  aklr_moe_workspace_layout l;
+  int rc = prepare(cfg, &l, workspace, workspace_bytes, stream);
+  if (rc) return rc;
+  if (cfg->n_tokens == 0) return AKLR_OK;
+  if (!rows_q || !rows_scale || !expert_ids || !weights || !w1 || !w1_scale || !w2 || !w2_scale || !out_rows)
+    return fail(AKLR_ERR_BAD_ARGUMENT, "NULL tensor argument");
+  return run_mx_experts(*cfg, l, nullptr, expert_ids, weights, nullptr, cfg->n_routed, w1, w1_scale, w2, w2_scale,
+                        swiglu_limit, nullptr, static_cast<uint8_t*>(workspace), stream,
+                        static_cast<const uint8_t*>(rows_q), rows_scale, out_rows);
+}
+
+int aklr_ep_gather_quant_mxfp8(const void* hidden_states, const int32_t* sorted_ids, int32_t n_send, int32_t hidden,
+                               int32_t routes_per_token, void* rows_q, uint8_t* rows_scale, void* stream) {
+  if (!hidden_states || !sorted_ids || !rows_q || !rows_scale) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
+  int rc = check_device();
+  if (rc) return rc;
+  aklr::MxQuantParams p{};
+  p.x = hidden_states;
+  p.sorted_ids = sorted_ids;
+  p.q = static_cast<uint8_t*>(rows_q);
+  p.scales = rows_scale;
+  p.n_rows = n_send;
+  p.hidden = hidden;
+  p.routes_per_token = routes_per_token;
+  p.row_major_scales = 1;
+  rc = aklr::launch_gather_quant_mxfp8(p, static_cast<cudaStream_t>(stream));
+  if (rc) return fail(rc, "ep MXFP8 gather quant: %s", aklr_status_string(rc));
+  g_launches += n_send > 0;
+  return AKLR_OK;
 }
 
 int aklr_ep_dispatch_meta(const int32_t* sorted_ids, const int32_t* topk_ids, const float* topk_weights,

@@ -17,11 +17,11 @@
 //   * scale factors: copied shared memory -> TMEM by tcgen05.cp (32x128b.warpx4) per K-block; a
 //     32-bit TMEM column holds the 4 scale bytes of a row's four K=32 steps, rows r in lane r % 32,
 //     column r / 32.  Activation scales are produced in that order by the quantising kernels; weight
-//     scales stay row-major in HBM ([rows, K/32] bytes, as the checkpoint stores them) and the idle
-//     epilogue warps re-order one 32-bit word per row per K-block into the stage.
+//     scales stay row-major in HBM ([rows, K/32] bytes, as the checkpoint stores them) and two
+//     staging warps re-order one 32-bit word per row per K-block into the stage.
 //
-// Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..9 stage
-// scale factors during the K loop and run the epilogue.  Persistent CTAs, bounded waits, no cluster,
+// Warp roles (384 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..9 epilogue,
+// warps 10..11 stage the scale factors ahead of the MMA warp (also across tile boundaries).  Persistent CTAs, bounded waits, no cluster,
 // no multicast.
 #include <cfloat>
 
@@ -30,9 +30,27 @@
 
 namespace aklr {
 
+#ifdef AKLR_GEMM_TIMING
+// Development aid, compiled only on request: cycles per role of CTA 0.
+// [0] mma wait acc_empty [1] mma wait full [2] mma wait sf_full [3] mma issue [4] sf wait empty [5] sf stage
+// [6] epi wait acc_full [7] epilogue [8] kblocks [9] tiles
+__device__ long long g_mx_timing[2][16];
+#define MT(slot, expr)                                         \
+  do {                                                         \
+    const long long t_begin_ = clock64();                      \
+    expr;                                                      \
+    if (blockIdx.x == 0) tacc[slot] += clock64() - t_begin_;   \
+  } while (0)
+#else
+#define MT(slot, expr) \
+  do {                 \
+    expr;              \
+  } while (0)
+#endif
+
 namespace {
 
-constexpr int kThreads = 320;
+constexpr int kThreads = 384;            // TMA warp, MMA warp, 8 epilogue warps, 2 scale-staging warps
 constexpr int kEpi = 256;
 constexpr int kBM = 128;
 constexpr int kBN = 256;
@@ -133,7 +151,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
     for (int s = 0; s < S; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
-      mbar_init(&sf_full[s], kEpi / 32);
+      mbar_init(&sf_full[s], 1);  // the one staging warp that owns the K-block
     }
     mbar_init(acc_full, 1);
     mbar_init(acc_empty, kEpi / 32);
@@ -183,14 +201,24 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
     if (lane == 0) {
       uint32_t it = 0, tile_no = 0;
       bool ok = true;
+#ifdef AKLR_GEMM_TIMING
+      long long tacc[16] = {0};
+#endif
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_no) {
         // the single accumulator must have been read out by the previous tile's epilogue
-        if (!mbar_wait(acc_empty, (tile_no & 1) ^ 1, abort_flag, p.status, 22)) break;
+        bool got;
+        MT(0, got = mbar_wait(acc_empty, (tile_no & 1) ^ 1, abort_flag, p.status, 22));
+        if (!got) break;
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
-          if (!mbar_wait(&full[s], ph, abort_flag, p.status, 23)) { ok = false; break; }
-          if (!mbar_wait(&sf_full[s], ph, abort_flag, p.status, 24)) { ok = false; break; }
+          MT(1, got = mbar_wait(&full[s], ph, abort_flag, p.status, 23));
+          if (!got) { ok = false; break; }
+          MT(2, got = mbar_wait(&sf_full[s], ph, abort_flag, p.status, 24));
+          if (!got) { ok = false; break; }
+#ifdef AKLR_GEMM_TIMING
+          const long long t_issue = clock64();
+#endif
           tc_fence_after_sync();
           const uint32_t a0 = smem_u32(smem + s * kStageBytes);
           const uint32_t sf0 = a0 + kABytes + kBBytes;
@@ -204,50 +232,124 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
             umma_mx(tmem_base, da + 2 * k, db + 2 * k, mx_idesc(kBN, k), tmem_base + kSfaCol, tmem_base + kSfbCol,
                     (kb > 0 || k > 0) ? 1u : 0u);
           tc_commit(&empty[s]);
+#ifdef AKLR_GEMM_TIMING
+          tacc[3] += clock64() - t_issue;
+#endif
         }
         if (ok) tc_commit(acc_full);
       }
+#ifdef AKLR_GEMM_TIMING
+      if (blockIdx.x == 0) {
+        for (int i = 0; i <= 3; ++i) g_mx_timing[GATE_UP][i] = tacc[i];
+        g_mx_timing[GATE_UP][8] = it;
+        g_mx_timing[GATE_UP][9] = tile_no;
+      }
+#endif
     }
+  } else if (warp >= 10) {
+    // ------------------- scale-factor staging, running ahead of the MMA warp -------------------
+    // The two staging warps take alternate K-blocks, so each has two MMA periods per stage; a
+    // lane moves 8 weight-row words (rows lane, lane+32, ...) and 16 bytes of activation scales.
+    const int sw = warp - 10;
+    const int KS = p.k >> 5;  // scale bytes per weight row
+    uint32_t it0 = 0;         // K-blocks before this tile
+#ifdef AKLR_GEMM_TIMING
+    long long tacc[16] = {0};
+#endif
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, it0 += KB) {
+      const int b = t / tiles_per_block, j = t - b * tiles_per_block;
+      const int e = p.block_expert[b];
+      const uint8_t* wsf[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const int i = lane + q * 32;
+        const int wrow = GATE_UP ? (i < 128 ? j * 128 + i : p.out_dim + j * 128 + (i - 128)) : j * 256 + i;
+        wsf[q] = p.w_scale + (static_cast<size_t>(e) * p.rows_per_expert + wrow) * KS;
+      }
+      const uint8_t* xsf = p.x_scale + static_cast<size_t>(b) * KB * kSfaBytes;
+      const int first = ((it0 & 1u) == static_cast<uint32_t>(sw)) ? 0 : 1;
+      // ring of kDepth own K-blocks of scale words in registers: loaded long before their stage
+      // frees up (down-projection rows are 64 bytes apart and miss to HBM on first touch)
+      constexpr int kDepth = 3;
+      uint32_t wq[kDepth][8];
+      uint4 aq[kDepth];
+#pragma unroll
+      for (int d = 0; d < kDepth; ++d) {
+        const int kb = first + 2 * d;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) wq[d][q] = kb < KB ? __ldg(reinterpret_cast<const uint32_t*>(wsf[q] + kb * 4)) : 0u;
+        aq[d] = kb < KB ? __ldg(reinterpret_cast<const uint4*>(xsf + kb * kSfaBytes) + lane) : make_uint4(0, 0, 0, 0);
+      }
+      for (int kb0 = first; kb0 < KB && ok; kb0 += 2 * kDepth) {
+#pragma unroll
+        for (int d = 0; d < kDepth; ++d) {
+          const int kb = kb0 + 2 * d;
+          if (kb < KB && ok) {
+            const uint32_t it = it0 + kb;
+            const int s = it % S;
+            const uint32_t ph = (it / S) & 1;
+            bool got;
+            MT(4, got = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 25));
+            if (!got) ok = false;
+#ifdef AKLR_GEMM_TIMING
+            const long long t_stage = clock64();
+#endif
+            uint8_t* sf = smem + s * kStageBytes + kABytes + kBBytes;
+            *reinterpret_cast<uint4*>(sf + lane * 16) = aq[d];
+#pragma unroll
+            for (int q = 0; q < 8; ++q)  // row lane + 32 q -> 16-byte line `lane`, word q % 4, chunk q / 4
+              *reinterpret_cast<uint32_t*>(sf + kSfaBytes + (q >> 2) * 512 + lane * 16 + (q & 3) * 4) = wq[d][q];
+            fence_proxy_async_smem();  // tcgen05.cp reads these bytes through the async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sf_full[s]);
+            const int nk = kb + 2 * kDepth;
+            if (nk < KB) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) wq[d][q] = __ldg(reinterpret_cast<const uint32_t*>(wsf[q] + nk * 4));
+              aq[d] = __ldg(reinterpret_cast<const uint4*>(xsf + nk * kSfaBytes) + lane);
+            }
+#ifdef AKLR_GEMM_TIMING
+            tacc[5] += clock64() - t_stage;
+#endif
+          }
+        }
+      }
+    }
+#ifdef AKLR_GEMM_TIMING
+    if (blockIdx.x == 0 && sw == 0 && lane == 0)
+      for (int i = 4; i <= 5; ++i) g_mx_timing[GATE_UP][i] = tacc[i];
+#endif
   } else {
-    // ------------------- scale-factor staging during the K loop, then the epilogue -------------
+    // ------------------------------------ epilogue warps ---------------------------------------
     const int quarter = warp & 3;
     const int half = (warp - 2) >> 2;
     const int et = threadIdx.x - 64;
     const int row = quarter * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    const int KS = p.k >> 5;  // scale bytes per weight row
-    uint32_t it = 0, tile_no = 0;
+    uint32_t tile_no = 0;
     bool bad = false;
+#ifdef AKLR_GEMM_TIMING
+    long long tacc[16] = {0};
+#endif
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_no) {
       if (epi_any(*abort_flag)) break;
       const int b = t / tiles_per_block, j = t - b * tiles_per_block;
-      const int e = p.block_expert[b];
       if (et < kBM) {
         const int rid = p.sorted_ids[b * kBM + et];
         rid_s[et] = rid;
         if (!GATE_UP) wgt_s[et] = rid >= 0 ? p.topk_weights[rid] : 0.0f;
       }
       epi_sync();  // the epilogue reads other threads' entries
-      // this thread's weight row of the tile (256 rows, one per staging thread)
-      const int wrow = GATE_UP ? (et < 128 ? j * 128 + et : p.out_dim + j * 128 + (et - 128)) : j * 256 + et;
-      const uint8_t* wsf = p.w_scale + (static_cast<size_t>(e) * p.rows_per_expert + wrow) * KS;
-      const uint8_t* xsf = p.x_scale + static_cast<size_t>(b) * KB * kSfaBytes;
-      for (int kb = 0; kb < KB; ++kb, ++it) {
-        const int s = it % S;
-        const uint32_t ph = (it / S) & 1;
-        if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 25)) bad = true;
-        uint8_t* sf = smem + s * kStageBytes + kABytes + kBBytes;
-        if (et < 32) *reinterpret_cast<uint4*>(sf + et * 16) = __ldg(reinterpret_cast<const uint4*>(xsf + kb * kSfaBytes) + et);
-        const int r = et & 127;
-        *reinterpret_cast<uint32_t*>(sf + kSfaBytes + (et >> 7) * 512 + (r & 31) * 16 + (r >> 5) * 4) =
-            __ldg(reinterpret_cast<const uint32_t*>(wsf + kb * 4));
-        fence_proxy_async_smem();  // tcgen05.cp reads these bytes through the async proxy
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sf_full[s]);
-      }
-
       // ---- epilogue: the whole K reduction is in TMEM ----
-      if (!mbar_wait(acc_full, tile_no & 1, abort_flag, p.status, 26)) bad = true;
+      {
+        bool got;
+        MT(6, got = mbar_wait(acc_full, tile_no & 1, abort_flag, p.status, 26));
+        if (!got) bad = true;
+      }
+#ifdef AKLR_GEMM_TIMING
+      const long long t_epi = clock64();
+#endif
       tc_fence_after_sync();
       float acc[128];
       {
@@ -317,7 +419,14 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
           *reinterpret_cast<uint4*>(dst + v * 16) = make_uint4(o[0], o[1], o[2], o[3]);
         }
       }
+#ifdef AKLR_GEMM_TIMING
+      tacc[7] += clock64() - t_epi;
+#endif
     }
+#ifdef AKLR_GEMM_TIMING
+    if (blockIdx.x == 0 && warp == 2 && lane == 0)
+      for (int i = 6; i <= 7; ++i) g_mx_timing[GATE_UP][i] = tacc[i];
+#endif
   }
 
   tc_fence_before_sync();
@@ -348,6 +457,16 @@ __global__ void __launch_bounds__(256) gather_quant_mxfp8_kernel(MxQuantParams p
     const int rid = p.sorted_ids[row];
     if (rid < 0) continue;
     const int token = rid / p.routes_per_token;
+    if (p.q_in) {  // rows quantised by their sender: move codes and scale byte
+      *reinterpret_cast<uint2*>(p.q + static_cast<size_t>(row) * p.hidden + grp * 32 + sub * 8) =
+          *reinterpret_cast<const uint2*>(p.q_in + static_cast<size_t>(token) * p.hidden + grp * 32 + sub * 8);
+      if (sub == 0) {
+        const int b = row >> 7, r = row & 127, kb = grp >> 2, ks = grp & 3;
+        p.scales[(static_cast<size_t>(b) * KB + kb) * kSfaBytes + (r & 31) * 16 + (r >> 5) * 4 + ks] =
+            p.scales_in[static_cast<size_t>(token) * groups_per_row + grp];
+      }
+      continue;
+    }
     const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.x) +
                                                       static_cast<size_t>(token) * p.hidden + grp * 32 + sub * 8);
     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -368,14 +487,24 @@ __global__ void __launch_bounds__(256) gather_quant_mxfp8_kernel(MxQuantParams p
     out.y = cvt_e4m3x2(v[4] * inv, v[5] * inv) | (static_cast<uint32_t>(cvt_e4m3x2(v[6] * inv, v[7] * inv)) << 16);
     *reinterpret_cast<uint2*>(p.q + static_cast<size_t>(row) * p.hidden + grp * 32 + sub * 8) = out;
     if (sub == 0) {
-      const int b = row >> 7, r = row & 127, kb = grp >> 2, ks = grp & 3;
-      p.scales[(static_cast<size_t>(b) * KB + kb) * kSfaBytes + (r & 31) * 16 + (r >> 5) * 4 + ks] =
-          static_cast<uint8_t>(ex + 127);
+      if (p.row_major_scales) {  // for transport to another rank: [row, hidden/32]
+        p.scales[static_cast<size_t>(row) * groups_per_row + grp] = static_cast<uint8_t>(ex + 127);
+      } else {
+        const int b = row >> 7, r = row & 127, kb = grp >> 2, ks = grp & 3;
+        p.scales[(static_cast<size_t>(b) * KB + kb) * kSfaBytes + (r & 31) * 16 + (r >> 5) * 4 + ks] =
+            static_cast<uint8_t>(ex + 127);
+      }
     }
   }
 }
 
 }  // namespace
+
+#ifdef AKLR_GEMM_TIMING
+extern "C" int aklr_debug_read_mx_timing(long long* host32) {
+  return cudaMemcpyFromSymbol(host32, g_mx_timing, sizeof(g_mx_timing)) == cudaSuccess ? 0 : -3;
+}
+#endif
 
 int launch_gather_quant_mxfp8(const MxQuantParams& p, cudaStream_t stream) {
   if (p.hidden % 128 != 0) return AKLR_ERR_UNSUPPORTED_SHAPE;

@@ -97,7 +97,10 @@ struct MxQuantParams {
   const int32_t* num_rows;    // device count of rows in use
   uint8_t* q;                 // [capacity, hidden] e4m3
   uint8_t* scales;            // [capacity/128, hidden/128, 512] e8m0 bytes in tcgen05.cp order
+  const uint8_t* q_in;        // rows already quantised by a sender ([n, hidden] e4m3), or null
+  const uint8_t* scales_in;   // their scale bytes [n, hidden/32]
   int n_rows, hidden, routes_per_token;
+  int row_major_scales;       // write scales as [row, hidden/32] (for transport) instead
 };
 int launch_gather_quant_mxfp8(const MxQuantParams& p, cudaStream_t stream);
 

@@ -26,7 +26,17 @@ import dataclasses
 import torch
 
 from aklr_b200 import _lib
-from aklr_b200.moe import FP8, Routing, Workspace, _config, _ptr, _stream, fused_experts_fp8, route
+from aklr_b200.moe import (
+    FP8,
+    Routing,
+    Workspace,
+    _config,
+    _ptr,
+    _stream,
+    fused_experts_fp8,
+    fused_experts_mxfp4,
+    route,
+)
 
 
 @dataclasses.dataclass
@@ -49,7 +59,16 @@ class StepState:
 
 
 class CudaKernels:
-    """The device side of the phases: libaklr_b200.so through the C ABI."""
+    """The device side of the phases: libaklr_b200.so through the C ABI.
+
+    ``fmt`` "fp8": e4m3 experts with 128 x 128 block scales, rows travel as FP8 + float32 scales per
+    1 x 128.  "mxfp4": e2m1 experts with e8m0 scales, rows travel as MXFP8 (one e8m0 byte per 32);
+    ``swiglu_limit`` then clamps gate and up as the reference's mega_moe does."""
+
+    def __init__(self, fmt: str = "fp8", swiglu_limit: float | None = None):
+        if fmt not in ("fp8", "mxfp4"):
+            raise ValueError(f"unknown expert format {fmt!r}")
+        self.fmt, self.swiglu_limit = fmt, swiglu_limit
 
     def route(self, logits, bias, routing):
         return route(logits, bias, routing)
@@ -79,10 +98,14 @@ class CudaKernels:
         device = hidden.device
         n_send, h = sorted_ids.numel(), hidden.shape[1]
         rows_q = torch.empty((n_send, h), dtype=torch.uint8, device=device)
-        rows_scale = torch.empty((n_send, h // 128), dtype=torch.float32, device=device)
         meta = torch.empty((2, n_send), dtype=torch.int32, device=device)
         position = torch.full((ids.numel(),), -1, dtype=torch.int32, device=device)
-        _lib.check(lib.aklr_ep_gather_quant(_ptr(hidden), _ptr(sorted_ids), n_send, h, ids.shape[1], _ptr(rows_q), _ptr(rows_scale), _stream()))
+        if self.fmt == "mxfp4":
+            rows_scale = torch.empty((n_send, h // 32), dtype=torch.uint8, device=device)
+            _lib.check(lib.aklr_ep_gather_quant_mxfp8(_ptr(hidden), _ptr(sorted_ids), n_send, h, ids.shape[1], _ptr(rows_q), _ptr(rows_scale), _stream()))
+        else:
+            rows_scale = torch.empty((n_send, h // 128), dtype=torch.float32, device=device)
+            _lib.check(lib.aklr_ep_gather_quant(_ptr(hidden), _ptr(sorted_ids), n_send, h, ids.shape[1], _ptr(rows_q), _ptr(rows_scale), _stream()))
         _lib.check(
             lib.aklr_ep_dispatch_meta(
                 _ptr(sorted_ids), _ptr(ids), _ptr(weights), n_send, ids.numel(), n_local, meta[0].data_ptr(),
@@ -99,6 +122,17 @@ class CudaKernels:
         if n == 0:
             return out
         e, two_i, _ = w1.shape
+        if self.fmt == "mxfp4":
+            cfg = _config(n, h, two_i // 2, e, Routing(topk=1), block_m=128)
+            ws = Workspace(cfg, device)
+            _lib.check(
+                _lib.load().aklr_moe_mxfp4_experts_prequant(
+                    ctypes.byref(cfg), _ptr(rows_q), _ptr(rows_scale), _ptr(expert_ids), _ptr(weights), _ptr(w1), _ptr(s1),
+                    _ptr(w2), _ptr(s2), float(self.swiglu_limit or 0.0), _ptr(out), ws.base.data_ptr(),
+                    ws.layout.total_bytes, _stream(),
+                )
+            )
+            return out
         cfg = _config(n, h, two_i // 2, e, Routing(topk=1))
         ws = Workspace(cfg, device)
         _lib.check(
@@ -114,6 +148,8 @@ class CudaKernels:
         n_tokens, n_shared = hidden.shape[0], w1.shape[0]
         ids = torch.arange(n_shared, dtype=torch.int32, device=hidden.device).repeat(n_tokens, 1).contiguous()
         ones = torch.ones((n_tokens, n_shared), dtype=torch.float32, device=hidden.device)
+        if self.fmt == "mxfp4":
+            return fused_experts_mxfp4(hidden, ids, ones, w1, s1, w2, s2, swiglu_limit=self.swiglu_limit)
         return fused_experts_fp8(hidden, ids, ones, w1, s1, w2, s2)
 
     def combine(self, rows, position, shared_rows, n_tokens, topk, hidden):
@@ -146,9 +182,11 @@ class ExpertParallelMoE:
         self._side = None
 
     # ---- phase 1: on the home rank --------------------------------------------------------------
-    def prepare(self, hidden: torch.Tensor, logits: torch.Tensor, bias: torch.Tensor | None) -> StepState:
+    def prepare(self, hidden: torch.Tensor, logits: torch.Tensor | None, bias: torch.Tensor | None, routed=None) -> StepState:
+        """``routed`` = (topk_ids int32 [T,K] global ids, topk_weights float32 [T,K]) skips the routing
+        (the reference's mega_moe takes the routing as input)."""
         k = self.kernels
-        if logits.shape[1] != self.n_local * self.world:
+        if routed is None and logits.shape[1] != self.n_local * self.world:
             raise ValueError(f"router has {logits.shape[1]} experts, the group holds {self.n_local * self.world}")
         shared_rows = shared_done = None
         if self.shared is not None:  # overlaps the dispatch: own tokens through the replicated shared experts
@@ -163,7 +201,8 @@ class ExpertParallelMoE:
                 hidden.record_stream(self._side)
             else:
                 shared_rows = k.shared(hidden, *self.shared)
-        ids, weights = k.route(logits, bias, self.routing)
+        ids, weights = routed if routed is not None else k.route(logits, bias, self.routing)
+        self.routing = dataclasses.replace(self.routing, topk=ids.shape[1])
         sorted_ids, counts = k.order_by_rank(ids, self.n_local, self.world)
         rows_q, rows_scale, meta, position = k.pack(hidden, ids, weights, sorted_ids, self.n_local)
         return StepState(Packed(rows_q, rows_scale, meta, counts), position, shared_rows, shared_done, hidden.shape[0])
@@ -173,7 +212,7 @@ class ExpertParallelMoE:
         expert_ids = received.meta[:, 0].contiguous()
         weights = received.meta[:, 1].contiguous().view(torch.float32)
         rows_q = received.rows_q
-        if rows_q.dtype != FP8 and rows_q.is_cuda:
+        if rows_q.dtype != FP8 and rows_q.is_cuda and getattr(self.kernels, "fmt", "fp8") == "fp8":
             rows_q = rows_q.view(FP8)
         return self.kernels.experts(rows_q, received.rows_scale, expert_ids, weights, *self.routed)
 
@@ -185,10 +224,10 @@ class ExpertParallelMoE:
         return self.kernels.combine(back_rows, state.position_of_route, state.shared_rows, state.n_tokens, self.routing.topk, hidden)
 
     # ---- all three over torch.distributed ------------------------------------------------------------
-    def forward(self, hidden, logits, bias, group=None) -> torch.Tensor:
+    def forward(self, hidden, logits, bias, group=None, routed=None) -> torch.Tensor:
         import torch.distributed as dist
 
-        state = self.prepare(hidden, logits, bias)
+        state = self.prepare(hidden, logits, bias, routed)
         send = state.send
         recv_counts_dev = torch.empty_like(send.counts)
         dist.all_to_all_single(recv_counts_dev, send.counts, group=group)

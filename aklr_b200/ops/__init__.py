@@ -37,6 +37,7 @@ __all__ = [
     "deepseek_v2_fp8_moe",
     "fused_moe",
     "init",
+    "mega_moe",
     "per_group_quant_fp8",
     "per_group_quant_mxfp8",
     "qwen3_moe_fp8_moe",
@@ -260,6 +261,54 @@ def qwen3_moe_fp8_moe(
 # format, quant_type "per_128x128" (the aiter enum name sglang passes for it,
 # aklr/plugins/sglang/models/deepseek_v2/baseline.py:159).
 # --------------------------------------------------------------------------------------------------
+def _mx_weights_key(call: Mapping[str, Any], hidden: int, device) -> tuple | None:
+    """(experts, inter) when w1/w2 are packed e2m1 (uint8 or float4_e2m1fn_x2) with e8m0 scales per 32."""
+    w1, w2, s1, s2 = call["w1"], call["w2"], call["w1_scale"], call["w2_scale"]
+    fp4 = (torch.uint8,) + ((torch.float4_e2m1fn_x2,) if hasattr(torch, "float4_e2m1fn_x2") else ())
+    e8 = (torch.uint8,) + ((torch.float8_e8m0fnu,) if hasattr(torch, "float8_e8m0fnu") else ())
+    if not (tensor_ok(w1, fp4, 3, device) and tensor_ok(w2, fp4, 3, device) and tensor_ok(s1, e8, 3, device) and tensor_ok(s2, e8, 3, device)):
+        return None
+    e, two_i, half_h = w1.shape
+    inter = two_i // 2
+    if half_h * 2 != hidden or hidden % 256 or inter % 128 or two_i % 256:
+        return None
+    if tuple(w2.shape) != (e, hidden, inter // 2) or tuple(s1.shape) != (e, two_i, hidden // 32) or tuple(s2.shape) != (e, hidden, inter // 32):
+        return None
+    return e, inter
+
+
+def _fused_moe_mx_key(call, x, device, n_tokens, hidden):
+    """The reference's own Points: MXFP4 experts (quant_type per_1x32), activations quantised to
+    MXFP8 (act_quant 8), gated SiLU, optional clamp (swiglu_limit)."""
+    if call["act_quant"] != 8 or _attr_name(call["activation"]) not in ("silu", None):
+        return None
+    if call["w1_scale"] is None or call["w2_scale"] is None:
+        return None
+    weights = _mx_weights_key(call, hidden, device)
+    if weights is None:
+        return None
+    unsupported = ("a1_scale", "a2_scale", "bias1", "bias2", "beta", "linear_beta", "num_local_tokens")
+    if any(call[name] is not None for name in unsupported) or call["doweight_stage1"]:
+        return None
+    limit = call["swiglu_limit"]
+    if limit is not None and not (isinstance(limit, (int, float)) and limit > 0):
+        return None
+    if call["gate_mode"] not in (None, "separated") or call["out_dtype"] not in (None, BF16):
+        return None
+    ids, wts = call["topk_ids"], call["topk_weights"]
+    if not tensor_ok(ids, torch.int32, 2, device) or not tensor_ok(wts, torch.float32, 2, device):
+        return None
+    if ids.shape != wts.shape or ids.shape[0] != n_tokens or not (1 <= ids.shape[1] <= 32):
+        return None
+    mask = call["expert_mask"]
+    if mask is not None and not tensor_ok(mask, torch.int32, 1, device):
+        return None
+    out = call["out"]
+    if out is not None and (not tensor_ok(out, BF16, 2, device) or out.shape != x.shape):
+        return None
+    return ("mxfp4", hidden, weights[0], weights[1], ids.shape[1], mask is not None, limit is not None)
+
+
 def _fused_moe_key(call):
     x = call["hidden_states"]
     if not tensor_ok(x, BF16, 2):
@@ -268,6 +317,8 @@ def _fused_moe_key(call):
     n_tokens, hidden = x.shape
     if not (1 <= n_tokens <= MAX_TOKENS):
         return None
+    if _attr_name(call["quant_type"]) == "per_1x32":
+        return _fused_moe_mx_key(call, x, device, n_tokens, hidden)
     if _attr_name(call["quant_type"]) != "per_128x128" or _attr_name(call["activation"]) not in ("silu", None):
         return None
     if call["w1_scale"] is None or call["w2_scale"] is None:
@@ -309,6 +360,20 @@ def _fused_moe_run(call, out):
     expert_map = None
     if mask is not None:  # a global id to its slot in w1, -1 off this rank (fused_moe/reference.py:78-84)
         expert_map = torch.where(mask == 1, torch.cumsum(mask, 0, dtype=torch.int32) - 1, -1).to(torch.int32)
+    if _attr_name(call["quant_type"]) == "per_1x32":
+        moe.fused_experts_mxfp4(
+            call["hidden_states"],
+            call["topk_ids"],
+            call["topk_weights"],
+            call["w1"].view(torch.uint8),
+            call["w1_scale"].view(torch.uint8),
+            call["w2"].view(torch.uint8),
+            call["w2_scale"].view(torch.uint8),
+            expert_map=expert_map,
+            swiglu_limit=call["swiglu_limit"],
+            out=out,
+        )
+        return
     moe.fused_experts_fp8(
         call["hidden_states"],
         call["topk_ids"],
@@ -382,6 +447,105 @@ def fused_moe(
     num_local_tokens=None,
     act_quant=4,
     out=None,
+): ...
+
+
+# --------------------------------------------------------------------------------------------------
+# mega_moe@1.0 -- expert parallel MXFP4 MoE given routing (aklr/ops/mega_moe/contract.py:42-151):
+# every rank of the group calls once per step; global expert e is local e % n_local of rank
+# e // n_local; MXFP8 activations, clamped SwiGLU, weighted sum back on the token's rank.
+# --------------------------------------------------------------------------------------------------
+def _mega_moe_key(call):
+    x = call["hidden_states"]
+    if not tensor_ok(x, BF16, 2):
+        return None
+    device = x.device
+    n_tokens, hidden = x.shape
+    if not (1 <= n_tokens <= MAX_TOKENS) or call["w1_scale"] is None or call["w2_scale"] is None:
+        return None
+    weights = _mx_weights_key(call, hidden, device)
+    if weights is None:
+        return None
+    ids, wts = call["topk_ids"], call["topk_weights"]
+    if not tensor_ok(ids, torch.int32, 2, device) or not tensor_ok(wts, torch.float32, 2, device) or ids.shape != wts.shape:
+        return None
+    if ids.shape[0] != n_tokens or not (1 <= ids.shape[1] <= 32):
+        return None
+    ep_size, limit = call["ep_size"], call["swiglu_limit"]
+    if not isinstance(ep_size, int) or ep_size < 1 or not isinstance(limit, (int, float)) or limit <= 0:
+        return None
+    if call["out_dtype"] not in (None, BF16):
+        return None
+    import torch.distributed as dist
+
+    world = dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
+    if world != ep_size:
+        return None
+    return (hidden, weights[0], weights[1], ids.shape[1], ep_size)
+
+
+def _mega_moe_run(call, out):
+    import torch.distributed as dist
+
+    from aklr_b200.ep import CudaKernels, ExpertParallelMoE
+
+    ep_size = call["ep_size"]
+    rank = dist.get_rank() if ep_size > 1 else 0
+    layer = ExpertParallelMoE(
+        moe.Routing(topk=call["topk_ids"].shape[1]),
+        call["w1"].view(torch.uint8),
+        call["w1_scale"].view(torch.uint8),
+        call["w2"].view(torch.uint8),
+        call["w2_scale"].view(torch.uint8),
+        rank,
+        ep_size,
+        kernels=CudaKernels("mxfp4", float(call["swiglu_limit"])),
+    )
+    routed = (call["topk_ids"], call["topk_weights"])
+    if ep_size == 1:
+        from aklr_b200.ep import run_in_process
+
+        result = run_in_process([layer], [(call["hidden_states"], None, None, routed)])[0]
+    else:
+        result = layer.forward(call["hidden_states"], None, None, routed=routed)
+    out.copy_(result)
+
+
+MEGA_MOE = OpContract(
+    contract_id="mega_moe@1.0",
+    description="Expert-parallel MXFP4 MoE given the routing: each rank's tokens through experts held anywhere in the group.",
+    params=[
+        Param("hidden_states"),
+        Param("w1"),
+        Param("w2"),
+        Param("topk_weights"),
+        Param("topk_ids"),
+        Param("w1_scale", None),
+        Param("w2_scale", None),
+        Param("ep_size", 1),
+        Param("swiglu_limit", 10.0),
+        Param("out_dtype", None),
+    ],
+    outputs=["out"],
+    key=_mega_moe_key,
+    alloc=_layer_alloc,
+    run=_mega_moe_run,
+    ranks="ep_size",
+)
+
+
+@api(MEGA_MOE)
+def mega_moe(
+    hidden_states,
+    w1,
+    w2,
+    topk_weights,
+    topk_ids,
+    w1_scale=None,
+    w2_scale=None,
+    ep_size=1,
+    swiglu_limit=10.0,
+    out_dtype=None,
 ): ...
 
 
@@ -536,6 +700,7 @@ CONTRACTS = (
     DEEPSEEK_V2_FP8_MOE,
     QWEN3_MOE_FP8_MOE,
     FUSED_MOE,
+    MEGA_MOE,
     BIASED_GROUPED_TOPK,
     PER_GROUP_QUANT_FP8,
     PER_GROUP_QUANT_MXFP8,

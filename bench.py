@@ -237,6 +237,7 @@ def main() -> None:
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling captures)")
     ap.add_argument("--routed-experts", type=int, default=0, help="shrink the layer to this many routed experts (profiling captures only)")
     ap.add_argument("--block-m", type=int, default=0, help="force the tokens-per-block of the grouped GEMMs")
+    ap.add_argument("--format", default="fp8", choices=["fp8", "mxfp4"], help="expert weight format (mxfp4: MXFP8 activations)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     cfg = wl.CONFIGS["deepseek_v3"]
@@ -288,6 +289,9 @@ def main() -> None:
 
     routing = routing_of(cfg)
     T = args.tokens
+    if args.format == "mxfp4":
+        bench_mxfp4(args, cfg, routing, device, lib)
+        return
     w1, s1, w2, s2 = wl.expert_weights(cfg, SEED, device)
     router_w = wl.router_weight(cfg, SEED, device)
     n_batches = 4
@@ -499,6 +503,57 @@ def main() -> None:
     if sweep is not None:
         line["sweep"] = sweep
     print(json.dumps(line), flush=True)
+
+
+def bench_mxfp4(args, cfg, routing, device, lib):
+    """The same layer with MXFP4 expert weights and MXFP8 activations (one GPU): extra measurement,
+    printed as one JSON line of the same shape with ``config.weights`` saying so."""
+    from aklr_b200.moe import Workspace, _config, fused_moe_mxfp4
+
+    T = args.tokens
+    w1, s1, w2, s2 = wl.mx_expert_weights(cfg, SEED, device)
+    bias = wl.router_inputs(cfg, 1, SEED + 1, device)[2]
+    batches = [wl.router_inputs(cfg, T, SEED + 1 + b, device)[:2] for b in range(4)]
+    out = torch.empty((T, cfg.hidden), dtype=torch.bfloat16, device=device)
+    ws = Workspace(_config(T, cfg.hidden, cfg.inter, cfg.n_routed, routing, batches[0][1], bias, 128), device)
+
+    def step(i):
+        hidden, logits = batches[i % 4]
+        fused_moe_mxfp4(hidden, logits, bias, w1, s1, w2, s2, routing, out=out, workspace=ws)
+
+    for i in range(args.warmup):
+        step(i)
+    ws.check_status()
+    launches0 = lib.aklr_kernel_launch_count()
+    sampler = ClockSampler(device.index or 0)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for i in range(args.steps):
+        step(args.warmup + i)
+    stop.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = start.elapsed_time(stop) / args.steps
+    experts_hit = distinct_experts(ws.topk_ids())
+    h, inter = cfg.hidden, cfg.inter
+    weight_bytes = experts_hit * (3 * h * inter // 2 + 3 * h * inter // 32)
+    flops = T * cfg.routes_per_token * cfg.flops_per_route
+    peak, kind = measured_peak_hbm()
+    config = workload_config(cfg, args)
+    config["weights"] = "mxfp4: e2m1 + e8m0 per 32 along K, N(0,0.02)"
+    config["activations"] = "bf16 N(0,1), quantised to MXFP8 (e4m3 + e8m0 per 32)"
+    print(json.dumps({
+        "metric": METRIC.replace("fp8", "mxfp4"), "value": T / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "mxfp4 x mxfp8", "data": "synthetic", "config": config, "clocks": clocks, "e2e": None,
+        "gpu_launches": int(lib.aklr_kernel_launch_count() - launches0),
+        "roofline": {"bound": "hbm" if weight_bytes / (peak * 1e9) > flops / 3.2e15 else "tensor",
+                     "achieved": weight_bytes / (ms * 1e-3) / 1e9, "peak": peak, "peak_kind": f"of {kind}", "unit": "GB/s",
+                     "frac": weight_bytes / (ms * 1e-3) / 1e9 / peak, "traffic": None, "tflops": flops / (ms * 1e-3) / 1e12,
+                     "note": "whole layer: weight bytes of the experts hit / layer time"},
+        "cpu_baseline": None,
+    }), flush=True)
 
 
 def orc_free_ids(cfg, logits, bias):

@@ -151,6 +151,15 @@ int aklr_moe_fp8_experts_prequant(const aklr_moe_config* cfg, const void* rows_q
                                   const int32_t* expert_ids, const float* weights, const void* w1,
                                   const float* w1_scale, const void* w2, const float* w2_scale, void* out_rows,
                                   void* workspace, size_t workspace_bytes, void* stream);
+/* The MXFP4 counterparts for `mega_moe` (MXFP8 rows travel with one e8m0 byte per 32 values,
+ * rows_scale uint8 [n, H/32] row-major). */
+int aklr_ep_gather_quant_mxfp8(const void* hidden_states, const int32_t* sorted_ids, int32_t n_send, int32_t hidden,
+                               int32_t routes_per_token, void* rows_q, uint8_t* rows_scale, void* stream);
+int aklr_moe_mxfp4_experts_prequant(const aklr_moe_config* cfg, const void* rows_q, const uint8_t* rows_scale,
+                                    const int32_t* expert_ids, const float* weights, const void* w1,
+                                    const uint8_t* w1_scale, const void* w2, const uint8_t* w2_scale,
+                                    float swiglu_limit, void* out_rows, void* workspace, size_t workspace_bytes,
+                                    void* stream);
 int aklr_ep_combine(const void* rows, const int32_t* position_of_route, const void* shared_rows, void* out,
                     int32_t n_tokens, int32_t topk, int32_t hidden, void* stream);
 

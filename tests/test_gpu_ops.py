@@ -1,0 +1,165 @@
+"""The ops through their reference-shaped api functions (dispatch registry included) on the device."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from aklr_b200 import workloads as wl
+from oracle import moe_oracle as orc
+from tests.golden import cases
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from aklr_b200 import ops as module
+
+    torch.cuda.set_device(0)
+    module.init()
+    return module
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def to_dev(args):
+    return {k: (v.to(dev()) if isinstance(v, torch.Tensor) else v) for k, v in args.items()}
+
+
+def test_deepseek_v2_fp8_moe_op(ops, golden):
+    cfg, a = cases.ds_small_layer()
+    out = ops.deepseek_v2_fp8_moe(
+        **to_dev(a), topk=cfg.topk, num_expert_group=cfg.num_expert_group, topk_group=cfg.topk_group,
+        renormalize=True, scoring_func="sigmoid",
+    )
+    assert isinstance(out, torch.Tensor) and out.dtype == torch.bfloat16
+    # the router GEMM runs on the device: compare against the oracle fed the device's logits
+    from aklr_b200.moe import router_logits
+
+    logits = router_logits(a["hidden_states"].to(dev()), a["router_weight"].to(dev())).cpu().float()
+    ref = orc.deepseek_v2_fp8_moe(
+        a["hidden_states"], None, a["correction_bias"], a["w1"], a["w1_scale"], a["w2"], a["w2_scale"], cfg.topk,
+        cfg.num_expert_group, cfg.topk_group, True, 2.5, logits=logits,
+    )
+    gates = orc.output_gates(out.cpu(), ref)
+    assert orc.gates_pass(gates), gates
+
+
+def test_qwen3_moe_fp8_moe_op_and_fallbacks(ops, golden):
+    cfg, a = cases.tiny_layer()
+    d = to_dev(a)
+    out = ops.qwen3_moe_fp8_moe(**d, topk=cfg.topk)
+    assert isinstance(out, torch.Tensor)
+    gates = orc.output_gates(out.cpu(), torch.from_numpy(np.asarray(golden["tiny.out"])))
+    assert gates["cosine"] > 0.999  # a logit one bf16 step off may reroute a token; see the layer tests for the gates
+    # out of contract: a non-contiguous input, a wrong dtype, an empty batch
+    assert ops.qwen3_moe_fp8_moe(**{**d, "hidden_states": d["hidden_states"].t().contiguous().t()}, topk=2) is ops.FallbackReason.OUT_OF_CONTRACT
+    assert ops.qwen3_moe_fp8_moe(**{**d, "hidden_states": d["hidden_states"].float()}, topk=2) is ops.FallbackReason.OUT_OF_CONTRACT
+    assert ops.qwen3_moe_fp8_moe(**{**d, "hidden_states": d["hidden_states"][:0]}, topk=2) is ops.FallbackReason.OUT_OF_CONTRACT
+    assert ops.qwen3_moe_fp8_moe.fallback_reason(**d, topk=2) is None
+    assert ops.qwen3_moe_fp8_moe.serving(**d, topk=2).arch == "sm_100a"
+
+
+def test_fused_moe_op_fp8_with_expert_mask(ops):
+    cfg = wl.CONFIGS["tiny"]
+    hidden, logits, _ = wl.router_inputs(cfg, 40, seed=31)
+    w1, s1, w2, s2 = wl.expert_weights(cfg, seed=32)
+    ids, weights = orc.softmax_topk(logits.float(), cfg.topk)
+    mask = torch.zeros(cfg.n_routed, dtype=torch.int32)
+    mask[2:6] = 1
+    d = dev()
+    out_buffer = torch.empty((40, cfg.hidden), dtype=torch.bfloat16, device=d)
+    out = ops.fused_moe(
+        hidden.to(d), w1[2:6].to(d), w2[2:6].to(d), weights.to(d), ids.to(torch.int32).to(d), expert_mask=mask.to(d),
+        activation="silu", quant_type="per_128x128", w1_scale=s1[2:6].to(d), w2_scale=s2[2:6].to(d), out=out_buffer,
+    )
+    assert out is out_buffer
+    local = torch.where((ids >= 2) & (ids < 6), ids - 2, -1)
+    ref = orc.fp8_experts(hidden, local, weights, w1[2:6], s1[2:6], w2[2:6], s2[2:6])
+    gates = orc.output_gates(out.cpu(), ref)
+    assert orc.gates_pass(gates), gates
+    # an output buffer that overlaps an input is refused
+    bad = ops.fused_moe(hidden.to(d), w1[2:6].to(d), w2[2:6].to(d), weights.to(d), ids.to(torch.int32).to(d),
+                        quant_type="per_128x128", w1_scale=s1[2:6].to(d), w2_scale=s2[2:6].to(d), out=hidden.to(d)[:40])
+    assert isinstance(bad, torch.Tensor)  # a fresh copy does not overlap: served
+    x = hidden.to(d)
+    assert ops.fused_moe(x, w1[2:6].to(d), w2[2:6].to(d), weights.to(d), ids.to(torch.int32).to(d), quant_type="per_128x128",
+                         w1_scale=s1[2:6].to(d), w2_scale=s2[2:6].to(d), out=x) is ops.FallbackReason.OUT_OF_CONTRACT
+
+
+def test_fused_moe_op_mxfp4(ops):
+    cfg = wl.MoEConfig("mx", hidden=512, inter=256, n_routed=8, topk=2)
+    w1, s1, w2, s2 = wl.mx_expert_weights(cfg, seed=3)
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(70, 512, generator=g).to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(8, generator=g)[:2] for _ in range(70)]).to(torch.int32)
+    wts = torch.rand(70, 2, generator=g)
+    d = dev()
+    out = ops.fused_moe(x.to(d), w1.to(d), w2.to(d), wts.to(d), ids.to(d), activation="silu", quant_type="per_1x32",
+                        w1_scale=s1.to(d), w2_scale=s2.to(d), act_quant=8)
+    assert isinstance(out, torch.Tensor)
+    ref = orc.mx_experts(x, ids.long(), wts, w1, s1, w2, s2, act_bits=8)
+    gates = orc.output_gates(out.cpu(), ref)
+    assert orc.gates_pass(gates), gates
+    # MXFP4 activations (act_quant 4, the reference's default) are not served
+    assert ops.fused_moe(x.to(d), w1.to(d), w2.to(d), wts.to(d), ids.to(d), quant_type="per_1x32", w1_scale=s1.to(d),
+                         w2_scale=s2.to(d)) is ops.FallbackReason.OUT_OF_CONTRACT
+
+
+def test_biased_grouped_topk_and_quant_ops(ops, golden):
+    logits, bias = cases.bgt()
+    d = dev()
+    w = torch.empty((96, 8), dtype=torch.float32, device=d)
+    ids = torch.empty((96, 8), dtype=torch.int32, device=d)
+    got_w, got_ids = ops.biased_grouped_topk(logits.to(d), bias.to(d), w, ids, 1, 1, True, 2.5)
+    assert got_w is w and got_ids is ids
+    assert torch.equal(ids.cpu(), torch.from_numpy(np.asarray(golden["bgt.ids"])))
+    torch.testing.assert_close(w.cpu(), torch.from_numpy(np.asarray(golden["bgt.weights"])), atol=1e-4, rtol=1e-4)
+    x = cases.quant_x().to(d)
+    q, s = ops.per_group_quant_fp8(x)
+    assert torch.equal(q.cpu().float(), torch.from_numpy(np.asarray(golden["quant_fp8.q"])))
+    assert s.shape == (4, 24)
+    q, s = ops.per_group_quant_mxfp8(x)
+    assert torch.equal(s.cpu(), torch.from_numpy(np.asarray(golden["quant_mxfp8.s"])))
+
+
+def test_mega_moe_op_single_rank_and_emulated_group(ops):
+    """ep_size 1 through the op; four emulated ranks through the phases, against the oracle over all
+    experts with the reference's clamp at 10."""
+    from aklr_b200.ep import CudaKernels, ExpertParallelMoE, run_in_process
+    from aklr_b200.moe import Routing
+
+    cfg = wl.MoEConfig("mx", hidden=256, inter=128, n_routed=8, topk=2)
+    w1, s1, w2, s2 = wl.mx_expert_weights(cfg, seed=11)
+    d = dev()
+
+    def inputs(seed, tokens):
+        g = torch.Generator().manual_seed(seed)
+        x = (torch.randn(tokens, 256, generator=g) * 3).to(torch.bfloat16)
+        ids = torch.stack([torch.randperm(8, generator=g)[:2] for _ in range(tokens)]).to(torch.int32)
+        return x, ids, torch.rand(tokens, 2, generator=g)
+
+    x, ids, wts = inputs(1, 50)
+    out = ops.mega_moe(x.to(d), w1.to(d), w2.to(d), wts.to(d), ids.to(d), w1_scale=s1.to(d), w2_scale=s2.to(d), ep_size=1)
+    assert isinstance(out, torch.Tensor)
+    ref = orc.mx_experts(x, ids.long(), wts, w1, s1, w2, s2, swiglu_limit=10.0)
+    gates = orc.output_gates(out.cpu(), ref)
+    assert orc.gates_pass(gates), gates
+
+    world, layers, ins = 4, [], []
+    for r in range(world):
+        mine = slice(2 * r, 2 * r + 2)
+        layers.append(ExpertParallelMoE(Routing(topk=2), w1[mine].to(d), s1[mine].to(d), w2[mine].to(d), s2[mine].to(d), r, world,
+                                        kernels=CudaKernels("mxfp4", 10.0)))
+        xr, idr, wtr = inputs(20 + r, 9 + 5 * r)
+        ins.append((xr.to(d), None, None, (idr.to(d), wtr.to(d))))
+    outs = run_in_process(layers, ins)
+    for r in range(world):
+        xr, idr, wtr = inputs(20 + r, 9 + 5 * r)
+        ref = orc.mx_experts(xr, idr.long(), wtr, w1, s1, w2, s2, swiglu_limit=10.0)
+        gates = orc.output_gates(outs[r].cpu(), ref)
+        assert orc.gates_pass(gates), (r, gates)
