@@ -307,9 +307,10 @@ def bench_ep(args, cfg, rank, world, device, clock_sampler, workload_config, met
         raise SystemExit(f"{cfg.n_routed} routed experts do not split over {world} ranks")
     n_local = cfg.n_routed // world
     mine = list(range(rank * n_local, (rank + 1) * n_local)) + list(range(cfg.n_routed, cfg.n_experts))
-    w1, s1, w2, s2 = wl.expert_weights(cfg, seed, device, experts=mine)
+    mx = getattr(args, "format", "fp8") == "mxfp4"
+    w1, s1, w2, s2 = (wl.mx_expert_weights if mx else wl.expert_weights)(cfg, seed, device, experts=mine)
     routing = Routing(cfg.topk, cfg.scoring, cfg.n_shared, cfg.num_expert_group, cfg.topk_group, cfg.renormalize, cfg.routed_scaling_factor)
-    layer = ExpertParallelMoE(routing, w1, s1, w2, s2, rank, world)
+    layer = ExpertParallelMoE(routing, w1, s1, w2, s2, rank, world, kernels=CudaKernels("mxfp4" if mx else "fp8"))
     bias = wl.router_inputs(cfg, 1, seed + 1, device)[2]
     n_batches, tokens = 4, args.tokens
     batches = [wl.router_inputs(cfg, tokens, seed + 1 + 97 * rank + b, device)[:2] for b in range(n_batches)]
@@ -336,7 +337,7 @@ def bench_ep(args, cfg, rank, world, device, clock_sampler, workload_config, met
     for i in range(args.warmup):
         step(i)
     torch.cuda.synchronize()
-    lib.aklr_profile_begin(2 * args.steps)
+    lib.aklr_profile_begin(0 if mx else 2 * args.steps)
     launches0 = lib.aklr_kernel_launch_count()
     sampler = clock_sampler(device.index) if rank == 0 else None
     ms_per_step = timed(lambda i: step(args.warmup + i), args.steps)
@@ -345,7 +346,7 @@ def bench_ep(args, cfg, rank, world, device, clock_sampler, workload_config, met
     # stage times of the routed-expert calls (every second recorded call; the other is the shared expert)
     stage_ms = [0.0] * 6
     buf = (ctypes.c_float * 6)()
-    for i in range(args.steps):
+    for i in range(0 if mx else args.steps):
         _lib.check(lib.aklr_profile_read(2 * i + 1, buf))
         for j in range(6):
             stage_ms[j] += buf[j] / args.steps
@@ -372,6 +373,11 @@ def bench_ep(args, cfg, rank, world, device, clock_sampler, workload_config, met
     gate_up_bytes = n_local * (2 * inter * h + 4 * (2 * inter // 128) * (h // 128)) + routes_local * (h + 4 * (h // 128) + inter)
     peak, peak_kind = measured_peak_hbm()
     achieved = gate_up_bytes / (stage_ms[3] * 1e-3) / 1e9 if stage_ms[3] > 0 else 0.0
+    config = workload_config(cfg, args)
+    if mx:
+        metric = metric.replace("fp8", "mxfp4")
+        config["weights"] = "mxfp4: e2m1 + e8m0 per 32 along K, N(0,0.02)"
+        config["activations"] = "bf16 N(0,1), quantised to MXFP8 (e4m3 + e8m0 per 32)"
     line = {
         "metric": metric,
         "value": world * tokens / (ms_per_step * 1e-3),
@@ -383,10 +389,11 @@ def bench_ep(args, cfg, rank, world, device, clock_sampler, workload_config, met
         "higher_is_better": True,
         "scaling": "weak",
         "vs_baseline": None,
-        "dtype": "fp8_e4m3",
+        "dtype": "mxfp4 x mxfp8" if mx else "fp8_e4m3",
         "data": "synthetic",
-        "config": workload_config(cfg, args),
+        "config": config,
         "clocks": clocks,
+        "tflops": world * tokens * cfg.routes_per_token * cfg.flops_per_route / (ms_per_step * 1e-3) / 1e12,
         "e2e": {
             "value": world * tokens / (e2e_ms * 1e-3),
             "unit": unit,
