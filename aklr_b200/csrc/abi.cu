@@ -98,6 +98,23 @@ int make_map_fp4(CUtensorMap* map, const void* base, uint64_t rows, uint64_t col
   return AKLR_OK;
 }
 
+// bf16 matrix [rows, cols]: box = box_rows x 64 elements (128 bytes), SWIZZLE_128B, zero fill outside.
+int make_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (!encode) return fail(AKLR_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  if (reinterpret_cast<uintptr_t>(base) % 16 != 0 || (cols * 2) % 16 != 0)
+    return fail(AKLR_ERR_BAD_ARGUMENT, "TMA operand must be 16-byte aligned with a 16-byte multiple row pitch");
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {64, box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(AKLR_ERR_CUDA, "cuTensorMapEncodeTiled (bf16) failed with CUresult %d", (int)r);
+  return AKLR_OK;
+}
+
 int sm_count() {
   int dev = 0, n = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return 0;
@@ -709,7 +726,20 @@ int aklr_router_gemm_bf16(const void* x, const void* w, void* logits, int32_t n_
   if (!x || !w || !logits) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
   int rc = check_device();
   if (rc) return rc;
-  rc = aklr::launch_router_gemm(x, w, logits, n_tokens, hidden, n_routed, static_cast<cudaStream_t>(stream));
+  // 64 tokens and up: tensor cores (128-token tiles); fewer: the warp-per-dot-product kernel, which
+  // spreads the router weight over many SMs
+  if (n_tokens >= 64 && hidden % 64 == 0 && n_routed >= 1) {
+    int n_tile = (n_routed + 15) / 16 * 16;
+    if (n_tile > 256) n_tile = 256;
+    CUtensorMap map_x, map_w;
+    rc = make_map_bf16(&map_x, x, n_tokens, hidden, 128);
+    if (rc) return rc;
+    rc = make_map_bf16(&map_w, w, n_routed, hidden, n_tile);
+    if (rc) return rc;
+    rc = aklr::launch_router_gemm_tc(map_x, map_w, logits, n_tokens, hidden, n_routed, n_tile, static_cast<cudaStream_t>(stream));
+  } else {
+    rc = aklr::launch_router_gemm(x, w, logits, n_tokens, hidden, n_routed, static_cast<cudaStream_t>(stream));
+  }
   if (rc) return fail(rc, "router GEMM: %s", aklr_status_string(rc));
   g_launches += 1;
   return AKLR_OK;

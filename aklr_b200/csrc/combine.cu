@@ -55,8 +55,8 @@ int launch_combine(const CombineParams& p, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
 }
 
-// One warp per (token, 8 experts): lanes stride the hidden dimension with 16-byte loads.
-constexpr int kRouterExperts = 8;
+// One warp per (token, kRouterExperts experts): lanes stride the hidden dimension with 16-byte loads.
+template <int kRouterExperts>
 __global__ void __launch_bounds__(256)
 router_gemm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w, uint16_t* __restrict__ logits,
                    int n_tokens, int hidden, int n_routed) {
@@ -104,13 +104,19 @@ int launch_router_gemm(const void* x, const void* w, void* logits, int n_tokens,
                        cudaStream_t stream) {
   if (hidden % 8 != 0) return AKLR_ERR_UNSUPPORTED_SHAPE;
   if (n_tokens == 0) return AKLR_OK;
-  const int groups = (n_routed + kRouterExperts - 1) / kRouterExperts;
+  // few tokens: one expert per warp so the router weight is streamed by many SMs
+  const int per_warp = n_tokens <= 16 ? 1 : 8;
+  const int groups = (n_routed + per_warp - 1) / per_warp;
   const int64_t items = static_cast<int64_t>(n_tokens) * groups;
   const int64_t blocks = (items + 7) / 8;
   if (blocks > 0x7FFFFFFF) return AKLR_ERR_TOO_LARGE;
-  router_gemm_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
-      static_cast<const uint16_t*>(x), static_cast<const uint16_t*>(w), static_cast<uint16_t*>(logits), n_tokens,
-      hidden, n_routed);
+  auto* xp = static_cast<const uint16_t*>(x);
+  auto* wp = static_cast<const uint16_t*>(w);
+  auto* lp = static_cast<uint16_t*>(logits);
+  if (per_warp == 1)
+    router_gemm_kernel<1><<<static_cast<int>(blocks), 256, 0, stream>>>(xp, wp, lp, n_tokens, hidden, n_routed);
+  else
+    router_gemm_kernel<8><<<static_cast<int>(blocks), 256, 0, stream>>>(xp, wp, lp, n_tokens, hidden, n_routed);
   return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
 }
 

@@ -153,6 +153,10 @@ struct EpCombineParams {
 };
 int launch_ep_combine(const EpCombineParams& p, cudaStream_t stream);
 
+// tensor-core router GEMM (router_gemm.cu): maps are bf16 [T,H] box 64 x 128 and [E,H] box 64 x n_tile
+int launch_router_gemm_tc(const CUtensorMap& map_x, const CUtensorMap& map_w, void* logits, int n_tokens, int hidden,
+                          int n_routed, int n_tile, cudaStream_t stream);
+
 // Opt a kernel in to the full 227 KB of dynamic shared memory, once per (kernel, device).
 int ensure_max_dynamic_smem(const void* kernel);
 

@@ -383,10 +383,30 @@ def main() -> None:
         dev_hidden = torch.empty_like(batches[0][0])
         ops.init()
 
+        # Three streams, two buffers each way: step i's H2D overlaps step i-1's compute and step
+        # i-2's D2H, as a serving loop would run it.  Every step still copies its own inputs in and
+        # its own result out inside the timed region.
+        copy_in, copy_out, compute = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
+        dev_in = [torch.empty_like(batches[0][0]) for _ in range(2)]
+        host_outs = [torch.empty((T, cfg.hidden), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+        in_ready = [torch.cuda.Event() for _ in range(2)]
+        in_free = [torch.cuda.Event() for _ in range(2)]
+        out_ready = [torch.cuda.Event() for _ in range(2)]
+        out_free = [torch.cuda.Event() for _ in range(2)]
+        results = [None, None]
+        for ev in in_free + out_free:
+            ev.record(compute)
+
         def e2e_step(i):
-            dev_hidden.copy_(host_hidden[i % n_batches], non_blocking=True)
+            k = i % 2
+            with torch.cuda.stream(copy_in):
+                copy_in.wait_event(in_free[k])
+                dev_in[k].copy_(host_hidden[i % n_batches], non_blocking=True)
+                in_ready[k].record(copy_in)
+            compute.wait_event(in_ready[k])
+            compute.wait_event(out_free[k])
             result = ops.deepseek_v2_fp8_moe(
-                hidden_states=dev_hidden,
+                hidden_states=dev_in[k],
                 router_weight=router_w,
                 correction_bias=bias,
                 w1=w1,
@@ -402,16 +422,25 @@ def main() -> None:
             )
             if not isinstance(result, torch.Tensor):
                 raise SystemExit(f"the op fell back: {result}")
-            host_out.copy_(result, non_blocking=True)
+            results[k] = result
+            in_free[k].record(compute)
+            out_ready[k].record(compute)
+            with torch.cuda.stream(copy_out):
+                copy_out.wait_event(out_ready[k])
+                host_outs[k].copy_(result, non_blocking=True)
+                result.record_stream(copy_out)
+                out_free[k].record(copy_out)
 
         for i in range(args.warmup):
             e2e_step(i)
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
+        e0.record(compute)
         for i in range(args.steps):
             e2e_step(i)
-        e1.record()
+        compute.wait_stream(copy_out)
+        compute.wait_stream(copy_in)
+        e1.record(compute)
         torch.cuda.synchronize()
         e2e_ms = e0.elapsed_time(e1) / args.steps
         e2e = {
@@ -420,7 +449,7 @@ def main() -> None:
             "ms_per_step": e2e_ms,
             "h2d_bytes_per_step": T * cfg.hidden * 2,
             "d2h_bytes_per_step": T * cfg.hidden * 2,
-            "api": "aklr_b200.ops.deepseek_v2_fp8_moe (router GEMM included)",
+            "api": "aklr_b200.ops.deepseek_v2_fp8_moe (router GEMM included); copies double-buffered on their own streams",
         }
 
     sweep = None

@@ -417,3 +417,18 @@ def test_layer_call_is_cuda_graph_capturable():
     eager = fused_moe_fp8(hidden2, logits2, bias, w1, s1, w2, s2, routing)
     assert torch.equal(replayed, eager)
     ws.check_status()
+
+
+@pytest.mark.parametrize("n_tokens,hidden,experts", [(300, 1024, 256), (64, 512, 40), (1000, 7168, 257), (5, 512, 64), (40, 256, 8)])
+def test_router_gemm_paths_round_like_the_oracle(n_tokens, hidden, experts):
+    """Tensor-core path (>= 64 tokens, ragged tiles, expert counts that are not tile multiples) and the
+    warp-per-dot-product path for few tokens."""
+    from aklr_b200.moe import router_logits
+
+    x = wl.normal(1, "x", (n_tokens, hidden), 1.0, dtype=torch.bfloat16)
+    w = wl.normal(2, "w", (experts, hidden), 0.05, dtype=torch.bfloat16)
+    got = router_logits(x.to(dev()), w.to(dev())).cpu().float()
+    ref = orc.router_logits(x, w)
+    step = ref.abs().clamp_min(1e-2) * 2.0**-7
+    assert ((got - ref).abs() <= step).all()
+    assert (got == ref).float().mean() > 0.95
