@@ -17,6 +17,7 @@ thread_local char g_error[512] = "";
 
 // ---- optional stage timing: a ring of CUDA events the caller switches on for a measurement ----
 constexpr int kStages = 6;  // route, sort, quant, gate_up, down, combine
+constexpr int kQuantOncePerTokenFrom = 512;  // tokens from which activations are quantised once per token, then gathered
 struct StageProfile {
   std::vector<cudaEvent_t> events;  // (kStages + 1) per recorded call
   int capacity = 0, used = 0;
@@ -234,7 +235,28 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   qp.block_m = l.block_m;
   qp.q_in = q_in;
   qp.scales_in = scales_in;
-  rc = q_in ? launch_gather_rows_fp8(qp, stream) : launch_gather_quant_fp8(qp, stream);
+  if (!q_in && routes_per_token > 1 && c.n_tokens >= kQuantOncePerTokenFrom) {
+    // A token's routes all carry the same quantised row: quantise every token once, then copy.
+    // The per-route output rows are not written before the down projection, so their space
+    // holds the per-token codes and scales until then.
+    uint8_t* tq = ws + l.rows;
+    float* ts = reinterpret_cast<float*>(tq + align_up(static_cast<int64_t>(c.n_tokens) * c.hidden, 256));
+    GatherQuantParams tp{};
+    tp.x = hidden_states;
+    tp.q = tq;
+    tp.scales = ts;
+    tp.n_rows = c.n_tokens;
+    tp.hidden = c.hidden;
+    tp.routes_per_token = 1;
+    rc = launch_gather_quant_fp8(tp, stream);
+    if (rc) return fail(rc, "activation quant launch failed");
+    g_launches += 1;
+    qp.q_in = tq;
+    qp.scales_in = ts;
+    rc = launch_gather_rows_fp8(qp, stream);
+  } else {
+    rc = q_in ? launch_gather_rows_fp8(qp, stream) : launch_gather_quant_fp8(qp, stream);
+  }
   if (rc) return fail(rc, "activation quant launch failed");
   g_launches += 1;
   profile_mark(stream, slot, 3);
@@ -259,7 +281,7 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   g1.block_m = l.block_m;
   g1.max_blocks = l.max_blocks;
   const bool tm1 = grouped_gemm_is_token_major(true, l.block_m, c.inter) && !g_force_swap_ab;
-  g1.stages = tm1 ? grouped_gemm_prefill_pick_stages(c.hidden) : grouped_gemm_pick_stages(true, l.block_m, c.hidden);
+  g1.stages = tm1 ? grouped_gemm_prefill_pick_stages(true) : grouped_gemm_pick_stages(true, l.block_m, c.hidden);
   if (g1.stages < 2) return fail(AKLR_ERR_UNSUPPORTED_SHAPE, "hidden=%d needs more shared memory than one SM has", c.hidden);
   rc = tm1 ? launch_grouped_gemm_prefill(g1, true, sms, stream) : launch_grouped_gemm_gate_up(g1, sms, stream);
   if (rc) return fail(rc, "gate_up grouped GEMM launch failed");
@@ -285,7 +307,7 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   g2.rows_per_expert = c.hidden;
   g2.block_m = l.block_m;
   g2.max_blocks = l.max_blocks;
-  g2.stages = tm2 ? grouped_gemm_prefill_pick_stages(c.inter) : grouped_gemm_pick_stages(false, l.block_m, c.inter);
+  g2.stages = tm2 ? grouped_gemm_prefill_pick_stages(false) : grouped_gemm_pick_stages(false, l.block_m, c.inter);
   if (g2.stages < 2) return fail(AKLR_ERR_UNSUPPORTED_SHAPE, "inter=%d needs more shared memory than one SM has", c.inter);
   rc = tm2 ? launch_grouped_gemm_prefill(g2, false, sms, stream) : launch_grouped_gemm_down(g2, sms, stream);
   if (rc) return fail(rc, "down grouped GEMM launch failed");

@@ -10,16 +10,26 @@
 // (activation scale of the thread's token x the weight block scale), so folding a partial into the
 // float32 accumulators is exactly one FMA per element with both operands in registers.
 //
-// Per thread the epilogue also becomes local: a token's 64 (gate_up) or 128 (down) channels sit in
-// one thread, which writes them as whole 16-byte vectors of its own output row.
+// A token's 64 (gate_up) or 128 (down) channels sit in one thread.  gate_up writes them as 16-byte
+// vectors of its own FP8 row; down stages bf16 rows in shared memory and writes 128 contiguous
+// bytes of 4 rows per instruction (direct stores would be 32 half-filled sectors each).
 //
-// Warp roles (64 + 128*kCS threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, the rest
-// epilogue (TMEM lane quarter = warp % 4, column split = (warp-2)/4).  Measured on B200: a warp
-// drains TMEM at about one column per 4.3 cycles when the tensor core is idle and one per 8 cycles
-// while MMAs run, whatever the tcgen05.ld width, and more warps per lane quarter add up; with this
-// tile the drain (256 columns per quarter per K-block) costs about as much as the MMAs, so 8 and 16
-// epilogue warps, and one N=256 or two N=128 MMA groups per K-block, all land within 10%.  Persistent CTAs, TMA
-// SWIZZLE_128B ring, two 256-column TMEM partial buffers, no cluster, no multicast, bounded waits.
+// Warp roles (384 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2-3 idle,
+// warps 4-11 epilogue (TMEM lane quarter = warp % 4, column split = (warp-4)/4).  The first
+// warpgroup gives its registers to the epilogue (setmaxnreg 40 / 232): 128 accumulators + 64
+// staging registers per epilogue thread do not fit the 168 an even split allows.
+//
+// What bounds it, measured on B200 by taking parts out (AKLR_EXP_NOMMA / AKLR_EXP_NODRAIN leave
+// out the MMAs / the TMEM loads and folds; both out = TMA ring + barriers only): the TMA ring
+// alone takes 570 ns per K-block per SM with L2-resident weights (48 KB per K-block -> 12.4 TB/s
+// L2 -> shared memory over 148 SMs) and 670 ns when the weights stream from HBM; the full kernel
+// 670 / 790 ns.  So the tile's operand traffic, not the tensor core (4 MMAs = 512 cycles) or the
+// epilogue, is the limit; the epilogue is hidden as long as (i) the MMA thread's loop is lean --
+// one commit per K-block, no divisions, descriptors carried forward -- because a lone thread pays
+// full latency per instruction, (ii) scales are prefetched from global memory two K-blocks ahead
+// instead of staged per tile, (iii) a batch of tcgen05.ld (4 x 8 columns) is in flight while the
+// previous one is folded with packed FMAs.  Persistent CTAs, TMA SWIZZLE_128B ring, two
+// 256-column TMEM partial buffers, no cluster, no multicast, bounded waits.
 #include <cfloat>
 
 #include "common.cuh"
@@ -28,9 +38,12 @@
 namespace aklr {
 
 #ifdef AKLR_GEMM_TIMING
-// Development aid, compiled only on request: cycle counts per role of CTA 0.
+// Development aid, compiled only on request: cycle counts per role of CTA 0 and a trace of
+// hand-off times (64 K-blocks) of the gate_up kernel.
 // [1] mma wait-full [2] mma wait-tmem-empty [3] mma issue [4] epi wait [5] epi ld+fma [6] setup [7] final [8] kblocks
 __device__ long long g_prefill_timing[2][16];
+__device__ long long g_prefill_trace[8][64];
+#define TR(slot) do { if (GATE_UP && blockIdx.x == 0 && it >= 120 && it < 184) g_prefill_trace[slot][it - 120] = clock64(); } while (0)
 #define PT(slot, expr)                                         \
   do {                                                         \
     const long long t_begin_ = clock64();                      \
@@ -49,28 +62,31 @@ namespace {
 constexpr int kCS = 2;                   // column splits: epilogue warps = 4 lane quarters x kCS
 constexpr int kEpiWarps = 4 * kCS;
 constexpr int kEpi = 32 * kEpiWarps;
-constexpr int kThreads = 64 + kEpi;
+constexpr int kFirstEpiWarp = 4;         // warps 0..3: TMA producer, MMA issuer, two idle (one warpgroup)
+constexpr int kThreads = 32 * kFirstEpiWarp + kEpi;
+constexpr int kRegsLean = 40, kRegsEpi = 232;  // setmaxnreg: 128*40 + 256*232 <= 64K registers
 constexpr int kBM = 128;                 // tokens per block
 constexpr int kBN = 256;                 // weight rows per tile
 constexpr int kABytes = kBM * 128;       // token tile of one K-block
 constexpr int kBBytes = kBN * 128;       // weight tile of one K-block
 constexpr int kStageBytes = kABytes + kBBytes;
-constexpr bool kSplitGroups = false;     // true: two N=128 MMA groups per K-block instead of one N=256
+constexpr int kBatch = 32;                // TMEM columns one epilogue thread loads per round
+constexpr bool kDouble = true;           // next round's loads in flight while this one is folded
+constexpr int kLdCols = 8;               // columns per tcgen05.ld
 
 struct PrefillLayout {
-  int off_xs, off_ws, off_rid, off_wgt, off_wmax, off_bars, total;
+  int off_out, off_rid, off_wmax, off_bars, total;
 };
 
-__host__ __device__ inline PrefillLayout prefill_layout(int k, int stages) {
+constexpr int kOutPassCols = 64;  // down: channels per thread staged per pass (128 bytes per row)
+
+__host__ __device__ inline PrefillLayout prefill_layout(bool gate_up, int stages) {
   PrefillLayout l;
-  const int kb = k / 128;
-  l.off_xs = stages * kStageBytes;            // float[kb][128] activation scales of the block
-  l.off_ws = l.off_xs + kb * kBM * 4;         // float[2][kb] weight block scales of the two halves
-  l.off_rid = l.off_ws + ((2 * kb * 4 + 15) & ~15);
-  l.off_wgt = l.off_rid + kBM * 4;            // float[128] route weights
-  l.off_wmax = l.off_wgt + kBM * 4;           // float[kCS][128] amax per column split
+  l.off_out = stages * kStageBytes;  // down: per epilogue warp 32 rows x 128 bytes of bf16 output
+  l.off_rid = l.off_out + (gate_up ? 0 : kEpiWarps * 32 * kOutPassCols * 2);
+  l.off_wmax = l.off_rid + kBM * 4;  // float[kCS][128] amax per column split (gate_up)
   l.off_bars = l.off_wmax + kCS * kBM * 4;
-  l.total = l.off_bars + (2 * stages + 8) * 8 + 16;
+  l.total = l.off_bars + (2 * stages + 4) * 8 + 16;
   return l;
 }
 
@@ -105,23 +121,18 @@ __device__ __forceinline__ bool epi_any(int flag) {
 template <bool GATE_UP>
 __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const __grid_constant__ GroupedGemmParams p) {
   constexpr int NH = kBN / kCS;   // accumulator columns per epilogue thread
-  constexpr int CH = 8;     // columns per tcgen05.ld
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int KB = p.k >> 7;
   const int S = p.stages;
-  const PrefillLayout L = prefill_layout(p.k, S);
-  float* xs_s = reinterpret_cast<float*>(smem + L.off_xs);
-  float* ws_s = reinterpret_cast<float*>(smem + L.off_ws);
+  const PrefillLayout L = prefill_layout(GATE_UP, S);
   int* rid_s = reinterpret_cast<int*>(smem + L.off_rid);
-  float* wgt_s = reinterpret_cast<float*>(smem + L.off_wgt);
   float* wmax = reinterpret_cast<float*>(smem + L.off_wmax);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.off_bars);
   uint64_t* empty = full + S;
-  uint64_t* tmem_full = empty + S;
-  uint64_t* tmem_empty = tmem_full + 4;
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(tmem_empty + 4);
+  uint64_t* tmem_empty = empty + S;
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -136,10 +147,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    for (int i = 0; i < 4; ++i) {  // buffer = (K-block parity) * 2 + column group
-      mbar_init(&tmem_full[i], 1);
-      mbar_init(&tmem_empty[i], GATE_UP ? kEpiWarps : kEpiWarps / 2);  // the warps that read the group
-    }
+    for (int i = 0; i < 2; ++i) mbar_init(&tmem_empty[i], kEpiWarps);  // buffer = K-block parity
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&p.map_w);
@@ -154,18 +162,21 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr;
 
+  // The accumulators of a 128 x 256 tile are 128 registers per epilogue thread, and the loads that
+  // drain TMEM want 64 more in flight: the producer warpgroup hands its registers over.
+  if (warp < kFirstEpiWarp) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsLean));
   if (warp == 0) {
     // ------------------------------- TMA producer ------------------------------------------
     if (lane == 0) {
-      uint32_t it = 0;
+      int s = 0;        // ring position and the parity of its current use
+      uint32_t ph = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const int b = t / tiles_per_block, j = t - b * tiles_per_block;
         const int e = p.block_expert[b];
         const int w_row = e * p.rows_per_expert + (GATE_UP ? j * 128 : j * 256);
-        for (int kb = 0; kb < KB; ++kb, ++it) {
-          const int s = it % S;
-          const uint32_t ph = (it / S) & 1;
+        for (int kb = 0; kb < KB; ++kb) {
           if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 11)) { ok = false; break; }
           uint8_t* st = smem + s * kStageBytes;
           mbar_expect_tx(&full[s], kStageBytes);
@@ -176,93 +187,89 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
           } else {
             tma_load_2d(st + kABytes, &p.map_w, &full[s], kb * 128, w_row);  // box of 256 rows
           }
+          if (++s == S) { s = 0; ph ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer --------------------------------------------
     if (lane == 0) {
+      // This thread is alone in its warp, so every instruction here costs its full latency:
+      // the loop carries ring positions and descriptors forward instead of recomputing them.
       uint32_t it = 0;
+      int s = 0;
+      uint32_t ph = 0, buf = 0, bph = 0;
+      const uint64_t desc0 = umma_desc_sw128(smem_u32(smem));
+      uint64_t da = desc0;  // descriptor of stage s' token tile; the weight tile follows it
       bool ok = true;
 #ifdef AKLR_GEMM_TIMING
       long long tacc[16] = {0};
 #endif
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         for (int kb = 0; kb < KB; ++kb, ++it) {
-          const int s = it % S;
-          const uint32_t ph = (it / S) & 1;
-          const int buf = it & 1;
-          const uint32_t bph = (it >> 1) & 1;
           bool got;
           PT(1, got = mbar_wait(&full[s], ph, abort_flag, p.status, 12));
           if (!got) { ok = false; break; }
-          const uint32_t a0 = smem_u32(smem + s * kStageBytes);
-          const uint64_t da = umma_desc_sw128(a0);
-          // Two column groups of 128 weight rows, each into its own TMEM buffer with its own
-          // hand-off: the epilogue starts on the first while the second is still being computed,
-          // and four buffers in flight hide the commit -> wake-up latency.
-          if (kSplitGroups) {
+#ifdef AKLR_GEMM_TIMING
+          TR(0);
+#endif
+          // One N=256 MMA per 32 K bytes into this K-block's TMEM buffer; a single commit per
+          // K-block: the barrier that frees the shared-memory stage also tells the epilogue that
+          // the partial is complete.
+          PT(2, got = mbar_wait(&tmem_empty[buf], bph ^ 1, abort_flag, p.status, 13));
+          if (!got) { ok = false; break; }
+#ifdef AKLR_GEMM_TIMING
+          TR(1);
+          const long long t_issue = clock64();
+#endif
+          tc_fence_after_sync();
+          const uint64_t db = da + (kABytes >> 4);
+          const uint32_t d = tmem_base + buf * 256;
+#ifndef AKLR_EXP_NOMMA
 #pragma unroll
-            for (int g = 0; g < 2; ++g) {
-              const int tb = buf * 2 + g;
-              PT(2, got = mbar_wait(&tmem_empty[tb], bph ^ 1, abort_flag, p.status, 13));
-              if (!got) { ok = false; break; }
-#ifdef AKLR_GEMM_TIMING
-              const long long t_issue = clock64();
+          for (int k = 0; k < 4; ++k) umma_f8f6f4(d, da + 2 * k, db + 2 * k, umma_idesc_e4m3(256), k > 0);
 #endif
-              tc_fence_after_sync();
-              const uint64_t db = umma_desc_sw128(a0 + kABytes + g * (kBBytes / 2));
-              const uint32_t d = tmem_base + tb * 128;
-#pragma unroll
-              for (int k = 0; k < 4; ++k) umma_f8f6f4(d, da + 2 * k, db + 2 * k, umma_idesc_e4m3(128), k > 0);
-              tc_commit(&tmem_full[tb]);
 #ifdef AKLR_GEMM_TIMING
-              tacc[3] += clock64() - t_issue;
+          TR(2);
+          tacc[3] += clock64() - t_issue;
+          const long long t_c2 = clock64();
 #endif
-            }
-          } else {  // one N=256 MMA per 32 K bytes over both groups' buffers (adjacent TMEM columns)
-            PT(2, got = mbar_wait(&tmem_empty[buf * 2], bph ^ 1, abort_flag, p.status, 13));
-            if (!got) { ok = false; break; }
-            PT(2, got = mbar_wait(&tmem_empty[buf * 2 + 1], bph ^ 1, abort_flag, p.status, 13));
-            if (!got) { ok = false; break; }
-#ifdef AKLR_GEMM_TIMING
-            const long long t_issue = clock64();
-#endif
-            tc_fence_after_sync();
-            const uint64_t db = umma_desc_sw128(a0 + kABytes);
-            const uint32_t d = tmem_base + buf * 256;
-#pragma unroll
-            for (int k = 0; k < 4; ++k) umma_f8f6f4(d, da + 2 * k, db + 2 * k, umma_idesc_e4m3(256), k > 0);
-            tc_commit(&tmem_full[buf * 2]);
-            tc_commit(&tmem_full[buf * 2 + 1]);
-#ifdef AKLR_GEMM_TIMING
-            tacc[3] += clock64() - t_issue;
-#endif
-          }
-          if (!ok) break;
           tc_commit(&empty[s]);
+#ifdef AKLR_GEMM_TIMING
+          TR(3);
+          tacc[12] += clock64() - t_c2;
+#endif
+          da += kStageBytes >> 4;
+          if (++s == S) { s = 0; ph ^= 1; da = desc0; }
+          bph ^= buf;
+          buf ^= 1;
         }
       }
 #ifdef AKLR_GEMM_TIMING
       if (blockIdx.x == 0) {
         for (int i = 1; i <= 3; ++i) g_prefill_timing[GATE_UP][i] = tacc[i];
+        for (int i = 10; i <= 12; ++i) g_prefill_timing[GATE_UP][i] = tacc[i];
         g_prefill_timing[GATE_UP][8] = it;
       }
 #endif
     }
+  }
   } else {
     // ------------------------------- epilogue warps ----------------------------------------
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsEpi));
     const int quarter = warp & 3;
-    const int cs = (warp - 2) >> 2;       // which column split this warp folds
-    const int et = threadIdx.x - 64;
+    const int cs = (warp - kFirstEpiWarp) >> 2;  // which column split this warp folds
     const int row = quarter * 32 + lane;  // token inside the block = TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const int IB = p.out_dim >> 7;
     uint32_t it = 0;
+    int ring = 0;          // shared-memory stage whose "empty" barrier reports MMA(it) complete
+    uint32_t ring_ph = 0;
     bool bad = false;
 #ifdef AKLR_GEMM_TIMING
     long long tacc[16] = {0};
     long long t_mark = clock64();
+    const long long t_kernel = t_mark;
 #endif
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
 #ifdef AKLR_GEMM_TIMING
@@ -272,24 +279,23 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
       if (epi_any(*abort_flag)) break;
       const int b = t / tiles_per_block, j = t - b * tiles_per_block;
       const int e = p.block_expert[b];
-      {
-        const float* xs = p.x_scale + static_cast<size_t>(b) * KB * kBM;
-        for (int i = et; i < KB * kBM; i += kEpi) xs_s[i] = __ldg(xs + i);
-        // weight block scales of the tile's two 128-row halves
-        const int rb0 = GATE_UP ? j : 2 * j;
-        const int rb1 = GATE_UP ? IB + j : 2 * j + 1;
-        const float* wsb = p.w_scale + static_cast<size_t>(e) * (p.rows_per_expert >> 7) * KB;
-        for (int i = et; i < KB; i += kEpi) {
-          ws_s[i] = __ldg(wsb + static_cast<size_t>(rb0) * KB + i);
-          ws_s[KB + i] = __ldg(wsb + static_cast<size_t>(rb1) * KB + i);
-        }
-        if (et < kBM) {
-          const int rid = p.sorted_ids[b * kBM + et];
-          rid_s[et] = rid;
-          if (!GATE_UP) wgt_s[et] = rid >= 0 ? p.topk_weights[rid] : 0.0f;
-        }
-      }
-      epi_sync();
+      // Scales come straight from global memory (L2 hits: the quantising kernel wrote them just
+      // before), two K-blocks ahead of their use; nothing is staged per tile.
+      const float* xs = p.x_scale + static_cast<size_t>(b) * KB * kBM + row;  // [K-block][token]
+      const float* wsb = p.w_scale + static_cast<size_t>(e) * (p.rows_per_expert >> 7) * KB;
+      const float* ws_lo = wsb + static_cast<size_t>(GATE_UP ? j : 2 * j + (cs * NH) / 128) * KB;
+      const float* ws_hi = GATE_UP ? wsb + static_cast<size_t>(IB + j) * KB : ws_lo;
+      float sx_q[3], wl_q[3], wh_q[3];  // K-blocks kb, kb+1, kb+2
+      sx_q[1] = __ldg(xs);
+      wl_q[1] = __ldg(ws_lo);
+      wh_q[1] = GATE_UP ? __ldg(ws_hi) : wl_q[1];
+      sx_q[2] = KB > 1 ? __ldg(xs + kBM) : 0.0f;
+      wl_q[2] = KB > 1 ? __ldg(ws_lo + 1) : 0.0f;
+      wh_q[2] = GATE_UP ? (KB > 1 ? __ldg(ws_hi + 1) : 0.0f) : wl_q[2];
+      const int rid = __ldg(p.sorted_ids + b * kBM + row);
+      float route_w = 0.0f;
+      // (the barrier inside epi_any above also means the previous tile's output pass is done with rid_s)
+      if (!GATE_UP && cs == 0) rid_s[row] = rid;
 
       // gate_up: first NH/2 accumulators gate channels cs*NH/2.., then the matching up channels
       // down:    NH output channels cs*NH..
@@ -302,49 +308,72 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
 
       for (int kb = 0; kb < KB; ++kb, ++it) {
         const int buf = it & 1;
-        const uint32_t bph = (it >> 1) & 1;
-        const float sx = xs_s[kb * kBM + row];
-        // gate_up: group 0 = gate columns, group 1 = up columns, this warp's NH/2 of each.
-        // down: this warp's NH channels lie in one group.
-        constexpr int GROUPS = GATE_UP ? 2 : 1;
-        constexpr int GC = NH / GROUPS;  // columns this thread takes from one group
+        sx_q[0] = sx_q[1]; sx_q[1] = sx_q[2];
+        wl_q[0] = wl_q[1]; wl_q[1] = wl_q[2];
+        wh_q[0] = wh_q[1]; wh_q[1] = wh_q[2];
+        if (kb + 2 < KB) {
+          sx_q[2] = __ldg(xs + (kb + 2) * kBM);
+          wl_q[2] = __ldg(ws_lo + kb + 2);
+          wh_q[2] = GATE_UP ? __ldg(ws_hi + kb + 2) : wl_q[2];
+        }
+        if (!GATE_UP && kb == (KB > 2 ? 2 : KB - 1)) route_w = rid >= 0 ? __ldg(p.topk_weights + rid) : 0.0f;
+        const float sx = sx_q[0];
+        // gate_up: this warp's NH/2 gate columns (weight rows 0..127 of the tile), then the matching
+        // up columns (rows 128..255).  down: NH channels, all inside one 128-row scale block.
+        constexpr int GC = GATE_UP ? NH / 2 : NH;  // consecutive TMEM columns before a jump
+        constexpr int NB = NH / kBatch;            // load batches per K-block
+        const float f_lo = sx * wl_q[0];
+        const float f_hi = sx * wh_q[0];
+        const uint64_t f2_lo = pack_f32x2(__float_as_uint(f_lo), __float_as_uint(f_lo));
+        const uint64_t f2_hi = pack_f32x2(__float_as_uint(f_hi), __float_as_uint(f_hi));
+        const uint32_t tcol = tmem_base + lane_addr + buf * 256 + (GATE_UP ? cs * GC : cs * NH);
+        auto batch_col = [&](int bi) -> uint32_t {  // TMEM address of batch bi
+          const int c = bi * kBatch;
+          return GATE_UP ? tcol + (c / GC) * 128 + (c % GC) : tcol + c;
+        };
+        bool got;
+        // MMA(it) complete = the "empty" barrier of its shared-memory stage completing phase it / S
+        PT(4, got = mbar_wait(&empty[ring], ring_ph, abort_flag, p.status, 14));
+        if (++ring == S) { ring = 0; ring_ph ^= 1; }
 #ifdef AKLR_GEMM_TIMING
         long long t_work = clock64();
+        if (warp == kFirstEpiWarp && lane == 0) TR(4);
 #endif
+        if (!got) bad = true;
+        tc_fence_after_sync();
+        // tcgen05.ld is latency-bound per warp (an x8 load returns after ~50 cycles, four of them
+        // issued back to back after ~60): keep a whole batch in flight, fold the previous one.
+        uint32_t r[kDouble ? 2 : 1][kBatch];
+        auto issue = [&](int bi) {
 #pragma unroll
-        for (int gi = 0; gi < GROUPS; ++gi) {
-          const int g = GATE_UP ? gi : (cs * NH) / 128;
-          const int tb = buf * 2 + g;
-          bool got;
-#ifdef AKLR_GEMM_TIMING
-          if (blockIdx.x == 0) tacc[5] += clock64() - t_work;
-#endif
-          PT(4, got = mbar_wait(&tmem_full[tb], bph, abort_flag, p.status, 14));
-#ifdef AKLR_GEMM_TIMING
-          t_work = clock64();
-#endif
-          if (!got) bad = true;
-          tc_fence_after_sync();
-          const float f = sx * ws_s[g * KB + kb];
-          const uint64_t f2 = pack_f32x2(__float_as_uint(f), __float_as_uint(f));
-          const uint32_t t0 = tmem_base + lane_addr + tb * 128 + (GATE_UP ? cs * GC : (cs * NH) % 128);
-          uint32_t r[2][CH];
-          AKLR_TMEM_LD_8(t0, r[0]);
-#pragma unroll
-          for (int k = 0; k < GC / CH; ++k) {
-            tc_wait_ld();
-            if (k + 1 < GC / CH) {
-              AKLR_TMEM_LD_8(t0 + (k + 1) * CH, r[(k + 1) & 1]);
+          for (int q = 0; q < kBatch / kLdCols; ++q) {
+            if constexpr (kLdCols == 8) {
+              AKLR_TMEM_LD_8(batch_col(bi) + q * 8, (r[kDouble ? bi & 1 : 0] + q * 8));
             } else {
-              tc_fence_before_sync();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(&tmem_empty[tb]);
+              AKLR_TMEM_LD_16(batch_col(bi) + q * 16, (r[kDouble ? bi & 1 : 0] + q * 16));
             }
+          }
+        };
+        auto release = [&]() {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+#ifdef AKLR_GEMM_TIMING
+          if (warp == kFirstEpiWarp && lane == 0) TR(5);
+#endif
+        };
+        if (kDouble) issue(0);
 #pragma unroll
-            for (int i = 0; i < CH; i += 2) {
-              const int at = (gi * GC + k * CH + i) / 2;
-              acc2[at] = fma_f32x2(pack_f32x2(r[k & 1][i], r[k & 1][i + 1]), f2, acc2[at]);
-            }
+        for (int bi = 0; bi < NB; ++bi) {
+          if (!kDouble) issue(bi);
+          tc_wait_ld();
+          if (kDouble && bi + 1 < NB) issue(bi + 1);
+          if (bi + 1 == NB) release();
+          const uint64_t f2 = (bi * kBatch) / GC == 0 ? f2_lo : f2_hi;
+#pragma unroll
+          for (int i = 0; i < kBatch; i += 2) {
+            const int at = (bi * kBatch + i) / 2;
+            acc2[at] = fma_f32x2(pack_f32x2(r[kDouble ? bi & 1 : 0][i], r[kDouble ? bi & 1 : 0][i + 1]), f2, acc2[at]);
           }
         }
 #ifdef AKLR_GEMM_TIMING
@@ -361,7 +390,6 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
         acc[2 * i] = lo_f32(acc2[i]);
         acc[2 * i + 1] = hi_f32(acc2[i]);
       }
-      const int rid = rid_s[row];
       if (GATE_UP) {
         constexpr int HC = NH / 2;  // h channels of this thread
         float m = 0.0f;
@@ -393,25 +421,47 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
             *reinterpret_cast<uint4*>(dst + v * 16) = make_uint4(w[0], w[1], w[2], w[3]);
           }
         }
-      } else if (rid >= 0 && !bad) {
-        const float w = wgt_s[row];
-        uint8_t* dst = static_cast<uint8_t*>(p.out_rows) +
-                       (static_cast<size_t>(rid) * p.out_dim + j * 256 + cs * NH) * 2;
+      } else {
+        // A thread owns 128 channels of one token, so direct stores would write 16 bytes per lane
+        // at 32 different rows (half-filled sectors, one L1 wavefront per lane).  Each warp stages
+        // its 32 rows x 64 channels in shared memory (16-byte chunks XOR-swizzled by row) and
+        // writes 128 contiguous bytes of 4 rows per instruction instead.
+        uint8_t* stage = smem + L.off_out + (warp - kFirstEpiWarp) * (32 * kOutPassCols * 2);
+        epi_sync();  // rid_s of this tile is visible
 #pragma unroll
-        for (int v = 0; v < NH / 8; ++v) {
-          uint32_t o[4];
+        for (int pass = 0; pass < NH / kOutPassCols; ++pass) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const __nv_bfloat162 two = __floats2bfloat162_rn(acc[v * 8 + 2 * q] * w, acc[v * 8 + 2 * q + 1] * w);
-            o[q] = *reinterpret_cast<const uint32_t*>(&two);
+          for (int v = 0; v < kOutPassCols / 8; ++v) {
+            uint32_t o[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int i = pass * kOutPassCols + v * 8 + 2 * q;
+              const __nv_bfloat162 two = __floats2bfloat162_rn(acc[i] * route_w, acc[i + 1] * route_w);
+              o[q] = *reinterpret_cast<const uint32_t*>(&two);
+            }
+            *reinterpret_cast<uint4*>(stage + lane * (kOutPassCols * 2) + ((v ^ (lane & 7)) << 4)) =
+                make_uint4(o[0], o[1], o[2], o[3]);
           }
-          *reinterpret_cast<uint4*>(dst + v * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = 4 * i + (lane >> 3), c = lane & 7;  // row of this warp's 32, 16-byte chunk
+            const int rr = rid_s[quarter * 32 + r];
+            const uint4 val = *reinterpret_cast<const uint4*>(stage + r * (kOutPassCols * 2) + ((c ^ (r & 7)) << 4));
+            if (rr >= 0 && !bad)
+              *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out_rows) +
+                                        (static_cast<size_t>(rr) * p.out_dim + j * 256 + cs * NH +
+                                         pass * kOutPassCols + c * 8) * 2) = val;
+          }
+          __syncwarp();
         }
       }
     }
 #ifdef AKLR_GEMM_TIMING
-    if (blockIdx.x == 0 && warp == 2 && lane == 0)
+    if (blockIdx.x == 0 && warp == kFirstEpiWarp && lane == 0) {
       for (int i = 4; i <= 7; ++i) g_prefill_timing[GATE_UP][i] = tacc[i];
+      g_prefill_timing[GATE_UP][9] = clock64() - t_kernel;
+    }
 #endif
   }
 
@@ -430,6 +480,9 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
 }  // namespace
 
 #ifdef AKLR_GEMM_TIMING
+extern "C" int aklr_debug_read_prefill_trace(long long* host512) {
+  return cudaMemcpyFromSymbol(host512, g_prefill_trace, sizeof(g_prefill_trace)) == cudaSuccess ? 0 : -3;
+}
 extern "C" int aklr_debug_read_prefill_timing(long long* host32) {
   return cudaMemcpyFromSymbol(host32, g_prefill_timing, sizeof(g_prefill_timing)) == cudaSuccess ? 0 : -3;
 }
@@ -439,16 +492,16 @@ bool grouped_gemm_is_token_major(bool gate_up, int block_m, int out_dim) {
   return block_m == 128 && (gate_up || out_dim % 256 == 0);
 }
 
-int grouped_gemm_prefill_pick_stages(int k) {
+int grouped_gemm_prefill_pick_stages(bool gate_up) {
   for (int s = 6; s >= 2; --s)
-    if (prefill_layout(k, s).total + 1024 <= 227 * 1024) return s;
+    if (prefill_layout(gate_up, s).total + 1024 <= 227 * 1024) return s;
   return 0;
 }
 
 int launch_grouped_gemm_prefill(const GroupedGemmParams& p, bool gate_up, int sm_count, cudaStream_t stream) {
   if (p.k % 128 != 0 || p.block_m != 128 || p.max_blocks < 1 || p.stages < 2) return AKLR_ERR_UNSUPPORTED_SHAPE;
   if (gate_up ? (p.out_dim % 128 != 0) : (p.out_dim % 256 != 0)) return AKLR_ERR_UNSUPPORTED_SHAPE;
-  const size_t smem = static_cast<size_t>(prefill_layout(p.k, p.stages).total) + 1024;
+  const size_t smem = static_cast<size_t>(prefill_layout(gate_up, p.stages).total) + 1024;
   if (smem > 227 * 1024) return AKLR_ERR_UNSUPPORTED_SHAPE;
   const long long tiles = static_cast<long long>(p.max_blocks) * (gate_up ? p.out_dim / 128 : p.out_dim / 256);
   const int grid = static_cast<int>(tiles < sm_count ? tiles : sm_count);

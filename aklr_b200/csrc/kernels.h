@@ -85,7 +85,7 @@ int launch_grouped_gemm_down(const GroupedGemmParams& p, int sm_count, cudaStrea
 // token-major variant for full 128-token blocks (grouped_gemm_prefill.cu); its down projection
 // needs map_w built with a 256-row box
 bool grouped_gemm_is_token_major(bool gate_up, int block_m, int out_dim);
-int grouped_gemm_prefill_pick_stages(int k);
+int grouped_gemm_prefill_pick_stages(bool gate_up);
 int launch_grouped_gemm_prefill(const GroupedGemmParams& p, bool gate_up, int sm_count, cudaStream_t stream);
 size_t grouped_gemm_smem_bytes(bool gate_up, int block_m, int k, int stages);
 int grouped_gemm_pick_stages(bool gate_up, int block_m, int k);

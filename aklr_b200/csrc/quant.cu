@@ -78,36 +78,53 @@ __global__ void __launch_bounds__(256) gather_quant_fp8_kernel(GatherQuantParams
   }
 }
 
-// Rows already quantised elsewhere (the sender of an expert-parallel dispatch): copy row rid's codes
-// and scales into the expert-sorted table.  One 16-byte vector per thread.
+// Rows already quantised elsewhere (each token once, or by the sender of an expert-parallel
+// dispatch): copy row rid's codes and scales into the expert-sorted table.  A CTA moves four rows
+// at a time, every thread with four independent 16-byte loads in flight.
+constexpr int kGatherRows = 4;
+
 __global__ void __launch_bounds__(256) gather_rows_fp8_kernel(GatherQuantParams p) {
+  __shared__ int src_s[kGatherRows];
   const int vec_per_row = p.hidden >> 4;
   const int groups_per_row = p.hidden >> 7;
   const int n_rows = p.num_rows ? min(*p.num_rows, p.n_rows) : p.n_rows;
-  const int64_t total = static_cast<int64_t>(n_rows) * vec_per_row;
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-    const int row = static_cast<int>(i / vec_per_row);
-    const int v = static_cast<int>(i - static_cast<int64_t>(row) * vec_per_row);
-    const int rid = p.sorted_ids[row];
-    if (rid < 0) continue;
-    const int src = rid / p.routes_per_token;
-    *reinterpret_cast<uint4*>(p.q + static_cast<size_t>(row) * p.hidden + v * 16) =
-        *reinterpret_cast<const uint4*>(p.q_in + static_cast<size_t>(src) * p.hidden + v * 16);
-    if ((v & 7) == 0) {  // the thread holding the first 16 bytes of a 128-group moves its scale
-      const int grp = v >> 3;
-      p.scales[(static_cast<size_t>(row / p.block_m) * groups_per_row + grp) * p.block_m + row % p.block_m] =
-          p.scales_in[static_cast<size_t>(src) * groups_per_row + grp];
+  for (int row0 = blockIdx.x * kGatherRows; row0 < n_rows; row0 += gridDim.x * kGatherRows) {
+    if (threadIdx.x < kGatherRows) {
+      const int row = row0 + threadIdx.x;
+      const int rid = row < n_rows ? p.sorted_ids[row] : -1;
+      src_s[threadIdx.x] = rid < 0 ? -1 : rid / p.routes_per_token;
     }
+    __syncthreads();
+    int src[kGatherRows];
+#pragma unroll
+    for (int r = 0; r < kGatherRows; ++r) src[r] = src_s[r];
+    for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
+      uint4 val[kGatherRows];
+#pragma unroll
+      for (int r = 0; r < kGatherRows; ++r)
+        if (src[r] >= 0)
+          val[r] = __ldg(reinterpret_cast<const uint4*>(p.q_in + static_cast<size_t>(src[r]) * p.hidden) + v);
+#pragma unroll
+      for (int r = 0; r < kGatherRows; ++r)
+        if (src[r] >= 0)
+          reinterpret_cast<uint4*>(p.q + static_cast<size_t>(row0 + r) * p.hidden)[v] = val[r];
+    }
+    for (int i = threadIdx.x; i < kGatherRows * groups_per_row; i += blockDim.x) {
+      const int r = i / groups_per_row, grp = i - r * groups_per_row;
+      const int row = row0 + r;
+      if (src_s[r] >= 0)
+        p.scales[(static_cast<size_t>(row / p.block_m) * groups_per_row + grp) * p.block_m + row % p.block_m] =
+            __ldg(p.scales_in + static_cast<size_t>(src_s[r]) * groups_per_row + grp);
+    }
+    __syncthreads();
   }
 }
 
 int launch_gather_rows_fp8(const GatherQuantParams& p, cudaStream_t stream) {
   if (p.hidden % 128 != 0 || p.block_m < 1) return AKLR_ERR_UNSUPPORTED_SHAPE;
   if (p.n_rows == 0) return AKLR_OK;
-  const int64_t total = static_cast<int64_t>(p.n_rows) * (p.hidden / 16);
-  const int64_t blocks = (total + 255) / 256;
-  const int grid = static_cast<int>(blocks < 148 * 16 ? blocks : 148 * 16);
+  const int64_t blocks = (static_cast<int64_t>(p.n_rows) + kGatherRows - 1) / kGatherRows;
+  const int grid = static_cast<int>(blocks < 148 * 32 ? blocks : 148 * 32);
   gather_rows_fp8_kernel<<<grid, 256, 0, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
 }
