@@ -80,6 +80,7 @@ SIGNATURES = {
     "aklr_moe_read_status": (c_int32, [c_void_p, POINTER(c_int32), c_void_p]),
     "aklr_kernel_launch_count": (c_int64, []),
     "aklr_debug_force_weight_major": (c_int32, [c_int32]),
+    "aklr_debug_force_cta_pairs": (c_int32, [c_int32]),
     "aklr_profile_begin": (c_int32, [c_int32]),
     "aklr_profile_read": (c_int32, [c_int32, POINTER(c_float)]),
 }

@@ -27,6 +27,14 @@ StageProfile g_profile;
 std::atomic<long long> g_launches{0};
 // Tests set this to run full blocks through the weight-major kernel too (aklr_debug_force_weight_major).
 std::atomic<bool> g_force_swap_ab{false};
+// CTA-pair (cta_group::2) variant of the token-major kernels: 1 = whenever block_m is 128, else off
+// (aklr_debug_force_cta_pairs).  Off by default: it cuts a CTA's operand traffic by a third, but
+// the kernel is bound by the per-K-block fold in the epilogue, so it measured within 2% of the
+// single-CTA kernel at 8+ blocks per expert and slower where experts have one or two blocks (an
+// odd last block wastes half a pair).
+std::atomic<int> g_force_pairs{-1};
+
+bool use_cta_pairs(const aklr_moe_config&) { return g_force_pairs.load() > 0; }
 
 void profile_mark(cudaStream_t stream, int slot, int stage) {
   if (g_profile.on && slot >= 0) cudaEventRecord(g_profile.events[slot * (kStages + 1) + stage], stream);
@@ -174,7 +182,7 @@ void layout_of(const aklr_moe_config& c, aklr_moe_workspace_layout* l) {
   l->topk_ids = take(routes * 4, 256);
   l->topk_weights = take(routes * 4, 256);
   l->sorted_ids = take(cap * 4, 256);
-  l->block_expert = take(max_blocks * 4, 256);
+  l->block_expert = take(max_blocks * 8, 256);  // block -> expert, then the table of block pairs
   l->counts = take(experts * 4, 256);
   l->chunk_hist = take((chunks > 0 ? chunks : 1) * experts * 4, 256);
   l->xq = take(cap * c.hidden, 1024);
@@ -218,6 +226,11 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   ap.n_experts = experts;
   ap.n_experts_global = n_experts_global;
   ap.block_m = l.block_m;
+  const bool pairs = l.block_m == 128 && !g_force_swap_ab && use_cta_pairs(c) &&
+                     grouped_gemm_is_token_major(true, l.block_m, c.inter) &&
+                     grouped_gemm_is_token_major(false, l.block_m, c.hidden);
+  int32_t* pair_table = block_expert + l.max_blocks;  // second half of the block table's space
+  if (pairs) ap.pair_table = pair_table;
   int rc = launch_align(ap, stream);
   if (rc) return fail(rc, "moe_align launch failed");
   g_launches += routes <= 4096 ? 1 : 3;
@@ -281,16 +294,17 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   g1.block_m = l.block_m;
   g1.max_blocks = l.max_blocks;
   const bool tm1 = grouped_gemm_is_token_major(true, l.block_m, c.inter) && !g_force_swap_ab;
-  g1.stages = tm1 ? grouped_gemm_prefill_pick_stages(true) : grouped_gemm_pick_stages(true, l.block_m, c.hidden);
+  g1.pair_table = pairs ? pair_table : nullptr;
+  g1.stages = tm1 ? grouped_gemm_prefill_pick_stages(true, pairs) : grouped_gemm_pick_stages(true, l.block_m, c.hidden);
   if (g1.stages < 2) return fail(AKLR_ERR_UNSUPPORTED_SHAPE, "hidden=%d needs more shared memory than one SM has", c.hidden);
-  rc = tm1 ? launch_grouped_gemm_prefill(g1, true, sms, stream) : launch_grouped_gemm_gate_up(g1, sms, stream);
+  rc = tm1 ? launch_grouped_gemm_prefill(g1, true, pairs, sms, stream) : launch_grouped_gemm_gate_up(g1, sms, stream);
   if (rc) return fail(rc, "gate_up grouped GEMM launch failed");
   g_launches += 1;
   profile_mark(stream, slot, 4);
 
   GroupedGemmParams g2{};
   const bool tm2 = grouped_gemm_is_token_major(false, l.block_m, c.hidden) && !g_force_swap_ab;
-  rc = make_map_u8(&g2.map_w, w2, static_cast<uint64_t>(experts) * c.hidden, c.inter, tm2 ? 256 : 128);
+  rc = make_map_u8(&g2.map_w, w2, static_cast<uint64_t>(experts) * c.hidden, c.inter, tm2 && !pairs ? 256 : 128);
   if (rc) return rc;
   rc = make_map_u8(&g2.map_x, ws + l.hq, l.capacity, c.inter, l.block_m);
   if (rc) return rc;
@@ -307,9 +321,10 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   g2.rows_per_expert = c.hidden;
   g2.block_m = l.block_m;
   g2.max_blocks = l.max_blocks;
-  g2.stages = tm2 ? grouped_gemm_prefill_pick_stages(false) : grouped_gemm_pick_stages(false, l.block_m, c.inter);
+  g2.pair_table = pairs ? pair_table : nullptr;
+  g2.stages = tm2 ? grouped_gemm_prefill_pick_stages(false, pairs) : grouped_gemm_pick_stages(false, l.block_m, c.inter);
   if (g2.stages < 2) return fail(AKLR_ERR_UNSUPPORTED_SHAPE, "inter=%d needs more shared memory than one SM has", c.inter);
-  rc = tm2 ? launch_grouped_gemm_prefill(g2, false, sms, stream) : launch_grouped_gemm_down(g2, sms, stream);
+  rc = tm2 ? launch_grouped_gemm_prefill(g2, false, pairs, sms, stream) : launch_grouped_gemm_down(g2, sms, stream);
   if (rc) return fail(rc, "down grouped GEMM launch failed");
   g_launches += 1;
   profile_mark(stream, slot, 5);
@@ -817,6 +832,11 @@ int aklr_moe_read_status(const void* workspace, int32_t* host_status, void* stre
 }
 
 int64_t aklr_kernel_launch_count(void) { return g_launches.load(); }
+
+int aklr_debug_force_cta_pairs(int32_t mode) {
+  g_force_pairs = mode < 0 ? -1 : (mode != 0 ? 1 : 0);
+  return AKLR_OK;
+}
 
 int aklr_debug_force_weight_major(int32_t on) {
   g_force_swap_ab = on != 0;

@@ -19,18 +19,26 @@
 // warpgroup gives its registers to the epilogue (setmaxnreg 40 / 232): 128 accumulators + 64
 // staging registers per epilogue thread do not fit the 168 an even split allows.
 //
-// What bounds it, measured on B200 by taking parts out (AKLR_EXP_NOMMA / AKLR_EXP_NODRAIN leave
-// out the MMAs / the TMEM loads and folds; both out = TMA ring + barriers only): the TMA ring
-// alone takes 570 ns per K-block per SM with L2-resident weights (48 KB per K-block -> 12.4 TB/s
-// L2 -> shared memory over 148 SMs) and 670 ns when the weights stream from HBM; the full kernel
-// 670 / 790 ns.  So the tile's operand traffic, not the tensor core (4 MMAs = 512 cycles) or the
-// epilogue, is the limit; the epilogue is hidden as long as (i) the MMA thread's loop is lean --
-// one commit per K-block, no divisions, descriptors carried forward -- because a lone thread pays
-// full latency per instruction, (ii) scales are prefetched from global memory two K-blocks ahead
-// instead of staged per tile, (iii) a batch of tcgen05.ld (4 x 8 columns) is in flight while the
-// previous one is folded with packed FMAs.  Persistent CTAs, TMA SWIZZLE_128B ring, two
-// 256-column TMEM partial buffers, no cluster, no multicast, bounded waits.
+// What bounds it, measured on B200 by taking parts out (-DAKLR_EXP_NOMMA: no MMAs,
+// -DAKLR_EXP_NOTMA: no operand loads): the epilogue's fold alone -- no loads, no MMAs -- already
+// takes ~510 ns per K-block per SM, loads added 570 ns (L2-resident weights) / 670 ns (weights
+// from HBM), the full kernel 670 / 790 ns, against 290 ns for the four MMAs.  Per K-block an
+// epilogue warp makes four round trips of tcgen05.ld (latency-bound, and tcgen05.wait::ld waits for
+// every load in flight, so only one batch overlaps the packed FMAs of the previous one) under a
+// register budget that allows 64 staging registers next to 128 accumulators.  What helped: one
+// commit per K-block and a lean MMA-issue loop (a lone thread pays full latency per instruction;
+// no divisions, descriptors carried forward), scales prefetched from global memory two K-blocks
+// ahead instead of staged per tile, register hand-over.  What did not: per-half hand-offs (two
+// N=128 MMA groups; 20% slower -- every extra commit and barrier round costs more than the
+// overlap gains), issuing the next K-block's first batch early, 16 epilogue warps, larger or
+// single-buffered load batches, CTA pairs (below).  Persistent CTAs, TMA SWIZZLE_128B ring,
+// two 256-column TMEM partial buffers, no multicast loads, bounded waits.
 #include <cfloat>
+#include <cstdio>
+#include <cstdlib>
+#include <map>
+#include <mutex>
+#include <utility>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -69,10 +77,8 @@ constexpr int kBM = 128;                 // tokens per block
 constexpr int kBN = 256;                 // weight rows per tile
 constexpr int kABytes = kBM * 128;       // token tile of one K-block
 constexpr int kBBytes = kBN * 128;       // weight tile of one K-block
-constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kBatch = 32;                // TMEM columns one epilogue thread loads per round
-constexpr bool kDouble = true;           // next round's loads in flight while this one is folded
-constexpr int kLdCols = 8;               // columns per tcgen05.ld
+__host__ __device__ constexpr int stage_bytes(bool pair) { return kABytes + (pair ? kBBytes / 2 : kBBytes); }  // a CTA of a pair holds half the weight rows
+constexpr int kBatch = 32;                // TMEM columns one epilogue thread loads per round (as 4 x 8)
 
 struct PrefillLayout {
   int off_out, off_rid, off_wmax, off_bars, total;
@@ -80,9 +86,9 @@ struct PrefillLayout {
 
 constexpr int kOutPassCols = 64;  // down: channels per thread staged per pass (128 bytes per row)
 
-__host__ __device__ inline PrefillLayout prefill_layout(bool gate_up, int stages) {
+__host__ __device__ inline PrefillLayout prefill_layout(bool gate_up, bool pair, int stages) {
   PrefillLayout l;
-  l.off_out = stages * kStageBytes;  // down: per epilogue warp 32 rows x 128 bytes of bf16 output
+  l.off_out = stages * stage_bytes(pair);  // down: per epilogue warp 32 rows x 128 bytes of bf16 output
   l.off_rid = l.off_out + (gate_up ? 0 : kEpiWarps * 32 * kOutPassCols * 2);
   l.off_wmax = l.off_rid + kBM * 4;  // float[kCS][128] amax per column split (gate_up)
   l.off_bars = l.off_wmax + kCS * kBM * 4;
@@ -118,15 +124,23 @@ __device__ __forceinline__ bool epi_any(int flag) {
   return any != 0;
 }
 
-template <bool GATE_UP>
+// PAIR: two CTAs of a cluster work on two token blocks of ONE expert with one M=256 MMA
+// (cta_group::2).  Each CTA loads its own 128 tokens and HALF of the tile's 256 weight rows (the
+// tensor cores read the other half from the partner's shared memory), so a K-block costs 32 KB of
+// L2 -> shared-memory traffic per CTA instead of 48 KB.  The even CTA issues the MMAs; TMA bytes of
+// both CTAs are counted on its "full" barrier, its commit arrives on the "empty" barrier of both,
+// and both CTAs' epilogue warps arrive on its "tmem_empty" barrier.  An expert's odd last block
+// runs with the odd CTA repeating the same tokens and writing nothing.
+template <bool GATE_UP, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const __grid_constant__ GroupedGemmParams p) {
   constexpr int NH = kBN / kCS;   // accumulator columns per epilogue thread
+  constexpr int kStageBytes = stage_bytes(PAIR);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int KB = p.k >> 7;
   const int S = p.stages;
-  const PrefillLayout L = prefill_layout(GATE_UP, S);
+  const PrefillLayout L = prefill_layout(GATE_UP, PAIR, S);
   int* rid_s = reinterpret_cast<int*>(smem + L.off_rid);
   float* wmax = reinterpret_cast<float*>(smem + L.off_wmax);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.off_bars);
@@ -136,29 +150,47 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int nb = *p.num_blocks;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;  // which CTA of the pair
+  // tiles are dealt to CTAs (or CTA pairs) round-robin
+  const int worker = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int n_workers = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  int nb = PAIR ? p.num_blocks[2] : p.num_blocks[0];  // units: runs of <= 2 blocks, or blocks
   if (nb > p.max_blocks) nb = p.max_blocks;
   // gate_up: one tile per 128 intermediate channels (128 gate + 128 up rows); down: per 256 channels
   const int tiles_per_block = GATE_UP ? (p.out_dim >> 7) : (p.out_dim >> 8);
   const int total_tiles = nb * tiles_per_block;
+  // unit u -> this CTA's token block and whether it is a real one
+  auto block_of = [&](int u, bool* live) -> int {
+    if (!PAIR) { *live = true; return u; }
+    const uint32_t entry = static_cast<uint32_t>(p.pair_table[u]);
+    const bool second = (entry >> 31) != 0;
+    *live = rank == 0 || second;
+    return static_cast<int>(entry & 0x7FFFFFFFu) + (second ? static_cast<int>(rank) : 0);
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    for (int i = 0; i < 2; ++i) mbar_init(&tmem_empty[i], kEpiWarps);  // buffer = K-block parity
+    for (int i = 0; i < 2; ++i) mbar_init(&tmem_empty[i], PAIR ? 2 * kEpiWarps : kEpiWarps);  // buffer = K-block parity
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&p.map_w);
     tma_prefetch_desc(&p.map_x);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_ptr, 512);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(tmem_ptr, 512);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_ptr, 512);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (PAIR) cluster_sync_all();  // the partner's barriers exist before anything arrives on them
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr;
 
@@ -172,20 +204,38 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
       int s = 0;        // ring position and the parity of its current use
       uint32_t ph = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const int b = t / tiles_per_block, j = t - b * tiles_per_block;
+      const uint32_t full0 = PAIR ? mapa_shared(smem_u32(full), 0) : 0u;  // the even CTA's "full" barriers
+      for (int t = worker; t < total_tiles && ok; t += n_workers) {
+        const int u = t / tiles_per_block, j = t - u * tiles_per_block;
+        bool live;
+        const int b = block_of(u, &live);
         const int e = p.block_expert[b];
         const int w_row = e * p.rows_per_expert + (GATE_UP ? j * 128 : j * 256);
         for (int kb = 0; kb < KB; ++kb) {
-          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 11)) { ok = false; break; }
+          if (!mbar_wait<PAIR>(&empty[s], ph ^ 1, abort_flag, p.status, 11)) { ok = false; break; }
           uint8_t* st = smem + s * kStageBytes;
-          mbar_expect_tx(&full[s], kStageBytes);
-          tma_load_2d(st, &p.map_x, &full[s], kb * 128, b * kBM);
-          if (GATE_UP) {  // gate rows, then the matching up rows: one 256-row K-major operand
-            tma_load_2d(st + kABytes, &p.map_w, &full[s], kb * 128, w_row);
-            tma_load_2d(st + kABytes + kBBytes / 2, &p.map_w, &full[s], kb * 128, w_row + p.out_dim);
+#ifdef AKLR_EXP_NOTMA
+          if (rank == 0) mbar_arrive(&full[s]);
+          (void)st;
+          if (++s == S) { s = 0; ph ^= 1; }
+          continue;
+#endif
+          if (PAIR) {
+            if (rank == 0) mbar_expect_tx(&full[s], 2 * kStageBytes);  // both CTAs' bytes
+            const uint32_t bar = full0 + s * 8;
+            tma_load_2d_pair(st, &p.map_x, bar, kb * 128, b * kBM);
+            // even CTA: gate rows (down: first 128 channels); odd CTA: up rows (down: the next 128)
+            tma_load_2d_pair(st + kABytes, &p.map_w, bar, kb * 128,
+                             w_row + static_cast<int>(rank) * (GATE_UP ? p.out_dim : 128));
           } else {
-            tma_load_2d(st + kABytes, &p.map_w, &full[s], kb * 128, w_row);  // box of 256 rows
+            mbar_expect_tx(&full[s], kStageBytes);
+            tma_load_2d(st, &p.map_x, &full[s], kb * 128, b * kBM);
+            if (GATE_UP) {  // gate rows, then the matching up rows: one 256-row K-major operand
+              tma_load_2d(st + kABytes, &p.map_w, &full[s], kb * 128, w_row);
+              tma_load_2d(st + kABytes + kBBytes / 2, &p.map_w, &full[s], kb * 128, w_row + p.out_dim);
+            } else {
+              tma_load_2d(st + kABytes, &p.map_w, &full[s], kb * 128, w_row);  // box of 256 rows
+            }
           }
           if (++s == S) { s = 0; ph ^= 1; }
         }
@@ -193,7 +243,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer --------------------------------------------
-    if (lane == 0) {
+    if (lane == 0 && rank == 0) {
       // This thread is alone in its warp, so every instruction here costs its full latency:
       // the loop carries ring positions and descriptors forward instead of recomputing them.
       uint32_t it = 0;
@@ -205,18 +255,20 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
 #ifdef AKLR_GEMM_TIMING
       long long tacc[16] = {0};
 #endif
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = worker; t < total_tiles && ok; t += n_workers) {
         for (int kb = 0; kb < KB; ++kb, ++it) {
           bool got;
-          PT(1, got = mbar_wait(&full[s], ph, abort_flag, p.status, 12));
+          PT(1, got = mbar_wait<PAIR>(&full[s], ph, abort_flag, p.status, 12));
           if (!got) { ok = false; break; }
 #ifdef AKLR_GEMM_TIMING
           TR(0);
 #endif
-          // One N=256 MMA per 32 K bytes into this K-block's TMEM buffer; a single commit per
+          // One N=256 MMA per 32 K bytes into this K-block's TMEM buffer and a single commit per
           // K-block: the barrier that frees the shared-memory stage also tells the epilogue that
-          // the partial is complete.
-          PT(2, got = mbar_wait(&tmem_empty[buf], bph ^ 1, abort_flag, p.status, 13));
+          // the partial is complete.  (Two N=128 groups with their own hand-offs, so that the
+          // epilogue could start on the first half earlier, measured 20% slower: every extra commit
+          // and barrier round costs more than the overlap gains.)
+          PT(2, got = mbar_wait<PAIR>(&tmem_empty[buf], bph ^ 1, abort_flag, p.status, 13));
           if (!got) { ok = false; break; }
 #ifdef AKLR_GEMM_TIMING
           TR(1);
@@ -227,14 +279,18 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
           const uint32_t d = tmem_base + buf * 256;
 #ifndef AKLR_EXP_NOMMA
 #pragma unroll
-          for (int k = 0; k < 4; ++k) umma_f8f6f4(d, da + 2 * k, db + 2 * k, umma_idesc_e4m3(256), k > 0);
+          for (int k = 0; k < 4; ++k) {
+            if (PAIR) umma_f8f6f4_pair(d, da + 2 * k, db + 2 * k, umma_idesc_e4m3(256, 256), k > 0);
+            else umma_f8f6f4(d, da + 2 * k, db + 2 * k, umma_idesc_e4m3(256), k > 0);
+          }
 #endif
 #ifdef AKLR_GEMM_TIMING
           TR(2);
           tacc[3] += clock64() - t_issue;
           const long long t_c2 = clock64();
 #endif
-          tc_commit(&empty[s]);
+          if (PAIR) tc_commit_pair(&empty[s], 3);
+          else tc_commit(&empty[s]);
 #ifdef AKLR_GEMM_TIMING
           TR(3);
           tacc[12] += clock64() - t_c2;
@@ -271,13 +327,16 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
     long long t_mark = clock64();
     const long long t_kernel = t_mark;
 #endif
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+    const uint32_t tmem_empty0 = PAIR ? mapa_shared(smem_u32(tmem_empty), 0) : 0u;  // in the even CTA
+    for (int t = worker; t < total_tiles; t += n_workers) {
 #ifdef AKLR_GEMM_TIMING
       tacc[7] += clock64() - t_mark;
       t_mark = clock64();
 #endif
       if (epi_any(*abort_flag)) break;
-      const int b = t / tiles_per_block, j = t - b * tiles_per_block;
+      const int u = t / tiles_per_block, j = t - u * tiles_per_block;
+      bool live;  // false: the odd CTA of a pair whose expert has no second block
+      const int b = block_of(u, &live);
       const int e = p.block_expert[b];
       // Scales come straight from global memory (L2 hits: the quantising kernel wrote them just
       // before), two K-blocks ahead of their use; nothing is staged per tile.
@@ -292,7 +351,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
       sx_q[2] = KB > 1 ? __ldg(xs + kBM) : 0.0f;
       wl_q[2] = KB > 1 ? __ldg(ws_lo + 1) : 0.0f;
       wh_q[2] = GATE_UP ? (KB > 1 ? __ldg(ws_hi + 1) : 0.0f) : wl_q[2];
-      const int rid = __ldg(p.sorted_ids + b * kBM + row);
+      const int rid = live ? __ldg(p.sorted_ids + b * kBM + row) : -1;
       float route_w = 0.0f;
       // (the barrier inside epi_any above also means the previous tile's output pass is done with rid_s)
       if (!GATE_UP && cs == 0) rid_s[row] = rid;
@@ -306,6 +365,22 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
 #pragma unroll
       for (int i = 0; i < NH / 2; ++i) acc2[i] = 0ull;
 
+      // gate_up: this warp's NH/2 gate columns (weight rows 0..127 of the tile), then the matching
+      // up columns (rows 128..255).  down: NH channels, all inside one 128-row scale block.
+      constexpr int GC = GATE_UP ? NH / 2 : NH;  // consecutive TMEM columns before a jump
+      constexpr int NB = NH / kBatch;            // load batches per K-block
+      // tcgen05.ld is latency-bound per warp and tcgen05.wait::ld waits for every load in flight,
+      // so the pattern is: one batch (4 x 8 columns) in flight while the previous one is folded.
+      // (Issuing the next K-block's first batch before the last fold of this one measured slower.)
+      uint32_t r[2][kBatch];
+      auto issue = [&](int buffer, int bi) {
+        const uint32_t tcol = tmem_base + lane_addr + buffer * 256 + (GATE_UP ? cs * GC : cs * NH);
+        const int c = bi * kBatch;
+        const uint32_t col = GATE_UP ? tcol + (c / GC) * 128 + (c % GC) : tcol + c;
+#pragma unroll
+        for (int q = 0; q < kBatch / 8; ++q) AKLR_TMEM_LD_8(col + q * 8, (r[bi & 1] + q * 8));
+      };
+
       for (int kb = 0; kb < KB; ++kb, ++it) {
         const int buf = it & 1;
         sx_q[0] = sx_q[1]; sx_q[1] = sx_q[2];
@@ -317,63 +392,42 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
           wh_q[2] = GATE_UP ? __ldg(ws_hi + kb + 2) : wl_q[2];
         }
         if (!GATE_UP && kb == (KB > 2 ? 2 : KB - 1)) route_w = rid >= 0 ? __ldg(p.topk_weights + rid) : 0.0f;
-        const float sx = sx_q[0];
-        // gate_up: this warp's NH/2 gate columns (weight rows 0..127 of the tile), then the matching
-        // up columns (rows 128..255).  down: NH channels, all inside one 128-row scale block.
-        constexpr int GC = GATE_UP ? NH / 2 : NH;  // consecutive TMEM columns before a jump
-        constexpr int NB = NH / kBatch;            // load batches per K-block
-        const float f_lo = sx * wl_q[0];
-        const float f_hi = sx * wh_q[0];
+        const float f_lo = sx_q[0] * wl_q[0];
+        const float f_hi = sx_q[0] * wh_q[0];
         const uint64_t f2_lo = pack_f32x2(__float_as_uint(f_lo), __float_as_uint(f_lo));
         const uint64_t f2_hi = pack_f32x2(__float_as_uint(f_hi), __float_as_uint(f_hi));
-        const uint32_t tcol = tmem_base + lane_addr + buf * 256 + (GATE_UP ? cs * GC : cs * NH);
-        auto batch_col = [&](int bi) -> uint32_t {  // TMEM address of batch bi
-          const int c = bi * kBatch;
-          return GATE_UP ? tcol + (c / GC) * 128 + (c % GC) : tcol + c;
-        };
         bool got;
         // MMA(it) complete = the "empty" barrier of its shared-memory stage completing phase it / S
-        PT(4, got = mbar_wait(&empty[ring], ring_ph, abort_flag, p.status, 14));
+        PT(4, got = mbar_wait<PAIR>(&empty[ring], ring_ph, abort_flag, p.status, 14));
         if (++ring == S) { ring = 0; ring_ph ^= 1; }
+        if (!got) bad = true;
+        tc_fence_after_sync();
+        issue(buf, 0);
 #ifdef AKLR_GEMM_TIMING
         long long t_work = clock64();
         if (warp == kFirstEpiWarp && lane == 0) TR(4);
 #endif
-        if (!got) bad = true;
-        tc_fence_after_sync();
-        // tcgen05.ld is latency-bound per warp (an x8 load returns after ~50 cycles, four of them
-        // issued back to back after ~60): keep a whole batch in flight, fold the previous one.
-        uint32_t r[kDouble ? 2 : 1][kBatch];
-        auto issue = [&](int bi) {
-#pragma unroll
-          for (int q = 0; q < kBatch / kLdCols; ++q) {
-            if constexpr (kLdCols == 8) {
-              AKLR_TMEM_LD_8(batch_col(bi) + q * 8, (r[kDouble ? bi & 1 : 0] + q * 8));
-            } else {
-              AKLR_TMEM_LD_16(batch_col(bi) + q * 16, (r[kDouble ? bi & 1 : 0] + q * 16));
-            }
-          }
-        };
-        auto release = [&]() {
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&tmem_empty[buf]);
-#ifdef AKLR_GEMM_TIMING
-          if (warp == kFirstEpiWarp && lane == 0) TR(5);
-#endif
-        };
-        if (kDouble) issue(0);
 #pragma unroll
         for (int bi = 0; bi < NB; ++bi) {
-          if (!kDouble) issue(bi);
           tc_wait_ld();
-          if (kDouble && bi + 1 < NB) issue(bi + 1);
-          if (bi + 1 == NB) release();
+          if (bi + 1 < NB) {
+            issue(buf, bi + 1);
+          } else {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+              if (PAIR) mbar_arrive_cluster(tmem_empty0 + buf * 8);
+              else mbar_arrive(&tmem_empty[buf]);
+            }
+#ifdef AKLR_GEMM_TIMING
+            if (warp == kFirstEpiWarp && lane == 0) TR(5);
+#endif
+          }
           const uint64_t f2 = (bi * kBatch) / GC == 0 ? f2_lo : f2_hi;
 #pragma unroll
           for (int i = 0; i < kBatch; i += 2) {
             const int at = (bi * kBatch + i) / 2;
-            acc2[at] = fma_f32x2(pack_f32x2(r[kDouble ? bi & 1 : 0][i], r[kDouble ? bi & 1 : 0][i + 1]), f2, acc2[at]);
+            acc2[at] = fma_f32x2(pack_f32x2(r[bi & 1][i], r[bi & 1][i + 1]), f2, acc2[at]);
           }
         }
 #ifdef AKLR_GEMM_TIMING
@@ -471,9 +525,11 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
     const uint64_t start = global_timer_ns();
     while (global_timer_ns() - start < 200000ull) __nanosleep(1000);
   }
+  if (PAIR) cluster_sync_all();  // the partner is done with this CTA's shared memory and barriers
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 512);
+    if (PAIR) tmem_dealloc_pair(tmem_base, 512);
+    else tmem_dealloc(tmem_base, 512);
   }
 }
 
@@ -492,25 +548,77 @@ bool grouped_gemm_is_token_major(bool gate_up, int block_m, int out_dim) {
   return block_m == 128 && (gate_up || out_dim % 256 == 0);
 }
 
-int grouped_gemm_prefill_pick_stages(bool gate_up) {
-  for (int s = 6; s >= 2; --s)
-    if (prefill_layout(gate_up, s).total + 1024 <= 227 * 1024) return s;
+int grouped_gemm_prefill_pick_stages(bool gate_up, bool pair) {
+  for (int s = 8; s >= 2; --s)
+    if (prefill_layout(gate_up, pair, s).total + 1024 <= 227 * 1024) return s;
   return 0;
 }
 
-int launch_grouped_gemm_prefill(const GroupedGemmParams& p, bool gate_up, int sm_count, cudaStream_t stream) {
+namespace {
+// CTA pairs that can be resident at once (a pair needs two SMs of one cluster-capable group)
+template <typename Kernel>
+int max_active_pairs(Kernel kernel, size_t smem) {
+  static std::mutex mu;
+  static std::map<std::pair<const void*, int>, int> cache;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  std::lock_guard<std::mutex> lock(mu);
+  const auto key = std::make_pair(reinterpret_cast<const void*>(kernel), dev);
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(2, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) n = 0;
+  if (getenv("AKLR_DEBUG_PAIRS")) fprintf(stderr, "max active CTA pairs: %d (smem %zu)\n", n, smem);
+  cache[key] = n;
+  return n;
+}
+}  // namespace
+
+int launch_grouped_gemm_prefill(const GroupedGemmParams& p, bool gate_up, bool pair, int sm_count, cudaStream_t stream) {
   if (p.k % 128 != 0 || p.block_m != 128 || p.max_blocks < 1 || p.stages < 2) return AKLR_ERR_UNSUPPORTED_SHAPE;
   if (gate_up ? (p.out_dim % 128 != 0) : (p.out_dim % 256 != 0)) return AKLR_ERR_UNSUPPORTED_SHAPE;
-  const size_t smem = static_cast<size_t>(prefill_layout(gate_up, p.stages).total) + 1024;
+  if (pair && !p.pair_table) return AKLR_ERR_BAD_ARGUMENT;
+  const size_t smem = static_cast<size_t>(prefill_layout(gate_up, pair, p.stages).total) + 1024;
   if (smem > 227 * 1024) return AKLR_ERR_UNSUPPORTED_SHAPE;
   const long long tiles = static_cast<long long>(p.max_blocks) * (gate_up ? p.out_dim / 128 : p.out_dim / 256);
-  const int grid = static_cast<int>(tiles < sm_count ? tiles : sm_count);
   auto run = [&](auto kernel) {
     if (ensure_max_dynamic_smem(reinterpret_cast<const void*>(kernel)) != AKLR_OK) return AKLR_ERR_CUDA;
-    kernel<<<grid, kThreads, smem, stream>>>(p);
-    return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+    if (!pair) {
+      const int grid = static_cast<int>(tiles < sm_count ? tiles : sm_count);
+      kernel<<<grid, kThreads, smem, stream>>>(p);
+      return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+    }
+    int pairs = max_active_pairs(kernel, smem);
+    if (pairs < 1) return AKLR_ERR_CUDA;
+    if (pairs > sm_count / 2) pairs = sm_count / 2;
+    if (tiles < pairs) pairs = static_cast<int>(tiles);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * pairs, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, p) == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
   };
-  return gate_up ? run(grouped_gemm_prefill_kernel<true>) : run(grouped_gemm_prefill_kernel<false>);
+  if (pair) return gate_up ? run(grouped_gemm_prefill_kernel<true, true>) : run(grouped_gemm_prefill_kernel<false, true>);
+  return gate_up ? run(grouped_gemm_prefill_kernel<true, false>) : run(grouped_gemm_prefill_kernel<false, false>);
 }
 
 }  // namespace aklr

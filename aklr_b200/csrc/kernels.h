@@ -29,7 +29,9 @@ struct AlignParams {
   int32_t* sorted_ids;        // [capacity] route ids, -1 in padding
   int32_t* block_expert;      // [max_blocks]
   int32_t* counts;            // [n_experts]
-  int32_t* num_blocks;        // [2]: blocks used, rows used (= blocks * block_m)
+  int32_t* num_blocks;        // [2]: blocks used, rows used (= blocks * block_m); [3] with pair_table: + pairs
+  int32_t* pair_table;        // optional [max_blocks]: first block of every run of <= 2 blocks of one
+                              // expert; bit 31 set when the second block exists
   int32_t* chunk_hist;        // [ceil(n_routes/1024) * n_experts] scratch
   int n_routes, n_experts, n_experts_global, block_m;
 };
@@ -67,7 +69,8 @@ struct GroupedGemmParams {
   const float* x_scale;        // [max_blocks, k/128, block_m]
   const int32_t* sorted_ids;   // [capacity]
   const int32_t* block_expert; // [max_blocks]
-  const int32_t* num_blocks;   // device count
+  const int32_t* num_blocks;   // device count ([2] = number of block pairs)
+  const int32_t* pair_table;   // CTA-pair kernel only
   const float* topk_weights;   // [n_routes] (down projection only)
   uint8_t* out_q;              // gate_up: [capacity, inter] e4m3
   float* out_scale;            // gate_up: [max_blocks, inter/128, block_m]
@@ -85,8 +88,10 @@ int launch_grouped_gemm_down(const GroupedGemmParams& p, int sm_count, cudaStrea
 // token-major variant for full 128-token blocks (grouped_gemm_prefill.cu); its down projection
 // needs map_w built with a 256-row box
 bool grouped_gemm_is_token_major(bool gate_up, int block_m, int out_dim);
-int grouped_gemm_prefill_pick_stages(bool gate_up);
-int launch_grouped_gemm_prefill(const GroupedGemmParams& p, bool gate_up, int sm_count, cudaStream_t stream);
+// pair: two CTAs of a cluster share one M=256 MMA over two token blocks of an expert (needs
+// pair_table; map_w with a 128-row box for both projections)
+int grouped_gemm_prefill_pick_stages(bool gate_up, bool pair);
+int launch_grouped_gemm_prefill(const GroupedGemmParams& p, bool gate_up, bool pair, int sm_count, cudaStream_t stream);
 size_t grouped_gemm_smem_bytes(bool gate_up, int block_m, int k, int stages);
 int grouped_gemm_pick_stages(bool gate_up, int block_m, int k);
 

@@ -246,6 +246,25 @@ __device__ void plan_blocks(const AlignParams& p, const int* total, int* base, i
     p.num_blocks[0] = scratch[tid];
     p.num_blocks[1] = scratch[tid] * p.block_m;
   }
+  int pair_running = 0;  // runs of <= 2 blocks before this thread's experts
+  if (p.pair_table) {
+    __syncthreads();
+    int local_pairs = 0;
+    for (int i = 0; i < per; ++i) {
+      const int e = tid * per + i;
+      if (e < p.n_experts) local_pairs += ((total[e] + p.block_m - 1) / p.block_m + 1) / 2;
+    }
+    scratch[tid] = local_pairs;
+    __syncthreads();
+    for (int off = 1; off < nt; off <<= 1) {
+      const int v = tid >= off ? scratch[tid - off] : 0;
+      __syncthreads();
+      scratch[tid] += v;
+      __syncthreads();
+    }
+    pair_running = scratch[tid] - local_pairs;
+    if (tid == nt - 1) p.num_blocks[2] = scratch[tid];
+  }
   for (int i = 0; i < per; ++i) {
     const int e = tid * per + i;
     if (e < p.n_experts) {
@@ -254,6 +273,10 @@ __device__ void plan_blocks(const AlignParams& p, const int* total, int* base, i
       base[e] = running * p.block_m;
       p.counts[e] = c;
       for (int b = 0; b < nb; ++b) p.block_expert[running + b] = e;
+      if (p.pair_table) {
+        for (int b = 0; b < nb; b += 2)
+          p.pair_table[pair_running++] = (running + b) | (b + 1 < nb ? static_cast<int>(0x80000000u) : 0);
+      }
       for (int r = c; r < nb * p.block_m; ++r) p.sorted_ids[running * p.block_m + r] = -1;
       running += nb;
     }

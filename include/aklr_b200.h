@@ -220,6 +220,9 @@ int64_t aklr_kernel_launch_count(void);
 /* Test aid: non-zero makes full 128-token blocks use the weight-major grouped GEMM (the decode
  * kernel) instead of the token-major one, so both can be checked on the same inputs. */
 int aklr_debug_force_weight_major(int32_t on);
+/* Token-major kernels as CTA pairs (cta_group::2: two token blocks of an expert per pair, each CTA
+ * loading half of the weight tile): mode 1 = whenever block_m is 128; 0 or negative = off (default). */
+int aklr_debug_force_cta_pairs(int32_t mode);
 int aklr_profile_begin(int32_t max_calls);
 int aklr_profile_read(int32_t call, float* stage_ms);
 

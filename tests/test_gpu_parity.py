@@ -391,6 +391,45 @@ def test_token_major_and_weight_major_kernels_agree(golden):
     assert close["sqnr_db"] > 45.0, close
 
 
+def test_cta_pair_kernels_match_the_single_cta_kernels(golden):
+    """The CTA-pair (cta_group::2) grouped GEMMs take two token blocks of an expert per pair and read
+    half of the weight tile from each CTA; per element the arithmetic is the single-CTA kernel's.
+    Token counts are chosen so experts end up with one, two and three blocks (odd runs included)."""
+    from aklr_b200 import _lib
+    from aklr_b200.moe import fused_moe_fp8
+
+    lib = _lib.load()
+    cfg, a = cases.ds_small_layer()
+    out_single, ws = run_layer(cfg, a, t(golden["ds_small.logits"]), 128)
+    lib.aklr_debug_force_cta_pairs(1)
+    try:
+        out_pair, ws_pair = run_layer(cfg, a, t(golden["ds_small.logits"]), 128)
+        ws_pair.check_status()
+    finally:
+        lib.aklr_debug_force_cta_pairs(-1)
+    assert torch.equal(out_pair.cpu(), out_single.cpu())
+    gates = orc.output_gates(out_pair.cpu(), t(golden["ds_small.out"]))
+    assert orc.gates_pass(gates), gates
+
+    # a batch large enough for several blocks per expert, against the same call without pairs
+    cfg = wl.CONFIGS["deepseek_small"]
+    d = dev()
+    w1, s1, w2, s2 = (x.to(d) for x in wl.expert_weights(cfg, seed=5))
+    hidden, logits, bias = (x.to(d) for x in wl.router_inputs(cfg, 1500, seed=6))
+    outs = []
+    for mode in (0, 1):
+        lib.aklr_debug_force_cta_pairs(mode)
+        try:
+            out, ws = fused_moe_fp8(hidden, logits, bias, w1, s1, w2, s2, routing_of(cfg), block_m=128, return_workspace=True)
+            ws.check_status()
+            outs.append(out.cpu())
+            blocks = ws.num_blocks()
+        finally:
+            lib.aklr_debug_force_cta_pairs(-1)
+    assert blocks > cfg.n_routed  # some experts have more than one block
+    assert torch.equal(outs[0], outs[1])
+
+
 def test_layer_call_is_cuda_graph_capturable():
     """No allocation, synchronisation or host read inside the call: it can be captured once a shape
     has run eagerly, and a replay on new input values gives what the eager call gives."""
