@@ -354,7 +354,8 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
                    const int32_t* topk_ids, const float* topk_weights, const int32_t* expert_map,
                    int n_experts_global, const void* w1, const uint8_t* w1_scale, const void* w2,
                    const uint8_t* w2_scale, float swiglu_limit, void* out, uint8_t* ws, cudaStream_t stream,
-                   const uint8_t* q_in = nullptr, const uint8_t* scales_in = nullptr, void* rows_out = nullptr) {
+                   const uint8_t* q_in = nullptr, const uint8_t* scales_in = nullptr, void* rows_out = nullptr,
+                   int slot = -1) {
   using namespace aklr;
   const int routes_per_token = c.topk + c.n_shared;
   const int routes = c.n_tokens * routes_per_token;
@@ -379,6 +380,7 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   int rc = launch_align(ap, stream);
   if (rc) return fail(rc, "moe_align launch failed");
   g_launches += routes <= 4096 ? 1 : 3;
+  profile_mark(stream, slot, 2);
 
   MxQuantParams qp{};
   qp.x = hidden_states;
@@ -394,6 +396,7 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   rc = launch_gather_quant_mxfp8(qp, stream);
   if (rc) return fail(rc, "MXFP8 activation quant launch failed");
   g_launches += 1;
+  profile_mark(stream, slot, 3);
 
   const int sms = sm_count();
   const int stages = grouped_gemm_mx_pick_stages();
@@ -419,6 +422,7 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   rc = launch_grouped_gemm_mx(g1, true, sms, stream);
   if (rc) return fail(rc, "MX gate_up grouped GEMM launch failed");
   g_launches += 1;
+  profile_mark(stream, slot, 4);
 
   MxGemmParams g2{};
   rc = make_map_fp4(&g2.map_w, w2, static_cast<uint64_t>(experts) * c.hidden, c.inter, 256);
@@ -441,7 +445,11 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   rc = launch_grouped_gemm_mx(g2, false, sms, stream);
   if (rc) return fail(rc, "MX down grouped GEMM launch failed");
   g_launches += 1;
-  if (rows_out) return AKLR_OK;
+  profile_mark(stream, slot, 5);
+  if (rows_out) {
+    profile_mark(stream, slot, 6);
+    return AKLR_OK;
+  }
 
   CombineParams cp{};
   cp.rows = ws + l.rows;
@@ -455,6 +463,7 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   rc = launch_combine(cp, stream);
   if (rc) return fail(rc, "combine launch failed");
   g_launches += 1;
+  profile_mark(stream, slot, 6);
   return AKLR_OK;
 }
 
@@ -608,10 +617,13 @@ int aklr_moe_mxfp4_forward(const aklr_moe_config* cfg, const void* hidden_states
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   int32_t* ids = reinterpret_cast<int32_t*>(ws + l.topk_ids);
   float* weights = reinterpret_cast<float*>(ws + l.topk_weights);
+  const int slot = profile_slot();
+  profile_mark(stream, slot, 0);
   rc = aklr_moe_route(cfg, logits, bias, sigmoid_table, ids, weights, stream_);
   if (rc) return rc;
+  profile_mark(stream, slot, 1);
   return run_mx_experts(*cfg, l, hidden_states, ids, weights, nullptr, cfg->n_routed + cfg->n_shared, w1, w1_scale, w2,
-                        w2_scale, swiglu_limit, out, ws, stream);
+                        w2_scale, swiglu_limit, out, ws, stream, nullptr, nullptr, nullptr, slot);
 }
 
 int aklr_moe_mxfp4_experts_prequant(const aklr_moe_config* cfg, const void* rows_q, const uint8_t* rows_scale,
@@ -630,9 +642,12 @@ int aklr_moe_mxfp4_experts_prequant(const aklr_moe_config* cfg, const void* rows
   if (cfg->n_tokens == 0) return AKLR_OK;
   if (!rows_q || !rows_scale || !expert_ids || !weights || !w1 || !w1_scale || !w2 || !w2_scale || !out_rows)
     return fail(AKLR_ERR_BAD_ARGUMENT, "NULL tensor argument");
+  const int slot = profile_slot();
+  profile_mark(stream, slot, 0);
+  profile_mark(stream, slot, 1);
   return run_mx_experts(*cfg, l, nullptr, expert_ids, weights, nullptr, cfg->n_routed, w1, w1_scale, w2, w2_scale,
                         swiglu_limit, nullptr, static_cast<uint8_t*>(workspace), stream,
-                        static_cast<const uint8_t*>(rows_q), rows_scale, out_rows);
+                        static_cast<const uint8_t*>(rows_q), rows_scale, out_rows, slot);
 }
 
 int aklr_ep_gather_quant_mxfp8(const void* hidden_states, const int32_t* sorted_ids, int32_t n_send, int32_t hidden,

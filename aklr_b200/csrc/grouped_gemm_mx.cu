@@ -172,15 +172,14 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
   if (warp == 0) {
     // ------------------------------- TMA producer ------------------------------------------
     if (lane == 0) {
-      uint32_t it = 0;
+      int s = 0;  // ring position and the parity of its current use
+      uint32_t ph = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const int b = t / tiles_per_block, j = t - b * tiles_per_block;
         const int e = p.block_expert[b];
         const int w_row = e * p.rows_per_expert + (GATE_UP ? j * 128 : j * 256);
-        for (int kb = 0; kb < KB; ++kb, ++it) {
-          const int s = it % S;
-          const uint32_t ph = (it / S) & 1;
+        for (int kb = 0; kb < KB; ++kb) {
           if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 21)) { ok = false; break; }
           uint8_t* st = smem + s * kStageBytes;
           // the transaction count of the unpacking fp4 load is its packed size (what crosses from
@@ -193,13 +192,22 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
           } else {
             tma_load_2d(st + kABytes, &p.map_w, &full[s], kb * 128, w_row);
           }
+          if (++s == S) { s = 0; ph ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer --------------------------------------------
     if (lane == 0) {
+      // A lone thread pays the full latency of every instruction: ring position, phase and the
+      // five descriptors are carried forward, not recomputed.
       uint32_t it = 0, tile_no = 0;
+      int s = 0;
+      uint32_t ph = 0;
+      const uint32_t base = smem_u32(smem);
+      const uint64_t da0 = umma_desc_sw128(base), db0 = umma_desc_sw128(base + kABytes);
+      const uint64_t sfa0 = sf_desc(base + kABytes + kBBytes);
+      uint32_t step = 0;  // (stage * kStageBytes) >> 4, added to the address field of each descriptor
       bool ok = true;
 #ifdef AKLR_GEMM_TIMING
       long long tacc[16] = {0};
@@ -210,8 +218,6 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
         MT(0, got = mbar_wait(acc_empty, (tile_no & 1) ^ 1, abort_flag, p.status, 22));
         if (!got) break;
         for (int kb = 0; kb < KB; ++kb, ++it) {
-          const int s = it % S;
-          const uint32_t ph = (it / S) & 1;
           MT(1, got = mbar_wait(&full[s], ph, abort_flag, p.status, 23));
           if (!got) { ok = false; break; }
           MT(2, got = mbar_wait(&sf_full[s], ph, abort_flag, p.status, 24));
@@ -220,13 +226,11 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
           const long long t_issue = clock64();
 #endif
           tc_fence_after_sync();
-          const uint32_t a0 = smem_u32(smem + s * kStageBytes);
-          const uint32_t sf0 = a0 + kABytes + kBBytes;
-          tmem_cp_32x128b_warpx4(tmem_base + kSfaCol, sf_desc(sf0));
-          tmem_cp_32x128b_warpx4(tmem_base + kSfbCol, sf_desc(sf0 + kSfaBytes));
-          tmem_cp_32x128b_warpx4(tmem_base + kSfbCol + 4, sf_desc(sf0 + kSfaBytes + 512));
-          const uint64_t da = umma_desc_sw128(a0);
-          const uint64_t db = umma_desc_sw128(a0 + kABytes);
+          const uint64_t sfa = sfa0 + step;
+          tmem_cp_32x128b_warpx4(tmem_base + kSfaCol, sfa);
+          tmem_cp_32x128b_warpx4(tmem_base + kSfbCol, sfa + (kSfaBytes >> 4));
+          tmem_cp_32x128b_warpx4(tmem_base + kSfbCol + 4, sfa + ((kSfaBytes + 512) >> 4));
+          const uint64_t da = da0 + step, db = db0 + step;
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             umma_mx(tmem_base, da + 2 * k, db + 2 * k, mx_idesc(kBN, k), tmem_base + kSfaCol, tmem_base + kSfbCol,
@@ -235,6 +239,8 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
 #ifdef AKLR_GEMM_TIMING
           tacc[3] += clock64() - t_issue;
 #endif
+          step += kStageBytes >> 4;
+          if (++s == S) { s = 0; ph ^= 1; step = 0; }
         }
         if (ok) tc_commit(acc_full);
       }
@@ -353,16 +359,18 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
       tc_fence_after_sync();
       float acc[128];
       {
+        // tcgen05.ld is latency-bound: all eight loads in flight, one wait, so that the accumulator
+        // goes back to the MMA warp after one round trip
+        uint32_t r[128];
         const uint32_t t0 = tmem_base + lane_addr + (GATE_UP ? half * 64 : half * 128);
 #pragma unroll
         for (int c = 0; c < 128; c += 16) {
-          uint32_t r[16];
           const uint32_t at = GATE_UP ? (c < 64 ? t0 + c : t0 + 128 + (c - 64)) : t0 + c;
-          AKLR_TMEM_LD_16(at, r);
-          tc_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) acc[c + i] = __uint_as_float(r[i]);
+          AKLR_TMEM_LD_16(at, (r + c));
         }
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 128; ++i) acc[i] = __uint_as_float(r[i]);
       }
       tc_fence_before_sync();
       __syncwarp();

@@ -537,6 +537,7 @@ def main() -> None:
 def bench_mxfp4(args, cfg, routing, device, lib):
     """The same layer with MXFP4 expert weights and MXFP8 activations (one GPU): extra measurement,
     printed as one JSON line of the same shape with ``config.weights`` saying so."""
+    from aklr_b200 import _lib
     from aklr_b200.moe import Workspace, _config, fused_moe_mxfp4
 
     T = args.tokens
@@ -557,6 +558,7 @@ def bench_mxfp4(args, cfg, routing, device, lib):
     sampler = ClockSampler(device.index or 0)
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
+    lib.aklr_profile_begin(args.steps)
     start.record()
     for i in range(args.steps):
         step(args.warmup + i)
@@ -564,6 +566,13 @@ def bench_mxfp4(args, cfg, routing, device, lib):
     torch.cuda.synchronize()
     clocks = sampler.stop()
     ms = start.elapsed_time(stop) / args.steps
+    stage_ms = [0.0] * 6
+    buf = (ctypes.c_float * 6)()
+    for i in range(args.steps):
+        _lib.check(lib.aklr_profile_read(i, buf))
+        for k in range(6):
+            stage_ms[k] += buf[k] / args.steps
+    lib.aklr_profile_begin(0)
     experts_hit = distinct_experts(ws.topk_ids())
     h, inter = cfg.hidden, cfg.inter
     weight_bytes = experts_hit * (3 * h * inter // 2 + 3 * h * inter // 32)
@@ -580,7 +589,10 @@ def bench_mxfp4(args, cfg, routing, device, lib):
         "roofline": {"bound": "hbm" if weight_bytes / (peak * 1e9) > flops / 3.2e15 else "tensor",
                      "achieved": weight_bytes / (ms * 1e-3) / 1e9, "peak": peak, "peak_kind": f"of {kind}", "unit": "GB/s",
                      "frac": weight_bytes / (ms * 1e-3) / 1e9 / peak, "traffic": None, "tflops": flops / (ms * 1e-3) / 1e12,
-                     "note": "whole layer: weight bytes of the experts hit / layer time"},
+                     "note": "whole layer: weight bytes of the experts hit / layer time",
+                     "stage_ms": dict(zip(["route", "sort", "quant", "gate_up", "down", "combine"], stage_ms)),
+                     "gate_up_tflops": 2 * flops / 3 / (stage_ms[3] * 1e-3) / 1e12 if stage_ms[3] > 0 else None,
+                     "down_tflops": flops / 3 / (stage_ms[4] * 1e-3) / 1e12 if stage_ms[4] > 0 else None},
         "cpu_baseline": None,
     }), flush=True)
 
