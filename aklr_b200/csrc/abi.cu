@@ -393,13 +393,31 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   qp.routes_per_token = routes_per_token;
   qp.q_in = q_in;
   qp.scales_in = scales_in;
+  if (!q_in && routes_per_token > 1 && c.n_tokens >= kQuantOncePerTokenFrom) {
+    // quantise every token once (codes and row-major scale bytes parked in the space of the
+    // per-route output rows, unused until the down projection), then copy per route
+    uint8_t* tq = ws + l.rows;
+    uint8_t* ts = tq + align_up(static_cast<int64_t>(c.n_tokens) * c.hidden, 256);
+    MxQuantParams tp{};
+    tp.x = hidden_states;
+    tp.q = tq;
+    tp.scales = ts;
+    tp.n_rows = c.n_tokens;
+    tp.hidden = c.hidden;
+    tp.routes_per_token = 1;
+    tp.row_major_scales = 1;
+    rc = launch_gather_quant_mxfp8(tp, stream);
+    if (rc) return fail(rc, "MXFP8 activation quant launch failed");
+    g_launches += 1;
+    qp.q_in = tq;
+    qp.scales_in = ts;
+  }
   rc = launch_gather_quant_mxfp8(qp, stream);
   if (rc) return fail(rc, "MXFP8 activation quant launch failed");
   g_launches += 1;
   profile_mark(stream, slot, 3);
 
   const int sms = sm_count();
-  const int stages = grouped_gemm_mx_pick_stages();
   MxGemmParams g1{};
   rc = make_map_fp4(&g1.map_w, w1, static_cast<uint64_t>(experts) * 2 * c.inter, c.hidden, 128);
   if (rc) return rc;
@@ -418,7 +436,7 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   g1.out_dim = c.inter;
   g1.rows_per_expert = 2 * c.inter;
   g1.max_blocks = l.max_blocks;
-  g1.stages = stages;
+  g1.stages = grouped_gemm_mx_pick_stages(true);
   rc = launch_grouped_gemm_mx(g1, true, sms, stream);
   if (rc) return fail(rc, "MX gate_up grouped GEMM launch failed");
   g_launches += 1;
@@ -441,7 +459,7 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   g2.out_dim = c.hidden;
   g2.rows_per_expert = c.hidden;
   g2.max_blocks = l.max_blocks;
-  g2.stages = stages;
+  g2.stages = grouped_gemm_mx_pick_stages(false);
   rc = launch_grouped_gemm_mx(g2, false, sms, stream);
   if (rc) return fail(rc, "MX down grouped GEMM launch failed");
   g_launches += 1;

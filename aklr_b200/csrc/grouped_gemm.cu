@@ -116,8 +116,7 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
   float* colscale = reinterpret_cast<float*>(smem + L.off_wscale);  // [BM]
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.off_bars);
   uint64_t* empty = full + S;
-  uint64_t* tmem_full = empty + S;
-  uint64_t* tmem_empty = tmem_full + 2;
+  uint64_t* tmem_empty = empty + S;
   uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
 
@@ -133,7 +132,6 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
       mbar_init(&empty[s], 1);
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&tmem_full[i], 1);
       mbar_init(&tmem_empty[i], kEpiThreads / 32);
     }
     *abort_flag = 0;
@@ -154,6 +152,8 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
     // ------------------------------- TMA producer ------------------------------------------
     if (lane == 0) {
       uint32_t it = 0;
+      int s = 0;  // ring position and the parity of its current use
+      uint32_t ph = 0;
       bool ok = true;
 #ifdef AKLR_GEMM_TIMING
       long long tacc[16] = {0};
@@ -164,8 +164,6 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
         const int e = p.block_expert[b];
         const int w_row = e * p.rows_per_expert + j * 128;
         for (int kb = 0; kb < KB; ++kb, ++it) {
-          const int s = it % S;
-          const uint32_t ph = (it / S) & 1;
           bool got;
           TIMING_ADD(0, got = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1));
           if (!got) { ok = false; break; }
@@ -174,6 +172,7 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
           tma_load_2d(st, &p.map_w, &full[s], kb * 128, w_row);
           if (GATE_UP) tma_load_2d(st + kWTileBytes, &p.map_w, &full[s], kb * 128, w_row + p.out_dim);
           tma_load_2d(st + (GATE_UP ? 2 : 1) * kWTileBytes, &p.map_x, &full[s], kb * 128, b * BM);
+          if (++s == S) { s = 0; ph ^= 1; }
         }
       }
 #ifdef AKLR_GEMM_TIMING
@@ -187,17 +186,20 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
   } else if (warp == 1) {
     // ------------------------------- MMA issuer --------------------------------------------
     if (lane == 0) {
-      uint32_t it = 0;
+      // A lone thread pays the full latency of every instruction: ring position, phases and
+      // descriptors are carried forward, and one commit per K-block serves both the producer (stage
+      // free) and the epilogue (partial complete).
+      int s = 0;
+      uint32_t ph = 0, buf = 0, bph = 0;
+      const uint64_t desc0 = umma_desc_sw128(smem_u32(smem));
+      const uint32_t stage_step = static_cast<uint32_t>(L.stage_bytes) >> 4;
+      uint64_t da0 = desc0;  // first weight tile of stage s; the second one and the token tile follow
       bool ok = true;
 #ifdef AKLR_GEMM_TIMING
       long long tacc[16] = {0};
 #endif
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        for (int kb = 0; kb < KB; ++kb, ++it) {
-          const int s = it % S;
-          const uint32_t ph = (it / S) & 1;
-          const int buf = it & 1;
-          const uint32_t bph = (it >> 1) & 1;
+        for (int kb = 0; kb < KB; ++kb) {
           bool got;
           TIMING_ADD(1, got = mbar_wait(&full[s], ph, abort_flag, p.status, 2));
           if (!got) { ok = false; break; }
@@ -207,21 +209,22 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
           const long long t_issue = clock64();
 #endif
           tc_fence_after_sync();
-          const uint32_t a0 = smem_u32(smem + s * L.stage_bytes);
-          const uint64_t da0 = umma_desc_sw128(a0);
-          const uint64_t da1 = umma_desc_sw128(a0 + kWTileBytes);
-          const uint64_t db = umma_desc_sw128(a0 + (GATE_UP ? 2 : 1) * kWTileBytes);
+          const uint64_t da1 = da0 + (kWTileBytes >> 4);
+          const uint64_t db = da0 + (((GATE_UP ? 2 : 1) * kWTileBytes) >> 4);
           const uint32_t d = tmem_base + buf * BUF_COLS;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {  // 32 K bytes per MMA: the descriptor start moves 32 B
             umma_f8f6f4(d, da0 + 2 * k, db + 2 * k, IDESC, k > 0);
             if (GATE_UP) umma_f8f6f4(d + BM, da1 + 2 * k, db + 2 * k, IDESC, k > 0);
           }
-          tc_commit(&empty[s]);         // the stage is free once these MMAs have read it
-          tc_commit(&tmem_full[buf]);   // and the partial is complete
+          tc_commit(&empty[s]);
 #ifdef AKLR_GEMM_TIMING
           tacc[3] += clock64() - t_issue;
 #endif
+          da0 += stage_step;
+          if (++s == S) { s = 0; ph ^= 1; da0 = desc0; }
+          bph ^= buf;
+          buf ^= 1;
         }
       }
 #ifdef AKLR_GEMM_TIMING
@@ -242,6 +245,8 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
     constexpr int CPT = NH / CH;             // chunks per accumulator tile
     constexpr int NC = TILES * CPT;          // chunks per K-block
     uint32_t it = 0;
+    int ring = 0;  // the stage whose "empty" barrier reports MMA(it) complete, and its parity
+    uint32_t ring_ph = 0;
     bool bad = false;
 #ifdef AKLR_GEMM_TIMING
     long long tacc[16] = {0};
@@ -300,9 +305,9 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
 
       for (int kb = 0; kb < KB; ++kb, ++it) {
         const int buf = it & 1;
-        const uint32_t bph = (it >> 1) & 1;
         bool got;
-        TIMING_ADD(4, got = mbar_wait(&tmem_full[buf], bph, abort_flag, p.status, 4));
+        TIMING_ADD(4, got = mbar_wait(&empty[ring], ring_ph, abort_flag, p.status, 4));
+        if (++ring == S) { ring = 0; ring_ph ^= 1; }
         if (!got) bad = true;
         tc_fence_after_sync();
 #ifdef AKLR_GEMM_TIMING

@@ -58,15 +58,19 @@ constexpr int kABytes = kBM * 128;
 constexpr int kBBytes = kBN * 128;          // unpacked: one byte per e2m1 element in shared memory
 constexpr int kSfaBytes = 512;              // 128 rows x 4 K-steps
 constexpr int kStageBytes = kABytes + kBBytes + 2048;  // operands + scale factors (padded to 2 KB)
+constexpr bool kTileResidentScales = false;  // staging variant for short reductions; measured slower, kept for reference
 constexpr int kSfaCol = 256, kSfbCol = 260;  // TMEM columns after the 256 accumulator columns
 
 struct MxLayout {
-  int off_rid, off_wgt, off_bars, total;
+  int off_out, off_rid, off_wgt, off_bars, total;
 };
 
-__host__ __device__ inline MxLayout mx_layout(int stages) {
+constexpr int kOutPassCols = 32;  // down: channels per thread staged per pass (64 bytes per row)
+
+__host__ __device__ inline MxLayout mx_layout(int stages, bool gate_up) {
   MxLayout l;
-  l.off_rid = stages * kStageBytes;
+  l.off_out = stages * kStageBytes;  // down: per epilogue warp 32 rows x 64 bytes of bf16 output
+  l.off_rid = l.off_out + (gate_up ? 0 : (kEpi / 32) * 32 * kOutPassCols * 2);
   l.off_wgt = l.off_rid + kBM * 4;
   l.off_bars = l.off_wgt + kBM * 4;
   l.total = l.off_bars + (3 * stages + 2) * 8 + 16;
@@ -130,7 +134,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int KB = p.k >> 7;
   const int S = p.stages;
-  const MxLayout L = mx_layout(S);
+  const MxLayout L = mx_layout(S, GATE_UP);
   int* rid_s = reinterpret_cast<int*>(smem + L.off_rid);
   float* wgt_s = reinterpret_cast<float*>(smem + L.off_wgt);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.off_bars);
@@ -146,12 +150,15 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
   if (nb > p.max_blocks) nb = p.max_blocks;
   const int tiles_per_block = GATE_UP ? (p.out_dim >> 7) : (p.out_dim >> 8);
   const int total_tiles = nb * tiles_per_block;
+  // Down projection with a short reduction (k = 512, 1024, 1536 or 2048): the staging warps keep a
+  // whole tile's weight scales in registers (see there).
+  const bool tile_regs = kTileResidentScales && !GATE_UP && (KB & 3) == 0 && KB <= 16;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
-      mbar_init(&sf_full[s], 1);  // the one staging warp that owns the K-block
+      mbar_init(&sf_full[s], tile_regs ? 2 : 1);  // both staging warps, or the one that owns the K-block
     }
     mbar_init(acc_full, 1);
     mbar_init(acc_empty, kEpi / 32);
@@ -263,7 +270,87 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
     long long tacc[16] = {0};
 #endif
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, it0 += KB) {
+    if (tile_regs) {
+      // A tile's weight scales are 256 rows x KS (<= 64) contiguous bytes.  Fetching one 4-byte word
+      // per row and K-block re-reads every 32-byte sector of those rows eight times and was the
+      // bottleneck of the down projection (the MMA warp waited ~500 cycles per K-block for scales).
+      // Here the 64 staging lanes hold the tile in registers -- rows lane64 + 64 j, j < 4, as KB/4
+      // 16-byte pieces of 4 K-blocks each -- and every lane writes its four words per K-block.  A
+      // piece is reloaded for the NEXT tile right after its last K-block, a whole tile ahead of use.
+      const int lane64 = sw * 32 + lane;
+      const int P = KB >> 2;
+      uint4 reg[4][4];
+      auto tile_base = [&](int t) -> const uint8_t* {
+        const int b = t / tiles_per_block, j = t - b * tiles_per_block;
+        const int e = p.block_expert[b];
+        return p.w_scale + (static_cast<size_t>(e) * p.rows_per_expert + j * 256) * KS;
+      };
+      auto load_piece = [&](const uint8_t* wb, int pc) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          reg[j][pc] = __ldg(reinterpret_cast<const uint4*>(wb + static_cast<size_t>(lane64 + 64 * j) * KS) + pc);
+      };
+      int t = blockIdx.x;
+      if (t < total_tiles) {
+        const uint8_t* wb = tile_base(t);
+#pragma unroll
+        for (int pc = 0; pc < 4; ++pc)
+          if (pc < P) load_piece(wb, pc);
+      }
+      // activation scales (already in tcgen05.cp order in global memory): warp 0, four K-blocks ahead
+      uint4 aq[4];
+      int ta = blockIdx.x, kba = 0;
+      auto aq_load = [&](uint4& a) {
+        if (ta < total_tiles) {
+          const int ba = ta / tiles_per_block;
+          a = __ldg(reinterpret_cast<const uint4*>(p.x_scale + (static_cast<size_t>(ba) * KB + kba) * kSfaBytes) + lane);
+          if (++kba == KB) {
+            kba = 0;
+            ta += gridDim.x;
+          }
+        }
+      };
+      if (sw == 0) {
+#pragma unroll
+        for (int d = 0; d < 4; ++d) aq_load(aq[d]);
+      }
+      int s = 0;
+      uint32_t ph = 0;
+      for (; t < total_tiles && ok; t += gridDim.x) {
+        const int tn = t + static_cast<int>(gridDim.x);
+        const uint8_t* wb_next = tn < total_tiles ? tile_base(tn) : nullptr;
+#pragma unroll
+        for (int kb = 0; kb < 16; ++kb) {
+          if (kb < KB && ok) {
+            bool got;
+            MT(4, got = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 25));
+            if (!got) ok = false;
+#ifdef AKLR_GEMM_TIMING
+            const long long t_stage = clock64();
+#endif
+            uint8_t* sf = smem + s * kStageBytes + kABytes + kBBytes;
+            if (sw == 0) *reinterpret_cast<uint4*>(sf + lane * 16) = aq[kb & 3];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {  // row lane64 + 64 j = lane + 32 q with q = sw + 2 j
+              const uint4 v = reg[j][kb >> 2];
+              const uint32_t word = (kb & 3) == 0 ? v.x : (kb & 3) == 1 ? v.y : (kb & 3) == 2 ? v.z : v.w;
+              const int q = sw + 2 * j;
+              *reinterpret_cast<uint32_t*>(sf + kSfaBytes + (q >> 2) * 512 + lane * 16 + (q & 3) * 4) = word;
+            }
+            fence_proxy_async_smem();  // tcgen05.cp reads these bytes through the async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sf_full[s]);
+            if (sw == 0) aq_load(aq[kb & 3]);
+            if ((kb & 3) == 3 && wb_next) load_piece(wb_next, kb >> 2);
+            if (++s == S) { s = 0; ph ^= 1; }
+#ifdef AKLR_GEMM_TIMING
+            tacc[5] += clock64() - t_stage;
+#endif
+          }
+        }
+      }
+    }
+    for (int t = blockIdx.x; !tile_regs && t < total_tiles && ok; t += gridDim.x, it0 += KB) {
       const int b = t / tiles_per_block, j = t - b * tiles_per_block;
       const int e = p.block_expert[b];
       const uint8_t* wsf[8];
@@ -413,18 +500,40 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
           *reinterpret_cast<uint16_t*>(p.out_scale + (static_cast<size_t>(b) * IB + j) * kSfaBytes + (row & 31) * 16 +
                                        (row >> 5) * 4 + half * 2) = static_cast<uint16_t>(scale_bytes);
         }
-      } else if (rid >= 0 && !bad) {
+      } else {
+        // A thread owns 128 channels of one token: direct stores would be 16 bytes per lane at 32
+        // different rows (half-filled sectors, one L1 wavefront per lane), and that store traffic
+        // also delays the scale-staging warps, which share the load/store path.  Each warp stages
+        // 32 rows x 32 channels in shared memory (16-byte chunks XOR-swizzled by row) and writes 64
+        // contiguous bytes of 8 rows per instruction.
         const float w = wgt_s[row];
-        uint8_t* dst = static_cast<uint8_t*>(p.out_rows) + (static_cast<size_t>(rid) * p.out_dim + j * 256 + half * 128) * 2;
+        uint8_t* stage = smem + L.off_out + (warp - 2) * (32 * kOutPassCols * 2);
 #pragma unroll
-        for (int v = 0; v < 16; ++v) {
-          uint32_t o[4];
+        for (int pass = 0; pass < 128 / kOutPassCols; ++pass) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const __nv_bfloat162 two = __floats2bfloat162_rn(acc[v * 8 + 2 * q] * w, acc[v * 8 + 2 * q + 1] * w);
-            o[q] = *reinterpret_cast<const uint32_t*>(&two);
+          for (int v = 0; v < kOutPassCols / 8; ++v) {
+            uint32_t o[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int i = pass * kOutPassCols + v * 8 + 2 * q;
+              const __nv_bfloat162 two = __floats2bfloat162_rn(acc[i] * w, acc[i + 1] * w);
+              o[q] = *reinterpret_cast<const uint32_t*>(&two);
+            }
+            *reinterpret_cast<uint4*>(stage + lane * (kOutPassCols * 2) + ((v ^ ((lane >> 1) & 3)) << 4)) =
+                make_uint4(o[0], o[1], o[2], o[3]);
           }
-          *reinterpret_cast<uint4*>(dst + v * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int r = 8 * i + (lane >> 2), c = lane & 3;  // row of this warp's 32, 16-byte chunk
+            const int rr = rid_s[quarter * 32 + r];
+            const uint4 val = *reinterpret_cast<const uint4*>(stage + r * (kOutPassCols * 2) + ((c ^ ((r >> 1) & 3)) << 4));
+            if (rr >= 0 && !bad)
+              *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out_rows) +
+                                        (static_cast<size_t>(rr) * p.out_dim + j * 256 + half * 128 +
+                                         pass * kOutPassCols + c * 8) * 2) = val;
+          }
+          __syncwarp();
         }
       }
 #ifdef AKLR_GEMM_TIMING
@@ -462,7 +571,7 @@ __global__ void __launch_bounds__(256) gather_quant_mxfp8_kernel(MxQuantParams p
   for (int64_t g = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 2; g < total; g += quads) {
     const int row = static_cast<int>(g / groups_per_row);
     const int grp = static_cast<int>(g - static_cast<int64_t>(row) * groups_per_row);
-    const int rid = p.sorted_ids[row];
+    const int rid = p.sorted_ids ? p.sorted_ids[row] : row;  // no table: quantise the rows in place order
     if (rid < 0) continue;
     const int token = rid / p.routes_per_token;
     if (p.q_in) {  // rows quantised by their sender: move codes and scale byte
@@ -506,6 +615,49 @@ __global__ void __launch_bounds__(256) gather_quant_mxfp8_kernel(MxQuantParams p
   }
 }
 
+// Rows quantised before (each token once, or by the sender of an expert-parallel dispatch): copy
+// row rid's codes into the expert-sorted table and its scale bytes into tcgen05.cp order.  A CTA
+// moves four rows at a time, every thread with four independent 16-byte loads in flight; a
+// K-block's four scale bytes of a row move as one word.
+constexpr int kGatherRows = 4;
+__global__ void __launch_bounds__(256) gather_rows_mxfp8_kernel(MxQuantParams p) {
+  __shared__ int src_s[kGatherRows];
+  const int vec_per_row = p.hidden >> 4;
+  const int KB = p.hidden >> 7;
+  const int n_rows = p.num_rows ? min(*p.num_rows, p.n_rows) : p.n_rows;
+  for (int row0 = blockIdx.x * kGatherRows; row0 < n_rows; row0 += gridDim.x * kGatherRows) {
+    if (threadIdx.x < kGatherRows) {
+      const int row = row0 + threadIdx.x;
+      const int rid = row < n_rows ? p.sorted_ids[row] : -1;
+      src_s[threadIdx.x] = rid < 0 ? -1 : rid / p.routes_per_token;
+    }
+    __syncthreads();
+    int src[kGatherRows];
+#pragma unroll
+    for (int r = 0; r < kGatherRows; ++r) src[r] = src_s[r];
+    for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
+      uint4 val[kGatherRows];
+#pragma unroll
+      for (int r = 0; r < kGatherRows; ++r)
+        if (src[r] >= 0)
+          val[r] = __ldg(reinterpret_cast<const uint4*>(p.q_in + static_cast<size_t>(src[r]) * p.hidden) + v);
+#pragma unroll
+      for (int r = 0; r < kGatherRows; ++r)
+        if (src[r] >= 0) reinterpret_cast<uint4*>(p.q + static_cast<size_t>(row0 + r) * p.hidden)[v] = val[r];
+    }
+    for (int i = threadIdx.x; i < kGatherRows * KB; i += blockDim.x) {
+      const int r = i / KB, kb = i - r * KB;
+      const int row = row0 + r;
+      if (src_s[r] >= 0) {
+        const uint32_t word = __ldg(reinterpret_cast<const uint32_t*>(p.scales_in + static_cast<size_t>(src_s[r]) * (KB * 4)) + kb);
+        const int b = row >> 7, rr = row & 127;
+        *reinterpret_cast<uint32_t*>(p.scales + (static_cast<size_t>(b) * KB + kb) * kSfaBytes + (rr & 31) * 16 + (rr >> 5) * 4) = word;
+      }
+    }
+    __syncthreads();
+  }
+}
+
 }  // namespace
 
 #ifdef AKLR_GEMM_TIMING
@@ -517,6 +669,13 @@ extern "C" int aklr_debug_read_mx_timing(long long* host32) {
 int launch_gather_quant_mxfp8(const MxQuantParams& p, cudaStream_t stream) {
   if (p.hidden % 128 != 0) return AKLR_ERR_UNSUPPORTED_SHAPE;
   if (p.n_rows == 0) return AKLR_OK;
+  if (p.q_in) {
+    if (!p.sorted_ids || !p.scales_in) return AKLR_ERR_BAD_ARGUMENT;
+    const int64_t blocks = (static_cast<int64_t>(p.n_rows) + kGatherRows - 1) / kGatherRows;
+    const int grid = static_cast<int>(blocks < 148 * 32 ? blocks : 148 * 32);
+    gather_rows_mxfp8_kernel<<<grid, 256, 0, stream>>>(p);
+    return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+  }
   const int64_t groups = static_cast<int64_t>(p.n_rows) * (p.hidden / 32);
   const int64_t blocks = (groups * 4 + 255) / 256;
   const int grid = static_cast<int>(blocks < 148 * 16 ? blocks : 148 * 16);
@@ -524,16 +683,16 @@ int launch_gather_quant_mxfp8(const MxQuantParams& p, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
 }
 
-int grouped_gemm_mx_pick_stages() {
+int grouped_gemm_mx_pick_stages(bool gate_up) {
   for (int s = 4; s >= 2; --s)
-    if (mx_layout(s).total + 1024 <= 227 * 1024) return s;
+    if (mx_layout(s, gate_up).total + 1024 <= 227 * 1024) return s;
   return 0;
 }
 
 int launch_grouped_gemm_mx(const MxGemmParams& p, bool gate_up, int sm_count, cudaStream_t stream) {
   if (p.k % 128 != 0 || p.max_blocks < 1 || p.stages < 2) return AKLR_ERR_UNSUPPORTED_SHAPE;
   if (gate_up ? (p.out_dim % 128 != 0) : (p.out_dim % 256 != 0)) return AKLR_ERR_UNSUPPORTED_SHAPE;
-  const size_t smem = static_cast<size_t>(mx_layout(p.stages).total) + 1024;
+  const size_t smem = static_cast<size_t>(mx_layout(p.stages, gate_up).total) + 1024;
   if (smem > 227 * 1024) return AKLR_ERR_UNSUPPORTED_SHAPE;
   const long long tiles = static_cast<long long>(p.max_blocks) * (gate_up ? p.out_dim / 128 : p.out_dim / 256);
   const int grid = static_cast<int>(tiles < sm_count ? tiles : sm_count);

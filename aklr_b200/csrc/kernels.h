@@ -125,7 +125,7 @@ struct MxGemmParams {
   float swiglu_limit;          // > 0: clamp gate above and up on both sides before the activation
   int k, out_dim, rows_per_expert, max_blocks, stages;
 };
-int grouped_gemm_mx_pick_stages();
+int grouped_gemm_mx_pick_stages(bool gate_up);
 int launch_grouped_gemm_mx(const MxGemmParams& p, bool gate_up, int sm_count, cudaStream_t stream);
 
 struct CombineParams {
