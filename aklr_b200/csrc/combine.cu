@@ -20,18 +20,35 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
     const int token = static_cast<int>(i / vec_per_row);
     const int v = static_cast<int>(i - static_cast<int64_t>(token) * vec_per_row);
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int s = 0; s < p.routes_per_token; ++s) {
-      const int route = token * p.routes_per_token + s;
-      int e = p.topk_ids[route];
-      if (e < 0 || e >= p.n_experts_global) continue;
-      if (p.expert_map && p.expert_map[e] < 0) continue;
-      const uint4 raw = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.rows) +
-                                                        static_cast<size_t>(route) * p.hidden + v * 8);
-      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    // Slots are summed in order, but their loads do not wait for one another: ids of a batch of
+    // slots first, then all of its rows, then the additions (a decode call is one latency chain).
+    constexpr int kBatchSlots = 9;
+    for (int s0 = 0; s0 < p.routes_per_token; s0 += kBatchSlots) {
+      bool live[kBatchSlots];
+      uint4 raw[kBatchSlots];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        acc[2 * q] += __uint_as_float(w[q] << 16);
-        acc[2 * q + 1] += __uint_as_float(w[q] & 0xFFFF0000u);
+      for (int d = 0; d < kBatchSlots; ++d) {
+        const int s = s0 + d;
+        live[d] = false;
+        if (s < p.routes_per_token) {
+          const int e = __ldg(p.topk_ids + token * p.routes_per_token + s);
+          live[d] = e >= 0 && e < p.n_experts_global && (!p.expert_map || __ldg(p.expert_map + e) >= 0);
+        }
+      }
+#pragma unroll
+      for (int d = 0; d < kBatchSlots; ++d)
+        if (live[d])
+          raw[d] = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.rows) +
+                                                   static_cast<size_t>(token * p.routes_per_token + s0 + d) * p.hidden + v * 8);
+#pragma unroll
+      for (int d = 0; d < kBatchSlots; ++d) {
+        if (!live[d]) continue;
+        const uint32_t w[4] = {raw[d].x, raw[d].y, raw[d].z, raw[d].w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          acc[2 * q] += __uint_as_float(w[q] << 16);
+          acc[2 * q + 1] += __uint_as_float(w[q] & 0xFFFF0000u);
+        }
       }
     }
     uint4 packed;

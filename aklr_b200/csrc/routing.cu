@@ -79,13 +79,19 @@ __global__ void __launch_bounds__(256) route_kernel(RouteParams p) {
   if (p.num_expert_group > 1 && p.topk_group < p.num_expert_group) {
     const int G = p.num_expert_group;
     const int gs = E / G;
+    int gid[VPT];  // group of each register's expert (one division each, not one per group and pass)
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int e = i * 32 + lane;
+      gid[i] = e < E ? e / gs : -1;
+    }
     float my_group_score = 0.0f;  // lane g holds group g's score
     for (int g = 0; g < G; ++g) {
       Key best{0u, 0u};
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         const int e = i * 32 + lane;
-        const Key k{(e < E && e / gs == g) ? rank[i] : 0u, ~static_cast<uint32_t>(e)};
+        const Key k{gid[i] == g ? rank[i] : 0u, ~static_cast<uint32_t>(e)};
         if (key_greater(k, best)) best = k;
       }
       const Key first = warp_max_key(best);
@@ -93,7 +99,7 @@ __global__ void __launch_bounds__(256) route_kernel(RouteParams p) {
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         const int e = i * 32 + lane;
-        const Key k{(e < E && e / gs == g) ? rank[i] : 0u, ~static_cast<uint32_t>(e)};
+        const Key k{gid[i] == g ? rank[i] : 0u, ~static_cast<uint32_t>(e)};
         const bool is_first = (k.hi == first.hi && k.lo == first.lo);
         if (!is_first && key_greater(k, second_local)) second_local = k;
       }
@@ -115,10 +121,8 @@ __global__ void __launch_bounds__(256) route_kernel(RouteParams p) {
       if (lane == g) gk.hi = 0u;
     }
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      const int e = i * 32 + lane;
-      if (e < E && !((kept_mask >> (e / gs)) & 1u)) rank[i] = 0u;
-    }
+    for (int i = 0; i < VPT; ++i)
+      if (gid[i] >= 0 && !((kept_mask >> gid[i]) & 1u)) rank[i] = 0u;
   }
 
   // ---- top-k by key; lane j keeps the j-th pick ----
@@ -221,6 +225,34 @@ __global__ void __launch_bounds__(kSortChunk) align_count_kernel(AlignParams p) 
     p.chunk_hist[static_cast<size_t>(blockIdx.x) * p.n_experts + e] = hist[e];
 }
 
+// Exclusive prefix sum of one value per thread over the CTA (blockDim.x a multiple of 32, <= 1024):
+// warp shuffles, then the warp totals by warp 0.  ``scratch`` holds >= 33 ints.  Two barriers.
+__device__ int block_exclusive_scan(int v, int* scratch, int* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  int inc = v;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const int u = __shfl_up_sync(0xFFFFFFFFu, inc, off);
+    if (lane >= off) inc += u;
+  }
+  __syncthreads();  // earlier readers of scratch are done
+  if (lane == 31) scratch[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    int w = lane < n_warps ? scratch[lane] : 0;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int u = __shfl_up_sync(0xFFFFFFFFu, w, off);
+      if (lane >= off) w += u;
+    }
+    scratch[lane] = w;  // inclusive totals of warps 0..lane
+    if (lane == 31) scratch[32] = w;
+  }
+  __syncthreads();
+  *total = scratch[32];
+  return inc - v + (warp > 0 ? scratch[warp - 1] : 0);
+}
+
 // Shared by the scan kernel and the one-CTA path: from per-expert totals in smem ``total`` compute
 // padded bases, the block table, counts, the pad fill.  ``base`` receives each expert's first row.
 __device__ void plan_blocks(const AlignParams& p, const int* total, int* base, int* scratch) {
@@ -232,19 +264,11 @@ __device__ void plan_blocks(const AlignParams& p, const int* total, int* base, i
     const int e = tid * per + i;
     if (e < p.n_experts) local_sum += (total[e] + p.block_m - 1) / p.block_m;
   }
-  scratch[tid] = local_sum;
-  __syncthreads();
-  // Hillis-Steele inclusive scan over nt partial sums
-  for (int off = 1; off < nt; off <<= 1) {
-    const int v = tid >= off ? scratch[tid - off] : 0;
-    __syncthreads();
-    scratch[tid] += v;
-    __syncthreads();
-  }
-  int running = scratch[tid] - local_sum;  // blocks before this thread's experts
+  int all_blocks;
+  int running = block_exclusive_scan(local_sum, scratch, &all_blocks);  // blocks before this thread's experts
   if (tid == nt - 1) {
-    p.num_blocks[0] = scratch[tid];
-    p.num_blocks[1] = scratch[tid] * p.block_m;
+    p.num_blocks[0] = all_blocks;
+    p.num_blocks[1] = all_blocks * p.block_m;
   }
   int pair_running = 0;  // runs of <= 2 blocks before this thread's experts
   if (p.pair_table) {
@@ -254,16 +278,9 @@ __device__ void plan_blocks(const AlignParams& p, const int* total, int* base, i
       const int e = tid * per + i;
       if (e < p.n_experts) local_pairs += ((total[e] + p.block_m - 1) / p.block_m + 1) / 2;
     }
-    scratch[tid] = local_pairs;
-    __syncthreads();
-    for (int off = 1; off < nt; off <<= 1) {
-      const int v = tid >= off ? scratch[tid - off] : 0;
-      __syncthreads();
-      scratch[tid] += v;
-      __syncthreads();
-    }
-    pair_running = scratch[tid] - local_pairs;
-    if (tid == nt - 1) p.num_blocks[2] = scratch[tid];
+    int all_pairs;
+    pair_running = block_exclusive_scan(local_pairs, scratch, &all_pairs);
+    if (tid == nt - 1) p.num_blocks[2] = all_pairs;
   }
   for (int i = 0; i < per; ++i) {
     const int e = tid * per + i;
@@ -295,7 +312,11 @@ __device__ void place_chunk(const AlignParams& p, int route, int* cursor) {
   const int rank_in_warp = __popc(same & ((1u << lane) - 1u));
   const bool leader = e >= 0 && rank_in_warp == 0;
   int start = 0;
-  for (int w = 0; w < (blockDim.x >> 5); ++w) {
+  const int chunk_first = route - static_cast<int>(threadIdx.x);  // first route of this chunk
+  const int in_chunk = p.n_routes - chunk_first < static_cast<int>(blockDim.x) ? p.n_routes - chunk_first
+                                                                                : static_cast<int>(blockDim.x);
+  const int busy_warps = in_chunk > 0 ? (in_chunk + 31) >> 5 : 0;  // warps past these hold no route
+  for (int w = 0; w < busy_warps; ++w) {
     if (warp == w && leader) {
       start = cursor[e];
       cursor[e] = start + __popc(same);
