@@ -13,6 +13,8 @@
 namespace aklr {
 
 __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
+  griddep_launch();
+  griddep_wait();
   const int vec_per_row = p.hidden >> 3;  // 8 bf16 per 16-byte vector
   const int64_t total = static_cast<int64_t>(p.n_tokens) * vec_per_row;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -68,8 +70,7 @@ int launch_combine(const CombineParams& p, cudaStream_t stream) {
   const int64_t total = static_cast<int64_t>(p.n_tokens) * (p.hidden / 8);
   const int64_t blocks = (total + 255) / 256;
   const int grid = static_cast<int>(blocks < 148 * 8 ? blocks : 148 * 8);
-  combine_kernel<<<grid, 256, 0, stream>>>(p);
-  return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+  return launch_kernel(combine_kernel, dim3(grid), dim3(256), 0, stream, 1, p) == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
 }
 
 // One warp per (token, kRouterExperts experts): lanes stride the hidden dimension with 16-byte loads.

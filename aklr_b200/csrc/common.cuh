@@ -36,6 +36,14 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
+// ---- programmatic dependent launch ------------------------------------------------------------
+// Kernels of a call are launched with programmatic stream serialisation: a kernel's CTAs may be
+// scheduled while the previous kernel is still finishing, do their local set-up (barriers, TMEM,
+// descriptor prefetch) and then wait here until everything before them in the stream is complete
+// and visible.  Nothing produced by an earlier kernel may be read before griddep_wait().
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- mbarrier -------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");

@@ -19,6 +19,7 @@
 // Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..9
 // epilogue (TMEM lane quarter = warp % 4, column half = (warp-2)/4).
 #include <cfloat>
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <utility>
@@ -121,10 +122,7 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int nb = *p.num_blocks;
-  if (nb > p.max_blocks) nb = p.max_blocks;
-  const int tiles_per_block = p.out_dim >> 7;
-  const int total_tiles = nb * tiles_per_block;
+  griddep_launch();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -147,6 +145,11 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr;
+  griddep_wait();  // everything below reads what earlier kernels of the call wrote
+  int nb = *p.num_blocks;
+  if (nb > p.max_blocks) nb = p.max_blocks;
+  const int tiles_per_block = p.out_dim >> 7;
+  const int total_tiles = nb * tiles_per_block;
 
   if (warp == 0) {
     // ------------------------------- TMA producer ------------------------------------------
@@ -416,6 +419,16 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
   }
 }
 
+bool pdl_enabled() {
+  // Opt-in (AKLR_PDL=1): measured on B200 it changes nothing for T >= 16 and costs 8 us at T = 1
+  // under CUDA-graph replay, where launch gaps are already small.
+  static const bool on = [] {
+    const char* v = getenv("AKLR_PDL");
+    return v && v[0] == '1';
+  }();
+  return on;
+}
+
 int ensure_max_dynamic_smem(const void* kernel) {
   static std::mutex lock;
   static std::map<std::pair<const void*, int>, bool> granted;
@@ -441,8 +454,7 @@ static int launch_grouped(const GroupedGemmParams& p, int sm_count, cudaStream_t
   const int grid = static_cast<int>(tiles < sm_count ? tiles : sm_count);
   auto run = [&](auto kernel) {
     if (ensure_max_dynamic_smem(reinterpret_cast<const void*>(kernel)) != AKLR_OK) return AKLR_ERR_CUDA;
-    kernel<<<grid, kGemmThreads, smem, stream>>>(p);
-    return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+    return launch_kernel(kernel, dim3(grid), dim3(kGemmThreads), smem, stream, 1, p) == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
   };
   switch (p.block_m) {
     case 16: return run(grouped_gemm_kernel<16, GATE_UP>);

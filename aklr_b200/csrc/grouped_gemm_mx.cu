@@ -146,13 +146,11 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int nb = *p.num_blocks;
-  if (nb > p.max_blocks) nb = p.max_blocks;
-  const int tiles_per_block = GATE_UP ? (p.out_dim >> 7) : (p.out_dim >> 8);
-  const int total_tiles = nb * tiles_per_block;
+  griddep_launch();
   // Down projection with a short reduction (k = 512, 1024, 1536 or 2048): the staging warps keep a
   // whole tile's weight scales in registers (see there).
-  const bool tile_regs = kTileResidentScales && !GATE_UP && (KB & 3) == 0 && KB <= 16;
+  const int KB_ = p.k >> 7;
+  const bool tile_regs = kTileResidentScales && !GATE_UP && (KB_ & 3) == 0 && KB_ <= 16;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -175,6 +173,11 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr;
+  griddep_wait();  // everything below reads what earlier kernels of the call wrote
+  int nb = *p.num_blocks;
+  if (nb > p.max_blocks) nb = p.max_blocks;
+  const int tiles_per_block = GATE_UP ? (p.out_dim >> 7) : (p.out_dim >> 8);
+  const int total_tiles = nb * tiles_per_block;
 
   if (warp == 0) {
     // ------------------------------- TMA producer ------------------------------------------
@@ -561,6 +564,8 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
 // Four lanes x 8 values per 1 x 32 group: rows
 // gathered through the sorted route table, e4m3 codes row-major, scale bytes in tcgen05.cp order.
 __global__ void __launch_bounds__(256) gather_quant_mxfp8_kernel(MxQuantParams p) {
+  griddep_launch();
+  griddep_wait();
   const int groups_per_row = p.hidden >> 5;
   const int n_rows = p.num_rows ? min(*p.num_rows, p.n_rows) : p.n_rows;
   const int64_t total = static_cast<int64_t>(n_rows) * groups_per_row;
@@ -622,6 +627,8 @@ __global__ void __launch_bounds__(256) gather_quant_mxfp8_kernel(MxQuantParams p
 constexpr int kGatherRows = 4;
 __global__ void __launch_bounds__(256) gather_rows_mxfp8_kernel(MxQuantParams p) {
   __shared__ int src_s[kGatherRows];
+  griddep_launch();
+  griddep_wait();
   const int vec_per_row = p.hidden >> 4;
   const int KB = p.hidden >> 7;
   const int n_rows = p.num_rows ? min(*p.num_rows, p.n_rows) : p.n_rows;
@@ -673,14 +680,12 @@ int launch_gather_quant_mxfp8(const MxQuantParams& p, cudaStream_t stream) {
     if (!p.sorted_ids || !p.scales_in) return AKLR_ERR_BAD_ARGUMENT;
     const int64_t blocks = (static_cast<int64_t>(p.n_rows) + kGatherRows - 1) / kGatherRows;
     const int grid = static_cast<int>(blocks < 148 * 32 ? blocks : 148 * 32);
-    gather_rows_mxfp8_kernel<<<grid, 256, 0, stream>>>(p);
-    return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+    return launch_kernel(gather_rows_mxfp8_kernel, dim3(grid), dim3(256), 0, stream, 1, p) == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
   }
   const int64_t groups = static_cast<int64_t>(p.n_rows) * (p.hidden / 32);
   const int64_t blocks = (groups * 4 + 255) / 256;
   const int grid = static_cast<int>(blocks < 148 * 16 ? blocks : 148 * 16);
-  gather_quant_mxfp8_kernel<<<grid, 256, 0, stream>>>(p);
-  return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+  return launch_kernel(gather_quant_mxfp8_kernel, dim3(grid), dim3(256), 0, stream, 1, p) == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
 }
 
 int grouped_gemm_mx_pick_stages(bool gate_up) {
@@ -698,8 +703,7 @@ int launch_grouped_gemm_mx(const MxGemmParams& p, bool gate_up, int sm_count, cu
   const int grid = static_cast<int>(tiles < sm_count ? tiles : sm_count);
   auto run = [&](auto kernel) {
     if (ensure_max_dynamic_smem(reinterpret_cast<const void*>(kernel)) != AKLR_OK) return AKLR_ERR_CUDA;
-    kernel<<<grid, kThreads, smem, stream>>>(p);
-    return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+    return launch_kernel(kernel, dim3(grid), dim3(kThreads), smem, stream, 1, p) == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
   };
   return gate_up ? run(grouped_gemm_mx_kernel<true>) : run(grouped_gemm_mx_kernel<false>);
 }

@@ -154,11 +154,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
   // tiles are dealt to CTAs (or CTA pairs) round-robin
   const int worker = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
   const int n_workers = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
-  int nb = PAIR ? p.num_blocks[2] : p.num_blocks[0];  // units: runs of <= 2 blocks, or blocks
-  if (nb > p.max_blocks) nb = p.max_blocks;
-  // gate_up: one tile per 128 intermediate channels (128 gate + 128 up rows); down: per 256 channels
-  const int tiles_per_block = GATE_UP ? (p.out_dim >> 7) : (p.out_dim >> 8);
-  const int total_tiles = nb * tiles_per_block;
+  griddep_launch();
   // unit u -> this CTA's token block and whether it is a real one
   auto block_of = [&](int u, bool* live) -> int {
     if (!PAIR) { *live = true; return u; }
@@ -193,6 +189,12 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
   if (PAIR) cluster_sync_all();  // the partner's barriers exist before anything arrives on them
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr;
+  griddep_wait();  // everything below reads what earlier kernels of the call wrote
+  int nb = PAIR ? p.num_blocks[2] : p.num_blocks[0];  // units: runs of <= 2 blocks, or blocks
+  if (nb > p.max_blocks) nb = p.max_blocks;
+  // gate_up: one tile per 128 intermediate channels (128 gate + 128 up rows); down: per 256 channels
+  const int tiles_per_block = GATE_UP ? (p.out_dim >> 7) : (p.out_dim >> 8);
+  const int total_tiles = nb * tiles_per_block;
 
   // The accumulators of a 128 x 256 tile are 128 registers per epilogue thread, and the loads that
   // drain TMEM want 64 more in flight: the producer warpgroup hands its registers over.
@@ -596,26 +598,13 @@ int launch_grouped_gemm_prefill(const GroupedGemmParams& p, bool gate_up, bool p
     if (ensure_max_dynamic_smem(reinterpret_cast<const void*>(kernel)) != AKLR_OK) return AKLR_ERR_CUDA;
     if (!pair) {
       const int grid = static_cast<int>(tiles < sm_count ? tiles : sm_count);
-      kernel<<<grid, kThreads, smem, stream>>>(p);
-      return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+      return launch_kernel(kernel, dim3(grid), dim3(kThreads), smem, stream, 1, p) == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
     }
     int pairs = max_active_pairs(kernel, smem);
     if (pairs < 1) return AKLR_ERR_CUDA;
     if (pairs > sm_count / 2) pairs = sm_count / 2;
     if (tiles < pairs) pairs = static_cast<int>(tiles);
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(2 * pairs, 1, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr{};
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = 2;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kernel, p) == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+    return launch_kernel(kernel, dim3(2 * pairs), dim3(kThreads), smem, stream, 2, p) == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
   };
   if (pair) return gate_up ? run(grouped_gemm_prefill_kernel<true, true>) : run(grouped_gemm_prefill_kernel<false, true>);
   return gate_up ? run(grouped_gemm_prefill_kernel<true, false>) : run(grouped_gemm_prefill_kernel<false, false>);

@@ -2,6 +2,7 @@
 #pragma once
 
 #include <cuda.h>
+#include <utility>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -164,6 +165,36 @@ int launch_router_gemm_tc(const CUtensorMap& map_x, const CUtensorMap& map_w, vo
 
 // Opt a kernel in to the full 227 KB of dynamic shared memory, once per (kernel, device).
 int ensure_max_dynamic_smem(const void* kernel);
+
+// Launch, with programmatic stream serialisation (see griddep_wait in common.cuh) when AKLR_PDL=1 is
+// in the environment (off by default: no measured gain).  ``cluster`` > 1 adds a cluster dimension.
+bool pdl_enabled();
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 int cluster, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  int n = 0;
+  if (pdl_enabled()) {
+    attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster > 1) {
+    attrs[n].id = cudaLaunchAttributeClusterDimension;
+    attrs[n].val.clusterDim.x = static_cast<unsigned>(cluster);
+    attrs[n].val.clusterDim.y = 1;
+    attrs[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 int launch_router_gemm(const void* x_bf16, const void* w_bf16, void* logits_bf16, int n_tokens, int hidden,
                        int n_routed, cudaStream_t stream);

@@ -42,6 +42,8 @@ __device__ __forceinline__ uint2 pack8_e4m3(const float (&v)[8]) {
 
 // One half-warp (16 lanes x 8 values) per 1 x 128 group.
 __global__ void __launch_bounds__(256) gather_quant_fp8_kernel(GatherQuantParams p) {
+  griddep_launch();
+  griddep_wait();
   const int groups_per_row = p.hidden >> 7;
   const int n_rows = p.num_rows ? min(*p.num_rows, p.n_rows) : p.n_rows;
   const int64_t total = static_cast<int64_t>(n_rows) * groups_per_row;
@@ -85,6 +87,8 @@ constexpr int kGatherRows = 4;
 
 __global__ void __launch_bounds__(256) gather_rows_fp8_kernel(GatherQuantParams p) {
   __shared__ int src_s[kGatherRows];
+  griddep_launch();
+  griddep_wait();
   const int vec_per_row = p.hidden >> 4;
   const int groups_per_row = p.hidden >> 7;
   const int n_rows = p.num_rows ? min(*p.num_rows, p.n_rows) : p.n_rows;
@@ -125,8 +129,7 @@ int launch_gather_rows_fp8(const GatherQuantParams& p, cudaStream_t stream) {
   if (p.n_rows == 0) return AKLR_OK;
   const int64_t blocks = (static_cast<int64_t>(p.n_rows) + kGatherRows - 1) / kGatherRows;
   const int grid = static_cast<int>(blocks < 148 * 32 ? blocks : 148 * 32);
-  gather_rows_fp8_kernel<<<grid, 256, 0, stream>>>(p);
-  return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+  return launch_kernel(gather_rows_fp8_kernel, dim3(grid), dim3(256), 0, stream, 1, p) == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
 }
 
 int launch_gather_quant_fp8(const GatherQuantParams& p, cudaStream_t stream) {
@@ -135,8 +138,7 @@ int launch_gather_quant_fp8(const GatherQuantParams& p, cudaStream_t stream) {
   const int64_t groups = static_cast<int64_t>(p.n_rows) * (p.hidden / 128);
   const int64_t blocks = (groups * 16 + 255) / 256;
   const int grid = static_cast<int>(blocks < 148 * 16 ? blocks : 148 * 16);
-  gather_quant_fp8_kernel<<<grid, 256, 0, stream>>>(p);
-  return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+  return launch_kernel(gather_quant_fp8_kernel, dim3(grid), dim3(256), 0, stream, 1, p) == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
 }
 
 __global__ void __launch_bounds__(256)

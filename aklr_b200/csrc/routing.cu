@@ -41,6 +41,8 @@ __global__ void __launch_bounds__(256) route_kernel(RouteParams p) {
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const int token = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  griddep_launch();
+  griddep_wait();
   if (token >= p.n_tokens) return;
   const int E = p.n_routed;
   const int ktot = p.topk + p.n_shared;
@@ -189,13 +191,14 @@ int launch_route(const RouteParams& p, cudaStream_t stream) {
   const int threads = 256, warps = threads / 32;
   const int blocks = (p.n_tokens + warps - 1) / warps;
   const int vpt = (p.n_routed + 31) / 32;
-  if (vpt <= 1) route_kernel<1><<<blocks, threads, 0, stream>>>(p);
-  else if (vpt <= 2) route_kernel<2><<<blocks, threads, 0, stream>>>(p);
-  else if (vpt <= 4) route_kernel<4><<<blocks, threads, 0, stream>>>(p);
-  else if (vpt <= 8) route_kernel<8><<<blocks, threads, 0, stream>>>(p);
-  else if (vpt <= 16) route_kernel<16><<<blocks, threads, 0, stream>>>(p);
-  else route_kernel<32><<<blocks, threads, 0, stream>>>(p);
-  return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+  cudaError_t err = cudaSuccess;
+  if (vpt <= 1) err = launch_kernel(route_kernel<1>, dim3(blocks), dim3(threads), 0, stream, 1, p);
+  else if (vpt <= 2) err = launch_kernel(route_kernel<2>, dim3(blocks), dim3(threads), 0, stream, 1, p);
+  else if (vpt <= 4) err = launch_kernel(route_kernel<4>, dim3(blocks), dim3(threads), 0, stream, 1, p);
+  else if (vpt <= 8) err = launch_kernel(route_kernel<8>, dim3(blocks), dim3(threads), 0, stream, 1, p);
+  else if (vpt <= 16) err = launch_kernel(route_kernel<16>, dim3(blocks), dim3(threads), 0, stream, 1, p);
+  else err = launch_kernel(route_kernel<32>, dim3(blocks), dim3(threads), 0, stream, 1, p);
+  return err == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
 }
 
 // =============================================================================================
@@ -213,6 +216,8 @@ __device__ __forceinline__ int local_expert(const AlignParams& p, int route) {
 // Pass 1: histogram of each 1024-route chunk -> chunk_hist[chunk][expert]
 __global__ void __launch_bounds__(kSortChunk) align_count_kernel(AlignParams p) {
   extern __shared__ int hist[];
+  griddep_launch();
+  griddep_wait();
   for (int e = threadIdx.x; e < p.n_experts; e += blockDim.x) hist[e] = 0;
   __syncthreads();
   const int route = blockIdx.x * kSortChunk + threadIdx.x;
@@ -332,6 +337,8 @@ __device__ void place_chunk(const AlignParams& p, int route, int* cursor) {
 // Pass 2 (one CTA): per-expert totals, per-chunk offsets, block table.
 __global__ void __launch_bounds__(1024) align_scan_kernel(AlignParams p, int n_chunks) {
   extern __shared__ int sm[];
+  griddep_launch();
+  griddep_wait();
   int* total = sm;                  // [n_experts]
   int* base = sm + p.n_experts;     // [n_experts]
   int* scratch = base + p.n_experts;  // [blockDim]
@@ -354,6 +361,8 @@ __global__ void __launch_bounds__(1024) align_scan_kernel(AlignParams p, int n_c
 // Pass 3: scatter each chunk
 __global__ void __launch_bounds__(kSortChunk) align_scatter_kernel(AlignParams p) {
   extern __shared__ int cursor[];
+  griddep_launch();
+  griddep_wait();
   for (int e = threadIdx.x; e < p.n_experts; e += blockDim.x)
     cursor[e] = p.chunk_hist[static_cast<size_t>(blockIdx.x) * p.n_experts + e];
   __syncthreads();
@@ -364,6 +373,8 @@ __global__ void __launch_bounds__(kSortChunk) align_scatter_kernel(AlignParams p
 constexpr int kSmallRoutes = 4096;
 __global__ void __launch_bounds__(kSortChunk) align_small_kernel(AlignParams p) {
   extern __shared__ int sm[];
+  griddep_launch();
+  griddep_wait();
   int* total = sm;
   int* base = sm + p.n_experts;
   int* scratch = base + p.n_experts;
@@ -384,15 +395,17 @@ __global__ void __launch_bounds__(kSortChunk) align_small_kernel(AlignParams p) 
 int launch_align(const AlignParams& p, cudaStream_t stream) {
   if (p.n_experts < 1 || p.n_experts > 2048 || p.block_m < 1) return AKLR_ERR_UNSUPPORTED_SHAPE;
   const size_t smem = (2 * static_cast<size_t>(p.n_experts) + 1024) * sizeof(int);
+  cudaError_t err = cudaSuccess;
   if (p.n_routes <= kSmallRoutes) {
-    align_small_kernel<<<1, kSortChunk, smem, stream>>>(p);
+    err = launch_kernel(align_small_kernel, dim3(1), dim3(kSortChunk), smem, stream, 1, p);
   } else {
     const int chunks = (p.n_routes + kSortChunk - 1) / kSortChunk;
-    align_count_kernel<<<chunks, kSortChunk, p.n_experts * sizeof(int), stream>>>(p);
-    align_scan_kernel<<<1, 1024, smem, stream>>>(p, chunks);
-    align_scatter_kernel<<<chunks, kSortChunk, p.n_experts * sizeof(int), stream>>>(p);
+    err = launch_kernel(align_count_kernel, dim3(chunks), dim3(kSortChunk), p.n_experts * sizeof(int), stream, 1, p);
+    if (err == cudaSuccess) err = launch_kernel(align_scan_kernel, dim3(1), dim3(1024), smem, stream, 1, p, chunks);
+    if (err == cudaSuccess)
+      err = launch_kernel(align_scatter_kernel, dim3(chunks), dim3(kSortChunk), p.n_experts * sizeof(int), stream, 1, p);
   }
-  return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+  return err == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
 }
 
 }  // namespace aklr
