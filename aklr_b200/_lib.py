@@ -63,6 +63,7 @@ SIGNATURES = {
     "aklr_moe_mxfp4_forward": (c_int32, [POINTER(MoeConfig)] + [c_void_p] * 8 + [c_float, c_void_p, c_void_p, c_size_t, c_void_p]),
     "aklr_ep_gather_quant_mxfp8": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p]),
     "aklr_moe_mxfp4_experts_prequant": (c_int32, [POINTER(MoeConfig)] + [c_void_p] * 8 + [c_float, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "aklr_ep_gather_rows": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p]),
     "aklr_ep_gather_quant": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p]),
     "aklr_ep_dispatch_meta": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p]),
     "aklr_moe_fp8_experts_prequant": (c_int32, [POINTER(MoeConfig)] + [c_void_p] * 9 + [c_void_p, c_size_t, c_void_p]),

@@ -722,6 +722,42 @@ int aklr_ep_gather_quant(const void* hidden_states, const int32_t* sorted_ids, i
   return AKLR_OK;
 }
 
+int aklr_ep_gather_rows(const void* tokens_q, const void* tokens_scale, const int32_t* sorted_ids, int32_t n_send,
+                        int32_t hidden, int32_t routes_per_token, int32_t mx, void* rows_q, void* rows_scale,
+                        void* stream) {
+  if (!tokens_q || !tokens_scale || !sorted_ids || !rows_q || !rows_scale) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
+  int rc = check_device();
+  if (rc) return rc;
+  if (mx) {
+    aklr::MxQuantParams p{};
+    p.sorted_ids = sorted_ids;
+    p.q = static_cast<uint8_t*>(rows_q);
+    p.scales = static_cast<uint8_t*>(rows_scale);
+    p.q_in = static_cast<const uint8_t*>(tokens_q);
+    p.scales_in = static_cast<const uint8_t*>(tokens_scale);
+    p.n_rows = n_send;
+    p.hidden = hidden;
+    p.routes_per_token = routes_per_token;
+    p.row_major_scales = 1;
+    rc = aklr::launch_gather_quant_mxfp8(p, static_cast<cudaStream_t>(stream));
+  } else {
+    aklr::GatherQuantParams p{};
+    p.sorted_ids = sorted_ids;
+    p.q = static_cast<uint8_t*>(rows_q);
+    p.scales = static_cast<float*>(rows_scale);
+    p.q_in = static_cast<const uint8_t*>(tokens_q);
+    p.scales_in = static_cast<const float*>(tokens_scale);
+    p.n_rows = n_send;
+    p.hidden = hidden;
+    p.routes_per_token = routes_per_token;
+    p.block_m = 1;  // [row, hidden/128] scales
+    rc = aklr::launch_gather_rows_fp8(p, static_cast<cudaStream_t>(stream));
+  }
+  if (rc) return fail(rc, "ep gather rows: %s", aklr_status_string(rc));
+  g_launches += n_send > 0;
+  return AKLR_OK;
+}
+
 int aklr_ep_combine(const void* rows, const int32_t* position_of_route, const void* shared_rows, void* out,
                     int32_t n_tokens, int32_t topk, int32_t hidden, void* stream) {
   if (!position_of_route || !out) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");

@@ -657,8 +657,12 @@ __global__ void __launch_bounds__(256) gather_rows_mxfp8_kernel(MxQuantParams p)
       const int row = row0 + r;
       if (src_s[r] >= 0) {
         const uint32_t word = __ldg(reinterpret_cast<const uint32_t*>(p.scales_in + static_cast<size_t>(src_s[r]) * (KB * 4)) + kb);
-        const int b = row >> 7, rr = row & 127;
-        *reinterpret_cast<uint32_t*>(p.scales + (static_cast<size_t>(b) * KB + kb) * kSfaBytes + (rr & 31) * 16 + (rr >> 5) * 4) = word;
+        if (p.row_major_scales) {  // for transport to another rank: [row, hidden/32]
+          *reinterpret_cast<uint32_t*>(p.scales + static_cast<size_t>(row) * (KB * 4) + kb * 4) = word;
+        } else {
+          const int b = row >> 7, rr = row & 127;
+          *reinterpret_cast<uint32_t*>(p.scales + (static_cast<size_t>(b) * KB + kb) * kSfaBytes + (rr & 31) * 16 + (rr >> 5) * 4) = word;
+        }
       }
     }
     __syncthreads();

@@ -100,12 +100,25 @@ class CudaKernels:
         rows_q = torch.empty((n_send, h), dtype=torch.uint8, device=device)
         meta = torch.empty((2, n_send), dtype=torch.int32, device=device)
         position = torch.full((ids.numel(),), -1, dtype=torch.int32, device=device)
-        if self.fmt == "mxfp4":
-            rows_scale = torch.empty((n_send, h // 32), dtype=torch.uint8, device=device)
-            _lib.check(lib.aklr_ep_gather_quant_mxfp8(_ptr(hidden), _ptr(sorted_ids), n_send, h, ids.shape[1], _ptr(rows_q), _ptr(rows_scale), _stream()))
+        mx = self.fmt == "mxfp4"
+        quant = lib.aklr_ep_gather_quant_mxfp8 if mx else lib.aklr_ep_gather_quant
+        scale_shape = (h // 32, torch.uint8) if mx else (h // 128, torch.float32)
+        rows_scale = torch.empty((n_send, scale_shape[0]), dtype=scale_shape[1], device=device)
+        n_tokens, topk = hidden.shape[0], ids.shape[1]
+        if topk > 1 and n_tokens >= 512:
+            # a token's routes carry the same quantised row: quantise each token once, then copy
+            identity = torch.arange(n_tokens, dtype=torch.int32, device=device)
+            tokens_q = torch.empty((n_tokens, h), dtype=torch.uint8, device=device)
+            tokens_scale = torch.empty((n_tokens, scale_shape[0]), dtype=scale_shape[1], device=device)
+            _lib.check(quant(_ptr(hidden), _ptr(identity), n_tokens, h, 1, _ptr(tokens_q), _ptr(tokens_scale), _stream()))
+            _lib.check(
+                lib.aklr_ep_gather_rows(
+                    _ptr(tokens_q), _ptr(tokens_scale), _ptr(sorted_ids), n_send, h, topk, int(mx), _ptr(rows_q),
+                    _ptr(rows_scale), _stream(),
+                )
+            )
         else:
-            rows_scale = torch.empty((n_send, h // 128), dtype=torch.float32, device=device)
-            _lib.check(lib.aklr_ep_gather_quant(_ptr(hidden), _ptr(sorted_ids), n_send, h, ids.shape[1], _ptr(rows_q), _ptr(rows_scale), _stream()))
+            _lib.check(quant(_ptr(hidden), _ptr(sorted_ids), n_send, h, topk, _ptr(rows_q), _ptr(rows_scale), _stream()))
         _lib.check(
             lib.aklr_ep_dispatch_meta(
                 _ptr(sorted_ids), _ptr(ids), _ptr(weights), n_send, ids.numel(), n_local, meta[0].data_ptr(),

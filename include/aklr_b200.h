@@ -153,6 +153,12 @@ int aklr_moe_fp8_experts_prequant(const aklr_moe_config* cfg, const void* rows_q
                                   void* workspace, size_t workspace_bytes, void* stream);
 /* The MXFP4 counterparts for `mega_moe` (MXFP8 rows travel with one e8m0 byte per 32 values,
  * rows_scale uint8 [n, H/32] row-major). */
+/* The same packing from rows quantised once per token (aklr_ep_gather_quant[_mxfp8] with the
+ * identity table and routes_per_token 1): copies token rid / routes_per_token's codes and row-major
+ * scales to send position.  mx = 0: float scales [*, H/128]; mx = 1: e8m0 bytes [*, H/32]. */
+int aklr_ep_gather_rows(const void* tokens_q, const void* tokens_scale, const int32_t* sorted_ids, int32_t n_send,
+                        int32_t hidden, int32_t routes_per_token, int32_t mx, void* rows_q, void* rows_scale,
+                        void* stream);
 int aklr_ep_gather_quant_mxfp8(const void* hidden_states, const int32_t* sorted_ids, int32_t n_send, int32_t hidden,
                                int32_t routes_per_token, void* rows_q, uint8_t* rows_scale, void* stream);
 int aklr_moe_mxfp4_experts_prequant(const aklr_moe_config* cfg, const void* rows_q, const uint8_t* rows_scale,

@@ -18,7 +18,7 @@ def routing_of(cfg):
     return Routing(cfg.topk, cfg.scoring, cfg.n_shared, cfg.num_expert_group, cfg.topk_group, cfg.renormalize, cfg.routed_scaling_factor)
 
 
-@pytest.mark.parametrize("world,tokens", [(2, (33, 7)), (4, (16, 1, 40, 5)), (8, (3,) * 8)])
+@pytest.mark.parametrize("world,tokens", [(2, (33, 7)), (4, (16, 1, 40, 5)), (8, (3,) * 8), (2, (600, 520))])
 def test_emulated_ranks_match_single_gpu_and_oracle(world, tokens):
     from aklr_b200.ep import ExpertParallelMoE, run_in_process
     from aklr_b200.moe import fused_moe_fp8
@@ -45,5 +45,11 @@ def test_emulated_ranks_match_single_gpu_and_oracle(world, tokens):
         )
         gates = orc.output_gates(outs[r].cpu(), ref)
         assert orc.gates_pass(gates), (r, gates)
-        # same kernels, same per-token arithmetic, same summation order: the same bits
-        assert torch.equal(outs[r], single), f"rank {r} differs from the single-GPU layer"
+        if max(tokens) < 512:
+            # same kernels, same per-token arithmetic, same summation order: the same bits
+            assert torch.equal(outs[r], single), f"rank {r} differs from the single-GPU layer"
+        else:
+            # from 512 tokens up the sender quantises each token once and copies rows; the two sides may
+            # also pick different block sizes (different grouped-GEMM kernels), so compare closely
+            close = orc.output_gates(outs[r].cpu(), single.cpu().float())
+            assert close["sqnr_db"] > 45.0, (r, close)

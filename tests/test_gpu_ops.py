@@ -163,3 +163,18 @@ def test_mega_moe_op_single_rank_and_emulated_group(ops):
         ref = orc.mx_experts(xr, idr.long(), wtr, w1, s1, w2, s2, swiglu_limit=10.0)
         gates = orc.output_gates(outs[r].cpu(), ref)
         assert orc.gates_pass(gates), (r, gates)
+
+    # from 512 tokens per rank the sender quantises each token once and copies its rows per route
+    world, layers, ins = 2, [], []
+    for r in range(world):
+        mine = slice(4 * r, 4 * r + 4)
+        layers.append(ExpertParallelMoE(Routing(topk=2), w1[mine].to(d), s1[mine].to(d), w2[mine].to(d), s2[mine].to(d), r, world,
+                                        kernels=CudaKernels("mxfp4", 10.0)))
+        xr, idr, wtr = inputs(40 + r, 520 + 80 * r)
+        ins.append((xr.to(d), None, None, (idr.to(d), wtr.to(d))))
+    outs = run_in_process(layers, ins)
+    for r in range(world):
+        xr, idr, wtr = inputs(40 + r, 520 + 80 * r)
+        ref = orc.mx_experts(xr, idr.long(), wtr, w1, s1, w2, s2, swiglu_limit=10.0)
+        gates = orc.output_gates(outs[r].cpu(), ref)
+        assert orc.gates_pass(gates), (r, gates)
