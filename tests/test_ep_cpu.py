@@ -67,6 +67,9 @@ def _worker(rank: int, world: int, port: int, results):
     try:
         weights = wl.expert_weights(CFG, seed=60)
         out = rank_layer(rank, world, weights).forward(*rank_inputs(rank))
+        # the same step as three interleaved parts gives every token the same result
+        split = rank_layer(rank, world, weights).forward(*rank_inputs(rank), micro_batches=3)
+        assert torch.equal(split, out)
         gates = orc.output_gates(out, reference_output(weights, rank))
         results.put((rank, tuple(out.shape), gates))
     finally:
