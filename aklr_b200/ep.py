@@ -439,7 +439,7 @@ def bench_ep(args, cfg, rank, world, device, clock_sampler, workload_config, met
         },
         "gpu_launches": int(launches),
         "roofline": {
-            "kernel": "grouped_gemm_kernel<gate_up> over the rows a rank receives (rank 0)",
+            "kernel": "grouped_gemm_prefill_kernel<gate_up> over the rows a rank receives (rank 0)",
             "bound": "hbm",
             "achieved": achieved,
             "peak": peak,

@@ -27,6 +27,9 @@ import time
 import torch
 
 ROOT = pathlib.Path(__file__).resolve().parent
+# gate_up grouped GEMM: measured DRAM traffic / algorithmic bytes in the ncu captures summarised in
+# profiles/grouped_gemm_prefill_t1024_e64.md (2.157 GB / 2.02 GB) and profiles/grouped_gemm_decode_t64_e64.md (ratio 1.03)
+TRAFFIC_PER_ALGORITHMIC_BYTE = {"prefill": 1.068, "decode": 1.03}
 sys.path.insert(0, str(ROOT))
 
 from aklr_b200 import workloads as wl  # noqa: E402
@@ -348,15 +351,23 @@ def main() -> None:
     peak, peak_kind = measured_peak_hbm()
     achieved = gate_up_bytes / (stage_ms[3] * 1e-3) / 1e9
     flops, layer_bytes = wl.roofline_work(cfg, T, experts_hit)
+    token_major = ws.layout.block_m == 128
+    # DRAM bytes of this kernel per launch: ncu (dram__bytes_read + dram__bytes_write) on the small
+    # capture of the same kernel divided by that capture's algorithmic bytes, times this launch's
+    # algorithmic bytes (traffic grows with the weights streamed; see profiles/)
+    traffic_ratio = TRAFFIC_PER_ALGORITHMIC_BYTE["prefill" if token_major else "decode"]
     roofline = {
-        "kernel": "grouped_gemm_kernel<gate_up> (tcgen05 FP8, SiLU*mul + requant epilogue)",
+        "kernel": ("grouped_gemm_prefill_kernel<gate_up>" if token_major else "grouped_gemm_kernel<gate_up>")
+        + " (tcgen05 FP8, SiLU*mul + requant epilogue)",
         "bound": "hbm",
         "achieved": achieved,
         "peak": peak,
         "peak_kind": f"of {peak_kind}",
         "unit": "GB/s",
         "frac": achieved / peak,
-        "traffic": None,
+        "traffic": gate_up_bytes * traffic_ratio,
+        "traffic_source": f"ncu capture of a smaller case of the same kernel: {traffic_ratio:.3f} x algorithmic bytes",
+        "block_m": ws.layout.block_m,
         "algorithmic_bytes_per_launch": gate_up_bytes,
         "ms_per_launch": stage_ms[3],
         "tflops": routes * 4 * h * i_dim / (stage_ms[3] * 1e-3) / 1e12,
