@@ -370,6 +370,30 @@ def test_deepseek_v3_full_width_on_sampled_tokens(n_tokens):
     assert torch.equal(out2.cpu(), out.cpu()[perm])
 
 
+@pytest.mark.parametrize("n_tokens", [16, 1024])
+def test_mixtral_full_width_on_sampled_tokens(n_tokens):
+    """Mixtral-8x7B widths (hidden 4096, intermediate 14336, 8 experts, top-2 softmax): the long
+    reduction of the down projection (112 K-blocks) through the weight-major (16 tokens) and the
+    token-major (1024 tokens) kernels, against the oracle on a sample of tokens."""
+    from aklr_b200.moe import fused_moe_fp8
+
+    cfg = wl.CONFIGS["mixtral"]
+    d = dev()
+    w1, s1, w2, s2 = wl.expert_weights(cfg, seed=51, device=d)
+    hidden, logits, _ = wl.router_inputs(cfg, n_tokens, seed=52)
+    out, ws = fused_moe_fp8(hidden.to(d), logits.to(d), None, w1, s1, w2, s2, routing_of(cfg), return_workspace=True)
+    ws.check_status()
+    ref_ids, ref_w = orc.softmax_topk(logits.float(), cfg.topk)
+    assert torch.equal(ws.topk_ids().cpu().long(), ref_ids)
+    assert torch.equal(ws.counts().cpu().long(), torch.bincount(ref_ids.flatten(), minlength=cfg.n_experts))
+    sample = torch.tensor([0, n_tokens // 2, n_tokens - 1])
+    ref = orc.fp8_experts(
+        hidden[sample], ref_ids[sample], ref_w[sample], _LazyExperts(w1), _LazyExperts(s1), _LazyExperts(w2), _LazyExperts(s2)
+    )
+    gates = orc.output_gates(out[sample.to(d)].cpu(), ref)
+    assert orc.gates_pass(gates), gates
+
+
 def test_token_major_and_weight_major_kernels_agree(golden):
     """Full 128-token blocks run the token-major grouped GEMM; forcing the weight-major one on the
     same inputs must pass the same gates and agree closely."""
