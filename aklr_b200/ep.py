@@ -369,12 +369,14 @@ def bench_ep(args, cfg, rank, world, device, clock_sampler, workload_config, met
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)  # the slowest rank's device time
         return float(ms) / steps
 
+    sampler = clock_sampler(device.index) if rank == 0 else None
     for i in range(args.warmup):
         step(i)
     torch.cuda.synchronize()
     lib.aklr_profile_begin(0 if mx else 2 * args.steps)
     launches0 = lib.aklr_kernel_launch_count()
-    sampler = clock_sampler(device.index) if rank == 0 else None
+    if sampler:
+        sampler.begin()
     ms_per_step = timed(lambda i: step(args.warmup + i), args.steps)
     clocks = sampler.stop() if sampler else None
     launches = lib.aklr_kernel_launch_count() - launches0

@@ -51,10 +51,11 @@ def measured_peak_hbm() -> tuple[float, str]:
 
 
 class ClockSampler:
-    """nvidia-smi sampled every 200 ms while the timed region runs."""
+    """nvidia-smi sampled every 50 ms, started before the warm-up so that it is already running;
+    only samples stamped between begin() and stop() -- the timed region -- count."""
 
     FIELDS = (
-        "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+        "timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
     )
@@ -62,19 +63,24 @@ class ClockSampler:
     def __init__(self, gpu_index: int):
         self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
         self.proc = None
+        self.t0 = time.time()
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(gpu_index)],
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50", "-i", str(gpu_index)],
                 stdout=self.file,
                 stderr=subprocess.DEVNULL,
             )
         except OSError:
             self.proc = None
 
+    def begin(self) -> None:
+        self.t0 = time.time()
+
     def stop(self) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.25)
+        t1 = time.time()
+        time.sleep(0.1)  # let the sample in flight land
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -82,21 +88,26 @@ class ClockSampler:
             self.proc.kill()
         self.file.flush()
         self.file.seek(0)
-        sm, sm_max, reasons = [], [], set()
+        import datetime
+
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = []
         for line in self.file.read().splitlines():
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 9:
                 continue
             try:
-                sm.append(float(parts[1]))
-                sm_max.append(float(parts[2]))
+                stamp = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((stamp, float(parts[1]), float(parts[2]), parts[5:9]))
             except ValueError:
                 continue
-            for name, flag in zip(names, parts[5:9]):
+        os.unlink(self.file.name)
+        inside = [r for r in rows if self.t0 <= r[0] <= t1] or rows  # a region shorter than the period: all samples
+        sm, sm_max, reasons = [r[1] for r in inside], [r[2] for r in inside], set()
+        for r in inside:
+            for name, flag in zip(names, r[3]):
                 if flag.lower().startswith("active"):
                     reasons.add(name)
-        os.unlink(self.file.name)
         return {
             "sm_mhz": statistics.median(sm) if sm else None,
             "sm_max_mhz": max(sm_max) if sm_max else None,
@@ -310,6 +321,7 @@ def main() -> None:
         hidden, logits = batches[i % n_batches]
         fused_moe_fp8(hidden, logits, bias, w1, s1, w2, s2, routing, out=out, workspace=ws, block_m=args.block_m)
 
+    sampler = ClockSampler(local_rank)
     for i in range(args.warmup):
         step(i)
     ws.check_status()
@@ -318,9 +330,9 @@ def main() -> None:
     # ---- timed region: K steps, CUDA events on the launching stream, clocks sampled meanwhile ----
     lib.aklr_profile_begin(args.steps)
     launches0 = lib.aklr_kernel_launch_count()
-    sampler = ClockSampler(local_rank)
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
+    sampler.begin()
     start.record()
     for i in range(args.steps):
         step(args.warmup + i)
@@ -442,10 +454,12 @@ def main() -> None:
                 result.record_stream(copy_out)
                 out_free[k].record(copy_out)
 
+        e2e_sampler = ClockSampler(local_rank)
         for i in range(args.warmup):
             e2e_step(i)
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e2e_sampler.begin()
         e0.record(compute)
         for i in range(args.steps):
             e2e_step(i)
@@ -453,6 +467,7 @@ def main() -> None:
         compute.wait_stream(copy_in)
         e1.record(compute)
         torch.cuda.synchronize()
+        e2e_clocks = e2e_sampler.stop()
         e2e_ms = e0.elapsed_time(e1) / args.steps
         e2e = {
             "value": T / (e2e_ms * 1e-3),
@@ -461,6 +476,7 @@ def main() -> None:
             "h2d_bytes_per_step": T * cfg.hidden * 2,
             "d2h_bytes_per_step": T * cfg.hidden * 2,
             "api": "aklr_b200.ops.deepseek_v2_fp8_moe (router GEMM included); copies double-buffered on their own streams",
+            "clocks": e2e_clocks,
         }
 
     sweep = None
@@ -562,14 +578,15 @@ def bench_mxfp4(args, cfg, routing, device, lib):
         hidden, logits = batches[i % 4]
         fused_moe_mxfp4(hidden, logits, bias, w1, s1, w2, s2, routing, out=out, workspace=ws)
 
+    sampler = ClockSampler(device.index or 0)
     for i in range(args.warmup):
         step(i)
     ws.check_status()
     launches0 = lib.aklr_kernel_launch_count()
-    sampler = ClockSampler(device.index or 0)
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     lib.aklr_profile_begin(args.steps)
+    sampler.begin()
     start.record()
     for i in range(args.steps):
         step(args.warmup + i)
