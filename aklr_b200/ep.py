@@ -355,13 +355,15 @@ def bench_ep(args, cfg, rank, world, device, clock_sampler, workload_config, met
         hidden, logits = batches[i % n_batches]
         return layer.forward(hidden, logits, bias)
 
-    def timed(fn, steps):
+    def timed(fn, steps, before_stop=None):
         dist.barrier()
         torch.cuda.synchronize()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         for i in range(steps):
             fn(i)
+        if before_stop is not None:
+            before_stop()
         stop.record()
         torch.cuda.synchronize()
         dist.barrier()
@@ -389,19 +391,44 @@ def bench_ep(args, cfg, rank, world, device, clock_sampler, workload_config, met
             stage_ms[j] += buf[j] / args.steps
     lib.aklr_profile_begin(0)
 
-    # end to end from pinned host buffers: H2D of activations and logits, D2H of the output
+    # end to end from pinned host buffers: every step copies its activations and logits in and its
+    # output out; two buffers each way and two copy streams, so step i's input copy overlaps step
+    # i-1's tail and its output copy overlaps step i+1's head, as a serving loop would run it
     host = [(h.cpu().pin_memory(), lg.cpu().pin_memory()) for h, lg in batches]
-    dev_hidden, dev_logits = torch.empty_like(batches[0][0]), torch.empty_like(batches[0][1])
-    host_out = torch.empty((tokens, cfg.hidden), dtype=torch.bfloat16).pin_memory()
+    dev_hidden = [torch.empty_like(batches[0][0]) for _ in range(2)]
+    dev_logits = [torch.empty_like(batches[0][1]) for _ in range(2)]
+    host_out = [torch.empty((tokens, cfg.hidden), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    copy_in, copy_out, compute = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
+    in_ready = [torch.cuda.Event() for _ in range(2)]
+    in_free = [torch.cuda.Event() for _ in range(2)]
+    out_free = [torch.cuda.Event() for _ in range(2)]
 
     def e2e_step(i):
-        dev_hidden.copy_(host[i % n_batches][0], non_blocking=True)
-        dev_logits.copy_(host[i % n_batches][1], non_blocking=True)
-        host_out.copy_(layer.forward(dev_hidden, dev_logits, bias), non_blocking=True)
+        k = i & 1
+        with torch.cuda.stream(copy_in):
+            copy_in.wait_event(in_free[k])  # the step that last read these buffers is past them
+            dev_hidden[k].copy_(host[i % n_batches][0], non_blocking=True)
+            dev_logits[k].copy_(host[i % n_batches][1], non_blocking=True)
+            in_ready[k].record(copy_in)
+        compute.wait_event(in_ready[k])
+        result = layer.forward(dev_hidden[k], dev_logits[k], bias)
+        in_free[k].record(compute)
+        done = torch.cuda.Event()
+        done.record(compute)
+        with torch.cuda.stream(copy_out):
+            copy_out.wait_event(done)
+            copy_out.wait_event(out_free[k])
+            host_out[k].copy_(result, non_blocking=True)
+            result.record_stream(copy_out)
+            out_free[k].record(copy_out)
+
+    def drain():
+        compute.wait_stream(copy_out)
+        compute.wait_stream(copy_in)
 
     for i in range(args.warmup):
         e2e_step(i)
-    e2e_ms = timed(e2e_step, args.steps)
+    e2e_ms = timed(e2e_step, args.steps, before_stop=drain)
 
     if rank != 0:
         return None
@@ -437,7 +464,7 @@ def bench_ep(args, cfg, rank, world, device, clock_sampler, workload_config, met
             "ms_per_step": e2e_ms,
             "h2d_bytes_per_step": tokens * (cfg.hidden + cfg.n_routed) * 2,
             "d2h_bytes_per_step": tokens * cfg.hidden * 2,
-            "api": "aklr_b200.ep.ExpertParallelMoE.forward (from router logits), per rank",
+            "api": "aklr_b200.ep.ExpertParallelMoE.forward (from router logits), per rank; copies double-buffered on their own streams",
         },
         "gpu_launches": int(launches),
         "roofline": {
