@@ -855,6 +855,17 @@ int aklr_router_gemm_bf16(const void* x, const void* w, void* logits, int32_t n_
   return AKLR_OK;
 }
 
+int aklr_router_gemm_f32(const void* x, const float* w, float* logits, int32_t n_tokens, int32_t hidden,
+                         int32_t n_routed, void* stream) {
+  if (!x || !w || !logits) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
+  int rc = check_device();
+  if (rc) return rc;
+  rc = aklr::launch_router_gemm_f32(x, w, logits, n_tokens, hidden, n_routed, static_cast<cudaStream_t>(stream));
+  if (rc) return fail(rc, "router GEMM (float32 weights): %s", aklr_status_string(rc));
+  g_launches += n_tokens > 0;
+  return AKLR_OK;
+}
+
 int aklr_per_group_quant_fp8(const void* x, void* q, float* scales, int32_t rows, int32_t hidden, void* stream) {
   if (!x || !q || !scales) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
   int rc = check_device();

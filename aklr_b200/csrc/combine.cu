@@ -118,6 +118,95 @@ router_gemm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ 
   }
 }
 
+// Router with float32 weights and float32 logits (MiniMax-M2's gate:
+// aklr/plugins/sglang/models/minimax_m2/reference.py:43-50 takes x @ router^T in float32, nothing
+// rounded).  CUDA cores, float32 FMAs in k order.
+//  * few tokens: one warp per (token, expert) dot product, so the weight is read by many SMs;
+//  * else a 64 x 64 tile per CTA, 16 k per step through shared memory, 4 x 4 outputs per thread.
+__global__ void __launch_bounds__(256)
+router_dot_f32_kernel(const uint16_t* __restrict__ x, const float* __restrict__ w, float* __restrict__ logits,
+                      int n_tokens, int hidden, int n_routed) {
+  const int lane = threadIdx.x & 31;
+  const int64_t item = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= static_cast<int64_t>(n_tokens) * n_routed) return;
+  const int token = static_cast<int>(item / n_routed), e = static_cast<int>(item - static_cast<int64_t>(token) * n_routed);
+  float acc = 0.0f;
+  for (int h = lane * 4; h < hidden; h += 128) {
+    const uint2 xr = *reinterpret_cast<const uint2*>(x + static_cast<size_t>(token) * hidden + h);
+    const float4 wr = *reinterpret_cast<const float4*>(w + static_cast<size_t>(e) * hidden + h);
+    acc = fmaf(__uint_as_float(xr.x << 16), wr.x, acc);
+    acc = fmaf(__uint_as_float(xr.x & 0xFFFF0000u), wr.y, acc);
+    acc = fmaf(__uint_as_float(xr.y << 16), wr.z, acc);
+    acc = fmaf(__uint_as_float(xr.y & 0xFFFF0000u), wr.w, acc);
+  }
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, off);
+  if (lane == 0) logits[static_cast<size_t>(token) * n_routed + e] = acc;
+}
+
+__global__ void __launch_bounds__(256)
+router_tile_f32_kernel(const uint16_t* __restrict__ x, const float* __restrict__ w, float* __restrict__ logits,
+                       int n_tokens, int hidden, int n_routed) {
+  constexpr int BM = 64, BN = 64, BK = 16;
+  __shared__ float xs[BK][BM + 4];
+  __shared__ float ws[BK][BN + 4];
+  const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+  const int token0 = blockIdx.x * BM, e0 = blockIdx.y * BN;
+  const int lrow = tid >> 2, lk = (tid & 3) * 4;  // this thread stages 4 k of one row of each tile
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < hidden; k0 += BK) {
+    uint2 xr = make_uint2(0u, 0u);
+    float4 wr = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (token0 + lrow < n_tokens) xr = *reinterpret_cast<const uint2*>(x + static_cast<size_t>(token0 + lrow) * hidden + k0 + lk);
+    if (e0 + lrow < n_routed) wr = *reinterpret_cast<const float4*>(w + static_cast<size_t>(e0 + lrow) * hidden + k0 + lk);
+    __syncthreads();  // the previous step is done with the tiles
+    xs[lk + 0][lrow] = __uint_as_float(xr.x << 16);
+    xs[lk + 1][lrow] = __uint_as_float(xr.x & 0xFFFF0000u);
+    xs[lk + 2][lrow] = __uint_as_float(xr.y << 16);
+    xs[lk + 3][lrow] = __uint_as_float(xr.y & 0xFFFF0000u);
+    ws[lk + 0][lrow] = wr.x;
+    ws[lk + 1][lrow] = wr.y;
+    ws[lk + 2][lrow] = wr.z;
+    ws[lk + 3][lrow] = wr.w;
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < BK; ++k) {
+      const float4 a = *reinterpret_cast<const float4*>(&xs[k][ty * 4]);
+      const float4 b = *reinterpret_cast<const float4*>(&ws[k][tx * 4]);
+      const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int token = token0 + ty * 4 + i;
+    if (token >= n_tokens) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int e = e0 + tx * 4 + j;
+      if (e < n_routed) logits[static_cast<size_t>(token) * n_routed + e] = acc[i][j];
+    }
+  }
+}
+
+int launch_router_gemm_f32(const void* x, const float* w, float* logits, int n_tokens, int hidden, int n_routed,
+                           cudaStream_t stream) {
+  if (hidden % 128 != 0) return AKLR_ERR_UNSUPPORTED_SHAPE;
+  if (n_tokens == 0 || n_routed == 0) return AKLR_OK;
+  auto* xp = static_cast<const uint16_t*>(x);
+  if (n_tokens <= 16) {
+    const int64_t blocks = (static_cast<int64_t>(n_tokens) * n_routed + 7) / 8;
+    router_dot_f32_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(xp, w, logits, n_tokens, hidden, n_routed);
+  } else {
+    const dim3 grid((n_tokens + 63) / 64, (n_routed + 63) / 64);
+    router_tile_f32_kernel<<<grid, 256, 0, stream>>>(xp, w, logits, n_tokens, hidden, n_routed);
+  }
+  return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+}
+
 int launch_router_gemm(const void* x, const void* w, void* logits, int n_tokens, int hidden, int n_routed,
                        cudaStream_t stream) {
   if (hidden % 8 != 0) return AKLR_ERR_UNSUPPORTED_SHAPE;

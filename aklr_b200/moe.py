@@ -417,6 +417,20 @@ def router_logits(hidden_states: torch.Tensor, router_weight: torch.Tensor) -> t
     return logits
 
 
+def router_logits_f32(hidden_states: torch.Tensor, router_weight: torch.Tensor) -> torch.Tensor:
+    """float32 [tokens, experts] = hidden_states (bf16) @ router_weight (float32)^T, nothing rounded."""
+    device = _need_cuda(hidden_states, router_weight)
+    if hidden_states.dtype != torch.bfloat16 or router_weight.dtype != torch.float32:
+        raise ValueError("hidden_states must be bfloat16 and router_weight float32")
+    n_tokens, h = hidden_states.shape
+    n_routed = router_weight.shape[0]
+    logits = torch.empty((n_tokens, n_routed), dtype=torch.float32, device=device)
+    _lib.check(
+        _lib.load().aklr_router_gemm_f32(_ptr(hidden_states), _ptr(router_weight), _ptr(logits), n_tokens, h, n_routed, _stream())
+    )
+    return logits
+
+
 def per_group_quant_fp8(x: torch.Tensor, quantized=None, scales=None):
     """(e4m3 [T,H], float32 scales [H/128, T]) -- the standalone op's scheme."""
     device = _need_cuda(x, quantized, scales)

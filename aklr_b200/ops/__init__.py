@@ -38,6 +38,7 @@ __all__ = [
     "fused_moe",
     "init",
     "mega_moe",
+    "minimax_m2_fp8_moe",
     "per_group_quant_fp8",
     "per_group_quant_mxfp8",
     "qwen3_moe_fp8_moe",
@@ -252,6 +253,97 @@ def qwen3_moe_fp8_moe(
     w2,
     w2_scale,
     topk=8,
+): ...
+
+
+# --------------------------------------------------------------------------------------------------
+# minimax_m2_fp8_moe@1.0  (aklr/plugins/sglang/models/minimax_m2/contract.py:48-110, api.py:17-28)
+# --------------------------------------------------------------------------------------------------
+def _minimax_key(call):
+    x, rw, bias = call["hidden_states"], call["router_weight"], call["correction_bias"]
+    if not tensor_ok(x, BF16, 2):
+        return None
+    device = x.device
+    n_tokens, hidden = x.shape
+    if not (1 <= n_tokens <= MAX_TOKENS) or not tensor_ok(rw, torch.float32, 2, device) or rw.shape[1] != hidden:
+        return None
+    n_routed = rw.shape[0]
+    if not (1 <= n_routed <= 1024) or not tensor_ok(bias, torch.float32, 1, device) or bias.shape[0] != n_routed:
+        return None
+    weights = _fp8_weights_key(call, hidden, device)
+    if weights is None or not (1 <= weights[0] <= n_routed):
+        return None
+    topk, offset = call["topk"], call["expert_offset"]
+    if not all(isinstance(v, int) and not isinstance(v, bool) for v in (topk, offset)):
+        return None
+    if not (1 <= topk <= min(32, n_routed)) or not (0 <= offset and offset + weights[0] <= n_routed):
+        return None
+    return ("row_major", hidden, n_routed, weights[0], weights[1], topk, offset)
+
+
+_EXPERT_MAPS: dict[tuple, torch.Tensor] = {}
+
+
+def _held_expert_map(n_routed: int, offset: int, n_experts: int, device) -> torch.Tensor | None:
+    """int32 [n_routed]: router row -> this rank's expert slot, -1 for experts held elsewhere."""
+    if offset == 0 and n_experts == n_routed:
+        return None
+    key = (n_routed, offset, n_experts, str(device))
+    if key not in _EXPERT_MAPS:
+        table = torch.full((n_routed,), -1, dtype=torch.int32)
+        table[offset : offset + n_experts] = torch.arange(n_experts, dtype=torch.int32)
+        _EXPERT_MAPS[key] = table.to(device)
+    return _EXPERT_MAPS[key]
+
+
+def _minimax_run(call, out):
+    x = call["hidden_states"]
+    logits = moe.router_logits_f32(x, call["router_weight"])
+    routing = moe.Routing(topk=call["topk"], scoring="sigmoid", renormalize=True, routed_scaling_factor=1.0)
+    ids, weights = moe.route(logits, call["correction_bias"], routing)
+    table = _held_expert_map(logits.shape[1], call["expert_offset"], call["w1"].shape[0], x.device)
+    moe.fused_experts_fp8(
+        x, ids, weights, call["w1"], call["w1_scale"], call["w2"], call["w2_scale"], expert_map=table, out=out
+    )
+
+
+MINIMAX_M2_FP8_MOE = OpContract(
+    contract_id="minimax_m2_fp8_moe@1.0",
+    description=(
+        "sglang's MiniMaxM2MoE on one rank with fp8 experts at a scale per 128 x 128 block: float32 gate "
+        "logits, each token's topk experts of the n_routed by sigmoid score + correction_bias, weighed by "
+        "their unbiased scores renormalised to sum 1; out is the share of the experts this rank holds "
+        "(expert_offset .. expert_offset + n_experts - 1), not yet summed over the ranks."
+    ),
+    params=[
+        Param("hidden_states"),
+        Param("router_weight"),
+        Param("correction_bias"),
+        Param("w1"),
+        Param("w1_scale"),
+        Param("w2"),
+        Param("w2_scale"),
+        Param("topk"),
+        Param("expert_offset", 0),
+    ],
+    outputs=["out"],
+    key=_minimax_key,
+    alloc=_layer_alloc,
+    run=_minimax_run,
+)
+
+
+@api(MINIMAX_M2_FP8_MOE)
+def minimax_m2_fp8_moe(
+    hidden_states,
+    router_weight,
+    correction_bias,
+    w1,
+    w1_scale,
+    w2,
+    w2_scale,
+    topk,
+    expert_offset=0,
 ): ...
 
 
@@ -699,6 +791,7 @@ def per_group_quant_mxfp8(x): ...
 CONTRACTS = (
     DEEPSEEK_V2_FP8_MOE,
     QWEN3_MOE_FP8_MOE,
+    MINIMAX_M2_FP8_MOE,
     FUSED_MOE,
     MEGA_MOE,
     BIASED_GROUPED_TOPK,

@@ -13,7 +13,7 @@ __all__ = ["SGLANG_HOOKED_METHOD", "register"]
 
 # the runtime starts after this sglang method: the rank's device is set by then
 SGLANG_HOOKED_METHOD = "sglang.srt.model_executor.model_runner.ModelRunner.init_torch_distributed"
-ROUTE_MODULES = ("deepseek_v2", "qwen3_moe")
+ROUTE_MODULES = ("deepseek_v2", "qwen3_moe", "minimax_m2")
 
 
 def register() -> None:

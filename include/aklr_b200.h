@@ -196,6 +196,11 @@ int aklr_moe_align_noalloc(const int32_t* topk_ids, const int32_t* expert_map, i
 int32_t aklr_moe_align_noalloc_max_scratch_ints(void);
 const char* aklr_moe_align_noalloc_last_error(void);
 
+/* logits float32 [T,E] = x (bf16 [T,H]) @ w (float32 [E,H])^T, nothing rounded: the gate of
+ * `minimax_m2_fp8_moe` (aklr/plugins/sglang/models/minimax_m2/reference.py:43-50). */
+int aklr_router_gemm_f32(const void* x, const float* w, float* logits, int32_t n_tokens, int32_t hidden,
+                         int32_t n_routed, void* stream);
+
 /* logits bf16 [T,E] = bf16(x [T,H] @ w [E,H]^T): `_router_logits`
  * (aklr/plugins/sglang/models/qwen3_moe/reference.py:24-31). */
 int aklr_router_gemm_bf16(const void* x, const void* w, void* logits, int32_t n_tokens, int32_t hidden,

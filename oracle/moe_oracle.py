@@ -300,6 +300,29 @@ def deepseek_v2_fp8_moe(
     return fp8_experts(hidden, ids, weights, w1, w1_scale, w2, w2_scale)
 
 
+def sigmoid_bias_topk(logits: torch.Tensor, bias: torch.Tensor, topk: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """(ids, weights): the ``topk`` experts by sigmoid score + bias (ties to the lower id), weighed by
+    their unbiased scores renormalised to sum 1.
+    Follows ``_routed`` (aklr/plugins/sglang/models/minimax_m2/reference.py:43-50)."""
+    scores = logits.sigmoid()
+    ids = first_largest(scores + bias, topk)
+    weights = scores.gather(-1, ids)
+    return ids, weights / weights.sum(dim=-1, keepdim=True)
+
+
+def minimax_m2_fp8_moe(hidden, router_weight, correction_bias, w1, w1_scale, w2, w2_scale, topk, expert_offset=0, logits=None):
+    """This rank's share of a MiniMax-M2 FP8 MoE: float32 gate (nothing rounded), biased sigmoid
+    top-k, the experts ``expert_offset .. expert_offset + len(w1) - 1`` held here; routes to the others
+    add nothing.  Follows ``minimax_m2_fp8_moe_reference`` and ``_held_experts``
+    (aklr/plugins/sglang/models/minimax_m2/reference.py:53-70,103-117)."""
+    if logits is None:
+        logits = hidden.float() @ router_weight.float().T
+    ids, weights = sigmoid_bias_topk(logits.float(), correction_bias.float(), topk)
+    local = ids - expert_offset
+    local = torch.where((local >= 0) & (local < w1.shape[0]), local, torch.full_like(local, -1))
+    return fp8_experts(hidden, local, weights, w1, w1_scale, w2, w2_scale)
+
+
 # --------------------------------------------------------------------------------------
 # MX formats (weights e2m1 + e8m0 per 32, activations MXFP8 e4m3 + power-of-two scale per 32)
 # --------------------------------------------------------------------------------------

@@ -36,6 +36,21 @@ def ds_small_layer():
     )
 
 
+def minimax_layer():
+    """MiniMax-M2-style layer: float32 gate over 16 routed experts, this rank holds experts 4..11."""
+    cfg, seed, tokens = wl.MoEConfig("minimax_small", hidden=256, inter=128, n_routed=8, topk=4, scoring="sigmoid"), 2468, 40
+    n_routed, offset = 16, 4
+    hidden, _, _ = wl.router_inputs(cfg, tokens, seed)
+    g = torch.Generator().manual_seed(seed + 5)
+    router = torch.randn(n_routed, cfg.hidden, generator=g) * (3.0 / cfg.hidden**0.5)
+    bias = 8.0 + 0.02 * torch.randn(n_routed, generator=g)
+    w1, s1, w2, s2 = wl.expert_weights(cfg, seed)
+    return cfg, dict(
+        hidden_states=hidden, router_weight=router, correction_bias=bias, w1=w1, w1_scale=s1, w2=w2, w2_scale=s2,
+        expert_offset=offset,
+    )
+
+
 def route_ds():
     _, logits, bias = wl.router_inputs(ROUTE_SHAPE, 192, 77)
     return logits, bias

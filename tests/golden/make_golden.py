@@ -99,6 +99,23 @@ def main() -> None:
         if isinstance(v, torch.Tensor):
             meta[f"ds_small.{k}"] = sha256_of(v)
 
+    # ---- layer: MiniMax-M2 (float32 gate, plain biased top-k, this rank holds 8 of 16 experts) ----
+    from aklr.plugins.sglang.models.minimax_m2 import reference as mm
+
+    cfg, rargs = cases.minimax_layer()
+    point = SimpleNamespace(
+        dtypes={**FP8_DTYPES, "router_weight": "float32", "correction_bias": "float32"},
+        attrs={"topk": cfg.topk},
+        axes={"n_experts": cfg.n_routed},
+    )
+    x32 = rargs["hidden_states"].float()
+    ids, weights = mm._routed(point, x32, rargs["router_weight"], rargs["correction_bias"])
+    out["minimax.ids"], out["minimax.weights"] = ids.numpy(), f32(weights)
+    out["minimax.out"] = f32(mm.minimax_m2_fp8_moe_reference(point, rargs))
+    for k, v in rargs.items():
+        if isinstance(v, torch.Tensor):
+            meta[f"minimax.{k}"] = sha256_of(v)
+
     # ---- routing only, at the full expert counts -----------------------------------------
     logits, bias = cases.route_ds()
     point = SimpleNamespace(

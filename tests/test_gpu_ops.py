@@ -49,6 +49,38 @@ def test_deepseek_v2_fp8_moe_op(ops, golden):
     assert orc.gates_pass(gates), gates
 
 
+def test_minimax_m2_fp8_moe_op(ops, golden):
+    """Float32 gate, biased sigmoid top-k without groups, this rank holding experts 4..11 of 16: against
+    the reference's stored output, and at larger batches (tile router kernel, token-major experts)
+    against the oracle fed the device's logits."""
+    from aklr_b200.moe import router_logits_f32
+
+    cfg, a = cases.minimax_layer()
+    d = to_dev(a)
+    out = ops.minimax_m2_fp8_moe(**d, topk=cfg.topk)
+    assert isinstance(out, torch.Tensor) and out.dtype == torch.bfloat16
+    logits = router_logits_f32(d["hidden_states"], d["router_weight"]).cpu()
+    torch.testing.assert_close(logits, a["hidden_states"].float() @ a["router_weight"].T, atol=2e-5, rtol=1e-5)
+    gates = orc.output_gates(out.cpu(), torch.from_numpy(np.asarray(golden["minimax.out"])))
+    assert orc.gates_pass(gates), gates
+    # every expert held here (no expert_offset), 700 tokens
+    g = torch.Generator().manual_seed(3)
+    hidden = torch.randn(700, cfg.hidden, generator=g).to(torch.bfloat16)
+    router = a["router_weight"][:8].contiguous()
+    bias = a["correction_bias"][:8].contiguous()
+    out = ops.minimax_m2_fp8_moe(
+        hidden_states=hidden.to(dev()), router_weight=router.to(dev()), correction_bias=bias.to(dev()), w1=d["w1"],
+        w1_scale=d["w1_scale"], w2=d["w2"], w2_scale=d["w2_scale"], topk=2,
+    )
+    logits = router_logits_f32(hidden.to(dev()), router.to(dev())).cpu()
+    ref = orc.minimax_m2_fp8_moe(hidden, None, bias, a["w1"], a["w1_scale"], a["w2"], a["w2_scale"], 2, logits=logits)
+    gates = orc.output_gates(out.cpu(), ref)
+    assert orc.gates_pass(gates), gates
+    # out of contract: a bf16 gate, an offset past the router's rows
+    assert ops.minimax_m2_fp8_moe(**{**d, "router_weight": d["router_weight"].bfloat16()}, topk=cfg.topk) is ops.FallbackReason.OUT_OF_CONTRACT
+    assert ops.minimax_m2_fp8_moe(**{**d, "expert_offset": 9}, topk=cfg.topk) is ops.FallbackReason.OUT_OF_CONTRACT
+
+
 def test_qwen3_moe_fp8_moe_op_and_fallbacks(ops, golden):
     cfg, a = cases.tiny_layer()
     d = to_dev(a)

@@ -69,6 +69,21 @@ def test_deepseek_small_layer_matches_reference(golden, golden_hashes):
     assert torch.equal(out, t(golden["ds_small.out"]))
 
 
+def test_minimax_layer_matches_reference(golden, golden_hashes):
+    torch.set_num_threads(1)
+    cfg, a = cases.minimax_layer()
+    check_inputs("minimax", {k: v for k, v in a.items() if isinstance(v, torch.Tensor)}, golden_hashes)
+    logits = a["hidden_states"].float() @ a["router_weight"].T
+    ids, w = orc.sigmoid_bias_topk(logits, a["correction_bias"], cfg.topk)
+    assert torch.equal(ids, t(golden["minimax.ids"])) and torch.equal(w, t(golden["minimax.weights"]))
+    out = orc.minimax_m2_fp8_moe(
+        a["hidden_states"], a["router_weight"], a["correction_bias"], a["w1"], a["w1_scale"], a["w2"], a["w2_scale"],
+        cfg.topk, a["expert_offset"],
+    )
+    assert torch.equal(out, t(golden["minimax.out"]))
+    assert (ids < a["expert_offset"]).any() and (ids >= a["expert_offset"] + cfg.n_routed).any()  # routes to other ranks exist
+
+
 def test_routing_matches_reference(golden, golden_hashes):
     logits, bias = cases.route_ds()
     assert orc.sha256_of(logits) == golden_hashes["route_ds.logits"]

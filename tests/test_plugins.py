@@ -42,11 +42,12 @@ def fake_sglang(monkeypatch):
         def register(target, fn, hook_type):
             registered.append((target, fn, hook_type))
 
-    modules = {name: types.ModuleType(name) for name in ("sglang", "sglang.srt", "sglang.srt.plugins", "sglang.srt.plugins.hook_registry", "sglang.srt.models", "sglang.srt.models.deepseek_v2", "sglang.srt.models.qwen3_moe")}
+    modules = {name: types.ModuleType(name) for name in ("sglang", "sglang.srt", "sglang.srt.plugins", "sglang.srt.plugins.hook_registry", "sglang.srt.models", "sglang.srt.models.deepseek_v2", "sglang.srt.models.qwen3_moe", "sglang.srt.models.minimax_m2")}
     modules["sglang.srt.plugins.hook_registry"].HookRegistry = HookRegistry
     modules["sglang.srt.plugins.hook_registry"].HookType = HookType
     modules["sglang.srt.models.deepseek_v2"].DeepseekV2MoE = type("DeepseekV2MoE", (), {"forward_normal": lambda self, hidden_states: "sglang"})
     modules["sglang.srt.models.qwen3_moe"].Qwen3MoeSparseMoeBlock = type("Qwen3MoeSparseMoeBlock", (), {"forward_normal": lambda self, hidden_states: "sglang"})
+    modules["sglang.srt.models.minimax_m2"].MiniMaxM2MoE = type("MiniMaxM2MoE", (), {"forward_normal": lambda self, hidden_states: "sglang"})
     for name, module in modules.items():
         monkeypatch.setitem(sys.modules, name, module)
         parent, _, child = name.rpartition(".")
@@ -57,14 +58,17 @@ def fake_sglang(monkeypatch):
 
 def test_sglang_install_hooks_only_routes_tested_on_the_installed_release(fake_sglang, monkeypatch):
     from aklr_b200.plugins.sglang import hook
-    from aklr_b200.plugins.sglang.models import deepseek_v2, qwen3_moe  # noqa: F401  (declare the routes)
+    from aklr_b200.plugins.sglang.models import deepseek_v2, minimax_m2, qwen3_moe  # noqa: F401  (declare the routes)
 
     monkeypatch.setattr(hook, "sglang_version", lambda: "0.5.22")
-    assert hook.install() == 1
-    assert [t for t, _, _ in fake_sglang.registered] == ["sglang.srt.models.qwen3_moe.Qwen3MoeSparseMoeBlock.forward_normal"]
+    assert hook.install() == 2
+    assert sorted(t for t, _, _ in fake_sglang.registered) == [
+        "sglang.srt.models.minimax_m2.MiniMaxM2MoE.forward_normal",
+        "sglang.srt.models.qwen3_moe.Qwen3MoeSparseMoeBlock.forward_normal",
+    ]
     fake_sglang.registered.clear()
     monkeypatch.setattr(hook, "sglang_version", lambda: "0.5.23")
-    assert hook.install() == 2
+    assert hook.install() == 3
     assert all(kind is fake_sglang.HookType.AROUND for _, _, kind in fake_sglang.registered)
     fake_sglang.registered.clear()
     monkeypatch.setattr(hook, "sglang_version", lambda: "0.9.0")
@@ -90,8 +94,9 @@ def test_sglang_around_serves_falls_back_and_skips_compiled_regions(monkeypatch,
 
 
 def test_sglang_routes_take_their_targets_parameters():
-    from aklr_b200.plugins.sglang.models import deepseek_v2, qwen3_moe
+    from aklr_b200.plugins.sglang.models import deepseek_v2, minimax_m2, qwen3_moe
 
+    assert list(inspect.signature(minimax_m2._moe_forward_normal).parameters) == ["self", "hidden_states"]
     assert list(inspect.signature(deepseek_v2._moe_forward_normal).parameters) == [
         "self", "hidden_states", "gemm_output_zero_allocator", "input_ids", "input_ids_global",
         "skip_shared_experts", "use_vision_topk", "return_moe_output", "leave_output_sum",
@@ -109,7 +114,7 @@ def test_sglang_register_starts_only_when_switched_on(fake_sglang, monkeypatch):
     fake_sglang.registered.clear()
     monkeypatch.setenv("AKLR_SGLANG_PLUGIN", "1")
     plugin.register()
-    assert len(fake_sglang.registered) == 3
+    assert len(fake_sglang.registered) == 4  # the start hook + three model routes
     monkeypatch.setenv("AKLR_SGLANG_PLUGIN", "maybe")
     with pytest.raises(SystemExit, match="cannot start"):
         plugin.register()
