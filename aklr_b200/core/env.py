@@ -1,53 +1,59 @@
-"""Environment switches, named as the reference names them (aklr/core/platform/env.py:27-104)."""
+"""The environment variables the runtime obeys.
+
+The names and accepted values are the reference's (aklr/core/platform/env.py:27-104), so a deployment
+script written for it keeps working: AKLR_DISABLE ("1" for everything, or a comma-separated list of
+contract ids), AKLR_SGLANG_PLUGIN / AKLR_VLLM_PLUGIN / AKLR_AITER_PLUGIN / AKLR_EXPORT ("0" or "1"),
+AKLR_EXPORT_DIR (a path) and AKLR_TRACE ("0", "plugin", "op", "all").  An empty value counts as unset;
+any other value raises ``ValueError`` naming the variable, so a typo stops the start instead of being
+read as "off".
+"""
 
 from __future__ import annotations
 
 import os
 
-ENV_DISABLE = "AKLR_DISABLE"
-ENV_SGLANG_PLUGIN = "AKLR_SGLANG_PLUGIN"
-ENV_VLLM_PLUGIN = "AKLR_VLLM_PLUGIN"
-ENV_AITER_PLUGIN = "AKLR_AITER_PLUGIN"
-ENV_TRACE = "AKLR_TRACE"
-ENV_EXPORT = "AKLR_EXPORT"
-ENV_EXPORT_DIR = "AKLR_EXPORT_DIR"
 DEFAULT_EXPORT_DIR = "aklr_export"
+TRACE_MODES = ("0", "plugin", "op", "all")
 
-_ALL = (ENV_DISABLE, ENV_SGLANG_PLUGIN, ENV_VLLM_PLUGIN, ENV_AITER_PLUGIN, ENV_TRACE, ENV_EXPORT, ENV_EXPORT_DIR)
+# variable -> RuntimeEnv attribute holding its on/off value
+_ON_OFF = {
+    "AKLR_SGLANG_PLUGIN": "is_sglang_plugin_enabled",
+    "AKLR_VLLM_PLUGIN": "is_vllm_plugin_enabled",
+    "AKLR_AITER_PLUGIN": "is_aiter_plugin_enabled",
+    "AKLR_EXPORT": "is_export_enabled",
+}
 
 
-def _switch(name: str) -> bool:
-    value = os.environ.get(name) or "0"
-    if value not in ("0", "1"):
-        raise ValueError(f"{name}={value!r}: expected '1' or '0'")
-    return value == "1"
+def _read(name: str, unset: str) -> str:
+    return os.environ.get(name) or unset
+
+
+def _one_of(name: str, allowed: tuple[str, ...]) -> str:
+    value = _read(name, allowed[0])
+    if value not in allowed:
+        raise ValueError(f"{name}={value!r}: expected {' or '.join(repr(a) for a in allowed)}")
+    return value
 
 
 def trace_mode() -> str:
-    """AKLR_TRACE: '0'/unset nothing, 'plugin' the routes, 'op' the dispatches, 'all' both."""
-    mode = os.environ.get(ENV_TRACE) or "0"
-    if mode not in ("0", "plugin", "op", "all"):
-        raise ValueError(f"{ENV_TRACE}={mode!r}: expected '0', 'plugin', 'op' or 'all'")
-    return mode
-
-
-class RuntimeEnv:
-    """What the environment asks of the runtime, read once; '' counts as unset and a bad
-    value raises ValueError naming its variable."""
-
-    def __init__(self) -> None:
-        disable = os.environ.get(ENV_DISABLE) or "0"
-        self.is_all_disabled = disable == "1"
-        self.disabled_contracts = (
-            frozenset() if disable in ("0", "1") else frozenset(part.strip() for part in disable.split(","))
-        )
-        self.is_sglang_plugin_enabled = _switch(ENV_SGLANG_PLUGIN)
-        self.is_vllm_plugin_enabled = _switch(ENV_VLLM_PLUGIN)
-        self.is_aiter_plugin_enabled = _switch(ENV_AITER_PLUGIN)
-        self.is_export_enabled = _switch(ENV_EXPORT)
-        self.export_dir = os.path.abspath(os.environ.get(ENV_EXPORT_DIR) or DEFAULT_EXPORT_DIR)
-        self.trace_mode = trace_mode()
+    """AKLR_TRACE: nothing ("0" or unset), the plugin routes, the op dispatches, or both."""
+    return _one_of("AKLR_TRACE", TRACE_MODES)
 
 
 def all_names() -> tuple[str, ...]:
-    return _ALL
+    """Every variable read here (tests clear them)."""
+    return ("AKLR_DISABLE", *_ON_OFF, "AKLR_TRACE", "AKLR_EXPORT_DIR")
+
+
+class RuntimeEnv:
+    """A snapshot of the variables above, validated when taken."""
+
+    def __init__(self) -> None:
+        for name, field in _ON_OFF.items():
+            setattr(self, field, _one_of(name, ("0", "1")) == "1")
+        self.trace_mode = trace_mode()
+        self.export_dir = os.path.abspath(_read("AKLR_EXPORT_DIR", DEFAULT_EXPORT_DIR))
+        disable = _read("AKLR_DISABLE", "0")
+        self.is_all_disabled = disable == "1"
+        named = () if disable in ("0", "1") else (part.strip() for part in disable.split(","))
+        self.disabled_contracts = frozenset(named)

@@ -855,6 +855,20 @@ int aklr_router_gemm_bf16(const void* x, const void* w, void* logits, int32_t n_
   return AKLR_OK;
 }
 
+int aklr_moe_shared_gate(const void* x, const void* shared_gate_weight, const int32_t* topk_ids_in,
+                         const float* topk_weights_in, int32_t* topk_ids, float* topk_weights, int32_t n_tokens,
+                         int32_t hidden, int32_t topk, int32_t shared_slot, void* stream) {
+  if (!x || !shared_gate_weight || !topk_ids || !topk_weights || (!topk_ids_in) != (!topk_weights_in))
+    return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
+  int rc = check_device();
+  if (rc) return rc;
+  rc = aklr::launch_shared_gate(x, shared_gate_weight, topk_ids_in, topk_weights_in, topk_ids, topk_weights, n_tokens, hidden,
+                                topk, shared_slot, static_cast<cudaStream_t>(stream));
+  if (rc) return fail(rc, "shared expert gate: %s", aklr_status_string(rc));
+  g_launches += n_tokens > 0;
+  return AKLR_OK;
+}
+
 int aklr_router_gemm_f32(const void* x, const float* w, float* logits, int32_t n_tokens, int32_t hidden,
                          int32_t n_routed, void* stream) {
   if (!x || !w || !logits) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");

@@ -118,6 +118,50 @@ router_gemm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ 
   }
 }
 
+// Qwen2-MoE's gated shared expert (aklr/plugins/sglang/models/qwen2_moe/reference.py:84-90): the
+// routing table gets one more slot per token, expert ``shared_slot`` at weight
+// sigmoid(x . shared_gate).  ``ids_in`` / ``weights_in`` [T, K] given: copied into the first K
+// slots of the [T, K+1] tables; null: those slots are already in place.  One warp per token.
+__global__ void __launch_bounds__(256)
+shared_gate_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ gate, const int32_t* __restrict__ ids_in,
+                   const float* __restrict__ weights_in, int32_t* __restrict__ ids, float* __restrict__ weights,
+                   int n_tokens, int hidden, int topk, int shared_slot) {
+  const int lane = threadIdx.x & 31;
+  const int token = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (token >= n_tokens) return;
+  float acc = 0.0f;
+  for (int h = lane * 8; h < hidden; h += 256) {
+    const uint4 xr = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(token) * hidden + h);
+    const uint4 gr = *reinterpret_cast<const uint4*>(gate + h);
+    const uint32_t xw[4] = {xr.x, xr.y, xr.z, xr.w}, gw[4] = {gr.x, gr.y, gr.z, gr.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      acc = fmaf(__uint_as_float(xw[q] << 16), __uint_as_float(gw[q] << 16), acc);
+      acc = fmaf(__uint_as_float(xw[q] & 0xFFFF0000u), __uint_as_float(gw[q] & 0xFFFF0000u), acc);
+    }
+  }
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, off);
+  const size_t row = static_cast<size_t>(token) * (topk + 1);
+  if (ids_in && lane < topk) {
+    ids[row + lane] = ids_in[static_cast<size_t>(token) * topk + lane];
+    weights[row + lane] = weights_in[static_cast<size_t>(token) * topk + lane];
+  }
+  if (lane == 0) {
+    ids[row + topk] = shared_slot;
+    weights[row + topk] = __fdiv_rn(1.0f, 1.0f + expf(-acc));
+  }
+}
+
+int launch_shared_gate(const void* x, const void* gate, const int32_t* ids_in, const float* weights_in, int32_t* ids,
+                       float* weights, int n_tokens, int hidden, int topk, int shared_slot, cudaStream_t stream) {
+  if (hidden % 8 != 0 || topk < 1 || topk > 31) return AKLR_ERR_UNSUPPORTED_SHAPE;
+  if (n_tokens == 0) return AKLR_OK;
+  shared_gate_kernel<<<(n_tokens + 7) / 8, 256, 0, stream>>>(static_cast<const uint16_t*>(x), static_cast<const uint16_t*>(gate),
+                                                          ids_in, weights_in, ids, weights, n_tokens, hidden, topk, shared_slot);
+  return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+}
+
 // Router with float32 weights and float32 logits (MiniMax-M2's gate:
 // aklr/plugins/sglang/models/minimax_m2/reference.py:43-50 takes x @ router^T in float32, nothing
 // rounded).  CUDA cores, float32 FMAs in k order.

@@ -196,6 +196,8 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
+int launch_shared_gate(const void* x_bf16, const void* gate_bf16, const int32_t* ids_in, const float* weights_in,
+                       int32_t* ids, float* weights, int n_tokens, int hidden, int topk, int shared_slot, cudaStream_t stream);
 int launch_router_gemm_f32(const void* x_bf16, const float* w, float* logits, int n_tokens, int hidden, int n_routed,
                            cudaStream_t stream);
 int launch_router_gemm(const void* x_bf16, const void* w_bf16, void* logits_bf16, int n_tokens, int hidden,

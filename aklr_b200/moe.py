@@ -417,6 +417,21 @@ def router_logits(hidden_states: torch.Tensor, router_weight: torch.Tensor) -> t
     return logits
 
 
+def with_gated_shared_slot(hidden_states, shared_gate_weight, topk_ids, topk_weights, shared_slot: int, copy_from=None):
+    """Slot K of the [tokens, K+1] routing tables <- expert ``shared_slot`` at sigmoid(x . gate).
+    ``copy_from`` = (ids [tokens, K] int32, weights [tokens, K] float32) fills the first K slots too."""
+    _need_cuda(hidden_states, shared_gate_weight, topk_ids, topk_weights)
+    n_tokens, h = hidden_states.shape
+    ids_in, w_in = copy_from if copy_from is not None else (None, None)
+    _lib.check(
+        _lib.load().aklr_moe_shared_gate(
+            _ptr(hidden_states), _ptr(shared_gate_weight), _ptr(ids_in), _ptr(w_in), _ptr(topk_ids), _ptr(topk_weights),
+            n_tokens, h, topk_ids.shape[1] - 1, shared_slot, _stream(),
+        )
+    )
+    return topk_ids, topk_weights
+
+
 def router_logits_f32(hidden_states: torch.Tensor, router_weight: torch.Tensor) -> torch.Tensor:
     """float32 [tokens, experts] = hidden_states (bf16) @ router_weight (float32)^T, nothing rounded."""
     device = _need_cuda(hidden_states, router_weight)

@@ -41,6 +41,9 @@ __all__ = [
     "minimax_m2_fp8_moe",
     "per_group_quant_fp8",
     "per_group_quant_mxfp8",
+    "qwen2_moe_fp8_experts",
+    "qwen2_moe_fp8_router_experts",
+    "qwen2_moe_router",
     "qwen3_moe_fp8_moe",
 ]
 
@@ -345,6 +348,189 @@ def minimax_m2_fp8_moe(
     topk,
     expert_offset=0,
 ): ...
+
+
+# --------------------------------------------------------------------------------------------------
+# qwen2_moe_router@1.0, qwen2_moe_fp8_experts@1.0, qwen2_moe_fp8_router_experts@1.0
+# (aklr/plugins/sglang/models/qwen2_moe/contract.py:161-265, api.py:24-52): softmax top-k over bf16
+# logits, FP8 experts, and a shared expert in w1/w2's last slot weighed by sigmoid(x . shared_gate_weight)
+# --------------------------------------------------------------------------------------------------
+def _qwen2_common_key(call, with_router: bool):
+    x, gate = call["hidden_states"], call["shared_gate_weight"]
+    if not tensor_ok(x, BF16, 2):
+        return None
+    device = x.device
+    n_tokens, hidden = x.shape
+    if not (1 <= n_tokens <= MAX_TOKENS) or not tensor_ok(gate, BF16, 2, device) or tuple(gate.shape) != (1, hidden):
+        return None
+    weights = _fp8_weights_key(call, hidden, device)
+    if weights is None or not (2 <= weights[0] <= 1025):
+        return None
+    n_routed = weights[0] - 1
+    if with_router:
+        rw = call["router_weight"]
+        if not tensor_ok(rw, BF16, 2, device) or tuple(rw.shape) != (n_routed, hidden):
+            return None
+    return n_tokens, hidden, n_routed, weights[1]
+
+
+def _qwen2_router_experts_key(call):
+    common = _qwen2_common_key(call, True)
+    topk = call["topk"]
+    if common is None or not isinstance(topk, int) or isinstance(topk, bool) or not (1 <= topk <= min(31, common[2])):
+        return None
+    return ("row_major", *common[1:], topk)
+
+
+def _qwen2_router_experts_run(call, out):
+    x = call["hidden_states"]
+    logits = moe.router_logits(x, call["router_weight"])
+    topk, n_routed = call["topk"], logits.shape[1]
+    ids, weights = moe.route(logits, None, moe.Routing(topk=topk, n_shared=1))  # slot topk = the shared expert
+    moe.with_gated_shared_slot(x, call["shared_gate_weight"], ids, weights, n_routed)
+    moe.fused_experts_fp8(x, ids, weights, call["w1"], call["w1_scale"], call["w2"], call["w2_scale"], out=out)
+
+
+QWEN2_MOE_FP8_ROUTER_EXPERTS = OpContract(
+    contract_id="qwen2_moe_fp8_router_experts@1.0",
+    description=(
+        "sglang's Qwen2MoeSparseMoeBlock router and experts on one rank with the shared expert fused in after "
+        "the routed ones: bf16 router logits, top-k by logit (ties to the lower id), softmax over the chosen, "
+        "and the shared expert by sigmoid(hidden_states shared_gate_weight^T); fp8 experts as in "
+        "deepseek_v2_fp8_moe."
+    ),
+    params=[
+        Param("hidden_states"),
+        Param("router_weight"),
+        Param("shared_gate_weight"),
+        Param("w1"),
+        Param("w1_scale"),
+        Param("w2"),
+        Param("w2_scale"),
+        Param("topk", 10),
+    ],
+    outputs=["out"],
+    key=_qwen2_router_experts_key,
+    alloc=_layer_alloc,
+    run=_qwen2_router_experts_run,
+)
+
+
+@api(QWEN2_MOE_FP8_ROUTER_EXPERTS)
+def qwen2_moe_fp8_router_experts(
+    hidden_states,
+    router_weight,
+    shared_gate_weight,
+    w1,
+    w1_scale,
+    w2,
+    w2_scale,
+    topk=10,
+): ...
+
+
+def _qwen2_experts_key(call):
+    common = _qwen2_common_key(call, False)
+    if common is None:
+        return None
+    n_tokens, _, n_routed, _ = common
+    wts, ids = call["topk_weights"], call["topk_ids"]
+    device = call["hidden_states"].device
+    if not tensor_ok(wts, torch.float32, 2, device) or not tensor_ok(ids, torch.int32, 2, device):
+        return None
+    if wts.shape != ids.shape or wts.shape[0] != n_tokens or not (1 <= wts.shape[1] <= min(31, n_routed)):
+        return None
+    return ("row_major", *common[1:], wts.shape[1])
+
+
+def _qwen2_experts_run(call, out):
+    x, ids_in, w_in = call["hidden_states"], call["topk_ids"], call["topk_weights"]
+    n_tokens, topk = ids_in.shape
+    ids = torch.empty((n_tokens, topk + 1), dtype=torch.int32, device=x.device)
+    weights = torch.empty((n_tokens, topk + 1), dtype=torch.float32, device=x.device)
+    moe.with_gated_shared_slot(x, call["shared_gate_weight"], ids, weights, call["w1"].shape[0] - 1, copy_from=(ids_in, w_in))
+    moe.fused_experts_fp8(x, ids, weights, call["w1"], call["w1_scale"], call["w2"], call["w2_scale"], out=out)
+
+
+QWEN2_MOE_FP8_EXPERTS = OpContract(
+    contract_id="qwen2_moe_fp8_experts@1.0",
+    description=(
+        "sglang's Qwen2MoeSparseMoeBlock experts on one rank at a given routing, the gated shared expert fused "
+        "in after the routed ones (w1/w2's last slot)."
+    ),
+    params=[
+        Param("hidden_states"),
+        Param("topk_weights"),
+        Param("topk_ids"),
+        Param("shared_gate_weight"),
+        Param("w1"),
+        Param("w1_scale"),
+        Param("w2"),
+        Param("w2_scale"),
+    ],
+    outputs=["out"],
+    key=_qwen2_experts_key,
+    alloc=_layer_alloc,
+    run=_qwen2_experts_run,
+)
+
+
+@api(QWEN2_MOE_FP8_EXPERTS)
+def qwen2_moe_fp8_experts(
+    hidden_states,
+    topk_weights,
+    topk_ids,
+    shared_gate_weight,
+    w1,
+    w1_scale,
+    w2,
+    w2_scale,
+): ...
+
+
+def _qwen2_router_key(call):
+    x, rw, wts, ids = call["hidden_states"], call["router_weight"], call["topk_weights"], call["topk_ids"]
+    if not tensor_ok(x, BF16, 2):
+        return None
+    device = x.device
+    n_tokens, hidden = x.shape
+    if not (1 <= n_tokens <= MAX_TOKENS) or not tensor_ok(rw, BF16, 2, device) or rw.shape[1] != hidden or hidden % 8:
+        return None
+    n_routed = rw.shape[0]
+    if not tensor_ok(wts, torch.float32, 2, device) or not tensor_ok(ids, torch.int32, 2, device):
+        return None
+    if wts.shape != ids.shape or wts.shape[0] != n_tokens or not (1 <= wts.shape[1] <= min(32, n_routed)) or n_routed > 1024:
+        return None
+    if overlaps(wts, ids) or overlaps(wts, x) or overlaps(ids, x):
+        return None
+    return (hidden, n_routed, wts.shape[1])
+
+
+def _qwen2_router_alloc(call, key):
+    return call["topk_weights"], call["topk_ids"]
+
+
+def _qwen2_router_run(call, outputs):
+    logits = moe.router_logits(call["hidden_states"], call["router_weight"])
+    moe.route(logits, None, moe.Routing(topk=call["topk_ids"].shape[1]), call["topk_ids"], call["topk_weights"])
+
+
+QWEN2_MOE_ROUTER = OpContract(
+    contract_id="qwen2_moe_router@1.0",
+    description=(
+        "sglang's Qwen2MoeSparseMoeBlock router: bf16 logits, each token's topk experts by descending logit "
+        "(ties to the lower id) weighed by the softmax of their logits."
+    ),
+    params=[Param("hidden_states"), Param("router_weight"), Param("topk_weights"), Param("topk_ids")],
+    outputs=["topk_weights", "topk_ids"],
+    key=_qwen2_router_key,
+    alloc=_qwen2_router_alloc,
+    run=_qwen2_router_run,
+)
+
+
+@api(QWEN2_MOE_ROUTER)
+def qwen2_moe_router(hidden_states, router_weight, topk_weights, topk_ids): ...
 
 
 # --------------------------------------------------------------------------------------------------
@@ -792,6 +978,9 @@ CONTRACTS = (
     DEEPSEEK_V2_FP8_MOE,
     QWEN3_MOE_FP8_MOE,
     MINIMAX_M2_FP8_MOE,
+    QWEN2_MOE_ROUTER,
+    QWEN2_MOE_FP8_EXPERTS,
+    QWEN2_MOE_FP8_ROUTER_EXPERTS,
     FUSED_MOE,
     MEGA_MOE,
     BIASED_GROUPED_TOPK,

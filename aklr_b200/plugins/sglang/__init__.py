@@ -13,29 +13,30 @@ __all__ = ["SGLANG_HOOKED_METHOD", "register"]
 
 # the runtime starts after this sglang method: the rank's device is set by then
 SGLANG_HOOKED_METHOD = "sglang.srt.model_executor.model_runner.ModelRunner.init_torch_distributed"
-ROUTE_MODULES = ("deepseek_v2", "qwen3_moe", "minimax_m2")
+ROUTE_MODULES = ("deepseek_v2", "qwen3_moe", "minimax_m2", "qwen2_moe")
+
+
+def _start_runtime(_result, *_args, **_kwargs) -> None:
+    DispatcherRegistry.default().init_once()
+
+
+def _hook_up() -> None:
+    from sglang.srt.plugins.hook_registry import HookRegistry, HookType
+
+    # always: the ops must be loadable by direct callers even when no route is installed
+    HookRegistry.register(SGLANG_HOOKED_METHOD, _start_runtime, HookType.AFTER)
+    env = RuntimeEnv()
+    if env.is_sglang_plugin_enabled and not env.is_all_disabled:
+        for module in ROUTE_MODULES:  # a route module declares its routes when imported
+            importlib.import_module(f"{__name__}.models.{module}")
+        hook.install()
 
 
 def register() -> None:
-    """Entry point sglang calls once per process; a plugin that cannot start ends the process
-    (sglang would only log the error)."""
+    """What sglang's ``sglang.srt.plugins`` entry point calls, once per process.  sglang only logs an
+    exception raised by a plugin and carries on without it; a deployment that asked for this plugin
+    should not run silently unaccelerated, so a failed start exits the process instead."""
     try:
-        _register()
-    except Exception as e:
-        raise SystemExit(f"aklr_b200: the sglang plugin cannot start: {e!r}") from e
-
-
-def _register() -> None:
-    from sglang.srt.plugins.hook_registry import HookRegistry, HookType
-
-    HookRegistry.register(
-        SGLANG_HOOKED_METHOD,
-        lambda result, *args, **kwargs: DispatcherRegistry.default().init_once(),
-        HookType.AFTER,
-    )
-    env = RuntimeEnv()
-    if env.is_all_disabled or not env.is_sglang_plugin_enabled:
-        return
-    for name in ROUTE_MODULES:  # importing a module declares its routes
-        importlib.import_module(f"{__name__}.models.{name}")
-    hook.install()
+        _hook_up()
+    except Exception as failure:
+        raise SystemExit(f"aklr_b200: the sglang plugin cannot start: {failure!r}") from failure

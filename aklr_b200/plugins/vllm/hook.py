@@ -58,76 +58,103 @@ def vllm_version() -> str:
     return Version(version("vllm")).public
 
 
-def _parameters(fn: Callable) -> list[tuple[str, object]]:
+def _calling_convention(fn: Callable) -> list[tuple[str, object]]:
+    """Parameter names and kinds: what a replacement must share with the function it replaces."""
     return [(p.name, p.kind) for p in inspect.signature(fn).parameters.values()]
 
 
-def install() -> list[str]:
-    """Validate the routes tested on the installed vLLM, then bind them all; returns the callees."""
-    installed = vllm_version()
-    blocked_groups = {
-        d.group for targets in _ROUTES.values() for d in targets.values()
-        if d.group is not None and installed not in d.versions
-    }
-    plan, untested, blocked = [], [], []
+@dataclass(frozen=True)
+class _Binding:
+    """One validated replacement, ready to be set: ``owner.attribute`` is ``callee``."""
+
+    callee: str
+    owner: object
+    attribute: str
+    replaced: Callable
+    route: Callable
+
+    @classmethod
+    def check(cls, route: Callable, callee: str, caller: str) -> "_Binding":
+        """Resolve ``callee`` and make sure replacing it can take effect and cannot break the caller:
+        ``caller``'s source must mention the callee's name followed by "(", and the route must take
+        the callee's parameters."""
+        owner_path, _, attribute = callee.rpartition(".")
+        if f"{attribute}(" not in inspect.getsource(pkgutil.resolve_name(caller)):
+            raise RuntimeError(f"{caller} does not call {callee}")
+        owner = pkgutil.resolve_name(owner_path)
+        replaced = getattr(owner, attribute)
+        if _calling_convention(route) != _calling_convention(replaced):
+            raise RuntimeError(f"{callee}: route {route.__qualname__} has incompatible parameters")
+        return cls(callee, owner, attribute, replaced, route)
+
+    def apply(self) -> None:
+        if self.callee not in _INSTALLED:
+            setattr(self.owner, self.attribute, _around(self.route, self.replaced, self.callee))
+            _INSTALLED[self.callee] = (self.owner, self.attribute, self.replaced)
+
+
+def _declarations():
     for route, targets in _ROUTES.items():
         for callee, declaration in targets.items():
-            if installed not in declaration.versions:
-                untested.append(declaration.caller)
-                continue
-            if declaration.group in blocked_groups:
-                blocked.append(f"{declaration.caller} (group={declaration.group})")
-                continue
-            caller_fn = pkgutil.resolve_name(declaration.caller)
-            attribute = callee.rsplit(".", 1)[-1]
-            if f"{attribute}(" not in inspect.getsource(caller_fn):
-                raise RuntimeError(f"{declaration.caller} does not call {callee}")
-            owner_name, _, _ = callee.rpartition(".")
-            owner = pkgutil.resolve_name(owner_name)
-            orig = getattr(owner, attribute)
-            if _parameters(route) != _parameters(orig):
-                raise RuntimeError(f"{callee}: route {route.__qualname__} has incompatible parameters")
-            plan.append((callee, owner, attribute, orig, route))
-    # everything validated: bind the batch
-    for callee, owner, attribute, orig, route in plan:
-        if callee in _INSTALLED:
-            continue
-        setattr(owner, attribute, _around(route, orig, callee))
-        _INSTALLED[callee] = (owner, attribute, orig)
-    notes = []
-    if untested:
-        notes.append(f"untested callers: {', '.join(dict.fromkeys(untested))}")
-    if blocked:
-        notes.append(f"blocked by untested group members: {', '.join(dict.fromkeys(blocked))}")
-    _LOGGER.warning("aklr_b200 hooks %d calls of vLLM %s%s", len(plan), installed, f"; {'; '.join(notes)}" if notes else "")
-    return [p[0] for p in plan]
+            yield route, callee, declaration
+
+
+def install() -> list[str]:
+    """Bind every route that stands on the installed vLLM; returns the callees replaced.
+
+    Two passes, so that a failed check leaves vLLM untouched: first every declaration is sorted into
+    untested (its versions do not name the installed release), held back (a member of its group is
+    untested: a group replaces cooperating functions and half of one is worse than none) or checked
+    into a ``_Binding``; then the bindings are applied."""
+    release = vllm_version()
+    partial_groups = {
+        declaration.group
+        for _, _, declaration in _declarations()
+        if declaration.group is not None and release not in declaration.versions
+    }
+    bindings: list[_Binding] = []
+    skipped: dict[str, list[str]] = {"untested callers": [], "blocked by untested group members": []}
+    for route, callee, declaration in _declarations():
+        if release not in declaration.versions:
+            skipped["untested callers"].append(declaration.caller)
+        elif declaration.group in partial_groups:
+            skipped["blocked by untested group members"].append(f"{declaration.caller} (group={declaration.group})")
+        else:
+            bindings.append(_Binding.check(route, callee, declaration.caller))
+    for binding in bindings:
+        binding.apply()
+    notes = "".join(f"; {what}: {', '.join(dict.fromkeys(who))}" for what, who in skipped.items() if who)
+    _LOGGER.warning("aklr_b200: %d vLLM calls hooked on vLLM %s%s", len(bindings), release, notes)
+    return [binding.callee for binding in bindings]
 
 
 def restore() -> None:
-    """Put every original callable back."""
-    for owner, attribute, orig in _INSTALLED.values():
-        setattr(owner, attribute, orig)
-    _INSTALLED.clear()
+    """Undo ``install``: every replaced attribute gets its original value back."""
+    while _INSTALLED:
+        _, (owner, attribute, replaced) = _INSTALLED.popitem()
+        setattr(owner, attribute, replaced)
 
 
 def original(callee: str) -> Callable:
-    """The callable ``callee`` named before its route was installed."""
+    """What ``callee`` named before ``install`` replaced it."""
     return _INSTALLED[callee][2]
 
 
 def _around(route: Callable, orig: Callable, callee: str) -> Callable:
-    route_name = f"{route.__module__}.{route.__qualname__}"
+    """``orig`` with ``route`` tried first.  Inside a ``torch.compile`` trace the route is not tried:
+    dynamo would trace the dispatch lookup and recompile per shape, so compiled regions keep vLLM's
+    own function."""
+    label = f"{route.__module__}.{route.__qualname__}"
 
     def hooked(*args, **kwargs):
-        # Dynamo would trace the dispatch lookup and recompile per shape: compiled regions keep vLLM's code
-        if not torch.compiler.is_compiling():
-            result = route(*args, **kwargs)
-            fallback = result if isinstance(result, FallbackReason) else None
-            if (tracer := dispatch.trace()) is not None and tracer.is_plugin:
-                tracer.plugin("vllm", callee, route_name, fallback)
-            if fallback is None:
-                return result
-        return orig(*args, **kwargs)
+        if torch.compiler.is_compiling():
+            return orig(*args, **kwargs)
+        answer = route(*args, **kwargs)
+        declined = isinstance(answer, FallbackReason)
+        tracer = dispatch.trace()
+        if tracer is not None and tracer.is_plugin:
+            tracer.plugin("vllm", callee, label, answer if declined else None)
+        return orig(*args, **kwargs) if declined else answer
 
     hooked.__wrapped__ = orig
     hooked.__name__ = getattr(orig, "__name__", "hooked")

@@ -196,6 +196,14 @@ int aklr_moe_align_noalloc(const int32_t* topk_ids, const int32_t* expert_map, i
 int32_t aklr_moe_align_noalloc_max_scratch_ints(void);
 const char* aklr_moe_align_noalloc_last_error(void);
 
+/* Qwen2-MoE's gated shared expert (`_experts`, aklr/plugins/sglang/models/qwen2_moe/reference.py:84-90):
+ * slot `topk` of the [T, topk+1] routing tables becomes expert `shared_slot` at weight
+ * sigmoid(x . shared_gate_weight) (both bf16).  topk_ids_in / topk_weights_in [T, topk] are copied into the
+ * first slots when given; NULL when those slots are already written (aklr_moe_route with n_shared 1). */
+int aklr_moe_shared_gate(const void* x, const void* shared_gate_weight, const int32_t* topk_ids_in,
+                         const float* topk_weights_in, int32_t* topk_ids, float* topk_weights, int32_t n_tokens,
+                         int32_t hidden, int32_t topk, int32_t shared_slot, void* stream);
+
 /* logits float32 [T,E] = x (bf16 [T,H]) @ w (float32 [E,H])^T, nothing rounded: the gate of
  * `minimax_m2_fp8_moe` (aklr/plugins/sglang/models/minimax_m2/reference.py:43-50). */
 int aklr_router_gemm_f32(const void* x, const float* w, float* logits, int32_t n_tokens, int32_t hidden,

@@ -300,6 +300,30 @@ def deepseek_v2_fp8_moe(
     return fp8_experts(hidden, ids, weights, w1, w1_scale, w2, w2_scale)
 
 
+def with_gated_shared_slot(hidden, shared_gate_weight, ids, weights, shared_slot: int):
+    """Append the shared expert ``shared_slot`` weighed by sigmoid(hidden . shared_gate_weight[0]).
+    Follows the head of ``_experts`` (aklr/plugins/sglang/models/qwen2_moe/reference.py:84-90)."""
+    shared_weight = (hidden.float() @ shared_gate_weight.float()[0]).sigmoid()
+    ids = torch.cat([ids, torch.full_like(ids[:, :1], shared_slot)], dim=-1)
+    return ids, torch.cat([weights, shared_weight[:, None]], dim=-1)
+
+
+def qwen2_moe_fp8_experts(hidden, topk_weights, topk_ids, shared_gate_weight, w1, w1_scale, w2, w2_scale):
+    """Routed experts at the given routing plus the gated shared expert in w1/w2's last slot.
+    Follows ``qwen2_moe_fp8_experts_reference`` (aklr/plugins/sglang/models/qwen2_moe/reference.py:135-143)."""
+    ids, weights = with_gated_shared_slot(hidden, shared_gate_weight, topk_ids.long(), topk_weights.float(), w1.shape[0] - 1)
+    return fp8_experts(hidden, ids, weights, w1, w1_scale, w2, w2_scale)
+
+
+def qwen2_moe_fp8_router_experts(hidden, router_weight, shared_gate_weight, w1, w1_scale, w2, w2_scale, topk, logits=None):
+    """bf16 router logits, softmax top-k, routed experts and the gated shared one.
+    Follows ``qwen2_moe_fp8_router_experts_reference`` (aklr/plugins/sglang/models/qwen2_moe/reference.py:146-155)."""
+    if logits is None:
+        logits = router_logits(hidden, router_weight)
+    ids, weights = softmax_topk(logits.float(), topk)
+    return qwen2_moe_fp8_experts(hidden, weights, ids, shared_gate_weight, w1, w1_scale, w2, w2_scale)
+
+
 def sigmoid_bias_topk(logits: torch.Tensor, bias: torch.Tensor, topk: int) -> tuple[torch.Tensor, torch.Tensor]:
     """(ids, weights): the ``topk`` experts by sigmoid score + bias (ties to the lower id), weighed by
     their unbiased scores renormalised to sum 1.

@@ -51,6 +51,17 @@ def minimax_layer():
     )
 
 
+def qwen2_layer():
+    """Qwen2-MoE-style layer: 12 routed experts, top-4 softmax, a gated shared expert in the last slot."""
+    cfg, seed, tokens = wl.MoEConfig("qwen2_small", hidden=256, inter=128, n_routed=12, topk=4, n_shared=1), 1357, 36
+    hidden, _, _ = wl.router_inputs(cfg, tokens, seed)
+    g = torch.Generator().manual_seed(seed + 3)
+    rw = (wl.router_weight(cfg, seed) * 30).to(torch.bfloat16)
+    gate = (torch.randn(1, cfg.hidden, generator=g) * (2.0 / cfg.hidden**0.5)).to(torch.bfloat16)
+    w1, s1, w2, s2 = wl.expert_weights(cfg, seed)
+    return cfg, dict(hidden_states=hidden, router_weight=rw, shared_gate_weight=gate, w1=w1, w1_scale=s1, w2=w2, w2_scale=s2)
+
+
 def route_ds():
     _, logits, bias = wl.router_inputs(ROUTE_SHAPE, 192, 77)
     return logits, bias

@@ -116,6 +116,22 @@ def main() -> None:
         if isinstance(v, torch.Tensor):
             meta[f"minimax.{k}"] = sha256_of(v)
 
+    # ---- layer: Qwen2-MoE (softmax top-k + shared expert gated by sigmoid(x . g)) ---------------
+    from aklr.plugins.sglang.models.qwen2_moe import reference as q2
+
+    cfg, rargs = cases.qwen2_layer()
+    point = SimpleNamespace(
+        dtypes={**FP8_DTYPES, "shared_gate_weight": "bfloat16", "topk_weights": "float32", "topk_ids": "int32"},
+        attrs={"topk": cfg.topk},
+        axes={"n_routed": cfg.n_routed, "n_experts": cfg.n_routed + 1, "topk": cfg.topk},
+    )
+    weights, ids = q2.qwen2_moe_router_reference(point, rargs)
+    out["qwen2.ids"], out["qwen2.weights"] = ids.numpy(), f32(weights)
+    out["qwen2.out"] = f32(q2.qwen2_moe_fp8_router_experts_reference(point, rargs))
+    out["qwen2.experts_out"] = f32(q2.qwen2_moe_fp8_experts_reference(point, {**rargs, "topk_weights": weights, "topk_ids": ids}))
+    for k, v in rargs.items():
+        meta[f"qwen2.{k}"] = sha256_of(v)
+
     # ---- routing only, at the full expert counts -----------------------------------------
     logits, bias = cases.route_ds()
     point = SimpleNamespace(

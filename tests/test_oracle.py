@@ -84,6 +84,22 @@ def test_minimax_layer_matches_reference(golden, golden_hashes):
     assert (ids < a["expert_offset"]).any() and (ids >= a["expert_offset"] + cfg.n_routed).any()  # routes to other ranks exist
 
 
+def test_qwen2_layer_matches_reference(golden, golden_hashes):
+    torch.set_num_threads(1)
+    cfg, a = cases.qwen2_layer()
+    check_inputs("qwen2", a, golden_hashes)
+    ids, w = orc.softmax_topk(orc.router_logits(a["hidden_states"], a["router_weight"]).float(), cfg.topk)
+    assert torch.equal(ids, t(golden["qwen2.ids"]).long()) and torch.equal(w, t(golden["qwen2.weights"]))
+    out = orc.qwen2_moe_fp8_router_experts(
+        a["hidden_states"], a["router_weight"], a["shared_gate_weight"], a["w1"], a["w1_scale"], a["w2"], a["w2_scale"], cfg.topk
+    )
+    assert torch.equal(out, t(golden["qwen2.out"]))
+    out = orc.qwen2_moe_fp8_experts(
+        a["hidden_states"], w, ids, a["shared_gate_weight"], a["w1"], a["w1_scale"], a["w2"], a["w2_scale"]
+    )
+    assert torch.equal(out, t(golden["qwen2.experts_out"]))
+
+
 def test_routing_matches_reference(golden, golden_hashes):
     logits, bias = cases.route_ds()
     assert orc.sha256_of(logits) == golden_hashes["route_ds.logits"]

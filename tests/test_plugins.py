@@ -42,11 +42,12 @@ def fake_sglang(monkeypatch):
         def register(target, fn, hook_type):
             registered.append((target, fn, hook_type))
 
-    modules = {name: types.ModuleType(name) for name in ("sglang", "sglang.srt", "sglang.srt.plugins", "sglang.srt.plugins.hook_registry", "sglang.srt.models", "sglang.srt.models.deepseek_v2", "sglang.srt.models.qwen3_moe", "sglang.srt.models.minimax_m2")}
+    modules = {name: types.ModuleType(name) for name in ("sglang", "sglang.srt", "sglang.srt.plugins", "sglang.srt.plugins.hook_registry", "sglang.srt.models", "sglang.srt.models.deepseek_v2", "sglang.srt.models.qwen3_moe", "sglang.srt.models.minimax_m2", "sglang.srt.models.qwen2_moe")}
     modules["sglang.srt.plugins.hook_registry"].HookRegistry = HookRegistry
     modules["sglang.srt.plugins.hook_registry"].HookType = HookType
     modules["sglang.srt.models.deepseek_v2"].DeepseekV2MoE = type("DeepseekV2MoE", (), {"forward_normal": lambda self, hidden_states: "sglang"})
     modules["sglang.srt.models.qwen3_moe"].Qwen3MoeSparseMoeBlock = type("Qwen3MoeSparseMoeBlock", (), {"forward_normal": lambda self, hidden_states: "sglang"})
+    modules["sglang.srt.models.qwen2_moe"].Qwen2MoeSparseMoeBlock = type("Qwen2MoeSparseMoeBlock", (), {"_forward_router_experts": lambda self, hidden_states, *, defer_finalize=False: "sglang"})
     modules["sglang.srt.models.minimax_m2"].MiniMaxM2MoE = type("MiniMaxM2MoE", (), {"forward_normal": lambda self, hidden_states: "sglang"})
     for name, module in modules.items():
         monkeypatch.setitem(sys.modules, name, module)
@@ -58,17 +59,18 @@ def fake_sglang(monkeypatch):
 
 def test_sglang_install_hooks_only_routes_tested_on_the_installed_release(fake_sglang, monkeypatch):
     from aklr_b200.plugins.sglang import hook
-    from aklr_b200.plugins.sglang.models import deepseek_v2, minimax_m2, qwen3_moe  # noqa: F401  (declare the routes)
+    from aklr_b200.plugins.sglang.models import deepseek_v2, minimax_m2, qwen2_moe, qwen3_moe  # noqa: F401  (declare the routes)
 
     monkeypatch.setattr(hook, "sglang_version", lambda: "0.5.22")
-    assert hook.install() == 2
+    assert hook.install() == 3
     assert sorted(t for t, _, _ in fake_sglang.registered) == [
         "sglang.srt.models.minimax_m2.MiniMaxM2MoE.forward_normal",
+        "sglang.srt.models.qwen2_moe.Qwen2MoeSparseMoeBlock._forward_router_experts",
         "sglang.srt.models.qwen3_moe.Qwen3MoeSparseMoeBlock.forward_normal",
     ]
     fake_sglang.registered.clear()
     monkeypatch.setattr(hook, "sglang_version", lambda: "0.5.23")
-    assert hook.install() == 3
+    assert hook.install() == 4
     assert all(kind is fake_sglang.HookType.AROUND for _, _, kind in fake_sglang.registered)
     fake_sglang.registered.clear()
     monkeypatch.setattr(hook, "sglang_version", lambda: "0.9.0")
@@ -94,9 +96,10 @@ def test_sglang_around_serves_falls_back_and_skips_compiled_regions(monkeypatch,
 
 
 def test_sglang_routes_take_their_targets_parameters():
-    from aklr_b200.plugins.sglang.models import deepseek_v2, minimax_m2, qwen3_moe
+    from aklr_b200.plugins.sglang.models import deepseek_v2, minimax_m2, qwen2_moe, qwen3_moe
 
     assert list(inspect.signature(minimax_m2._moe_forward_normal).parameters) == ["self", "hidden_states"]
+    assert list(inspect.signature(qwen2_moe._forward_router_experts).parameters) == ["self", "hidden_states", "defer_finalize"]
     assert list(inspect.signature(deepseek_v2._moe_forward_normal).parameters) == [
         "self", "hidden_states", "gemm_output_zero_allocator", "input_ids", "input_ids_global",
         "skip_shared_experts", "use_vision_topk", "return_moe_output", "leave_output_sum",
@@ -114,7 +117,7 @@ def test_sglang_register_starts_only_when_switched_on(fake_sglang, monkeypatch):
     fake_sglang.registered.clear()
     monkeypatch.setenv("AKLR_SGLANG_PLUGIN", "1")
     plugin.register()
-    assert len(fake_sglang.registered) == 4  # the start hook + three model routes
+    assert len(fake_sglang.registered) == 5  # the start hook + four model routes
     monkeypatch.setenv("AKLR_SGLANG_PLUGIN", "maybe")
     with pytest.raises(SystemExit, match="cannot start"):
         plugin.register()
@@ -165,6 +168,29 @@ def test_moe_blocks_predicates(monkeypatch):
     assert moe_blocks.topk_falls_back(topk(use_grouped_topk=True), scoring_func="softmax", biased=False)
     assert moe_blocks.topk_falls_back(topk(renormalize=False), scoring_func="softmax", biased=False)
     assert moe_blocks.topk_falls_back(topk(scoring_func="sigmoid"), scoring_func="softmax", biased=False)
+
+
+def test_conditions_name_what_is_unmet(monkeypatch, caplog):
+    import logging
+
+    from aklr_b200.plugins.sglang import conditions
+    from aklr_b200.plugins.sglang.models import moe_blocks
+
+    monkeypatch.setattr(moe_blocks, "_on_sm100", lambda experts: True)
+    assert moe_blocks.experts_unmet(_experts(), ("Fp8MoEMethod",)) is None
+    assert moe_blocks.experts_unmet(_experts(reduce_results=True), ("Fp8MoEMethod",)) == "the ranks' sum left to the caller"
+    gelu = _experts()
+    gelu.quant_method.runner.config.activation = "gelu"
+    assert moe_blocks.experts_unmet(gelu, ("Fp8MoEMethod",)) == "SiLU activation"
+    assert "QuarkW4A4MXFp4MoE" in moe_blocks.experts_unmet(_experts(), ("QuarkW4A4MXFp4MoE",))
+    assert conditions.attr(gelu, "quant_method.runner.config.activation") == "gelu"
+    assert conditions.attr(gelu, "quant_method.nothing.here", 7) == 7
+    with pytest.raises(AttributeError, match="nothing"):
+        conditions.attr(gelu, "quant_method.nothing")
+    with caplog.at_level(logging.INFO, logger=conditions.__name__):
+        assert conditions.leave_to_sglang("pkg.f", "SiLU activation") is FallbackReason.OUT_OF_CONTRACT
+        conditions.leave_to_sglang("pkg.f", "SiLU activation")
+    assert len([r for r in caplog.records if "pkg.f stays on sglang: SiLU activation" in r.getMessage()]) == 1
 
 
 def test_deepseek_route_maps_the_module_to_the_op_arguments():
