@@ -44,6 +44,19 @@ class MoeConfig(ctypes.Structure):
     ]
 
 
+class MxOptions(ctypes.Structure):
+    """``aklr_mx_options`` of the public header."""
+
+    _fields_ = [
+        ("activation", c_int32),
+        ("weight_in_stage1", c_int32),
+        ("swiglu_limit", c_float),
+        ("beta", c_float),
+        ("linear_beta", c_float),
+        ("num_local_tokens", c_void_p),
+    ]
+
+
 class WorkspaceLayout(ctypes.Structure):
     _fields_ = [(name, c_int64) for name in (
         "total_bytes", "status", "topk_ids", "topk_weights", "sorted_ids", "block_expert", "counts",
@@ -60,6 +73,7 @@ SIGNATURES = {
     "aklr_moe_fp8_forward": (c_int32, [POINTER(MoeConfig)] + [c_void_p] * 9 + [c_void_p, c_size_t, c_void_p]),
     "aklr_moe_fp8_experts": (c_int32, [POINTER(MoeConfig)] + [c_void_p] * 9 + [c_void_p, c_size_t, c_void_p]),
     "aklr_moe_mxfp4_experts": (c_int32, [POINTER(MoeConfig)] + [c_void_p] * 8 + [c_float, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "aklr_moe_mxfp4_experts_ex": (c_int32, [POINTER(MoeConfig)] + [c_void_p] * 8 + [POINTER(MxOptions), c_void_p, c_void_p, c_size_t, c_void_p]),
     "aklr_moe_mxfp4_forward": (c_int32, [POINTER(MoeConfig)] + [c_void_p] * 8 + [c_float, c_void_p, c_void_p, c_size_t, c_void_p]),
     "aklr_ep_gather_quant_mxfp8": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p]),
     "aklr_moe_mxfp4_experts_prequant": (c_int32, [POINTER(MoeConfig)] + [c_void_p] * 8 + [c_float, c_void_p, c_void_p, c_size_t, c_void_p]),

@@ -357,7 +357,7 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
 int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, const void* hidden_states,
                    const int32_t* topk_ids, const float* topk_weights, const int32_t* expert_map,
                    int n_experts_global, const void* w1, const uint8_t* w1_scale, const void* w2,
-                   const uint8_t* w2_scale, float swiglu_limit, void* out, uint8_t* ws, cudaStream_t stream,
+                   const uint8_t* w2_scale, const aklr_mx_options& opt, void* out, uint8_t* ws, cudaStream_t stream,
                    const uint8_t* q_in = nullptr, const uint8_t* scales_in = nullptr, void* rows_out = nullptr,
                    int slot = -1) {
   using namespace aklr;
@@ -381,6 +381,8 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   ap.n_experts = experts;
   ap.n_experts_global = n_experts_global;
   ap.block_m = 128;
+  ap.num_local_tokens = opt.num_local_tokens;
+  ap.routes_per_token = routes_per_token;
   int rc = launch_align(ap, stream);
   if (rc) return fail(rc, "moe_align launch failed");
   g_launches += routes <= 4096 ? 1 : 3;
@@ -435,7 +437,11 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   g1.out_q = ws + l.hq;
   g1.out_scale = ws + l.hs;
   g1.status = status;
-  g1.swiglu_limit = swiglu_limit;
+  g1.swiglu_limit = opt.swiglu_limit;
+  g1.activation = opt.activation;
+  g1.beta = opt.beta;
+  g1.linear_beta = opt.linear_beta;
+  g1.stage1_weights = opt.weight_in_stage1 ? topk_weights : nullptr;
   g1.k = c.hidden;
   g1.out_dim = c.inter;
   g1.rows_per_expert = 2 * c.inter;
@@ -456,7 +462,7 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   g2.sorted_ids = sorted_ids;
   g2.block_expert = block_expert;
   g2.num_blocks = num_blocks;
-  g2.topk_weights = topk_weights;
+  g2.topk_weights = opt.weight_in_stage1 ? nullptr : topk_weights;
   g2.out_rows = rows_out ? rows_out : ws + l.rows;
   g2.status = status;
   g2.k = c.inter;
@@ -482,11 +488,18 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   cp.hidden = c.hidden;
   cp.routes_per_token = routes_per_token;
   cp.n_experts_global = n_experts_global;
+  cp.num_local_tokens = opt.num_local_tokens;
   rc = launch_combine(cp, stream);
   if (rc) return fail(rc, "combine launch failed");
   g_launches += 1;
   profile_mark(stream, slot, 6);
   return AKLR_OK;
+}
+
+aklr_mx_options clamp_only(float swiglu_limit) {
+  aklr_mx_options opt{};
+  opt.swiglu_limit = swiglu_limit;
+  return opt;
 }
 
 int prepare(const aklr_moe_config* cfg, aklr_moe_workspace_layout* l, void* workspace, size_t workspace_bytes,
@@ -601,14 +614,19 @@ int aklr_moe_fp8_experts_prequant(const aklr_moe_config* cfg, const void* rows_q
                      out_rows);
 }
 
-int aklr_moe_mxfp4_experts(const aklr_moe_config* cfg, const void* hidden_states, const int32_t* topk_ids,
-                           const float* topk_weights, const int32_t* expert_map, const void* w1,
-                           const uint8_t* w1_scale, const void* w2, const uint8_t* w2_scale, float swiglu_limit,
-                           void* out, void* workspace, size_t workspace_bytes, void* stream_) {
+int aklr_moe_mxfp4_experts_ex(const aklr_moe_config* cfg, const void* hidden_states, const int32_t* topk_ids,
+                              const float* topk_weights, const int32_t* expert_map, const void* w1,
+                              const uint8_t* w1_scale, const void* w2, const uint8_t* w2_scale,
+                              const aklr_mx_options* options, void* out, void* workspace, size_t workspace_bytes,
+                              void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  if (!cfg) return fail(AKLR_ERR_BAD_ARGUMENT, "cfg is NULL");
+  if (!cfg || !options) return fail(AKLR_ERR_BAD_ARGUMENT, "cfg or options is NULL");
   if (cfg->block_m != 128) return fail(AKLR_ERR_BAD_ARGUMENT, "the MXFP4 path works on 128-token blocks: set block_m = 128");
   if (cfg->hidden % 256 != 0) return fail(AKLR_ERR_UNSUPPORTED_SHAPE, "the MXFP4 path needs hidden %% 256 == 0 (got %d)", cfg->hidden);
+  if (options->activation < AKLR_ACT_SILU || options->activation > AKLR_ACT_SITUV2)
+    return fail(AKLR_ERR_BAD_ARGUMENT, "activation %d is not one of AKLR_ACT_*", options->activation);
+  if (options->activation == AKLR_ACT_SITUV2 && !(options->beta > 0.0f && options->linear_beta > 0.0f))
+    return fail(AKLR_ERR_BAD_ARGUMENT, "AKLR_ACT_SITUV2 needs beta > 0 and linear_beta > 0");
   aklr_moe_workspace_layout l;
   int rc = prepare(cfg, &l, workspace, workspace_bytes, stream);
   if (rc) return rc;
@@ -619,7 +637,16 @@ int aklr_moe_mxfp4_experts(const aklr_moe_config* cfg, const void* hidden_states
   const int global = expert_map ? cfg->n_experts_global : local;
   if (expert_map && global < 1) return fail(AKLR_ERR_BAD_ARGUMENT, "n_experts_global must be set with an expert map");
   return run_mx_experts(*cfg, l, hidden_states, topk_ids, topk_weights, expert_map, global, w1, w1_scale, w2, w2_scale,
-                        swiglu_limit, out, static_cast<uint8_t*>(workspace), stream);
+                        *options, out, static_cast<uint8_t*>(workspace), stream);
+}
+
+int aklr_moe_mxfp4_experts(const aklr_moe_config* cfg, const void* hidden_states, const int32_t* topk_ids,
+                           const float* topk_weights, const int32_t* expert_map, const void* w1,
+                           const uint8_t* w1_scale, const void* w2, const uint8_t* w2_scale, float swiglu_limit,
+                           void* out, void* workspace, size_t workspace_bytes, void* stream_) {
+  const aklr_mx_options options = clamp_only(swiglu_limit);
+  return aklr_moe_mxfp4_experts_ex(cfg, hidden_states, topk_ids, topk_weights, expert_map, w1, w1_scale, w2, w2_scale,
+                                   &options, out, workspace, workspace_bytes, stream_);
 }
 
 int aklr_moe_mxfp4_forward(const aklr_moe_config* cfg, const void* hidden_states, const void* logits,
@@ -645,7 +672,7 @@ int aklr_moe_mxfp4_forward(const aklr_moe_config* cfg, const void* hidden_states
   if (rc) return rc;
   profile_mark(stream, slot, 1);
   return run_mx_experts(*cfg, l, hidden_states, ids, weights, nullptr, cfg->n_routed + cfg->n_shared, w1, w1_scale, w2,
-                        w2_scale, swiglu_limit, out, ws, stream, nullptr, nullptr, nullptr, slot);
+                        w2_scale, clamp_only(swiglu_limit), out, ws, stream, nullptr, nullptr, nullptr, slot);
 }
 
 int aklr_moe_mxfp4_experts_prequant(const aklr_moe_config* cfg, const void* rows_q, const uint8_t* rows_scale,
@@ -668,7 +695,7 @@ int aklr_moe_mxfp4_experts_prequant(const aklr_moe_config* cfg, const void* rows
   profile_mark(stream, slot, 0);
   profile_mark(stream, slot, 1);
   return run_mx_experts(*cfg, l, nullptr, expert_ids, weights, nullptr, cfg->n_routed, w1, w1_scale, w2, w2_scale,
-                        swiglu_limit, nullptr, static_cast<uint8_t*>(workspace), stream,
+                        clamp_only(swiglu_limit), nullptr, static_cast<uint8_t*>(workspace), stream,
                         static_cast<const uint8_t*>(rows_q), rows_scale, out_rows, slot);
 }
 

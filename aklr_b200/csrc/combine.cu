@@ -22,6 +22,7 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
     const int token = static_cast<int>(i / vec_per_row);
     const int v = static_cast<int>(i - static_cast<int64_t>(token) * vec_per_row);
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const bool received = !p.num_local_tokens || token < __ldg(p.num_local_tokens);
     // Slots are summed in order, but their loads do not wait for one another: ids of a batch of
     // slots first, then all of its rows, then the additions (a decode call is one latency chain).
     constexpr int kBatchSlots = 9;
@@ -34,7 +35,7 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
         live[d] = false;
         if (s < p.routes_per_token) {
           const int e = __ldg(p.topk_ids + token * p.routes_per_token + s);
-          live[d] = e >= 0 && e < p.n_experts_global && (!p.expert_map || __ldg(p.expert_map + e) >= 0);
+          live[d] = received && e >= 0 && e < p.n_experts_global && (!p.expert_map || __ldg(p.expert_map + e) >= 0);
         }
       }
 #pragma unroll

@@ -128,6 +128,22 @@ __device__ __forceinline__ int mxfp8_exponent(float amax) {
   return e < -126 ? -126 : (e > 127 ? 127 : e);
 }
 
+// act(gate) * up for the activations of the reference's experts-only op
+// (aklr/ops/fused_moe/reference.py:113-121).  The branch is uniform over the grid.
+__device__ __forceinline__ float gated_product(int activation, float gate, float up, float beta, float linear_beta) {
+  switch (activation) {
+    case AKLR_ACT_GELU:  // exact (erf) GELU
+      return 0.5f * gate * (1.0f + erff(gate * 0.70710678118654752f)) * up;
+    case AKLR_ACT_SWIGLU_OAI:  // gpt-oss: alpha 1.702, up biased by 1
+      return __fdividef(gate, 1.0f + __expf(-1.702f * gate)) * (up + 1.0f);
+    case AKLR_ACT_SITUV2:
+      return beta * tanhf(__fdividef(gate, beta)) * __fdividef(1.0f, 1.0f + __expf(-gate)) *
+             (linear_beta * tanhf(__fdividef(up, linear_beta)));
+    default:
+      return __fdividef(gate, 1.0f + __expf(-gate)) * up;
+  }
+}
+
 template <bool GATE_UP>
 __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __grid_constant__ MxGemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -434,7 +450,10 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
       if (et < kBM) {
         const int rid = p.sorted_ids[b * kBM + et];
         rid_s[et] = rid;
-        if (!GATE_UP) wgt_s[et] = rid >= 0 ? p.topk_weights[rid] : 0.0f;
+        // down: the route weight, or 1 when the gate_up projection already carried it; gate_up: the
+        // route weight when it is applied there (doweight_stage1), else 1
+        const float* weights = GATE_UP ? p.stage1_weights : p.topk_weights;
+        wgt_s[et] = rid < 0 ? 0.0f : (weights ? weights[rid] : 1.0f);
       }
       epi_sync();  // the epilogue reads other threads' entries
       // ---- epilogue: the whole K reduction is in TMEM ----
@@ -469,6 +488,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
       const int rid = rid_s[row];
       if (GATE_UP) {
         const int IB = p.out_dim >> 7;
+        const float w1row = p.stage1_weights ? wgt_s[row] : 1.0f;  // exact when the weight is not applied here
         // two 1 x 32 groups of this thread's 64 h channels
         uint32_t packed[16];
         uint32_t scale_bytes = 0;
@@ -477,12 +497,12 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
           float m = 0.0f;
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            float gate = acc[g * 32 + i], up = acc[64 + g * 32 + i];
+            float gate = acc[g * 32 + i] * w1row, up = acc[64 + g * 32 + i] * w1row;
             if (p.swiglu_limit > 0.0f) {
               gate = fminf(gate, p.swiglu_limit);
               up = fminf(fmaxf(up, -p.swiglu_limit), p.swiglu_limit);
             }
-            const float h = __fdividef(gate, 1.0f + __expf(-gate)) * up;
+            const float h = gated_product(p.activation, gate, up, p.beta, p.linear_beta);
             acc[g * 32 + i] = __bfloat162float(__float2bfloat16_rn(h));
             m = fmaxf(m, fabsf(acc[g * 32 + i]));
           }

@@ -8,6 +8,12 @@
 
 #define AKLR_SCORING_SOFTMAX 0
 #define AKLR_SCORING_SIGMOID 1
+#ifndef AKLR_ACT_SILU  // the public header defines the same values
+#define AKLR_ACT_SILU 0
+#define AKLR_ACT_GELU 1
+#define AKLR_ACT_SWIGLU_OAI 2
+#define AKLR_ACT_SITUV2 3
+#endif
 
 namespace aklr {
 
@@ -34,7 +40,9 @@ struct AlignParams {
   int32_t* pair_table;        // optional [max_blocks]: first block of every run of <= 2 blocks of one
                               // expert; bit 31 set when the second block exists
   int32_t* chunk_hist;        // [ceil(n_routes/1024) * n_experts] scratch
+  const int32_t* num_local_tokens;  // optional device scalar: routes of tokens at or past it are dropped
   int n_routes, n_experts, n_experts_global, block_m;
+  int routes_per_token;       // read with num_local_tokens only
 };
 int launch_align(const AlignParams& p, cudaStream_t stream);
 
@@ -124,6 +132,9 @@ struct MxGemmParams {
   void* out_rows;              // down: [n_routes, hidden] bf16
   int32_t* status;
   float swiglu_limit;          // > 0: clamp gate above and up on both sides before the activation
+  int activation;              // gate_up: AKLR_ACT_* of the public header
+  float beta, linear_beta;     // gate_up, AKLR_ACT_SITUV2: saturation of gate and up
+  const float* stage1_weights; // gate_up: route weights applied to the projection before the activation, or null
   int k, out_dim, rows_per_expert, max_blocks, stages;
 };
 int grouped_gemm_mx_pick_stages(bool gate_up);
@@ -134,6 +145,7 @@ struct CombineParams {
   const int32_t* topk_ids;   // [n_tokens, routes_per_token] global ids
   const int32_t* expert_map; // null or global -> local (-1: not here, the route adds nothing)
   void* out;                 // [n_tokens, hidden] bf16
+  const int32_t* num_local_tokens;  // optional device scalar: tokens at or past it get zeros
   int n_tokens, hidden, routes_per_token, n_experts_global;
 };
 int launch_combine(const CombineParams& p, cudaStream_t stream);

@@ -209,6 +209,8 @@ constexpr int kSortChunk = 1024;  // routes per CTA, one per thread
 __device__ __forceinline__ int local_expert(const AlignParams& p, int route) {
   int e = p.topk_ids[route];
   if (e < 0 || e >= p.n_experts_global) return -1;
+  // rows a rank did not receive (aklr/ops/fused_moe/reference.py:85-86)
+  if (p.num_local_tokens && route / p.routes_per_token >= __ldg(p.num_local_tokens)) return -1;
   if (p.expert_map) e = p.expert_map[e];
   return (e >= 0 && e < p.n_experts) ? e : -1;
 }

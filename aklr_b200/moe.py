@@ -280,6 +280,10 @@ def _check_mx_weights(hidden_states, w1, w1_scale, w2, w2_scale):
     return e, inter, h
 
 
+# the AKLR_ACT_* values of the public header, by the reference's attribute names
+ACTIVATIONS = {"silu": 0, "gelu": 1, "swiglu": 2, "situv2": 3}
+
+
 def fused_experts_mxfp4(
     hidden_states: torch.Tensor,
     topk_ids: torch.Tensor,
@@ -292,9 +296,21 @@ def fused_experts_mxfp4(
     swiglu_limit: float | None = None,
     out: torch.Tensor | None = None,
     return_workspace: bool = False,
+    activation: str = "silu",
+    weight_in_stage1: bool = False,
+    beta: float | None = None,
+    linear_beta: float | None = None,
+    num_local_tokens: torch.Tensor | None = None,
 ):
-    """MXFP4-weight experts with MXFP8 activations, routing given (block-scaled tcgen05 MMA)."""
-    device = _need_cuda(hidden_states, topk_ids, topk_weights, w1, w1_scale, w2, w2_scale, expert_map, out)
+    """MXFP4-weight experts with MXFP8 activations, routing given (block-scaled tcgen05 MMA).
+    ``activation`` one of ACTIVATIONS; ``weight_in_stage1`` applies the route weight to the gate_up
+    projection instead of the output; ``num_local_tokens`` (int32 device scalar) zeroes the rows at
+    or past it (aklr/ops/fused_moe/reference.py:85-127)."""
+    device = _need_cuda(hidden_states, topk_ids, topk_weights, w1, w1_scale, w2, w2_scale, expert_map, out, num_local_tokens)
+    options = _lib.MxOptions(
+        ACTIVATIONS[activation], int(weight_in_stage1), float(swiglu_limit or 0.0), float(beta or 0.0),
+        float(linear_beta or 0.0), _ptr(num_local_tokens),
+    )
     e, inter, h = _check_mx_weights(hidden_states, w1, w1_scale, w2, w2_scale)
     if topk_ids.dtype != torch.int32 or topk_weights.dtype != torch.float32 or topk_ids.shape != topk_weights.shape:
         raise ValueError("topk_ids int32 and topk_weights float32 must share the shape [tokens, routes]")
@@ -305,9 +321,9 @@ def fused_experts_mxfp4(
     if out is None:
         out = torch.empty_like(hidden_states)
     _lib.check(
-        _lib.load().aklr_moe_mxfp4_experts(
+        _lib.load().aklr_moe_mxfp4_experts_ex(
             ctypes.byref(cfg), _ptr(hidden_states), _ptr(topk_ids), _ptr(topk_weights), _ptr(expert_map), _ptr(w1),
-            _ptr(w1_scale), _ptr(w2), _ptr(w2_scale), float(swiglu_limit or 0.0), _ptr(out), ws.base.data_ptr(),
+            _ptr(w1_scale), _ptr(w2), _ptr(w2_scale), ctypes.byref(options), _ptr(out), ws.base.data_ptr(),
             ws.layout.total_bytes, _stream(),
         )
     )

@@ -556,20 +556,35 @@ def _mx_weights_key(call: Mapping[str, Any], hidden: int, device) -> tuple | Non
 
 
 def _fused_moe_mx_key(call, x, device, n_tokens, hidden):
-    """The reference's own Points: MXFP4 experts (quant_type per_1x32), activations quantised to
-    MXFP8 (act_quant 8), gated SiLU, optional clamp (swiglu_limit)."""
-    if call["act_quant"] != 8 or _attr_name(call["activation"]) not in ("silu", None):
+    """MXFP4 experts (quant_type per_1x32) with activations quantised to MXFP8 (act_quant 8) and
+    gate rows before up rows: the activations silu, gelu, gpt-oss's swiglu (from 256 tokens, where the
+    reference quantises; it needs its clamp) and situv2 (with both betas); an optional clamp; the
+    route weight in either stage; an expert mask, with or without a count of rows received."""
+    activation = _attr_name(call["activation"]) or "silu"
+    if call["act_quant"] != 8 or activation not in moe.ACTIVATIONS:
         return None
     if call["w1_scale"] is None or call["w2_scale"] is None:
         return None
     weights = _mx_weights_key(call, hidden, device)
     if weights is None:
         return None
-    unsupported = ("a1_scale", "a2_scale", "bias1", "bias2", "beta", "linear_beta", "num_local_tokens")
-    if any(call[name] is not None for name in unsupported) or call["doweight_stage1"]:
+    if any(call[name] is not None for name in ("a1_scale", "a2_scale", "bias1", "bias2")):
+        return None
+    if not isinstance(call["doweight_stage1"], bool):
         return None
     limit = call["swiglu_limit"]
     if limit is not None and not (isinstance(limit, (int, float)) and limit > 0):
+        return None
+    if activation == "swiglu" and (limit is None or n_tokens < 256):
+        return None
+    betas = (call["beta"], call["linear_beta"])
+    if activation == "situv2":
+        if not all(isinstance(b, (int, float)) and not isinstance(b, bool) and b > 0 for b in betas):
+            return None
+    elif any(b is not None for b in betas):
+        return None
+    received = call["num_local_tokens"]
+    if received is not None and (call["expert_mask"] is None or not tensor_ok(received, torch.int32, 1, device) or received.numel() != 1):
         return None
     if call["gate_mode"] not in (None, "separated") or call["out_dtype"] not in (None, BF16):
         return None
@@ -584,7 +599,8 @@ def _fused_moe_mx_key(call, x, device, n_tokens, hidden):
     out = call["out"]
     if out is not None and (not tensor_ok(out, BF16, 2, device) or out.shape != x.shape):
         return None
-    return ("mxfp4", hidden, weights[0], weights[1], ids.shape[1], mask is not None, limit is not None)
+    return ("mxfp4", hidden, weights[0], weights[1], ids.shape[1], mask is not None, limit is not None, activation,
+            call["doweight_stage1"], received is not None)
 
 
 def _fused_moe_key(call):
@@ -650,6 +666,11 @@ def _fused_moe_run(call, out):
             expert_map=expert_map,
             swiglu_limit=call["swiglu_limit"],
             out=out,
+            activation=_attr_name(call["activation"]) or "silu",
+            weight_in_stage1=call["doweight_stage1"],
+            beta=call["beta"],
+            linear_beta=call["linear_beta"],
+            num_local_tokens=call["num_local_tokens"],
         )
         return
     moe.fused_experts_fp8(

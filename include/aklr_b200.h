@@ -37,6 +37,11 @@ extern "C" {
 #define AKLR_SCORING_SIGMOID 1
 #define AKLR_DTYPE_BF16 0
 #define AKLR_DTYPE_F32 1
+/* act(gate) in act(gate) * up (aklr/ops/fused_moe/reference.py:113-121) */
+#define AKLR_ACT_SILU 0       /* gate * sigmoid(gate) */
+#define AKLR_ACT_GELU 1       /* exact (erf) GELU */
+#define AKLR_ACT_SWIGLU_OAI 2 /* gpt-oss: gate * sigmoid(1.702 gate) * (up + 1) */
+#define AKLR_ACT_SITUV2 3     /* beta tanh(gate/beta) sigmoid(gate) * linear_beta tanh(up/linear_beta) */
 
 /* One fused-MoE layer call.  Expert slots in w1/w2: the n_routed routed experts, then n_shared
  * shared experts every token visits at weight 1 (aklr/plugins/sglang/models/deepseek_v2/
@@ -128,6 +133,23 @@ int aklr_moe_mxfp4_forward(const aklr_moe_config* cfg, const void* hidden_states
                            const void* bias, const float* sigmoid_table, const void* w1, const uint8_t* w1_scale,
                            const void* w2, const uint8_t* w2_scale, float swiglu_limit, void* out, void* workspace,
                            size_t workspace_bytes, void* stream);
+
+/* The remaining attributes of `fused_moe` (aklr/ops/fused_moe/contract.py:90-140, reference.py:85-127).
+ * A zeroed struct is aklr_moe_mxfp4_experts with no clamp. */
+typedef struct aklr_mx_options {
+  int32_t activation;              /* AKLR_ACT_* */
+  int32_t weight_in_stage1;        /* doweight_stage1: the route weight multiplies the gate_up projection
+                                      (before clamp and activation) instead of the expert's output */
+  float swiglu_limit;              /* > 0: clamp gate (above) and up (both sides) before the activation */
+  float beta, linear_beta;         /* AKLR_ACT_SITUV2 only; both > 0 */
+  const int32_t* num_local_tokens; /* device scalar or NULL: routes of tokens at or past it add nothing and
+                                      their output rows are zero (rows this rank did not receive) */
+} aklr_mx_options;
+int aklr_moe_mxfp4_experts_ex(const aklr_moe_config* cfg, const void* hidden_states, const int32_t* topk_ids,
+                              const float* topk_weights, const int32_t* expert_map, const void* w1,
+                              const uint8_t* w1_scale, const void* w2, const uint8_t* w2_scale,
+                              const aklr_mx_options* options, void* out, void* workspace, size_t workspace_bytes,
+                              void* stream);
 
 /* Expert parallelism (the reference's `mega_moe` contract: every rank holds n_local experts, global
  * expert e is local e % n_local of rank e / n_local; aklr/ops/mega_moe/contract.py:42-51,

@@ -399,14 +399,27 @@ def mx_experts(
     w2_scale: torch.Tensor,
     swiglu_limit: float | None = None,
     act_bits: int = 8,
+    activation: str = "silu",
+    weight_in_stage1: bool = False,
+    beta: float | None = None,
+    linear_beta: float | None = None,
+    num_local_tokens: int | None = None,
 ) -> torch.Tensor:
     """MXFP4-weight experts given the routing: activations MXFP8 (act_bits 8) or MXFP4 (4) per
     1 x 32, the gated product rounded to bf16 before it is quantised, each route weighted,
     the routes of a token summed.  Negative ids add nothing.  ``swiglu_limit`` clamps gate
     (above) and up (both sides) before the activation when given.
-    Follows ``fused_moe_reference`` (aklr/ops/fused_moe/reference.py:64-127, silu branch) and
+    ``activation`` silu, gelu (erf), swiglu (gpt-oss: gate sigmoid(1.702 gate) (up + 1)) or situv2
+    (beta tanh(gate/beta) sigmoid(gate) times linear_beta tanh(up/linear_beta)); ``weight_in_stage1``
+    multiplies the gate_up projection by the route weight instead of the output; rows at or past
+    ``num_local_tokens`` add nothing.
+    Follows ``fused_moe_reference`` (aklr/ops/fused_moe/reference.py:64-127) and
     ``mega_moe_reference`` (aklr/ops/mega_moe/reference.py:18-48)."""
     quantize = mxfp8_input if act_bits == 8 else mxfp4_input
+    weights = weights.float()
+    if num_local_tokens is not None:
+        ids = ids.clone()
+        ids[num_local_tokens:] = -1
     x = quantize(hidden.float())
     out = x.new_zeros((*ids.shape, x.shape[-1]))
     for e in ids.unique().tolist():
@@ -415,12 +428,25 @@ def mx_experts(
         routed = ids == e
         tokens = routed.nonzero(as_tuple=True)[0]
         projected = x[tokens] @ mx_weight(w1[e], w1_scale[e]).mT
+        if weight_in_stage1:
+            projected = projected * weights[routed].unsqueeze(-1)
         gate, up = projected.chunk(2, dim=-1)
         if swiglu_limit is not None:
             gate, up = gate.clamp(max=swiglu_limit), up.clamp(-swiglu_limit, swiglu_limit)
-        gated = bf16_round(torch.nn.functional.silu(gate) * up)
-        out[routed] = quantize(gated) @ mx_weight(w2[e], w2_scale[e]).mT
-    return (out * weights.float().unsqueeze(-1)).sum(dim=1)
+        if activation == "silu":
+            gated = torch.nn.functional.silu(gate) * up
+        elif activation == "gelu":
+            gated = torch.nn.functional.gelu(gate) * up
+        elif activation == "swiglu":
+            gated = gate * torch.sigmoid(1.702 * gate) * (up + 1)
+        elif activation == "situv2":
+            gated = beta * torch.tanh(gate / beta) * torch.sigmoid(gate) * (linear_beta * torch.tanh(up / linear_beta))
+        else:
+            raise ValueError(f"activation {activation!r}")
+        out[routed] = quantize(bf16_round(gated)) @ mx_weight(w2[e], w2_scale[e]).mT
+    if not weight_in_stage1:
+        out = out * weights.unsqueeze(-1)
+    return out.sum(dim=1)
 
 
 # --------------------------------------------------------------------------------------

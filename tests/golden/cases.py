@@ -104,6 +104,24 @@ def mx_case(seed: int, tokens: int = 12, hidden: int = 128, inter: int = 64, exp
     return dict(hidden_states=x, w1=w1, w1_scale=s1, w2=w2, w2_scale=s2, topk_ids=ids, topk_weights=wts)
 
 
+def mx_variants():
+    """The other attributes of the experts-only op, one case each: (name, inputs, reference attrs, oracle
+    keywords).  gpt-oss's swiglu has 256 tokens: below that the reference leaves activations unquantised."""
+    mask = torch.tensor([1, 0, 1, 1, 0, 1], dtype=torch.int32)
+    local = mx_case(13)
+    held = {k: local[k][:4] for k in ("w1", "w1_scale", "w2", "w2_scale")}
+    return [
+        ("gelu", mx_case(11), {"activation": "gelu"}, {"activation": "gelu"}),
+        ("swiglu", {**mx_case(12, tokens=256), "swiglu_limit": 7.0}, {"activation": "swiglu"},
+         {"activation": "swiglu", "swiglu_limit": 7.0}),
+        ("situv2", {**mx_case(14), "beta": 3.0, "linear_beta": 5.0}, {"activation": "situv2"},
+         {"activation": "situv2", "beta": 3.0, "linear_beta": 5.0}),
+        ("stage1", mx_case(15), {"doweight_stage1": True}, {"weight_in_stage1": True}),
+        ("local", {**local, **held, "expert_mask": mask, "num_local_tokens": torch.tensor([9], dtype=torch.int32)},
+         {"has_expert_mask": True, "has_num_local_tokens": True}, {"num_local_tokens": 9}),
+    ]
+
+
 def mega_group():
     """Two ranks, 3 experts each: global expert e = local e % 3 of rank e // 3."""
     base = mx_case(7)

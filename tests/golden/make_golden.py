@@ -202,6 +202,15 @@ def main() -> None:
     out["mx_moe_a4.out"] = f32(fused_moe_reference(point, rargs))
     for k, v in rargs.items():
         meta[f"mx_moe.{k}"] = sha256_of(v)
+    # the op's other attributes at act_quant 8: activations, stage-1 weighting, rows not received
+    for name, vargs, vattrs, _ in cases.mx_variants():
+        point.attrs.update({"act_quant": 8, "activation": "silu", "doweight_stage1": False, "has_expert_mask": False,
+                            "has_num_local_tokens": False, **vattrs})
+        point.axes["n_tokens"] = vargs["hidden_states"].shape[0]
+        out[f"mx_moe_{name}.out"] = f32(fused_moe_reference(point, vargs))
+        for k, v in vargs.items():
+            if torch.is_tensor(v):
+                meta[f"mx_moe_{name}.{k}"] = sha256_of(v)
     # two ranks, 3 experts each: global expert e = local e % 3 of rank e // 3
     point = SimpleNamespace(
         dtypes={"hidden_states": "bfloat16", "topk_weights": "float32"}, axes={"n_experts": 3}

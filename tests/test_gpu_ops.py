@@ -195,6 +195,52 @@ def test_fused_moe_op_mxfp4(ops):
                          w2_scale=s2.to(d)) is ops.FallbackReason.OUT_OF_CONTRACT
 
 
+def test_fused_moe_op_mxfp4_attributes(ops):
+    """The op's other attributes on the MXFP4 path against the oracle (itself pinned to the reference's
+    outputs for each of them): gelu, gpt-oss's swiglu with its clamp, situv2, the route weight applied
+    in stage 1, and an expert mask with a count of rows received.  300 tokens: three 128-row blocks per
+    busy expert, and past the 256 rows from which the reference quantises swiglu's activations."""
+    cfg = wl.MoEConfig("mx", hidden=512, inter=256, n_routed=8, topk=2)
+    w1, s1, w2, s2 = wl.mx_expert_weights(cfg, seed=5)
+    g = torch.Generator().manual_seed(6)
+    n = 300
+    x = torch.randn(n, 512, generator=g).to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(8, generator=g)[:2] for _ in range(n)]).to(torch.int32)
+    wts = torch.rand(n, 2, generator=g) + 0.25
+    d = dev()
+
+    def run(**kw):
+        return ops.fused_moe(x.to(d), kw.pop("w1", w1).to(d), kw.pop("w2", w2).to(d), wts.to(d), ids.to(d), quant_type="per_1x32",
+                             w1_scale=kw.pop("w1_scale", s1).to(d), w2_scale=kw.pop("w2_scale", s2).to(d), act_quant=8, **kw)
+
+    def check(out, ref, what):
+        assert isinstance(out, torch.Tensor), (what, out)
+        gates = orc.output_gates(out.cpu(), ref)
+        assert orc.gates_pass(gates), (what, gates)
+
+    base = (x, ids.long(), wts, w1, s1, w2, s2)
+    check(run(activation="gelu"), orc.mx_experts(*base, activation="gelu"), "gelu")
+    check(run(activation="swiglu", swiglu_limit=7.0), orc.mx_experts(*base, activation="swiglu", swiglu_limit=7.0), "swiglu")
+    check(run(activation="situv2", beta=3.0, linear_beta=5.0),
+          orc.mx_experts(*base, activation="situv2", beta=3.0, linear_beta=5.0), "situv2")
+    check(run(doweight_stage1=True), orc.mx_experts(*base, weight_in_stage1=True), "stage1")
+    # experts 0, 2, 3, 5, 6 held here; rows from 211 on were not received
+    mask = torch.tensor([1, 0, 1, 1, 0, 1, 1, 0], dtype=torch.int32)
+    held = mask.bool()
+    slot = torch.where(held[ids.long()], (mask.long().cumsum(0) - 1)[ids.long()], -1)
+    received = torch.tensor([211], dtype=torch.int32)
+    out = run(w1=w1[held], w1_scale=s1[held], w2=w2[held], w2_scale=s2[held], expert_mask=mask.to(d), num_local_tokens=received.to(d))
+    ref = orc.mx_experts(x, slot, wts, w1[held], s1[held], w2[held], s2[held], num_local_tokens=211)
+    check(out, ref, "mask + rows received")
+    assert not out[211:].any() and out[:211].any()
+    # out of contract: swiglu below 256 tokens or without its clamp, situv2 without its betas, a row count without a mask
+    few = dict(quant_type="per_1x32", w1_scale=s1.to(d), w2_scale=s2.to(d), act_quant=8)
+    assert ops.fused_moe(x[:100].to(d), w1.to(d), w2.to(d), wts[:100].to(d), ids[:100].to(d), activation="swiglu", swiglu_limit=7.0, **few) is ops.FallbackReason.OUT_OF_CONTRACT
+    assert run(activation="swiglu") is ops.FallbackReason.OUT_OF_CONTRACT
+    assert run(activation="situv2", beta=3.0) is ops.FallbackReason.OUT_OF_CONTRACT
+    assert run(num_local_tokens=received.to(d)) is ops.FallbackReason.OUT_OF_CONTRACT
+
+
 def test_biased_grouped_topk_and_quant_ops(ops, golden):
     logits, bias = cases.bgt()
     d = dev()

@@ -158,6 +158,20 @@ def test_mx_experts_match_reference(golden, golden_hashes):
         assert torch.equal(out, t(golden[f"mega.rank{r}.out"]))
 
 
+def test_mx_experts_variants_match_reference(golden, golden_hashes):
+    """Activations, stage-1 weighting, the expert mask with rows not received: each against the
+    reference's stored output, bit for bit."""
+    torch.set_num_threads(1)
+    for name, a, _, kw in cases.mx_variants():
+        check_inputs(f"mx_moe_{name}", {k: v for k, v in a.items() if torch.is_tensor(v)}, golden_hashes)
+        ids = a["topk_ids"].long()
+        if "expert_mask" in a:  # a global id to its slot in w1, -1 off this rank
+            held = a["expert_mask"].long()
+            ids = torch.where(held[ids] == 1, (held.cumsum(0) - 1)[ids], -1)
+        out = orc.mx_experts(a["hidden_states"], ids, a["topk_weights"], a["w1"], a["w1_scale"], a["w2"], a["w2_scale"], **kw)
+        assert torch.equal(out, t(golden[f"mx_moe_{name}.out"])), name
+
+
 def test_moe_align_is_a_stable_padded_sort():
     ids = torch.tensor([[2, 0], [2, 1], [0, 2], [-1, 2]])
     sorted_ids, block_expert, counts = orc.moe_align(ids, 4, 4)
