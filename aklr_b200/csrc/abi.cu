@@ -202,13 +202,47 @@ void layout_of(const aklr_moe_config& c, aklr_moe_workspace_layout* l) {
 }
 
 // Everything after the routing table exists: sort, quantise, two grouped GEMMs, combine.
+aklr::RouteParams route_params(const aklr_moe_config& c, const void* logits, const void* bias, const float* sigmoid_table,
+                               int32_t* topk_ids, float* topk_weights) {
+  aklr::RouteParams p{};
+  p.logits = logits;
+  p.bias = bias;
+  p.sigmoid_table = sigmoid_table;
+  p.topk_ids = topk_ids;
+  p.topk_weights = topk_weights;
+  p.n_tokens = c.n_tokens;
+  p.n_routed = c.n_routed;
+  p.n_shared = c.n_shared;
+  p.topk = c.topk;
+  p.scoring = c.scoring;
+  p.num_expert_group = c.num_expert_group < 1 ? 1 : c.num_expert_group;
+  p.topk_group = c.topk_group < 1 ? 1 : c.topk_group;
+  p.renormalize = c.renormalize;
+  p.logits_are_bf16 = c.logits_dtype == AKLR_DTYPE_BF16;
+  p.bias_is_bf16 = c.bias_dtype == AKLR_DTYPE_BF16;
+  p.routed_scaling_factor = c.routed_scaling_factor;
+  return p;
+}
+
+// Whether a call's routing and sort run as the one-CTA decode prologue.
+std::atomic<int> g_fused_prologue{1};  // aklr_debug_fused_prologue(0) keeps the two kernels (tests compare)
+bool fused_prologue_serves(const aklr_moe_config& c) {
+  return g_fused_prologue.load() && c.n_tokens >= 1 && c.n_tokens <= aklr::kDecodePrologueTokens && c.n_routed <= aklr::kDecodePrologueExperts &&
+         c.n_tokens * (c.topk + c.n_shared) <= 1024 &&
+         (c.num_expert_group > 1 && c.topk_group < c.num_expert_group ? c.num_expert_group : 1) * c.topk <=
+             aklr::kDecodePrologueExperts;
+}
+
 int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, const void* hidden_states,
                 const int32_t* topk_ids, const float* topk_weights, const int32_t* expert_map,
                 int n_experts_global, const void* w1, const float* w1_scale, const void* w2,
                 const float* w2_scale, void* out, uint8_t* ws, cudaStream_t stream, int slot,
-                const uint8_t* q_in = nullptr, const float* scales_in = nullptr, void* rows_out = nullptr) {
+                const uint8_t* q_in = nullptr, const float* scales_in = nullptr, void* rows_out = nullptr,
+                const aklr::RouteParams* route = nullptr) {
   // q_in/scales_in: the rows arrive already quantised (expert-parallel receive side);
-  // rows_out: write the weighted per-route rows there and skip the combine.
+  // rows_out: write the weighted per-route rows there and skip the combine;
+  // route: the routing has not run yet -- a decode batch does it and the sort in one kernel (the
+  // caller checked fused_prologue_serves).
   using namespace aklr;
   const int routes_per_token = c.topk + c.n_shared;
   const int routes = c.n_tokens * routes_per_token;
@@ -235,9 +269,16 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
                      grouped_gemm_is_token_major(false, l.block_m, c.hidden);
   int32_t* pair_table = block_expert + l.max_blocks;  // second half of the block table's space
   if (pairs) ap.pair_table = pair_table;
-  int rc = launch_align(ap, stream);
-  if (rc) return fail(rc, "moe_align launch failed");
-  g_launches += routes <= 4096 ? 1 : 3;
+  int rc = AKLR_OK;
+  if (route) {
+    rc = launch_decode_prologue(*route, ap, stream);
+    if (rc) return fail(rc, "decode prologue launch failed");
+    g_launches += 1;
+  } else {
+    rc = launch_align(ap, stream);
+    if (rc) return fail(rc, "moe_align launch failed");
+    g_launches += routes <= 4096 ? 1 : 3;
+  }
   profile_mark(stream, slot, 2);
 
   GatherQuantParams qp{};
@@ -566,6 +607,12 @@ int aklr_moe_fp8_forward(const aklr_moe_config* cfg, const void* hidden_states, 
   float* weights = reinterpret_cast<float*>(ws + l.topk_weights);
   const int slot = profile_slot();
   profile_mark(stream, slot, 0);
+  if (fused_prologue_serves(*cfg)) {
+    const aklr::RouteParams route = route_params(*cfg, logits, bias, sigmoid_table, ids, weights);
+    profile_mark(stream, slot, 1);
+    return run_experts(*cfg, l, hidden_states, ids, weights, nullptr, cfg->n_routed + cfg->n_shared, w1, w1_scale, w2,
+                       w2_scale, out, ws, stream, slot, nullptr, nullptr, nullptr, &route);
+  }
   rc = aklr_moe_route(cfg, logits, bias, sigmoid_table, ids, weights, stream_);
   if (rc) return rc;
   profile_mark(stream, slot, 1);
@@ -806,23 +853,7 @@ int aklr_moe_route(const aklr_moe_config* cfg, const void* logits, const void* b
   if (!cfg || !logits || !topk_ids || !topk_weights) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
   int rc = check_device();
   if (rc) return rc;
-  aklr::RouteParams p{};
-  p.logits = logits;
-  p.bias = bias;
-  p.sigmoid_table = sigmoid_table;
-  p.topk_ids = topk_ids;
-  p.topk_weights = topk_weights;
-  p.n_tokens = cfg->n_tokens;
-  p.n_routed = cfg->n_routed;
-  p.n_shared = cfg->n_shared;
-  p.topk = cfg->topk;
-  p.scoring = cfg->scoring;
-  p.num_expert_group = cfg->num_expert_group < 1 ? 1 : cfg->num_expert_group;
-  p.topk_group = cfg->topk_group < 1 ? 1 : cfg->topk_group;
-  p.renormalize = cfg->renormalize;
-  p.logits_are_bf16 = cfg->logits_dtype == AKLR_DTYPE_BF16;
-  p.bias_is_bf16 = cfg->bias_dtype == AKLR_DTYPE_BF16;
-  p.routed_scaling_factor = cfg->routed_scaling_factor;
+  const aklr::RouteParams p = route_params(*cfg, logits, bias, sigmoid_table, topk_ids, topk_weights);
   rc = aklr::launch_route(p, static_cast<cudaStream_t>(stream));
   if (rc) return fail(rc, "routing: %s", aklr_status_string(rc));
   g_launches += p.n_tokens > 0;
@@ -960,6 +991,11 @@ int64_t aklr_kernel_launch_count(void) { return g_launches.load(); }
 
 int aklr_debug_force_cta_pairs(int32_t mode) {
   g_force_pairs = mode < 0 ? -1 : (mode != 0 ? 1 : 0);
+  return AKLR_OK;
+}
+
+int aklr_debug_fused_prologue(int32_t on) {
+  g_fused_prologue = on != 0;
   return AKLR_OK;
 }
 

@@ -63,6 +63,12 @@ struct GatherQuantParams {
   int n_rows, hidden, routes_per_token, block_m;
 };
 int launch_gather_quant_fp8(const GatherQuantParams& p, cudaStream_t stream);
+
+// Routing and sort of a decode batch (1..kDecodePrologueTokens tokens, up to kDecodePrologueExperts routed
+// experts) in one CTA.
+constexpr int kDecodePrologueTokens = 8;
+constexpr int kDecodePrologueExperts = 256;
+int launch_decode_prologue(const RouteParams& rp, const AlignParams& ap, cudaStream_t stream);
 int launch_gather_rows_fp8(const GatherQuantParams& p, cudaStream_t stream);
 
 // standalone quant ops

@@ -14,70 +14,15 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "quant_rows.cuh"
 
 namespace aklr {
 
-__device__ __forceinline__ void unpack8(const uint4& raw, float (&v)[8]) {
-  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    v[2 * i] = __uint_as_float(w[i] << 16);
-    v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-  }
-}
-
-__device__ __forceinline__ float amax8(const float (&v)[8]) {
-  float m = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[i]));
-  return m;
-}
-
-__device__ __forceinline__ uint2 pack8_e4m3(const float (&v)[8]) {
-  uint2 out;
-  out.x = cvt_e4m3x2(v[0], v[1]) | (static_cast<uint32_t>(cvt_e4m3x2(v[2], v[3])) << 16);
-  out.y = cvt_e4m3x2(v[4], v[5]) | (static_cast<uint32_t>(cvt_e4m3x2(v[6], v[7])) << 16);
-  return out;
-}
-
-// One half-warp (16 lanes x 8 values) per 1 x 128 group.
 __global__ void __launch_bounds__(256) gather_quant_fp8_kernel(GatherQuantParams p) {
   griddep_launch();
   griddep_wait();
-  const int groups_per_row = p.hidden >> 7;
-  const int n_rows = p.num_rows ? min(*p.num_rows, p.n_rows) : p.n_rows;
-  const int64_t total = static_cast<int64_t>(n_rows) * groups_per_row;
-  const int sub = threadIdx.x & 15;
-  const uint32_t group_mask = 0xFFFFu << (threadIdx.x & 16);  // the lanes of this half-warp
-  const int64_t half_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 4;
-  for (int64_t g = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4; g < total;
-       g += half_warps) {
-    const int row = static_cast<int>(g / groups_per_row);
-    const int grp = static_cast<int>(g - static_cast<int64_t>(row) * groups_per_row);
-    int token = row;
-    if (p.sorted_ids) {
-      const int rid = p.sorted_ids[row];
-      token = rid < 0 ? -1 : rid / p.routes_per_token;
-    }
-    if (token < 0) continue;  // padding rows are never read back
-    const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.x) +
-                                                      static_cast<size_t>(token) * p.hidden + grp * 128 + sub * 8);
-    float v[8];
-    unpack8(raw, v);
-    float m = amax8(v);
-#pragma unroll
-    for (int off = 8; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(group_mask, m, off, 16));
-    const float scale = fmaxf(__fdiv_rn(m, 448.0f), FLT_MIN);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = __fdiv_rn(v[i], scale);
-    *reinterpret_cast<uint2*>(p.q + static_cast<size_t>(row) * p.hidden + grp * 128 + sub * 8) = pack8_e4m3(v);
-    if (sub == 0) {
-      if (p.block_m > 0)  // [block][group][row in block]: what the grouped GEMM stages per tile
-        p.scales[(static_cast<size_t>(row / p.block_m) * groups_per_row + grp) * p.block_m + row % p.block_m] = scale;
-      else
-        p.scales[static_cast<size_t>(row) * groups_per_row + grp] = scale;
-    }
-  }
+  gather_quant_fp8_groups(p, (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4,
+                          (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 4);
 }
 
 // Rows already quantised elsewhere (each token once, or by the sender of an expert-parallel

@@ -178,8 +178,155 @@ __global__ void __launch_bounds__(256) route_kernel(RouteParams p) {
   }
 }
 
-int launch_route(const RouteParams& p, cudaStream_t stream) {
-  if (p.n_tokens == 0) return AKLR_OK;
+// ---------------------------------------------------------------------------------------------
+// Routing by counting: one thread per expert, for small batches.  The warp-per-token kernel above
+// walks ~2500 dependent instructions (every pick is a warp reduction); at a handful of tokens that
+// chain IS the latency.  Here an expert's position in the order is the number of keys greater than
+// its own, counted from shared memory with no cross-thread dependency, and keys are the same
+// (value image, ~expert) pairs, so the picks, their order and the weights are bit-identical.
+// Grouped routing counts inside the group first (the two best give the group score, the topk best
+// are the only candidates that can be picked), ranks the groups the same way, then counts among the
+// kept groups' candidates.
+// ---------------------------------------------------------------------------------------------
+template <int kExperts, int kCandidates>
+struct RouteSharedT {
+  unsigned long long key[kExperts];      // per expert
+  unsigned long long cand[kCandidates];  // [group][topk]: candidates of the kept groups, 0 elsewhere
+  unsigned long long gkey[32];    // per group
+  float gtop[64];                 // [group][2]: its two best biased scores
+  int kept[32];
+  int sel_id[32];
+  float sel_score[32];
+};
+using RouteShared = RouteSharedT<1024, 1024>;  // any shape launch_route accepts
+
+__device__ __forceinline__ unsigned long long route_key(uint32_t image, int index) {
+  return (static_cast<unsigned long long>(image) << 32) | static_cast<uint32_t>(~index);
+}
+
+__device__ __forceinline__ float value_of_image(uint32_t o) {
+  const uint32_t u = (o & 0x80000000u) ? (o & 0x7FFFFFFFu) : ~o;
+  return __uint_as_float(u);
+}
+
+// Thread e's expert of ``token``: what weighs it (``s``) and the image of what ranks it.  Split from
+// the counting so that a CTA routing several tokens has all their loads in flight at once.
+__device__ __forceinline__ void route_load(const RouteParams& p, int token, int e, float& s, uint32_t& image) {
+  const int E = p.n_routed;
+  s = 0.0f;
+  image = 0u;
+  if (e < E) {
+    float logit;
+    uint32_t bits16 = 0;
+    if (p.logits_are_bf16) {
+      bits16 = reinterpret_cast<const uint16_t*>(p.logits)[static_cast<size_t>(token) * E + e];
+      logit = bf16_bits_to_float(bits16);
+    } else {
+      logit = reinterpret_cast<const float*>(p.logits)[static_cast<size_t>(token) * E + e];
+    }
+    if (p.scoring == AKLR_SCORING_SIGMOID) {
+      s = (p.logits_are_bf16 && p.sigmoid_table) ? p.sigmoid_table[bits16] : sigmoid_exact(logit);
+      float b = 0.0f;
+      if (p.bias) b = p.bias_is_bf16 ? bf16_bits_to_float(reinterpret_cast<const uint16_t*>(p.bias)[e])
+                                     : reinterpret_cast<const float*>(p.bias)[e];
+      image = ordered_bits(s + b);
+    } else {
+      s = logit;
+      image = ordered_bits(logit);
+    }
+  }
+}
+
+// A team of ``team`` threads (a multiple of 32, at least max(n_routed, 32)) routes one token: thread
+// ``e`` of the team owns expert e, threads past n_routed only keep the barriers.  ``barrier`` 0 is
+// the CTA's (the team is the CTA); teams sharing a CTA each pass their own named barrier 1..15.
+__device__ __forceinline__ void team_sync(int barrier, int team) {
+  if (barrier == 0) __syncthreads();
+  else asm volatile("bar.sync %0, %1;" ::"r"(barrier), "r"(team) : "memory");
+}
+
+template <class Shared>
+__device__ void route_by_counting(const RouteParams& p, int token, int e, int team, int barrier, float s, uint32_t image,
+                                  Shared& sh) {
+  const int E = p.n_routed;
+  const bool has = e < E;
+  const unsigned long long key = has ? route_key(image, e) : 0ull;
+  const bool grouped = p.num_expert_group > 1 && p.topk_group < p.num_expert_group;
+  const int G = grouped ? p.num_expert_group : 1;
+  const int gs = E / G;
+  sh.key[e] = key;
+  for (int i = e; i < G * p.topk; i += team) sh.cand[i] = 0ull;
+  team_sync(barrier, team);
+  int g = 0, rank = 0;  // the expert's group and its position inside it
+  if (has) {
+    g = e / gs;
+    const unsigned long long* mine = sh.key + g * gs;
+    for (int i = 0; i < gs; ++i) rank += mine[i] > key;
+  }
+  int final_rank = rank;
+  if (grouped) {
+    if (has && rank < 2) sh.gtop[g * 2 + rank] = value_of_image(image);
+    team_sync(barrier, team);
+    if (e < G) sh.gkey[e] = route_key(ordered_bits(sh.gtop[2 * e] + sh.gtop[2 * e + 1]), e);
+    team_sync(barrier, team);
+    if (e < G) {
+      int ahead = 0;
+      for (int i = 0; i < G; ++i) ahead += sh.gkey[i] > sh.gkey[e];
+      sh.kept[e] = ahead < p.topk_group;
+    }
+    team_sync(barrier, team);
+    const bool candidate = has && rank < p.topk && sh.kept[g];
+    if (candidate) sh.cand[g * p.topk + rank] = key;
+    team_sync(barrier, team);
+    final_rank = p.topk;  // not picked
+    if (candidate) {
+      final_rank = 0;
+      for (int i = 0; i < G * p.topk; ++i) final_rank += sh.cand[i] > key;
+    }
+  }
+  if (has && final_rank < p.topk) {
+    sh.sel_id[final_rank] = e;
+    sh.sel_score[final_rank] = s;
+  }
+  team_sync(barrier, team);
+  const int ktot = p.topk + p.n_shared;
+  if (e < p.topk) {
+    const float my_score = sh.sel_score[e];
+    float w;
+    if (p.scoring == AKLR_SCORING_SIGMOID) {
+      float total = 0.0f;
+      for (int j = 0; j < p.topk; ++j) total += sh.sel_score[j];
+      w = p.renormalize ? __fdiv_rn(my_score, total) : my_score;
+      w *= p.routed_scaling_factor;
+    } else {  // softmax over the chosen logits (slot 0 holds the largest)
+      const float top_logit = sh.sel_score[0];
+      float total = 0.0f;
+      for (int j = 0; j < p.topk; ++j) total += expf(sh.sel_score[j] - top_logit);
+      w = __fdiv_rn(expf(my_score - top_logit), total);
+    }
+    p.topk_ids[static_cast<size_t>(token) * ktot + e] = sh.sel_id[e];
+    p.topk_weights[static_cast<size_t>(token) * ktot + e] = w;
+  } else if (e < ktot) {  // shared experts: the slots after the routed ones, at weight 1
+    p.topk_ids[static_cast<size_t>(token) * ktot + e] = E + (e - p.topk);
+    p.topk_weights[static_cast<size_t>(token) * ktot + e] = 1.0f;
+  }
+  team_sync(barrier, team);  // the next token reuses the shared arrays
+}
+
+__global__ void __launch_bounds__(1024) route_count_kernel(RouteParams p) {
+  __shared__ RouteShared sh;
+  griddep_launch();
+  griddep_wait();
+  float s;
+  uint32_t image;
+  route_load(p, blockIdx.x, threadIdx.x, s, image);
+  route_by_counting(p, blockIdx.x, threadIdx.x, blockDim.x, 0, s, image, sh);
+}
+
+// Batches up to this many tokens are routed by counting (one CTA per token).
+constexpr int kCountingRouteTokens = 2048;
+
+static int check_route_shape(const RouteParams& p) {
   if (p.n_routed < 1 || p.n_routed > 1024 || p.topk < 1 || p.topk + p.n_shared > 32 || p.topk > p.n_routed)
     return AKLR_ERR_UNSUPPORTED_SHAPE;
   if (p.num_expert_group > 1) {
@@ -187,6 +334,17 @@ int launch_route(const RouteParams& p, cudaStream_t stream) {
         p.n_routed / p.num_expert_group < 2 || p.topk_group > p.num_expert_group || p.topk_group < 1 ||
         p.topk > p.topk_group * (p.n_routed / p.num_expert_group))
       return AKLR_ERR_UNSUPPORTED_SHAPE;
+  }
+  return AKLR_OK;
+}
+
+int launch_route(const RouteParams& p, cudaStream_t stream) {
+  if (p.n_tokens == 0) return AKLR_OK;
+  if (int rc = check_route_shape(p)) return rc;
+  if (p.n_tokens <= kCountingRouteTokens) {
+    const int per_token = p.n_routed < 32 ? 32 : (p.n_routed + 31) & ~31;
+    return launch_kernel(route_count_kernel, dim3(p.n_tokens), dim3(per_token), 0, stream, 1, p) == cudaSuccess
+               ? AKLR_OK : AKLR_ERR_CUDA;
   }
   const int threads = 256, warps = threads / 32;
   const int blocks = (p.n_tokens + warps - 1) / warps;
@@ -373,10 +531,7 @@ __global__ void __launch_bounds__(kSortChunk) align_scatter_kernel(AlignParams p
 
 // All three passes in one CTA, for up to kSmallRoutes routes (decode batches).
 constexpr int kSmallRoutes = 4096;
-__global__ void __launch_bounds__(kSortChunk) align_small_kernel(AlignParams p) {
-  extern __shared__ int sm[];
-  griddep_launch();
-  griddep_wait();
+__device__ void align_small_body(const AlignParams& p, int* sm) {
   int* total = sm;
   int* base = sm + p.n_experts;
   int* scratch = base + p.n_experts;
@@ -388,10 +543,65 @@ __global__ void __launch_bounds__(kSortChunk) align_small_kernel(AlignParams p) 
   }
   __syncthreads();
   plan_blocks(p, total, base, scratch);
-  for (int start = 0; start < p.n_routes; start += kSortChunk) {
+  for (int start = 0; start < p.n_routes; start += blockDim.x) {  // a chunk is one route per thread
     place_chunk(p, start + threadIdx.x, base);
     __syncthreads();
   }
+}
+
+__global__ void __launch_bounds__(kSortChunk) align_small_kernel(AlignParams p) {
+  extern __shared__ int sm[];
+  griddep_launch();
+  griddep_wait();
+  align_small_body(p, sm);
+}
+
+// Routing and sort of a decode call in one CTA: route each token by counting, then sort the routes
+// (the sort reads the ids the same CTA just wrote, after a barrier).  At one to eight tokens the two
+// kernels this replaces spend their time on launch and drain, not on work.  The activation
+// quantisation stays a kernel of its own: it is memory latency over many rows and needs many SMs
+// (inside this CTA it took 50 us for one token, 300 us for eight).
+constexpr int kPrologueTeams = kSortChunk / kDecodePrologueExperts;  // tokens routed side by side
+__global__ void __launch_bounds__(kSortChunk) decode_prologue_kernel(RouteParams rp, AlignParams ap) {
+  extern __shared__ int sm[];
+  using TeamShared = RouteSharedT<kDecodePrologueExperts, kDecodePrologueExperts>;
+  __shared__ TeamShared sh[kPrologueTeams];
+  griddep_launch();
+  griddep_wait();
+  // Teams of 256 threads route tokens team, team + 4, ... side by side, each on its own named
+  // barrier.  A team's loads for both of its tokens are issued before it counts (one memory round
+  // trip), and the counting is a rolled loop: a decode call streams hundreds of MB through L2 between
+  // two runs of this kernel, so its instructions come from DRAM every time and unrolled copies cost
+  // more in instruction fetch than they save.
+  const int team = threadIdx.x / kDecodePrologueExperts, e = threadIdx.x % kDecodePrologueExperts;
+  constexpr int kRounds = kDecodePrologueTokens / kPrologueTeams;
+  float s[kRounds];
+  uint32_t image[kRounds];
+#pragma unroll
+  for (int r = 0; r < kRounds; ++r) {
+    const int token = team + r * kPrologueTeams;
+    if (token < rp.n_tokens) route_load(rp, token, e, s[r], image[r]);
+  }
+#pragma unroll
+  for (int r = 0; r < kRounds; ++r) {
+    const int token = team + r * kPrologueTeams;  // uniform over the team
+    if (token < rp.n_tokens)
+      route_by_counting(rp, token, e, kDecodePrologueExperts, 1 + team, s[r], image[r], sh[team]);
+  }
+  __syncthreads();  // every token's ids are written
+  align_small_body(ap, sm);
+}
+
+int launch_decode_prologue(const RouteParams& rp, const AlignParams& ap, cudaStream_t stream) {
+  if (rp.n_tokens < 1 || rp.n_tokens > kDecodePrologueTokens || rp.n_routed > kDecodePrologueExperts || ap.n_routes > kSmallRoutes)
+    return AKLR_ERR_UNSUPPORTED_SHAPE;
+  if (ap.n_experts < 1 || ap.n_experts > 2048 || ap.block_m < 1) return AKLR_ERR_UNSUPPORTED_SHAPE;
+  if (int rc = check_route_shape(rp)) return rc;
+  const int groups = rp.num_expert_group > 1 && rp.topk_group < rp.num_expert_group ? rp.num_expert_group : 1;
+  if (groups * rp.topk > kDecodePrologueExperts) return AKLR_ERR_UNSUPPORTED_SHAPE;  // the teams' candidate tables
+  const size_t smem = (2 * static_cast<size_t>(ap.n_experts) + 1024) * sizeof(int);
+  return launch_kernel(decode_prologue_kernel, dim3(1), dim3(kSortChunk), smem, stream, 1, rp, ap) == cudaSuccess
+             ? AKLR_OK : AKLR_ERR_CUDA;
 }
 
 int launch_align(const AlignParams& p, cudaStream_t stream) {

@@ -248,6 +248,7 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--sweep", action="store_true", help="also time decode/prefill token counts (extra keys)")
+    ap.add_argument("--sweep-tokens", default="1,16,64,256,1024,16384", help="token counts of --sweep, comma-separated")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling captures)")
     ap.add_argument("--routed-experts", type=int, default=0, help="shrink the layer to this many routed experts (profiling captures only)")
     ap.add_argument("--block-m", type=int, default=0, help="force the tokens-per-block of the grouped GEMMs")
@@ -482,7 +483,7 @@ def main() -> None:
     sweep = None
     if args.sweep:
         sweep = []
-        for t_sweep in (1, 16, 64, 256, 1024, 16384):
+        for t_sweep in (int(v) for v in args.sweep_tokens.split(",")):
             bs = [wl.router_inputs(cfg, t_sweep, SEED + 50 + b, device)[:2] for b in range(8)]
             o = torch.empty((t_sweep, cfg.hidden), dtype=torch.bfloat16, device=device)
             wsx = Workspace(_config(t_sweep, cfg.hidden, cfg.inter, cfg.n_routed, routing, bs[0][1], bias), device)

@@ -264,6 +264,9 @@ int aklr_debug_force_weight_major(int32_t on);
 /* Token-major kernels as CTA pairs (cta_group::2: two token blocks of an expert per pair, each CTA
  * loading half of the weight tile): mode 1 = whenever block_m is 128; 0 or negative = off (default). */
 int aklr_debug_force_cta_pairs(int32_t mode);
+/* aklr_moe_fp8_forward on 1..8 tokens runs routing and sort as one kernel;
+ * 0 makes it launch the separate kernels instead (tests compare the two), non-zero restores the default. */
+int aklr_debug_fused_prologue(int32_t on);
 int aklr_profile_begin(int32_t max_calls);
 int aklr_profile_read(int32_t call, float* stage_ms);
 

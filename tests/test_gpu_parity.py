@@ -454,6 +454,45 @@ def test_cta_pair_kernels_match_the_single_cta_kernels(golden):
     assert torch.equal(outs[0], outs[1])
 
 
+@pytest.mark.parametrize("name", ["deepseek_small", "qwen3"])
+@pytest.mark.parametrize("n_tokens", [1, 3, 8])
+def test_decode_prologue_kernel_matches_the_separate_kernels(name, n_tokens):
+    """One to eight tokens: routing and sort run as one kernel.  Everything it leaves in the workspace,
+    and the layer output, equals bit for bit what the two kernels leave."""
+    from aklr_b200 import _lib
+    from aklr_b200.moe import fused_moe_fp8
+
+    lib = _lib.load()
+    cfg = wl.CONFIGS[name]
+    d = dev()
+    w1, s1, w2, s2 = (x.to(d) for x in wl.expert_weights(cfg, seed=21))
+    hidden, logits, bias = wl.router_inputs(cfg, n_tokens, seed=300 + n_tokens)
+    bias_d = bias.to(d) if bias is not None and cfg.scoring == "sigmoid" else None
+    got = []
+    for fused in (1, 0):
+        lib.aklr_debug_fused_prologue(fused)
+        try:
+            launches = lib.aklr_kernel_launch_count()
+            out, ws = fused_moe_fp8(hidden.to(d), logits.to(d), bias_d, w1, s1, w2, s2, routing_of(cfg), return_workspace=True)
+            ws.check_status()
+            rows = ws.num_blocks() * ws.layout.block_m
+            xq, xs = ws.xq()
+            live = ws.sorted_ids()[:rows].cpu() >= 0
+            got.append(dict(out=out.cpu(), ids=ws.topk_ids().cpu(), weights=ws.topk_weights().cpu(), counts=ws.counts().cpu(),
+                            sorted=ws.sorted_ids()[:rows].cpu(), block_expert=ws.block_expert().cpu(),
+                            xq=xq[:rows].cpu().view(torch.uint8)[live], xs=xs[:rows].cpu()[live],
+                            launches=lib.aklr_kernel_launch_count() - launches))
+        finally:
+            lib.aklr_debug_fused_prologue(1)
+    one, three = got
+    assert one["launches"] == three["launches"] - 1
+    for key in ("ids", "weights", "counts", "sorted", "block_expert", "xq", "xs", "out"):
+        assert torch.equal(one[key], three[key]), key
+    ref_ids = orc.grouped_sigmoid_topk(logits.float(), bias.float(), cfg.topk, cfg.num_expert_group, cfg.topk_group, True, cfg.routed_scaling_factor)[0] \
+        if cfg.scoring == "sigmoid" else orc.softmax_topk(logits.float(), cfg.topk)[0]
+    assert torch.equal(one["ids"][:, : cfg.topk].long(), ref_ids)
+
+
 def test_layer_call_is_cuda_graph_capturable():
     """No allocation, synchronisation or host read inside the call: it can be captured once a shape
     has run eagerly, and a replay on new input values gives what the eager call gives."""
