@@ -454,7 +454,7 @@ def test_cta_pair_kernels_match_the_single_cta_kernels(golden):
     assert torch.equal(outs[0], outs[1])
 
 
-@pytest.mark.parametrize("name", ["deepseek_small", "qwen3"])
+@pytest.mark.parametrize("name", ["deepseek_small", "qwen3", "eight_experts"])
 @pytest.mark.parametrize("n_tokens", [1, 3, 8])
 def test_decode_prologue_kernel_matches_the_separate_kernels(name, n_tokens):
     """One to eight tokens: routing and sort run as one kernel.  Everything it leaves in the workspace,
@@ -463,7 +463,8 @@ def test_decode_prologue_kernel_matches_the_separate_kernels(name, n_tokens):
     from aklr_b200.moe import fused_moe_fp8
 
     lib = _lib.load()
-    cfg = wl.CONFIGS[name]
+    # eight experts, top-2 softmax: Mixtral's routing shape, a team of 256 threads with 8 at work
+    cfg = wl.CONFIGS.get(name) or wl.MoEConfig(name, hidden=256, inter=128, n_routed=8, topk=2)
     d = dev()
     w1, s1, w2, s2 = (x.to(d) for x in wl.expert_weights(cfg, seed=21))
     hidden, logits, bias = wl.router_inputs(cfg, n_tokens, seed=300 + n_tokens)
