@@ -250,6 +250,8 @@ def main() -> None:
     ap.add_argument("--sweep", action="store_true", help="also time decode/prefill token counts (extra keys)")
     ap.add_argument("--sweep-tokens", default="1,16,64,256,1024,16384", help="token counts of --sweep, comma-separated")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling captures)")
+    ap.add_argument("--model", default="deepseek_v3", choices=["deepseek_v3", "mixtral", "qwen3"],
+                    help="mixtral / qwen3: the other FP8 configurations, one GPU, timed as CUDA-graph replays over their token counts")
     ap.add_argument("--routed-experts", type=int, default=0, help="shrink the layer to this many routed experts (profiling captures only)")
     ap.add_argument("--block-m", type=int, default=0, help="force the tokens-per-block of the grouped GEMMs")
     ap.add_argument("--format", default="fp8", choices=["fp8", "mxfp4"], help="expert weight format (mxfp4: MXFP8 activations)")
@@ -306,6 +308,9 @@ def main() -> None:
     T = args.tokens
     if args.format == "mxfp4":
         bench_mxfp4(args, cfg, routing, device, lib)
+        return
+    if args.model != "deepseek_v3":
+        bench_other_model(args, wl.CONFIGS[args.model], device, lib)
         return
     w1, s1, w2, s2 = wl.expert_weights(cfg, SEED, device)
     router_w = wl.router_weight(cfg, SEED, device)
@@ -623,6 +628,70 @@ def bench_mxfp4(args, cfg, routing, device, lib):
                      "gate_up_tflops": 2 * flops / 3 / (stage_ms[3] * 1e-3) / 1e12 if stage_ms[3] > 0 else None,
                      "down_tflops": flops / 3 / (stage_ms[4] * 1e-3) / 1e12 if stage_ms[4] > 0 else None},
         "cpu_baseline": None,
+    }), flush=True)
+
+
+# token counts the other FP8 configurations are quoted on
+OTHER_MODEL_TOKENS = {"mixtral": (1, 16, 64, 256, 1024, 4096), "qwen3": (1, 32, 256, 2048, 8192)}
+
+
+def bench_other_model(args, cfg, device, lib):
+    """Mixtral-8x7B or Qwen3-30B-A3B widths with softmax top-k routing (seeded logits; Qwen3's carry a
+    Zipf(1.1) popularity bias), one GPU: every token count as a CUDA graph of 8 layer calls on rotating
+    batches, replayed.  One JSON line; ``value`` is the largest token count's throughput."""
+    from aklr_b200.moe import Workspace, _config, fused_moe_fp8
+
+    routing = routing_of(cfg)
+    w1, s1, w2, s2 = wl.expert_weights(cfg, SEED, device)
+    peak, kind = measured_peak_hbm()
+    sampler = ClockSampler(device.index or 0)
+    launches0 = lib.aklr_kernel_launch_count()
+    sweep = []
+    sampler.begin()
+    for tokens in OTHER_MODEL_TOKENS[args.model]:
+        batches = [wl.router_inputs(cfg, tokens, SEED + 50 + b, device)[:2] for b in range(8)]
+        out = torch.empty((tokens, cfg.hidden), dtype=torch.bfloat16, device=device)
+        ws = Workspace(_config(tokens, cfg.hidden, cfg.inter, cfg.n_routed, routing, batches[0][1], None), device)
+        for hidden, logits in batches:  # every batch once outside a capture
+            fused_moe_fp8(hidden, logits, None, w1, s1, w2, s2, routing, out=out, workspace=ws)
+        ws.check_status()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for hidden, logits in batches:
+                fused_moe_fp8(hidden, logits, None, w1, s1, w2, s2, routing, out=out, workspace=ws)
+        for _ in range(max(args.warmup, 3)):
+            graph.replay()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(args.steps):
+            graph.replay()
+        stop.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(stop) / (args.steps * 8)
+        hit = sum(distinct_experts(orc_free_ids(cfg, logits, None)) for _, logits in batches) / 8
+        flops, nbytes = wl.roofline_work(cfg, tokens, hit)
+        t_hbm, t_tensor = nbytes / (peak * 1e9), flops / 3.2e15
+        sweep.append({
+            "tokens": tokens, "us_per_call": ms * 1e3, "tokens_per_s": tokens / (ms * 1e-3), "experts_hit": hit,
+            "frac_of_hbm_roofline": t_hbm / (ms * 1e-3), "tflops": flops / (ms * 1e-3) / 1e12,
+            "bound": "hbm" if t_hbm > t_tensor else "tensor", "block_m": ws.layout.block_m,
+        })
+    clocks = sampler.stop()
+    last = sweep[-1]
+    config = workload_config(cfg, args)
+    config["workload"] = f"{cfg.name} fp8 fused-moe layer, token counts {[s['tokens'] for s in sweep]}"
+    config["routing"] = f"softmax over the top-{cfg.topk} logits" + (", " + wl.zipf_note() if cfg.zipf_s > 0 else "")
+    config["timing"] = "cuda graph replay of 8 calls on rotating batches; weights stream from HBM every call"
+    print(json.dumps({
+        "metric": METRIC, "value": last["tokens_per_s"], "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": last["us_per_call"] * 1e-3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp8_e4m3", "data": "synthetic", "config": config, "clocks": clocks, "e2e": None,
+        "gpu_launches": int(lib.aklr_kernel_launch_count() - launches0),
+        "roofline": {"bound": last["bound"], "achieved": last["frac_of_hbm_roofline"] * peak, "peak": peak, "peak_kind": f"of {kind}",
+                     "unit": "GB/s", "frac": last["frac_of_hbm_roofline"], "traffic": None,
+                     "note": "whole layer at the largest token count: algorithmic bytes / layer time"},
+        "cpu_baseline": None, "sweep": sweep,
     }), flush=True)
 
 
