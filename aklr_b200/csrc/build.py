@@ -10,7 +10,7 @@ import sys
 HERE = pathlib.Path(__file__).resolve().parent
 LIB = HERE.parent / "libaklr_b200.so"
 SOURCES = ["abi.cu", "routing.cu", "quant.cu", "grouped_gemm.cu", "grouped_gemm_prefill.cu", "grouped_gemm_mx.cu", "combine.cu", "router_gemm.cu", "ep.cu", "no_alloc.cu"]
-HEADERS = ["common.cuh", "kernels.h", "../../include/aklr_b200.h"]
+HEADERS = ["common.cuh", "kernels.h", "quant_rows.cuh", "../../include/aklr_b200.h"]
 
 
 def nvcc_path() -> str:

@@ -251,6 +251,14 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
     int ring = 0;  // the stage whose "empty" barrier reports MMA(it) complete, and its parity
     uint32_t ring_ph = 0;
     bool bad = false;
+    constexpr int kPreBatch = 4;
+    constexpr bool kPrefetch = BM <= 32;  // the decode blocks; larger ones have no registers to spare
+    float pre_s[kPreBatch], pre_w0[kPreBatch], pre_w1[kPreBatch], pre_weight = 0.0f;
+    int pre_rid = -1;
+    bool have_pre = false;
+    // experts of this CTA's current and next tile, read a tile ahead of the addresses that need them
+    int e_cur = blockIdx.x < total_tiles ? p.block_expert[blockIdx.x / tiles_per_block] : 0;
+    int e_ahead = blockIdx.x + gridDim.x < total_tiles ? p.block_expert[(blockIdx.x + gridDim.x) / tiles_per_block] : 0;
 #ifdef AKLR_GEMM_TIMING
     long long tacc[16] = {0};
     long long t_mark = clock64();
@@ -262,26 +270,33 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
 #endif
       if (epi_bar_any(*abort_flag)) break;   // also fences the aliased smem against the last tile
       const int b = t / tiles_per_block, j = t - b * tiles_per_block;
-      const int e = p.block_expert[b];
+      const int e = e_cur;
       // Combined scale table of the tile, ftab[tile][kb][n] = activation scale x weight block
       // scale, so the K loop is one shared-memory float4 per four columns and one FMA per element.
+      // The first batch of its inputs, the tile's route ids and (down) route weights were loaded
+      // during the previous tile of this CTA (``pre_*``): a tile of a short reduction (6..16 K-blocks)
+      // would otherwise spend a third of its time waiting for these dependent global loads.
       {
         const float* ws0 = p.w_scale + (static_cast<size_t>(e) * (p.rows_per_expert >> 7) + j) * KB;
         const float* xs = p.x_scale + static_cast<size_t>(b) * KB * BM;  // [kb][n] of this block
-        constexpr int kBatch = 4;  // loads of a batch are issued together: one L2 round trip, not four
-        for (int base = et; base < BM * KB; base += kEpiThreads * kBatch) {
-          float s[kBatch], w0[kBatch], w1[kBatch];
+        for (int base = et; base < BM * KB; base += kEpiThreads * kPreBatch) {
+          float s[kPreBatch], w0[kPreBatch], w1[kPreBatch];
+          const bool from_pre = have_pre && base == et;
 #pragma unroll
-          for (int u = 0; u < kBatch; ++u) {
-            const int i = base + u * kEpiThreads;
-            const bool in = i < BM * KB;
-            const int kb = in ? i / BM : 0;
-            s[u] = in ? __ldg(xs + i) : 0.0f;
-            w0[u] = __ldg(ws0 + kb);
-            w1[u] = GATE_UP ? __ldg(ws0 + static_cast<size_t>(IB) * KB + kb) : 0.0f;
+          for (int u = 0; u < kPreBatch; ++u) {  // loads of a batch are issued together: one L2 round trip
+            if (from_pre) {
+              s[u] = pre_s[u], w0[u] = pre_w0[u], w1[u] = pre_w1[u];
+            } else {
+              const int i = base + u * kEpiThreads;
+              const bool in = i < BM * KB;
+              const int kb = in ? i / BM : 0;
+              s[u] = in ? __ldg(xs + i) : 0.0f;
+              w0[u] = __ldg(ws0 + kb);
+              w1[u] = GATE_UP ? __ldg(ws0 + static_cast<size_t>(IB) * KB + kb) : 0.0f;
+            }
           }
 #pragma unroll
-          for (int u = 0; u < kBatch; ++u) {
+          for (int u = 0; u < kPreBatch; ++u) {
             const int i = base + u * kEpiThreads;
             if (i < BM * KB) {
               ftab[i] = s[u] * w0[u];
@@ -291,11 +306,34 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
         }
       }
       if (et < BM) {
-        const int rid = p.sorted_ids[b * BM + et];
+        const int rid = have_pre ? pre_rid : p.sorted_ids[b * BM + et];
         rid_s[et] = rid;
-        if (!GATE_UP) colscale[et] = rid >= 0 ? p.topk_weights[rid] : 0.0f;
+        if (!GATE_UP) colscale[et] = have_pre ? pre_weight : (rid >= 0 ? p.topk_weights[rid] : 0.0f);
       }
       epi_bar_sync();
+      {  // issue the next tile's loads; they land while this tile's K loop runs
+        const int tn = t + gridDim.x;
+        have_pre = kPrefetch && tn < total_tiles;
+        if (have_pre) {
+          const int bn = tn / tiles_per_block, jn = tn - bn * tiles_per_block;
+          const int en = e_ahead;
+          const float* ws0 = p.w_scale + (static_cast<size_t>(en) * (p.rows_per_expert >> 7) + jn) * KB;
+          const float* xs = p.x_scale + static_cast<size_t>(bn) * KB * BM;
+#pragma unroll
+          for (int u = 0; u < kPreBatch; ++u) {
+            const int i = et + u * kEpiThreads;
+            const bool in = i < BM * KB;
+            const int kb = in ? i / BM : 0;
+            pre_s[u] = in ? __ldg(xs + i) : 0.0f;
+            pre_w0[u] = __ldg(ws0 + kb);
+            pre_w1[u] = GATE_UP ? __ldg(ws0 + static_cast<size_t>(IB) * KB + kb) : 0.0f;
+          }
+          pre_rid = et < BM ? p.sorted_ids[bn * BM + et] : -1;
+        }
+        e_cur = e_ahead;
+        const int t2 = tn + gridDim.x;
+        e_ahead = t2 < total_tiles ? p.block_expert[t2 / tiles_per_block] : 0;
+      }
 
 #ifdef AKLR_GEMM_TIMING
       tacc[6] += clock64() - t_mark;
@@ -351,6 +389,8 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
       t_mark = clock64();
 #endif
 
+      // the next tile's route weights: their ids have arrived by now, and the epilogue below hides this load
+      if (!GATE_UP && have_pre && et < BM) pre_weight = pre_rid >= 0 ? p.topk_weights[pre_rid] : 0.0f;
       epi_bar_sync();  // every warp is done with the scale table: the region becomes the out tile
       if (GATE_UP) {
         // h = silu(gate) * up, rounded to bf16; then 1 x 128 requant over this tile's 128 channels
