@@ -99,6 +99,7 @@ SIGNATURES = {
     "aklr_debug_force_weight_major": (c_int32, [c_int32]),
     "aklr_debug_force_cta_pairs": (c_int32, [c_int32]),
     "aklr_debug_fused_prologue": (c_int32, [c_int32]),
+    "aklr_debug_small_activation_boxes": (c_int32, [c_int32]),
     "aklr_profile_begin": (c_int32, [c_int32]),
     "aklr_profile_read": (c_int32, [c_int32, POINTER(c_float)]),
 }

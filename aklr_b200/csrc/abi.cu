@@ -33,6 +33,9 @@ std::atomic<bool> g_force_swap_ab{false};
 // single-CTA kernel at 8+ blocks per expert and slower where experts have one or two blocks (an
 // odd last block wastes half a pair).
 std::atomic<int> g_force_pairs{-1};
+// MXFP4 path: blocks with at most 32 / 64 routed rows load only those activation rows
+// (aklr_debug_small_activation_boxes(0) loads all 128 always; tests compare).
+std::atomic<int> g_small_boxes{1};
 
 bool use_cta_pairs(const aklr_moe_config&) { return g_force_pairs.load() > 0; }
 
@@ -470,6 +473,11 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   if (rc) return rc;
   rc = make_map_u8(&g1.map_x, ws + l.xq, l.capacity, c.hidden, 128);
   if (rc) return rc;
+  rc = make_map_u8(&g1.map_x_rows32, ws + l.xq, l.capacity, c.hidden, 32);
+  if (rc) return rc;
+  rc = make_map_u8(&g1.map_x_rows64, ws + l.xq, l.capacity, c.hidden, 64);
+  if (rc) return rc;
+  g1.small_boxes = g_small_boxes.load();
   g1.w_scale = w1_scale;
   g1.x_scale = ws + l.xs;
   g1.sorted_ids = sorted_ids;
@@ -498,6 +506,11 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   if (rc) return rc;
   rc = make_map_u8(&g2.map_x, ws + l.hq, l.capacity, c.inter, 128);
   if (rc) return rc;
+  rc = make_map_u8(&g2.map_x_rows32, ws + l.hq, l.capacity, c.inter, 32);
+  if (rc) return rc;
+  rc = make_map_u8(&g2.map_x_rows64, ws + l.hq, l.capacity, c.inter, 64);
+  if (rc) return rc;
+  g2.small_boxes = g_small_boxes.load();
   g2.w_scale = w2_scale;
   g2.x_scale = ws + l.hs;
   g2.sorted_ids = sorted_ids;
@@ -996,6 +1009,11 @@ int aklr_debug_force_cta_pairs(int32_t mode) {
 
 int aklr_debug_fused_prologue(int32_t on) {
   g_fused_prologue = on != 0;
+  return AKLR_OK;
+}
+
+int aklr_debug_small_activation_boxes(int32_t on) {
+  g_small_boxes = on != 0;
   return AKLR_OK;
 }
 

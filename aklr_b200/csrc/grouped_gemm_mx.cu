@@ -128,19 +128,20 @@ __device__ __forceinline__ int mxfp8_exponent(float amax) {
   return e < -126 ? -126 : (e > 127 ? 127 : e);
 }
 
-// act(gate) * up for the activations of the reference's experts-only op
-// (aklr/ops/fused_moe/reference.py:113-121).  The branch is uniform over the grid.
-__device__ __forceinline__ float gated_product(int activation, float gate, float up, float beta, float linear_beta) {
+// act(gate) * up for the activations of the reference's experts-only op other than SiLU
+// (aklr/ops/fused_moe/reference.py:113-121).  Deliberately NOT inlined: the epilogue calls it from a
+// loop unrolled 64 times, and with erff and tanhf expanded in every copy the loop grew to hundreds of
+// KB of straight-line code that missed the instruction cache once per element (gate_up epilogue
+// 6 k -> 77 k cycles per tile, the whole kernel 1.7x slower, SiLU included).
+__device__ __noinline__ float gated_product_other(int activation, float gate, float up, float beta, float linear_beta) {
   switch (activation) {
     case AKLR_ACT_GELU:  // exact (erf) GELU
       return 0.5f * gate * (1.0f + erff(gate * 0.70710678118654752f)) * up;
     case AKLR_ACT_SWIGLU_OAI:  // gpt-oss: alpha 1.702, up biased by 1
       return __fdividef(gate, 1.0f + __expf(-1.702f * gate)) * (up + 1.0f);
-    case AKLR_ACT_SITUV2:
+    default:  // AKLR_ACT_SITUV2
       return beta * tanhf(__fdividef(gate, beta)) * __fdividef(1.0f, 1.0f + __expf(-gate)) *
              (linear_beta * tanhf(__fdividef(up, linear_beta)));
-    default:
-      return __fdividef(gate, 1.0f + __expf(-gate)) * up;
   }
 }
 
@@ -205,13 +206,25 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
         const int b = t / tiles_per_block, j = t - b * tiles_per_block;
         const int e = p.block_expert[b];
         const int w_row = e * p.rows_per_expert + (GATE_UP ? j * 128 : j * 256);
+        // A decode batch leaves most of a 128-row block as padding (the sort puts the routed rows
+        // first, -1 after them).  Loading all 128 activation rows per K-block made shared-memory
+        // fill traffic from L2, not HBM, the bound (32 KB per K-block against 16 KB of weights): a
+        // block with at most 32 or 64 routed rows loads only those.  The rows left stale feed TMEM
+        // lanes whose results are never stored.
+        const CUtensorMap* map_x = &p.map_x;
+        uint32_t x_bytes = kABytes;
+        if (p.small_boxes) {
+          const int id32 = p.sorted_ids[b * kBM + 32], id64 = p.sorted_ids[b * kBM + 64];
+          if (id32 < 0) { map_x = &p.map_x_rows32; x_bytes = 32 * 128; }
+          else if (id64 < 0) { map_x = &p.map_x_rows64; x_bytes = 64 * 128; }
+        }
         for (int kb = 0; kb < KB; ++kb) {
           if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 21)) { ok = false; break; }
           uint8_t* st = smem + s * kStageBytes;
           // the transaction count of the unpacking fp4 load is its packed size (what crosses from
           // global memory), not the padded bytes it writes: expecting the padded size never completes
-          mbar_expect_tx(&full[s], kABytes + kBBytes / 2);
-          tma_load_2d(st, &p.map_x, &full[s], kb * 128, b * kBM);
+          mbar_expect_tx(&full[s], x_bytes + kBBytes / 2);
+          tma_load_2d(st, map_x, &full[s], kb * 128, b * kBM);
           if (GATE_UP) {
             tma_load_2d(st + kABytes, &p.map_w, &full[s], kb * 128, w_row);
             tma_load_2d(st + kABytes + kBBytes / 2, &p.map_w, &full[s], kb * 128, w_row + p.out_dim);
@@ -484,11 +497,16 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty);
+#ifdef AKLR_GEMM_TIMING
+      const long long t_loaded = clock64();
+      tacc[10] += t_loaded - t_epi;
+#endif
 
       const int rid = rid_s[row];
       if (GATE_UP) {
         const int IB = p.out_dim >> 7;
         const float w1row = p.stage1_weights ? wgt_s[row] : 1.0f;  // exact when the weight is not applied here
+        const bool silu = p.activation == AKLR_ACT_SILU;  // uniform over the grid
         // two 1 x 32 groups of this thread's 64 h channels
         uint32_t packed[16];
         uint32_t scale_bytes = 0;
@@ -502,7 +520,8 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
               gate = fminf(gate, p.swiglu_limit);
               up = fminf(fmaxf(up, -p.swiglu_limit), p.swiglu_limit);
             }
-            const float h = gated_product(p.activation, gate, up, p.beta, p.linear_beta);
+            const float h = silu ? __fdividef(gate, 1.0f + __expf(-gate)) * up
+                                 : gated_product_other(p.activation, gate, up, p.beta, p.linear_beta);
             acc[g * 32 + i] = __bfloat162float(__float2bfloat16_rn(h));
             m = fmaxf(m, fabsf(acc[g * 32 + i]));
           }
@@ -514,6 +533,9 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
             packed[g * 8 + i / 4] = cvt_e4m3x2(acc[g * 32 + i] * inv, acc[g * 32 + i + 1] * inv) |
                                     (static_cast<uint32_t>(cvt_e4m3x2(acc[g * 32 + i + 2] * inv, acc[g * 32 + i + 3] * inv)) << 16);
         }
+#ifdef AKLR_GEMM_TIMING
+        tacc[11] += clock64() - t_loaded;
+#endif
         if (rid >= 0 && !bad) {
           uint8_t* dst = p.out_q + static_cast<size_t>(b * kBM + row) * p.out_dim + j * 128 + half * 64;
 #pragma unroll
@@ -566,6 +588,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
 #ifdef AKLR_GEMM_TIMING
     if (blockIdx.x == 0 && warp == 2 && lane == 0)
       for (int i = 6; i <= 7; ++i) g_mx_timing[GATE_UP][i] = tacc[i];
+      for (int i = 10; i <= 11; ++i) g_mx_timing[GATE_UP][i] = tacc[i];
 #endif
   }
 

@@ -127,6 +127,9 @@ int launch_gather_quant_mxfp8(const MxQuantParams& p, cudaStream_t stream);
 struct MxGemmParams {
   CUtensorMap map_w;           // packed e2m1 weights [experts*rows_per_expert, k], 16U4_ALIGN16B, box 128 x 128|256
   CUtensorMap map_x;           // e4m3 activations [capacity, k], box 128 x 128
+  CUtensorMap map_x_rows32;    // the same matrix with boxes of 32 and 64 rows: a block with that few routed
+  CUtensorMap map_x_rows64;    // rows loads only those (the tile's other rows are never read back)
+  int small_boxes;             // non-zero: the two maps above are set
   const uint8_t* w_scale;      // e8m0 [experts, rows_per_expert, k/32]
   const uint8_t* x_scale;      // e8m0 [max_blocks, k/128, 512]
   const int32_t* sorted_ids;

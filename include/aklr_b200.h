@@ -267,6 +267,9 @@ int aklr_debug_force_cta_pairs(int32_t mode);
 /* aklr_moe_fp8_forward on 1..8 tokens runs routing and sort as one kernel;
  * 0 makes it launch the separate kernels instead (tests compare the two), non-zero restores the default. */
 int aklr_debug_fused_prologue(int32_t on);
+/* The MXFP4 grouped GEMMs load only the first 32 or 64 activation rows of a 128-row block that has no more
+ * routed rows than that; 0 makes them load all 128 always (tests compare), non-zero restores the default. */
+int aklr_debug_small_activation_boxes(int32_t on);
 int aklr_profile_begin(int32_t max_calls);
 int aklr_profile_read(int32_t call, float* stage_ms);
 

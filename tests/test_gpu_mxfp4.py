@@ -44,6 +44,28 @@ def test_mxfp4_experts_match_the_oracle(shape, limit):
     assert orc.gates_pass(gates, min_sqnr_db=30.0), gates
 
 
+@pytest.mark.parametrize("shape", [(256, 128, 6, 2, 40), (512, 256, 8, 4, 150), (1024, 384, 4, 2, 300)])
+def test_blocks_with_few_rows_load_only_those_rows(shape):
+    """A 128-row block with at most 32 or 64 routed rows loads only those activation rows (13, 75 and
+    128 + 22 rows per expert here): bit for bit the output of loading all 128."""
+    from aklr_b200 import _lib
+    from aklr_b200.moe import fused_experts_mxfp4
+
+    lib = _lib.load()
+    hidden, inter, experts, topk, tokens = shape
+    args = [t.to(dev()) for t in case(hidden, inter, experts, topk, tokens, seed=7 + tokens)]
+    outs = []
+    for small in (1, 0):
+        lib.aklr_debug_small_activation_boxes(small)
+        try:
+            out, ws = fused_experts_mxfp4(*args, return_workspace=True)
+            ws.check_status()
+            outs.append(out.cpu())
+        finally:
+            lib.aklr_debug_small_activation_boxes(1)
+    assert torch.equal(outs[0], outs[1])
+
+
 def test_first_mxfp8_quantisation_is_bit_exact():
     from aklr_b200.moe import fused_experts_mxfp4
 
