@@ -115,6 +115,36 @@ def test_routing_matches_oracle_on_ragged_batches(name, n_tokens):
     assert_routing(ids, w, ref_ids, ref_w)
 
 
+@pytest.mark.parametrize("n_tokens", [5, 2100])  # routed by counting (one CTA per token) / by warp reductions
+@pytest.mark.parametrize(
+    "shape",
+    [
+        dict(n_routed=40, topk=3),                                             # not a multiple of 32
+        dict(n_routed=8, topk=8),                                              # every expert picked
+        dict(n_routed=1024, topk=31, n_shared=1),                              # the widest table
+        dict(n_routed=72, topk=5, n_shared=2, scoring="sigmoid", num_expert_group=4, topk_group=2,
+             renormalize=True, routed_scaling_factor=1.5),                    # groups of 18, two shared slots
+        dict(n_routed=96, topk=6, scoring="sigmoid", num_expert_group=3, topk_group=3, renormalize=False),  # all groups kept
+    ],
+)
+def test_routing_on_odd_shapes(shape, n_tokens):
+    from aklr_b200.moe import route
+
+    cfg = wl.MoEConfig("odd", hidden=128, inter=128, **shape)
+    _, logits, bias = wl.router_inputs(cfg, n_tokens, seed=17 + n_tokens)
+    if cfg.scoring == "sigmoid":
+        ref_ids, ref_w = orc.grouped_sigmoid_topk(
+            logits.float(), bias.float(), cfg.topk, cfg.num_expert_group, cfg.topk_group, cfg.renormalize, cfg.routed_scaling_factor
+        )
+    else:
+        ref_ids, ref_w = orc.softmax_topk(logits.float(), cfg.topk)
+    for k in range(cfg.n_shared):  # shared experts follow the routed ones at weight 1
+        ref_ids = torch.cat([ref_ids, torch.full_like(ref_ids[:, :1], cfg.n_routed + k)], dim=-1)
+        ref_w = torch.cat([ref_w, torch.ones_like(ref_w[:, :1])], dim=-1)
+    ids, w = route(logits.to(dev()), None if bias is None else bias.to(dev()), routing_of(cfg))
+    assert_routing(ids, w, ref_ids, ref_w)
+
+
 # ------------------------------------------------------------------------------------------------
 # sort
 # ------------------------------------------------------------------------------------------------
