@@ -1,11 +1,14 @@
 // Top-k routing and the moe_align token sort, sm_100a.
 //
-// Routing: one warp per token.  Each expert's ranking value becomes a 64-bit key
-// (order-preserving image of the float in the high word, ~expert in the low word), so a warp
-// arg-max of keys picks the largest value and, among equals, the lowest expert id -- the order
-// the reference's stable descending sort defines
+// Routing: each expert's ranking value becomes a 64-bit key (order-preserving image of the float in
+// the high word, ~expert in the low word), so "greater key" means the larger value and, among
+// equals, the lower expert id -- the order the reference's stable descending sort defines
 // (aklr/plugins/sglang/models/deepseek_v2/reference.py:114-143,
 //  aklr/plugins/sglang/models/qwen3_moe/reference.py:34-41, aklr/ops/topk/reference.py:17-35).
+// Two kernels pick by those keys and give bit-identical tables: large batches take one warp per
+// token (every pick a warp arg-max), batches up to 2048 tokens one CTA per token with one thread per
+// expert that COUNTS the keys greater than its own (no chain of dependent reductions: ~3 us
+// instead of ~15 us for a handful of tokens).  One to eight tokens run routing and sort as one CTA.
 //
 // Sort: a stable counting sort of routes (token*K + slot) by expert, each expert's run padded
 // with -1 to a multiple of block_m, plus a block -> expert table.  The reference defines no order
