@@ -651,14 +651,14 @@ def bench_other_model(args, cfg, device, lib):
     for tokens in OTHER_MODEL_TOKENS[args.model]:
         batches = [wl.router_inputs(cfg, tokens, SEED + 50 + b, device)[:2] for b in range(8)]
         out = torch.empty((tokens, cfg.hidden), dtype=torch.bfloat16, device=device)
-        ws = Workspace(_config(tokens, cfg.hidden, cfg.inter, cfg.n_routed, routing, batches[0][1], None), device)
+        ws = Workspace(_config(tokens, cfg.hidden, cfg.inter, cfg.n_routed, routing, batches[0][1], None, args.block_m), device)
         for hidden, logits in batches:  # every batch once outside a capture
-            fused_moe_fp8(hidden, logits, None, w1, s1, w2, s2, routing, out=out, workspace=ws)
+            fused_moe_fp8(hidden, logits, None, w1, s1, w2, s2, routing, out=out, workspace=ws, block_m=args.block_m)
         ws.check_status()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             for hidden, logits in batches:
-                fused_moe_fp8(hidden, logits, None, w1, s1, w2, s2, routing, out=out, workspace=ws)
+                fused_moe_fp8(hidden, logits, None, w1, s1, w2, s2, routing, out=out, workspace=ws, block_m=args.block_m)
         for _ in range(max(args.warmup, 3)):
             graph.replay()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
