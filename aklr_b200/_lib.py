@@ -14,6 +14,8 @@ LIB_PATH = pathlib.Path(__file__).resolve().parent / "libaklr_b200.so"
 
 SCORING = {"softmax": 0, "sigmoid": 1}
 DTYPE_BF16, DTYPE_F32 = 0, 1
+# aklr_moe_config.variant bits (AKLR_VARIANT_* of the header)
+VARIANT_WEIGHT_MAJOR, VARIANT_CTA_PAIRS, VARIANT_SEPARATE_PROLOGUE, VARIANT_FULL_ACTIVATION_BOXES = 1, 2, 4, 8
 
 
 class AklrError(RuntimeError):
@@ -41,6 +43,7 @@ class MoeConfig(ctypes.Structure):
         ("bias_dtype", c_int32),
         ("block_m", c_int32),
         ("n_experts_global", c_int32),
+        ("variant", c_int32),
     ]
 
 
@@ -96,10 +99,8 @@ SIGNATURES = {
     "aklr_moe_act_quant_fp8": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_void_p]),
     "aklr_moe_read_status": (c_int32, [c_void_p, POINTER(c_int32), c_void_p]),
     "aklr_kernel_launch_count": (c_int64, []),
-    "aklr_debug_force_weight_major": (c_int32, [c_int32]),
-    "aklr_debug_force_cta_pairs": (c_int32, [c_int32]),
-    "aklr_debug_fused_prologue": (c_int32, [c_int32]),
-    "aklr_debug_small_activation_boxes": (c_int32, [c_int32]),
+    "aklr_device_status": (c_int32, [POINTER(c_int32), c_int32]),
+    "aklr_selftest_wait_expiry": (c_int32, [c_int64, c_void_p, c_void_p]),
     "aklr_profile_begin": (c_int32, [c_int32]),
     "aklr_profile_read": (c_int32, [c_int32, POINTER(c_float)]),
 }

@@ -74,7 +74,9 @@ class OpContract:
     (wrong dtype/shape/layout/alignment/attr) -- the reference's generated fast_key
     (aklr/core/contract/fastkey/_fast_key_fn.py).  ``alloc(call, key)``: the outputs, the
     caller's buffers where ``call`` holds them.  ``run(call, outputs)``: launches on the current
-    stream; no sync, no host reads."""
+    stream; no sync, no host reads -- unless the contract says ``capturable=False`` (its ``run`` reads
+    something back on the host, e.g. the split sizes of an uneven all-to-all): such an op is never
+    served inside a CUDA-graph capture, where it returns ``OUT_OF_CONTRACT`` instead."""
 
     contract_id: str
     params: Sequence[Param]
@@ -85,6 +87,7 @@ class OpContract:
     description: str = ""
     ranks: str | None = None
     group_init: Callable[[], None] | None = None
+    capturable: bool = True
 
     @property
     def name(self) -> str:
@@ -206,6 +209,8 @@ class KernelDispatcher:
         """(key, outcome): outcome is a FallbackReason or None when the call is served."""
         if not self.is_open:
             return None, self.closed_reason
+        if not self.contract.capturable and _is_capturing():
+            return None, FallbackReason.OUT_OF_CONTRACT  # its run() reads from the host: not inside a capture
         key = self.contract.key(call)
         if key is None:
             return None, FallbackReason.OUT_OF_CONTRACT

@@ -5,6 +5,7 @@
 #include <cstdio>
 #include <cstring>
 #include <atomic>
+#include <mutex>
 #include <vector>
 
 #include "../../include/aklr_b200.h"
@@ -25,19 +26,14 @@ struct StageProfile {
 };
 StageProfile g_profile;
 std::atomic<long long> g_launches{0};
-// Tests set this to run full blocks through the weight-major kernel too (aklr_debug_force_weight_major).
-std::atomic<bool> g_force_swap_ab{false};
-// CTA-pair (cta_group::2) variant of the token-major kernels: 1 = whenever block_m is 128, else off
-// (aklr_debug_force_cta_pairs).  Off by default: it cuts a CTA's operand traffic by a third, but
-// the kernel is bound by the per-K-block fold in the epilogue, so it measured within 2% of the
-// single-CTA kernel at 8+ blocks per expert and slower where experts have one or two blocks (an
-// odd last block wastes half a pair).
-std::atomic<int> g_force_pairs{-1};
-// MXFP4 path: blocks with at most 32 / 64 routed rows load only those activation rows
-// (aklr_debug_small_activation_boxes(0) loads all 128 always; tests compare).
-std::atomic<int> g_small_boxes{1};
 
-bool use_cta_pairs(const aklr_moe_config&) { return g_force_pairs.load() > 0; }
+// Kernel choices a caller can override per call (aklr_moe_config::variant, AKLR_VARIANT_*).
+// CTA pairs are off unless asked for: they cut a CTA's operand traffic by a third, but measured
+// within 2% of the single-CTA kernel at 8+ blocks per expert and slower where experts have one or
+// two blocks (an odd last block wastes half a pair).
+bool force_weight_major(const aklr_moe_config& c) { return (c.variant & AKLR_VARIANT_WEIGHT_MAJOR) != 0; }
+bool use_cta_pairs(const aklr_moe_config& c) { return (c.variant & AKLR_VARIANT_CTA_PAIRS) != 0; }
+bool small_activation_boxes(const aklr_moe_config& c) { return (c.variant & AKLR_VARIANT_FULL_ACTIVATION_BOXES) == 0; }
 
 void profile_mark(cudaStream_t stream, int slot, int stage) {
   if (g_profile.on && slot >= 0) cudaEventRecord(g_profile.events[slot * (kStages + 1) + stage], stream);
@@ -134,12 +130,77 @@ int sm_count() {
   return n;
 }
 
+// ---- a failure every later call hears of ---------------------------------------------------------
+// A kernel whose bounded wait gave up records it in the call's workspace, which only a caller that
+// asks (aklr_moe_read_status) ever reads.  So the kernel also writes the pair (code, location) into
+// two int32 of mapped pinned host memory that belong to its device, and every entry point looks at
+// them -- a plain host read, no copy, no synchronisation -- before it launches anything: the first
+// call after a failure returns AKLR_ERR_KERNEL_WAIT_TIMEOUT and clears the pair.
+constexpr int kMaxDevices = 64;
+std::mutex g_host_status_lock;
+int32_t* g_host_status = nullptr;            // [kMaxDevices][2], one allocation for the process
+int32_t* g_host_status_dev[kMaxDevices] = {};  // the same words as each device addresses them
+
+int32_t* host_status_words(int dev, cudaStream_t stream) {
+  if (dev < 0 || dev >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> guard(g_host_status_lock);
+  if (g_host_status_dev[dev]) return g_host_status_dev[dev];
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone) {
+    cudaGetLastError();
+    return nullptr;  // never set up inside a capture; the next eager call does it
+  }
+  if (!g_host_status) {
+    void* host = nullptr;
+    if (cudaHostAlloc(&host, sizeof(int32_t) * 2 * kMaxDevices, cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    memset(host, 0, sizeof(int32_t) * 2 * kMaxDevices);
+    g_host_status = static_cast<int32_t*>(host);
+  }
+  void* device_view = nullptr;
+  if (cudaHostGetDevicePointer(&device_view, g_host_status + 2 * dev, 0) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  g_host_status_dev[dev] = static_cast<int32_t*>(device_view);
+  return g_host_status_dev[dev];
+}
+
+// Entry-point check: an sm_100 device is current and no earlier kernel on it reported a failed wait.
 int check_device() {
-  int dev = 0, major = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return fail(AKLR_ERR_NO_DEVICE, "no CUDA device is current");
-  cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
-  if (major != 10) return fail(AKLR_ERR_NO_DEVICE, "this library holds sm_100a code only; device has capability %d.x", major);
+  int rc = aklr::require_sm100_device(g_error, sizeof(g_error));
+  if (rc) return rc;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (g_host_status && dev >= 0 && dev < kMaxDevices) {
+    volatile int32_t* words = g_host_status + 2 * dev;
+    const int32_t code = words[0];
+    if (code != 0) {
+      const int32_t where = words[1];
+      words[0] = 0;
+      words[1] = 0;
+      return fail(code, "a kernel of an earlier call on device %d gave up a wait (location %d): what that call and the "
+                        "calls after it wrote is not valid; this call launched nothing", dev, where);
+    }
+  }
   return AKLR_OK;
+}
+
+// Waits on a barrier nothing arrives on, with the caller's limit: what a stuck pipeline looks like
+// to the error path, without one (aklr_selftest_wait_expiry).
+__global__ void wait_expiry_kernel(long long limit_cycles, int32_t* status, int32_t* host_status) {
+  __shared__ uint64_t never;
+  __shared__ int abort_word;
+  if (threadIdx.x == 0) {
+    aklr::mbar_init(&never, 1);
+    abort_word = 0;
+    aklr::fence_mbar_init();
+    volatile int* abort_flag = &abort_word;
+    aklr::mbar_wait(&never, 0, abort_flag, status, 99, limit_cycles);
+    if (abort_word) aklr::publish_wait_failure(status, host_status);
+  }
 }
 
 int pick_block_m(const aklr_moe_config& c) {
@@ -228,9 +289,8 @@ aklr::RouteParams route_params(const aklr_moe_config& c, const void* logits, con
 }
 
 // Whether a call's routing and sort run as the one-CTA decode prologue.
-std::atomic<int> g_fused_prologue{1};  // aklr_debug_fused_prologue(0) keeps the two kernels (tests compare)
 bool fused_prologue_serves(const aklr_moe_config& c) {
-  return g_fused_prologue.load() && c.n_tokens >= 1 && c.n_tokens <= aklr::kDecodePrologueTokens && c.n_routed <= aklr::kDecodePrologueExperts &&
+  return (c.variant & AKLR_VARIANT_SEPARATE_PROLOGUE) == 0 && c.n_tokens >= 1 && c.n_tokens <= aklr::kDecodePrologueTokens && c.n_routed <= aklr::kDecodePrologueExperts &&
          c.n_tokens * (c.topk + c.n_shared) <= 1024 &&
          (c.num_expert_group > 1 && c.topk_group < c.num_expert_group ? c.num_expert_group : 1) * c.topk <=
              aklr::kDecodePrologueExperts;
@@ -267,7 +327,7 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   ap.n_experts = experts;
   ap.n_experts_global = n_experts_global;
   ap.block_m = l.block_m;
-  const bool pairs = l.block_m == 128 && !g_force_swap_ab && use_cta_pairs(c) &&
+  const bool pairs = l.block_m == 128 && !force_weight_major(c) && use_cta_pairs(c) &&
                      grouped_gemm_is_token_major(true, l.block_m, c.inter) &&
                      grouped_gemm_is_token_major(false, l.block_m, c.hidden);
   int32_t* pair_table = block_expert + l.max_blocks;  // second half of the block table's space
@@ -336,12 +396,13 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   g1.out_q = ws + l.hq;
   g1.out_scale = reinterpret_cast<float*>(ws + l.hs);
   g1.status = status;
+  g1.host_status = aklr::host_visible_status(stream);
   g1.k = c.hidden;
   g1.out_dim = c.inter;
   g1.rows_per_expert = 2 * c.inter;
   g1.block_m = l.block_m;
   g1.max_blocks = l.max_blocks;
-  const bool tm1 = grouped_gemm_is_token_major(true, l.block_m, c.inter) && !g_force_swap_ab;
+  const bool tm1 = grouped_gemm_is_token_major(true, l.block_m, c.inter) && !force_weight_major(c);
   g1.pair_table = pairs ? pair_table : nullptr;
   g1.stages = tm1 ? grouped_gemm_prefill_pick_stages(true, pairs) : grouped_gemm_pick_stages(true, l.block_m, c.hidden);
   if (g1.stages < 2) return fail(AKLR_ERR_UNSUPPORTED_SHAPE, "hidden=%d needs more shared memory than one SM has", c.hidden);
@@ -351,7 +412,7 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   profile_mark(stream, slot, 4);
 
   GroupedGemmParams g2{};
-  const bool tm2 = grouped_gemm_is_token_major(false, l.block_m, c.hidden) && !g_force_swap_ab;
+  const bool tm2 = grouped_gemm_is_token_major(false, l.block_m, c.hidden) && !force_weight_major(c);
   rc = make_map_u8(&g2.map_w, w2, static_cast<uint64_t>(experts) * c.hidden, c.inter, tm2 && !pairs ? 256 : 128);
   if (rc) return rc;
   rc = make_map_u8(&g2.map_x, ws + l.hq, l.capacity, c.inter, l.block_m);
@@ -364,6 +425,7 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   g2.topk_weights = topk_weights;
   g2.out_rows = rows_out ? rows_out : ws + l.rows;
   g2.status = status;
+  g2.host_status = g1.host_status;
   g2.k = c.inter;
   g2.out_dim = c.hidden;
   g2.rows_per_expert = c.hidden;
@@ -477,7 +539,7 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   if (rc) return rc;
   rc = make_map_u8(&g1.map_x_rows64, ws + l.xq, l.capacity, c.hidden, 64);
   if (rc) return rc;
-  g1.small_boxes = g_small_boxes.load();
+  g1.small_boxes = small_activation_boxes(c);
   g1.w_scale = w1_scale;
   g1.x_scale = ws + l.xs;
   g1.sorted_ids = sorted_ids;
@@ -486,6 +548,7 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   g1.out_q = ws + l.hq;
   g1.out_scale = ws + l.hs;
   g1.status = status;
+  g1.host_status = aklr::host_visible_status(stream);
   g1.swiglu_limit = opt.swiglu_limit;
   g1.activation = opt.activation;
   g1.beta = opt.beta;
@@ -510,7 +573,7 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   if (rc) return rc;
   rc = make_map_u8(&g2.map_x_rows64, ws + l.hq, l.capacity, c.inter, 64);
   if (rc) return rc;
-  g2.small_boxes = g_small_boxes.load();
+  g2.small_boxes = small_activation_boxes(c);
   g2.w_scale = w2_scale;
   g2.x_scale = ws + l.hs;
   g2.sorted_ids = sorted_ids;
@@ -519,6 +582,7 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   g2.topk_weights = opt.weight_in_stage1 ? nullptr : topk_weights;
   g2.out_rows = rows_out ? rows_out : ws + l.rows;
   g2.status = status;
+  g2.host_status = g1.host_status;
   g2.k = c.inter;
   g2.out_dim = c.hidden;
   g2.rows_per_expert = c.hidden;
@@ -575,6 +639,28 @@ int prepare(const aklr_moe_config* cfg, aklr_moe_workspace_layout* l, void* work
 }
 
 }  // namespace
+
+namespace aklr {
+int require_sm100_device(char* message, size_t message_bytes) {
+  int dev = 0, major = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    snprintf(message, message_bytes, "no CUDA device is current");
+    return AKLR_ERR_NO_DEVICE;
+  }
+  cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+  if (major != 10) {
+    snprintf(message, message_bytes, "this library holds sm_100a code only; device has capability %d.x", major);
+    return AKLR_ERR_NO_DEVICE;
+  }
+  return AKLR_OK;
+}
+void count_kernel_launches(int n) { g_launches += n; }
+int32_t* host_visible_status(cudaStream_t stream) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  return host_status_words(dev, stream);
+}
+}  // namespace aklr
 
 extern "C" {
 
@@ -917,7 +1003,8 @@ int aklr_router_gemm_bf16(const void* x, const void* w, void* logits, int32_t n_
     if (rc) return rc;
     rc = make_map_bf16(&map_w, w, n_routed, hidden, n_tile);
     if (rc) return rc;
-    rc = aklr::launch_router_gemm_tc(map_x, map_w, logits, n_tokens, hidden, n_routed, n_tile, static_cast<cudaStream_t>(stream));
+    rc = aklr::launch_router_gemm_tc(map_x, map_w, logits, n_tokens, hidden, n_routed, n_tile,
+                                     aklr::host_visible_status(static_cast<cudaStream_t>(stream)), static_cast<cudaStream_t>(stream));
   } else {
     rc = aklr::launch_router_gemm(x, w, logits, n_tokens, hidden, n_routed, static_cast<cudaStream_t>(stream));
   }
@@ -1002,23 +1089,31 @@ int aklr_moe_read_status(const void* workspace, int32_t* host_status, void* stre
 
 int64_t aklr_kernel_launch_count(void) { return g_launches.load(); }
 
-int aklr_debug_force_cta_pairs(int32_t mode) {
-  g_force_pairs = mode < 0 ? -1 : (mode != 0 ? 1 : 0);
+int aklr_device_status(int32_t* code_and_location, int32_t clear) {
+  int dev = 0;
+  if (!code_and_location) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return fail(AKLR_ERR_NO_DEVICE, "no CUDA device is current");
+  code_and_location[0] = code_and_location[1] = 0;
+  if (!g_host_status) return AKLR_OK;
+  volatile int32_t* words = g_host_status + 2 * dev;
+  code_and_location[0] = words[0];
+  code_and_location[1] = words[1];
+  if (clear) words[0] = words[1] = 0;
   return AKLR_OK;
 }
 
-int aklr_debug_fused_prologue(int32_t on) {
-  g_fused_prologue = on != 0;
-  return AKLR_OK;
-}
-
-int aklr_debug_small_activation_boxes(int32_t on) {
-  g_small_boxes = on != 0;
-  return AKLR_OK;
-}
-
-int aklr_debug_force_weight_major(int32_t on) {
-  g_force_swap_ab = on != 0;
+int aklr_selftest_wait_expiry(int64_t limit_cycles, int32_t* status, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!status || limit_cycles < 1 || limit_cycles > 4000000000ll)
+    return fail(AKLR_ERR_BAD_ARGUMENT, "status must be a device pointer and the limit 1..4e9 cycles");
+  int rc = check_device();
+  if (rc) return rc;
+  cudaError_t err = cudaMemsetAsync(status, 0, 8, stream);
+  if (err != cudaSuccess) return cuda_fail(err, "clearing the status words");
+  wait_expiry_kernel<<<1, 32, 0, stream>>>(limit_cycles, status, aklr::host_visible_status(stream));
+  err = cudaGetLastError();
+  if (err != cudaSuccess) return cuda_fail(err, "launching the wait self-test");
+  g_launches += 1;
   return AKLR_OK;
 }
 

@@ -91,7 +91,7 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 // the other CTA of a pair).
 template <bool SPIN = false>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int where) {
+                                          int* status, int where, long long limit = AKLR_WAIT_LIMIT_CYCLES) {
   long long start = 0;
   for (uint32_t spin = 1;; ++spin) {
     if (SPIN ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity)) return true;
@@ -99,13 +99,25 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
       if (*abort_flag) return false;
       const long long now = clock64();
       if (start == 0) start = now;
-      if (now - start > AKLR_WAIT_LIMIT_CYCLES) {
+      if (now - start > limit) {
         *abort_flag = 1;
         if (atomicCAS(status, 0, AKLR_ERR_KERNEL_WAIT_TIMEOUT) == 0) status[1] = where;
         return false;
       }
     }
   }
+}
+
+// After a wait gave up, one thread of the CTA copies the call's status words to the device's
+// host-visible pair (mapped pinned host memory, or null): the host looks at it at the start of every
+// later call, so a caller that never reads its workspace's status still hears of the failure.
+__device__ __forceinline__ void publish_wait_failure(const int* status, int32_t* host_visible) {
+  if (host_visible == nullptr || status[0] == 0) return;
+  volatile int32_t* v = host_visible;
+  v[1] = status[1];
+  __threadfence_system();
+  v[0] = status[0];
+  __threadfence_system();
 }
 
 // ---- TMA --------------------------------------------------------------------------------------

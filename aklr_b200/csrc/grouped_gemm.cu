@@ -29,24 +29,6 @@
 
 namespace aklr {
 
-#ifdef AKLR_GEMM_TIMING
-// Development aid (never compiled into the shipped library): CTA 0 accumulates cycle counts per
-// pipeline role.  [0] producer wait-empty, [1] mma wait-full, [2] mma wait-tmem-empty, [3] mma issue,
-// [4] epi wait-tmem-full, [5] epi ld+fma, [6] epi tile set-up, [7] epi final, [8] K-blocks, [9] total
-__device__ long long g_gemm_timing[2][16];
-#define TIMING_ADD(slot, expr)                                   \
-  do {                                                           \
-    const long long t_begin_ = clock64();                        \
-    expr;                                                        \
-    if (blockIdx.x == 0) tacc[slot] += clock64() - t_begin_;     \
-  } while (0)
-#else
-#define TIMING_ADD(slot, expr) \
-  do {                         \
-    expr;                      \
-  } while (0)
-#endif
-
 constexpr int kGemmThreads = 320;
 constexpr int kEpiThreads = 256;
 constexpr int kWTileBytes = 128 * 128;  // 128 channels x 128 K bytes
@@ -96,8 +78,11 @@ __device__ __forceinline__ bool epi_bar_any(int flag) {
   return any != 0;
 }
 
+// Registers per thread: 320 threads leave room for 200 each; the two largest gate_up variants keep
+// 64 / 128 accumulators next to their load batches and need more than the 168 the compiler picks by
+// itself from the block size.
 template <int BM, bool GATE_UP>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __maxnreg__((GATE_UP && BM >= 64) ? 200 : 168)
 grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
   constexpr int NH = BM / 2;                        // columns per epilogue warp
   constexpr int CH = (NH >= 16 && !(GATE_UP && BM == 128)) ? 16 : 8;  // columns per tcgen05.ld (register budget)
@@ -158,17 +143,13 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
       int s = 0;  // ring position and the parity of its current use
       uint32_t ph = 0;
       bool ok = true;
-#ifdef AKLR_GEMM_TIMING
-      long long tacc[16] = {0};
-      const long long t_role = clock64();
-#endif
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const int b = t / tiles_per_block, j = t - b * tiles_per_block;
         const int e = p.block_expert[b];
         const int w_row = e * p.rows_per_expert + j * 128;
         for (int kb = 0; kb < KB; ++kb, ++it) {
           bool got;
-          TIMING_ADD(0, got = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1));
+          got = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1);
           if (!got) { ok = false; break; }
           uint8_t* st = smem + s * L.stage_bytes;
           mbar_expect_tx(&full[s], L.stage_bytes);
@@ -178,13 +159,6 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
           if (++s == S) { s = 0; ph ^= 1; }
         }
       }
-#ifdef AKLR_GEMM_TIMING
-      if (blockIdx.x == 0) {
-        g_gemm_timing[GATE_UP][0] = tacc[0];
-        g_gemm_timing[GATE_UP][8] = it;
-        g_gemm_timing[GATE_UP][9] = clock64() - t_role;
-      }
-#endif
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer --------------------------------------------
@@ -198,19 +172,13 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
       const uint32_t stage_step = static_cast<uint32_t>(L.stage_bytes) >> 4;
       uint64_t da0 = desc0;  // first weight tile of stage s; the second one and the token tile follow
       bool ok = true;
-#ifdef AKLR_GEMM_TIMING
-      long long tacc[16] = {0};
-#endif
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         for (int kb = 0; kb < KB; ++kb) {
           bool got;
-          TIMING_ADD(1, got = mbar_wait(&full[s], ph, abort_flag, p.status, 2));
+          got = mbar_wait(&full[s], ph, abort_flag, p.status, 2);
           if (!got) { ok = false; break; }
-          TIMING_ADD(2, got = mbar_wait(&tmem_empty[buf], bph ^ 1, abort_flag, p.status, 3));
+          got = mbar_wait(&tmem_empty[buf], bph ^ 1, abort_flag, p.status, 3);
           if (!got) { ok = false; break; }
-#ifdef AKLR_GEMM_TIMING
-          const long long t_issue = clock64();
-#endif
           tc_fence_after_sync();
           const uint64_t da1 = da0 + (kWTileBytes >> 4);
           const uint64_t db = da0 + (((GATE_UP ? 2 : 1) * kWTileBytes) >> 4);
@@ -221,19 +189,12 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
             if (GATE_UP) umma_f8f6f4(d + BM, da1 + 2 * k, db + 2 * k, IDESC, k > 0);
           }
           tc_commit(&empty[s]);
-#ifdef AKLR_GEMM_TIMING
-          tacc[3] += clock64() - t_issue;
-#endif
           da0 += stage_step;
           if (++s == S) { s = 0; ph ^= 1; da0 = desc0; }
           bph ^= buf;
           buf ^= 1;
         }
       }
-#ifdef AKLR_GEMM_TIMING
-      if (blockIdx.x == 0)
-        for (int i = 1; i <= 3; ++i) g_gemm_timing[GATE_UP][i] = tacc[i];
-#endif
     }
   } else {
     // ------------------------------- epilogue warps ----------------------------------------
@@ -259,15 +220,7 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
     // experts of this CTA's current and next tile, read a tile ahead of the addresses that need them
     int e_cur = blockIdx.x < total_tiles ? p.block_expert[blockIdx.x / tiles_per_block] : 0;
     int e_ahead = blockIdx.x + gridDim.x < total_tiles ? p.block_expert[(blockIdx.x + gridDim.x) / tiles_per_block] : 0;
-#ifdef AKLR_GEMM_TIMING
-    long long tacc[16] = {0};
-    long long t_mark = clock64();
-#endif
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-#ifdef AKLR_GEMM_TIMING
-      tacc[7] += clock64() - t_mark;
-      t_mark = clock64();
-#endif
       if (epi_bar_any(*abort_flag)) break;   // also fences the aliased smem against the last tile
       const int b = t / tiles_per_block, j = t - b * tiles_per_block;
       const int e = e_cur;
@@ -335,9 +288,6 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
         e_ahead = t2 < total_tiles ? p.block_expert[t2 / tiles_per_block] : 0;
       }
 
-#ifdef AKLR_GEMM_TIMING
-      tacc[6] += clock64() - t_mark;
-#endif
       float acc[TILES][NH];
 #pragma unroll
       for (int a = 0; a < TILES; ++a)
@@ -347,13 +297,10 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
       for (int kb = 0; kb < KB; ++kb, ++it) {
         const int buf = it & 1;
         bool got;
-        TIMING_ADD(4, got = mbar_wait(&empty[ring], ring_ph, abort_flag, p.status, 4));
+        got = mbar_wait(&empty[ring], ring_ph, abort_flag, p.status, 4);
         if (++ring == S) { ring = 0; ring_ph ^= 1; }
         if (!got) bad = true;
         tc_fence_after_sync();
-#ifdef AKLR_GEMM_TIMING
-        const long long t_work = clock64();
-#endif
         const float* fk = ftab + kb * BM + half * NH;
         const uint32_t t0 = tmem_base + lane_addr + buf * BUF_COLS + half * NH;
         // software pipeline: the load of chunk k+1 is in flight while chunk k is folded in
@@ -381,13 +328,7 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
             acc[a][c + i + 3] = fmaf(__uint_as_float(r[k & 1][i + 3]), f4.w, acc[a][c + i + 3]);
           }
         }
-#ifdef AKLR_GEMM_TIMING
-        tacc[5] += clock64() - t_work;
-#endif
       }
-#ifdef AKLR_GEMM_TIMING
-      t_mark = clock64();
-#endif
 
       // the next tile's route weights: their ids have arrived by now, and the epilogue below hides this load
       if (!GATE_UP && have_pre && et < BM) pre_weight = pre_rid >= 0 ? p.topk_weights[pre_rid] : 0.0f;
@@ -441,15 +382,12 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
         }
       }
     }
-#ifdef AKLR_GEMM_TIMING
-    if (blockIdx.x == 0 && warp == 2 && lane == 0)
-      for (int i = 4; i <= 7; ++i) g_gemm_timing[GATE_UP][i] = tacc[i];
-#endif
   }
 
   tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag) {  // a wait gave up: let copies in flight land before shared memory is released
+    if (threadIdx.x == 0) publish_wait_failure(p.status, p.host_status);
     const uint64_t start = global_timer_ns();
     while (global_timer_ns() - start < 200000ull) __nanosleep(1000);
   }
@@ -505,11 +443,6 @@ static int launch_grouped(const GroupedGemmParams& p, int sm_count, cudaStream_t
   }
 }
 
-#ifdef AKLR_GEMM_TIMING
-extern "C" int aklr_debug_read_gemm_timing(long long* host32) {
-  return cudaMemcpyFromSymbol(host32, g_gemm_timing, sizeof(g_gemm_timing)) == cudaSuccess ? 0 : -3;
-}
-#endif
 
 int launch_grouped_gemm_gate_up(const GroupedGemmParams& p, int sm_count, cudaStream_t stream) {
   return launch_grouped<true>(p, sm_count, stream);

@@ -595,6 +595,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
   tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag) {
+    if (threadIdx.x == 0) publish_wait_failure(p.status, p.host_status);
     const uint64_t start = global_timer_ns();
     while (global_timer_ns() - start < 200000ull) __nanosleep(1000);
   }

@@ -19,8 +19,8 @@
 // warpgroup gives its registers to the epilogue (setmaxnreg 40 / 232): 128 accumulators + 64
 // staging registers per epilogue thread do not fit the 168 an even split allows.
 //
-// What bounds it, measured on B200 by taking parts out (-DAKLR_EXP_NOMMA: no MMAs,
-// -DAKLR_EXP_NOTMA: no operand loads): the epilogue's fold alone -- no loads, no MMAs -- already
+// What bounds it, measured on B200 by taking parts out (experimental builds without the MMAs and
+// without the operand loads): the epilogue's fold alone -- no loads, no MMAs -- already
 // takes ~510 ns per K-block per SM, loads added 570 ns (L2-resident weights) / 670 ns (weights
 // from HBM), the full kernel 670 / 790 ns, against 290 ns for the four MMAs.  Per K-block an
 // epilogue warp makes four round trips of tcgen05.ld (latency-bound, and tcgen05.wait::ld waits for
@@ -34,8 +34,6 @@
 // single-buffered load batches, CTA pairs (below).  Persistent CTAs, TMA SWIZZLE_128B ring,
 // two 256-column TMEM partial buffers, no multicast loads, bounded waits.
 #include <cfloat>
-#include <cstdio>
-#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <utility>
@@ -44,26 +42,6 @@
 #include "kernels.h"
 
 namespace aklr {
-
-#ifdef AKLR_GEMM_TIMING
-// Development aid, compiled only on request: cycle counts per role of CTA 0 and a trace of
-// hand-off times (64 K-blocks) of the gate_up kernel.
-// [1] mma wait-full [2] mma wait-tmem-empty [3] mma issue [4] epi wait [5] epi ld+fma [6] setup [7] final [8] kblocks
-__device__ long long g_prefill_timing[2][16];
-__device__ long long g_prefill_trace[8][64];
-#define TR(slot) do { if (GATE_UP && blockIdx.x == 0 && it >= 120 && it < 184) g_prefill_trace[slot][it - 120] = clock64(); } while (0)
-#define PT(slot, expr)                                         \
-  do {                                                         \
-    const long long t_begin_ = clock64();                      \
-    expr;                                                      \
-    if (blockIdx.x == 0) tacc[slot] += clock64() - t_begin_;   \
-  } while (0)
-#else
-#define PT(slot, expr) \
-  do {                 \
-    expr;              \
-  } while (0)
-#endif
 
 namespace {
 
@@ -216,12 +194,6 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
         for (int kb = 0; kb < KB; ++kb) {
           if (!mbar_wait<PAIR>(&empty[s], ph ^ 1, abort_flag, p.status, 11)) { ok = false; break; }
           uint8_t* st = smem + s * kStageBytes;
-#ifdef AKLR_EXP_NOTMA
-          if (rank == 0) mbar_arrive(&full[s]);
-          (void)st;
-          if (++s == S) { s = 0; ph ^= 1; }
-          continue;
-#endif
           if (PAIR) {
             if (rank == 0) mbar_expect_tx(&full[s], 2 * kStageBytes);  // both CTAs' bytes
             const uint32_t bar = full0 + s * 8;
@@ -254,62 +226,34 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
       const uint64_t desc0 = umma_desc_sw128(smem_u32(smem));
       uint64_t da = desc0;  // descriptor of stage s' token tile; the weight tile follows it
       bool ok = true;
-#ifdef AKLR_GEMM_TIMING
-      long long tacc[16] = {0};
-#endif
       for (int t = worker; t < total_tiles && ok; t += n_workers) {
         for (int kb = 0; kb < KB; ++kb, ++it) {
           bool got;
-          PT(1, got = mbar_wait<PAIR>(&full[s], ph, abort_flag, p.status, 12));
+          got = mbar_wait<PAIR>(&full[s], ph, abort_flag, p.status, 12);
           if (!got) { ok = false; break; }
-#ifdef AKLR_GEMM_TIMING
-          TR(0);
-#endif
           // One N=256 MMA per 32 K bytes into this K-block's TMEM buffer and a single commit per
           // K-block: the barrier that frees the shared-memory stage also tells the epilogue that
           // the partial is complete.  (Two N=128 groups with their own hand-offs, so that the
           // epilogue could start on the first half earlier, measured 20% slower: every extra commit
           // and barrier round costs more than the overlap gains.)
-          PT(2, got = mbar_wait<PAIR>(&tmem_empty[buf], bph ^ 1, abort_flag, p.status, 13));
+          got = mbar_wait<PAIR>(&tmem_empty[buf], bph ^ 1, abort_flag, p.status, 13);
           if (!got) { ok = false; break; }
-#ifdef AKLR_GEMM_TIMING
-          TR(1);
-          const long long t_issue = clock64();
-#endif
           tc_fence_after_sync();
           const uint64_t db = da + (kABytes >> 4);
           const uint32_t d = tmem_base + buf * 256;
-#ifndef AKLR_EXP_NOMMA
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             if (PAIR) umma_f8f6f4_pair(d, da + 2 * k, db + 2 * k, umma_idesc_e4m3(256, 256), k > 0);
             else umma_f8f6f4(d, da + 2 * k, db + 2 * k, umma_idesc_e4m3(256), k > 0);
           }
-#endif
-#ifdef AKLR_GEMM_TIMING
-          TR(2);
-          tacc[3] += clock64() - t_issue;
-          const long long t_c2 = clock64();
-#endif
           if (PAIR) tc_commit_pair(&empty[s], 3);
           else tc_commit(&empty[s]);
-#ifdef AKLR_GEMM_TIMING
-          TR(3);
-          tacc[12] += clock64() - t_c2;
-#endif
           da += kStageBytes >> 4;
           if (++s == S) { s = 0; ph ^= 1; da = desc0; }
           bph ^= buf;
           buf ^= 1;
         }
       }
-#ifdef AKLR_GEMM_TIMING
-      if (blockIdx.x == 0) {
-        for (int i = 1; i <= 3; ++i) g_prefill_timing[GATE_UP][i] = tacc[i];
-        for (int i = 10; i <= 12; ++i) g_prefill_timing[GATE_UP][i] = tacc[i];
-        g_prefill_timing[GATE_UP][8] = it;
-      }
-#endif
     }
   }
   } else {
@@ -324,17 +268,8 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
     int ring = 0;          // shared-memory stage whose "empty" barrier reports MMA(it) complete
     uint32_t ring_ph = 0;
     bool bad = false;
-#ifdef AKLR_GEMM_TIMING
-    long long tacc[16] = {0};
-    long long t_mark = clock64();
-    const long long t_kernel = t_mark;
-#endif
     const uint32_t tmem_empty0 = PAIR ? mapa_shared(smem_u32(tmem_empty), 0) : 0u;  // in the even CTA
     for (int t = worker; t < total_tiles; t += n_workers) {
-#ifdef AKLR_GEMM_TIMING
-      tacc[7] += clock64() - t_mark;
-      t_mark = clock64();
-#endif
       if (epi_any(*abort_flag)) break;
       const int u = t / tiles_per_block, j = t - u * tiles_per_block;
       bool live;  // false: the odd CTA of a pair whose expert has no second block
@@ -360,9 +295,6 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
 
       // gate_up: first NH/2 accumulators gate channels cs*NH/2.., then the matching up channels
       // down:    NH output channels cs*NH..
-#ifdef AKLR_GEMM_TIMING
-      tacc[6] += clock64() - t_mark;
-#endif
       uint64_t acc2[NH / 2];  // pairs of float32 accumulators
 #pragma unroll
       for (int i = 0; i < NH / 2; ++i) acc2[i] = 0ull;
@@ -400,15 +332,11 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
         const uint64_t f2_hi = pack_f32x2(__float_as_uint(f_hi), __float_as_uint(f_hi));
         bool got;
         // MMA(it) complete = the "empty" barrier of its shared-memory stage completing phase it / S
-        PT(4, got = mbar_wait<PAIR>(&empty[ring], ring_ph, abort_flag, p.status, 14));
+        got = mbar_wait<PAIR>(&empty[ring], ring_ph, abort_flag, p.status, 14);
         if (++ring == S) { ring = 0; ring_ph ^= 1; }
         if (!got) bad = true;
         tc_fence_after_sync();
         issue(buf, 0);
-#ifdef AKLR_GEMM_TIMING
-        long long t_work = clock64();
-        if (warp == kFirstEpiWarp && lane == 0) TR(4);
-#endif
 #pragma unroll
         for (int bi = 0; bi < NB; ++bi) {
           tc_wait_ld();
@@ -421,9 +349,6 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
               if (PAIR) mbar_arrive_cluster(tmem_empty0 + buf * 8);
               else mbar_arrive(&tmem_empty[buf]);
             }
-#ifdef AKLR_GEMM_TIMING
-            if (warp == kFirstEpiWarp && lane == 0) TR(5);
-#endif
           }
           const uint64_t f2 = (bi * kBatch) / GC == 0 ? f2_lo : f2_hi;
 #pragma unroll
@@ -432,13 +357,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
             acc2[at] = fma_f32x2(pack_f32x2(r[bi & 1][i], r[bi & 1][i + 1]), f2, acc2[at]);
           }
         }
-#ifdef AKLR_GEMM_TIMING
-        if (blockIdx.x == 0) tacc[5] += clock64() - t_work;
-#endif
       }
-#ifdef AKLR_GEMM_TIMING
-      t_mark = clock64();
-#endif
 
       float acc[NH];
 #pragma unroll
@@ -513,17 +432,12 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
         }
       }
     }
-#ifdef AKLR_GEMM_TIMING
-    if (blockIdx.x == 0 && warp == kFirstEpiWarp && lane == 0) {
-      for (int i = 4; i <= 7; ++i) g_prefill_timing[GATE_UP][i] = tacc[i];
-      g_prefill_timing[GATE_UP][9] = clock64() - t_kernel;
-    }
-#endif
   }
 
   tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag) {  // a wait gave up: let copies in flight land before shared memory is released
+    if (threadIdx.x == 0) publish_wait_failure(p.status, p.host_status);
     const uint64_t start = global_timer_ns();
     while (global_timer_ns() - start < 200000ull) __nanosleep(1000);
   }
@@ -537,14 +451,6 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
 
 }  // namespace
 
-#ifdef AKLR_GEMM_TIMING
-extern "C" int aklr_debug_read_prefill_trace(long long* host512) {
-  return cudaMemcpyFromSymbol(host512, g_prefill_trace, sizeof(g_prefill_trace)) == cudaSuccess ? 0 : -3;
-}
-extern "C" int aklr_debug_read_prefill_timing(long long* host32) {
-  return cudaMemcpyFromSymbol(host32, g_prefill_timing, sizeof(g_prefill_timing)) == cudaSuccess ? 0 : -3;
-}
-#endif
 
 bool grouped_gemm_is_token_major(bool gate_up, int block_m, int out_dim) {
   return block_m == 128 && (gate_up || out_dim % 256 == 0);
@@ -581,7 +487,6 @@ int max_active_pairs(Kernel kernel, size_t smem) {
   cfg.numAttrs = 1;
   int n = 0;
   if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) n = 0;
-  if (getenv("AKLR_DEBUG_PAIRS")) fprintf(stderr, "max active CTA pairs: %d (smem %zu)\n", n, smem);
   cache[key] = n;
   return n;
 }

@@ -91,6 +91,7 @@ struct GroupedGemmParams {
   float* out_scale;            // gate_up: [max_blocks, inter/128, block_m]
   void* out_rows;              // down: [n_routes, hidden] bf16 per-route contributions
   int32_t* status;             // [2] error word + location
+  int32_t* host_status;        // the device's host-visible copy of a failure (or null)
   int k;                       // reduction length (hidden for gate_up, inter for down)
   int out_dim;                 // inter (gate_up) or hidden (down)
   int rows_per_expert;         // 2*inter (gate_up) or hidden (down)
@@ -140,6 +141,7 @@ struct MxGemmParams {
   uint8_t* out_scale;          // gate_up: [max_blocks, inter/128, 512]
   void* out_rows;              // down: [n_routes, hidden] bf16
   int32_t* status;
+  int32_t* host_status;        // the device's host-visible copy of a failure (or null)
   float swiglu_limit;          // > 0: clamp gate above and up on both sides before the activation
   int activation;              // gate_up: AKLR_ACT_* of the public header
   float beta, linear_beta;     // gate_up, AKLR_ACT_SITUV2: saturation of gate and up
@@ -182,7 +184,17 @@ int launch_ep_combine(const EpCombineParams& p, cudaStream_t stream);
 
 // tensor-core router GEMM (router_gemm.cu): maps are bf16 [T,H] box 64 x 128 and [E,H] box 64 x n_tile
 int launch_router_gemm_tc(const CUtensorMap& map_x, const CUtensorMap& map_w, void* logits, int n_tokens, int hidden,
-                          int n_routed, int n_tile, cudaStream_t stream);
+                          int n_routed, int n_tile, int32_t* host_status, cudaStream_t stream);
+
+// Shared by the files that hold extern "C" entry points: the device check (sm_100 only) and the
+// process-wide count of kernels this library has launched (aklr_kernel_launch_count).
+int require_sm100_device(char* message, size_t message_bytes);
+void count_kernel_launches(int n);
+// Two int32 of mapped pinned host memory per device (error code, location) that a kernel whose wait
+// gave up writes and every entry point reads before it launches anything; the device-side address
+// for the current device, or null when it could not be set up (then only the workspace's status
+// words report a failure).  ``stream`` is looked at only to avoid setting up inside a capture.
+int32_t* host_visible_status(cudaStream_t stream);
 
 // Opt a kernel in to the full 227 KB of dynamic shared memory, once per (kernel, device).
 int ensure_max_dynamic_smem(const void* kernel);

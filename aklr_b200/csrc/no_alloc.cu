@@ -83,8 +83,10 @@ int aklr_moe_align_noalloc(const int32_t* topk_ids, const int32_t* expert_map, i
              n_routes, n_experts, needed, kNoAllocScratchInts);
     return AKLR_ERR_TOO_LARGE;
   }
+  int rc = aklr::require_sm100_device(g_noalloc_error, sizeof(g_noalloc_error));
+  if (rc) return rc;
   int32_t* scratch = nullptr;
-  int rc = scratch_for_current_device(&scratch);
+  rc = scratch_for_current_device(&scratch);
   if (rc) return rc;
   aklr::AlignParams p{};
   p.topk_ids = topk_ids;
@@ -99,8 +101,12 @@ int aklr_moe_align_noalloc(const int32_t* topk_ids, const int32_t* expert_map, i
   p.n_experts_global = expert_map ? n_experts_global : n_experts;
   p.block_m = block_m;
   rc = aklr::launch_align(p, static_cast<cudaStream_t>(stream));
-  if (rc) snprintf(g_noalloc_error, sizeof(g_noalloc_error), "moe_align launch failed (status %d)", rc);
-  return rc;
+  if (rc) {
+    snprintf(g_noalloc_error, sizeof(g_noalloc_error), "moe_align launch failed (status %d)", rc);
+    return rc;
+  }
+  aklr::count_kernel_launches(n_routes <= 4096 ? 1 : 3);
+  return AKLR_OK;
 }
 
 }  // extern "C"

@@ -20,6 +20,7 @@ struct RouterParams {
   CUtensorMap map_w;  // bf16 [E, H], box 64 x n_tile
   uint16_t* logits;   // bf16 [T, E]
   int32_t* status;    // optional [2]
+  int32_t* host_status;  // the device's host-visible copy of a failure (or null)
   int n_tokens, hidden, n_routed, n_tile;
 };
 
@@ -139,6 +140,7 @@ __global__ void __launch_bounds__(kThreads, 1) router_gemm_tc_kernel(const __gri
   tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag) {
+    if (threadIdx.x == 0) publish_wait_failure(status, p.host_status);
     const uint64_t start = global_timer_ns();
     while (global_timer_ns() - start < 200000ull) __nanosleep(1000);
   }
@@ -151,13 +153,14 @@ __global__ void __launch_bounds__(kThreads, 1) router_gemm_tc_kernel(const __gri
 }  // namespace
 
 int launch_router_gemm_tc(const CUtensorMap& map_x, const CUtensorMap& map_w, void* logits, int n_tokens, int hidden,
-                          int n_routed, int n_tile, cudaStream_t stream) {
+                          int n_routed, int n_tile, int32_t* host_status, cudaStream_t stream) {
   if (hidden % 64 != 0 || n_tile % 16 != 0 || n_tile < 16 || n_tile > 256) return AKLR_ERR_UNSUPPORTED_SHAPE;
   RouterParams p{};
   p.map_x = map_x;
   p.map_w = map_w;
   p.logits = static_cast<uint16_t*>(logits);
   p.status = nullptr;
+  p.host_status = host_status;
   p.n_tokens = n_tokens;
   p.hidden = hidden;
   p.n_routed = n_routed;

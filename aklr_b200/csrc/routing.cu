@@ -333,10 +333,12 @@ static int check_route_shape(const RouteParams& p) {
   if (p.n_routed < 1 || p.n_routed > 1024 || p.topk < 1 || p.topk + p.n_shared > 32 || p.topk > p.n_routed)
     return AKLR_ERR_UNSUPPORTED_SHAPE;
   if (p.num_expert_group > 1) {
-    if (p.num_expert_group > 32 || p.n_routed % p.num_expert_group != 0 ||
-        p.n_routed / p.num_expert_group < 2 || p.topk_group > p.num_expert_group || p.topk_group < 1 ||
-        p.topk > p.topk_group * (p.n_routed / p.num_expert_group))
+    if (p.num_expert_group > 32 || p.n_routed % p.num_expert_group != 0 || p.topk_group > p.num_expert_group ||
+        p.topk_group < 1 || p.topk > p.topk_group * (p.n_routed / p.num_expert_group))
       return AKLR_ERR_UNSUPPORTED_SHAPE;
+    // a group's score is the sum of its two best experts; when every group is kept the kernels
+    // never form it, so single-expert groups are fine there
+    if (p.topk_group < p.num_expert_group && p.n_routed / p.num_expert_group < 2) return AKLR_ERR_UNSUPPORTED_SHAPE;
   }
   return AKLR_OK;
 }

@@ -68,7 +68,7 @@ class Routing:
     routed_scaling_factor: float = 1.0
 
 
-def _config(n_tokens, hidden, inter, n_routed, r: Routing, logits=None, bias=None, block_m=0, n_global=0) -> MoeConfig:
+def _config(n_tokens, hidden, inter, n_routed, r: Routing, logits=None, bias=None, block_m=0, n_global=0, variant=0) -> MoeConfig:
     def code(t):
         if t is None or t.dtype == torch.bfloat16:
             return _lib.DTYPE_BF16
@@ -92,6 +92,7 @@ def _config(n_tokens, hidden, inter, n_routed, r: Routing, logits=None, bias=Non
         bias_dtype=code(bias),
         block_m=block_m,
         n_experts_global=n_global,
+        variant=variant,
     )
 
 
@@ -190,14 +191,16 @@ def fused_moe_fp8(
     block_m: int = 0,
     workspace: Workspace | None = None,
     return_workspace: bool = False,
+    variant: int = 0,
 ):
-    """The whole FP8 layer from router logits: routing, sort, quant, gate_up, down, combine."""
+    """The whole FP8 layer from router logits: routing, sort, quant, gate_up, down, combine.
+    ``variant``: ``_lib.VARIANT_*`` bits overriding a kernel choice for this call (tests)."""
     device = _need_cuda(hidden_states, logits, bias, w1, w1_scale, w2, w2_scale, out)
     e, inter, h = _check_weights(hidden_states, w1, w1_scale, w2, w2_scale)
     n_tokens, n_routed = logits.shape
     if n_routed + routing.n_shared != e or hidden_states.shape[0] != n_tokens:
         raise ValueError("w1 must hold the routed experts followed by the shared ones")
-    cfg = _config(n_tokens, h, inter, n_routed, routing, logits, bias, block_m)
+    cfg = _config(n_tokens, h, inter, n_routed, routing, logits, bias, block_m, variant=variant)
     ws = workspace or Workspace(cfg, device)
     if out is None:
         out = torch.empty_like(hidden_states)
@@ -301,6 +304,7 @@ def fused_experts_mxfp4(
     beta: float | None = None,
     linear_beta: float | None = None,
     num_local_tokens: torch.Tensor | None = None,
+    variant: int = 0,
 ):
     """MXFP4-weight experts with MXFP8 activations, routing given (block-scaled tcgen05 MMA).
     ``activation`` one of ACTIVATIONS; ``weight_in_stage1`` applies the route weight to the gate_up
@@ -316,7 +320,7 @@ def fused_experts_mxfp4(
         raise ValueError("topk_ids int32 and topk_weights float32 must share the shape [tokens, routes]")
     n_tokens, routes = topk_ids.shape
     n_global = 0 if expert_map is None else expert_map.numel()
-    cfg = _config(n_tokens, h, inter, e, Routing(topk=routes), None, None, 128, n_global)
+    cfg = _config(n_tokens, h, inter, e, Routing(topk=routes), None, None, 128, n_global, variant)
     ws = Workspace(cfg, device)
     if out is None:
         out = torch.empty_like(hidden_states)

@@ -783,23 +783,33 @@ def _mega_moe_key(call):
     return (hidden, weights[0], weights[1], ids.shape[1], ep_size)
 
 
-def _mega_moe_run(call, out):
+# one layer object per (weight tensors, group size, top-k, clamp): building it is host work only, but
+# it holds the side stream and the views of the weights, which a serving loop reuses every step
+_MEGA_MOE_LAYERS: dict = {}
+
+
+def _mega_moe_layer(call):
     import torch.distributed as dist
 
     from aklr_b200.ep import CudaKernels, ExpertParallelMoE
 
+    ep_size, topk, limit = call["ep_size"], call["topk_ids"].shape[1], float(call["swiglu_limit"])
+    tensors = (call["w1"], call["w1_scale"], call["w2"], call["w2_scale"])
+    key = tuple((t.data_ptr(), tuple(t.shape)) for t in tensors) + (ep_size, topk, limit)
+    layer = _MEGA_MOE_LAYERS.get(key)
+    if layer is None:
+        if len(_MEGA_MOE_LAYERS) >= 64:  # weights are long-lived; a churn of keys means the caller rebuilt them
+            _MEGA_MOE_LAYERS.clear()
+        rank = dist.get_rank() if ep_size > 1 else 0
+        layer = _MEGA_MOE_LAYERS[key] = ExpertParallelMoE(
+            moe.Routing(topk=topk), *(t.view(torch.uint8) for t in tensors), rank, ep_size, kernels=CudaKernels("mxfp4", limit)
+        )
+    return layer
+
+
+def _mega_moe_run(call, out):
     ep_size = call["ep_size"]
-    rank = dist.get_rank() if ep_size > 1 else 0
-    layer = ExpertParallelMoE(
-        moe.Routing(topk=call["topk_ids"].shape[1]),
-        call["w1"].view(torch.uint8),
-        call["w1_scale"].view(torch.uint8),
-        call["w2"].view(torch.uint8),
-        call["w2_scale"].view(torch.uint8),
-        rank,
-        ep_size,
-        kernels=CudaKernels("mxfp4", float(call["swiglu_limit"])),
-    )
+    layer = _mega_moe_layer(call)
     routed = (call["topk_ids"], call["topk_weights"])
     if ep_size == 1:
         from aklr_b200.ep import run_in_process
@@ -830,6 +840,7 @@ MEGA_MOE = OpContract(
     alloc=_layer_alloc,
     run=_mega_moe_run,
     ranks="ep_size",
+    capturable=False,  # the uneven all-to-all takes its split sizes on the host
 )
 
 

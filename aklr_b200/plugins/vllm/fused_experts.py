@@ -15,6 +15,25 @@ from aklr_b200.plugins.vllm.hook import vllm_route
 
 _MODULE = "vllm.model_executor.layers.fused_moe.fused_moe"
 
+# expert maps already looked at: (address, length, tensor version) -> whether the kept experts' local
+# slots are 0, 1, 2, ... in order of their global id.  The map is a long-lived tensor of the layer, so
+# the one host read it costs happens on the first eager call, never inside a graph capture.
+_ASCENDING_MAPS: dict[tuple, bool] = {}
+
+
+def _slots_ascend(expert_map: torch.Tensor) -> bool:
+    key = (expert_map.data_ptr(), expert_map.numel(), expert_map._version, str(expert_map.device))
+    known = _ASCENDING_MAPS.get(key)
+    if known is None:
+        if expert_map.is_cuda and torch.cuda.is_current_stream_capturing():
+            return False  # not seen eagerly yet: decline rather than read from the host inside a capture
+        kept = expert_map[expert_map >= 0].cpu()
+        known = bool(torch.equal(kept, torch.arange(kept.numel(), dtype=kept.dtype)))
+        if len(_ASCENDING_MAPS) >= 256:
+            _ASCENDING_MAPS.clear()
+        _ASCENDING_MAPS[key] = known
+    return known
+
 
 @vllm_route(f"{_MODULE}.outplace_fused_experts", f"{_MODULE}.fused_experts_impl", versions=("0.22.0",))
 def _fused_experts_impl(
@@ -64,7 +83,9 @@ def _fused_experts_impl(
     expert_mask = None
     if expert_map is not None:
         # vLLM maps a global id to its local slot or -1; the op takes the 0/1 mask and numbers the
-        # kept experts in order, which is the same map when local slots ascend with the global id
+        # kept experts in order, which is the same map only when local slots ascend with the global id
+        if not _slots_ascend(expert_map):
+            return FallbackReason.OUT_OF_CONTRACT
         expert_mask = (expert_map >= 0).to(torch.int32)
     return fused_moe(
         hidden_states=hidden_states,

@@ -1,10 +1,14 @@
 /* C ABI of the B200 (sm_100a) fused-MoE library, libaklr_b200.so.
  *
  * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as void*: a
- * cudaStream_t), launches on that stream, never synchronises, never allocates device memory and
- * keeps no state between calls: scratch comes from the caller as one workspace buffer whose size
- * the matching *_workspace_bytes function gives.  Return value: 0, or a negative AKLR_ERR_* code
- * (aklr_status_string names it).  Nothing here falls back to a CPU path.
+ * cudaStream_t) and launches on that stream.  The compute entry points never synchronise, never
+ * allocate device memory and keep no state between calls: scratch comes from the caller as one
+ * workspace buffer whose size aklr_moe_fp8_workspace gives.  The exceptions say so where they are
+ * declared: aklr_moe_align_noalloc keeps its scratch in an array inside the library that all its
+ * calls on a device share; aklr_moe_read_status and aklr_profile_read wait for the stream because
+ * their job is to read a result back; aklr_profile_begin switches a process-wide event recorder.
+ * Return value: 0, or a negative AKLR_ERR_* code (aklr_status_string names it).  Nothing here falls
+ * back to a CPU path.
  *
  * Each function cites the reference interface it stands in for (paths inside the reference
  * project).  The reference's kernels are Python `run(*, <tensors>, out)` callables served by its
@@ -22,7 +26,7 @@
 extern "C" {
 #endif
 
-#define AKLR_B200_ABI_VERSION 1
+#define AKLR_B200_ABI_VERSION 2
 
 #define AKLR_OK 0
 #define AKLR_ERR_BAD_ARGUMENT -1
@@ -62,7 +66,16 @@ typedef struct aklr_moe_config {
   int32_t bias_dtype;        /* AKLR_DTYPE_* of correction_bias */
   int32_t block_m;           /* tokens per expert block: 16/32/64/128, 0 = library picks */
   int32_t n_experts_global;  /* experts-only entry with an expert map: ids range over this; else 0 */
+  int32_t variant;           /* 0, or AKLR_VARIANT_* bits: kernel choices of THIS call (nothing global) */
 } aklr_moe_config;
+
+/* aklr_moe_config::variant.  Each bit overrides one kernel choice the library otherwise makes by
+ * itself, for this call only, so that two variants can be compared on the same inputs (the results
+ * agree; the tests check it).  No counterpart in the reference. */
+#define AKLR_VARIANT_WEIGHT_MAJOR 1           /* full 128-token blocks through the weight-major (decode) GEMM */
+#define AKLR_VARIANT_CTA_PAIRS 2              /* token-major GEMMs as CTA pairs (cta_group::2, no multicast) */
+#define AKLR_VARIANT_SEPARATE_PROLOGUE 4      /* 1..8 tokens: routing and sort as two kernels, not one */
+#define AKLR_VARIANT_FULL_ACTIVATION_BOXES 8  /* MXFP4 GEMMs load all 128 activation rows of every block */
 
 /* Byte offsets of the intermediates inside the workspace (for tests and debuggers). */
 typedef struct aklr_moe_workspace_layout {
@@ -251,6 +264,22 @@ int aklr_moe_act_quant_fp8(const void* x, void* q, float* scales, int32_t rows, 
  * device-side wait completed. */
 int aklr_moe_read_status(const void* workspace, int32_t* host_status, void* stream);
 
+/* A failed device-side wait, heard by callers that never read a workspace.  Every wait inside the
+ * kernels is bounded; one that gives up makes its kernel drain and return, and records
+ * (AKLR_ERR_KERNEL_WAIT_TIMEOUT, location) in the workspace AND in two int32 of pinned host memory
+ * per device.  Every entry point reads that pair first (a host read; no copy, no synchronisation):
+ * the first call on the device after such a failure launches nothing, returns the code (the message
+ * names the location) and clears the pair.  What the failed call and the calls enqueued after it
+ * wrote is not valid.  aklr_device_status reads (and optionally clears) the current device's pair
+ * without launching anything.  The pinned words are allocated once per process at the first eager
+ * call.  No counterpart in the reference, whose kernels have no bounded waits. */
+int aklr_device_status(int32_t* code_and_location, int32_t clear);
+/* Self-test of that path: one thread waits, for at most limit_cycles SM cycles, on a barrier that
+ * nothing arrives on, then reports as a stuck pipeline would (status: int32[2] on the device, and
+ * the device's host-visible pair).  The kernel always returns; the context stays usable.  Lets an
+ * integrator see what their error handling does with the code without needing a real failure. */
+int aklr_selftest_wait_expiry(int64_t limit_cycles, int32_t* status, void* stream);
+
 /* Measurement aids (no counterpart in the reference, which times with rocprofiler:
  * aklr/core/utils/testing.py:171-252).  aklr_kernel_launch_count: kernels this library has
  * launched in this process.  aklr_profile_begin(n): record CUDA events around the six stages
@@ -258,18 +287,6 @@ int aklr_moe_read_status(const void* workspace, int32_t* host_status, void* stre
  * n = 0 switches it off.  aklr_profile_read(call, ms[6]) waits for that call and gives its
  * stage durations in milliseconds. */
 int64_t aklr_kernel_launch_count(void);
-/* Test aid: non-zero makes full 128-token blocks use the weight-major grouped GEMM (the decode
- * kernel) instead of the token-major one, so both can be checked on the same inputs. */
-int aklr_debug_force_weight_major(int32_t on);
-/* Token-major kernels as CTA pairs (cta_group::2: two token blocks of an expert per pair, each CTA
- * loading half of the weight tile): mode 1 = whenever block_m is 128; 0 or negative = off (default). */
-int aklr_debug_force_cta_pairs(int32_t mode);
-/* aklr_moe_fp8_forward on 1..8 tokens runs routing and sort as one kernel;
- * 0 makes it launch the separate kernels instead (tests compare the two), non-zero restores the default. */
-int aklr_debug_fused_prologue(int32_t on);
-/* The MXFP4 grouped GEMMs load only the first 32 or 64 activation rows of a 128-row block that has no more
- * routed rows than that; 0 makes them load all 128 always (tests compare), non-zero restores the default. */
-int aklr_debug_small_activation_boxes(int32_t on);
 int aklr_profile_begin(int32_t max_calls);
 int aklr_profile_read(int32_t call, float* stage_ms);
 

@@ -39,7 +39,7 @@ def test_every_declared_symbol_is_exported_and_bound(lib):
 
 
 def test_version_and_status_strings(lib):
-    assert lib.aklr_abi_version() == 1
+    assert lib.aklr_abi_version() == 2
     assert lib.aklr_status_string(0) == b"ok"
     assert b"workspace" in lib.aklr_status_string(-2)
 

@@ -200,3 +200,31 @@ def test_real_ops_decline_cpu_tensors_instead_of_computing():
     finally:
         if not was_open:
             dispatcher.close(d.FallbackReason.NO_SCHEMA)
+
+
+def test_an_op_whose_run_reads_the_host_is_not_served_inside_a_capture(monkeypatch):
+    """``capturable=False`` (mega_moe: split sizes of the uneven all-to-all are read on the host): inside a
+    CUDA-graph capture the api returns a FallbackReason instead of breaking the capture, warm key or not."""
+    contract = make_contract()
+    contract.capturable = False
+    dispatcher, fn = make_api(contract)
+    dispatcher.open()
+    a, b = torch.ones(2, 3), torch.ones(4, 3)
+    assert torch.equal(fn(a, b), torch.full((2, 4), 3.0))  # eager: served, and the key is warm now
+    monkeypatch.setattr(d, "_is_capturing", lambda: True)
+    assert fn(a, b) is d.FallbackReason.OUT_OF_CONTRACT
+    assert fn.fallback_reason(a, b) is d.FallbackReason.OUT_OF_CONTRACT
+    capturable, fn2 = make_api(make_contract("toy_gemm2@1.0"))
+    capturable.open()
+    assert fn2(a, b) is d.FallbackReason.NOT_WARMED  # an ordinary op: only its first sight inside a capture falls back
+    monkeypatch.setattr(d, "_is_capturing", lambda: False)
+    fn2(a, b)
+    monkeypatch.setattr(d, "_is_capturing", lambda: True)
+    assert torch.equal(fn2(a, b), torch.full((2, 4), 3.0))
+
+
+def test_mega_moe_declares_that_it_cannot_be_captured():
+    from aklr_b200 import ops
+
+    assert ops.MEGA_MOE.capturable is False
+    assert all(c.capturable for c in (ops.FUSED_MOE, ops.BIASED_GROUPED_TOPK))

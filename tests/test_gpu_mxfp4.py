@@ -51,18 +51,13 @@ def test_blocks_with_few_rows_load_only_those_rows(shape):
     from aklr_b200 import _lib
     from aklr_b200.moe import fused_experts_mxfp4
 
-    lib = _lib.load()
     hidden, inter, experts, topk, tokens = shape
     args = [t.to(dev()) for t in case(hidden, inter, experts, topk, tokens, seed=7 + tokens)]
     outs = []
-    for small in (1, 0):
-        lib.aklr_debug_small_activation_boxes(small)
-        try:
-            out, ws = fused_experts_mxfp4(*args, return_workspace=True)
-            ws.check_status()
-            outs.append(out.cpu())
-        finally:
-            lib.aklr_debug_small_activation_boxes(1)
+    for variant in (0, _lib.VARIANT_FULL_ACTIVATION_BOXES):
+        out, ws = fused_experts_mxfp4(*args, return_workspace=True, variant=variant)
+        ws.check_status()
+        outs.append(out.cpu())
     assert torch.equal(outs[0], outs[1])
 
 

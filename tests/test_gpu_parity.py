@@ -125,6 +125,7 @@ def test_routing_matches_oracle_on_ragged_batches(name, n_tokens):
         dict(n_routed=72, topk=5, n_shared=2, scoring="sigmoid", num_expert_group=4, topk_group=2,
              renormalize=True, routed_scaling_factor=1.5),                    # groups of 18, two shared slots
         dict(n_routed=96, topk=6, scoring="sigmoid", num_expert_group=3, topk_group=3, renormalize=False),  # all groups kept
+        dict(n_routed=8, topk=3, scoring="sigmoid", num_expert_group=8, topk_group=8, renormalize=True),    # one expert per group, all kept
     ],
 )
 def test_routing_on_odd_shapes(shape, n_tokens):
@@ -132,7 +133,11 @@ def test_routing_on_odd_shapes(shape, n_tokens):
 
     cfg = wl.MoEConfig("odd", hidden=128, inter=128, **shape)
     _, logits, bias = wl.router_inputs(cfg, n_tokens, seed=17 + n_tokens)
-    if cfg.scoring == "sigmoid":
+    if cfg.scoring == "sigmoid" and cfg.n_routed == cfg.num_expert_group:
+        # one expert per group, every group kept: the standalone op's statement, which forms no group score
+        ref_w, ref_ids = orc.biased_grouped_topk(logits.float(), bias.float(), cfg.topk, cfg.renormalize, cfg.routed_scaling_factor)
+        ref_ids = ref_ids.long()
+    elif cfg.scoring == "sigmoid":
         ref_ids, ref_w = orc.grouped_sigmoid_topk(
             logits.float(), bias.float(), cfg.topk, cfg.num_expert_group, cfg.topk_group, cfg.renormalize, cfg.routed_scaling_factor
         )
@@ -223,7 +228,7 @@ def test_router_gemm_rounds_like_the_oracle():
 # ------------------------------------------------------------------------------------------------
 # whole layer
 # ------------------------------------------------------------------------------------------------
-def run_layer(cfg, args, logits, block_m):
+def run_layer(cfg, args, logits, block_m, variant=0):
     from aklr_b200.moe import fused_moe_fp8
 
     d = dev()
@@ -239,6 +244,7 @@ def run_layer(cfg, args, logits, block_m):
         routing_of(cfg),
         block_m=block_m,
         return_workspace=True,
+        variant=variant,
     )
     ws.check_status()
     return out, ws
@@ -430,14 +436,9 @@ def test_token_major_and_weight_major_kernels_agree(golden):
     from aklr_b200 import _lib
 
     cfg, a = cases.ds_small_layer()
-    lib = _lib.load()
     out_tm, ws = run_layer(cfg, a, t(golden["ds_small.logits"]), 128)
     check_intermediates(cfg, a, ws, t(golden["ds_small.ids"]))
-    lib.aklr_debug_force_weight_major(1)
-    try:
-        out_wm, _ = run_layer(cfg, a, t(golden["ds_small.logits"]), 128)
-    finally:
-        lib.aklr_debug_force_weight_major(0)
+    out_wm, _ = run_layer(cfg, a, t(golden["ds_small.logits"]), 128, variant=_lib.VARIANT_WEIGHT_MAJOR)
     for out in (out_tm, out_wm):
         gates = orc.output_gates(out.cpu(), t(golden["ds_small.out"]))
         assert orc.gates_pass(gates), gates
@@ -452,15 +453,9 @@ def test_cta_pair_kernels_match_the_single_cta_kernels(golden):
     from aklr_b200 import _lib
     from aklr_b200.moe import fused_moe_fp8
 
-    lib = _lib.load()
     cfg, a = cases.ds_small_layer()
     out_single, ws = run_layer(cfg, a, t(golden["ds_small.logits"]), 128)
-    lib.aklr_debug_force_cta_pairs(1)
-    try:
-        out_pair, ws_pair = run_layer(cfg, a, t(golden["ds_small.logits"]), 128)
-        ws_pair.check_status()
-    finally:
-        lib.aklr_debug_force_cta_pairs(-1)
+    out_pair, ws_pair = run_layer(cfg, a, t(golden["ds_small.logits"]), 128, variant=_lib.VARIANT_CTA_PAIRS)
     assert torch.equal(out_pair.cpu(), out_single.cpu())
     gates = orc.output_gates(out_pair.cpu(), t(golden["ds_small.out"]))
     assert orc.gates_pass(gates), gates
@@ -471,15 +466,11 @@ def test_cta_pair_kernels_match_the_single_cta_kernels(golden):
     w1, s1, w2, s2 = (x.to(d) for x in wl.expert_weights(cfg, seed=5))
     hidden, logits, bias = (x.to(d) for x in wl.router_inputs(cfg, 1500, seed=6))
     outs = []
-    for mode in (0, 1):
-        lib.aklr_debug_force_cta_pairs(mode)
-        try:
-            out, ws = fused_moe_fp8(hidden, logits, bias, w1, s1, w2, s2, routing_of(cfg), block_m=128, return_workspace=True)
-            ws.check_status()
-            outs.append(out.cpu())
-            blocks = ws.num_blocks()
-        finally:
-            lib.aklr_debug_force_cta_pairs(-1)
+    for variant in (0, _lib.VARIANT_CTA_PAIRS):
+        out, ws = fused_moe_fp8(hidden, logits, bias, w1, s1, w2, s2, routing_of(cfg), block_m=128, return_workspace=True, variant=variant)
+        ws.check_status()
+        outs.append(out.cpu())
+        blocks = ws.num_blocks()
     assert blocks > cfg.n_routed  # some experts have more than one block
     assert torch.equal(outs[0], outs[1])
 
@@ -500,21 +491,17 @@ def test_decode_prologue_kernel_matches_the_separate_kernels(name, n_tokens):
     hidden, logits, bias = wl.router_inputs(cfg, n_tokens, seed=300 + n_tokens)
     bias_d = bias.to(d) if bias is not None and cfg.scoring == "sigmoid" else None
     got = []
-    for fused in (1, 0):
-        lib.aklr_debug_fused_prologue(fused)
-        try:
-            launches = lib.aklr_kernel_launch_count()
-            out, ws = fused_moe_fp8(hidden.to(d), logits.to(d), bias_d, w1, s1, w2, s2, routing_of(cfg), return_workspace=True)
-            ws.check_status()
-            rows = ws.num_blocks() * ws.layout.block_m
-            xq, xs = ws.xq()
-            live = ws.sorted_ids()[:rows].cpu() >= 0
-            got.append(dict(out=out.cpu(), ids=ws.topk_ids().cpu(), weights=ws.topk_weights().cpu(), counts=ws.counts().cpu(),
-                            sorted=ws.sorted_ids()[:rows].cpu(), block_expert=ws.block_expert().cpu(),
-                            xq=xq[:rows].cpu().view(torch.uint8)[live], xs=xs[:rows].cpu()[live],
-                            launches=lib.aklr_kernel_launch_count() - launches))
-        finally:
-            lib.aklr_debug_fused_prologue(1)
+    for variant in (0, _lib.VARIANT_SEPARATE_PROLOGUE):
+        launches = lib.aklr_kernel_launch_count()
+        out, ws = fused_moe_fp8(hidden.to(d), logits.to(d), bias_d, w1, s1, w2, s2, routing_of(cfg), return_workspace=True, variant=variant)
+        ws.check_status()
+        rows = ws.num_blocks() * ws.layout.block_m
+        xq, xs = ws.xq()
+        live = ws.sorted_ids()[:rows].cpu() >= 0
+        got.append(dict(out=out.cpu(), ids=ws.topk_ids().cpu(), weights=ws.topk_weights().cpu(), counts=ws.counts().cpu(),
+                        sorted=ws.sorted_ids()[:rows].cpu(), block_expert=ws.block_expert().cpu(),
+                        xq=xq[:rows].cpu().view(torch.uint8)[live], xs=xs[:rows].cpu()[live],
+                        launches=lib.aklr_kernel_launch_count() - launches))
     one, three = got
     assert one["launches"] == three["launches"] - 1
     for key in ("ids", "weights", "counts", "sorted", "block_expert", "xq", "xs", "out"):

@@ -256,6 +256,24 @@ def test_vllm_route_declines_what_the_op_does_not_take():
         FallbackReason.NO_SCHEMA, FallbackReason.OUT_OF_CONTRACT)
 
 
+def test_vllm_route_takes_an_expert_map_only_when_local_slots_ascend(monkeypatch):
+    """vLLM's expert_map names a local slot per global expert; the op numbers the kept experts in order of
+    their global id.  The two agree only for ascending slots: any other map stays with vLLM."""
+    from aklr_b200.plugins.vllm import fused_experts
+
+    seen = {}
+    monkeypatch.setattr(fused_experts, "fused_moe", lambda **kw: seen.update(kw) or "served")
+    x = torch.zeros(2, 128, dtype=torch.bfloat16)
+    ascending = torch.tensor([-1, 0, -1, 1, 2, -1], dtype=torch.int32)
+    shuffled = torch.tensor([-1, 2, -1, 0, 1, -1], dtype=torch.int32)
+    kw = dict(use_fp8_w8a8=True, block_shape=[128, 128])
+    assert fused_experts._fused_experts_impl(x, None, None, None, None, False, expert_map=ascending, **kw) == "served"
+    assert seen["expert_mask"].tolist() == [0, 1, 0, 1, 1, 0]
+    assert fused_experts._fused_experts_impl(x, None, None, None, None, False, expert_map=shuffled, **kw) is FallbackReason.OUT_OF_CONTRACT
+    shuffled.copy_(ascending)  # rewritten in place: looked at again
+    assert fused_experts._fused_experts_impl(x, None, None, None, None, False, expert_map=shuffled, **kw) == "served"
+
+
 def test_vllm_groups_install_together_or_not_at_all(monkeypatch):
     from aklr_b200.plugins.vllm import hook
 
