@@ -402,7 +402,7 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   g1.rows_per_expert = 2 * c.inter;
   g1.block_m = l.block_m;
   g1.max_blocks = l.max_blocks;
-  const bool tm1 = grouped_gemm_is_token_major(true, l.block_m, c.inter) && !force_weight_major(c);
+  const bool tm1 = grouped_gemm_is_token_major(true, l.block_m, c.inter);  // at 128 tokens per block always
   g1.pair_table = pairs ? pair_table : nullptr;
   g1.stages = tm1 ? grouped_gemm_prefill_pick_stages(true, pairs) : grouped_gemm_pick_stages(true, l.block_m, c.hidden);
   if (g1.stages < 2) return fail(AKLR_ERR_UNSUPPORTED_SHAPE, "hidden=%d needs more shared memory than one SM has", c.hidden);

@@ -78,14 +78,11 @@ __device__ __forceinline__ bool epi_bar_any(int flag) {
   return any != 0;
 }
 
-// Registers per thread: 320 threads leave room for 200 each; the two largest gate_up variants keep
-// 64 / 128 accumulators next to their load batches and need more than the 168 the compiler picks by
-// itself from the block size.
 template <int BM, bool GATE_UP>
-__global__ void __maxnreg__((GATE_UP && BM >= 64) ? 200 : 168)
+__global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
   constexpr int NH = BM / 2;                        // columns per epilogue warp
-  constexpr int CH = (NH >= 16 && !(GATE_UP && BM == 128)) ? 16 : 8;  // columns per tcgen05.ld (register budget)
+  constexpr int CH = (NH >= 16 && !(GATE_UP && BM >= 64)) ? 16 : 8;  // columns per tcgen05.ld (register budget: 168 per thread)
   constexpr int BUF_COLS = (GATE_UP ? 2 : 1) * BM;  // TMEM columns of one partial buffer
   constexpr int TMEM_COLS = 2 * BUF_COLS < 32 ? 32 : 2 * BUF_COLS;
   constexpr uint32_t IDESC = umma_idesc_e4m3(BM);
@@ -438,7 +435,11 @@ static int launch_grouped(const GroupedGemmParams& p, int sm_count, cudaStream_t
     case 16: return run(grouped_gemm_kernel<16, GATE_UP>);
     case 32: return run(grouped_gemm_kernel<32, GATE_UP>);
     case 64: return run(grouped_gemm_kernel<64, GATE_UP>);
-    case 128: return run(grouped_gemm_kernel<128, GATE_UP>);
+    case 128:
+      // gate_up on 128-token blocks is always the token-major kernel's; a weight-major one would keep
+      // 128 accumulators per thread and spill
+      if constexpr (GATE_UP) return AKLR_ERR_UNSUPPORTED_SHAPE;
+      else return run(grouped_gemm_kernel<128, false>);
     default: return AKLR_ERR_UNSUPPORTED_SHAPE;
   }
 }

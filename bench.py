@@ -6,9 +6,14 @@ One step = one layer call over a batch of T tokens per GPU (routing -> sort -> q
 down -> combine).  Prints ONE JSON line.  ``value`` is tokens/s with inputs resident in HBM;
 ``e2e`` is the same through the reference-facing op (``deepseek_v2_fp8_moe``, router GEMM
 included) from pinned HOST buffers with both copies timed; ``roofline`` describes the dominant
-kernel (the gate_up grouped GEMM); ``cpu_baseline`` is the CPU oracle timed on a bounded sample.
+kernel (the gate_up grouped GEMM); ``cpu_baseline`` is the reference's CPU implementation of the
+path timed on a bounded sample.  The same line also carries, as sub-records: ``sustained`` (two
+seconds of back-to-back steps with the clocks seen), ``sweep`` (other token counts as CUDA-graph
+replays), ``models`` (the Mixtral-8x7B and Qwen3-30B-A3B widths) and ``mxfp4`` (MXFP4 weights with
+MXFP8 activations at 8192 tokens).
 N > 1: expert parallelism, each rank holds n_routed/N routed experts + the shared expert and its
-own T tokens (weak scaling); dispatch and combine are NCCL all-to-alls.
+own T tokens (weak scaling); dispatch and combine are NCCL all-to-alls; before anything is timed
+rank 0 checks tokens of its own against the CPU oracle (``parity``; a failed gate exits non-zero).
 """
 
 from __future__ import annotations
@@ -23,12 +28,13 @@ import subprocess
 import sys
 import tempfile
 import time
+import types
 
 import torch
 
 ROOT = pathlib.Path(__file__).resolve().parent
-# gate_up grouped GEMM: measured DRAM traffic / algorithmic bytes in the ncu captures summarised in
-# profiles/grouped_gemm_prefill_t1024_e64.md (2.157 GB / 2.02 GB) and profiles/grouped_gemm_decode_t64_e64.md (ratio 1.01)
+# DRAM bytes the gate_up grouped GEMM moves per algorithmic byte, from ncu captures of smaller cases
+# of the same kernels (dram__bytes_read.sum + dram__bytes_write.sum over the launch's algorithmic bytes)
 TRAFFIC_PER_ALGORITHMIC_BYTE = {"prefill": 1.068, "decode": 1.01}
 sys.path.insert(0, str(ROOT))
 
@@ -38,16 +44,22 @@ METRIC = "fp8_fused_moe_tokens_per_s"
 UNIT = "tokens/s"
 SEED = 2024
 FALLBACK_HBM_GBS = 6650.0
+STAGES = ["route", "sort", "quant", "gate_up", "down", "combine"]
+# token counts each configuration is quoted on
+SWEEP_TOKENS = {"deepseek_v3": (1, 64, 256, 16384), "mixtral": (1, 16, 64, 256, 1024, 4096), "qwen3": (1, 32, 256, 2048, 8192)}
+CPU_SAMPLE_TOKENS = 8  # tokens per step of the CPU legs: about 60 of the 257 experts, 2.6 GB of weights
 
 
-def measured_peak_hbm() -> tuple[float, str]:
+def measured_peaks() -> tuple[float, float, str]:
+    """(HBM GB/s, dense FP8 TFLOP/s taken as twice the measured bf16 burst, 'measured' | 'fallback')."""
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
         try:
-            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+            peaks = json.loads(path.read_text())
+            return float(peaks["hbm_gbs"]), 2.0 * float(peaks["bf16_tflops"]), "measured"
         except Exception:
             pass
-    return FALLBACK_HBM_GBS, "fallback"
+    return FALLBACK_HBM_GBS, 2.0 * 1590.0, "fallback"
 
 
 class ClockSampler:
@@ -123,70 +135,148 @@ def routing_of(cfg):
 
 
 # --------------------------------------------------------------------------------------------------
-# CPU oracle timing (cpu_baseline leg and the --impl reference arm)
+# The reference's CPU implementation of the path (cpu_baseline leg and the --impl reference arm)
 # --------------------------------------------------------------------------------------------------
 class HostExperts:
-    """Expert weights on the host, drawn one expert at a time on first use (outside timing)."""
+    """One field (0: w1, 1: w1_scale, 2: w2, 3: w2_scale) of the layer's experts on the host, indexable by
+    expert like the stacked tensor; an expert is drawn on first use (outside timing)."""
 
-    def __init__(self, cfg, seed, which):
-        self.cfg, self.seed, self.which, self.cache = cfg, seed, which, {}
+    def __init__(self, cfg, seed, which, cache):
+        self.cfg, self.seed, self.which, self.cache = cfg, seed, which, cache
 
     def prefetch(self, experts):
+        draw_on = "cuda" if torch.cuda.is_available() else "cpu"
         for e in experts:
             if e not in self.cache:
-                self.cache[e] = wl.one_expert_weights(self.cfg, self.seed, e, "cpu")
+                self.cache[e] = tuple(t.cpu() for t in wl.one_expert_weights(self.cfg, self.seed, e, draw_on))
 
     def __getitem__(self, e):
         self.prefetch([e])
         return self.cache[e][self.which]
 
 
-def oracle_step(cfg, hidden, logits, bias, host, orc):
-    ids, w = orc.grouped_sigmoid_topk(
-        logits.float(), bias.float(), cfg.topk, cfg.num_expert_group, cfg.topk_group, cfg.renormalize, cfg.routed_scaling_factor
-    )
-    ids, w = orc.with_shared_slot(ids, w, cfg.n_routed)
-    return orc.fp8_experts(hidden, ids, w, host[0], host[1], host[2], host[3])
+class CpuPath:
+    """The layer on the host cores: the reference's own ``deepseek_v2_fp8_moe_reference`` where its package
+    can be imported (an install under baseline/_ref travels with the repository), else the restatement
+    under oracle/ (the same arithmetic function by function)."""
+
+    def __init__(self, cfg):
+        from oracle import moe_oracle as orc
+
+        self.cfg, self.orc = cfg, orc
+        self.cores = os.cpu_count() or 1
+        torch.set_num_threads(self.cores)
+        cache: dict = {}
+        self.host = [HostExperts(cfg, SEED, i, cache) for i in range(4)]
+        self.router_w = wl.router_weight(cfg, SEED)
+        self.kind, self.reference, self.fp8_linear = "port", None, None
+        ref_dir = ROOT / "baseline" / "_ref"
+        if (ref_dir / "aklr").is_dir():
+            sys.path.insert(0, str(ref_dir))
+            try:
+                from aklr.plugins.sglang.models.deepseek_v2 import reference as ref_module
+
+                self.reference = ref_module.deepseek_v2_fp8_moe_reference
+                self.fp8_linear = ref_module._fp8_linear
+                self.kind = "reference"
+            except Exception as e:  # the port below is the same arithmetic
+                print(f"bench: the reference package under {ref_dir} did not import ({e!r}); timing the port", file=sys.stderr)
+            finally:
+                sys.path.remove(str(ref_dir))
+        self.point = types.SimpleNamespace(
+            dtypes={"hidden_states": "bfloat16", "router_weight": "bfloat16", "correction_bias": "bfloat16", "w1": "float8_e4m3fn",
+                    "w1_scale": "float32", "w2": "float8_e4m3fn", "w2_scale": "float32"},
+            attrs={"topk": cfg.topk, "num_expert_group": cfg.num_expert_group, "topk_group": cfg.topk_group, "renormalize": cfg.renormalize},
+            axes={"n_routed": cfg.n_routed},
+        )
+
+    def experts_hit(self, hidden, bias):
+        logits = self.orc.router_logits(hidden, self.router_w)
+        ids, _ = self.orc.grouped_sigmoid_topk(logits, bias.float(), self.cfg.topk, self.cfg.num_expert_group, self.cfg.topk_group,
+                                               self.cfg.renormalize, self.cfg.routed_scaling_factor)
+        return sorted(set(ids.flatten().tolist()) | set(range(self.cfg.n_routed, self.cfg.n_experts)))
+
+    def step(self, hidden, bias):
+        c = self.cfg
+        if self.reference is not None:
+            args = dict(hidden_states=hidden, router_weight=self.router_w, correction_bias=bias, w1=self.host[0], w1_scale=self.host[1],
+                        w2=self.host[2], w2_scale=self.host[3], routed_scaling_factor=c.routed_scaling_factor)
+            return self.reference(self.point, args)
+        return self.orc.deepseek_v2_fp8_moe(hidden, self.router_w, bias, self.host[0], self.host[1], self.host[2], self.host[3], c.topk,
+                                            c.num_expert_group, c.topk_group, c.renormalize, c.routed_scaling_factor)
+
+    def time_steps(self, sample_tokens, steps, warmup):
+        """(tokens/s, seconds in the timed steps): ``steps`` calls on ``sample_tokens`` tokens each."""
+        batches = []
+        for s in range(steps + warmup):
+            hidden, _, bias = wl.router_inputs(self.cfg, sample_tokens, SEED + 1000 + s)
+            self.host[0].prefetch(self.experts_hit(hidden, bias))
+            batches.append((hidden, bias))
+        for hidden, bias in batches[:warmup]:
+            self.step(hidden, bias)
+        t0 = time.perf_counter()
+        for hidden, bias in batches[warmup:]:
+            self.step(hidden, bias)
+        elapsed = time.perf_counter() - t0
+        return sample_tokens * steps / elapsed, elapsed
+
+    def full_batch_estimate(self, n_tokens):
+        """Tokens/s the same code would reach on the whole batch, where every expert is decoded once for
+        about 128 rows instead of once for one or two: (time of one expert's MLP on 1 row) x experts +
+        (extra time per row, from the MLP on 128 rows) x the other routes.  An estimate, labelled as one."""
+        c, orc = self.cfg, self.orc
+        e = c.n_routed  # the shared expert: drawn for every sample already
+        w1, s1, w2, s2 = (h[e] for h in self.host)
+        rows = wl.normal(SEED, "estimate", (128, c.hidden), 1.0, dtype=torch.bfloat16).float()
+
+        def mlp(x):
+            if self.fp8_linear is not None:
+                gate, up = self.fp8_linear(x, w1.float(), s1).chunk(2, dim=-1)
+                return self.fp8_linear(torch.nn.functional.silu(gate) * up, w2.float(), s2)
+            gate, up = (orc.fp8_input(x) @ orc.dequant_block_weight(w1, s1).T).chunk(2, dim=-1)
+            return orc.fp8_input(torch.nn.functional.silu(gate) * up) @ orc.dequant_block_weight(w2, s2).T
+
+        def best_of(x, n=3):
+            times = []
+            for _ in range(n):
+                t0 = time.perf_counter()
+                mlp(x)
+                times.append(time.perf_counter() - t0)
+            return min(times)
+
+        t_one, t_block = best_of(rows[:1]), best_of(rows)
+        per_row = max(t_block - t_one, 0.0) / 127
+        routes = n_tokens * c.routes_per_token
+        seconds = c.n_experts * t_one + max(routes - c.n_experts, 0) * per_row
+        return {
+            "value": n_tokens / seconds,
+            "unit": UNIT,
+            "seconds_per_step": seconds,
+            "method": f"{c.n_experts} experts x {t_one * 1e3:.0f} ms (one expert's MLP on 1 row, weights decoded) + "
+                      f"{routes - c.n_experts} further routes x {per_row * 1e6:.0f} us (from the MLP on 128 rows); an estimate, not a measurement",
+        }
 
 
-def oracle_experts_hit(cfg, logits, bias, orc):
-    ids, _ = orc.grouped_sigmoid_topk(
-        logits.float(), bias.float(), cfg.topk, cfg.num_expert_group, cfg.topk_group, cfg.renormalize, cfg.routed_scaling_factor
-    )
-    return sorted(set(ids.flatten().tolist()) | set(range(cfg.n_routed, cfg.n_experts)))
-
-
-def time_cpu_oracle(cfg, n_tokens, sample_tokens, steps, warmup):
-    """Tokens/s of the CPU oracle over ``steps`` calls on ``sample_tokens`` tokens each."""
-    from oracle import moe_oracle as orc
-
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    host = [HostExperts(cfg, SEED, i) for i in range(4)]
-    for h in host[1:]:
-        h.cache = host[0].cache
-    batches = []
-    for s in range(steps + warmup):
-        hidden, logits, bias = wl.router_inputs(cfg, sample_tokens, SEED + 1000 + s)
-        host[0].prefetch(oracle_experts_hit(cfg, logits, bias, orc))
-        batches.append((hidden, logits, bias))
-    for hidden, logits, bias in batches[:warmup]:
-        oracle_step(cfg, hidden, logits, bias, host, orc)
-    t0 = time.perf_counter()
-    for hidden, logits, bias in batches[warmup:]:
-        oracle_step(cfg, hidden, logits, bias, host, orc)
-    elapsed = time.perf_counter() - t0
-    return sample_tokens * steps / elapsed, elapsed, cores
+def cpu_record(cpu: CpuPath, value, elapsed, steps, sample) -> dict:
+    return {
+        "value": value,
+        "unit": UNIT,
+        "cores": cpu.cores,
+        "kind": cpu.kind,
+        "sample": f"{steps} steps of {sample} tokens of the workload ({elapsed:.1f} s timed), router GEMM included, "
+                  "expert weights already in host memory; every step decodes the ~60 experts its tokens hit",
+    }
 
 
 def run_reference_arm(args, cfg):
-    """The reference's CPU implementation of the path (its torch reference, restated in oracle/)
-    on this box's host cores, on a bounded sample of the workload per step."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    """The reference's CPU implementation of the path on this box's host cores, on a bounded sample of
+    the workload per step."""
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    sample = 1  # tokens per step: one DeepSeek-V3 token visits 9 experts of 44 MB
-    value, elapsed, cores = time_cpu_oracle(cfg, args.tokens, sample, args.steps, args.warmup)
+    cpu = CpuPath(cfg)
+    value, elapsed = cpu.time_steps(CPU_SAMPLE_TOKENS, args.steps, args.warmup)
+    record = cpu_record(cpu, value, elapsed, args.steps, CPU_SAMPLE_TOKENS)
+    record["full_batch_estimate"] = cpu.full_batch_estimate(args.tokens)
     line = {
         "impl": "reference",
         "metric": METRIC,
@@ -202,13 +292,7 @@ def run_reference_arm(args, cfg):
         "dtype": "fp8_e4m3",
         "data": "synthetic",
         "config": workload_config(cfg, args),
-        "cpu_baseline": {
-            "value": value,
-            "unit": UNIT,
-            "cores": cores,
-            "kind": "port",
-            "sample": f"{sample} token(s) of the workload per step, {args.steps} steps, expert weights already in host memory",
-        },
+        "cpu_baseline": record,
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -233,10 +317,115 @@ def workload_config(cfg, args):
 
 
 # --------------------------------------------------------------------------------------------------
-# GPU arm
+# GPU arm, one GPU
 # --------------------------------------------------------------------------------------------------
 def distinct_experts(ids: torch.Tensor) -> int:
     return int(torch.unique(ids).numel())
+
+
+def device_ids(cfg, logits, bias):
+    """Routing ids of a batch computed by the routing kernel itself (for experts-hit counts)."""
+    from aklr_b200.moe import route
+
+    return route(logits, bias, routing_of(cfg))[0]
+
+
+def read_stage_ms(lib, calls, first=0, stride=1):
+    from aklr_b200 import _lib
+
+    stage_ms = [0.0] * 6
+    buf = (ctypes.c_float * 6)()
+    for i in range(calls):
+        _lib.check(lib.aklr_profile_read(first + stride * i, buf))
+        for j in range(6):
+            stage_ms[j] += buf[j] / calls
+    return stage_ms
+
+
+def graph_sweep(cfg, tokens_list, weights, bias, device, peak_hbm, peak_fp8, layer_call, block_m=0):
+    """Each token count as one CUDA graph of 8 layer calls on rotating batches, replayed (the reference's
+    measurement protocol): at small counts the host cannot issue the launches as fast as they run."""
+    from aklr_b200.moe import Workspace, _config
+
+    routing = routing_of(cfg)
+    rows = []
+    for tokens in tokens_list:
+        batches = [wl.router_inputs(cfg, tokens, SEED + 50 + b, device)[:2] for b in range(8)]
+        out = torch.empty((tokens, cfg.hidden), dtype=torch.bfloat16, device=device)
+        ws = Workspace(_config(tokens, cfg.hidden, cfg.inter, cfg.n_routed, routing, batches[0][1], bias, block_m), device)
+        for hidden, logits in batches:  # every batch once outside a capture
+            layer_call(hidden, logits, bias, *weights, routing, out=out, workspace=ws, block_m=block_m)
+        ws.check_status()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for hidden, logits in batches:
+                layer_call(hidden, logits, bias, *weights, routing, out=out, workspace=ws, block_m=block_m)
+        for _ in range(3):
+            graph.replay()
+        replays = 2 if tokens >= 1024 else 8
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(replays):
+            graph.replay()
+        stop.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(stop) / (replays * 8)
+        hit = sum(distinct_experts(device_ids(cfg, logits, bias)) for _, logits in batches) / 8
+        flops, nbytes = wl.roofline_work(cfg, tokens, hit)
+        t_hbm, t_tensor = nbytes / (peak_hbm * 1e9), flops / (peak_fp8 * 1e12)
+        rows.append({
+            "tokens": tokens, "us_per_call": ms * 1e3, "tokens_per_s": tokens / (ms * 1e-3), "experts_hit": hit,
+            "bound": "hbm" if t_hbm > t_tensor else "tensor", "frac_of_hbm_roofline": t_hbm / (ms * 1e-3),
+            "tflops": flops / (ms * 1e-3) / 1e12, "frac_of_fp8_peak": flops / (ms * 1e-3) / 1e12 / peak_fp8, "block_m": ws.layout.block_m,
+        })
+        del graph, ws, out, batches
+    return rows
+
+
+def bench_mxfp4_record(cfg, tokens, steps, warmup, device, lib, peak_hbm, peak_fp8):
+    """Configuration 5 on one GPU: the same layer with MXFP4 expert weights and MXFP8 activations."""
+    from aklr_b200.moe import Workspace, _config, fused_moe_mxfp4
+
+    routing = routing_of(cfg)
+    w1, s1, w2, s2 = wl.mx_expert_weights(cfg, SEED, device)
+    bias = wl.router_inputs(cfg, 1, SEED + 1, device)[2]
+    batches = [wl.router_inputs(cfg, tokens, SEED + 1 + b, device)[:2] for b in range(4)]
+    out = torch.empty((tokens, cfg.hidden), dtype=torch.bfloat16, device=device)
+    ws = Workspace(_config(tokens, cfg.hidden, cfg.inter, cfg.n_routed, routing, batches[0][1], bias, 128), device)
+
+    def step(i):
+        hidden, logits = batches[i % 4]
+        fused_moe_mxfp4(hidden, logits, bias, w1, s1, w2, s2, routing, out=out, workspace=ws)
+
+    for i in range(warmup):
+        step(i)
+    ws.check_status()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    lib.aklr_profile_begin(steps)
+    start.record()
+    for i in range(steps):
+        step(warmup + i)
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / steps
+    stage_ms = read_stage_ms(lib, steps)
+    lib.aklr_profile_begin(0)
+    hit = distinct_experts(ws.topk_ids())
+    h, inter = cfg.hidden, cfg.inter
+    weight_bytes = hit * (3 * h * inter // 2 + 3 * h * inter // 32)
+    flops = tokens * cfg.routes_per_token * cfg.flops_per_route
+    return {
+        "workload": f"deepseek_v3 widths, mxfp4 weights (e2m1 + e8m0 per 32) x mxfp8 activations, {tokens} tokens",
+        "tokens": tokens, "ms_per_step": ms, "tokens_per_s": tokens / (ms * 1e-3), "tflops": flops / (ms * 1e-3) / 1e12,
+        "frac_of_fp8_peak": flops / (ms * 1e-3) / 1e12 / peak_fp8,
+        "frac_of_hbm_roofline": weight_bytes / (peak_hbm * 1e9) / (ms * 1e-3),
+        "gate_up_tflops": 2 * flops / 3 / (stage_ms[3] * 1e-3) / 1e12 if stage_ms[3] > 0 else None,
+        "down_tflops": flops / 3 / (stage_ms[4] * 1e-3) / 1e12 if stage_ms[4] > 0 else None,
+        "stage_ms": dict(zip(STAGES, stage_ms)),
+        "parity": "tests/test_gpu_full_width.py checks this shape against the oracle",
+    }
 
 
 def main() -> None:
@@ -247,14 +436,13 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=4096, help="tokens per GPU per step")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--sweep", action="store_true", help="also time decode/prefill token counts (extra keys)")
-    ap.add_argument("--sweep-tokens", default="1,16,64,256,1024,16384", help="token counts of --sweep, comma-separated")
-    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling captures)")
-    ap.add_argument("--model", default="deepseek_v3", choices=["deepseek_v3", "mixtral", "qwen3"],
-                    help="mixtral / qwen3: the other FP8 configurations, one GPU, timed as CUDA-graph replays over their token counts")
+    ap.add_argument("--headline-only", action="store_true", help="skip the sub-records (sustained, sweep, models, mxfp4, e2e, cpu): profiling captures")
+    ap.add_argument("--sweep-tokens", default="", help="token counts of the sweep sub-record, comma-separated (default: the configuration's)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
     ap.add_argument("--routed-experts", type=int, default=0, help="shrink the layer to this many routed experts (profiling captures only)")
     ap.add_argument("--block-m", type=int, default=0, help="force the tokens-per-block of the grouped GEMMs")
-    ap.add_argument("--format", default="fp8", choices=["fp8", "mxfp4"], help="expert weight format (mxfp4: MXFP8 activations)")
+    ap.add_argument("--variant", type=int, default=0, help="aklr_moe_config.variant bits for the headline leg")
+    ap.add_argument("--format", default="fp8", choices=["fp8", "mxfp4"], help="mxfp4: only the MXFP4 record, as the line's value")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     cfg = wl.CONFIGS["deepseek_v3"]
@@ -291,27 +479,39 @@ def main() -> None:
     lib = _lib.load()
 
     if world > 1:
-        from aklr_b200.ep import bench_ep
-
-        line = bench_ep(args, cfg, rank, world, device, ClockSampler, workload_config, METRIC, UNIT, measured_peak_hbm)
+        line = bench_ep(args, cfg, rank, world, device, lib)
         dist.destroy_process_group()
         sys.stdout.flush()
         os.dup2(saved_stdout, 1)
         if line is not None:
             print(line, flush=True)
         return
+    print(json.dumps(bench_one_gpu(args, cfg, device, local_rank, lib)), flush=True)
 
-    from aklr_b200 import ops
+
+def bench_one_gpu(args, cfg, device, local_rank, lib) -> dict:
+    from aklr_b200 import _lib, ops
     from aklr_b200.moe import Workspace, _config, fused_moe_fp8
 
     routing = routing_of(cfg)
     T = args.tokens
+    peak, peak_fp8, peak_kind = measured_peaks()
     if args.format == "mxfp4":
-        bench_mxfp4(args, cfg, routing, device, lib)
-        return
-    if args.model != "deepseek_v3":
-        bench_other_model(args, wl.CONFIGS[args.model], device, lib)
-        return
+        sampler = ClockSampler(local_rank)
+        sampler.begin()
+        launches0 = lib.aklr_kernel_launch_count()
+        record = bench_mxfp4_record(cfg, T, args.steps, args.warmup, device, lib, peak, peak_fp8)
+        config = workload_config(cfg, args)
+        config["workload"] = record["workload"]
+        config["weights"], config["activations"] = "mxfp4: e2m1 + e8m0 per 32 along K, N(0,0.02)", "bf16 N(0,1), quantised to MXFP8"
+        return {"metric": METRIC.replace("fp8", "mxfp4"), "value": record["tokens_per_s"], "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": record["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "mxfp4 x mxfp8", "data": "synthetic", "config": config, "clocks": sampler.stop(), "e2e": None,
+                "gpu_launches": int(lib.aklr_kernel_launch_count() - launches0),
+                "roofline": {"bound": "tensor", "achieved": record["tflops"], "peak": peak_fp8, "peak_kind": f"2 x bf16 burst, of {peak_kind}",
+                             "unit": "TFLOP/s", "frac": record["frac_of_fp8_peak"], "traffic": None, "detail": record},
+                "cpu_baseline": None}
+
     w1, s1, w2, s2 = wl.expert_weights(cfg, SEED, device)
     router_w = wl.router_weight(cfg, SEED, device)
     n_batches = 4
@@ -321,11 +521,11 @@ def main() -> None:
         batches.append((hidden, logits))
     bias = wl.router_inputs(cfg, 1, SEED + 1, device)[2]
     out = torch.empty((T, cfg.hidden), dtype=torch.bfloat16, device=device)
-    ws = Workspace(_config(T, cfg.hidden, cfg.inter, cfg.n_routed, routing, batches[0][1], bias, args.block_m), device)
+    ws = Workspace(_config(T, cfg.hidden, cfg.inter, cfg.n_routed, routing, batches[0][1], bias, args.block_m, variant=args.variant), device)
 
     def step(i):
         hidden, logits = batches[i % n_batches]
-        fused_moe_fp8(hidden, logits, bias, w1, s1, w2, s2, routing, out=out, workspace=ws, block_m=args.block_m)
+        fused_moe_fp8(hidden, logits, bias, w1, s1, w2, s2, routing, out=out, workspace=ws, block_m=args.block_m, variant=args.variant)
 
     sampler = ClockSampler(local_rank)
     for i in range(args.warmup):
@@ -346,33 +546,22 @@ def main() -> None:
     torch.cuda.synchronize()
     clocks = sampler.stop()
     launches = lib.aklr_kernel_launch_count() - launches0
-    total_ms = start.elapsed_time(stop)
-    ms_per_step = total_ms / args.steps
+    ms_per_step = start.elapsed_time(stop) / args.steps
     ws.check_status()
-
-    stage_names = ["route", "sort", "quant", "gate_up", "down", "combine"]
-    stage_ms = [0.0] * 6
-    buf = (ctypes.c_float * 6)()
-    for i in range(args.steps):
-        _lib.check(lib.aklr_profile_read(i, buf))
-        for j in range(6):
-            stage_ms[j] += buf[j] / args.steps
+    stage_ms = read_stage_ms(lib, args.steps)
     lib.aklr_profile_begin(0)
 
     # ---- roofline of the dominant kernel (gate_up grouped GEMM): algorithmic bytes / its time ----
-    ids = ws.topk_ids()
-    experts_hit = distinct_experts(ids)
+    experts_hit = distinct_experts(ws.topk_ids())
     routes = T * cfg.routes_per_token
     h, i_dim = cfg.hidden, cfg.inter
     gate_up_bytes = experts_hit * (2 * i_dim * h + 4 * (2 * i_dim // 128) * (h // 128)) + routes * h + routes * (h // 128) * 4 + routes * i_dim
     down_bytes = experts_hit * (h * i_dim + 4 * (h // 128) * (i_dim // 128)) + routes * i_dim + routes * h * 2
-    peak, peak_kind = measured_peak_hbm()
     achieved = gate_up_bytes / (stage_ms[3] * 1e-3) / 1e9
     flops, layer_bytes = wl.roofline_work(cfg, T, experts_hit)
     token_major = ws.layout.block_m == 128
-    # DRAM bytes of this kernel per launch: ncu (dram__bytes_read + dram__bytes_write) on the small
-    # capture of the same kernel divided by that capture's algorithmic bytes, times this launch's
-    # algorithmic bytes (traffic grows with the weights streamed; see profiles/)
+    # DRAM bytes of this launch: the ratio measured by ncu on a smaller case of the same kernel times
+    # this launch's algorithmic bytes (the traffic grows with the weights streamed)
     traffic_ratio = TRAFFIC_PER_ALGORITHMIC_BYTE["prefill" if token_major else "decode"]
     roofline = {
         "kernel": ("grouped_gemm_prefill_kernel<gate_up>" if token_major else "grouped_gemm_kernel<gate_up>")
@@ -389,7 +578,7 @@ def main() -> None:
         "algorithmic_bytes_per_launch": gate_up_bytes,
         "ms_per_launch": stage_ms[3],
         "tflops": routes * 4 * h * i_dim / (stage_ms[3] * 1e-3) / 1e12,
-        "stage_ms": dict(zip(stage_names, stage_ms)),
+        "stage_ms": dict(zip(STAGES, stage_ms)),
         "down": {
             "achieved": down_bytes / (stage_ms[4] * 1e-3) / 1e9,
             "frac": down_bytes / (stage_ms[4] * 1e-3) / 1e9 / peak,
@@ -403,18 +592,36 @@ def main() -> None:
             "experts_hit": experts_hit,
         },
     }
+    line = {
+        "metric": METRIC,
+        "value": T / (ms_per_step * 1e-3),
+        "unit": UNIT,
+        "n_gpus": 1,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": ms_per_step,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "fp8_e4m3",
+        "data": "synthetic",
+        "config": workload_config(cfg, args),
+        "clocks": clocks,
+        "e2e": None,
+        "gpu_launches": int(launches),
+        "roofline": roofline,
+        "cpu_baseline": None,
+    }
+    if args.headline_only:
+        return line
 
-    e2e = None
     if not args.no_e2e:
         # ---- end to end through the op API from pinned host buffers --------------------------------
-        host_hidden = [b[0].cpu().pin_memory() for b in batches]
-        host_out = torch.empty((T, cfg.hidden), dtype=torch.bfloat16).pin_memory()
-        dev_hidden = torch.empty_like(batches[0][0])
-        ops.init()
-
         # Three streams, two buffers each way: step i's H2D overlaps step i-1's compute and step
         # i-2's D2H, as a serving loop would run it.  Every step still copies its own inputs in and
         # its own result out inside the timed region.
+        host_hidden = [b[0].cpu().pin_memory() for b in batches]
+        ops.init()
         copy_in, copy_out, compute = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
         dev_in = [torch.empty_like(batches[0][0]) for _ in range(2)]
         host_outs = [torch.empty((T, cfg.hidden), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
@@ -422,7 +629,6 @@ def main() -> None:
         in_free = [torch.cuda.Event() for _ in range(2)]
         out_ready = [torch.cuda.Event() for _ in range(2)]
         out_free = [torch.cuda.Event() for _ in range(2)]
-        results = [None, None]
         for ev in in_free + out_free:
             ev.record(compute)
 
@@ -435,23 +641,12 @@ def main() -> None:
             compute.wait_event(in_ready[k])
             compute.wait_event(out_free[k])
             result = ops.deepseek_v2_fp8_moe(
-                hidden_states=dev_in[k],
-                router_weight=router_w,
-                correction_bias=bias,
-                w1=w1,
-                w1_scale=s1,
-                w2=w2,
-                w2_scale=s2,
-                topk=cfg.topk,
-                num_expert_group=cfg.num_expert_group,
-                topk_group=cfg.topk_group,
-                renormalize=cfg.renormalize,
-                scoring_func="sigmoid",
-                routed_scaling_factor=cfg.routed_scaling_factor,
+                hidden_states=dev_in[k], router_weight=router_w, correction_bias=bias, w1=w1, w1_scale=s1, w2=w2, w2_scale=s2,
+                topk=cfg.topk, num_expert_group=cfg.num_expert_group, topk_group=cfg.topk_group, renormalize=cfg.renormalize,
+                scoring_func="sigmoid", routed_scaling_factor=cfg.routed_scaling_factor,
             )
             if not isinstance(result, torch.Tensor):
                 raise SystemExit(f"the op fell back: {result}")
-            results[k] = result
             in_free[k].record(compute)
             out_ready[k].record(compute)
             with torch.cuda.stream(copy_out):
@@ -473,80 +668,266 @@ def main() -> None:
         compute.wait_stream(copy_in)
         e1.record(compute)
         torch.cuda.synchronize()
-        e2e_clocks = e2e_sampler.stop()
         e2e_ms = e0.elapsed_time(e1) / args.steps
-        e2e = {
+        line["e2e"] = {
             "value": T / (e2e_ms * 1e-3),
             "unit": UNIT,
             "ms_per_step": e2e_ms,
             "h2d_bytes_per_step": T * cfg.hidden * 2,
             "d2h_bytes_per_step": T * cfg.hidden * 2,
             "api": "aklr_b200.ops.deepseek_v2_fp8_moe (router GEMM included); copies double-buffered on their own streams",
-            "clocks": e2e_clocks,
+            "clocks": e2e_sampler.stop(),
         }
+        del host_hidden, dev_in, host_outs
 
-    sweep = None
-    if args.sweep:
-        sweep = []
-        for t_sweep in (int(v) for v in args.sweep_tokens.split(",")):
-            bs = [wl.router_inputs(cfg, t_sweep, SEED + 50 + b, device)[:2] for b in range(8)]
-            o = torch.empty((t_sweep, cfg.hidden), dtype=torch.bfloat16, device=device)
-            wsx = Workspace(_config(t_sweep, cfg.hidden, cfg.inter, cfg.n_routed, routing, bs[0][1], bias), device)
-            for k in range(8):  # every batch once outside a capture
-                fused_moe_fp8(bs[k][0], bs[k][1], bias, w1, s1, w2, s2, routing, out=o, workspace=wsx)
-            torch.cuda.synchronize()
-            # one CUDA graph holding 8 layer calls on the rotating batches, replayed: the reference's
-            # protocol (graph replay) -- at T <= 16 the host cannot issue 7 launches as fast as they run
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                for k in range(8):
-                    fused_moe_fp8(bs[k][0], bs[k][1], bias, w1, s1, w2, s2, routing, out=o, workspace=wsx)
-            graph.replay()
-            n = 2 if t_sweep >= 1024 else 6
-            a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            hit = 0
-            torch.cuda.synchronize()
-            a.record()
-            for k in range(n):
-                graph.replay()
-            b_.record()
-            torch.cuda.synchronize()
-            n *= 8
-            for k in range(8):
-                hit += distinct_experts(orc_free_ids(cfg, bs[k][1], bias)) / 8
-            ms = a.elapsed_time(b_) / n
-            _, by = wl.roofline_work(cfg, t_sweep, hit)
-            fl = t_sweep * cfg.routes_per_token * cfg.flops_per_route
-            sweep.append(
-                {
-                    "tokens": t_sweep,
-                    "us_per_call": ms * 1e3,
-                    "tokens_per_s": t_sweep / (ms * 1e-3),
-                    "experts_hit": hit,
-                    "frac_of_hbm_roofline": by / (peak * 1e9) / (ms * 1e-3),
-                    "tflops": fl / (ms * 1e-3) / 1e12,
-                    "block_m": wsx.layout.block_m,
-                    "timing": "cuda graph replay of 8 calls on rotating batches",
-                }
-            )
+    # ---- the headline again for two seconds: the clocks settle under the power cap ---------------
+    n_long = max(args.steps, int(2000.0 / ms_per_step) + 1)
+    long_sampler = ClockSampler(local_rank)
+    for i in range(3):
+        step(i)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    long_sampler.begin()
+    a.record()
+    for i in range(n_long):
+        step(i)
+    b.record()
+    torch.cuda.synchronize()
+    long_clocks = long_sampler.stop()
+    long_ms = a.elapsed_time(b) / n_long
+    ws.check_status()
+    line["sustained"] = {
+        "steps": n_long, "seconds": long_ms * n_long * 1e-3, "ms_per_step": long_ms, "tokens_per_s": T / (long_ms * 1e-3),
+        "clocks": long_clocks, "ms_times_mhz": long_ms * long_clocks["sm_mhz"] if long_clocks.get("sm_mhz") else None,
+        "headline_ms_times_mhz": ms_per_step * clocks["sm_mhz"] if clocks.get("sm_mhz") else None,
+    }
 
-    cpu_baseline = None
+    # ---- other token counts of this configuration, then the other two FP8 configurations ----------
+    tokens_list = [int(v) for v in args.sweep_tokens.split(",")] if args.sweep_tokens else list(SWEEP_TOKENS["deepseek_v3"])
+    line["sweep"] = graph_sweep(cfg, tokens_list, (w1, s1, w2, s2), bias, device, peak, peak_fp8, fused_moe_fp8, args.block_m)
+    line["sweep_timing"] = "cuda graph replay of 8 calls on rotating batches; weights stream from HBM every call"
+    del w1, s1, w2, s2, ws, out, batches
+    torch.cuda.empty_cache()
+    line["models"] = {}
+    for name in ("mixtral", "qwen3"):
+        other = wl.CONFIGS[name]
+        weights = wl.expert_weights(other, SEED, device)
+        line["models"][name] = {
+            "workload": f"{name} widths: hidden {other.hidden}, intermediate {other.inter}, {other.n_routed} experts, softmax top-{other.topk}"
+                        + (", " + wl.zipf_note() if other.zipf_s > 0 else ""),
+            "sweep": graph_sweep(other, SWEEP_TOKENS[name], weights, None, device, peak, peak_fp8, fused_moe_fp8),
+        }
+        del weights
+        torch.cuda.empty_cache()
+    line["mxfp4"] = bench_mxfp4_record(cfg, 8192, min(args.steps, 10), 3, device, lib, peak, peak_fp8)
+    torch.cuda.empty_cache()
+
     if not args.no_cpu_baseline:
-        sample, cpu_steps = 2, 2
-        v, elapsed, cores = time_cpu_oracle(cfg, T, sample, cpu_steps, 1)
-        cpu_baseline = {
-            "value": v,
-            "unit": UNIT,
-            "cores": cores,
-            "kind": "port",
-            "sample": f"{cpu_steps} calls of {sample} tokens ({elapsed:.1f} s), expert weights already in host memory",
-        }
+        cpu = CpuPath(cfg)
+        cpu_steps = 3
+        value, elapsed = cpu.time_steps(CPU_SAMPLE_TOKENS, cpu_steps, 1)
+        line["cpu_baseline"] = cpu_record(cpu, value, elapsed, cpu_steps, CPU_SAMPLE_TOKENS)
+        line["cpu_baseline"]["full_batch_estimate"] = cpu.full_batch_estimate(T)
+    return line
 
+
+# --------------------------------------------------------------------------------------------------
+# GPU arm, N > 1: expert parallelism
+# --------------------------------------------------------------------------------------------------
+def ep_parity(cfg, layer, hidden, logits, bias, mx, device, n_check=4):
+    """Rank 0: ``n_check`` of its own tokens through ``layer.forward`` (all ranks take part in the call)
+    against the CPU oracle.  Expert weights are seeded per expert, so the experts those tokens hit are
+    drawn again here, whichever rank holds them."""
+    from oracle import moe_oracle as orc
+
+    out = layer.forward(hidden, logits, bias)
+    torch.cuda.synchronize()
+    if layer.rank != 0:
+        return None
+    n_tokens = hidden.shape[0]
+    loudest = int(out.float().abs().amax(dim=1).argmax())
+    wanted = [0, n_tokens - 1, loudest, n_tokens // 2, n_tokens // 3, 1]
+    sample = torch.tensor(sorted(list(dict.fromkeys(t for t in wanted if 0 <= t < n_tokens))[:n_check]))
+    ids, w = orc.grouped_sigmoid_topk(logits[sample.to(device)].cpu().float(), bias.cpu().float(), cfg.topk, cfg.num_expert_group, cfg.topk_group,
+                                      cfg.renormalize, cfg.routed_scaling_factor)
+    ids, w = orc.with_shared_slot(ids, w, cfg.n_routed)
+    draw = wl.mx_expert_weights if mx else wl.expert_weights
+    cache = {}
+
+    class Lazy:
+        def __init__(self, which):
+            self.which = which
+
+        def __getitem__(self, e):
+            if e not in cache:
+                cache[e] = tuple(t[0].cpu() for t in draw(cfg, SEED, device, experts=[e]))
+            return cache[e][self.which]
+
+    x = hidden[sample.to(device)].cpu()
+    ref = orc.mx_experts(x, ids, w, *(Lazy(i) for i in range(4)), act_bits=8) if mx else orc.fp8_experts(x, ids, w, *(Lazy(i) for i in range(4)))
+    gates = orc.output_gates(out[sample.to(device)].cpu(), ref)
+    gates["tokens"] = int(sample.numel())
+    gates["passed"] = bool(orc.gates_pass(gates))
+    gates["against"] = "cpu oracle on rank 0's sampled tokens, experts drawn again from their seeds"
+    return gates
+
+
+def bench_ep(args, cfg, rank, world, device, lib):
+    """Every rank holds n_routed/N routed experts + the shared expert and ``args.tokens`` tokens of its own
+    (weak scaling).  Rank 0 returns the JSON line."""
+    import torch.distributed as dist
+
+    from aklr_b200 import _lib
+    from aklr_b200.ep import CudaKernels, ExpertParallelMoE
+    from aklr_b200.moe import router_logits
+
+    if cfg.n_routed % world:
+        raise SystemExit(f"{cfg.n_routed} routed experts do not split over {world} ranks")
+    n_local = cfg.n_routed // world
+    mine = list(range(rank * n_local, (rank + 1) * n_local)) + list(range(cfg.n_routed, cfg.n_experts))
+    routing = routing_of(cfg)
+    peak, peak_fp8, peak_kind = measured_peaks()
+    bias = wl.router_inputs(cfg, 1, SEED + 1, device)[2]
+    router_w = wl.router_weight(cfg, SEED, device)
+
+    def timed(fn, steps, before_stop=None):
+        dist.barrier()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(steps):
+            fn(i)
+        if before_stop is not None:
+            before_stop()
+        stop.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        ms = torch.tensor([start.elapsed_time(stop)], device=device)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)  # the slowest rank's device time
+        return float(ms) / steps
+
+    def leg(mx: bool, tokens: int, steps: int, with_e2e: bool):
+        w1, s1, w2, s2 = (wl.mx_expert_weights if mx else wl.expert_weights)(cfg, SEED, device, experts=mine)
+        layer = ExpertParallelMoE(routing, w1, s1, w2, s2, rank, world, kernels=CudaKernels("mxfp4" if mx else "fp8"))
+        n_batches = 4
+        batches = [wl.router_inputs(cfg, tokens, SEED + 1 + 97 * rank + b, device)[:2] for b in range(n_batches)]
+        parity = ep_parity(cfg, layer, batches[0][0], batches[0][1], bias, mx, device)
+        verdict = torch.tensor([1 if (parity is None or parity["passed"]) else 0], device=device)
+        dist.all_reduce(verdict, op=dist.ReduceOp.MIN)
+        if int(verdict) == 0:
+            if rank == 0:
+                print(f"bench: expert-parallel output failed the parity gates: {parity}", file=sys.stderr)
+            raise SystemExit(3)
+
+        def step(i):
+            hidden, logits = batches[i % n_batches]
+            return layer.forward(hidden, logits, bias)
+
+        sampler = ClockSampler(device.index) if rank == 0 else None
+        for i in range(args.warmup):
+            step(i)
+        torch.cuda.synchronize()
+        lib.aklr_profile_begin(0 if mx else 2 * steps)
+        launches0 = lib.aklr_kernel_launch_count()
+        if sampler:
+            sampler.begin()
+        ms_per_step = timed(lambda i: step(args.warmup + i), steps)
+        clocks = sampler.stop() if sampler else None
+        launches = lib.aklr_kernel_launch_count() - launches0
+        # stage times of the routed-expert calls (every second recorded call; the other is the shared expert)
+        stage_ms = [0.0] * 6 if mx else read_stage_ms(lib, steps, first=1, stride=2)
+        lib.aklr_profile_begin(0)
+        # rows this rank's experts received and the experts among them that were hit, counted on the last batch
+        ids = device_ids(cfg, batches[0][1], bias)[:, : cfg.topk].contiguous()
+        gathered = [torch.empty_like(ids) for _ in range(world)]
+        dist.all_gather(gathered, ids)
+        all_ids = torch.cat(gathered).flatten()
+        local = all_ids[(all_ids >= rank * n_local) & (all_ids < (rank + 1) * n_local)]
+        rows_received, experts_hit = int(local.numel()), int(torch.unique(local).numel())
+        record = {"ms_per_step": ms_per_step, "clocks": clocks, "launches": int(launches), "stage_ms": dict(zip(STAGES, stage_ms)),
+                  "parity": parity, "rows_received_rank0": rows_received, "experts_hit_rank0": experts_hit}
+
+        if with_e2e:
+            # End to end from pinned host buffers through the same surface as one GPU: hidden states in,
+            # router GEMM on the device, layer, output back to the host.  Two buffers each way and two
+            # copy streams; step i's input copy is enqueued before the host blocks on step i's counts.
+            host = [h.cpu().pin_memory() for h, _ in batches]
+            dev_hidden = [torch.empty_like(batches[0][0]) for _ in range(2)]
+            host_out = [torch.empty((tokens, cfg.hidden), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+            copy_in, copy_out, compute = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
+            in_ready = [torch.cuda.Event() for _ in range(2)]
+            in_free = [torch.cuda.Event() for _ in range(2)]
+            out_free = [torch.cuda.Event() for _ in range(2)]
+
+            def enqueue_input(i):
+                k = i & 1
+                with torch.cuda.stream(copy_in):
+                    copy_in.wait_event(in_free[k])  # the step that last read this buffer is past it
+                    dev_hidden[k].copy_(host[i % n_batches], non_blocking=True)
+                    in_ready[k].record(copy_in)
+
+            def e2e_step(i):
+                k = i & 1
+                if i == 0:
+                    enqueue_input(0)
+                compute.wait_event(in_ready[k])
+                enqueue_input(i + 1)  # the next step's copy is in the queue before this step's host read
+                result = layer.forward(dev_hidden[k], router_logits(dev_hidden[k], router_w), bias)
+                in_free[k].record(compute)
+                done = torch.cuda.Event()
+                done.record(compute)
+                with torch.cuda.stream(copy_out):
+                    copy_out.wait_event(done)
+                    copy_out.wait_event(out_free[k])
+                    host_out[k].copy_(result, non_blocking=True)
+                    result.record_stream(copy_out)
+                    out_free[k].record(copy_out)
+
+            def drain():
+                compute.wait_stream(copy_out)
+                compute.wait_stream(copy_in)
+
+            for ev in in_free + out_free:
+                ev.record(compute)
+            for i in range(args.warmup):
+                e2e_step(i)
+            drain()
+            torch.cuda.synchronize()
+            for ev in in_free + out_free:
+                ev.record(compute)
+            record["e2e_ms"] = timed(e2e_step, steps, before_stop=drain)
+
+            # the same copies with no compute between them, all ranks at once: what the box's host memory
+            # and PCIe links allow for this pattern
+            def copy_only(i):
+                k = i & 1
+                with torch.cuda.stream(copy_in):
+                    dev_hidden[k].copy_(host[i % n_batches], non_blocking=True)
+                with torch.cuda.stream(copy_out):
+                    host_out[k].copy_(dev_hidden[k], non_blocking=True)
+
+            for i in range(3):
+                copy_only(i)
+            drain()
+            record["copy_only_ms"] = timed(copy_only, steps, before_stop=drain)
+        return record
+
+    fp8 = leg(False, args.tokens, args.steps, not args.no_e2e)
+    torch.cuda.empty_cache()
+    mxfp4 = None if args.headline_only else leg(True, 8192, min(args.steps, 10), False)
+    if rank != 0:
+        return None
+
+    tokens, ms_per_step, stage_ms = args.tokens, fp8["ms_per_step"], [fp8["stage_ms"][s] for s in STAGES]
+    h, inter = cfg.hidden, cfg.inter
+    rows, hit = fp8["rows_received_rank0"], fp8["experts_hit_rank0"]
+    gate_up_bytes = hit * (2 * inter * h + 4 * (2 * inter // 128) * (h // 128)) + rows * (h + 4 * (h // 128) + inter)
+    achieved = gate_up_bytes / (stage_ms[3] * 1e-3) / 1e9 if stage_ms[3] > 0 else 0.0
     line = {
         "metric": METRIC,
-        "value": T / (ms_per_step * 1e-3),
+        "value": world * tokens / (ms_per_step * 1e-3),
         "unit": UNIT,
-        "n_gpus": 1,
+        "n_gpus": world,
         "steps": args.steps,
         "warmup": args.warmup,
         "ms_per_step": ms_per_step,
@@ -556,150 +937,51 @@ def main() -> None:
         "dtype": "fp8_e4m3",
         "data": "synthetic",
         "config": workload_config(cfg, args),
-        "clocks": clocks,
-        "e2e": e2e,
-        "gpu_launches": int(launches),
-        "roofline": roofline,
-        "cpu_baseline": cpu_baseline,
-    }
-    if sweep is not None:
-        line["sweep"] = sweep
-    print(json.dumps(line), flush=True)
-
-
-def bench_mxfp4(args, cfg, routing, device, lib):
-    """The same layer with MXFP4 expert weights and MXFP8 activations (one GPU): extra measurement,
-    printed as one JSON line of the same shape with ``config.weights`` saying so."""
-    from aklr_b200 import _lib
-    from aklr_b200.moe import Workspace, _config, fused_moe_mxfp4
-
-    T = args.tokens
-    w1, s1, w2, s2 = wl.mx_expert_weights(cfg, SEED, device)
-    bias = wl.router_inputs(cfg, 1, SEED + 1, device)[2]
-    batches = [wl.router_inputs(cfg, T, SEED + 1 + b, device)[:2] for b in range(4)]
-    out = torch.empty((T, cfg.hidden), dtype=torch.bfloat16, device=device)
-    ws = Workspace(_config(T, cfg.hidden, cfg.inter, cfg.n_routed, routing, batches[0][1], bias, 128), device)
-
-    def step(i):
-        hidden, logits = batches[i % 4]
-        fused_moe_mxfp4(hidden, logits, bias, w1, s1, w2, s2, routing, out=out, workspace=ws)
-
-    sampler = ClockSampler(device.index or 0)
-    for i in range(args.warmup):
-        step(i)
-    ws.check_status()
-    launches0 = lib.aklr_kernel_launch_count()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    lib.aklr_profile_begin(args.steps)
-    sampler.begin()
-    start.record()
-    for i in range(args.steps):
-        step(args.warmup + i)
-    stop.record()
-    torch.cuda.synchronize()
-    clocks = sampler.stop()
-    ms = start.elapsed_time(stop) / args.steps
-    stage_ms = [0.0] * 6
-    buf = (ctypes.c_float * 6)()
-    for i in range(args.steps):
-        _lib.check(lib.aklr_profile_read(i, buf))
-        for k in range(6):
-            stage_ms[k] += buf[k] / args.steps
-    lib.aklr_profile_begin(0)
-    experts_hit = distinct_experts(ws.topk_ids())
-    h, inter = cfg.hidden, cfg.inter
-    weight_bytes = experts_hit * (3 * h * inter // 2 + 3 * h * inter // 32)
-    flops = T * cfg.routes_per_token * cfg.flops_per_route
-    peak, kind = measured_peak_hbm()
-    config = workload_config(cfg, args)
-    config["weights"] = "mxfp4: e2m1 + e8m0 per 32 along K, N(0,0.02)"
-    config["activations"] = "bf16 N(0,1), quantised to MXFP8 (e4m3 + e8m0 per 32)"
-    print(json.dumps({
-        "metric": METRIC.replace("fp8", "mxfp4"), "value": T / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "mxfp4 x mxfp8", "data": "synthetic", "config": config, "clocks": clocks, "e2e": None,
-        "gpu_launches": int(lib.aklr_kernel_launch_count() - launches0),
-        "roofline": {"bound": "hbm" if weight_bytes / (peak * 1e9) > flops / 3.2e15 else "tensor",
-                     "achieved": weight_bytes / (ms * 1e-3) / 1e9, "peak": peak, "peak_kind": f"of {kind}", "unit": "GB/s",
-                     "frac": weight_bytes / (ms * 1e-3) / 1e9 / peak, "traffic": None, "tflops": flops / (ms * 1e-3) / 1e12,
-                     "note": "whole layer: weight bytes of the experts hit / layer time",
-                     "stage_ms": dict(zip(["route", "sort", "quant", "gate_up", "down", "combine"], stage_ms)),
-                     "gate_up_tflops": 2 * flops / 3 / (stage_ms[3] * 1e-3) / 1e12 if stage_ms[3] > 0 else None,
-                     "down_tflops": flops / 3 / (stage_ms[4] * 1e-3) / 1e12 if stage_ms[4] > 0 else None},
+        "clocks": fp8["clocks"],
+        "tflops": world * tokens * cfg.routes_per_token * cfg.flops_per_route / (ms_per_step * 1e-3) / 1e12,
+        "parity": fp8["parity"],
+        "e2e": None,
+        "gpu_launches": fp8["launches"],
+        "roofline": {
+            "kernel": "gate_up grouped GEMM over the rows rank 0's experts received",
+            "bound": "hbm",
+            "achieved": achieved,
+            "peak": peak,
+            "peak_kind": f"of {peak_kind}",
+            "unit": "GB/s",
+            "frac": achieved / peak,
+            "traffic": gate_up_bytes * TRAFFIC_PER_ALGORITHMIC_BYTE["prefill"],
+            "traffic_source": "ncu capture of a smaller case of the same kernel on one GPU, scaled by algorithmic bytes",
+            "algorithmic_bytes_per_launch": gate_up_bytes,
+            "ms_per_launch": stage_ms[3],
+            "tflops": rows * 4 * h * inter / (stage_ms[3] * 1e-3) / 1e12 if stage_ms[3] > 0 else None,
+            "stage_ms": fp8["stage_ms"],
+            "rows_received": rows,
+            "experts_hit": hit,
+            "note": "rows and experts counted from the routing of one batch of every rank (rank 0's share)",
+        },
         "cpu_baseline": None,
-    }), flush=True)
-
-
-# token counts the other FP8 configurations are quoted on
-OTHER_MODEL_TOKENS = {"mixtral": (1, 16, 64, 256, 1024, 4096), "qwen3": (1, 32, 256, 2048, 8192)}
-
-
-def bench_other_model(args, cfg, device, lib):
-    """Mixtral-8x7B or Qwen3-30B-A3B widths with softmax top-k routing (seeded logits; Qwen3's carry a
-    Zipf(1.1) popularity bias), one GPU: every token count as a CUDA graph of 8 layer calls on rotating
-    batches, replayed.  One JSON line; ``value`` is the largest token count's throughput."""
-    from aklr_b200.moe import Workspace, _config, fused_moe_fp8
-
-    routing = routing_of(cfg)
-    w1, s1, w2, s2 = wl.expert_weights(cfg, SEED, device)
-    peak, kind = measured_peak_hbm()
-    sampler = ClockSampler(device.index or 0)
-    launches0 = lib.aklr_kernel_launch_count()
-    sweep = []
-    sampler.begin()
-    for tokens in OTHER_MODEL_TOKENS[args.model]:
-        batches = [wl.router_inputs(cfg, tokens, SEED + 50 + b, device)[:2] for b in range(8)]
-        out = torch.empty((tokens, cfg.hidden), dtype=torch.bfloat16, device=device)
-        ws = Workspace(_config(tokens, cfg.hidden, cfg.inter, cfg.n_routed, routing, batches[0][1], None, args.block_m), device)
-        for hidden, logits in batches:  # every batch once outside a capture
-            fused_moe_fp8(hidden, logits, None, w1, s1, w2, s2, routing, out=out, workspace=ws, block_m=args.block_m)
-        ws.check_status()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            for hidden, logits in batches:
-                fused_moe_fp8(hidden, logits, None, w1, s1, w2, s2, routing, out=out, workspace=ws, block_m=args.block_m)
-        for _ in range(max(args.warmup, 3)):
-            graph.replay()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        start.record()
-        for _ in range(args.steps):
-            graph.replay()
-        stop.record()
-        torch.cuda.synchronize()
-        ms = start.elapsed_time(stop) / (args.steps * 8)
-        hit = sum(distinct_experts(orc_free_ids(cfg, logits, None)) for _, logits in batches) / 8
-        flops, nbytes = wl.roofline_work(cfg, tokens, hit)
-        t_hbm, t_tensor = nbytes / (peak * 1e9), flops / 3.2e15
-        sweep.append({
-            "tokens": tokens, "us_per_call": ms * 1e3, "tokens_per_s": tokens / (ms * 1e-3), "experts_hit": hit,
-            "frac_of_hbm_roofline": t_hbm / (ms * 1e-3), "tflops": flops / (ms * 1e-3) / 1e12,
-            "bound": "hbm" if t_hbm > t_tensor else "tensor", "block_m": ws.layout.block_m,
-        })
-    clocks = sampler.stop()
-    last = sweep[-1]
-    config = workload_config(cfg, args)
-    config["workload"] = f"{cfg.name} fp8 fused-moe layer, token counts {[s['tokens'] for s in sweep]}"
-    config["routing"] = f"softmax over the top-{cfg.topk} logits" + (", " + wl.zipf_note() if cfg.zipf_s > 0 else "")
-    config["timing"] = "cuda graph replay of 8 calls on rotating batches; weights stream from HBM every call"
-    print(json.dumps({
-        "metric": METRIC, "value": last["tokens_per_s"], "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
-        "ms_per_step": last["us_per_call"] * 1e-3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "fp8_e4m3", "data": "synthetic", "config": config, "clocks": clocks, "e2e": None,
-        "gpu_launches": int(lib.aklr_kernel_launch_count() - launches0),
-        "roofline": {"bound": last["bound"], "achieved": last["frac_of_hbm_roofline"] * peak, "peak": peak, "peak_kind": f"of {kind}",
-                     "unit": "GB/s", "frac": last["frac_of_hbm_roofline"], "traffic": None,
-                     "note": "whole layer at the largest token count: algorithmic bytes / layer time"},
-        "cpu_baseline": None, "sweep": sweep,
-    }), flush=True)
-
-
-def orc_free_ids(cfg, logits, bias):
-    """Routing ids of a batch computed by the routing kernel itself (for experts-hit counts)."""
-    from aklr_b200.moe import route
-
-    return route(logits, bias, routing_of(cfg))[0]
+    }
+    if "e2e_ms" in fp8:
+        line["e2e"] = {
+            "value": world * tokens / (fp8["e2e_ms"] * 1e-3),
+            "unit": UNIT,
+            "ms_per_step": fp8["e2e_ms"],
+            "h2d_bytes_per_step": tokens * cfg.hidden * 2,
+            "d2h_bytes_per_step": tokens * cfg.hidden * 2,
+            "api": "router GEMM + aklr_b200.ep.ExpertParallelMoE.forward per rank, from pinned host hidden states; copies on their own streams",
+            "copy_only_ms_per_step": fp8["copy_only_ms"],
+            "copy_only_note": "the same H2D + D2H per step on every rank at once with no compute: the floor this box's host memory and PCIe set",
+        }
+    if mxfp4 is not None:
+        t5 = 8192
+        line["mxfp4"] = {
+            "workload": f"deepseek_v3 widths, mxfp4 weights x mxfp8 activations, {t5} tokens per GPU, ep{world}",
+            "ms_per_step": mxfp4["ms_per_step"], "tokens_per_s": world * t5 / (mxfp4["ms_per_step"] * 1e-3),
+            "tflops": world * t5 * cfg.routes_per_token * cfg.flops_per_route / (mxfp4["ms_per_step"] * 1e-3) / 1e12,
+            "parity": mxfp4["parity"], "clocks": mxfp4["clocks"],
+        }
+    return json.dumps(line)
 
 
 if __name__ == "__main__":

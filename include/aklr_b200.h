@@ -72,7 +72,7 @@ typedef struct aklr_moe_config {
 /* aklr_moe_config::variant.  Each bit overrides one kernel choice the library otherwise makes by
  * itself, for this call only, so that two variants can be compared on the same inputs (the results
  * agree; the tests check it).  No counterpart in the reference. */
-#define AKLR_VARIANT_WEIGHT_MAJOR 1           /* full 128-token blocks through the weight-major (decode) GEMM */
+#define AKLR_VARIANT_WEIGHT_MAJOR 1           /* 128-token blocks: down projection through the weight-major (decode) GEMM */
 #define AKLR_VARIANT_CTA_PAIRS 2              /* token-major GEMMs as CTA pairs (cta_group::2, no multicast) */
 #define AKLR_VARIANT_SEPARATE_PROLOGUE 4      /* 1..8 tokens: routing and sort as two kernels, not one */
 #define AKLR_VARIANT_FULL_ACTIVATION_BOXES 8  /* MXFP4 GEMMs load all 128 activation rows of every block */
