@@ -85,6 +85,12 @@ SIGNATURES = {
     "aklr_ep_dispatch_meta": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p]),
     "aklr_moe_fp8_experts_prequant": (c_int32, [POINTER(MoeConfig)] + [c_void_p] * 9 + [c_void_p, c_size_t, c_void_p]),
     "aklr_ep_combine": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p]),
+    "aklr_ep_row_bytes": (c_int32, [c_int32, c_int32, c_int32]),
+    "aklr_ep_plan": (c_int32, [c_void_p, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p]),
+    "aklr_ep_pack": (c_int32, [c_void_p] * 5 + [c_int32] * 6 + [c_void_p, c_void_p, c_void_p, c_void_p]),
+    "aklr_ep_unpack_meta": (c_int32, [c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p]),
+    "aklr_moe_fp8_experts_rows": (c_int32, [POINTER(MoeConfig), c_void_p, c_int32, c_void_p, c_int32] + [c_void_p] * 7 + [c_void_p, c_size_t, c_void_p]),
+    "aklr_moe_mxfp4_experts_rows": (c_int32, [POINTER(MoeConfig), c_void_p, c_int32, c_void_p, c_int32] + [c_void_p] * 6 + [c_float, c_void_p, c_void_p, c_size_t, c_void_p]),
     "aklr_moe_route": (c_int32, [POINTER(MoeConfig)] + [c_void_p] * 5 + [c_void_p]),
     "aklr_moe_align": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32] + [c_void_p] * 5 + [c_void_p]),
     "aklr_moe_align_max_blocks": (c_int64, [c_int64, c_int64, c_int64]),

@@ -301,7 +301,7 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
                 int n_experts_global, const void* w1, const float* w1_scale, const void* w2,
                 const float* w2_scale, void* out, uint8_t* ws, cudaStream_t stream, int slot,
                 const uint8_t* q_in = nullptr, const float* scales_in = nullptr, void* rows_out = nullptr,
-                const aklr::RouteParams* route = nullptr) {
+                const aklr::RouteParams* route = nullptr, int q_in_stride = 0, int scales_in_stride = 0) {
   // q_in/scales_in: the rows arrive already quantised (expert-parallel receive side);
   // rows_out: write the weighted per-route rows there and skip the combine;
   // route: the routing has not run yet -- a decode batch does it and the sort in one kernel (the
@@ -356,6 +356,8 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   qp.block_m = l.block_m;
   qp.q_in = q_in;
   qp.scales_in = scales_in;
+  qp.q_in_stride = q_in_stride;
+  qp.scales_in_stride = scales_in_stride;
   if (!q_in && routes_per_token > 1 && c.n_tokens >= kQuantOncePerTokenFrom) {
     // A token's routes all carry the same quantised row: quantise every token once, then copy.
     // The per-route output rows are not written before the down projection, so their space
@@ -465,7 +467,7 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
                    int n_experts_global, const void* w1, const uint8_t* w1_scale, const void* w2,
                    const uint8_t* w2_scale, const aklr_mx_options& opt, void* out, uint8_t* ws, cudaStream_t stream,
                    const uint8_t* q_in = nullptr, const uint8_t* scales_in = nullptr, void* rows_out = nullptr,
-                   int slot = -1) {
+                   int slot = -1, int q_in_stride = 0, int scales_in_stride = 0) {
   using namespace aklr;
   const int routes_per_token = c.topk + c.n_shared;
   const int routes = c.n_tokens * routes_per_token;
@@ -505,6 +507,8 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   qp.routes_per_token = routes_per_token;
   qp.q_in = q_in;
   qp.scales_in = scales_in;
+  qp.q_in_stride = q_in_stride;
+  qp.scales_in_stride = scales_in_stride;
   if (!q_in && routes_per_token > 1 && c.n_tokens >= kQuantOncePerTokenFrom) {
     // quantise every token once (codes and row-major scale bytes parked in the space of the
     // per-route output rows, unused until the down projection), then copy per route
@@ -843,6 +847,117 @@ int aklr_moe_mxfp4_experts_prequant(const aklr_moe_config* cfg, const void* rows
   return run_mx_experts(*cfg, l, nullptr, expert_ids, weights, nullptr, cfg->n_routed, w1, w1_scale, w2, w2_scale,
                         clamp_only(swiglu_limit), nullptr, static_cast<uint8_t*>(workspace), stream,
                         static_cast<const uint8_t*>(rows_q), rows_scale, out_rows, slot);
+}
+
+int aklr_moe_fp8_experts_rows(const aklr_moe_config* cfg, const void* rows_q, int32_t rows_q_pitch, const float* rows_scale,
+                              int32_t rows_scale_pitch, const int32_t* topk_ids, const float* topk_weights, const void* w1,
+                              const float* w1_scale, const void* w2, const float* w2_scale, void* out, void* workspace,
+                              size_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  aklr_moe_workspace_layout l;
+  if (cfg && cfg->n_shared != 0) return fail(AKLR_ERR_BAD_ARGUMENT, "rows that arrive quantised have no shared slots: n_shared 0");
+  if (rows_q_pitch < 0 || rows_scale_pitch < 0 || rows_q_pitch % 16 != 0 || rows_scale_pitch % 4 != 0)
+    return fail(AKLR_ERR_BAD_ARGUMENT, "row pitches must be multiples of 16 (codes) and 4 (scales) bytes, or 0 for dense rows");
+  int rc = prepare(cfg, &l, workspace, workspace_bytes, stream);
+  if (rc) return rc;
+  if (cfg->n_tokens == 0) return AKLR_OK;
+  if (!rows_q || !rows_scale || !topk_ids || !topk_weights || !w1 || !w1_scale || !w2 || !w2_scale || !out)
+    return fail(AKLR_ERR_BAD_ARGUMENT, "NULL tensor argument");
+  if (reinterpret_cast<uintptr_t>(rows_q) % 16 != 0 || reinterpret_cast<uintptr_t>(rows_scale) % 4 != 0)
+    return fail(AKLR_ERR_BAD_ARGUMENT, "rows_q must be 16-byte aligned and rows_scale 4-byte aligned");
+  const int slot = profile_slot();
+  profile_mark(stream, slot, 0);
+  profile_mark(stream, slot, 1);
+  return run_experts(*cfg, l, nullptr, topk_ids, topk_weights, nullptr, cfg->n_routed, w1, w1_scale, w2, w2_scale, out,
+                     static_cast<uint8_t*>(workspace), stream, slot, static_cast<const uint8_t*>(rows_q), rows_scale, nullptr,
+                     nullptr, rows_q_pitch, rows_scale_pitch);
+}
+
+int aklr_moe_mxfp4_experts_rows(const aklr_moe_config* cfg, const void* rows_q, int32_t rows_q_pitch, const uint8_t* rows_scale,
+                                int32_t rows_scale_pitch, const int32_t* topk_ids, const float* topk_weights, const void* w1,
+                                const uint8_t* w1_scale, const void* w2, const uint8_t* w2_scale, float swiglu_limit, void* out,
+                                void* workspace, size_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!cfg) return fail(AKLR_ERR_BAD_ARGUMENT, "cfg is NULL");
+  if (cfg->n_shared != 0 || cfg->block_m != 128)
+    return fail(AKLR_ERR_BAD_ARGUMENT, "rows that arrive quantised: n_shared 0, block_m 128");
+  if (cfg->hidden % 256 != 0) return fail(AKLR_ERR_UNSUPPORTED_SHAPE, "the MXFP4 path needs hidden %% 256 == 0");
+  if (rows_q_pitch < 0 || rows_scale_pitch < 0 || rows_q_pitch % 16 != 0 || rows_scale_pitch % 4 != 0)
+    return fail(AKLR_ERR_BAD_ARGUMENT, "row pitches must be multiples of 16 (codes) and 4 (scales) bytes, or 0 for dense rows");
+  aklr_moe_workspace_layout l;
+  int rc = prepare(cfg, &l, workspace, workspace_bytes, stream);
+  if (rc) return rc;
+  if (cfg->n_tokens == 0) return AKLR_OK;
+  if (!rows_q || !rows_scale || !topk_ids || !topk_weights || !w1 || !w1_scale || !w2 || !w2_scale || !out)
+    return fail(AKLR_ERR_BAD_ARGUMENT, "NULL tensor argument");
+  if (reinterpret_cast<uintptr_t>(rows_q) % 16 != 0 || reinterpret_cast<uintptr_t>(rows_scale) % 4 != 0)
+    return fail(AKLR_ERR_BAD_ARGUMENT, "rows_q must be 16-byte aligned and rows_scale 4-byte aligned");
+  const int slot = profile_slot();
+  profile_mark(stream, slot, 0);
+  profile_mark(stream, slot, 1);
+  return run_mx_experts(*cfg, l, nullptr, topk_ids, topk_weights, nullptr, cfg->n_routed, w1, w1_scale, w2, w2_scale,
+                        clamp_only(swiglu_limit), out, static_cast<uint8_t*>(workspace), stream,
+                        static_cast<const uint8_t*>(rows_q), rows_scale, nullptr, slot, rows_q_pitch, rows_scale_pitch);
+}
+
+int32_t aklr_ep_row_bytes(int32_t hidden, int32_t topk, int32_t mx) {
+  const int scale_bytes = mx ? hidden / 32 : hidden / 128 * 4;
+  return (hidden + scale_bytes + 8 * topk + 15) / 16 * 16;
+}
+
+int aklr_ep_plan(const int32_t* topk_ids, int32_t n_tokens, int32_t topk, int32_t experts_per_rank, int32_t* first_rank,
+                 int32_t* position_of_route, void* stream) {
+  if (!topk_ids || !first_rank || !position_of_route) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
+  int rc = check_device();
+  if (rc) return rc;
+  aklr::EpPlanParams p{topk_ids, first_rank, position_of_route, n_tokens, topk, experts_per_rank};
+  rc = aklr::launch_ep_first_slots(p, static_cast<cudaStream_t>(stream));
+  if (rc) return fail(rc, "ep plan: %s", aklr_status_string(rc));
+  g_launches += n_tokens > 0;
+  return AKLR_OK;
+}
+
+int aklr_ep_pack(const void* tokens_q, const void* tokens_scale, const int32_t* sorted_ids, const int32_t* topk_ids,
+                 const float* topk_weights, int32_t n_send, int32_t n_tokens, int32_t topk, int32_t hidden,
+                 int32_t experts_per_rank, int32_t mx, const int32_t* n_send_device, void* packed,
+                 int32_t* position_of_route, void* stream) {
+  if (!tokens_q || !tokens_scale || !sorted_ids || !topk_ids || !topk_weights || !packed || !position_of_route)
+    return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
+  int rc = check_device();
+  if (rc) return rc;
+  aklr::EpPackParams p{};
+  p.tokens_q = static_cast<const uint8_t*>(tokens_q);
+  p.tokens_scale = static_cast<const uint8_t*>(tokens_scale);
+  p.sorted_ids = sorted_ids;
+  p.n_send_device = n_send_device;
+  p.topk_ids = topk_ids;
+  p.topk_weights = topk_weights;
+  p.packed = static_cast<uint8_t*>(packed);
+  p.position_of_route = position_of_route;
+  p.n_send = n_send;
+  p.n_tokens = n_tokens;
+  p.topk = topk;
+  p.hidden = hidden;
+  p.scale_bytes = mx ? hidden / 32 : hidden / 128 * 4;
+  p.row_bytes = aklr_ep_row_bytes(hidden, topk, mx);
+  p.experts_per_rank = experts_per_rank;
+  rc = aklr::launch_ep_pack(p, static_cast<cudaStream_t>(stream));
+  if (rc) return fail(rc, "ep pack: %s", aklr_status_string(rc));
+  g_launches += n_send > 0;
+  return AKLR_OK;
+}
+
+int aklr_ep_unpack_meta(const void* packed, int32_t n_rows, int32_t hidden, int32_t topk, int32_t mx, int32_t* topk_ids,
+                        float* topk_weights, void* stream) {
+  if (!packed || !topk_ids || !topk_weights) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
+  int rc = check_device();
+  if (rc) return rc;
+  const int scale_bytes = mx ? hidden / 32 : hidden / 128 * 4;
+  rc = aklr::launch_ep_unpack_meta(static_cast<const uint8_t*>(packed), n_rows, aklr_ep_row_bytes(hidden, topk, mx),
+                                   hidden + scale_bytes, topk, topk_ids, topk_weights, static_cast<cudaStream_t>(stream));
+  if (rc) return fail(rc, "ep unpack: %s", aklr_status_string(rc));
+  g_launches += n_rows > 0;
+  return AKLR_OK;
 }
 
 int aklr_ep_gather_quant_mxfp8(const void* hidden_states, const int32_t* sorted_ids, int32_t n_send, int32_t hidden,

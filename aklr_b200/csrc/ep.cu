@@ -26,6 +26,91 @@ int launch_ep_meta(const EpMetaParams& p, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
 }
 
+// ---- one row per (token, destination rank) ------------------------------------------------------
+// A token whose routes name several experts of one rank sends that rank ONE row; the rank runs all of
+// them and returns one row, their weighted sum.  first_rank[t, s] = rank of slot s when no earlier slot
+// of the token goes to the same rank, else -1: sorting these "pairs" by rank (moe_align, block 1) gives
+// the send order.  position_of_route starts at -1 everywhere; pack fills in the sent slots.
+__global__ void __launch_bounds__(256) ep_first_slots_kernel(EpPlanParams p) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= p.n_tokens) return;
+  const int32_t* ids = p.topk_ids + static_cast<size_t>(t) * p.topk;
+  for (int s = 0; s < p.topk; ++s) {
+    const int e = ids[s];
+    int rank = e >= 0 ? e / p.experts_per_rank : -1;
+    for (int q = 0; q < s && rank >= 0; ++q)
+      if (ids[q] >= 0 && ids[q] / p.experts_per_rank == rank) rank = -1;
+    p.first_rank[static_cast<size_t>(t) * p.topk + s] = rank;
+    p.position_of_route[static_cast<size_t>(t) * p.topk + s] = -1;
+  }
+}
+
+int launch_ep_first_slots(const EpPlanParams& p, cudaStream_t stream) {
+  if (p.n_tokens == 0) return AKLR_OK;
+  if (p.topk < 1 || p.topk > 32 || p.experts_per_rank < 1) return AKLR_ERR_BAD_ARGUMENT;
+  ep_first_slots_kernel<<<(p.n_tokens + 255) / 256, 256, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+}
+
+// Send row i = token t's quantised row, its scales, and for each of the token's slots the expert id local
+// to the destination rank (or -1 when the slot goes elsewhere) with its weight: one buffer, one all-to-all.
+// Row layout: [hidden codes][scale_bytes scales][topk int32 ids][topk float weights], padded to row_bytes.
+__global__ void __launch_bounds__(256) ep_pack_kernel(EpPackParams p) {
+  const int vec_per_row = p.hidden >> 4;
+  const int scale_words = p.scale_bytes >> 2;
+  const int n_send = p.n_send_device ? min(__ldg(p.n_send_device), p.n_send) : p.n_send;
+  for (int i = blockIdx.x; i < n_send; i += gridDim.x) {
+    const int rid = p.sorted_ids[i];
+    if (rid < 0 || rid >= p.n_tokens * p.topk) continue;
+    const int t = rid / p.topk;
+    uint8_t* dst = p.packed + static_cast<size_t>(i) * p.row_bytes;
+    const uint4* src = reinterpret_cast<const uint4*>(p.tokens_q + static_cast<size_t>(t) * p.hidden);
+    for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) reinterpret_cast<uint4*>(dst)[v] = __ldg(src + v);
+    const uint32_t* ssrc = reinterpret_cast<const uint32_t*>(p.tokens_scale + static_cast<size_t>(t) * p.scale_bytes);
+    for (int v = threadIdx.x; v < scale_words; v += blockDim.x)
+      reinterpret_cast<uint32_t*>(dst + p.hidden)[v] = __ldg(ssrc + v);
+    if (threadIdx.x < p.topk) {
+      const int s = threadIdx.x;
+      const int rank = p.topk_ids[rid] / p.experts_per_rank;
+      const int e = p.topk_ids[static_cast<size_t>(t) * p.topk + s];
+      const bool here = e >= 0 && e / p.experts_per_rank == rank;
+      int32_t* meta = reinterpret_cast<int32_t*>(dst + p.hidden + p.scale_bytes);
+      meta[s] = here ? e % p.experts_per_rank : -1;
+      reinterpret_cast<float*>(meta + p.topk)[s] = here ? p.topk_weights[static_cast<size_t>(t) * p.topk + s] : 0.0f;
+    }
+    if (threadIdx.x == 0) p.position_of_route[rid] = i;
+  }
+}
+
+int launch_ep_pack(const EpPackParams& p, cudaStream_t stream) {
+  if (p.n_send == 0) return AKLR_OK;
+  if (p.hidden % 16 != 0 || p.scale_bytes % 4 != 0 || p.row_bytes % 16 != 0 || p.topk < 1 || p.topk > 32 ||
+      p.row_bytes < p.hidden + p.scale_bytes + 8 * p.topk)
+    return AKLR_ERR_BAD_ARGUMENT;
+  const int grid = p.n_send < 148 * 16 ? p.n_send : 148 * 16;
+  ep_pack_kernel<<<grid, 256, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+}
+
+// Receiver: the ids and weights of the rows received, as the [rows, topk] tables the expert call takes.
+__global__ void __launch_bounds__(256) ep_unpack_meta_kernel(const uint8_t* packed, int n_rows, int row_bytes, int meta_offset,
+                                                             int topk, int32_t* ids, float* weights) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_rows * topk) return;
+  const int row = i / topk, s = i - row * topk;
+  const int32_t* meta = reinterpret_cast<const int32_t*>(packed + static_cast<size_t>(row) * row_bytes + meta_offset);
+  ids[i] = meta[s];
+  weights[i] = reinterpret_cast<const float*>(meta + topk)[s];
+}
+
+int launch_ep_unpack_meta(const uint8_t* packed, int n_rows, int row_bytes, int meta_offset, int topk, int32_t* ids,
+                          float* weights, cudaStream_t stream) {
+  if (n_rows == 0) return AKLR_OK;
+  if (meta_offset % 4 != 0 || row_bytes % 4 != 0 || topk < 1) return AKLR_ERR_BAD_ARGUMENT;
+  ep_unpack_meta_kernel<<<(n_rows * topk + 255) / 256, 256, 0, stream>>>(packed, n_rows, row_bytes, meta_offset, topk, ids, weights);
+  return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+}
+
 // out[t] = bf16( sum_k rows[position(t,k)] + shared[t] ), float32 sum in slot order, shared last:
 // the order of the single-GPU combine, so both give the same bits.
 __global__ void __launch_bounds__(256) ep_combine_kernel(EpCombineParams p) {

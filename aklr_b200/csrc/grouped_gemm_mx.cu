@@ -30,23 +30,6 @@
 
 namespace aklr {
 
-#ifdef AKLR_GEMM_TIMING
-// Development aid, compiled only on request: cycles per role of CTA 0.
-// [0] mma wait acc_empty [1] mma wait full [2] mma wait sf_full [3] mma issue [4] sf wait empty [5] sf stage
-// [6] epi wait acc_full [7] epilogue [8] kblocks [9] tiles
-__device__ long long g_mx_timing[2][16];
-#define MT(slot, expr)                                         \
-  do {                                                         \
-    const long long t_begin_ = clock64();                      \
-    expr;                                                      \
-    if (blockIdx.x == 0) tacc[slot] += clock64() - t_begin_;   \
-  } while (0)
-#else
-#define MT(slot, expr) \
-  do {                 \
-    expr;              \
-  } while (0)
-#endif
 
 namespace {
 
@@ -248,22 +231,16 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
       const uint64_t sfa0 = sf_desc(base + kABytes + kBBytes);
       uint32_t step = 0;  // (stage * kStageBytes) >> 4, added to the address field of each descriptor
       bool ok = true;
-#ifdef AKLR_GEMM_TIMING
-      long long tacc[16] = {0};
-#endif
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_no) {
         // the single accumulator must have been read out by the previous tile's epilogue
         bool got;
-        MT(0, got = mbar_wait(acc_empty, (tile_no & 1) ^ 1, abort_flag, p.status, 22));
+        got = mbar_wait(acc_empty, (tile_no & 1) ^ 1, abort_flag, p.status, 22);
         if (!got) break;
         for (int kb = 0; kb < KB; ++kb, ++it) {
-          MT(1, got = mbar_wait(&full[s], ph, abort_flag, p.status, 23));
+          got = mbar_wait(&full[s], ph, abort_flag, p.status, 23);
           if (!got) { ok = false; break; }
-          MT(2, got = mbar_wait(&sf_full[s], ph, abort_flag, p.status, 24));
+          got = mbar_wait(&sf_full[s], ph, abort_flag, p.status, 24);
           if (!got) { ok = false; break; }
-#ifdef AKLR_GEMM_TIMING
-          const long long t_issue = clock64();
-#endif
           tc_fence_after_sync();
           const uint64_t sfa = sfa0 + step;
           tmem_cp_32x128b_warpx4(tmem_base + kSfaCol, sfa);
@@ -275,21 +252,11 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
             umma_mx(tmem_base, da + 2 * k, db + 2 * k, mx_idesc(kBN, k), tmem_base + kSfaCol, tmem_base + kSfbCol,
                     (kb > 0 || k > 0) ? 1u : 0u);
           tc_commit(&empty[s]);
-#ifdef AKLR_GEMM_TIMING
-          tacc[3] += clock64() - t_issue;
-#endif
           step += kStageBytes >> 4;
           if (++s == S) { s = 0; ph ^= 1; step = 0; }
         }
         if (ok) tc_commit(acc_full);
       }
-#ifdef AKLR_GEMM_TIMING
-      if (blockIdx.x == 0) {
-        for (int i = 0; i <= 3; ++i) g_mx_timing[GATE_UP][i] = tacc[i];
-        g_mx_timing[GATE_UP][8] = it;
-        g_mx_timing[GATE_UP][9] = tile_no;
-      }
-#endif
     }
   } else if (warp >= 10) {
     // ------------------- scale-factor staging, running ahead of the MMA warp -------------------
@@ -298,9 +265,6 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
     const int sw = warp - 10;
     const int KS = p.k >> 5;  // scale bytes per weight row
     uint32_t it0 = 0;         // K-blocks before this tile
-#ifdef AKLR_GEMM_TIMING
-    long long tacc[16] = {0};
-#endif
     bool ok = true;
     if (tile_regs) {
       // A tile's weight scales are 256 rows x KS (<= 64) contiguous bytes.  Fetching one 4-byte word
@@ -355,11 +319,8 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
         for (int kb = 0; kb < 16; ++kb) {
           if (kb < KB && ok) {
             bool got;
-            MT(4, got = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 25));
+            got = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 25);
             if (!got) ok = false;
-#ifdef AKLR_GEMM_TIMING
-            const long long t_stage = clock64();
-#endif
             uint8_t* sf = smem + s * kStageBytes + kABytes + kBBytes;
             if (sw == 0) *reinterpret_cast<uint4*>(sf + lane * 16) = aq[kb & 3];
 #pragma unroll
@@ -375,9 +336,6 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
             if (sw == 0) aq_load(aq[kb & 3]);
             if ((kb & 3) == 3 && wb_next) load_piece(wb_next, kb >> 2);
             if (++s == S) { s = 0; ph ^= 1; }
-#ifdef AKLR_GEMM_TIMING
-            tacc[5] += clock64() - t_stage;
-#endif
           }
         }
       }
@@ -415,11 +373,8 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
             const int s = it % S;
             const uint32_t ph = (it / S) & 1;
             bool got;
-            MT(4, got = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 25));
+            got = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 25);
             if (!got) ok = false;
-#ifdef AKLR_GEMM_TIMING
-            const long long t_stage = clock64();
-#endif
             uint8_t* sf = smem + s * kStageBytes + kABytes + kBBytes;
             *reinterpret_cast<uint4*>(sf + lane * 16) = aq[d];
 #pragma unroll
@@ -434,17 +389,10 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
               for (int q = 0; q < 8; ++q) wq[d][q] = __ldg(reinterpret_cast<const uint32_t*>(wsf[q] + nk * 4));
               aq[d] = __ldg(reinterpret_cast<const uint4*>(xsf + nk * kSfaBytes) + lane);
             }
-#ifdef AKLR_GEMM_TIMING
-            tacc[5] += clock64() - t_stage;
-#endif
           }
         }
       }
     }
-#ifdef AKLR_GEMM_TIMING
-    if (blockIdx.x == 0 && sw == 0 && lane == 0)
-      for (int i = 4; i <= 5; ++i) g_mx_timing[GATE_UP][i] = tacc[i];
-#endif
   } else {
     // ------------------------------------ epilogue warps ---------------------------------------
     const int quarter = warp & 3;
@@ -454,9 +402,6 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     uint32_t tile_no = 0;
     bool bad = false;
-#ifdef AKLR_GEMM_TIMING
-    long long tacc[16] = {0};
-#endif
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_no) {
       if (epi_any(*abort_flag)) break;
       const int b = t / tiles_per_block, j = t - b * tiles_per_block;
@@ -472,12 +417,9 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
       // ---- epilogue: the whole K reduction is in TMEM ----
       {
         bool got;
-        MT(6, got = mbar_wait(acc_full, tile_no & 1, abort_flag, p.status, 26));
+        got = mbar_wait(acc_full, tile_no & 1, abort_flag, p.status, 26);
         if (!got) bad = true;
       }
-#ifdef AKLR_GEMM_TIMING
-      const long long t_epi = clock64();
-#endif
       tc_fence_after_sync();
       float acc[128];
       {
@@ -497,10 +439,6 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty);
-#ifdef AKLR_GEMM_TIMING
-      const long long t_loaded = clock64();
-      tacc[10] += t_loaded - t_epi;
-#endif
 
       const int rid = rid_s[row];
       if (GATE_UP) {
@@ -533,9 +471,6 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
             packed[g * 8 + i / 4] = cvt_e4m3x2(acc[g * 32 + i] * inv, acc[g * 32 + i + 1] * inv) |
                                     (static_cast<uint32_t>(cvt_e4m3x2(acc[g * 32 + i + 2] * inv, acc[g * 32 + i + 3] * inv)) << 16);
         }
-#ifdef AKLR_GEMM_TIMING
-        tacc[11] += clock64() - t_loaded;
-#endif
         if (rid >= 0 && !bad) {
           uint8_t* dst = p.out_q + static_cast<size_t>(b * kBM + row) * p.out_dim + j * 128 + half * 64;
 #pragma unroll
@@ -581,15 +516,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
           __syncwarp();
         }
       }
-#ifdef AKLR_GEMM_TIMING
-      tacc[7] += clock64() - t_epi;
-#endif
     }
-#ifdef AKLR_GEMM_TIMING
-    if (blockIdx.x == 0 && warp == 2 && lane == 0)
-      for (int i = 6; i <= 7; ++i) g_mx_timing[GATE_UP][i] = tacc[i];
-      for (int i = 10; i <= 11; ++i) g_mx_timing[GATE_UP][i] = tacc[i];
-#endif
   }
 
   tc_fence_before_sync();
@@ -675,6 +602,8 @@ __global__ void __launch_bounds__(256) gather_rows_mxfp8_kernel(MxQuantParams p)
   griddep_wait();
   const int vec_per_row = p.hidden >> 4;
   const int KB = p.hidden >> 7;
+  const size_t q_pitch = p.q_in_stride ? p.q_in_stride : p.hidden;
+  const size_t s_pitch = p.scales_in_stride ? p.scales_in_stride : KB * 4;
   const int n_rows = p.num_rows ? min(*p.num_rows, p.n_rows) : p.n_rows;
   for (int row0 = blockIdx.x * kGatherRows; row0 < n_rows; row0 += gridDim.x * kGatherRows) {
     if (threadIdx.x < kGatherRows) {
@@ -691,7 +620,7 @@ __global__ void __launch_bounds__(256) gather_rows_mxfp8_kernel(MxQuantParams p)
 #pragma unroll
       for (int r = 0; r < kGatherRows; ++r)
         if (src[r] >= 0)
-          val[r] = __ldg(reinterpret_cast<const uint4*>(p.q_in + static_cast<size_t>(src[r]) * p.hidden) + v);
+          val[r] = __ldg(reinterpret_cast<const uint4*>(p.q_in + static_cast<size_t>(src[r]) * q_pitch) + v);
 #pragma unroll
       for (int r = 0; r < kGatherRows; ++r)
         if (src[r] >= 0) reinterpret_cast<uint4*>(p.q + static_cast<size_t>(row0 + r) * p.hidden)[v] = val[r];
@@ -700,7 +629,7 @@ __global__ void __launch_bounds__(256) gather_rows_mxfp8_kernel(MxQuantParams p)
       const int r = i / KB, kb = i - r * KB;
       const int row = row0 + r;
       if (src_s[r] >= 0) {
-        const uint32_t word = __ldg(reinterpret_cast<const uint32_t*>(p.scales_in + static_cast<size_t>(src_s[r]) * (KB * 4)) + kb);
+        const uint32_t word = __ldg(reinterpret_cast<const uint32_t*>(p.scales_in + static_cast<size_t>(src_s[r]) * s_pitch) + kb);
         if (p.row_major_scales) {  // for transport to another rank: [row, hidden/32]
           *reinterpret_cast<uint32_t*>(p.scales + static_cast<size_t>(row) * (KB * 4) + kb * 4) = word;
         } else {
@@ -715,11 +644,6 @@ __global__ void __launch_bounds__(256) gather_rows_mxfp8_kernel(MxQuantParams p)
 
 }  // namespace
 
-#ifdef AKLR_GEMM_TIMING
-extern "C" int aklr_debug_read_mx_timing(long long* host32) {
-  return cudaMemcpyFromSymbol(host32, g_mx_timing, sizeof(g_mx_timing)) == cudaSuccess ? 0 : -3;
-}
-#endif
 
 int launch_gather_quant_mxfp8(const MxQuantParams& p, cudaStream_t stream) {
   if (p.hidden % 128 != 0) return AKLR_ERR_UNSUPPORTED_SHAPE;

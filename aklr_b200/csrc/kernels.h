@@ -61,6 +61,7 @@ struct GatherQuantParams {
   uint8_t* q;                 // [rows, hidden] e4m3
   float* scales;              // block_m == 0: [rows, hidden/128]; else [rows/block_m, hidden/128, block_m]
   int n_rows, hidden, routes_per_token, block_m;
+  int q_in_stride, scales_in_stride;  // gather_rows only: bytes between source rows (0: dense)
 };
 int launch_gather_quant_fp8(const GatherQuantParams& p, cudaStream_t stream);
 
@@ -122,6 +123,7 @@ struct MxQuantParams {
   const uint8_t* scales_in;   // their scale bytes [n, hidden/32]
   int n_rows, hidden, routes_per_token;
   int row_major_scales;       // write scales as [row, hidden/32] (for transport) instead
+  int q_in_stride, scales_in_stride;  // rows quantised before: bytes between source rows (0: dense)
 };
 int launch_gather_quant_mxfp8(const MxQuantParams& p, cudaStream_t stream);
 
@@ -172,6 +174,29 @@ struct EpMetaParams {
   int n_send, n_routes, experts_per_rank;
 };
 int launch_ep_meta(const EpMetaParams& p, cudaStream_t stream);
+
+struct EpPlanParams {
+  const int32_t* topk_ids;     // [n_tokens, topk] global expert ids (negative: no route)
+  int32_t* first_rank;         // [n_tokens, topk] destination rank of the first slot per (token, rank), else -1
+  int32_t* position_of_route;  // [n_tokens, topk] set to -1
+  int n_tokens, topk, experts_per_rank;
+};
+int launch_ep_first_slots(const EpPlanParams& p, cudaStream_t stream);
+
+struct EpPackParams {
+  const uint8_t* tokens_q;      // [n_tokens, hidden] e4m3, each token quantised once
+  const uint8_t* tokens_scale;  // [n_tokens, scale_bytes]
+  const int32_t* sorted_ids;    // [n_send] first slots (token * topk + slot) ordered by destination rank
+  const int32_t* n_send_device; // optional device count of rows to send (the host only knows the bound n_send)
+  const int32_t* topk_ids;      // [n_tokens, topk]
+  const float* topk_weights;    // [n_tokens, topk]
+  uint8_t* packed;              // [n_send, row_bytes]
+  int32_t* position_of_route;   // [n_tokens, topk]: send position of the first slots
+  int n_send, n_tokens, topk, hidden, scale_bytes, row_bytes, experts_per_rank;
+};
+int launch_ep_pack(const EpPackParams& p, cudaStream_t stream);
+int launch_ep_unpack_meta(const uint8_t* packed, int n_rows, int row_bytes, int meta_offset, int topk, int32_t* ids,
+                          float* weights, cudaStream_t stream);
 
 struct EpCombineParams {
   const void* rows;                  // [n_send, hidden] bf16, weighted, in send order

@@ -36,6 +36,8 @@ __global__ void __launch_bounds__(256) gather_rows_fp8_kernel(GatherQuantParams 
   griddep_wait();
   const int vec_per_row = p.hidden >> 4;
   const int groups_per_row = p.hidden >> 7;
+  const size_t q_pitch = p.q_in_stride ? p.q_in_stride : p.hidden;
+  const size_t s_pitch = p.scales_in_stride ? p.scales_in_stride : groups_per_row * sizeof(float);
   const int n_rows = p.num_rows ? min(*p.num_rows, p.n_rows) : p.n_rows;
   for (int row0 = blockIdx.x * kGatherRows; row0 < n_rows; row0 += gridDim.x * kGatherRows) {
     if (threadIdx.x < kGatherRows) {
@@ -52,7 +54,7 @@ __global__ void __launch_bounds__(256) gather_rows_fp8_kernel(GatherQuantParams 
 #pragma unroll
       for (int r = 0; r < kGatherRows; ++r)
         if (src[r] >= 0)
-          val[r] = __ldg(reinterpret_cast<const uint4*>(p.q_in + static_cast<size_t>(src[r]) * p.hidden) + v);
+          val[r] = __ldg(reinterpret_cast<const uint4*>(p.q_in + static_cast<size_t>(src[r]) * q_pitch) + v);
 #pragma unroll
       for (int r = 0; r < kGatherRows; ++r)
         if (src[r] >= 0)
@@ -63,7 +65,7 @@ __global__ void __launch_bounds__(256) gather_rows_fp8_kernel(GatherQuantParams 
       const int row = row0 + r;
       if (src_s[r] >= 0)
         p.scales[(static_cast<size_t>(row / p.block_m) * groups_per_row + grp) * p.block_m + row % p.block_m] =
-            __ldg(p.scales_in + static_cast<size_t>(src_s[r]) * groups_per_row + grp);
+            __ldg(reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(p.scales_in) + static_cast<size_t>(src_s[r]) * s_pitch) + grp);
     }
     __syncthreads();
   }

@@ -1,5 +1,5 @@
-"""Expert parallelism for the FP8 fused-MoE layer: tokens stay on their home rank, experts are
-sharded, NCCL all-to-alls carry routes out (FP8 rows + scales) and weighted bf16 rows back.
+"""Expert parallelism for the fused-MoE layer: tokens stay on their home rank, experts are sharded,
+one NCCL all-to-all carries quantised token rows out and one carries bf16 rows back.
 
 Ownership is the reference's (aklr/ops/mega_moe/contract.py:42-51, reference.py:25,38): with
 ``n_local`` routed experts per rank, global expert ``e`` is local expert ``e % n_local`` of rank
@@ -7,15 +7,23 @@ Ownership is the reference's (aklr/ops/mega_moe/contract.py:42-51, reference.py:
 stream while the dispatch is in flight.  No kernel waits on another rank: every exchange is a
 host-ordered collective whose payload lands in local HBM before a kernel reads it.
 
+What travels is one row per (token, destination rank), not one per route: a token whose routes name
+several experts of one rank sends that rank its quantised row once, with the list of (local expert,
+weight) pairs; the rank runs them all and returns ONE row, their weighted sum.  With DeepSeek-V3's
+group-limited routing (8 groups, 4 kept) a token reaches at most 4 of 8 ranks, so both all-to-alls
+carry half of what one row per route would.  The row, its scales and the pairs are one packed buffer
+(``RowLayout``), so a direction is one collective.
+
 One step of one rank is three phases, so that a test can drive several ranks in one process:
 
-    state = layer.prepare(hidden, logits, bias)          # route, order by rank, quantise, pack
-    received = comm.exchange(state.send, state.send_counts)
+    state = layer.prepare(hidden, logits, bias)          # route, plan, quantise, pack
+    received = exchange(state.packed, ...)               # all-to-all by destination rank
     rows = layer.compute(received)                       # local experts over the rows received
-    back = comm.exchange_back(rows, ...)
-    out = layer.finish(state, back)                      # weighted sum at home + shared experts
+    back = exchange back                                 # all-to-all, same splits reversed
+    out = layer.finish(state, back)                      # sum at home + shared experts
 
-``ExpertParallelMoE.forward`` runs them over ``torch.distributed``.
+``ExpertParallelMoE.forward`` runs them over ``torch.distributed``.  It reads the split sizes of the
+uneven all-to-all on the host once per step, so it cannot be captured in a CUDA graph.
 """
 
 from __future__ import annotations
@@ -27,7 +35,6 @@ import torch
 
 from aklr_b200 import _lib
 from aklr_b200.moe import (
-    FP8,
     Routing,
     Workspace,
     _config,
@@ -39,23 +46,38 @@ from aklr_b200.moe import (
 )
 
 
-@dataclasses.dataclass
-class Packed:
-    """What one rank sends: rows ordered by destination rank."""
+@dataclasses.dataclass(frozen=True)
+class RowLayout:
+    """Bytes of one travelling row: [hidden e4m3 codes][scales][topk int32 local expert ids][topk float32
+    weights], padded to 16 bytes.  Scales: float32 per 128 values (FP8 experts) or one e8m0 byte per 32
+    (MXFP4 experts).  ``aklr_ep_row_bytes`` computes the same size."""
 
-    rows_q: torch.Tensor      # uint8 view of e4m3 [n_send, H]
-    rows_scale: torch.Tensor  # float32 [n_send, H/128]
-    meta: torch.Tensor        # int32 [n_send, 2]: expert id on the destination, weight bits
-    counts: torch.Tensor      # int32 [world] rows per destination (device)
+    hidden: int
+    topk: int
+    mx: bool
+
+    @property
+    def scale_bytes(self) -> int:
+        return self.hidden // 32 if self.mx else self.hidden // 128 * 4
+
+    @property
+    def meta_offset(self) -> int:
+        return self.hidden + self.scale_bytes
+
+    @property
+    def row_bytes(self) -> int:
+        return (self.meta_offset + 8 * self.topk + 15) // 16 * 16
 
 
 @dataclasses.dataclass
 class StepState:
-    send: Packed
-    position_of_route: torch.Tensor
+    packed: torch.Tensor             # uint8 [capacity, row_bytes]; the first sum(counts) rows are sent
+    counts: torch.Tensor             # int32 [world] rows per destination rank (device)
+    position_of_route: torch.Tensor  # int32 [n_tokens * topk]: send position of a (token, rank)'s first slot, else -1
     shared_rows: torch.Tensor | None
     shared_done: torch.cuda.Event | None
     n_tokens: int
+    layout: RowLayout
 
 
 class CudaKernels:
@@ -70,16 +92,23 @@ class CudaKernels:
             raise ValueError(f"unknown expert format {fmt!r}")
         self.fmt, self.swiglu_limit = fmt, swiglu_limit
 
+    @property
+    def mx(self) -> bool:
+        return self.fmt == "mxfp4"
+
     def route(self, logits, bias, routing):
         return route(logits, bias, routing)
 
-    def order_by_rank(self, ids, n_local, world):
-        """(routes sorted by destination rank int32 [R], rows per rank int32 [world])."""
+    def plan(self, ids, n_local, world):
+        """(first slots sorted by destination rank int32 [T*K] -- the first sum(counts) entries count --,
+        rows per rank int32 [world], position_of_route int32 [T*K] filled with -1)."""
         lib = _lib.load()
         device = ids.device
+        n_tokens, topk = ids.shape
         n_routes = ids.numel()
-        n_experts = n_local * world
-        rank_of = (torch.arange(n_experts, dtype=torch.int32, device=device) // n_local).contiguous()
+        first_rank = torch.empty(n_routes, dtype=torch.int32, device=device)
+        position = torch.empty(n_routes, dtype=torch.int32, device=device)
+        _lib.check(lib.aklr_ep_plan(_ptr(ids), n_tokens, topk, n_local, _ptr(first_rank), _ptr(position), _stream()))
         sorted_ids = torch.empty(n_routes + world, dtype=torch.int32, device=device)
         block_rank = torch.empty(n_routes + world, dtype=torch.int32, device=device)
         counts = torch.empty(world, dtype=torch.int32, device=device)
@@ -87,71 +116,64 @@ class CudaKernels:
         scratch = torch.empty(max(1, (n_routes + 1023) // 1024) * world, dtype=torch.int32, device=device)
         _lib.check(
             lib.aklr_moe_align(
-                _ptr(ids), _ptr(rank_of), n_routes, world, n_experts, 1, _ptr(sorted_ids), _ptr(block_rank),
-                _ptr(counts), _ptr(num_blocks), _ptr(scratch), _stream(),
+                _ptr(first_rank), None, n_routes, world, world, 1, _ptr(sorted_ids), _ptr(block_rank), _ptr(counts),
+                _ptr(num_blocks), _ptr(scratch), _stream(),
             )
         )
-        return sorted_ids[:n_routes], counts
+        return sorted_ids, counts, position, num_blocks
 
-    def pack(self, hidden, ids, weights, sorted_ids, n_local):
+    def pack(self, hidden, ids, weights, plan, n_local, layout: RowLayout):
+        """The packed send rows (uint8 [T*K, row_bytes]; the rows past sum(counts) are not written)."""
         lib = _lib.load()
+        sorted_ids, _, position, num_blocks = plan
         device = hidden.device
-        n_send, h = sorted_ids.numel(), hidden.shape[1]
-        rows_q = torch.empty((n_send, h), dtype=torch.uint8, device=device)
-        meta = torch.empty((2, n_send), dtype=torch.int32, device=device)
-        position = torch.full((ids.numel(),), -1, dtype=torch.int32, device=device)
-        mx = self.fmt == "mxfp4"
-        quant = lib.aklr_ep_gather_quant_mxfp8 if mx else lib.aklr_ep_gather_quant
-        scale_shape = (h // 32, torch.uint8) if mx else (h // 128, torch.float32)
-        rows_scale = torch.empty((n_send, scale_shape[0]), dtype=scale_shape[1], device=device)
-        n_tokens, topk = hidden.shape[0], ids.shape[1]
-        if topk > 1 and n_tokens >= 512:
-            # a token's routes carry the same quantised row: quantise each token once, then copy
+        n_tokens, h = hidden.shape
+        topk = ids.shape[1]
+        tokens_q = torch.empty((n_tokens, h), dtype=torch.uint8, device=device)
+        tokens_scale = torch.empty((n_tokens, layout.scale_bytes), dtype=torch.uint8, device=device)
+        if self.mx:
             identity = torch.arange(n_tokens, dtype=torch.int32, device=device)
-            tokens_q = torch.empty((n_tokens, h), dtype=torch.uint8, device=device)
-            tokens_scale = torch.empty((n_tokens, scale_shape[0]), dtype=scale_shape[1], device=device)
-            _lib.check(quant(_ptr(hidden), _ptr(identity), n_tokens, h, 1, _ptr(tokens_q), _ptr(tokens_scale), _stream()))
-            _lib.check(
-                lib.aklr_ep_gather_rows(
-                    _ptr(tokens_q), _ptr(tokens_scale), _ptr(sorted_ids), n_send, h, topk, int(mx), _ptr(rows_q),
-                    _ptr(rows_scale), _stream(),
-                )
-            )
+            _lib.check(lib.aklr_ep_gather_quant_mxfp8(_ptr(hidden), _ptr(identity), n_tokens, h, 1, _ptr(tokens_q), _ptr(tokens_scale), _stream()))
         else:
-            _lib.check(quant(_ptr(hidden), _ptr(sorted_ids), n_send, h, topk, _ptr(rows_q), _ptr(rows_scale), _stream()))
+            _lib.check(lib.aklr_moe_act_quant_fp8(_ptr(hidden), _ptr(tokens_q), _ptr(tokens_scale), n_tokens, h, _stream()))
+        packed = torch.empty((n_tokens * topk, layout.row_bytes), dtype=torch.uint8, device=device)
         _lib.check(
-            lib.aklr_ep_dispatch_meta(
-                _ptr(sorted_ids), _ptr(ids), _ptr(weights), n_send, ids.numel(), n_local, meta[0].data_ptr(),
-                meta[1].data_ptr(), _ptr(position), _stream(),
+            lib.aklr_ep_pack(
+                _ptr(tokens_q), _ptr(tokens_scale), _ptr(sorted_ids), _ptr(ids), _ptr(weights), n_tokens * topk, n_tokens, topk, h,
+                n_local, int(self.mx), num_blocks[1:].data_ptr(), _ptr(packed), _ptr(position), _stream(),
             )
         )
-        return rows_q, rows_scale, meta.t().contiguous(), position
+        return packed
 
-    def experts(self, rows_q, rows_scale, expert_ids, weights, w1, s1, w2, s2):
-        """Weighted bf16 rows [n, H] of rows that arrive quantised, one route each."""
-        device = rows_q.device
-        n, h = rows_q.shape
+    def experts(self, received, layout: RowLayout, w1, s1, w2, s2):
+        """bf16 [n, H]: for each row received, the weighted sum of the local experts its pairs name."""
+        lib = _lib.load()
+        device = received.device
+        n, h, topk = received.shape[0], layout.hidden, layout.topk
         out = torch.empty((n, h), dtype=torch.bfloat16, device=device)
         if n == 0:
             return out
-        e, two_i, _ = w1.shape
-        if self.fmt == "mxfp4":
-            cfg = _config(n, h, two_i // 2, e, Routing(topk=1), block_m=128)
+        ids = torch.empty((n, topk), dtype=torch.int32, device=device)
+        weights = torch.empty((n, topk), dtype=torch.float32, device=device)
+        _lib.check(lib.aklr_ep_unpack_meta(_ptr(received), n, h, topk, int(self.mx), _ptr(ids), _ptr(weights), _stream()))
+        e, two_i = w1.shape[0], w1.shape[1]
+        base = received.data_ptr()
+        if self.mx:
+            cfg = _config(n, h, two_i // 2, e, Routing(topk=topk), block_m=128)
             ws = Workspace(cfg, device)
             _lib.check(
-                _lib.load().aklr_moe_mxfp4_experts_prequant(
-                    ctypes.byref(cfg), _ptr(rows_q), _ptr(rows_scale), _ptr(expert_ids), _ptr(weights), _ptr(w1), _ptr(s1),
-                    _ptr(w2), _ptr(s2), float(self.swiglu_limit or 0.0), _ptr(out), ws.base.data_ptr(),
-                    ws.layout.total_bytes, _stream(),
+                lib.aklr_moe_mxfp4_experts_rows(
+                    ctypes.byref(cfg), base, layout.row_bytes, base + h, layout.row_bytes, _ptr(ids), _ptr(weights), _ptr(w1), _ptr(s1),
+                    _ptr(w2), _ptr(s2), float(self.swiglu_limit or 0.0), _ptr(out), ws.base.data_ptr(), ws.layout.total_bytes, _stream(),
                 )
             )
             return out
-        cfg = _config(n, h, two_i // 2, e, Routing(topk=1))
+        cfg = _config(n, h, two_i // 2, e, Routing(topk=topk))
         ws = Workspace(cfg, device)
         _lib.check(
-            _lib.load().aklr_moe_fp8_experts_prequant(
-                ctypes.byref(cfg), _ptr(rows_q), _ptr(rows_scale), _ptr(expert_ids), _ptr(weights), _ptr(w1),
-                _ptr(s1), _ptr(w2), _ptr(s2), _ptr(out), ws.base.data_ptr(), ws.layout.total_bytes, _stream(),
+            lib.aklr_moe_fp8_experts_rows(
+                ctypes.byref(cfg), base, layout.row_bytes, base + h, layout.row_bytes, _ptr(ids), _ptr(weights), _ptr(w1), _ptr(s1),
+                _ptr(w2), _ptr(s2), _ptr(out), ws.base.data_ptr(), ws.layout.total_bytes, _stream(),
             )
         )
         return out
@@ -161,7 +183,7 @@ class CudaKernels:
         n_tokens, n_shared = hidden.shape[0], w1.shape[0]
         ids = torch.arange(n_shared, dtype=torch.int32, device=hidden.device).repeat(n_tokens, 1).contiguous()
         ones = torch.ones((n_tokens, n_shared), dtype=torch.float32, device=hidden.device)
-        if self.fmt == "mxfp4":
+        if self.mx:
             return fused_experts_mxfp4(hidden, ids, ones, w1, s1, w2, s2, swiglu_limit=self.swiglu_limit)
         return fused_experts_fp8(hidden, ids, ones, w1, s1, w2, s2)
 
@@ -175,7 +197,7 @@ class CudaKernels:
 
 
 class ExpertParallelMoE:
-    """One rank's share of an expert-parallel FP8 MoE layer.
+    """One rank's share of an expert-parallel MoE layer.
 
     ``w1``/``w2`` (+ scales) hold this rank's ``n_local`` routed experts followed by the layer's
     shared experts (replicated).  ``routing`` describes the whole layer (global expert count =
@@ -216,25 +238,20 @@ class ExpertParallelMoE:
                 shared_rows = k.shared(hidden, *self.shared)
         ids, weights = routed if routed is not None else k.route(logits, bias, self.routing)
         self.routing = dataclasses.replace(self.routing, topk=ids.shape[1])
-        sorted_ids, counts = k.order_by_rank(ids, self.n_local, self.world)
-        rows_q, rows_scale, meta, position = k.pack(hidden, ids, weights, sorted_ids, self.n_local)
-        return StepState(Packed(rows_q, rows_scale, meta, counts), position, shared_rows, shared_done, hidden.shape[0])
+        layout = RowLayout(hidden.shape[1], ids.shape[1], bool(getattr(k, "mx", False)))
+        plan = k.plan(ids, self.n_local, self.world)
+        packed = k.pack(hidden, ids, weights, plan, self.n_local, layout)
+        return StepState(packed, plan[1], plan[2], shared_rows, shared_done, hidden.shape[0], layout)
 
     # ---- phase 2: on the rank that holds the experts ---------------------------------------------
-    def compute(self, received: Packed) -> torch.Tensor:
-        expert_ids = received.meta[:, 0].contiguous()
-        weights = received.meta[:, 1].contiguous().view(torch.float32)
-        rows_q = received.rows_q
-        if rows_q.dtype != FP8 and rows_q.is_cuda and getattr(self.kernels, "fmt", "fp8") == "fp8":
-            rows_q = rows_q.view(FP8)
-        return self.kernels.experts(rows_q, received.rows_scale, expert_ids, weights, *self.routed)
+    def compute(self, received: torch.Tensor, layout: RowLayout) -> torch.Tensor:
+        return self.kernels.experts(received, layout, *self.routed)
 
     # ---- phase 3: back home ------------------------------------------------------------------------
     def finish(self, state: StepState, back_rows: torch.Tensor) -> torch.Tensor:
         if state.shared_done is not None:
             torch.cuda.current_stream().wait_event(state.shared_done)
-        hidden = back_rows.shape[1]
-        return self.kernels.combine(back_rows, state.position_of_route, state.shared_rows, state.n_tokens, self.routing.topk, hidden)
+        return self.kernels.combine(back_rows, state.position_of_route, state.shared_rows, state.n_tokens, state.layout.topk, state.layout.hidden)
 
     # ---- all three over torch.distributed ------------------------------------------------------------
     def forward(self, hidden, logits, bias, group=None, routed=None, micro_batches: int = 1) -> torch.Tensor:
@@ -251,9 +268,9 @@ class ExpertParallelMoE:
         for lo, hi in zip(bounds[:-1], bounds[1:]):
             part_routed = None if routed is None else (routed[0][lo:hi], routed[1][lo:hi])
             state = self.prepare(hidden[lo:hi], None if logits is None else logits[lo:hi], bias, part_routed)
-            recv_counts_dev = torch.empty_like(state.send.counts)
-            dist.all_to_all_single(recv_counts_dev, state.send.counts, group=group)
-            both = torch.stack([state.send.counts, recv_counts_dev])
+            recv_counts_dev = torch.empty_like(state.counts)
+            dist.all_to_all_single(recv_counts_dev, state.counts, group=group)
+            both = torch.stack([state.counts, recv_counts_dev])
             if both.is_cuda:  # the one host read of the part: pinned, asynchronous, waited for below
                 host = torch.empty(both.shape, dtype=both.dtype, pin_memory=True)
                 host.copy_(both, non_blocking=True)
@@ -267,42 +284,26 @@ class ExpertParallelMoE:
             if ready is not None:
                 ready.synchronize()
             send_counts, recv_counts = host[0].tolist(), host[1].tolist()
-            received = exchange(state.send, send_counts, recv_counts, group)
-            rows = self.compute(received)
-            back = torch.empty((sum(send_counts), rows.shape[1]), dtype=rows.dtype, device=rows.device)
+            n_send, n_recv = sum(send_counts), sum(recv_counts)
+            received = torch.empty((n_recv, state.layout.row_bytes), dtype=torch.uint8, device=hidden.device)
+            dist.all_to_all_single(received, state.packed[:n_send], output_split_sizes=recv_counts, input_split_sizes=send_counts, group=group)
+            rows = self.compute(received, state.layout)
+            back = torch.empty((n_send, rows.shape[1]), dtype=rows.dtype, device=rows.device)
             dist.all_to_all_single(back, rows, output_split_sizes=send_counts, input_split_sizes=recv_counts, group=group)
             outs.append(self.finish(state, back))
         return outs[0] if len(outs) == 1 else torch.cat(outs)
 
 
-def exchange(send: Packed, send_counts, recv_counts, group=None) -> Packed:
-    """The dispatch all-to-all: rows, scales and metadata, split by destination rank."""
-    import torch.distributed as dist
-
-    n_recv = sum(recv_counts)
-
-    def a2a(t: torch.Tensor) -> torch.Tensor:
-        out = torch.empty((n_recv, *t.shape[1:]), dtype=t.dtype, device=t.device)
-        dist.all_to_all_single(out, t, output_split_sizes=recv_counts, input_split_sizes=send_counts, group=group)
-        return out
-
-    return Packed(a2a(send.rows_q), a2a(send.rows_scale), a2a(send.meta), torch.tensor(recv_counts, dtype=torch.int32))
-
-
-def exchange_in_process(sends: list[Packed]) -> tuple[list[Packed], list[list[int]]]:
-    """The same data movement among ranks that live in one process (tests, single-GPU emulation).
-    Returns what each rank receives and each rank's send counts."""
-    world = len(sends)
-    counts = [s.counts.cpu().tolist() for s in sends]
+def exchange_in_process(states: list[StepState]) -> tuple[list[torch.Tensor], list[list[int]]]:
+    """The dispatch among ranks that live in one process (tests, single-GPU emulation): what each rank
+    receives (rows ordered by source rank) and each rank's send counts."""
+    world = len(states)
+    counts = [s.counts.cpu().tolist() for s in states]
     starts = [[sum(c[:d]) for d in range(world)] for c in counts]
     received = []
     for dst in range(world):
-        def gather(field):
-            parts = [getattr(sends[src], field)[starts[src][dst] : starts[src][dst] + counts[src][dst]] for src in range(world)]
-            return torch.cat(parts)
-
-        recv_counts = torch.tensor([counts[src][dst] for src in range(world)], dtype=torch.int32)
-        received.append(Packed(gather("rows_q"), gather("rows_scale"), gather("meta"), recv_counts))
+        parts = [states[src].packed[starts[src][dst] : starts[src][dst] + counts[src][dst]] for src in range(world)]
+        received.append(torch.cat(parts))
     return received, counts
 
 
@@ -322,165 +323,7 @@ def exchange_back_in_process(rows_per_rank: list[torch.Tensor], counts: list[lis
 def run_in_process(layers: list[ExpertParallelMoE], inputs: list[tuple]) -> list[torch.Tensor]:
     """All ranks' steps in one process: phase by phase, never two ranks' kernels waiting on each other."""
     states = [layer.prepare(*inp) for layer, inp in zip(layers, inputs)]
-    received, counts = exchange_in_process([s.send for s in states])
-    rows = [layer.compute(r) for layer, r in zip(layers, received)]
+    received, counts = exchange_in_process(states)
+    rows = [layer.compute(r, s.layout) for layer, r, s in zip(layers, received, states)]
     back = exchange_back_in_process(rows, counts)
     return [layer.finish(s, b) for layer, s, b in zip(layers, states, back)]
-
-
-def bench_ep(args, cfg, rank, world, device, clock_sampler, workload_config, metric, unit, measured_peak_hbm):
-    """The N-GPU leg of bench.py: every rank holds n_routed/N routed experts + the shared expert
-    and ``args.tokens`` tokens of its own (weak scaling).  Rank 0 prints the JSON line."""
-    import json
-
-    import torch.distributed as dist
-
-    from aklr_b200 import workloads as wl
-
-    seed = 2024
-    if cfg.n_routed % world:
-        raise SystemExit(f"{cfg.n_routed} routed experts do not split over {world} ranks")
-    n_local = cfg.n_routed // world
-    mine = list(range(rank * n_local, (rank + 1) * n_local)) + list(range(cfg.n_routed, cfg.n_experts))
-    mx = getattr(args, "format", "fp8") == "mxfp4"
-    w1, s1, w2, s2 = (wl.mx_expert_weights if mx else wl.expert_weights)(cfg, seed, device, experts=mine)
-    routing = Routing(cfg.topk, cfg.scoring, cfg.n_shared, cfg.num_expert_group, cfg.topk_group, cfg.renormalize, cfg.routed_scaling_factor)
-    layer = ExpertParallelMoE(routing, w1, s1, w2, s2, rank, world, kernels=CudaKernels("mxfp4" if mx else "fp8"))
-    bias = wl.router_inputs(cfg, 1, seed + 1, device)[2]
-    n_batches, tokens = 4, args.tokens
-    batches = [wl.router_inputs(cfg, tokens, seed + 1 + 97 * rank + b, device)[:2] for b in range(n_batches)]
-    lib = _lib.load()
-
-    def step(i):  # one part per step: two interleaved halves measured 7 % slower at N=8 (twice the collectives)
-        hidden, logits = batches[i % n_batches]
-        return layer.forward(hidden, logits, bias)
-
-    def timed(fn, steps, before_stop=None):
-        dist.barrier()
-        torch.cuda.synchronize()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for i in range(steps):
-            fn(i)
-        if before_stop is not None:
-            before_stop()
-        stop.record()
-        torch.cuda.synchronize()
-        dist.barrier()
-        ms = torch.tensor([start.elapsed_time(stop)], device=device)
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)  # the slowest rank's device time
-        return float(ms) / steps
-
-    sampler = clock_sampler(device.index) if rank == 0 else None
-    for i in range(args.warmup):
-        step(i)
-    torch.cuda.synchronize()
-    lib.aklr_profile_begin(0 if mx else 2 * args.steps)
-    launches0 = lib.aklr_kernel_launch_count()
-    if sampler:
-        sampler.begin()
-    ms_per_step = timed(lambda i: step(args.warmup + i), args.steps)
-    clocks = sampler.stop() if sampler else None
-    launches = lib.aklr_kernel_launch_count() - launches0
-    # stage times of the routed-expert calls (every second recorded call; the other is the shared expert)
-    stage_ms = [0.0] * 6
-    buf = (ctypes.c_float * 6)()
-    for i in range(0 if mx else args.steps):
-        _lib.check(lib.aklr_profile_read(2 * i + 1, buf))
-        for j in range(6):
-            stage_ms[j] += buf[j] / args.steps
-    lib.aklr_profile_begin(0)
-
-    # end to end from pinned host buffers: every step copies its activations and logits in and its
-    # output out; two buffers each way and two copy streams, so step i's input copy overlaps step
-    # i-1's tail and its output copy overlaps step i+1's head, as a serving loop would run it
-    host = [(h.cpu().pin_memory(), lg.cpu().pin_memory()) for h, lg in batches]
-    dev_hidden = [torch.empty_like(batches[0][0]) for _ in range(2)]
-    dev_logits = [torch.empty_like(batches[0][1]) for _ in range(2)]
-    host_out = [torch.empty((tokens, cfg.hidden), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
-    copy_in, copy_out, compute = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
-    in_ready = [torch.cuda.Event() for _ in range(2)]
-    in_free = [torch.cuda.Event() for _ in range(2)]
-    out_free = [torch.cuda.Event() for _ in range(2)]
-
-    def e2e_step(i):
-        k = i & 1
-        with torch.cuda.stream(copy_in):
-            copy_in.wait_event(in_free[k])  # the step that last read these buffers is past them
-            dev_hidden[k].copy_(host[i % n_batches][0], non_blocking=True)
-            dev_logits[k].copy_(host[i % n_batches][1], non_blocking=True)
-            in_ready[k].record(copy_in)
-        compute.wait_event(in_ready[k])
-        result = layer.forward(dev_hidden[k], dev_logits[k], bias)
-        in_free[k].record(compute)
-        done = torch.cuda.Event()
-        done.record(compute)
-        with torch.cuda.stream(copy_out):
-            copy_out.wait_event(done)
-            copy_out.wait_event(out_free[k])
-            host_out[k].copy_(result, non_blocking=True)
-            result.record_stream(copy_out)
-            out_free[k].record(copy_out)
-
-    def drain():
-        compute.wait_stream(copy_out)
-        compute.wait_stream(copy_in)
-
-    for i in range(args.warmup):
-        e2e_step(i)
-    e2e_ms = timed(e2e_step, args.steps, before_stop=drain)
-
-    if rank != 0:
-        return None
-    h, inter = cfg.hidden, cfg.inter
-    routes_local = tokens * cfg.topk  # expected rows received per rank under uniform routing
-    gate_up_bytes = n_local * (2 * inter * h + 4 * (2 * inter // 128) * (h // 128)) + routes_local * (h + 4 * (h // 128) + inter)
-    peak, peak_kind = measured_peak_hbm()
-    achieved = gate_up_bytes / (stage_ms[3] * 1e-3) / 1e9 if stage_ms[3] > 0 else 0.0
-    config = workload_config(cfg, args)
-    if mx:
-        metric = metric.replace("fp8", "mxfp4")
-        config["weights"] = "mxfp4: e2m1 + e8m0 per 32 along K, N(0,0.02)"
-        config["activations"] = "bf16 N(0,1), quantised to MXFP8 (e4m3 + e8m0 per 32)"
-    line = {
-        "metric": metric,
-        "value": world * tokens / (ms_per_step * 1e-3),
-        "unit": unit,
-        "n_gpus": world,
-        "steps": args.steps,
-        "warmup": args.warmup,
-        "ms_per_step": ms_per_step,
-        "higher_is_better": True,
-        "scaling": "weak",
-        "vs_baseline": None,
-        "dtype": "mxfp4 x mxfp8" if mx else "fp8_e4m3",
-        "data": "synthetic",
-        "config": config,
-        "clocks": clocks,
-        "tflops": world * tokens * cfg.routes_per_token * cfg.flops_per_route / (ms_per_step * 1e-3) / 1e12,
-        "e2e": {
-            "value": world * tokens / (e2e_ms * 1e-3),
-            "unit": unit,
-            "ms_per_step": e2e_ms,
-            "h2d_bytes_per_step": tokens * (cfg.hidden + cfg.n_routed) * 2,
-            "d2h_bytes_per_step": tokens * cfg.hidden * 2,
-            "api": "aklr_b200.ep.ExpertParallelMoE.forward (from router logits), per rank; copies double-buffered on their own streams",
-        },
-        "gpu_launches": int(launches),
-        "roofline": {
-            "kernel": "grouped_gemm_prefill_kernel<gate_up> over the rows a rank receives (rank 0)",
-            "bound": "hbm",
-            "achieved": achieved,
-            "peak": peak,
-            "peak_kind": f"of {peak_kind}",
-            "unit": "GB/s",
-            "frac": achieved / peak,
-            "traffic": None,
-            "algorithmic_bytes_per_launch": gate_up_bytes,
-            "ms_per_launch": stage_ms[3],
-            "stage_ms": dict(zip(["route", "sort", "quant", "gate_up", "down", "combine"], stage_ms)),
-            "note": "all local experts assumed hit; rows = tokens*topk (uniform routing expectation)",
-        },
-        "cpu_baseline": None,
-    }
-    return json.dumps(line)

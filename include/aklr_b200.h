@@ -204,6 +204,42 @@ int aklr_moe_mxfp4_experts_prequant(const aklr_moe_config* cfg, const void* rows
 int aklr_ep_combine(const void* rows, const int32_t* position_of_route, const void* shared_rows, void* out,
                     int32_t n_tokens, int32_t topk, int32_t hidden, void* stream);
 
+/* One row per (token, destination rank) instead of one per route: a token whose routes name several
+ * experts of one rank sends that rank its row once, the rank runs all of them and returns their weighted
+ * sum as one row -- the "pre-sum per (token, rank)" the reference's expert-parallel notes describe for
+ * mega_moe (aklr/ops/mega_moe/contract.py:44-51 fixes who owns what; message shape: the reference's
+ * mega_moe_buffers, kernel e9d234d2dd4d06d9, mega_moe_buffers.py:154-167).
+ *   aklr_ep_plan      first_rank[t, s] = rank of slot s if no earlier slot of token t goes to that rank, else -1
+ *                     (sort it by rank with aklr_moe_align, block_m 1); position_of_route[t, s] = -1;
+ *   aklr_ep_pack      send row i = [hidden e4m3 codes][scales][topk int32 ids local to the destination, -1 where the
+ *                     slot goes elsewhere][topk float weights], aklr_ep_row_bytes(hidden, topk, mx) bytes a row, from
+ *                     tokens quantised once (aklr_moe_act_quant_fp8: float scales [T, H/128]; mx: aklr_ep_gather_quant_mxfp8
+ *                     with the identity table: e8m0 bytes [T, H/32]); records position_of_route for the sent slots;
+ *                     n_send is the host's bound on the rows, n_send_device (or NULL) the device's count of them;
+ *   (ONE NCCL all-to-all of the packed rows -- issued by the caller)
+ *   aklr_ep_unpack_meta  the ids / weights tables [rows, topk] of the rows received;
+ *   aklr_moe_fp8_experts_rows / aklr_moe_mxfp4_experts_rows  experts over rows that arrive quantised, topk routes
+ *                     per row (negative id: none), codes and scales read in place from the packed rows (pitches in
+ *                     bytes, 0 = dense); out [rows, H] bf16 = each row's weighted sum;
+ *   (ONE NCCL all-to-all of the bf16 rows back), then aklr_ep_combine as above. */
+int32_t aklr_ep_row_bytes(int32_t hidden, int32_t topk, int32_t mx);
+int aklr_ep_plan(const int32_t* topk_ids, int32_t n_tokens, int32_t topk, int32_t experts_per_rank, int32_t* first_rank,
+                 int32_t* position_of_route, void* stream);
+int aklr_ep_pack(const void* tokens_q, const void* tokens_scale, const int32_t* sorted_ids, const int32_t* topk_ids,
+                 const float* topk_weights, int32_t n_send, int32_t n_tokens, int32_t topk, int32_t hidden,
+                 int32_t experts_per_rank, int32_t mx, const int32_t* n_send_device, void* packed,
+                 int32_t* position_of_route, void* stream);
+int aklr_ep_unpack_meta(const void* packed, int32_t n_rows, int32_t hidden, int32_t topk, int32_t mx, int32_t* topk_ids,
+                        float* topk_weights, void* stream);
+int aklr_moe_fp8_experts_rows(const aklr_moe_config* cfg, const void* rows_q, int32_t rows_q_pitch, const float* rows_scale,
+                              int32_t rows_scale_pitch, const int32_t* topk_ids, const float* topk_weights, const void* w1,
+                              const float* w1_scale, const void* w2, const float* w2_scale, void* out, void* workspace,
+                              size_t workspace_bytes, void* stream);
+int aklr_moe_mxfp4_experts_rows(const aklr_moe_config* cfg, const void* rows_q, int32_t rows_q_pitch, const uint8_t* rows_scale,
+                                int32_t rows_scale_pitch, const int32_t* topk_ids, const float* topk_weights, const void* w1,
+                                const uint8_t* w1_scale, const void* w2, const uint8_t* w2_scale, float swiglu_limit, void* out,
+                                void* workspace, size_t workspace_bytes, void* stream);
+
 /* Routing alone: `biased_grouped_topk` (aklr/ops/topk/api.py:12-22, reference.py:17-35) and the
  * routing halves of the two layer ops.  Writes topk_ids int32 / topk_weights float
  * [T, topk + n_shared]. */

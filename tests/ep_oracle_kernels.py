@@ -1,5 +1,6 @@
 """CPU stand-in for the device side of the expert-parallel phases, built on the oracle: lets the
-host logic (ownership, split sizes, ordering, the exchanges) run over gloo without a GPU."""
+host logic (ownership, one row per (token, rank), the packed row layout, split sizes, the exchanges)
+run over gloo without a GPU."""
 
 from __future__ import annotations
 
@@ -9,6 +10,8 @@ from oracle import moe_oracle as orc
 
 
 class OracleKernels:
+    mx = False
+
     def route(self, logits, bias, routing):
         if routing.scoring == "sigmoid":
             ids, w = orc.grouped_sigmoid_topk(
@@ -19,19 +22,39 @@ class OracleKernels:
             ids, w = orc.softmax_topk(logits.float(), routing.topk)
         return ids.to(torch.int32), w.float()
 
-    def order_by_rank(self, ids, n_local, world):
-        ranks = (ids.reshape(-1).long() // n_local)
-        order = torch.sort(ranks, stable=True).indices.to(torch.int32)
-        return order, torch.bincount(ranks, minlength=world).to(torch.int32)
+    def plan(self, ids, n_local, world):
+        n_tokens, topk = ids.shape
+        ranks = ids.long() // n_local
+        first = torch.ones_like(ranks, dtype=torch.bool)
+        for s in range(1, topk):  # a slot is a first slot when no earlier slot of its token goes to the same rank
+            first[:, s] = ~(ranks[:, :s] == ranks[:, s : s + 1]).any(dim=1)
+        first &= ids >= 0
+        first_rank = torch.where(first, ranks, torch.full_like(ranks, -1)).reshape(-1)
+        routes = first.reshape(-1).nonzero().flatten()
+        order = routes[torch.sort(first_rank[routes], stable=True).indices].to(torch.int32)
+        sorted_ids = torch.full((n_tokens * topk + world,), -1, dtype=torch.int32)
+        sorted_ids[: order.numel()] = order
+        counts = torch.bincount(first_rank[routes], minlength=world).to(torch.int32)
+        position = torch.full((n_tokens * topk,), -1, dtype=torch.int32)
+        return sorted_ids, counts, position, torch.tensor([order.numel(), order.numel()], dtype=torch.int32)
 
-    def pack(self, hidden, ids, weights, sorted_ids, n_local):
-        tokens = sorted_ids.long() // ids.shape[1]
-        codes, scales = orc.fp8_group_quant(hidden.float()[tokens])
-        flat_ids, flat_w = ids.reshape(-1)[sorted_ids.long()], weights.reshape(-1)[sorted_ids.long()]
-        meta = torch.stack([(flat_ids % n_local).to(torch.int32), flat_w.contiguous().view(torch.int32)], dim=1).contiguous()
-        position = torch.full((ids.numel(),), -1, dtype=torch.int32)
-        position[sorted_ids.long()] = torch.arange(sorted_ids.numel(), dtype=torch.int32)
-        return codes.view(torch.uint8), scales, meta, position
+    def pack(self, hidden, ids, weights, plan, n_local, layout):
+        sorted_ids, _, position, num_blocks = plan
+        n_send, topk, h = int(num_blocks[1]), ids.shape[1], hidden.shape[1]
+        rids = sorted_ids[:n_send].long()
+        tokens = rids // topk
+        codes, scales = orc.fp8_group_quant(hidden.float())
+        packed = torch.zeros((ids.numel(), layout.row_bytes), dtype=torch.uint8)
+        packed[:n_send, :h] = codes.view(torch.uint8)[tokens]
+        packed[:n_send, h : layout.meta_offset] = scales.contiguous().view(torch.uint8).reshape(hidden.shape[0], -1)[tokens]
+        rank = (ids.reshape(-1)[rids].long() // n_local).unsqueeze(1)
+        here = (ids[tokens].long() // n_local == rank) & (ids[tokens] >= 0)
+        local = torch.where(here, ids[tokens] % n_local, torch.full_like(ids[tokens], -1)).to(torch.int32)
+        w = torch.where(here, weights[tokens], torch.zeros_like(weights[tokens])).float()
+        packed[:n_send, layout.meta_offset : layout.meta_offset + 4 * topk] = local.contiguous().view(torch.uint8).reshape(n_send, -1)
+        packed[:n_send, layout.meta_offset + 4 * topk : layout.meta_offset + 8 * topk] = w.contiguous().view(torch.uint8).reshape(n_send, -1)
+        position[rids] = torch.arange(n_send, dtype=torch.int32)
+        return packed
 
     @staticmethod
     def _mlp_rows(xq, w1, s1, w2, s2, expert_ids):
@@ -42,11 +65,20 @@ class OracleKernels:
             out[rows] = orc.fp8_input(torch.nn.functional.silu(gate) * up) @ orc.dequant_block_weight(w2[e], s2[e]).T
         return out
 
-    def experts(self, rows_q, rows_scale, expert_ids, weights, w1, s1, w2, s2):
-        codes = rows_q.view(orc.FP8).float()
-        xq = (codes.unflatten(-1, (-1, 128)) * rows_scale.unsqueeze(-1)).flatten(-2)
-        y = self._mlp_rows(xq, w1, s1, w2, s2, expert_ids.long())
-        return (y * weights.unsqueeze(-1)).to(torch.bfloat16)
+    def experts(self, received, layout, w1, s1, w2, s2):
+        n, h, topk = received.shape[0], layout.hidden, layout.topk
+        codes = received[:, :h].contiguous().view(orc.FP8).float()
+        scales = received[:, h : layout.meta_offset].contiguous().view(torch.float32)
+        ids = received[:, layout.meta_offset : layout.meta_offset + 4 * topk].contiguous().view(torch.int32)
+        weights = received[:, layout.meta_offset + 4 * topk : layout.meta_offset + 8 * topk].contiguous().view(torch.float32)
+        xq = (codes.unflatten(-1, (-1, 128)) * scales.unsqueeze(-1)).flatten(-2)
+        total = torch.zeros((n, h))
+        for s in range(topk):  # slot order, each route's row rounded to bf16 before the float32 sum, as the kernels do
+            live = (ids[:, s] >= 0).nonzero().flatten()
+            if live.numel():
+                y = self._mlp_rows(xq[live], w1, s1, w2, s2, ids[live, s].long())
+                total[live] += (y * weights[live, s : s + 1]).to(torch.bfloat16).float()
+        return total.to(torch.bfloat16)
 
     def shared(self, hidden, w1, s1, w2, s2):
         xq = orc.fp8_input(hidden.float())

@@ -45,11 +45,31 @@ def test_emulated_ranks_match_single_gpu_and_oracle(world, tokens):
         )
         gates = orc.output_gates(outs[r].cpu(), ref)
         assert orc.gates_pass(gates), (r, gates)
-        if max(tokens) < 512:
-            # same kernels, same per-token arithmetic, same summation order: the same bits
-            assert torch.equal(outs[r], single), f"rank {r} differs from the single-GPU layer"
-        else:
-            # from 512 tokens up the sender quantises each token once and copies rows; the two sides may
-            # also pick different block sizes (different grouped-GEMM kernels), so compare closely
-            close = orc.output_gates(outs[r].cpu(), single.cpu().float())
-            assert close["sqnr_db"] > 45.0, (r, close)
+        # one row per (token, rank): a rank's routes of a token are summed there and rounded to bf16 once more
+        # than on one GPU, so the two agree closely, not bit for bit
+        close = orc.output_gates(outs[r].cpu(), single.cpu().float())
+        assert close["sqnr_db"] > 45.0, (r, close)
+
+
+def test_a_token_sends_one_row_per_rank_it_reaches():
+    """The plan counts (token, rank) pairs, not routes: with 8 groups of experts and 4 kept, at one group per
+    rank a token reaches at most 4 of 8 ranks whatever its 8 routes are; the rows sent are exactly the distinct
+    (token, rank) pairs of the routing, ordered by rank, and every pair's position is recorded."""
+    from aklr_b200.ep import CudaKernels
+    from aklr_b200.moe import route
+
+    cfg = wl.CONFIGS["deepseek_small"]
+    d = torch.device("cuda:0")
+    world, n_local = 8, cfg.n_routed // 8
+    _, logits, bias = wl.router_inputs(cfg, 300, seed=90)
+    ids, _ = route(logits.to(d), bias.to(d), routing_of(cfg))
+    ids = ids[:, : cfg.topk].contiguous()
+    sorted_ids, counts, position, num_blocks = CudaKernels().plan(ids, n_local, world)
+    torch.cuda.synchronize()
+    ranks = ids.cpu().long() // n_local
+    pairs = sorted({(t, int(r)) for t in range(300) for r in ranks[t].tolist()}, key=lambda p: (p[1], p[0]))
+    assert int(num_blocks[1]) == len(pairs) <= 300 * 4
+    assert counts.cpu().tolist() == [sum(1 for p in pairs if p[1] == r) for r in range(world)]
+    sent = sorted_ids[: len(pairs)].cpu().long()
+    assert [(int(rid) // cfg.topk, int(ranks.reshape(-1)[rid])) for rid in sent] == pairs
+    assert (position.cpu() == -1).all()  # pack fills the positions in
