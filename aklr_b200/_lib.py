@@ -85,6 +85,7 @@ SIGNATURES = {
     "aklr_ep_dispatch_meta": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p]),
     "aklr_moe_fp8_experts_prequant": (c_int32, [POINTER(MoeConfig)] + [c_void_p] * 9 + [c_void_p, c_size_t, c_void_p]),
     "aklr_ep_combine": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p]),
+    "aklr_ep_counts_to_host": (c_int32, [c_void_p, c_void_p, c_int32, c_void_p, c_void_p]),
     "aklr_ep_row_bytes": (c_int32, [c_int32, c_int32, c_int32]),
     "aklr_ep_plan": (c_int32, [c_void_p, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p]),
     "aklr_ep_pack": (c_int32, [c_void_p] * 5 + [c_int32] * 6 + [c_void_p, c_void_p, c_void_p, c_void_p]),

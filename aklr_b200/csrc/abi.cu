@@ -960,6 +960,17 @@ int aklr_ep_unpack_meta(const void* packed, int32_t n_rows, int32_t hidden, int3
   return AKLR_OK;
 }
 
+int aklr_ep_counts_to_host(const int32_t* send_counts, const int32_t* recv_counts, int32_t world, int32_t* host_mapped,
+                           void* stream) {
+  if (!send_counts || !recv_counts || !host_mapped) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
+  int rc = check_device();
+  if (rc) return rc;
+  rc = aklr::launch_ep_counts_to_host(send_counts, recv_counts, world, host_mapped, static_cast<cudaStream_t>(stream));
+  if (rc) return fail(rc, "ep counts to host: %s", aklr_status_string(rc));
+  g_launches += 1;
+  return AKLR_OK;
+}
+
 int aklr_ep_gather_quant_mxfp8(const void* hidden_states, const int32_t* sorted_ids, int32_t n_send, int32_t hidden,
                                int32_t routes_per_token, void* rows_q, uint8_t* rows_scale, void* stream) {
   if (!hidden_states || !sorted_ids || !rows_q || !rows_scale) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");

@@ -111,6 +111,27 @@ int launch_ep_unpack_meta(const uint8_t* packed, int n_rows, int row_bytes, int 
   return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
 }
 
+// The split sizes of the uneven all-to-all have to reach the host.  A device-to-host copy would queue on
+// the copy engine behind whatever large copy a serving loop has in flight there (a step's output going
+// back to the host: milliseconds); stores from an SM into mapped pinned host memory do not.
+__global__ void ep_counts_to_host_kernel(const int32_t* send_counts, const int32_t* recv_counts, int world,
+                                         int32_t* host_mapped) {
+  const int i = threadIdx.x;
+  if (i < world) {
+    volatile int32_t* out = host_mapped;
+    out[i] = send_counts[i];
+    out[world + i] = recv_counts[i];
+  }
+  __threadfence_system();
+}
+
+int launch_ep_counts_to_host(const int32_t* send_counts, const int32_t* recv_counts, int world, int32_t* host_mapped,
+                             cudaStream_t stream) {
+  if (world < 1 || world > 1024) return AKLR_ERR_BAD_ARGUMENT;
+  ep_counts_to_host_kernel<<<1, (world + 31) / 32 * 32, 0, stream>>>(send_counts, recv_counts, world, host_mapped);
+  return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+}
+
 // out[t] = bf16( sum_k rows[position(t,k)] + shared[t] ), float32 sum in slot order, shared last:
 // the order of the single-GPU combine, so both give the same bits.
 __global__ void __launch_bounds__(256) ep_combine_kernel(EpCombineParams p) {

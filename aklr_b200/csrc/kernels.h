@@ -198,6 +198,9 @@ int launch_ep_pack(const EpPackParams& p, cudaStream_t stream);
 int launch_ep_unpack_meta(const uint8_t* packed, int n_rows, int row_bytes, int meta_offset, int topk, int32_t* ids,
                           float* weights, cudaStream_t stream);
 
+int launch_ep_counts_to_host(const int32_t* send_counts, const int32_t* recv_counts, int world, int32_t* host_mapped,
+                             cudaStream_t stream);
+
 struct EpCombineParams {
   const void* rows;                  // [n_send, hidden] bf16, weighted, in send order
   const int32_t* position_of_route;  // [n_tokens * topk]

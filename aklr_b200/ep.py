@@ -253,6 +253,16 @@ class ExpertParallelMoE:
             torch.cuda.current_stream().wait_event(state.shared_done)
         return self.kernels.combine(back_rows, state.position_of_route, state.shared_rows, state.n_tokens, state.layout.topk, state.layout.hidden)
 
+    def _counts_buffer(self) -> torch.Tensor:
+        """Pinned int32 [2, world] for one part's split sizes; a small ring, so that a buffer is not rewritten
+        while the host may still be reading the one of a few parts ago."""
+        ring = getattr(self, "_counts_ring", None)
+        if ring is None:
+            ring = self._counts_ring = [torch.zeros((2, self.world), dtype=torch.int32).pin_memory() for _ in range(8)]
+            self._counts_next = 0
+        self._counts_next = (self._counts_next + 1) % len(ring)
+        return ring[self._counts_next]
+
     # ---- all three over torch.distributed ------------------------------------------------------------
     def forward(self, hidden, logits, bias, group=None, routed=None, micro_batches: int = 1) -> torch.Tensor:
         """``micro_batches`` > 1 splits the tokens into that many consecutive parts whose steps are
@@ -270,14 +280,15 @@ class ExpertParallelMoE:
             state = self.prepare(hidden[lo:hi], None if logits is None else logits[lo:hi], bias, part_routed)
             recv_counts_dev = torch.empty_like(state.counts)
             dist.all_to_all_single(recv_counts_dev, state.counts, group=group)
-            both = torch.stack([state.counts, recv_counts_dev])
-            if both.is_cuda:  # the one host read of the part: pinned, asynchronous, waited for below
-                host = torch.empty(both.shape, dtype=both.dtype, pin_memory=True)
-                host.copy_(both, non_blocking=True)
+            if recv_counts_dev.is_cuda:
+                # the one host read of the part, waited for below: a kernel stores the counts into pinned host
+                # memory (a device-to-host copy would queue behind any large copy on the copy engine)
+                host = self._counts_buffer()
+                _lib.check(_lib.load().aklr_ep_counts_to_host(_ptr(state.counts), _ptr(recv_counts_dev), self.world, host.data_ptr(), _stream()))
                 ready = torch.cuda.Event()
                 ready.record()
             else:
-                host, ready = both, None
+                host, ready = torch.stack([state.counts, recv_counts_dev]), None
             pending.append((state, host, ready))
         outs = []
         for state, host, ready in pending:

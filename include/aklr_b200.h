@@ -222,6 +222,12 @@ int aklr_ep_combine(const void* rows, const int32_t* position_of_route, const vo
  *                     per row (negative id: none), codes and scales read in place from the packed rows (pitches in
  *                     bytes, 0 = dense); out [rows, H] bf16 = each row's weighted sum;
  *   (ONE NCCL all-to-all of the bf16 rows back), then aklr_ep_combine as above. */
+/* The split sizes of the uneven all-to-all for the host: [send_counts | recv_counts] (2 x world int32) stored
+ * by a kernel into pinned host memory the device can address (cudaHostAlloc memory under unified addressing),
+ * not by a device-to-host copy, which would wait on the copy engine behind any large copy in flight there.
+ * The caller records an event after it and waits for that event before reading. */
+int aklr_ep_counts_to_host(const int32_t* send_counts, const int32_t* recv_counts, int32_t world, int32_t* host_mapped,
+                           void* stream);
 int32_t aklr_ep_row_bytes(int32_t hidden, int32_t topk, int32_t mx);
 int aklr_ep_plan(const int32_t* topk_ids, int32_t n_tokens, int32_t topk, int32_t experts_per_rank, int32_t* first_rank,
                  int32_t* position_of_route, void* stream);
