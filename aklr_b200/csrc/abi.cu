@@ -34,6 +34,7 @@ std::atomic<long long> g_launches{0};
 bool force_weight_major(const aklr_moe_config& c) { return (c.variant & AKLR_VARIANT_WEIGHT_MAJOR) != 0; }
 bool use_cta_pairs(const aklr_moe_config& c) { return (c.variant & AKLR_VARIANT_CTA_PAIRS) != 0; }
 bool small_activation_boxes(const aklr_moe_config& c) { return (c.variant & AKLR_VARIANT_FULL_ACTIVATION_BOXES) == 0; }
+bool bf16_activations(const aklr_moe_config& c) { return (c.variant & AKLR_VARIANT_BF16_ACTIVATIONS) != 0; }
 
 void profile_mark(cudaStream_t stream, int slot, int stage) {
   if (g_profile.on && slot >= 0) cudaEventRecord(g_profile.events[slot * (kStages + 1) + stage], stream);
@@ -253,10 +254,13 @@ void layout_of(const aklr_moe_config& c, aklr_moe_workspace_layout* l) {
   l->block_expert = take(max_blocks * 8, 256);  // block -> expert, then the table of block pairs
   l->counts = take(experts * 4, 256);
   l->chunk_hist = take((chunks > 0 ? chunks : 1) * experts * 4, 256);
-  l->xq = take(cap * c.hidden, 1024);
-  l->xs = take(cap * (c.hidden / 128) * 4, 256);
-  l->hq = take(cap * c.inter, 1024);
-  l->hs = take(cap * (c.inter / 128) * 4, 256);
+  // activations kept in bf16 travel as two e4m3 terms: every one of these four buffers twice, the
+  // second term right after the first (offsets below name the first)
+  const int64_t terms = bf16_activations(c) ? 2 : 1;
+  l->xq = take(terms * align_up(cap * c.hidden, 1024), 1024);
+  l->xs = take(terms * align_up(cap * (c.hidden / 128) * 4, 256), 256);
+  l->hq = take(terms * align_up(cap * c.inter, 1024), 1024);
+  l->hs = take(terms * align_up(cap * (c.inter / 128) * 4, 256), 256);
   l->rows = take(routes * c.hidden * 2, 1024);
   l->total_bytes = align_up(at, 256);
   l->block_m = bm;
@@ -509,7 +513,18 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   qp.scales_in = scales_in;
   qp.q_in_stride = q_in_stride;
   qp.scales_in_stride = scales_in_stride;
-  if (!q_in && routes_per_token > 1 && c.n_tokens >= kQuantOncePerTokenFrom) {
+  const bool split = bf16_activations(c);
+  const int64_t cap = l.capacity;
+  uint8_t* xq_lo = ws + l.xq + align_up(cap * c.hidden, 1024);
+  uint8_t* xs_lo = ws + l.xs + align_up(cap * (c.hidden / 128) * 4, 256);
+  uint8_t* hq_lo = ws + l.hq + align_up(cap * c.inter, 1024);
+  uint8_t* hs_lo = ws + l.hs + align_up(cap * (c.inter / 128) * 4, 256);
+  if (split) {
+    if (q_in) return fail(AKLR_ERR_BAD_ARGUMENT, "rows that arrive quantised cannot be bf16 activations");
+    qp.q_lo = xq_lo;
+    qp.scales_lo = xs_lo;
+  }
+  if (!split && !q_in && routes_per_token > 1 && c.n_tokens >= kQuantOncePerTokenFrom) {
     // quantise every token once (codes and row-major scale bytes parked in the space of the
     // per-route output rows, unused until the down projection), then copy per route
     uint8_t* tq = ws + l.rows;
@@ -543,7 +558,15 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   if (rc) return rc;
   rc = make_map_u8(&g1.map_x_rows64, ws + l.xq, l.capacity, c.hidden, 64);
   if (rc) return rc;
-  g1.small_boxes = small_activation_boxes(c);
+  g1.small_boxes = small_activation_boxes(c) && !split;
+  g1.split = split;
+  if (split) {
+    rc = make_map_u8(&g1.map_x_lo, xq_lo, l.capacity, c.hidden, 128);
+    if (rc) return rc;
+    g1.x_scale_lo = xs_lo;
+    g1.out_q_lo = hq_lo;
+    g1.out_scale_lo = hs_lo;
+  }
   g1.w_scale = w1_scale;
   g1.x_scale = ws + l.xs;
   g1.sorted_ids = sorted_ids;
@@ -562,7 +585,7 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   g1.out_dim = c.inter;
   g1.rows_per_expert = 2 * c.inter;
   g1.max_blocks = l.max_blocks;
-  g1.stages = grouped_gemm_mx_pick_stages(true);
+  g1.stages = grouped_gemm_mx_pick_stages(true, split);
   rc = launch_grouped_gemm_mx(g1, true, sms, stream);
   if (rc) return fail(rc, "MX gate_up grouped GEMM launch failed");
   g_launches += 1;
@@ -577,7 +600,13 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   if (rc) return rc;
   rc = make_map_u8(&g2.map_x_rows64, ws + l.hq, l.capacity, c.inter, 64);
   if (rc) return rc;
-  g2.small_boxes = small_activation_boxes(c);
+  g2.small_boxes = small_activation_boxes(c) && !split;
+  g2.split = split;
+  if (split) {
+    rc = make_map_u8(&g2.map_x_lo, hq_lo, l.capacity, c.inter, 128);
+    if (rc) return rc;
+    g2.x_scale_lo = hs_lo;
+  }
   g2.w_scale = w2_scale;
   g2.x_scale = ws + l.hs;
   g2.sorted_ids = sorted_ids;
@@ -591,7 +620,7 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   g2.out_dim = c.hidden;
   g2.rows_per_expert = c.hidden;
   g2.max_blocks = l.max_blocks;
-  g2.stages = grouped_gemm_mx_pick_stages(false);
+  g2.stages = grouped_gemm_mx_pick_stages(false, split);
   rc = launch_grouped_gemm_mx(g2, false, sms, stream);
   if (rc) return fail(rc, "MX down grouped GEMM launch failed");
   g_launches += 1;

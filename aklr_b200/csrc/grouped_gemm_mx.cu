@@ -40,9 +40,13 @@ constexpr int kBN = 256;
 constexpr int kABytes = kBM * 128;
 constexpr int kBBytes = kBN * 128;          // unpacked: one byte per e2m1 element in shared memory
 constexpr int kSfaBytes = 512;              // 128 rows x 4 K-steps
-constexpr int kStageBytes = kABytes + kBBytes + 2048;  // operands + scale factors (padded to 2 KB)
+// One pipeline stage: [activations 16 KB][second activation term 16 KB, SPLIT only][weights 32 KB]
+// [activation scales 512][weight scales 1024][second term's scales 512].
+__host__ __device__ constexpr int stage_bytes(bool split) { return (split ? 2 : 1) * kABytes + kBBytes + 2048; }
+__host__ __device__ constexpr int stage_b_offset(bool split) { return (split ? 2 : 1) * kABytes; }
+constexpr int kSfLoOffset = kSfaBytes + 1024;  // the second term's activation scales inside the 2 KB scale area
 constexpr bool kTileResidentScales = false;  // staging variant for short reductions; measured slower, kept for reference
-constexpr int kSfaCol = 256, kSfbCol = 260;  // TMEM columns after the 256 accumulator columns
+constexpr int kSfaCol = 256, kSfbCol = 260, kSfaLoCol = 268;  // TMEM columns after the 256 accumulator columns
 
 struct MxLayout {
   int off_out, off_rid, off_wgt, off_bars, total;
@@ -50,9 +54,9 @@ struct MxLayout {
 
 constexpr int kOutPassCols = 32;  // down: channels per thread staged per pass (64 bytes per row)
 
-__host__ __device__ inline MxLayout mx_layout(int stages, bool gate_up) {
+__host__ __device__ inline MxLayout mx_layout(int stages, bool gate_up, bool split) {
   MxLayout l;
-  l.off_out = stages * kStageBytes;  // down: per epilogue warp 32 rows x 64 bytes of bf16 output
+  l.off_out = stages * stage_bytes(split);  // down: per epilogue warp 32 rows x 64 bytes of bf16 output
   l.off_rid = l.off_out + (gate_up ? 0 : (kEpi / 32) * 32 * kOutPassCols * 2);
   l.off_wgt = l.off_rid + kBM * 4;
   l.off_bars = l.off_wgt + kBM * 4;
@@ -111,6 +115,16 @@ __device__ __forceinline__ int mxfp8_exponent(float amax) {
   return e < -126 ? -126 : (e > 127 ? 127 : e);
 }
 
+// Two values already divided by their group's scale -> their e4m3 codes and the codes of what the
+// first rounding left over, times lo_mul (2^4 unless the second scale was clamped): hi + lo / lo_mul
+// is the input exactly when it has 8 significant bits, as a bf16 value has.
+__device__ __forceinline__ void e4m3x2_two_terms(float s0, float s1, float lo_mul, uint16_t& hi, uint16_t& lo) {
+  hi = cvt_e4m3x2(s0, s1);
+  const __half2_raw back = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(hi), __NV_E4M3);
+  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&back));
+  lo = cvt_e4m3x2((s0 - f.x) * lo_mul, (s1 - f.y) * lo_mul);
+}
+
 // act(gate) * up for the activations of the reference's experts-only op other than SiLU
 // (aklr/ops/fused_moe/reference.py:113-121).  Deliberately NOT inlined: the epilogue calls it from a
 // loop unrolled 64 times, and with erff and tanhf expanded in every copy the loop grew to hundreds of
@@ -128,13 +142,19 @@ __device__ __noinline__ float gated_product_other(int activation, float gate, fl
   }
 }
 
-template <bool GATE_UP>
+// SPLIT: the activations are bf16 values carried as two e4m3 terms (MxQuantParams): per K step the
+// MMA warp issues the product of each term with the SAME weight tile and weight scales into the same
+// accumulator -- twice the tensor work of the MXFP8 path, no rounding of the activations.
+template <bool GATE_UP, bool SPLIT>
 __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __grid_constant__ MxGemmParams p) {
+  constexpr int kStageBytes = stage_bytes(SPLIT);
+  constexpr int kOffB = stage_b_offset(SPLIT);
+  constexpr int kOffSf = kOffB + kBBytes;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int KB = p.k >> 7;
   const int S = p.stages;
-  const MxLayout L = mx_layout(S, GATE_UP);
+  const MxLayout L = mx_layout(S, GATE_UP, SPLIT);
   int* rid_s = reinterpret_cast<int*>(smem + L.off_rid);
   float* wgt_s = reinterpret_cast<float*>(smem + L.off_wgt);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.off_bars);
@@ -164,6 +184,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
     fence_mbar_init();
     tma_prefetch_desc(&p.map_w);
     tma_prefetch_desc(&p.map_x);
+    if (SPLIT) tma_prefetch_desc(&p.map_x_lo);
   }
   if (warp == 1) {
     tmem_alloc(tmem_ptr, 512);
@@ -196,7 +217,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
         // lanes whose results are never stored.
         const CUtensorMap* map_x = &p.map_x;
         uint32_t x_bytes = kABytes;
-        if (p.small_boxes) {
+        if (!SPLIT && p.small_boxes) {
           const int id32 = p.sorted_ids[b * kBM + 32], id64 = p.sorted_ids[b * kBM + 64];
           if (id32 < 0) { map_x = &p.map_x_rows32; x_bytes = 32 * 128; }
           else if (id64 < 0) { map_x = &p.map_x_rows64; x_bytes = 64 * 128; }
@@ -206,13 +227,14 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
           uint8_t* st = smem + s * kStageBytes;
           // the transaction count of the unpacking fp4 load is its packed size (what crosses from
           // global memory), not the padded bytes it writes: expecting the padded size never completes
-          mbar_expect_tx(&full[s], x_bytes + kBBytes / 2);
+          mbar_expect_tx(&full[s], (SPLIT ? 2 : 1) * x_bytes + kBBytes / 2);
           tma_load_2d(st, map_x, &full[s], kb * 128, b * kBM);
+          if (SPLIT) tma_load_2d(st + kABytes, &p.map_x_lo, &full[s], kb * 128, b * kBM);
           if (GATE_UP) {
-            tma_load_2d(st + kABytes, &p.map_w, &full[s], kb * 128, w_row);
-            tma_load_2d(st + kABytes + kBBytes / 2, &p.map_w, &full[s], kb * 128, w_row + p.out_dim);
+            tma_load_2d(st + kOffB, &p.map_w, &full[s], kb * 128, w_row);
+            tma_load_2d(st + kOffB + kBBytes / 2, &p.map_w, &full[s], kb * 128, w_row + p.out_dim);
           } else {
-            tma_load_2d(st + kABytes, &p.map_w, &full[s], kb * 128, w_row);
+            tma_load_2d(st + kOffB, &p.map_w, &full[s], kb * 128, w_row);
           }
           if (++s == S) { s = 0; ph ^= 1; }
         }
@@ -227,8 +249,8 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
       int s = 0;
       uint32_t ph = 0;
       const uint32_t base = smem_u32(smem);
-      const uint64_t da0 = umma_desc_sw128(base), db0 = umma_desc_sw128(base + kABytes);
-      const uint64_t sfa0 = sf_desc(base + kABytes + kBBytes);
+      const uint64_t da0 = umma_desc_sw128(base), db0 = umma_desc_sw128(base + kOffB);
+      const uint64_t sfa0 = sf_desc(base + kOffSf);
       uint32_t step = 0;  // (stage * kStageBytes) >> 4, added to the address field of each descriptor
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_no) {
@@ -246,11 +268,16 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
           tmem_cp_32x128b_warpx4(tmem_base + kSfaCol, sfa);
           tmem_cp_32x128b_warpx4(tmem_base + kSfbCol, sfa + (kSfaBytes >> 4));
           tmem_cp_32x128b_warpx4(tmem_base + kSfbCol + 4, sfa + ((kSfaBytes + 512) >> 4));
+          if (SPLIT) tmem_cp_32x128b_warpx4(tmem_base + kSfaLoCol, sfa + (kSfLoOffset >> 4));
           const uint64_t da = da0 + step, db = db0 + step;
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
+          for (int k = 0; k < 4; ++k) {
             umma_mx(tmem_base, da + 2 * k, db + 2 * k, mx_idesc(kBN, k), tmem_base + kSfaCol, tmem_base + kSfbCol,
                     (kb > 0 || k > 0) ? 1u : 0u);
+            if (SPLIT)  // the second term: the next 16 KB of the stage, its own activation scales
+              umma_mx(tmem_base, da + (kABytes >> 4) + 2 * k, db + 2 * k, mx_idesc(kBN, k), tmem_base + kSfaLoCol,
+                      tmem_base + kSfbCol, 1u);
+          }
           tc_commit(&empty[s]);
           step += kStageBytes >> 4;
           if (++s == S) { s = 0; ph ^= 1; step = 0; }
@@ -321,7 +348,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
             bool got;
             got = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 25);
             if (!got) ok = false;
-            uint8_t* sf = smem + s * kStageBytes + kABytes + kBBytes;
+            uint8_t* sf = smem + s * kStageBytes + kOffSf;
             if (sw == 0) *reinterpret_cast<uint4*>(sf + lane * 16) = aq[kb & 3];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {  // row lane64 + 64 j = lane + 32 q with q = sw + 2 j
@@ -351,18 +378,20 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
         wsf[q] = p.w_scale + (static_cast<size_t>(e) * p.rows_per_expert + wrow) * KS;
       }
       const uint8_t* xsf = p.x_scale + static_cast<size_t>(b) * KB * kSfaBytes;
+      const uint8_t* xsf_lo = SPLIT ? p.x_scale_lo + static_cast<size_t>(b) * KB * kSfaBytes : nullptr;
       const int first = ((it0 & 1u) == static_cast<uint32_t>(sw)) ? 0 : 1;
       // ring of kDepth own K-blocks of scale words in registers: loaded long before their stage
       // frees up (down-projection rows are 64 bytes apart and miss to HBM on first touch)
       constexpr int kDepth = 3;
       uint32_t wq[kDepth][8];
-      uint4 aq[kDepth];
+      uint4 aq[kDepth], aq_lo[SPLIT ? kDepth : 1];
 #pragma unroll
       for (int d = 0; d < kDepth; ++d) {
         const int kb = first + 2 * d;
 #pragma unroll
         for (int q = 0; q < 8; ++q) wq[d][q] = kb < KB ? __ldg(reinterpret_cast<const uint32_t*>(wsf[q] + kb * 4)) : 0u;
         aq[d] = kb < KB ? __ldg(reinterpret_cast<const uint4*>(xsf + kb * kSfaBytes) + lane) : make_uint4(0, 0, 0, 0);
+        if (SPLIT) aq_lo[d] = kb < KB ? __ldg(reinterpret_cast<const uint4*>(xsf_lo + kb * kSfaBytes) + lane) : make_uint4(0, 0, 0, 0);
       }
       for (int kb0 = first; kb0 < KB && ok; kb0 += 2 * kDepth) {
 #pragma unroll
@@ -375,8 +404,9 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
             bool got;
             got = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 25);
             if (!got) ok = false;
-            uint8_t* sf = smem + s * kStageBytes + kABytes + kBBytes;
+            uint8_t* sf = smem + s * kStageBytes + kOffSf;
             *reinterpret_cast<uint4*>(sf + lane * 16) = aq[d];
+            if (SPLIT) *reinterpret_cast<uint4*>(sf + kSfLoOffset + lane * 16) = aq_lo[d];
 #pragma unroll
             for (int q = 0; q < 8; ++q)  // row lane + 32 q -> 16-byte line `lane`, word q % 4, chunk q / 4
               *reinterpret_cast<uint32_t*>(sf + kSfaBytes + (q >> 2) * 512 + lane * 16 + (q & 3) * 4) = wq[d][q];
@@ -388,6 +418,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
 #pragma unroll
               for (int q = 0; q < 8; ++q) wq[d][q] = __ldg(reinterpret_cast<const uint32_t*>(wsf[q] + nk * 4));
               aq[d] = __ldg(reinterpret_cast<const uint4*>(xsf + nk * kSfaBytes) + lane);
+              if (SPLIT) aq_lo[d] = __ldg(reinterpret_cast<const uint4*>(xsf_lo + nk * kSfaBytes) + lane);
             }
           }
         }
@@ -446,8 +477,8 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
         const float w1row = p.stage1_weights ? wgt_s[row] : 1.0f;  // exact when the weight is not applied here
         const bool silu = p.activation == AKLR_ACT_SILU;  // uniform over the grid
         // two 1 x 32 groups of this thread's 64 h channels
-        uint32_t packed[16];
-        uint32_t scale_bytes = 0;
+        uint32_t packed[16], packed_lo[SPLIT ? 16 : 1];
+        uint32_t scale_bytes = 0, scale_bytes_lo = 0;
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
           float m = 0.0f;
@@ -466,10 +497,25 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
           const int ex = mxfp8_exponent(m);
           const float inv = __uint_as_float(static_cast<uint32_t>(127 - ex) << 23);  // 2^-ex, exact
           scale_bytes |= static_cast<uint32_t>(ex + 127) << (8 * g);
+          if (SPLIT) {
+            // h stays the bf16 value it is: two e4m3 terms, the second at 2^(ex-4) (see MxQuantParams)
+            const int ex_lo = ex - 4 < -127 ? -127 : ex - 4;
+            const float lo_mul = __uint_as_float(static_cast<uint32_t>(127 + ex - ex_lo) << 23);
+            scale_bytes_lo |= static_cast<uint32_t>(ex_lo + 127) << (8 * g);
 #pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            packed[g * 8 + i / 4] = cvt_e4m3x2(acc[g * 32 + i] * inv, acc[g * 32 + i + 1] * inv) |
-                                    (static_cast<uint32_t>(cvt_e4m3x2(acc[g * 32 + i + 2] * inv, acc[g * 32 + i + 3] * inv)) << 16);
+            for (int i = 0; i < 32; i += 4) {
+              uint16_t h0, l0, h1, l1;
+              e4m3x2_two_terms(acc[g * 32 + i] * inv, acc[g * 32 + i + 1] * inv, lo_mul, h0, l0);
+              e4m3x2_two_terms(acc[g * 32 + i + 2] * inv, acc[g * 32 + i + 3] * inv, lo_mul, h1, l1);
+              packed[g * 8 + i / 4] = h0 | (static_cast<uint32_t>(h1) << 16);
+              packed_lo[g * 8 + i / 4] = l0 | (static_cast<uint32_t>(l1) << 16);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              packed[g * 8 + i / 4] = cvt_e4m3x2(acc[g * 32 + i] * inv, acc[g * 32 + i + 1] * inv) |
+                                      (static_cast<uint32_t>(cvt_e4m3x2(acc[g * 32 + i + 2] * inv, acc[g * 32 + i + 3] * inv)) << 16);
+          }
         }
         if (rid >= 0 && !bad) {
           uint8_t* dst = p.out_q + static_cast<size_t>(b * kBM + row) * p.out_dim + j * 128 + half * 64;
@@ -477,8 +523,16 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
           for (int v = 0; v < 4; ++v)
             *reinterpret_cast<uint4*>(dst + v * 16) = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
           // scale bytes in the order the down projection's tcgen05.cp wants them
-          *reinterpret_cast<uint16_t*>(p.out_scale + (static_cast<size_t>(b) * IB + j) * kSfaBytes + (row & 31) * 16 +
-                                       (row >> 5) * 4 + half * 2) = static_cast<uint16_t>(scale_bytes);
+          const size_t scale_at = (static_cast<size_t>(b) * IB + j) * kSfaBytes + (row & 31) * 16 + (row >> 5) * 4 + half * 2;
+          *reinterpret_cast<uint16_t*>(p.out_scale + scale_at) = static_cast<uint16_t>(scale_bytes);
+          if (SPLIT) {
+            uint8_t* dst_lo = p.out_q_lo + static_cast<size_t>(b * kBM + row) * p.out_dim + j * 128 + half * 64;
+#pragma unroll
+            for (int v = 0; v < 4; ++v)
+              *reinterpret_cast<uint4*>(dst_lo + v * 16) =
+                  make_uint4(packed_lo[4 * v], packed_lo[4 * v + 1], packed_lo[4 * v + 2], packed_lo[4 * v + 3]);
+            *reinterpret_cast<uint16_t*>(p.out_scale_lo + scale_at) = static_cast<uint16_t>(scale_bytes_lo);
+          }
         }
       } else {
         // A thread owns 128 channels of one token: direct stores would be 16 bytes per lane at 32
@@ -576,8 +630,27 @@ __global__ void __launch_bounds__(256) gather_quant_mxfp8_kernel(MxQuantParams p
     const int ex = mxfp8_exponent(m);
     const float inv = __uint_as_float(static_cast<uint32_t>(127 - ex) << 23);
     uint2 out;
-    out.x = cvt_e4m3x2(v[0] * inv, v[1] * inv) | (static_cast<uint32_t>(cvt_e4m3x2(v[2] * inv, v[3] * inv)) << 16);
-    out.y = cvt_e4m3x2(v[4] * inv, v[5] * inv) | (static_cast<uint32_t>(cvt_e4m3x2(v[6] * inv, v[7] * inv)) << 16);
+    if (p.q_lo) {  // the value itself, as two e4m3 terms
+      const int ex_lo = ex - 4 < -127 ? -127 : ex - 4;
+      const float lo_mul = __uint_as_float(static_cast<uint32_t>(127 + ex - ex_lo) << 23);
+      uint16_t hi[4], lo[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) e4m3x2_two_terms(v[2 * i] * inv, v[2 * i + 1] * inv, lo_mul, hi[i], lo[i]);
+      out.x = hi[0] | (static_cast<uint32_t>(hi[1]) << 16);
+      out.y = hi[2] | (static_cast<uint32_t>(hi[3]) << 16);
+      uint2 out_lo;
+      out_lo.x = lo[0] | (static_cast<uint32_t>(lo[1]) << 16);
+      out_lo.y = lo[2] | (static_cast<uint32_t>(lo[3]) << 16);
+      *reinterpret_cast<uint2*>(p.q_lo + static_cast<size_t>(row) * p.hidden + grp * 32 + sub * 8) = out_lo;
+      if (sub == 0) {
+        const int b = row >> 7, r = row & 127, kb = grp >> 2, ks = grp & 3;
+        p.scales_lo[(static_cast<size_t>(b) * KB + kb) * kSfaBytes + (r & 31) * 16 + (r >> 5) * 4 + ks] =
+            static_cast<uint8_t>(ex_lo + 127);
+      }
+    } else {
+      out.x = cvt_e4m3x2(v[0] * inv, v[1] * inv) | (static_cast<uint32_t>(cvt_e4m3x2(v[2] * inv, v[3] * inv)) << 16);
+      out.y = cvt_e4m3x2(v[4] * inv, v[5] * inv) | (static_cast<uint32_t>(cvt_e4m3x2(v[6] * inv, v[7] * inv)) << 16);
+    }
     *reinterpret_cast<uint2*>(p.q + static_cast<size_t>(row) * p.hidden + grp * 32 + sub * 8) = out;
     if (sub == 0) {
       if (p.row_major_scales) {  // for transport to another rank: [row, hidden/32]
@@ -647,6 +720,7 @@ __global__ void __launch_bounds__(256) gather_rows_mxfp8_kernel(MxQuantParams p)
 
 int launch_gather_quant_mxfp8(const MxQuantParams& p, cudaStream_t stream) {
   if (p.hidden % 128 != 0) return AKLR_ERR_UNSUPPORTED_SHAPE;
+  if ((p.q_lo != nullptr) != (p.scales_lo != nullptr) || (p.q_lo && (p.q_in || p.row_major_scales))) return AKLR_ERR_BAD_ARGUMENT;
   if (p.n_rows == 0) return AKLR_OK;
   if (p.q_in) {
     if (!p.sorted_ids || !p.scales_in) return AKLR_ERR_BAD_ARGUMENT;
@@ -660,16 +734,18 @@ int launch_gather_quant_mxfp8(const MxQuantParams& p, cudaStream_t stream) {
   return launch_kernel(gather_quant_mxfp8_kernel, dim3(grid), dim3(256), 0, stream, 1, p) == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
 }
 
-int grouped_gemm_mx_pick_stages(bool gate_up) {
+int grouped_gemm_mx_pick_stages(bool gate_up, bool split) {
   for (int s = 4; s >= 2; --s)
-    if (mx_layout(s, gate_up).total + 1024 <= 227 * 1024) return s;
+    if (mx_layout(s, gate_up, split).total + 1024 <= 227 * 1024) return s;
   return 0;
 }
 
 int launch_grouped_gemm_mx(const MxGemmParams& p, bool gate_up, int sm_count, cudaStream_t stream) {
   if (p.k % 128 != 0 || p.max_blocks < 1 || p.stages < 2) return AKLR_ERR_UNSUPPORTED_SHAPE;
   if (gate_up ? (p.out_dim % 128 != 0) : (p.out_dim % 256 != 0)) return AKLR_ERR_UNSUPPORTED_SHAPE;
-  const size_t smem = static_cast<size_t>(mx_layout(p.stages, gate_up).total) + 1024;
+  const bool split = p.split != 0;
+  if (split && (!p.x_scale_lo || (gate_up && (!p.out_q_lo || !p.out_scale_lo)))) return AKLR_ERR_BAD_ARGUMENT;
+  const size_t smem = static_cast<size_t>(mx_layout(p.stages, gate_up, split).total) + 1024;
   if (smem > 227 * 1024) return AKLR_ERR_UNSUPPORTED_SHAPE;
   const long long tiles = static_cast<long long>(p.max_blocks) * (gate_up ? p.out_dim / 128 : p.out_dim / 256);
   const int grid = static_cast<int>(tiles < sm_count ? tiles : sm_count);
@@ -677,7 +753,8 @@ int launch_grouped_gemm_mx(const MxGemmParams& p, bool gate_up, int sm_count, cu
     if (ensure_max_dynamic_smem(reinterpret_cast<const void*>(kernel)) != AKLR_OK) return AKLR_ERR_CUDA;
     return launch_kernel(kernel, dim3(grid), dim3(kThreads), smem, stream, 1, p) == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
   };
-  return gate_up ? run(grouped_gemm_mx_kernel<true>) : run(grouped_gemm_mx_kernel<false>);
+  if (split) return gate_up ? run(grouped_gemm_mx_kernel<true, true>) : run(grouped_gemm_mx_kernel<false, true>);
+  return gate_up ? run(grouped_gemm_mx_kernel<true, false>) : run(grouped_gemm_mx_kernel<false, false>);
 }
 
 }  // namespace aklr

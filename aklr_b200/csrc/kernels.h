@@ -124,6 +124,11 @@ struct MxQuantParams {
   int n_rows, hidden, routes_per_token;
   int row_major_scales;       // write scales as [row, hidden/32] (for transport) instead
   int q_in_stride, scales_in_stride;  // rows quantised before: bytes between source rows (0: dense)
+  // Activations kept in bf16 (no MXFP8 rounding): every value travels as TWO e4m3 codes whose block
+  // scales are 2^ex and 2^(ex-4), hi + lo = the bf16 value exactly (8 significant bits = 4 + 4) except
+  // for elements below 2^-22 of their group's largest.  q_lo / scales_lo: the second term, same shapes.
+  uint8_t* q_lo;
+  uint8_t* scales_lo;
 };
 int launch_gather_quant_mxfp8(const MxQuantParams& p, cudaStream_t stream);
 
@@ -149,8 +154,15 @@ struct MxGemmParams {
   float beta, linear_beta;     // gate_up, AKLR_ACT_SITUV2: saturation of gate and up
   const float* stage1_weights; // gate_up: route weights applied to the projection before the activation, or null
   int k, out_dim, rows_per_expert, max_blocks, stages;
+  // bf16 activations as two e4m3 terms (see MxQuantParams): the second term's operand map, scales and,
+  // for gate_up, outputs; split != 0 issues two MMAs per K step on the same weight tile
+  int split;
+  CUtensorMap map_x_lo;
+  const uint8_t* x_scale_lo;
+  uint8_t* out_q_lo;
+  uint8_t* out_scale_lo;
 };
-int grouped_gemm_mx_pick_stages(bool gate_up);
+int grouped_gemm_mx_pick_stages(bool gate_up, bool split = false);
 int launch_grouped_gemm_mx(const MxGemmParams& p, bool gate_up, int sm_count, cudaStream_t stream);
 
 struct CombineParams {

@@ -305,12 +305,19 @@ def fused_experts_mxfp4(
     linear_beta: float | None = None,
     num_local_tokens: torch.Tensor | None = None,
     variant: int = 0,
+    act_bits: int = 8,
 ):
-    """MXFP4-weight experts with MXFP8 activations, routing given (block-scaled tcgen05 MMA).
+    """MXFP4-weight experts, routing given (block-scaled tcgen05 MMA).  ``act_bits`` 8: activations
+    quantised to MXFP8 per 1 x 32; 16: kept in bf16 (each value enters the MMAs as two e4m3 terms whose
+    sum is the bf16 value) -- the reference's gate_mode 'interleave' and gpt-oss swiglu below 256 rows.
     ``activation`` one of ACTIVATIONS; ``weight_in_stage1`` applies the route weight to the gate_up
     projection instead of the output; ``num_local_tokens`` (int32 device scalar) zeroes the rows at
     or past it (aklr/ops/fused_moe/reference.py:85-127)."""
     device = _need_cuda(hidden_states, topk_ids, topk_weights, w1, w1_scale, w2, w2_scale, expert_map, out, num_local_tokens)
+    if act_bits not in (8, 16):
+        raise ValueError("act_bits: 8 (MXFP8 activations) or 16 (bf16 activations)")
+    if act_bits == 16:
+        variant |= _lib.VARIANT_BF16_ACTIVATIONS
     options = _lib.MxOptions(
         ACTIVATIONS[activation], int(weight_in_stage1), float(swiglu_limit or 0.0), float(beta or 0.0),
         float(linear_beta or 0.0), _ptr(num_local_tokens),

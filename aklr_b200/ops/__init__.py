@@ -555,14 +555,29 @@ def _mx_weights_key(call: Mapping[str, Any], hidden: int, device) -> tuple | Non
     return e, inter
 
 
+def _mx_act_bits(call, activation: str, n_tokens: int) -> int | None:
+    """Bits the activations keep on the MXFP4 path, as the reference decides it
+    (aklr/ops/fused_moe/reference.py:90-97): 16 (bf16, nothing rounded) under gate_mode 'interleave' and for
+    gpt-oss swiglu below 256 rows, whatever act_quant says; else act_quant, of which 8 (MXFP8) is served."""
+    if call["gate_mode"] == "interleave" or (activation == "swiglu" and n_tokens < 256):
+        return 16
+    return 8 if call["act_quant"] == 8 else None
+
+
 def _fused_moe_mx_key(call, x, device, n_tokens, hidden):
-    """MXFP4 experts (quant_type per_1x32) with activations quantised to MXFP8 (act_quant 8) and
-    gate rows before up rows: the activations silu, gelu, gpt-oss's swiglu (from 256 tokens, where the
-    reference quantises; it needs its clamp) and situv2 (with both betas); an optional clamp; the
-    route weight in either stage; an expert mask, with or without a count of rows received."""
+    """MXFP4 experts (quant_type per_1x32), weights row-major with gate rows before up rows.  Activations
+    quantised to MXFP8 (act_quant 8), or kept in bf16 where the reference keeps them: gate_mode 'interleave'
+    (DeepSeek-V4's clamped SwiGLU: silu with its clamp) and gpt-oss swiglu below 256 tokens.  Activations
+    silu, gelu, gpt-oss's swiglu (with its clamp) and situv2 (with both betas); an optional clamp; the route
+    weight in either stage; an expert mask, with or without a count of rows received."""
     activation = _attr_name(call["activation"]) or "silu"
-    if call["act_quant"] != 8 or activation not in moe.ACTIVATIONS:
+    if activation not in moe.ACTIVATIONS or call["gate_mode"] not in (None, "separated", "interleave"):
         return None
+    act_bits = _mx_act_bits(call, activation, n_tokens)
+    if act_bits is None:
+        return None
+    if call["gate_mode"] == "interleave" and (activation != "silu" or call["swiglu_limit"] is None):
+        return None  # the reference's constraint: interleave is silu with the clamp
     if call["w1_scale"] is None or call["w2_scale"] is None:
         return None
     weights = _mx_weights_key(call, hidden, device)
@@ -575,7 +590,7 @@ def _fused_moe_mx_key(call, x, device, n_tokens, hidden):
     limit = call["swiglu_limit"]
     if limit is not None and not (isinstance(limit, (int, float)) and limit > 0):
         return None
-    if activation == "swiglu" and (limit is None or n_tokens < 256):
+    if activation == "swiglu" and limit is None:
         return None
     betas = (call["beta"], call["linear_beta"])
     if activation == "situv2":
@@ -586,7 +601,7 @@ def _fused_moe_mx_key(call, x, device, n_tokens, hidden):
     received = call["num_local_tokens"]
     if received is not None and (call["expert_mask"] is None or not tensor_ok(received, torch.int32, 1, device) or received.numel() != 1):
         return None
-    if call["gate_mode"] not in (None, "separated") or call["out_dtype"] not in (None, BF16):
+    if call["out_dtype"] not in (None, BF16):
         return None
     ids, wts = call["topk_ids"], call["topk_weights"]
     if not tensor_ok(ids, torch.int32, 2, device) or not tensor_ok(wts, torch.float32, 2, device):
@@ -600,7 +615,7 @@ def _fused_moe_mx_key(call, x, device, n_tokens, hidden):
     if out is not None and (not tensor_ok(out, BF16, 2, device) or out.shape != x.shape):
         return None
     return ("mxfp4", hidden, weights[0], weights[1], ids.shape[1], mask is not None, limit is not None, activation,
-            call["doweight_stage1"], received is not None)
+            call["doweight_stage1"], received is not None, act_bits)
 
 
 def _fused_moe_key(call):
@@ -671,6 +686,7 @@ def _fused_moe_run(call, out):
             beta=call["beta"],
             linear_beta=call["linear_beta"],
             num_local_tokens=call["num_local_tokens"],
+            act_bits=_mx_act_bits(call, _attr_name(call["activation"]) or "silu", call["hidden_states"].shape[0]),
         )
         return
     moe.fused_experts_fp8(

@@ -76,6 +76,13 @@ typedef struct aklr_moe_config {
 #define AKLR_VARIANT_CTA_PAIRS 2              /* token-major GEMMs as CTA pairs (cta_group::2, no multicast) */
 #define AKLR_VARIANT_SEPARATE_PROLOGUE 4      /* 1..8 tokens: routing and sort as two kernels, not one */
 #define AKLR_VARIANT_FULL_ACTIVATION_BOXES 8  /* MXFP4 GEMMs load all 128 activation rows of every block */
+/* A numerics mode rather than a kernel choice (it also sizes the workspace, so set it before asking for the layout):
+ * the MXFP4 expert entry points keep the activations in bf16 instead of rounding them to MXFP8 -- what the reference's
+ * fused_moe does under gate_mode "interleave" and for gpt-oss swiglu below 256 rows (aklr/ops/fused_moe/
+ * reference.py:90-93) and its deepseek_v2_mxfp4_moe always (aklr/plugins/sglang/models/deepseek_v2/reference.py:91-111).
+ * Every activation enters the block-scaled MMAs as TWO e4m3 terms at scales 2^ex and 2^(ex-4) whose sum is the bf16 value
+ * exactly (8 significant bits = 4 + 4; elements below 2^-22 of their 32-group's largest lose low bits). */
+#define AKLR_VARIANT_BF16_ACTIVATIONS 16
 
 /* Byte offsets of the intermediates inside the workspace (for tests and debuggers). */
 typedef struct aklr_moe_workspace_layout {

@@ -406,7 +406,9 @@ def mx_experts(
     num_local_tokens: int | None = None,
 ) -> torch.Tensor:
     """MXFP4-weight experts given the routing: activations MXFP8 (act_bits 8) or MXFP4 (4) per
-    1 x 32, the gated product rounded to bf16 before it is quantised, each route weighted,
+    1 x 32, or left as they are (16: what the reference does under gate_mode 'interleave' and for
+    gpt-oss swiglu below 256 rows, aklr/ops/fused_moe/reference.py:90-93), the gated product rounded
+    to bf16 before it is quantised, each route weighted,
     the routes of a token summed.  Negative ids add nothing.  ``swiglu_limit`` clamps gate
     (above) and up (both sides) before the activation when given.
     ``activation`` silu, gelu (erf), swiglu (gpt-oss: gate sigmoid(1.702 gate) (up + 1)) or situv2
@@ -415,7 +417,9 @@ def mx_experts(
     ``num_local_tokens`` add nothing.
     Follows ``fused_moe_reference`` (aklr/ops/fused_moe/reference.py:64-127) and
     ``mega_moe_reference`` (aklr/ops/mega_moe/reference.py:18-48)."""
-    quantize = mxfp8_input if act_bits == 8 else mxfp4_input
+    if act_bits not in (4, 8, 16):
+        raise ValueError("act_bits: 4 (MXFP4), 8 (MXFP8) or 16 (activations kept in bf16)")
+    quantize = mxfp8_input if act_bits == 8 else mxfp4_input if act_bits == 4 else (lambda t: t)
     weights = weights.float()
     if num_local_tokens is not None:
         ids = ids.clone()

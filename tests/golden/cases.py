@@ -119,6 +119,14 @@ def mx_variants():
         ("stage1", mx_case(15), {"doweight_stage1": True}, {"weight_in_stage1": True}),
         ("local", {**local, **held, "expert_mask": mask, "num_local_tokens": torch.tensor([9], dtype=torch.int32)},
          {"has_expert_mask": True, "has_num_local_tokens": True}, {"num_local_tokens": 9}),
+        # activations kept in bf16: DeepSeek-V4's clamped SwiGLU (gate_mode 'interleave', with the expert mask and
+        # the rows-received bound its published workload has), and gpt-oss swiglu below 256 rows
+        ("interleave", {**mx_case(16, tokens=40), **{k: mx_case(16, tokens=40)[k][:4] for k in ("w1", "w1_scale", "w2", "w2_scale")},
+                        "expert_mask": mask, "num_local_tokens": torch.tensor([33], dtype=torch.int32), "swiglu_limit": 7.0},
+         {"gate_mode": "interleave", "has_expert_mask": True, "has_num_local_tokens": True},
+         {"act_bits": 16, "swiglu_limit": 7.0, "num_local_tokens": 33}),
+        ("swiglu_bf16", {**mx_case(17, tokens=70), "swiglu_limit": 7.0}, {"activation": "swiglu"},
+         {"activation": "swiglu", "swiglu_limit": 7.0, "act_bits": 16}),
     ]
 
 

@@ -205,7 +205,7 @@ def main() -> None:
     # the op's other attributes at act_quant 8: activations, stage-1 weighting, rows not received
     for name, vargs, vattrs, _ in cases.mx_variants():
         point.attrs.update({"act_quant": 8, "activation": "silu", "doweight_stage1": False, "has_expert_mask": False,
-                            "has_num_local_tokens": False, **vattrs})
+                            "has_num_local_tokens": False, "gate_mode": "separated", **vattrs})
         point.axes["n_tokens"] = vargs["hidden_states"].shape[0]
         out[f"mx_moe_{name}.out"] = f32(fused_moe_reference(point, vargs))
         for k, v in vargs.items():

@@ -102,3 +102,27 @@ def test_mxfp4_layer_from_logits_with_deepseek_routing():
     ref = orc.mx_experts(hidden, ids, w, w1, s1, w2, s2, act_bits=8)
     gates = orc.output_gates(out.cpu(), ref)
     assert orc.gates_pass(gates, min_sqnr_db=30.0), gates
+
+
+@pytest.mark.parametrize("shape", [(256, 128, 6, 2, 40), (512, 256, 8, 4, 150), (1024, 384, 4, 2, 300), (7168, 2048, 3, 2, 200)])
+@pytest.mark.parametrize("limit", [None, 7.0])
+def test_mxfp4_experts_with_bf16_activations_match_the_oracle(shape, limit):
+    """Activations kept in bf16 (the reference's gate_mode 'interleave' and small-batch swiglu): every value enters
+    the block-scaled MMAs as two e4m3 terms whose sum is the bf16 value, so the result is the oracle's over
+    unquantised activations up to float32 summation order -- far inside the gates (the last shape has DeepSeek-V3's
+    widths: 56 and 16 K-blocks per tile)."""
+    from aklr_b200.moe import fused_experts_mxfp4
+
+    hidden, inter, experts, topk, tokens = shape
+    x, ids, wts, w1, s1, w2, s2 = case(hidden, inter, experts, topk, tokens, seed=100 + tokens)
+    x = (x.float() * torch.exp2(torch.randint(-6, 7, (tokens, 1)).float())).to(torch.bfloat16)  # rows of very different size
+    d = dev()
+    out, ws = fused_experts_mxfp4(x.to(d), ids.to(d), wts.to(d), w1.to(d), s1.to(d), w2.to(d), s2.to(d), swiglu_limit=limit,
+                                  return_workspace=True, act_bits=16)
+    ws.check_status()
+    ref = orc.mx_experts(x, ids.long(), wts, w1, s1, w2, s2, swiglu_limit=limit, act_bits=16)
+    gates = orc.output_gates(out.cpu(), ref)
+    assert orc.gates_pass(gates, min_sqnr_db=40.0), gates
+    rounded = orc.mx_experts(x, ids.long(), wts, w1, s1, w2, s2, swiglu_limit=limit, act_bits=8)
+    # and it is the unrounded statement it matches, not the MXFP8 one
+    assert orc.sqnr_db(out.cpu().float(), orc.bf16_round(ref)) > orc.sqnr_db(out.cpu().float(), orc.bf16_round(rounded)) + 6.0

@@ -233,10 +233,24 @@ def test_fused_moe_op_mxfp4_attributes(ops):
     ref = orc.mx_experts(x, slot, wts, w1[held], s1[held], w2[held], s2[held], num_local_tokens=211)
     check(out, ref, "mask + rows received")
     assert not out[211:].any() and out[:211].any()
-    # out of contract: swiglu below 256 tokens or without its clamp, situv2 without its betas, a row count without a mask
+    # activations kept in bf16, as the reference keeps them: gate_mode 'interleave' (silu with its clamp; the op's
+    # default act_quant) with the mask and the rows-received bound, and gpt-oss swiglu below 256 tokens
+    kept = dict(quant_type="per_1x32", w1_scale=s1[held].to(d), w2_scale=s2[held].to(d))
+    out = ops.fused_moe(x.to(d), w1[held].to(d), w2[held].to(d), wts.to(d), ids.to(d), expert_mask=mask.to(d), gate_mode="interleave",
+                        swiglu_limit=7.0, num_local_tokens=received.to(d), **kept)
+    check(out, orc.mx_experts(x, slot, wts, w1[held], s1[held], w2[held], s2[held], num_local_tokens=211, swiglu_limit=7.0, act_bits=16),
+          "interleave: bf16 activations")
     few = dict(quant_type="per_1x32", w1_scale=s1.to(d), w2_scale=s2.to(d), act_quant=8)
-    assert ops.fused_moe(x[:100].to(d), w1.to(d), w2.to(d), wts[:100].to(d), ids[:100].to(d), activation="swiglu", swiglu_limit=7.0, **few) is ops.FallbackReason.OUT_OF_CONTRACT
+    out = ops.fused_moe(x[:100].to(d), w1.to(d), w2.to(d), wts[:100].to(d), ids[:100].to(d), activation="swiglu", swiglu_limit=7.0, **few)
+    check(out, orc.mx_experts(x[:100], ids[:100].long(), wts[:100], w1, s1, w2, s2, activation="swiglu", swiglu_limit=7.0, act_bits=16),
+          "swiglu below 256 rows: bf16 activations")
+    # out of contract: swiglu or interleave without the clamp, interleave with another activation, situv2 without its
+    # betas, a row count without a mask, MXFP4 activations
     assert run(activation="swiglu") is ops.FallbackReason.OUT_OF_CONTRACT
+    assert run(gate_mode="interleave") is ops.FallbackReason.OUT_OF_CONTRACT
+    assert run(gate_mode="interleave", activation="gelu", swiglu_limit=7.0) is ops.FallbackReason.OUT_OF_CONTRACT
+    assert ops.fused_moe(x.to(d), w1.to(d), w2.to(d), wts.to(d), ids.to(d), quant_type="per_1x32", w1_scale=s1.to(d),
+                         w2_scale=s2.to(d)) is ops.FallbackReason.OUT_OF_CONTRACT
     assert run(activation="situv2", beta=3.0) is ops.FallbackReason.OUT_OF_CONTRACT
     assert run(num_local_tokens=received.to(d)) is ops.FallbackReason.OUT_OF_CONTRACT
 
