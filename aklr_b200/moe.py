@@ -354,14 +354,18 @@ def fused_moe_mxfp4(
     out: torch.Tensor | None = None,
     workspace: Workspace | None = None,
     return_workspace: bool = False,
+    act_bits: int = 8,
 ):
-    """The whole MXFP4 layer from router logits (the routing of ``fused_moe_fp8``)."""
+    """The whole MXFP4 layer from router logits (the routing of ``fused_moe_fp8``).  ``act_bits`` as in
+    ``fused_experts_mxfp4``: 8 MXFP8 activations, 16 activations kept in bf16."""
     device = _need_cuda(hidden_states, logits, bias, w1, w1_scale, w2, w2_scale, out)
     e, inter, h = _check_mx_weights(hidden_states, w1, w1_scale, w2, w2_scale)
     n_tokens, n_routed = logits.shape
     if n_routed + routing.n_shared != e or hidden_states.shape[0] != n_tokens:
         raise ValueError("w1 must hold the routed experts followed by the shared ones")
-    cfg = _config(n_tokens, h, inter, n_routed, routing, logits, bias, 128)
+    if act_bits not in (8, 16):
+        raise ValueError("act_bits: 8 (MXFP8 activations) or 16 (bf16 activations)")
+    cfg = _config(n_tokens, h, inter, n_routed, routing, logits, bias, 128, variant=_lib.VARIANT_BF16_ACTIVATIONS if act_bits == 16 else 0)
     ws = workspace or Workspace(cfg, device)
     if out is None:
         out = torch.empty_like(hidden_states)

@@ -35,6 +35,7 @@ __all__ = [
     "LoadError",
     "biased_grouped_topk",
     "deepseek_v2_fp8_moe",
+    "deepseek_v2_mxfp4_moe",
     "fused_moe",
     "init",
     "mega_moe",
@@ -174,6 +175,84 @@ DEEPSEEK_V2_FP8_MOE = OpContract(
     alloc=_layer_alloc,
     run=_deepseek_run,
 )
+
+
+# --------------------------------------------------------------------------------------------------
+# deepseek_v2_mxfp4_moe@1.0 (aklr/plugins/sglang/models/deepseek_v2/contract.py:93-176): the same block with
+# MXFP4 experts, ungrouped routing, a float32 correction bias, and activations that are never quantised
+# --------------------------------------------------------------------------------------------------
+def _deepseek_mx_key(call):
+    x, rw, bias = call["hidden_states"], call["router_weight"], call["correction_bias"]
+    if not tensor_ok(x, BF16, 2):
+        return None
+    device = x.device
+    n_tokens, hidden = x.shape
+    if not (1 <= n_tokens <= MAX_TOKENS):
+        return None
+    if not tensor_ok(rw, BF16, 2, device) or rw.shape[1] != hidden:
+        return None
+    n_routed = rw.shape[0]
+    if not tensor_ok(bias, torch.float32, 1, device) or bias.shape[0] != n_routed:
+        return None
+    weights = _mx_weights_key(call, hidden, device)
+    if weights is None or weights[0] != n_routed + 1 or not (1 <= n_routed <= 1024) or weights[1] % 256:
+        return None
+    topk = call["topk"]
+    if not isinstance(topk, int) or isinstance(topk, bool) or not (1 <= topk <= min(31, n_routed)):
+        return None
+    if call["num_expert_group"] != 1 or call["topk_group"] != 1:
+        return None
+    if _attr_name(call["scoring_func"]) != "sigmoid" or not isinstance(call["renormalize"], bool):
+        return None
+    factor = call["routed_scaling_factor"]
+    if not isinstance(factor, (int, float)) or not math.isfinite(factor) or factor <= 0:
+        return None
+    return ("row_major", hidden, n_routed, weights[1], topk, call["renormalize"], float(factor))
+
+
+def _deepseek_mx_run(call, out):
+    x = call["hidden_states"]
+    logits = moe.router_logits(x, call["router_weight"])
+    routing = moe.Routing(topk=call["topk"], scoring="sigmoid", n_shared=1, renormalize=call["renormalize"],
+                          routed_scaling_factor=float(call["routed_scaling_factor"]))
+    moe.fused_moe_mxfp4(
+        x, logits, call["correction_bias"], call["w1"].view(torch.uint8), call["w1_scale"].view(torch.uint8),
+        call["w2"].view(torch.uint8), call["w2_scale"].view(torch.uint8), routing, out=out, act_bits=16,
+    )
+
+
+DEEPSEEK_V2_MXFP4_MOE = OpContract(
+    contract_id="deepseek_v2_mxfp4_moe@1.0",
+    description=(
+        "sglang's DeepseekV2MoE on one rank with MXFP4 experts (fp4 values at an e8m0 scale per 32) and the shared "
+        "expert in their last slot: router logits in bf16, sigmoid scores + float32 correction bias, plain top-k, "
+        "renormalised unbiased scores x routed_scaling_factor, shared expert at weight 1; each expert "
+        "down(silu(gate(x)) * up(x)) on activations that are not quantised."
+    ),
+    params=list(DEEPSEEK_V2_FP8_MOE.params),
+    outputs=["out"],
+    key=_deepseek_mx_key,
+    alloc=_layer_alloc,
+    run=_deepseek_mx_run,
+)
+
+
+@api(DEEPSEEK_V2_MXFP4_MOE)
+def deepseek_v2_mxfp4_moe(
+    hidden_states,
+    router_weight,
+    correction_bias,
+    w1,
+    w1_scale,
+    w2,
+    w2_scale,
+    topk,
+    num_expert_group,
+    topk_group,
+    renormalize,
+    scoring_func,
+    routed_scaling_factor,
+): ...
 
 
 @api(DEEPSEEK_V2_FP8_MOE)

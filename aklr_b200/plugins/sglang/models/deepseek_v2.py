@@ -1,15 +1,17 @@
-"""DeepSeek-V2/V3 on sglang: ``DeepseekV2MoE.forward_normal`` served by ``deepseek_v2_fp8_moe`` (the
-reference routes the same function: aklr/plugins/sglang/models/deepseek_v2/api.py:53-139)."""
+"""DeepSeek-V2/V3 on sglang: ``DeepseekV2MoE.forward_normal`` served by ``deepseek_v2_fp8_moe`` (experts in FP8
+at a scale per 128 x 128 block) or ``deepseek_v2_mxfp4_moe`` (Quark's MXFP4 experts, ungrouped routing) -- the
+reference routes the same function to the same two ops: aklr/plugins/sglang/models/deepseek_v2/api.py:53-139."""
 
 from __future__ import annotations
 
 from aklr_b200.core.dispatch import FallbackReason
-from aklr_b200.ops import deepseek_v2_fp8_moe
+from aklr_b200.ops import deepseek_v2_fp8_moe, deepseek_v2_mxfp4_moe
 from aklr_b200.plugins.sglang.conditions import leave_to_sglang, when
 from aklr_b200.plugins.sglang.hook import sglang_route
 from aklr_b200.plugins.sglang.models import moe_blocks
 
 TARGET = "sglang.srt.models.deepseek_v2.DeepseekV2MoE.forward_normal"
+EXPERT_FORMATS = ("QuarkW4A4MXFp4MoE", "Fp8MoEMethod")  # the experts' formats the two ops take
 
 
 def _unmet(mlp, call_flags: dict) -> str | None:
@@ -21,19 +23,30 @@ def _unmet(mlp, call_flags: dict) -> str | None:
     return (
         when(moe_blocks.masks_padded_rows(), "no padded rows masked by the top-k")
         or moe_blocks.runtime_unmet()
-        or moe_blocks.experts_unmet(mlp.experts, ("Fp8MoEMethod",))
+        or moe_blocks.experts_unmet(mlp.experts, EXPERT_FORMATS)
         or when(mlp._fuse_shared_experts_inside_sbo, "shared experts not fused into single-batch overlap")
         or when(mlp.is_hash, "no hash routing")
         or when(mlp.gate.e_score_correction_bias_vl is not None, "no vision-language correction bias")
     )
 
 
-def _moe_arguments(mlp, hidden_states) -> dict:
-    """``deepseek_v2_fp8_moe``'s keyword arguments read off the module."""
+def _moe_call(mlp, hidden_states):
+    """(op, keyword arguments) for the experts' format."""
+    if moe_blocks.experts_format(mlp.experts) == "QuarkW4A4MXFp4MoE":
+        arguments = _moe_arguments(mlp, hidden_states, keep_bias_dtype=True, weights=False)
+        experts = mlp.experts
+        arguments.update(w1=experts.w13_weight, w1_scale=experts.w13_weight_scale, w2=experts.w2_weight, w2_scale=experts.w2_weight_scale)
+        return deepseek_v2_mxfp4_moe, arguments
+    return deepseek_v2_fp8_moe, _moe_arguments(mlp, hidden_states)
+
+
+def _moe_arguments(mlp, hidden_states, keep_bias_dtype: bool = False, weights: bool = True) -> dict:
+    """The layer ops' keyword arguments read off the module (``deepseek_v2_fp8_moe`` takes the bias in the logits'
+    dtype, ``deepseek_v2_mxfp4_moe`` as the module holds it, in float32)."""
     routing = mlp.topk.topk_config
     groups, kept_groups = (routing.num_expert_group, routing.topk_group) if routing.use_grouped_topk else (1, 1)
     bias = routing.correction_bias
-    if bias is not None and bias.dtype != hidden_states.dtype:
+    if not keep_bias_dtype and bias is not None and bias.dtype != hidden_states.dtype:
         bias = routing.correction_bias_for_dtype(hidden_states.dtype)  # the op adds it to logits of that dtype
     return dict(
         hidden_states=hidden_states,
@@ -46,7 +59,7 @@ def _moe_arguments(mlp, hidden_states) -> dict:
         renormalize=routing.renormalize,
         scoring_func=routing.scoring_func,
         routed_scaling_factor=mlp.routed_scaling_factor,
-        **moe_blocks.fp8_expert_weights(mlp.experts),
+        **(moe_blocks.fp8_expert_weights(mlp.experts) if weights else {}),
     )
 
 
@@ -72,7 +85,8 @@ def _moe_forward_normal(
     )
     if (why := _unmet(self, flags)) is not None:
         return leave_to_sglang(TARGET, why)
-    out = deepseek_v2_fp8_moe(**_moe_arguments(self, hidden_states))
+    op, arguments = _moe_call(self, hidden_states)
+    out = op(**arguments)
     if self.reduce_results and not isinstance(out, FallbackReason):
         from sglang.srt.layers.moe import post_experts_all_reduce
 

@@ -172,12 +172,28 @@ _GATED_SILU = (
 )
 
 
+# Quark's MXFP4 experts at dynamic input scales (the reference's _supported_runner,
+# aklr/plugins/sglang/models/moe_blocks.py:104-126)
+_QUARK_MXFP4 = (
+    Condition("Quark's fused-MoE method itself", lambda e: type(e.quant_method).__name__ == "QuarkFusedMoEMethod"),
+    Condition("dynamic input scales", lambda e: not e.scheme.static_input_scales),
+    Condition("no zeroed intermediate padding on presharded weights",
+              lambda e: not (attr(e, "intermediate_pad", 0) != 0 and e.use_presharded_weights)),
+    Condition("a runner", lambda e: attr(e.scheme, "runner", None) is not None),
+)
+
+
 def experts_unmet(experts, formats) -> str | None:
     """What keeps ``experts`` from running as the ops compute them; ``formats`` are the format class
     names the calling route serves."""
     found = experts_format(experts)
     if found not in formats:
         return f"experts in {found}, not one of {', '.join(formats)}"
+    if found == "QuarkW4A4MXFp4MoE":
+        unmet = first_unmet(experts, _MODULE) or first_unmet(experts, _QUARK_MXFP4)
+        if unmet is None and not _on_sm100(experts):
+            unmet = "weights on a compute capability 10.x device"
+        return unmet or first_unmet(experts.scheme.runner.config, _GATED_SILU)
     if found != "Fp8MoEMethod":
         return f"{found} experts have no kernel here"
     method = experts.quant_method

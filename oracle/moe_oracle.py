@@ -453,6 +453,30 @@ def mx_experts(
     return out.sum(dim=1)
 
 
+def deepseek_v2_mxfp4_moe(hidden, router_weight, correction_bias, w1, w1_scale, w2, w2_scale, topk, renormalize,
+                          routed_scaling_factor, logits=None):
+    """Ungrouped sigmoid routing (scores + bias pick, unbiased scores weigh), the shared expert appended at
+    weight 1, MXFP4 experts on activations that are never quantised or rounded in between.
+    Follows ``deepseek_v2_mxfp4_moe_reference`` with ``_routed`` and ``_mlp``
+    (aklr/plugins/sglang/models/deepseek_v2/reference.py:41-62, 91-111)."""
+    x = hidden.float()
+    if logits is None:
+        logits = router_logits(hidden, router_weight)
+    scores = logits.sigmoid()
+    ids = first_largest(scores + correction_bias.float(), topk)
+    weights = scores.gather(-1, ids)
+    if renormalize:
+        weights = weights / weights.sum(dim=-1, keepdim=True)
+    ids, weights = with_shared_slot(ids, weights * routed_scaling_factor, logits.shape[-1])
+    out = torch.zeros_like(x)
+    for e in ids.unique().tolist():  # the reference's _experts: experts in ascending order, index_add in float32
+        tokens, slots = (ids == e).nonzero(as_tuple=True)
+        gate, up = (x[tokens] @ mx_weight(w1[e], w1_scale[e]).T).chunk(2, dim=-1)
+        y = (torch.nn.functional.silu(gate) * up) @ mx_weight(w2[e], w2_scale[e]).T
+        out.index_add_(0, tokens, weights[tokens, slots, None] * y)
+    return out
+
+
 # --------------------------------------------------------------------------------------
 # comparison measures
 # --------------------------------------------------------------------------------------

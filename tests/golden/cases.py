@@ -62,6 +62,19 @@ def qwen2_layer():
     return cfg, dict(hidden_states=hidden, router_weight=rw, shared_gate_weight=gate, w1=w1, w1_scale=s1, w2=w2, w2_scale=s2)
 
 
+def ds_mx_layer():
+    """deepseek_v2_mxfp4_moe: ungrouped sigmoid routing with a float32 bias near 8 (the contract's spread), 16 routed
+    MXFP4 experts + the shared one, unquantised activations."""
+    cfg = wl.MoEConfig("ds_mx", hidden=256, inter=256, n_routed=16, topk=4, scoring="sigmoid", n_shared=1, routed_scaling_factor=2.5)
+    seed, tokens = 977, 40
+    hidden = wl.normal(seed, "hidden", (tokens, cfg.hidden), 1.0, dtype=torch.bfloat16)
+    rw = (wl.router_weight(cfg, seed) * 40).to(torch.bfloat16)
+    bias = 8.0 + wl.normal(seed, "bias", (cfg.n_routed,), 0.05)
+    w1, s1, w2, s2 = wl.mx_expert_weights(cfg, seed)
+    return cfg, dict(hidden_states=hidden, router_weight=rw, correction_bias=bias, w1=w1, w1_scale=s1, w2=w2, w2_scale=s2,
+                     routed_scaling_factor=2.5)
+
+
 def route_ds():
     _, logits, bias = wl.router_inputs(ROUTE_SHAPE, 192, 77)
     return logits, bias

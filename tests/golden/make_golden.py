@@ -99,6 +99,19 @@ def main() -> None:
         if isinstance(v, torch.Tensor):
             meta[f"ds_small.{k}"] = sha256_of(v)
 
+    # ---- layer: DeepSeek routing without groups over MXFP4 experts, activations not quantised ----------
+    cfg, rargs = cases.ds_mx_layer()
+    point = SimpleNamespace(
+        dtypes={"hidden_states": "bfloat16", "router_weight": "bfloat16", "correction_bias": "float32", "w1": "float4_e2m1",
+                "w1_scale": "float8_e8m0", "w2": "float4_e2m1", "w2_scale": "float8_e8m0"},
+        attrs={"topk": cfg.topk, "num_expert_group": 1, "topk_group": 1, "renormalize": True},
+        axes={"n_routed": cfg.n_routed},
+    )
+    out["ds_mx.out"] = f32(ds.deepseek_v2_mxfp4_moe_reference(point, rargs))
+    for k, v in rargs.items():
+        if isinstance(v, torch.Tensor):
+            meta[f"ds_mx.{k}"] = sha256_of(v)
+
     # ---- layer: MiniMax-M2 (float32 gate, plain biased top-k, this rank holds 8 of 16 experts) ----
     from aklr.plugins.sglang.models.minimax_m2 import reference as mm
 

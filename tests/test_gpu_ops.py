@@ -49,6 +49,28 @@ def test_deepseek_v2_fp8_moe_op(ops, golden):
     assert orc.gates_pass(gates), gates
 
 
+def test_deepseek_v2_mxfp4_moe_op(ops, golden):
+    """MXFP4 experts, ungrouped routing with a float32 bias, activations never quantised: against the reference's
+    stored output (the kernels round the gated product to bf16, the reference does not: far inside the gates)."""
+    cfg, a = cases.ds_mx_layer()
+    args = {k: v for k, v in to_dev(a).items() if k != "routed_scaling_factor"}
+    out = ops.deepseek_v2_mxfp4_moe(**args, topk=cfg.topk, num_expert_group=1, topk_group=1, renormalize=True,
+                                    scoring_func="sigmoid", routed_scaling_factor=2.5)
+    assert isinstance(out, torch.Tensor) and out.dtype == torch.bfloat16
+    from aklr_b200.moe import router_logits
+
+    logits = router_logits(a["hidden_states"].to(dev()), a["router_weight"].to(dev())).cpu().float()
+    ref = orc.deepseek_v2_mxfp4_moe(a["hidden_states"], a["router_weight"], a["correction_bias"], a["w1"], a["w1_scale"], a["w2"],
+                                    a["w2_scale"], cfg.topk, True, 2.5, logits=logits)
+    gates = orc.output_gates(out.cpu(), ref)
+    assert orc.gates_pass(gates, min_sqnr_db=40.0), gates
+    stored = orc.output_gates(out.cpu(), torch.from_numpy(np.asarray(golden["ds_mx.out"])))
+    assert stored["sqnr_db"] > 35.0, stored  # the host's router GEMM may round a logit the other way: a weight moves by a bf16 step
+    # grouped routing and a bf16 bias are not this contract
+    assert ops.deepseek_v2_mxfp4_moe(**args, topk=cfg.topk, num_expert_group=4, topk_group=2, renormalize=True,
+                                     scoring_func="sigmoid", routed_scaling_factor=2.5) is ops.FallbackReason.OUT_OF_CONTRACT
+
+
 def test_minimax_m2_fp8_moe_op(ops, golden):
     """Float32 gate, biased sigmoid top-k without groups, this rank holding experts 4..11 of 16: against
     the reference's stored output, and at larger batches (tile router kernel, token-major experts)

@@ -172,6 +172,15 @@ def test_mx_experts_variants_match_reference(golden, golden_hashes):
         assert torch.equal(out, t(golden[f"mx_moe_{name}.out"])), name
 
 
+def test_deepseek_mxfp4_layer_matches_reference(golden, golden_hashes):
+    torch.set_num_threads(1)
+    cfg, a = cases.ds_mx_layer()
+    check_inputs("ds_mx", {k: v for k, v in a.items() if torch.is_tensor(v)}, golden_hashes)
+    out = orc.deepseek_v2_mxfp4_moe(a["hidden_states"], a["router_weight"], a["correction_bias"], a["w1"], a["w1_scale"], a["w2"],
+                                    a["w2_scale"], cfg.topk, True, 2.5)
+    assert torch.equal(out, t(golden["ds_mx.out"]))
+
+
 def test_moe_align_is_a_stable_padded_sort():
     ids = torch.tensor([[2, 0], [2, 1], [0, 2], [-1, 2]])
     sorted_ids, block_expert, counts = orc.moe_align(ids, 4, 4)

@@ -207,6 +207,16 @@ def test_deepseek_route_maps_the_module_to_the_op_arguments():
     assert args["correction_bias"] is bias and args["routed_scaling_factor"] == 2.5
     routing.use_grouped_topk = False
     assert deepseek_v2._moe_arguments(mlp, torch.zeros(2, 4, dtype=torch.bfloat16))["num_expert_group"] == 1
+    # Quark's MXFP4 experts go to the other op, with the bias as the module holds it (float32) and the e8m0 scales
+    from aklr_b200 import ops
+
+    QuarkW4A4MXFp4MoE = type("QuarkW4A4MXFp4MoE", (), {})
+    bias32 = torch.zeros(4, dtype=torch.float32)
+    routing.correction_bias = bias32
+    mlp.experts = SimpleNamespace(scheme=QuarkW4A4MXFp4MoE(), w13_weight="w13", w13_weight_scale="e13", w2_weight="w2", w2_weight_scale="e2")
+    op, args = deepseek_v2._moe_call(mlp, torch.zeros(2, 4, dtype=torch.bfloat16))
+    assert op is ops.deepseek_v2_mxfp4_moe and args["correction_bias"] is bias32
+    assert args["w1_scale"] == "e13" and args["w2_scale"] == "e2" and args["topk"] == 8
 
 
 # ------------------------------------------------------------------------------------------------
