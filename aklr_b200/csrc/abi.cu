@@ -35,6 +35,7 @@ bool force_weight_major(const aklr_moe_config& c) { return (c.variant & AKLR_VAR
 bool use_cta_pairs(const aklr_moe_config& c) { return (c.variant & AKLR_VARIANT_CTA_PAIRS) != 0; }
 bool small_activation_boxes(const aklr_moe_config& c) { return (c.variant & AKLR_VARIANT_FULL_ACTIVATION_BOXES) == 0; }
 bool bf16_activations(const aklr_moe_config& c) { return (c.variant & AKLR_VARIANT_BF16_ACTIVATIONS) != 0; }
+bool mxfp4_activations(const aklr_moe_config& c) { return (c.variant & AKLR_VARIANT_MXFP4_ACTIVATIONS) != 0; }
 
 void profile_mark(cudaStream_t stream, int slot, int stage) {
   if (g_profile.on && slot >= 0) cudaEventRecord(g_profile.events[slot * (kStages + 1) + stage], stream);
@@ -514,6 +515,10 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   qp.q_in_stride = q_in_stride;
   qp.scales_in_stride = scales_in_stride;
   const bool split = bf16_activations(c);
+  const bool fp4 = mxfp4_activations(c);
+  if (split && fp4) return fail(AKLR_ERR_BAD_ARGUMENT, "activations are kept in bf16 or quantised to MXFP4, not both");
+  if (fp4 && q_in) return fail(AKLR_ERR_BAD_ARGUMENT, "rows that arrive quantised are MXFP8");
+  qp.act_fp4 = fp4;
   const int64_t cap = l.capacity;
   uint8_t* xq_lo = ws + l.xq + align_up(cap * c.hidden, 1024);
   uint8_t* xs_lo = ws + l.xs + align_up(cap * (c.hidden / 128) * 4, 256);
@@ -537,6 +542,7 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
     tp.hidden = c.hidden;
     tp.routes_per_token = 1;
     tp.row_major_scales = 1;
+    tp.act_fp4 = fp4;
     rc = launch_gather_quant_mxfp8(tp, stream);
     if (rc) return fail(rc, "MXFP8 activation quant launch failed");
     g_launches += 1;
@@ -560,6 +566,7 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   if (rc) return rc;
   g1.small_boxes = small_activation_boxes(c) && !split;
   g1.split = split;
+  g1.act_fp4 = fp4;
   if (split) {
     rc = make_map_u8(&g1.map_x_lo, xq_lo, l.capacity, c.hidden, 128);
     if (rc) return rc;

@@ -24,6 +24,7 @@
 // warps 10..11 stage the scale factors ahead of the MMA warp (also across tile boundaries).  Persistent CTAs, bounded waits, no cluster,
 // no multicast.
 #include <cfloat>
+#include <cuda_fp4.h>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -113,6 +114,22 @@ __device__ __forceinline__ int mxfp8_exponent(float amax) {
   const uint32_t bits = __float_as_uint(__fdiv_rn(amax, 448.0f));
   int e = static_cast<int>(bits >> 23) - 127 + ((bits & 0x7FFFFFu) != 0u ? 1 : 0);
   return e < -126 ? -126 : (e > 127 ? 127 : e);
+}
+
+// MXFP4 activations (aklr/ops/fused_moe/reference.py:21-37): the exponent that puts the group's largest value
+// in (3, 6] -- frexp(max(amax, 1e-10)) = (m, e), exponent e - 3 + (m > 0.75) -- clamped to [-127, 127].
+__device__ __forceinline__ int mxfp4_exponent(float amax) {
+  const uint32_t bits = __float_as_uint(fmaxf(amax, 1e-10f));
+  const int e = static_cast<int>(bits >> 23) - 127 - 2 + ((bits & 0x7FFFFFu) > 0x400000u ? 1 : 0);
+  return e < -127 ? -127 : (e > 127 ? 127 : e);
+}
+// Two values already divided by their group's scale -> the e4m3 bytes of their nearest e2m1 grid values
+// (0, .5, 1, 1.5, 2, 3, 4, 6; exact ties to the even code, which is round-to-nearest-even in e2m1).
+__device__ __forceinline__ uint16_t e2m1_grid_as_e4m3x2(float s0, float s1) {
+  const __nv_fp4x2_storage_t q = __nv_cvt_float2_to_fp4x2(make_float2(s0, s1), __NV_E2M1, cudaRoundNearest);
+  const __half2_raw back = __nv_cvt_fp4x2_to_halfraw2(q, __NV_E2M1);
+  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&back));
+  return cvt_e4m3x2(f.x, f.y);
 }
 
 // Two values already divided by their group's scale -> their e4m3 codes and the codes of what the
@@ -494,10 +511,15 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
             acc[g * 32 + i] = __bfloat162float(__float2bfloat16_rn(h));
             m = fmaxf(m, fabsf(acc[g * 32 + i]));
           }
-          const int ex = mxfp8_exponent(m);
+          const int ex = p.act_fp4 ? mxfp4_exponent(m) : mxfp8_exponent(m);
           const float inv = __uint_as_float(static_cast<uint32_t>(127 - ex) << 23);  // 2^-ex, exact
           scale_bytes |= static_cast<uint32_t>(ex + 127) << (8 * g);
-          if (SPLIT) {
+          if (!SPLIT && p.act_fp4) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              packed[g * 8 + i / 4] = e2m1_grid_as_e4m3x2(acc[g * 32 + i] * inv, acc[g * 32 + i + 1] * inv) |
+                                      (static_cast<uint32_t>(e2m1_grid_as_e4m3x2(acc[g * 32 + i + 2] * inv, acc[g * 32 + i + 3] * inv)) << 16);
+          } else if (SPLIT) {
             // h stays the bf16 value it is: two e4m3 terms, the second at 2^(ex-4) (see MxQuantParams)
             const int ex_lo = ex - 4 < -127 ? -127 : ex - 4;
             const float lo_mul = __uint_as_float(static_cast<uint32_t>(127 + ex - ex_lo) << 23);
@@ -627,10 +649,13 @@ __global__ void __launch_bounds__(256) gather_quant_mxfp8_kernel(MxQuantParams p
     }
     m = fmaxf(m, __shfl_xor_sync(group_mask, m, 2, 4));
     m = fmaxf(m, __shfl_xor_sync(group_mask, m, 1, 4));
-    const int ex = mxfp8_exponent(m);
+    const int ex = p.act_fp4 ? mxfp4_exponent(m) : mxfp8_exponent(m);
     const float inv = __uint_as_float(static_cast<uint32_t>(127 - ex) << 23);
     uint2 out;
-    if (p.q_lo) {  // the value itself, as two e4m3 terms
+    if (p.act_fp4) {
+      out.x = e2m1_grid_as_e4m3x2(v[0] * inv, v[1] * inv) | (static_cast<uint32_t>(e2m1_grid_as_e4m3x2(v[2] * inv, v[3] * inv)) << 16);
+      out.y = e2m1_grid_as_e4m3x2(v[4] * inv, v[5] * inv) | (static_cast<uint32_t>(e2m1_grid_as_e4m3x2(v[6] * inv, v[7] * inv)) << 16);
+    } else if (p.q_lo) {  // the value itself, as two e4m3 terms
       const int ex_lo = ex - 4 < -127 ? -127 : ex - 4;
       const float lo_mul = __uint_as_float(static_cast<uint32_t>(127 + ex - ex_lo) << 23);
       uint16_t hi[4], lo[4];
@@ -720,7 +745,7 @@ __global__ void __launch_bounds__(256) gather_rows_mxfp8_kernel(MxQuantParams p)
 
 int launch_gather_quant_mxfp8(const MxQuantParams& p, cudaStream_t stream) {
   if (p.hidden % 128 != 0) return AKLR_ERR_UNSUPPORTED_SHAPE;
-  if ((p.q_lo != nullptr) != (p.scales_lo != nullptr) || (p.q_lo && (p.q_in || p.row_major_scales))) return AKLR_ERR_BAD_ARGUMENT;
+  if ((p.q_lo != nullptr) != (p.scales_lo != nullptr) || (p.q_lo && (p.q_in || p.row_major_scales || p.act_fp4))) return AKLR_ERR_BAD_ARGUMENT;
   if (p.n_rows == 0) return AKLR_OK;
   if (p.q_in) {
     if (!p.sorted_ids || !p.scales_in) return AKLR_ERR_BAD_ARGUMENT;

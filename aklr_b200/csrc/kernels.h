@@ -129,6 +129,10 @@ struct MxQuantParams {
   // for elements below 2^-22 of their group's largest.  q_lo / scales_lo: the second term, same shapes.
   uint8_t* q_lo;
   uint8_t* scales_lo;
+  // Activations quantised to MXFP4 instead of MXFP8 (the reference's act_quant 4): the scale puts the
+  // group's largest value in (3, 6], values round to the e2m1 grid (ties to the even code).  Every e2m1
+  // value is also an e4m3 value, so the codes are stored as e4m3 bytes and the same MMAs consume them.
+  int act_fp4;
 };
 int launch_gather_quant_mxfp8(const MxQuantParams& p, cudaStream_t stream);
 
@@ -157,6 +161,7 @@ struct MxGemmParams {
   // bf16 activations as two e4m3 terms (see MxQuantParams): the second term's operand map, scales and,
   // for gate_up, outputs; split != 0 issues two MMAs per K step on the same weight tile
   int split;
+  int act_fp4;  // gate_up: requantise the gated product to the MXFP4 grid (see MxQuantParams)
   CUtensorMap map_x_lo;
   const uint8_t* x_scale_lo;
   uint8_t* out_q_lo;

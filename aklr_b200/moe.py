@@ -283,6 +283,14 @@ def _check_mx_weights(hidden_states, w1, w1_scale, w2, w2_scale):
     return e, inter, h
 
 
+def _act_bits_variant(act_bits: int) -> int:
+    """The numerics mode of the MXFP4 entry points for the bits the activations keep: 4 MXFP4, 8 MXFP8, 16 bf16."""
+    try:
+        return {4: _lib.VARIANT_MXFP4_ACTIVATIONS, 8: 0, 16: _lib.VARIANT_BF16_ACTIVATIONS}[act_bits]
+    except KeyError:
+        raise ValueError("act_bits: 4 (MXFP4 activations), 8 (MXFP8) or 16 (kept in bf16)") from None
+
+
 # the AKLR_ACT_* values of the public header, by the reference's attribute names
 ACTIVATIONS = {"silu": 0, "gelu": 1, "swiglu": 2, "situv2": 3}
 
@@ -308,16 +316,13 @@ def fused_experts_mxfp4(
     act_bits: int = 8,
 ):
     """MXFP4-weight experts, routing given (block-scaled tcgen05 MMA).  ``act_bits`` 8: activations
-    quantised to MXFP8 per 1 x 32; 16: kept in bf16 (each value enters the MMAs as two e4m3 terms whose
+    quantised to MXFP8 per 1 x 32; 4: to MXFP4 (the reference op's default); 16: kept in bf16 (each value enters the MMAs as two e4m3 terms whose
     sum is the bf16 value) -- the reference's gate_mode 'interleave' and gpt-oss swiglu below 256 rows.
     ``activation`` one of ACTIVATIONS; ``weight_in_stage1`` applies the route weight to the gate_up
     projection instead of the output; ``num_local_tokens`` (int32 device scalar) zeroes the rows at
     or past it (aklr/ops/fused_moe/reference.py:85-127)."""
     device = _need_cuda(hidden_states, topk_ids, topk_weights, w1, w1_scale, w2, w2_scale, expert_map, out, num_local_tokens)
-    if act_bits not in (8, 16):
-        raise ValueError("act_bits: 8 (MXFP8 activations) or 16 (bf16 activations)")
-    if act_bits == 16:
-        variant |= _lib.VARIANT_BF16_ACTIVATIONS
+    variant |= _act_bits_variant(act_bits)
     options = _lib.MxOptions(
         ACTIVATIONS[activation], int(weight_in_stage1), float(swiglu_limit or 0.0), float(beta or 0.0),
         float(linear_beta or 0.0), _ptr(num_local_tokens),
@@ -363,9 +368,7 @@ def fused_moe_mxfp4(
     n_tokens, n_routed = logits.shape
     if n_routed + routing.n_shared != e or hidden_states.shape[0] != n_tokens:
         raise ValueError("w1 must hold the routed experts followed by the shared ones")
-    if act_bits not in (8, 16):
-        raise ValueError("act_bits: 8 (MXFP8 activations) or 16 (bf16 activations)")
-    cfg = _config(n_tokens, h, inter, n_routed, routing, logits, bias, 128, variant=_lib.VARIANT_BF16_ACTIVATIONS if act_bits == 16 else 0)
+    cfg = _config(n_tokens, h, inter, n_routed, routing, logits, bias, 128, variant=_act_bits_variant(act_bits))
     ws = workspace or Workspace(cfg, device)
     if out is None:
         out = torch.empty_like(hidden_states)

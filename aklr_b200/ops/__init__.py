@@ -637,10 +637,10 @@ def _mx_weights_key(call: Mapping[str, Any], hidden: int, device) -> tuple | Non
 def _mx_act_bits(call, activation: str, n_tokens: int) -> int | None:
     """Bits the activations keep on the MXFP4 path, as the reference decides it
     (aklr/ops/fused_moe/reference.py:90-97): 16 (bf16, nothing rounded) under gate_mode 'interleave' and for
-    gpt-oss swiglu below 256 rows, whatever act_quant says; else act_quant, of which 8 (MXFP8) is served."""
+    gpt-oss swiglu below 256 rows, whatever act_quant says; else act_quant: 4 (MXFP4, the default) or 8 (MXFP8)."""
     if call["gate_mode"] == "interleave" or (activation == "swiglu" and n_tokens < 256):
         return 16
-    return 8 if call["act_quant"] == 8 else None
+    return call["act_quant"] if call["act_quant"] in (4, 8) and not isinstance(call["act_quant"], bool) else None
 
 
 def _fused_moe_mx_key(call, x, device, n_tokens, hidden):

@@ -83,6 +83,11 @@ typedef struct aklr_moe_config {
  * Every activation enters the block-scaled MMAs as TWO e4m3 terms at scales 2^ex and 2^(ex-4) whose sum is the bf16 value
  * exactly (8 significant bits = 4 + 4; elements below 2^-22 of their 32-group's largest lose low bits). */
 #define AKLR_VARIANT_BF16_ACTIVATIONS 16
+/* Another numerics mode of the MXFP4 expert entry points: activations (the input and the gated product) quantised to
+ * MXFP4 per 1 x 32 as the reference's fused_moe does at its default act_quant 4 (aklr/ops/fused_moe/reference.py:21-37):
+ * scale 2^e with the group's largest value in (3, 6], values rounded to the e2m1 grid, ties to the even code.  The codes
+ * travel as e4m3 bytes (every e2m1 value is an e4m3 value), so the products are exact and the MMAs are the MXFP8 path's. */
+#define AKLR_VARIANT_MXFP4_ACTIVATIONS 32
 
 /* Byte offsets of the intermediates inside the workspace (for tests and debuggers). */
 typedef struct aklr_moe_workspace_layout {

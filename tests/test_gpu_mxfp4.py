@@ -61,19 +61,24 @@ def test_blocks_with_few_rows_load_only_those_rows(shape):
     assert torch.equal(outs[0], outs[1])
 
 
-def test_first_mxfp8_quantisation_is_bit_exact():
+@pytest.mark.parametrize("act_bits", [8, 4])
+def test_first_activation_quantisation_is_bit_exact(act_bits):
+    """MXFP8 (act_quant 8) and MXFP4 (act_quant 4, whose grid values are stored as e4m3 bytes): codes and scale
+    bytes of the input rows reproduce the oracle's dequantised values exactly, zero rows and tiny rows included."""
     from aklr_b200.moe import fused_experts_mxfp4
 
     x, ids, wts, w1, s1, w2, s2 = case(256, 128, 6, 2, 40, seed=3)
     x[3] = 0
+    x[5] = (x[5].float() * 2.0**-60).to(torch.bfloat16)
+    x[7, :32] = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0] * 4).to(torch.bfloat16)  # exact ties of the e2m1 grid
     d = dev()
-    out, ws = fused_experts_mxfp4(x.to(d), ids.to(d), wts.to(d), w1.to(d), s1.to(d), w2.to(d), s2.to(d), return_workspace=True)
+    out, ws = fused_experts_mxfp4(x.to(d), ids.to(d), wts.to(d), w1.to(d), s1.to(d), w2.to(d), s2.to(d), return_workspace=True, act_bits=act_bits)
     sorted_ids = ws.sorted_ids().cpu()
     xq = ws._view(ws.layout.xq, ws.layout.capacity * 256, torch.float8_e4m3fn).view(-1, 256).cpu().float()
     sf = ws._view(ws.layout.xs, ws.layout.capacity * 8, torch.uint8).cpu()
     rows = (sorted_ids >= 0).nonzero().flatten()
     tokens = sorted_ids[rows].long() // 2
-    ref = orc.mxfp8_input(x.float())  # dequantised
+    ref = (orc.mxfp8_input if act_bits == 8 else orc.mxfp4_input)(x.float())  # dequantised
     # rebuild the dequantised rows from codes and the scale bytes in their tcgen05.cp order
     kb_count = 256 // 128
     for r, tok in zip(rows.tolist(), tokens.tolist()):
@@ -126,3 +131,22 @@ def test_mxfp4_experts_with_bf16_activations_match_the_oracle(shape, limit):
     rounded = orc.mx_experts(x, ids.long(), wts, w1, s1, w2, s2, swiglu_limit=limit, act_bits=8)
     # and it is the unrounded statement it matches, not the MXFP8 one
     assert orc.sqnr_db(out.cpu().float(), orc.bf16_round(ref)) > orc.sqnr_db(out.cpu().float(), orc.bf16_round(rounded)) + 6.0
+
+
+@pytest.mark.parametrize("shape", [(256, 128, 6, 2, 40), (512, 256, 8, 4, 150), (1024, 384, 4, 2, 300)])
+def test_mxfp4_experts_with_mxfp4_activations_match_the_oracle(shape):
+    """The reference op's default: activations and the gated product quantised to MXFP4 (act_quant 4).  The same
+    codes as the oracle except where the second quantisation sits on a tie (a grid step there is a quarter of the
+    value), so the SQNR floor is the reference's own for this format family, 13 dB (aklr/ops/fused_moe/contract.py),
+    with the measured value far above it."""
+    from aklr_b200.moe import fused_experts_mxfp4
+
+    hidden, inter, experts, topk, tokens = shape
+    x, ids, wts, w1, s1, w2, s2 = case(hidden, inter, experts, topk, tokens, seed=200 + tokens)
+    d = dev()
+    out, ws = fused_experts_mxfp4(x.to(d), ids.to(d), wts.to(d), w1.to(d), s1.to(d), w2.to(d), s2.to(d), return_workspace=True, act_bits=4)
+    ws.check_status()
+    ref = orc.mx_experts(x, ids.long(), wts, w1, s1, w2, s2, act_bits=4)
+    gates = orc.output_gates(out.cpu(), ref)
+    assert gates["sqnr_db"] >= 25.0 and gates["cosine"] >= 0.998, gates
+

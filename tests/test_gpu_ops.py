@@ -213,8 +213,13 @@ def test_fused_moe_op_mxfp4(ops):
     gates = orc.output_gates(out.cpu(), ref)
     assert orc.gates_pass(gates), gates
     # MXFP4 activations (act_quant 4, the reference's default) are not served
+    # the op's default arguments: MXFP4 activations (act_quant 4)
+    out = ops.fused_moe(x.to(d), w1.to(d), w2.to(d), wts.to(d), ids.to(d), quant_type="per_1x32", w1_scale=s1.to(d), w2_scale=s2.to(d))
+    assert isinstance(out, torch.Tensor)
+    a4 = orc.output_gates(out.cpu(), orc.mx_experts(*base, act_bits=4))
+    assert a4["sqnr_db"] >= 25.0 and a4["cosine"] >= 0.998, a4
     assert ops.fused_moe(x.to(d), w1.to(d), w2.to(d), wts.to(d), ids.to(d), quant_type="per_1x32", w1_scale=s1.to(d),
-                         w2_scale=s2.to(d)) is ops.FallbackReason.OUT_OF_CONTRACT
+                         w2_scale=s2.to(d), act_quant=6) is ops.FallbackReason.OUT_OF_CONTRACT
 
 
 def test_fused_moe_op_mxfp4_attributes(ops):
@@ -267,12 +272,17 @@ def test_fused_moe_op_mxfp4_attributes(ops):
     check(out, orc.mx_experts(x[:100], ids[:100].long(), wts[:100], w1, s1, w2, s2, activation="swiglu", swiglu_limit=7.0, act_bits=16),
           "swiglu below 256 rows: bf16 activations")
     # out of contract: swiglu or interleave without the clamp, interleave with another activation, situv2 without its
-    # betas, a row count without a mask, MXFP4 activations
+    # betas, a row count without a mask, activation bits other than 4 or 8
     assert run(activation="swiglu") is ops.FallbackReason.OUT_OF_CONTRACT
     assert run(gate_mode="interleave") is ops.FallbackReason.OUT_OF_CONTRACT
     assert run(gate_mode="interleave", activation="gelu", swiglu_limit=7.0) is ops.FallbackReason.OUT_OF_CONTRACT
+    # the op's default arguments: MXFP4 activations (act_quant 4)
+    out = ops.fused_moe(x.to(d), w1.to(d), w2.to(d), wts.to(d), ids.to(d), quant_type="per_1x32", w1_scale=s1.to(d), w2_scale=s2.to(d))
+    assert isinstance(out, torch.Tensor)
+    a4 = orc.output_gates(out.cpu(), orc.mx_experts(*base, act_bits=4))
+    assert a4["sqnr_db"] >= 25.0 and a4["cosine"] >= 0.998, a4
     assert ops.fused_moe(x.to(d), w1.to(d), w2.to(d), wts.to(d), ids.to(d), quant_type="per_1x32", w1_scale=s1.to(d),
-                         w2_scale=s2.to(d)) is ops.FallbackReason.OUT_OF_CONTRACT
+                         w2_scale=s2.to(d), act_quant=6) is ops.FallbackReason.OUT_OF_CONTRACT
     assert run(activation="situv2", beta=3.0) is ops.FallbackReason.OUT_OF_CONTRACT
     assert run(num_local_tokens=received.to(d)) is ops.FallbackReason.OUT_OF_CONTRACT
 
