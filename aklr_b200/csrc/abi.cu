@@ -1189,6 +1189,29 @@ int aklr_moe_shared_gate(const void* x, const void* shared_gate_weight, const in
   return AKLR_OK;
 }
 
+int aklr_silu_mul_bf16(const void* gate_up, void* out, int32_t n_tokens, int32_t inter, void* stream) {
+  if (!gate_up || !out) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
+  if (n_tokens < 0) return fail(AKLR_ERR_BAD_ARGUMENT, "n_tokens %d", n_tokens);
+  int rc = check_device();
+  if (rc) return rc;
+  rc = aklr::launch_silu_mul_bf16(gate_up, out, n_tokens, inter, static_cast<cudaStream_t>(stream));
+  if (rc) return fail(rc, "silu(gate) * up: %s", aklr_status_string(rc));
+  g_launches += n_tokens > 0;
+  return AKLR_OK;
+}
+
+int aklr_moe_add_gated_rows(const void* x, const void* shared_gate_weight, const void* rows, void* out, int32_t n_tokens,
+                            int32_t hidden, void* stream) {
+  if (!x || !shared_gate_weight || !rows || !out) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
+  if (n_tokens < 0) return fail(AKLR_ERR_BAD_ARGUMENT, "n_tokens %d", n_tokens);
+  int rc = check_device();
+  if (rc) return rc;
+  rc = aklr::launch_add_gated_rows(x, shared_gate_weight, rows, out, n_tokens, hidden, static_cast<cudaStream_t>(stream));
+  if (rc) return fail(rc, "gated shared rows: %s", aklr_status_string(rc));
+  g_launches += n_tokens > 0;
+  return AKLR_OK;
+}
+
 int aklr_router_gemm_f32(const void* x, const float* w, float* logits, int32_t n_tokens, int32_t hidden,
                          int32_t n_routed, void* stream) {
   if (!x || !w || !logits) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");

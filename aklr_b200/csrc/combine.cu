@@ -7,6 +7,8 @@
 //
 // router: logits = bf16( x @ W^T ) with float32 accumulation, the rounding point of the
 // reference's _router_logits (aklr/plugins/sglang/models/qwen3_moe/reference.py:24-31).
+#include <algorithm>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -160,6 +162,88 @@ int launch_shared_gate(const void* x, const void* gate, const int32_t* ids_in, c
   if (n_tokens == 0) return AKLR_OK;
   shared_gate_kernel<<<(n_tokens + 7) / 8, 256, 0, stream>>>(static_cast<const uint16_t*>(x), static_cast<const uint16_t*>(gate),
                                                           ids_in, weights_in, ids, weights, n_tokens, hidden, topk, shared_slot);
+  return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+}
+
+// A shared expert kept apart from the routed ones in bf16 (qwen2_moe_mxfp4_moe,
+// aklr/plugins/sglang/models/qwen2_moe/reference.py:160-185): its two projections are dense bf16
+// GEMMs the caller runs; these are the two steps around them.
+//  * silu_mul: h[t, i] = bf16( silu(gate_up[t, i]) * gate_up[t, I + i] ), 8 values per thread;
+//  * add_gated_rows: out[t] = bf16( out[t] + sigmoid(x[t] . gate) * rows[t] ), one warp per token.
+__global__ void __launch_bounds__(256)
+silu_mul_bf16_kernel(const uint16_t* __restrict__ gate_up, uint16_t* __restrict__ out, int64_t n_vectors, int vec_per_row) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vectors; i += stride) {
+    const int64_t row = i / vec_per_row;
+    const int64_t v = i - row * vec_per_row;
+    const uint4 g = *reinterpret_cast<const uint4*>(gate_up + (row * 2 * vec_per_row + v) * 8);
+    const uint4 u = *reinterpret_cast<const uint4*>(gate_up + (row * 2 * vec_per_row + vec_per_row + v) * 8);
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+    uint32_t r[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float g0 = __uint_as_float(gw[q] << 16), g1 = __uint_as_float(gw[q] & 0xFFFF0000u);
+      const float u0 = __uint_as_float(uw[q] << 16), u1 = __uint_as_float(uw[q] & 0xFFFF0000u);
+      const __nv_bfloat162 pair = __floats2bfloat162_rn(__fdiv_rn(g0, 1.0f + expf(-g0)) * u0, __fdiv_rn(g1, 1.0f + expf(-g1)) * u1);
+      r[q] = *reinterpret_cast<const uint32_t*>(&pair);
+    }
+    *reinterpret_cast<uint4*>(out + i * 8) = make_uint4(r[0], r[1], r[2], r[3]);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+add_gated_rows_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ gate, const uint16_t* __restrict__ rows,
+                      uint16_t* __restrict__ out, int n_tokens, int hidden) {
+  const int lane = threadIdx.x & 31;
+  const int token = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (token >= n_tokens) return;
+  const size_t base = static_cast<size_t>(token) * hidden;
+  float acc = 0.0f;
+  for (int h = lane * 8; h < hidden; h += 256) {
+    const uint4 xr = *reinterpret_cast<const uint4*>(x + base + h);
+    const uint4 gr = *reinterpret_cast<const uint4*>(gate + h);
+    const uint32_t xw[4] = {xr.x, xr.y, xr.z, xr.w}, gw[4] = {gr.x, gr.y, gr.z, gr.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      acc = fmaf(__uint_as_float(xw[q] << 16), __uint_as_float(gw[q] << 16), acc);
+      acc = fmaf(__uint_as_float(xw[q] & 0xFFFF0000u), __uint_as_float(gw[q] & 0xFFFF0000u), acc);
+    }
+  }
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, off);
+  const float weight = __fdiv_rn(1.0f, 1.0f + expf(-acc));
+  for (int h = lane * 8; h < hidden; h += 256) {
+    const uint4 rr = *reinterpret_cast<const uint4*>(rows + base + h);
+    const uint4 orr = *reinterpret_cast<const uint4*>(out + base + h);
+    const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w}, ow[4] = {orr.x, orr.y, orr.z, orr.w};
+    uint32_t res[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float lo = fmaf(weight, __uint_as_float(rw[q] << 16), __uint_as_float(ow[q] << 16));
+      const float hi = fmaf(weight, __uint_as_float(rw[q] & 0xFFFF0000u), __uint_as_float(ow[q] & 0xFFFF0000u));
+      const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
+      res[q] = *reinterpret_cast<const uint32_t*>(&pair);
+    }
+    *reinterpret_cast<uint4*>(out + base + h) = make_uint4(res[0], res[1], res[2], res[3]);
+  }
+}
+
+int launch_silu_mul_bf16(const void* gate_up, void* out, int n_tokens, int inter, cudaStream_t stream) {
+  if (inter % 8 != 0 || inter < 8) return AKLR_ERR_UNSUPPORTED_SHAPE;
+  if (n_tokens == 0) return AKLR_OK;
+  const int vec_per_row = inter / 8;
+  const int64_t n_vectors = static_cast<int64_t>(n_tokens) * vec_per_row;
+  const int grid = static_cast<int>(std::min<int64_t>((n_vectors + 255) / 256, 148 * 8));
+  silu_mul_bf16_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(gate_up), static_cast<uint16_t*>(out), n_vectors, vec_per_row);
+  return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+}
+
+int launch_add_gated_rows(const void* x, const void* gate, const void* rows, void* out, int n_tokens, int hidden,
+                          cudaStream_t stream) {
+  if (hidden % 8 != 0) return AKLR_ERR_UNSUPPORTED_SHAPE;
+  if (n_tokens == 0) return AKLR_OK;
+  add_gated_rows_kernel<<<(n_tokens + 7) / 8, 256, 0, stream>>>(static_cast<const uint16_t*>(x), static_cast<const uint16_t*>(gate),
+                                                             static_cast<const uint16_t*>(rows), static_cast<uint16_t*>(out), n_tokens, hidden);
   return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
 }
 

@@ -276,6 +276,9 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
 
 int launch_shared_gate(const void* x_bf16, const void* gate_bf16, const int32_t* ids_in, const float* weights_in,
                        int32_t* ids, float* weights, int n_tokens, int hidden, int topk, int shared_slot, cudaStream_t stream);
+int launch_silu_mul_bf16(const void* gate_up_bf16, void* out_bf16, int n_tokens, int inter, cudaStream_t stream);
+int launch_add_gated_rows(const void* x_bf16, const void* gate_bf16, const void* rows_bf16, void* out_bf16, int n_tokens,
+                          int hidden, cudaStream_t stream);
 int launch_router_gemm_f32(const void* x_bf16, const float* w, float* logits, int n_tokens, int hidden, int n_routed,
                            cudaStream_t stream);
 int launch_router_gemm(const void* x_bf16, const void* w_bf16, void* logits_bf16, int n_tokens, int hidden,

@@ -466,6 +466,24 @@ def with_gated_shared_slot(hidden_states, shared_gate_weight, topk_ids, topk_wei
     return topk_ids, topk_weights
 
 
+def add_bf16_shared_expert(hidden_states, shared_w1, shared_w2, shared_gate_weight, out):
+    """out += sigmoid(x . shared_gate_weight) * down(silu(gate(x)) * up(x)) of a shared expert held in bf16 apart
+    from the routed ones (aklr/plugins/sglang/models/qwen2_moe/reference.py:160-185).  The two projections are plain
+    dense GEMMs (torch.mm: the library GEMM); the gated product and the weighted add are this library's kernels."""
+    _need_cuda(hidden_states, shared_w1, shared_w2, shared_gate_weight, out)
+    n_tokens, h = hidden_states.shape
+    inter = shared_w2.shape[1]
+    if tuple(shared_w1.shape) != (2 * inter, h) or tuple(shared_w2.shape) != (h, inter) or shared_gate_weight.numel() != h:
+        raise ValueError("shared_w1 [2*inter, hidden], shared_w2 [hidden, inter], shared_gate_weight [1, hidden]")
+    lib = _lib.load()
+    gate_up = torch.mm(hidden_states, shared_w1.t())
+    gated = torch.empty((n_tokens, inter), dtype=torch.bfloat16, device=hidden_states.device)
+    _lib.check(lib.aklr_silu_mul_bf16(_ptr(gate_up), _ptr(gated), n_tokens, inter, _stream()))
+    rows = torch.mm(gated, shared_w2.t())
+    _lib.check(lib.aklr_moe_add_gated_rows(_ptr(hidden_states), _ptr(shared_gate_weight), _ptr(rows), _ptr(out), n_tokens, h, _stream()))
+    return out
+
+
 def router_logits_f32(hidden_states: torch.Tensor, router_weight: torch.Tensor) -> torch.Tensor:
     """float32 [tokens, experts] = hidden_states (bf16) @ router_weight (float32)^T, nothing rounded."""
     device = _need_cuda(hidden_states, router_weight)

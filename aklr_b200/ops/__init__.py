@@ -40,10 +40,12 @@ __all__ = [
     "init",
     "mega_moe",
     "minimax_m2_fp8_moe",
+    "minimax_m2_mxfp4_moe",
     "per_group_quant_fp8",
     "per_group_quant_mxfp8",
     "qwen2_moe_fp8_experts",
     "qwen2_moe_fp8_router_experts",
+    "qwen2_moe_mxfp4_moe",
     "qwen2_moe_router",
     "qwen3_moe_fp8_moe",
 ]
@@ -341,7 +343,7 @@ def qwen3_moe_fp8_moe(
 # --------------------------------------------------------------------------------------------------
 # minimax_m2_fp8_moe@1.0  (aklr/plugins/sglang/models/minimax_m2/contract.py:48-110, api.py:17-28)
 # --------------------------------------------------------------------------------------------------
-def _minimax_key(call):
+def _minimax_key(call, mx: bool = False):
     x, rw, bias = call["hidden_states"], call["router_weight"], call["correction_bias"]
     if not tensor_ok(x, BF16, 2):
         return None
@@ -352,8 +354,8 @@ def _minimax_key(call):
     n_routed = rw.shape[0]
     if not (1 <= n_routed <= 1024) or not tensor_ok(bias, torch.float32, 1, device) or bias.shape[0] != n_routed:
         return None
-    weights = _fp8_weights_key(call, hidden, device)
-    if weights is None or not (1 <= weights[0] <= n_routed):
+    weights = (_mx_weights_key if mx else _fp8_weights_key)(call, hidden, device)
+    if weights is None or not (1 <= weights[0] <= n_routed) or (mx and weights[1] % 256):
         return None
     topk, offset = call["topk"], call["expert_offset"]
     if not all(isinstance(v, int) and not isinstance(v, bool) for v in (topk, offset)):
@@ -413,6 +415,49 @@ MINIMAX_M2_FP8_MOE = OpContract(
     alloc=_layer_alloc,
     run=_minimax_run,
 )
+
+
+def _minimax_mx_run(call, out):
+    x = call["hidden_states"]
+    logits = moe.router_logits_f32(x, call["router_weight"])
+    routing = moe.Routing(topk=call["topk"], scoring="sigmoid", renormalize=True, routed_scaling_factor=1.0)
+    ids, weights = moe.route(logits, call["correction_bias"], routing)
+    table = _held_expert_map(logits.shape[1], call["expert_offset"], call["w1"].shape[0], x.device)
+    moe.fused_experts_mxfp4(
+        x, ids, weights, call["w1"].view(torch.uint8), call["w1_scale"].view(torch.uint8), call["w2"].view(torch.uint8),
+        call["w2_scale"].view(torch.uint8), expert_map=table, out=out, act_bits=16,
+    )
+
+
+# minimax_m2_mxfp4_moe@1.0 (aklr/plugins/sglang/models/minimax_m2/contract.py, api.py:31-42; reference.py:114-132):
+# the same routing over MXFP4 experts, activations never quantised
+MINIMAX_M2_MXFP4_MOE = OpContract(
+    contract_id="minimax_m2_mxfp4_moe@1.0",
+    description=(
+        "sglang's MiniMaxM2MoE on one rank with MXFP4 experts (fp4 values at an e8m0 scale per 32): float32 gate "
+        "logits, biased sigmoid top-k, renormalised unbiased scores; each held expert down(silu(gate(x)) * up(x)) on "
+        "activations that are not quantised; out is this rank's share."
+    ),
+    params=list(MINIMAX_M2_FP8_MOE.params),
+    outputs=["out"],
+    key=lambda call: _minimax_key(call, mx=True),
+    alloc=_layer_alloc,
+    run=_minimax_mx_run,
+)
+
+
+@api(MINIMAX_M2_MXFP4_MOE)
+def minimax_m2_mxfp4_moe(
+    hidden_states,
+    router_weight,
+    correction_bias,
+    w1,
+    w1_scale,
+    w2,
+    w2_scale,
+    topk,
+    expert_offset=0,
+): ...
 
 
 @api(MINIMAX_M2_FP8_MOE)
@@ -564,6 +609,88 @@ def qwen2_moe_fp8_experts(
     w1_scale,
     w2,
     w2_scale,
+): ...
+
+
+# --------------------------------------------------------------------------------------------------
+# qwen2_moe_mxfp4_moe@1.0 (aklr/plugins/sglang/models/qwen2_moe/contract.py:308-394, api.py:55-66): the whole
+# block with MXFP4 routed experts on unquantised activations and the shared expert apart in bf16
+# --------------------------------------------------------------------------------------------------
+def _qwen2_mx_key(call):
+    x, rw, gate = call["hidden_states"], call["router_weight"], call["shared_gate_weight"]
+    sw1, sw2, topk = call["shared_w1"], call["shared_w2"], call["topk"]
+    if not tensor_ok(x, BF16, 2):
+        return None
+    device = x.device
+    n_tokens, hidden = x.shape
+    if not (1 <= n_tokens <= MAX_TOKENS) or not tensor_ok(gate, BF16, 2, device) or tuple(gate.shape) != (1, hidden):
+        return None
+    if not tensor_ok(rw, BF16, 2, device) or rw.shape[1] != hidden or not (1 <= rw.shape[0] <= 1024):
+        return None
+    n_routed = rw.shape[0]
+    weights = _mx_weights_key(call, hidden, device)
+    if weights is None or weights[0] != n_routed or weights[1] % 256:
+        return None
+    if not tensor_ok(sw1, BF16, 2, device) or not tensor_ok(sw2, BF16, 2, device):
+        return None
+    shared_inter = sw2.shape[1]
+    if tuple(sw1.shape) != (2 * shared_inter, hidden) or sw2.shape[0] != hidden or shared_inter % 128 or not (128 <= shared_inter <= 16384):
+        return None
+    if not isinstance(topk, int) or isinstance(topk, bool) or not (1 <= topk <= min(32, n_routed)):
+        return None
+    return ("row_major", hidden, n_routed, weights[1], shared_inter, topk)
+
+
+def _qwen2_mx_run(call, out):
+    x = call["hidden_states"]
+    logits = moe.router_logits(x, call["router_weight"])
+    ids, weights = moe.route(logits, None, moe.Routing(topk=call["topk"]))
+    moe.fused_experts_mxfp4(
+        x, ids, weights, call["w1"].view(torch.uint8), call["w1_scale"].view(torch.uint8), call["w2"].view(torch.uint8),
+        call["w2_scale"].view(torch.uint8), out=out, act_bits=16,
+    )
+    moe.add_bf16_shared_expert(x, call["shared_w1"], call["shared_w2"], call["shared_gate_weight"], out)
+
+
+QWEN2_MOE_MXFP4_MOE = OpContract(
+    contract_id="qwen2_moe_mxfp4_moe@1.0",
+    description=(
+        "sglang's Qwen2MoeSparseMoeBlock.forward on one rank with MXFP4 routed experts and the shared expert apart in "
+        "bf16: bf16 router logits, top-k by logit, softmax over the chosen; each routed expert down(silu(gate(x)) * "
+        "up(x)) of its MXFP4 weights on unquantised activations; the shared expert of its bf16 weights weighed by "
+        "sigmoid(hidden_states shared_gate_weight^T) and added; out is this rank's share."
+    ),
+    params=[
+        Param("hidden_states"),
+        Param("router_weight"),
+        Param("w1"),
+        Param("w1_scale"),
+        Param("w2"),
+        Param("w2_scale"),
+        Param("shared_w1"),
+        Param("shared_w2"),
+        Param("shared_gate_weight"),
+        Param("topk", 10),
+    ],
+    outputs=["out"],
+    key=_qwen2_mx_key,
+    alloc=_layer_alloc,
+    run=_qwen2_mx_run,
+)
+
+
+@api(QWEN2_MOE_MXFP4_MOE)
+def qwen2_moe_mxfp4_moe(
+    hidden_states,
+    router_weight,
+    w1,
+    w1_scale,
+    w2,
+    w2_scale,
+    shared_w1,
+    shared_w2,
+    shared_gate_weight,
+    topk=10,
 ): ...
 
 
@@ -1103,11 +1230,14 @@ def per_group_quant_mxfp8(x): ...
 
 CONTRACTS = (
     DEEPSEEK_V2_FP8_MOE,
+    DEEPSEEK_V2_MXFP4_MOE,
     QWEN3_MOE_FP8_MOE,
     MINIMAX_M2_FP8_MOE,
+    MINIMAX_M2_MXFP4_MOE,
     QWEN2_MOE_ROUTER,
     QWEN2_MOE_FP8_EXPERTS,
     QWEN2_MOE_FP8_ROUTER_EXPERTS,
+    QWEN2_MOE_MXFP4_MOE,
     FUSED_MOE,
     MEGA_MOE,
     BIASED_GROUPED_TOPK,

@@ -34,8 +34,7 @@ def _moe_call(mlp, hidden_states):
     """(op, keyword arguments) for the experts' format."""
     if moe_blocks.experts_format(mlp.experts) == "QuarkW4A4MXFp4MoE":
         arguments = _moe_arguments(mlp, hidden_states, keep_bias_dtype=True, weights=False)
-        experts = mlp.experts
-        arguments.update(w1=experts.w13_weight, w1_scale=experts.w13_weight_scale, w2=experts.w2_weight, w2_scale=experts.w2_weight_scale)
+        arguments.update(moe_blocks.mxfp4_expert_weights(mlp.experts))
         return deepseek_v2_mxfp4_moe, arguments
     return deepseek_v2_fp8_moe, _moe_arguments(mlp, hidden_states)
 

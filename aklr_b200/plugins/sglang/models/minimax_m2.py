@@ -1,18 +1,16 @@
-"""MiniMax-M2 on sglang: ``MiniMaxM2MoE.forward_normal`` served by ``minimax_m2_fp8_moe`` (the
-reference routes the same function: aklr/plugins/sglang/models/minimax_m2/api.py:47-88).
-
-Only FP8 experts are served.  The model's MXFP4 checkpoints keep their activations unquantised
-against e8m0-per-32 weights (minimax_m2/reference.py:120-132), a mix this build has no kernel for, so
-those stay on sglang."""
+"""MiniMax-M2 on sglang: ``MiniMaxM2MoE.forward_normal`` served by ``minimax_m2_fp8_moe`` (experts in FP8 at a
+scale per 128 x 128 block) or ``minimax_m2_mxfp4_moe`` (Quark's MXFP4 experts, activations left unquantised) -- the
+reference routes the same function to the same two ops: aklr/plugins/sglang/models/minimax_m2/api.py:45-88."""
 
 from __future__ import annotations
 
-from aklr_b200.ops import minimax_m2_fp8_moe
+from aklr_b200.ops import minimax_m2_fp8_moe, minimax_m2_mxfp4_moe
 from aklr_b200.plugins.sglang.conditions import leave_to_sglang, when
 from aklr_b200.plugins.sglang.hook import sglang_route
 from aklr_b200.plugins.sglang.models import moe_blocks
 
 TARGET = "sglang.srt.models.minimax_m2.MiniMaxM2MoE.forward_normal"
+EXPERT_FORMATS = ("Fp8MoEMethod", "QuarkW4A4MXFp4MoE")
 
 
 def _unmet(moe) -> str | None:
@@ -23,8 +21,23 @@ def _unmet(moe) -> str | None:
         # under DP attention the experts see rows gathered from every attention rank
         or when(is_dp_attention_enabled(), "DP attention off")
         or moe_blocks.topk_unmet(moe.topk, scoring_func="sigmoid", biased=True)
-        or moe_blocks.experts_unmet(moe.experts, ("Fp8MoEMethod",))
+        or moe_blocks.experts_unmet(moe.experts, EXPERT_FORMATS)
     )
+
+
+def _moe_call(moe):
+    """(op, its keyword arguments but the input) for the experts' format; ``expert_offset`` is the gate row of
+    this rank's first expert."""
+    experts, routing = moe.experts, moe.topk.topk_config
+    arguments = dict(
+        router_weight=moe.gate.weight,
+        correction_bias=routing.correction_bias,
+        topk=routing.top_k,
+        expert_offset=experts.moe_ep_rank * experts._num_local_routed,
+    )
+    if moe_blocks.experts_format(experts) == "QuarkW4A4MXFp4MoE":
+        return minimax_m2_mxfp4_moe, {**arguments, **moe_blocks.mxfp4_expert_weights(experts)}
+    return minimax_m2_fp8_moe, {**arguments, **moe_blocks.fp8_expert_weights(experts)}
 
 
 @sglang_route(TARGET, versions=("0.5.22", "0.5.23"))
@@ -33,13 +46,5 @@ def _moe_forward_normal(self, hidden_states):
     sglang after the block, as they are for its own path."""
     if (why := _unmet(self)) is not None:
         return leave_to_sglang(TARGET, why)
-    experts, routing = self.experts, self.topk.topk_config
-    first_local_expert = experts.moe_ep_rank * experts._num_local_routed
-    return minimax_m2_fp8_moe(
-        hidden_states=hidden_states,
-        router_weight=self.gate.weight,
-        correction_bias=routing.correction_bias,
-        topk=routing.top_k,
-        expert_offset=first_local_expert,  # the gate row of w1[0]
-        **moe_blocks.fp8_expert_weights(experts),
-    )
+    op, arguments = _moe_call(self)
+    return op(hidden_states=hidden_states, **arguments)

@@ -215,3 +215,13 @@ def fp8_expert_weights(experts) -> dict:
         "w2": experts.w2_weight,
         "w2_scale": experts.w2_weight_scale_inv,
     }
+
+
+def mxfp4_expert_weights(experts) -> dict:
+    """The four weight arguments every MXFP4 op takes, from a FusedMoE under Quark's W4A4 MXFP4 scheme."""
+    return {
+        "w1": experts.w13_weight,
+        "w1_scale": experts.w13_weight_scale,
+        "w2": experts.w2_weight,
+        "w2_scale": experts.w2_weight_scale,
+    }

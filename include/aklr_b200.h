@@ -293,6 +293,16 @@ int aklr_moe_shared_gate(const void* x, const void* shared_gate_weight, const in
                          const float* topk_weights_in, int32_t* topk_ids, float* topk_weights, int32_t n_tokens,
                          int32_t hidden, int32_t topk, int32_t shared_slot, void* stream);
 
+/* A shared expert held apart from the routed ones in bf16 (`qwen2_moe_mxfp4_moe_reference`,
+ * aklr/plugins/sglang/models/qwen2_moe/reference.py:160-185): its two projections are plain dense bf16 GEMMs
+ * (the caller's GEMM library); these are the steps around them.
+ * aklr_silu_mul_bf16: out bf16 [T, inter] = silu(gate_up[:, :inter]) * gate_up[:, inter:], gate_up bf16 [T, 2*inter].
+ * aklr_moe_add_gated_rows: out[t] = bf16(out[t] + sigmoid(x[t] . shared_gate_weight) * rows[t]), all bf16 [T, hidden]
+ * (shared_gate_weight bf16 [hidden]); out is the routed experts' sum the layer call wrote. */
+int aklr_silu_mul_bf16(const void* gate_up, void* out, int32_t n_tokens, int32_t inter, void* stream);
+int aklr_moe_add_gated_rows(const void* x, const void* shared_gate_weight, const void* rows, void* out, int32_t n_tokens,
+                            int32_t hidden, void* stream);
+
 /* logits float32 [T,E] = x (bf16 [T,H]) @ w (float32 [E,H])^T, nothing rounded: the gate of
  * `minimax_m2_fp8_moe` (aklr/plugins/sglang/models/minimax_m2/reference.py:43-50). */
 int aklr_router_gemm_f32(const void* x, const float* w, float* logits, int32_t n_tokens, int32_t hidden,

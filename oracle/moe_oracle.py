@@ -468,13 +468,50 @@ def deepseek_v2_mxfp4_moe(hidden, router_weight, correction_bias, w1, w1_scale, 
     if renormalize:
         weights = weights / weights.sum(dim=-1, keepdim=True)
     ids, weights = with_shared_slot(ids, weights * routed_scaling_factor, logits.shape[-1])
+    return mx_experts_unquantised(x, ids, weights, w1, w1_scale, w2, w2_scale)
+
+
+def mx_experts_unquantised(x, ids, weights, w1, w1_scale, w2, w2_scale):
+    """MXFP4 experts on float32 activations, nothing rounded: the experts hit in ascending order, each one's rows
+    weighed and added in float32 (``index_add_``), ids below 0 adding nothing -- the loop the three layer
+    references share (``_experts``, aklr/plugins/sglang/models/deepseek_v2/reference.py:91-111; ``_held_experts``,
+    aklr/plugins/sglang/models/minimax_m2/reference.py:53-70; aklr/plugins/sglang/models/qwen2_moe/reference.py:179-183)."""
     out = torch.zeros_like(x)
-    for e in ids.unique().tolist():  # the reference's _experts: experts in ascending order, index_add in float32
+    for e in ids.unique().tolist():
+        if e < 0:
+            continue
         tokens, slots = (ids == e).nonzero(as_tuple=True)
         gate, up = (x[tokens] @ mx_weight(w1[e], w1_scale[e]).T).chunk(2, dim=-1)
         y = (torch.nn.functional.silu(gate) * up) @ mx_weight(w2[e], w2_scale[e]).T
         out.index_add_(0, tokens, weights[tokens, slots, None] * y)
     return out
+
+
+def minimax_m2_mxfp4_moe(hidden, router_weight, correction_bias, w1, w1_scale, w2, w2_scale, topk, expert_offset=0, logits=None):
+    """This rank's share of a MiniMax-M2 MoE over MXFP4 experts: float32 gate, biased sigmoid top-k, unquantised
+    activations.  Follows ``minimax_m2_mxfp4_moe_reference`` (aklr/plugins/sglang/models/minimax_m2/reference.py:114-132)."""
+    x = hidden.float()
+    if logits is None:
+        logits = x @ router_weight.float().T
+    ids, weights = sigmoid_bias_topk(logits.float(), correction_bias.float(), topk)
+    local = ids - expert_offset
+    local = torch.where((local >= 0) & (local < w1.shape[0]), local, torch.full_like(local, -1))
+    return mx_experts_unquantised(x, local, weights, w1, w1_scale, w2, w2_scale)
+
+
+def qwen2_moe_mxfp4_moe(hidden, router_weight, w1, w1_scale, w2, w2_scale, shared_w1, shared_w2, shared_gate_weight, topk,
+                        logits=None):
+    """bf16 router logits, softmax top-k, MXFP4 routed experts on unquantised activations, plus the bf16 shared
+    expert weighed by sigmoid(hidden . shared_gate_weight[0]).  Follows ``qwen2_moe_mxfp4_moe_reference`` and
+    ``_silu_mlp`` (aklr/plugins/sglang/models/qwen2_moe/reference.py:152-185)."""
+    x = hidden.float()
+    if logits is None:
+        logits = router_logits(hidden, router_weight)
+    ids, weights = softmax_topk(logits.float(), topk)
+    out = mx_experts_unquantised(x, ids, weights, w1, w1_scale, w2, w2_scale)
+    shared_weight = (x @ shared_gate_weight.float()[0]).sigmoid()
+    gate, up = (x @ shared_w1.float().T).chunk(2, dim=-1)
+    return out + shared_weight[:, None] * ((torch.nn.functional.silu(gate) * up) @ shared_w2.float().T)
 
 
 # --------------------------------------------------------------------------------------

@@ -75,6 +75,33 @@ def ds_mx_layer():
                      routed_scaling_factor=2.5)
 
 
+def minimax_mx_layer():
+    """minimax_m2_mxfp4_moe: float32 gate over 16 routed experts, this rank holds the MXFP4 experts 4..11."""
+    cfg = wl.MoEConfig("minimax_mx", hidden=256, inter=256, n_routed=8, topk=4, scoring="sigmoid")
+    seed, tokens, n_routed, offset = 8642, 40, 16, 4
+    hidden = wl.normal(seed, "hidden", (tokens, cfg.hidden), 1.0, dtype=torch.bfloat16)
+    router = wl.normal(seed, "router", (n_routed, cfg.hidden), 3.0 / cfg.hidden**0.5)
+    bias = 8.0 + wl.normal(seed, "bias", (n_routed,), 0.02)
+    w1, s1, w2, s2 = wl.mx_expert_weights(cfg, seed)
+    return cfg, dict(hidden_states=hidden, router_weight=router, correction_bias=bias, w1=w1, w1_scale=s1, w2=w2, w2_scale=s2,
+                     expert_offset=offset)
+
+
+def qwen2_mx_layer():
+    """qwen2_moe_mxfp4_moe: 12 routed MXFP4 experts, top-4 softmax, a bf16 shared expert (inter 384) apart from them,
+    its down projection drawn 8 times a Lecun normal's spread as the reference's contract draws it."""
+    cfg = wl.MoEConfig("qwen2_mx", hidden=256, inter=256, n_routed=12, topk=4)
+    seed, tokens, shared_inter = 7531, 36, 384
+    hidden = wl.normal(seed, "hidden", (tokens, cfg.hidden), 1.0, dtype=torch.bfloat16)
+    rw = (wl.router_weight(cfg, seed) * 30).to(torch.bfloat16)
+    gate = wl.normal(seed, "shared_gate", (1, cfg.hidden), 2.0 / cfg.hidden**0.5, dtype=torch.bfloat16)
+    sw1 = wl.normal(seed, "shared_w1", (2 * shared_inter, cfg.hidden), cfg.hidden**-0.5, dtype=torch.bfloat16)
+    sw2 = wl.normal(seed, "shared_w2", (cfg.hidden, shared_inter), 8.0 * shared_inter**-0.5, dtype=torch.bfloat16)
+    w1, s1, w2, s2 = wl.mx_expert_weights(cfg, seed)
+    return cfg, dict(hidden_states=hidden, router_weight=rw, w1=w1, w1_scale=s1, w2=w2, w2_scale=s2, shared_w1=sw1,
+                     shared_w2=sw2, shared_gate_weight=gate)
+
+
 def route_ds():
     _, logits, bias = wl.router_inputs(ROUTE_SHAPE, 192, 77)
     return logits, bias

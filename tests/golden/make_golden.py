@@ -145,6 +145,30 @@ def main() -> None:
     for k, v in rargs.items():
         meta[f"qwen2.{k}"] = sha256_of(v)
 
+    # ---- layers over MXFP4 experts with unquantised activations: MiniMax-M2 and Qwen2-MoE (bf16 shared expert apart)
+    mx_dtypes = {"hidden_states": "bfloat16", "w1": "float4_e2m1", "w1_scale": "float8_e8m0", "w2": "float4_e2m1",
+                 "w2_scale": "float8_e8m0"}
+    cfg, rargs = cases.minimax_mx_layer()
+    point = SimpleNamespace(
+        dtypes={**mx_dtypes, "router_weight": "float32", "correction_bias": "float32"},
+        attrs={"topk": cfg.topk},
+        axes={"n_experts": cfg.n_routed},
+    )
+    out["minimax_mx.out"] = f32(mm.minimax_m2_mxfp4_moe_reference(point, rargs))
+    for k, v in rargs.items():
+        if isinstance(v, torch.Tensor):
+            meta[f"minimax_mx.{k}"] = sha256_of(v)
+    cfg, rargs = cases.qwen2_mx_layer()
+    point = SimpleNamespace(
+        dtypes={**mx_dtypes, "router_weight": "bfloat16", "shared_w1": "bfloat16", "shared_w2": "bfloat16",
+                "shared_gate_weight": "bfloat16"},
+        attrs={"topk": cfg.topk},
+        axes={"n_routed": cfg.n_routed},
+    )
+    out["qwen2_mx.out"] = f32(q2.qwen2_moe_mxfp4_moe_reference(point, rargs))
+    for k, v in rargs.items():
+        meta[f"qwen2_mx.{k}"] = sha256_of(v)
+
     # ---- routing only, at the full expert counts -----------------------------------------
     logits, bias = cases.route_ds()
     point = SimpleNamespace(

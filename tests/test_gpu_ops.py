@@ -71,6 +71,59 @@ def test_deepseek_v2_mxfp4_moe_op(ops, golden):
                                      scoring_func="sigmoid", routed_scaling_factor=2.5) is ops.FallbackReason.OUT_OF_CONTRACT
 
 
+def test_minimax_m2_mxfp4_moe_op(ops, golden):
+    """MXFP4 experts under MiniMax-M2's routing (float32 gate, this rank holding experts 4..11 of 16), activations
+    never quantised: against the reference's stored output, and at 600 tokens against the oracle on the device's logits."""
+    from aklr_b200.moe import router_logits_f32
+
+    cfg, a = cases.minimax_mx_layer()
+    d = to_dev(a)
+    out = ops.minimax_m2_mxfp4_moe(**d, topk=cfg.topk)
+    assert isinstance(out, torch.Tensor) and out.dtype == torch.bfloat16
+    gates = orc.output_gates(out.cpu(), torch.from_numpy(np.asarray(golden["minimax_mx.out"])))
+    assert orc.gates_pass(gates, min_sqnr_db=40.0), gates
+    hidden = torch.randn(600, cfg.hidden, generator=torch.Generator().manual_seed(4)).to(torch.bfloat16)
+    big = {**d, "hidden_states": hidden.to(dev())}
+    out = ops.minimax_m2_mxfp4_moe(**big, topk=cfg.topk)
+    logits = router_logits_f32(big["hidden_states"], d["router_weight"]).cpu()
+    ref = orc.minimax_m2_mxfp4_moe(hidden, a["router_weight"], a["correction_bias"], a["w1"], a["w1_scale"], a["w2"], a["w2_scale"],
+                                   cfg.topk, a["expert_offset"], logits=logits)
+    gates = orc.output_gates(out.cpu(), ref)
+    assert orc.gates_pass(gates, min_sqnr_db=40.0), gates
+    # FP8 weights are the other op's contract
+    assert ops.minimax_m2_mxfp4_moe(**{**d, "w1": d["w1"].view(torch.float8_e4m3fn)}, topk=cfg.topk) is ops.FallbackReason.OUT_OF_CONTRACT
+
+
+def test_qwen2_moe_mxfp4_moe_op(ops, golden):
+    """The whole Qwen2-MoE block with MXFP4 routed experts and the shared expert apart in bf16: against the
+    reference's stored output and, at 500 tokens, the oracle on the device's logits.  The reference's own floor
+    for this op is 11 dB (aklr/plugins/sglang/models/qwen2_moe/contract.py:306); the shared expert's two GEMMs
+    round to bf16 here and not in the reference, which leaves the output above 40 dB."""
+    from aklr_b200.moe import router_logits
+
+    cfg, a = cases.qwen2_mx_layer()
+    d = to_dev(a)
+    out = ops.qwen2_moe_mxfp4_moe(**d, topk=cfg.topk)
+    assert isinstance(out, torch.Tensor) and out.dtype == torch.bfloat16
+    stored = orc.output_gates(out.cpu(), torch.from_numpy(np.asarray(golden["qwen2_mx.out"])))
+    assert stored["sqnr_db"] > 35.0 and stored["cosine"] > 0.9995, stored
+    hidden = torch.randn(500, cfg.hidden, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16)
+    big = {**d, "hidden_states": hidden.to(dev())}
+    out = ops.qwen2_moe_mxfp4_moe(**big, topk=cfg.topk)
+    logits = router_logits(big["hidden_states"], d["router_weight"]).cpu().float()
+    ref = orc.qwen2_moe_mxfp4_moe(hidden, a["router_weight"], a["w1"], a["w1_scale"], a["w2"], a["w2_scale"], a["shared_w1"],
+                                  a["shared_w2"], a["shared_gate_weight"], cfg.topk, logits=logits)
+    gates = orc.output_gates(out.cpu(), ref)
+    assert orc.gates_pass(gates, min_sqnr_db=40.0), gates
+    # a kernel that dropped the shared expert would be far off: it carries half of the output
+    no_shared = orc.qwen2_moe_mxfp4_moe(hidden, a["router_weight"], a["w1"], a["w1_scale"], a["w2"], a["w2_scale"], a["shared_w1"],
+                                        torch.zeros_like(a["shared_w2"]), a["shared_gate_weight"], cfg.topk, logits=logits)
+    assert orc.sqnr_db(out.cpu().float(), no_shared) < 6.0
+    # a shared expert whose width is not a multiple of 128 is outside the contract
+    bad = {**d, "shared_w1": d["shared_w1"][:700].contiguous(), "shared_w2": d["shared_w2"][:, :350].contiguous()}
+    assert ops.qwen2_moe_mxfp4_moe(**bad, topk=cfg.topk) is ops.FallbackReason.OUT_OF_CONTRACT
+
+
 def test_minimax_m2_fp8_moe_op(ops, golden):
     """Float32 gate, biased sigmoid top-k without groups, this rank holding experts 4..11 of 16: against
     the reference's stored output, and at larger batches (tile router kernel, token-major experts)

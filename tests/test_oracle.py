@@ -181,6 +181,28 @@ def test_deepseek_mxfp4_layer_matches_reference(golden, golden_hashes):
     assert torch.equal(out, t(golden["ds_mx.out"]))
 
 
+def test_minimax_mxfp4_layer_matches_reference(golden, golden_hashes):
+    torch.set_num_threads(1)
+    cfg, a = cases.minimax_mx_layer()
+    check_inputs("minimax_mx", {k: v for k, v in a.items() if torch.is_tensor(v)}, golden_hashes)
+    out = orc.minimax_m2_mxfp4_moe(a["hidden_states"], a["router_weight"], a["correction_bias"], a["w1"], a["w1_scale"], a["w2"],
+                                   a["w2_scale"], cfg.topk, a["expert_offset"])
+    assert torch.equal(out, t(golden["minimax_mx.out"]))
+
+
+def test_qwen2_mxfp4_layer_with_a_bf16_shared_expert_matches_reference(golden, golden_hashes):
+    torch.set_num_threads(1)
+    cfg, a = cases.qwen2_mx_layer()
+    check_inputs("qwen2_mx", a, golden_hashes)
+    out = orc.qwen2_moe_mxfp4_moe(a["hidden_states"], a["router_weight"], a["w1"], a["w1_scale"], a["w2"], a["w2_scale"],
+                                  a["shared_w1"], a["shared_w2"], a["shared_gate_weight"], cfg.topk)
+    assert torch.equal(out, t(golden["qwen2_mx.out"]))
+    # the shared expert carries about as much of the output as the routed ones, so dropping it fails any gate
+    routed_only = orc.qwen2_moe_mxfp4_moe(a["hidden_states"], a["router_weight"], a["w1"], a["w1_scale"], a["w2"], a["w2_scale"],
+                                          a["shared_w1"], torch.zeros_like(a["shared_w2"]), a["shared_gate_weight"], cfg.topk)
+    assert orc.sqnr_db(routed_only, out) < 6.0
+
+
 def test_moe_align_is_a_stable_padded_sort():
     ids = torch.tensor([[2, 0], [2, 1], [0, 2], [-1, 2]])
     sorted_ids, block_expert, counts = orc.moe_align(ids, 4, 4)

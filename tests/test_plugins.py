@@ -47,7 +47,7 @@ def fake_sglang(monkeypatch):
     modules["sglang.srt.plugins.hook_registry"].HookType = HookType
     modules["sglang.srt.models.deepseek_v2"].DeepseekV2MoE = type("DeepseekV2MoE", (), {"forward_normal": lambda self, hidden_states: "sglang"})
     modules["sglang.srt.models.qwen3_moe"].Qwen3MoeSparseMoeBlock = type("Qwen3MoeSparseMoeBlock", (), {"forward_normal": lambda self, hidden_states: "sglang"})
-    modules["sglang.srt.models.qwen2_moe"].Qwen2MoeSparseMoeBlock = type("Qwen2MoeSparseMoeBlock", (), {"_forward_router_experts": lambda self, hidden_states, *, defer_finalize=False: "sglang"})
+    modules["sglang.srt.models.qwen2_moe"].Qwen2MoeSparseMoeBlock = type("Qwen2MoeSparseMoeBlock", (), {"_forward_router_experts": lambda self, hidden_states, *, defer_finalize=False: "sglang", "forward": lambda self, hidden_states, forward_batch=None, defer_finalize=False: "sglang"})
     modules["sglang.srt.models.minimax_m2"].MiniMaxM2MoE = type("MiniMaxM2MoE", (), {"forward_normal": lambda self, hidden_states: "sglang"})
     for name, module in modules.items():
         monkeypatch.setitem(sys.modules, name, module)
@@ -62,15 +62,16 @@ def test_sglang_install_hooks_only_routes_tested_on_the_installed_release(fake_s
     from aklr_b200.plugins.sglang.models import deepseek_v2, minimax_m2, qwen2_moe, qwen3_moe  # noqa: F401  (declare the routes)
 
     monkeypatch.setattr(hook, "sglang_version", lambda: "0.5.22")
-    assert hook.install() == 3
+    assert hook.install() == 4
     assert sorted(t for t, _, _ in fake_sglang.registered) == [
         "sglang.srt.models.minimax_m2.MiniMaxM2MoE.forward_normal",
         "sglang.srt.models.qwen2_moe.Qwen2MoeSparseMoeBlock._forward_router_experts",
+        "sglang.srt.models.qwen2_moe.Qwen2MoeSparseMoeBlock.forward",
         "sglang.srt.models.qwen3_moe.Qwen3MoeSparseMoeBlock.forward_normal",
     ]
     fake_sglang.registered.clear()
     monkeypatch.setattr(hook, "sglang_version", lambda: "0.5.23")
-    assert hook.install() == 4
+    assert hook.install() == 5
     assert all(kind is fake_sglang.HookType.AROUND for _, _, kind in fake_sglang.registered)
     fake_sglang.registered.clear()
     monkeypatch.setattr(hook, "sglang_version", lambda: "0.9.0")
@@ -100,6 +101,7 @@ def test_sglang_routes_take_their_targets_parameters():
 
     assert list(inspect.signature(minimax_m2._moe_forward_normal).parameters) == ["self", "hidden_states"]
     assert list(inspect.signature(qwen2_moe._forward_router_experts).parameters) == ["self", "hidden_states", "defer_finalize"]
+    assert list(inspect.signature(qwen2_moe._forward).parameters) == ["self", "hidden_states", "forward_batch", "defer_finalize"]
     assert list(inspect.signature(deepseek_v2._moe_forward_normal).parameters) == [
         "self", "hidden_states", "gemm_output_zero_allocator", "input_ids", "input_ids_global",
         "skip_shared_experts", "use_vision_topk", "return_moe_output", "leave_output_sum",
@@ -117,7 +119,7 @@ def test_sglang_register_starts_only_when_switched_on(fake_sglang, monkeypatch):
     fake_sglang.registered.clear()
     monkeypatch.setenv("AKLR_SGLANG_PLUGIN", "1")
     plugin.register()
-    assert len(fake_sglang.registered) == 5  # the start hook + four model routes
+    assert len(fake_sglang.registered) == 6  # the start hook + five model routes
     monkeypatch.setenv("AKLR_SGLANG_PLUGIN", "maybe")
     with pytest.raises(SystemExit, match="cannot start"):
         plugin.register()
@@ -217,6 +219,46 @@ def test_deepseek_route_maps_the_module_to_the_op_arguments():
     op, args = deepseek_v2._moe_call(mlp, torch.zeros(2, 4, dtype=torch.bfloat16))
     assert op is ops.deepseek_v2_mxfp4_moe and args["correction_bias"] is bias32
     assert args["w1_scale"] == "e13" and args["w2_scale"] == "e2" and args["topk"] == 8
+
+
+def test_minimax_and_qwen2_routes_pick_the_op_for_the_experts_format():
+    from aklr_b200 import ops
+    from aklr_b200.plugins.sglang.models import minimax_m2, qwen2_moe
+
+    QuarkW4A4MXFp4MoE = type("QuarkW4A4MXFp4MoE", (), {})
+    quark = SimpleNamespace(scheme=QuarkW4A4MXFp4MoE(), w13_weight="w13", w13_weight_scale="e13", w2_weight="w2", w2_weight_scale="e2",
+                            moe_ep_rank=2, _num_local_routed=32)
+    fp8 = _experts(w13_weight="w13", w13_weight_scale_inv="s13", w2_weight="w2", w2_weight_scale_inv="s2", moe_ep_rank=1, _num_local_routed=64)
+    topk = SimpleNamespace(topk_config=SimpleNamespace(correction_bias="bias", top_k=8))
+    gate = SimpleNamespace(weight="gate")
+    op, args = minimax_m2._moe_call(SimpleNamespace(experts=quark, topk=topk, gate=gate))
+    assert op is ops.minimax_m2_mxfp4_moe and args["expert_offset"] == 64 and args["w1_scale"] == "e13" and args["topk"] == 8
+    op, args = minimax_m2._moe_call(SimpleNamespace(experts=fp8, topk=topk, gate=gate))
+    assert op is ops.minimax_m2_fp8_moe and args["expert_offset"] == 64 and args["w2_scale"] == "s2"
+    # Qwen2: the whole block's arguments, the bf16 shared expert's two weights among them
+    shared = SimpleNamespace(gate_up_proj=SimpleNamespace(weight="sw1"), down_proj=SimpleNamespace(weight="sw2"))
+    block = SimpleNamespace(experts=quark, shared_expert=shared, gate=gate, shared_expert_gate=SimpleNamespace(weight="sg"),
+                            topk=SimpleNamespace(topk_config=SimpleNamespace(top_k=10)))
+    args = qwen2_moe._block_arguments(block, "x")
+    assert set(args) == {"hidden_states", "router_weight", "w1", "w1_scale", "w2", "w2_scale", "shared_w1", "shared_w2",
+                         "shared_gate_weight", "topk"}
+    assert args["shared_w1"] == "sw1" and args["shared_w2"] == "sw2" and args["shared_gate_weight"] == "sg" and args["topk"] == 10
+    # what the shared expert has to look like, by name
+    def linear(kind, **kw):
+        layer = type(kind, (), {})()
+        layer.quant_method, layer.bias = type("UnquantizedLinearMethod", (), {})(), None
+        for k, v in kw.items():
+            setattr(layer, k, v)
+        return layer
+    mlp = type("Qwen2MoeMLP", (), {})()
+    mlp.act_fn, mlp._enable_silu_fp4_quant_fusion = type("SiluAndMul", (), {})(), False
+    mlp.gate_up_proj = linear("MergedColumnParallelLinear", gather_output=False)
+    mlp.down_proj = linear("RowParallelLinear", input_is_parallel=True, reduce_results=False, use_decode_attn_tp=False)
+    assert qwen2_moe._shared_expert_unmet(mlp) is None
+    mlp.down_proj.reduce_results = True
+    assert "sum over the ranks" in qwen2_moe._shared_expert_unmet(mlp)
+    mlp.down_proj.reduce_results, mlp.gate_up_proj.bias = False, torch.zeros(1)
+    assert "gate_up projection a plain bf16" in qwen2_moe._shared_expert_unmet(mlp)
 
 
 # ------------------------------------------------------------------------------------------------
