@@ -17,6 +17,7 @@ DTYPE_BF16, DTYPE_F32 = 0, 1
 # aklr_moe_config.variant bits (AKLR_VARIANT_* of the header)
 VARIANT_WEIGHT_MAJOR, VARIANT_CTA_PAIRS, VARIANT_SEPARATE_PROLOGUE, VARIANT_FULL_ACTIVATION_BOXES = 1, 2, 4, 8
 VARIANT_BF16_ACTIVATIONS, VARIANT_MXFP4_ACTIVATIONS = 16, 32  # numerics modes of the MXFP4 entry points
+VARIANT_DEEP_PIPELINE = 64
 
 
 class AklrError(RuntimeError):

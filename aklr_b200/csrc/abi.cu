@@ -33,6 +33,7 @@ std::atomic<long long> g_launches{0};
 // two blocks (an odd last block wastes half a pair).
 bool force_weight_major(const aklr_moe_config& c) { return (c.variant & AKLR_VARIANT_WEIGHT_MAJOR) != 0; }
 bool use_cta_pairs(const aklr_moe_config& c) { return (c.variant & AKLR_VARIANT_CTA_PAIRS) != 0; }
+bool deep_pipeline(const aklr_moe_config& c) { return (c.variant & AKLR_VARIANT_DEEP_PIPELINE) != 0; }
 bool small_activation_boxes(const aklr_moe_config& c) { return (c.variant & AKLR_VARIANT_FULL_ACTIVATION_BOXES) == 0; }
 bool bf16_activations(const aklr_moe_config& c) { return (c.variant & AKLR_VARIANT_BF16_ACTIVATIONS) != 0; }
 bool mxfp4_activations(const aklr_moe_config& c) { return (c.variant & AKLR_VARIANT_MXFP4_ACTIVATIONS) != 0; }
@@ -391,7 +392,10 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
 
   const int sms = sm_count();
   GroupedGemmParams g1{};
-  rc = make_map_u8(&g1.map_w, w1, static_cast<uint64_t>(experts) * 2 * c.inter, c.hidden, 128);
+  // 128-token blocks on 128 x 128 tiles, four partials in flight (both projections or neither)
+  const bool deep = l.block_m == 128 && deep_pipeline(c) && !pairs && !force_weight_major(c) && c.inter % 128 == 0 &&
+                    c.hidden % 128 == 0;
+  rc = make_map_u8(&g1.map_w, w1, static_cast<uint64_t>(experts) * 2 * c.inter, c.hidden, deep ? 64 : 128);
   if (rc) return rc;
   rc = make_map_u8(&g1.map_x, ws + l.xq, l.capacity, c.hidden, l.block_m);
   if (rc) return rc;
@@ -411,16 +415,18 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   g1.max_blocks = l.max_blocks;
   const bool tm1 = grouped_gemm_is_token_major(true, l.block_m, c.inter);  // at 128 tokens per block always
   g1.pair_table = pairs ? pair_table : nullptr;
-  g1.stages = tm1 ? grouped_gemm_prefill_pick_stages(true, pairs) : grouped_gemm_pick_stages(true, l.block_m, c.hidden);
+  g1.stages = deep ? grouped_gemm_deep_pick_stages(true)
+              : tm1 ? grouped_gemm_prefill_pick_stages(true, pairs) : grouped_gemm_pick_stages(true, l.block_m, c.hidden);
   if (g1.stages < 2) return fail(AKLR_ERR_UNSUPPORTED_SHAPE, "hidden=%d needs more shared memory than one SM has", c.hidden);
-  rc = tm1 ? launch_grouped_gemm_prefill(g1, true, pairs, sms, stream) : launch_grouped_gemm_gate_up(g1, sms, stream);
+  rc = deep ? launch_grouped_gemm_deep(g1, true, sms, stream)
+       : tm1 ? launch_grouped_gemm_prefill(g1, true, pairs, sms, stream) : launch_grouped_gemm_gate_up(g1, sms, stream);
   if (rc) return fail(rc, "gate_up grouped GEMM launch failed");
   g_launches += 1;
   profile_mark(stream, slot, 4);
 
   GroupedGemmParams g2{};
   const bool tm2 = grouped_gemm_is_token_major(false, l.block_m, c.hidden) && !force_weight_major(c);
-  rc = make_map_u8(&g2.map_w, w2, static_cast<uint64_t>(experts) * c.hidden, c.inter, tm2 && !pairs ? 256 : 128);
+  rc = make_map_u8(&g2.map_w, w2, static_cast<uint64_t>(experts) * c.hidden, c.inter, tm2 && !pairs && !deep ? 256 : 128);
   if (rc) return rc;
   rc = make_map_u8(&g2.map_x, ws + l.hq, l.capacity, c.inter, l.block_m);
   if (rc) return rc;
@@ -439,9 +445,11 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   g2.block_m = l.block_m;
   g2.max_blocks = l.max_blocks;
   g2.pair_table = pairs ? pair_table : nullptr;
-  g2.stages = tm2 ? grouped_gemm_prefill_pick_stages(false, pairs) : grouped_gemm_pick_stages(false, l.block_m, c.inter);
+  g2.stages = deep ? grouped_gemm_deep_pick_stages(false)
+              : tm2 ? grouped_gemm_prefill_pick_stages(false, pairs) : grouped_gemm_pick_stages(false, l.block_m, c.inter);
   if (g2.stages < 2) return fail(AKLR_ERR_UNSUPPORTED_SHAPE, "inter=%d needs more shared memory than one SM has", c.inter);
-  rc = tm2 ? launch_grouped_gemm_prefill(g2, false, pairs, sms, stream) : launch_grouped_gemm_down(g2, sms, stream);
+  rc = deep ? launch_grouped_gemm_deep(g2, false, sms, stream)
+       : tm2 ? launch_grouped_gemm_prefill(g2, false, pairs, sms, stream) : launch_grouped_gemm_down(g2, sms, stream);
   if (rc) return fail(rc, "down grouped GEMM launch failed");
   g_launches += 1;
   profile_mark(stream, slot, 5);

@@ -24,6 +24,7 @@ SOURCES = [
     "quant.cu",
     "grouped_gemm.cu",
     "grouped_gemm_prefill.cu",
+    "grouped_gemm_deep.cu",
     "grouped_gemm_mx.cu",
     "combine.cu",
     "router_gemm.cu",

@@ -57,6 +57,7 @@ constexpr int kABytes = kBM * 128;       // token tile of one K-block
 constexpr int kBBytes = kBN * 128;       // weight tile of one K-block
 __host__ __device__ constexpr int stage_bytes(bool pair) { return kABytes + (pair ? kBBytes / 2 : kBBytes); }  // a CTA of a pair holds half the weight rows
 constexpr int kBatch = 32;                // TMEM columns one epilogue thread loads per round (as 4 x 8)
+constexpr int kPrefetchAhead = 8;         // K-blocks between a weight tile's L2 prefetch and its load
 
 struct PrefillLayout {
   int off_out, off_rid, off_wmax, off_bars, total;
@@ -209,6 +210,23 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
               tma_load_2d(st + kABytes + kBBytes / 2, &p.map_w, &full[s], kb * 128, w_row + p.out_dim);
             } else {
               tma_load_2d(st + kABytes, &p.map_w, &full[s], kb * 128, w_row);  // box of 256 rows
+            }
+            // The ring holds four K-blocks, less than the latency of a weight tile that comes from HBM:
+            // ask the L2 for the weights kPrefetchAhead K-blocks further on (this tile's, then the next one's).
+            int pk = kb + kPrefetchAhead, prow = w_row;
+            if (pk >= KB) {
+              pk -= KB;
+              const int tn = t + n_workers;
+              if (tn < total_tiles && pk < KB) {
+                const int un = tn / tiles_per_block, jn = tn - un * tiles_per_block;
+                prow = p.block_expert[un] * p.rows_per_expert + (GATE_UP ? jn * 128 : jn * 256);
+              } else {
+                pk = -1;
+              }
+            }
+            if (pk >= 0) {
+              tma_prefetch_l2_2d(&p.map_w, pk * 128, prow);
+              if (GATE_UP) tma_prefetch_l2_2d(&p.map_w, pk * 128, prow + p.out_dim);
             }
           }
           if (++s == S) { s = 0; ph ^= 1; }

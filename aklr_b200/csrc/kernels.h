@@ -109,6 +109,10 @@ bool grouped_gemm_is_token_major(bool gate_up, int block_m, int out_dim);
 // pair_table; map_w with a 128-row box for both projections)
 int grouped_gemm_prefill_pick_stages(bool gate_up, bool pair);
 int launch_grouped_gemm_prefill(const GroupedGemmParams& p, bool gate_up, bool pair, int sm_count, cudaStream_t stream);
+// the same on 128 x 128 tiles with four TMEM partials in flight (grouped_gemm_deep.cu); map_w with a
+// 64-row box for gate_up and a 128-row box for down; out_dim a multiple of 128 for both
+int grouped_gemm_deep_pick_stages(bool gate_up);
+int launch_grouped_gemm_deep(const GroupedGemmParams& p, bool gate_up, int sm_count, cudaStream_t stream);
 size_t grouped_gemm_smem_bytes(bool gate_up, int block_m, int k, int stages);
 int grouped_gemm_pick_stages(bool gate_up, int block_m, int k);
 

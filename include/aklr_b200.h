@@ -76,6 +76,7 @@ typedef struct aklr_moe_config {
 #define AKLR_VARIANT_CTA_PAIRS 2              /* token-major GEMMs as CTA pairs (cta_group::2, no multicast) */
 #define AKLR_VARIANT_SEPARATE_PROLOGUE 4      /* 1..8 tokens: routing and sort as two kernels, not one */
 #define AKLR_VARIANT_FULL_ACTIVATION_BOXES 8  /* MXFP4 GEMMs load all 128 activation rows of every block */
+#define AKLR_VARIANT_DEEP_PIPELINE 64         /* FP8 token-major GEMMs on 128 x 128 tiles with four partials in flight */
 /* A numerics mode rather than a kernel choice (it also sizes the workspace, so set it before asking for the layout):
  * the MXFP4 expert entry points keep the activations in bf16 instead of rounding them to MXFP8 -- what the reference's
  * fused_moe does under gate_mode "interleave" and for gpt-oss swiglu below 256 rows (aklr/ops/fused_moe/

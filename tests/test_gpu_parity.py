@@ -80,6 +80,40 @@ def test_tied_logits_route_to_the_lower_expert(golden):
     assert ids.cpu().tolist() == [[31, 368, 571]]
 
 
+def test_float32_logits_route_like_the_oracle_up_to_near_ties():
+    """Float32 logits (MiniMax-M2's gate, biased_grouped_topk on float32) are scored 1 / (1 + expf(-x)) on the
+    device, which may differ from torch's CPU sigmoid in the last bit.  Over 24 seeded batches (256 experts, top-8,
+    bias near 8 as the model holds it): every pick that differs from the oracle's sits on a near-tie -- the two
+    biased scores involved are within 4 ulp of each other in the oracle -- and weights agree to 1e-6."""
+    from aklr_b200.moe import Routing, route
+
+    mismatched_tokens, checked, worst_gap = 0, 0, 0.0
+    for seed in range(24):
+        g = torch.Generator().manual_seed(9000 + seed)
+        n_tokens = (1, 7, 64, 300, 1024, 2048)[seed % 6]
+        logits = torch.randn(n_tokens, 256, generator=g) * (0.5 + 0.25 * (seed % 5))
+        bias = 8.0 + 0.02 * torch.randn(256, generator=g)
+        ref_ids, ref_w = orc.sigmoid_bias_topk(logits, bias, 8)
+        ids, w = route(logits.to(dev()), bias.to(dev()), Routing(topk=8, scoring="sigmoid", renormalize=True))
+        ids, w = ids.cpu().long(), w.cpu()
+        checked += n_tokens
+        biased = logits.sigmoid() + bias
+        for tok in (ids != ref_ids).any(dim=-1).nonzero().flatten().tolist():
+            mismatched_tokens += 1
+            ours, theirs = set(ids[tok].tolist()), set(ref_ids[tok].tolist())
+            if ours == theirs:  # the same experts in another order: two picks within the margin swapped places
+                moved = [e for e, r in zip(ids[tok].tolist(), ref_ids[tok].tolist()) if e != r]
+            else:
+                moved = sorted(ours ^ theirs)
+            scores = biased[tok, moved]
+            gap = (scores.max() - scores.min()).item()
+            worst_gap = max(worst_gap, gap)
+            assert gap <= 4 * 2.0**-20, (seed, tok, moved, gap)  # 4 ulp of a value in [8, 16)
+        same = (ids == ref_ids).all(dim=-1)
+        torch.testing.assert_close(w[same], ref_w[same], atol=1e-6, rtol=1e-6)
+    assert mismatched_tokens <= checked // 200, (mismatched_tokens, checked, worst_gap)
+
+
 def test_softmax_routing_matches_golden(golden):
     from aklr_b200.moe import Routing, route
 
@@ -473,6 +507,35 @@ def test_cta_pair_kernels_match_the_single_cta_kernels(golden):
         blocks = ws.num_blocks()
     assert blocks > cfg.n_routed  # some experts have more than one block
     assert torch.equal(outs[0], outs[1])
+
+
+def test_deep_pipeline_kernels_match_the_two_buffer_kernels(golden):
+    """128 x 128 tiles with four partials in flight: per element the same float32 operations in the same order
+    as the 128 x 256 kernels, so outputs are bit-identical -- on the golden layer, on a batch with several blocks
+    per expert, and on a width whose down projection has an odd K-block count (inter 640 -> 5)."""
+    from aklr_b200 import _lib
+    from aklr_b200.moe import Routing, fused_moe_fp8
+
+    cfg, a = cases.ds_small_layer()
+    out_ref, _ = run_layer(cfg, a, t(golden["ds_small.logits"]), 128)
+    out_deep, ws = run_layer(cfg, a, t(golden["ds_small.logits"]), 128, variant=_lib.VARIANT_DEEP_PIPELINE)
+    check_intermediates(cfg, a, ws, t(golden["ds_small.ids"]))
+    assert torch.equal(out_deep.cpu(), out_ref.cpu())
+
+    d = dev()
+    shapes = [wl.CONFIGS["deepseek_small"], wl.MoEConfig("odd_k", hidden=768, inter=640, n_routed=8, topk=2)]
+    for cfg, n_tokens in zip(shapes, (1500, 900)):
+        w1, s1, w2, s2 = (x.to(d) for x in wl.expert_weights(cfg, seed=5))
+        hidden, logits, bias = wl.router_inputs(cfg, n_tokens, seed=6)
+        bias = bias.to(d) if cfg.scoring == "sigmoid" else None
+        outs = []
+        for variant in (0, _lib.VARIANT_DEEP_PIPELINE):
+            out, ws = fused_moe_fp8(hidden.to(d), logits.to(d), bias, w1, s1, w2, s2, routing_of(cfg), block_m=128,
+                                    return_workspace=True, variant=variant)
+            ws.check_status()
+            outs.append(out.cpu())
+        assert ws.num_blocks() > cfg.n_routed
+        assert torch.equal(outs[0], outs[1]), cfg.name
 
 
 @pytest.mark.parametrize("name", ["deepseek_small", "qwen3", "eight_experts"])
