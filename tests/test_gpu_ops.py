@@ -265,11 +265,10 @@ def test_fused_moe_op_mxfp4(ops):
     ref = orc.mx_experts(x, ids.long(), wts, w1, s1, w2, s2, act_bits=8)
     gates = orc.output_gates(out.cpu(), ref)
     assert orc.gates_pass(gates), gates
-    # MXFP4 activations (act_quant 4, the reference's default) are not served
     # the op's default arguments: MXFP4 activations (act_quant 4)
     out = ops.fused_moe(x.to(d), w1.to(d), w2.to(d), wts.to(d), ids.to(d), quant_type="per_1x32", w1_scale=s1.to(d), w2_scale=s2.to(d))
     assert isinstance(out, torch.Tensor)
-    a4 = orc.output_gates(out.cpu(), orc.mx_experts(*base, act_bits=4))
+    a4 = orc.output_gates(out.cpu(), orc.mx_experts(x, ids.long(), wts, w1, s1, w2, s2, act_bits=4))
     assert a4["sqnr_db"] >= 25.0 and a4["cosine"] >= 0.998, a4
     assert ops.fused_moe(x.to(d), w1.to(d), w2.to(d), wts.to(d), ids.to(d), quant_type="per_1x32", w1_scale=s1.to(d),
                          w2_scale=s2.to(d), act_quant=6) is ops.FallbackReason.OUT_OF_CONTRACT
@@ -332,7 +331,7 @@ def test_fused_moe_op_mxfp4_attributes(ops):
     # the op's default arguments: MXFP4 activations (act_quant 4)
     out = ops.fused_moe(x.to(d), w1.to(d), w2.to(d), wts.to(d), ids.to(d), quant_type="per_1x32", w1_scale=s1.to(d), w2_scale=s2.to(d))
     assert isinstance(out, torch.Tensor)
-    a4 = orc.output_gates(out.cpu(), orc.mx_experts(*base, act_bits=4))
+    a4 = orc.output_gates(out.cpu(), orc.mx_experts(x, ids.long(), wts, w1, s1, w2, s2, act_bits=4))
     assert a4["sqnr_db"] >= 25.0 and a4["cosine"] >= 0.998, a4
     assert ops.fused_moe(x.to(d), w1.to(d), w2.to(d), wts.to(d), ids.to(d), quant_type="per_1x32", w1_scale=s1.to(d),
                          w2_scale=s2.to(d), act_quant=6) is ops.FallbackReason.OUT_OF_CONTRACT
