@@ -19,19 +19,17 @@
 // warpgroup gives its registers to the epilogue (setmaxnreg 40 / 232): 128 accumulators + 64
 // staging registers per epilogue thread do not fit the 168 an even split allows.
 //
-// What bounds it, measured on B200 by taking parts out (experimental builds without the MMAs and
-// without the operand loads): the epilogue's fold alone -- no loads, no MMAs -- already
-// takes ~510 ns per K-block per SM, loads added 570 ns (L2-resident weights) / 670 ns (weights
-// from HBM), the full kernel 670 / 790 ns, against 290 ns for the four MMAs.  Per K-block an
-// epilogue warp makes four round trips of tcgen05.ld (latency-bound, and tcgen05.wait::ld waits for
-// every load in flight, so only one batch overlaps the packed FMAs of the previous one) under a
-// register budget that allows 64 staging registers next to 128 accumulators.  What helped: one
-// commit per K-block and a lean MMA-issue loop (a lone thread pays full latency per instruction;
-// no divisions, descriptors carried forward), scales prefetched from global memory two K-blocks
-// ahead instead of staged per tile, register hand-over.  What did not: per-half hand-offs (two
-// N=128 MMA groups; 20% slower -- every extra commit and barrier round costs more than the
-// overlap gains), issuing the next K-block's first batch early, 16 epilogue warps, larger or
-// single-buffered load batches, CTA pairs (below).  Persistent CTAs, TMA SWIZZLE_128B ring,
+// What bounds it, measured on B200 piece by piece on all 148 SMs: the four MMAs of a K-block take 512 cycles
+// with nothing else running (nominal) and 665-750 next to the fold; the fold alone 333-364 (8 tcgen05.ld x32
+// per warp + 128 packed FMAs per thread); a TMA ring alone delivers 48 KB per ~520 cycles; the kernel's
+// period is 1100-1450.  No piece explains it: the hand-offs of the MMA <-> fold cycle each arrive late (512
+// TMEM columns hold exactly two N=256 partials, and a ring stage is held until the MMAs that read it are
+// done).  What helped: one commit per K-block and a lean MMA-issue loop, scales prefetched from global
+// memory two K-blocks ahead instead of staged per tile, register hand-over (setmaxnreg), weight tiles
+// prefetched into L2 ahead of the ring.  What did not: per-half hand-offs (two N=128 MMA groups; 20%
+// slower), 128 x 128 tiles with four partials in flight (grouped_gemm_deep.cu; 40% slower), two MMA-issuing
+// threads, one polling lane per warp, issuing the next K-block's first batch early, 16 epilogue warps,
+// larger or single-buffered load batches, CTA pairs (below).  Persistent CTAs, TMA SWIZZLE_128B ring,
 // two 256-column TMEM partial buffers, no multicast loads, bounded waits.
 #include <cfloat>
 #include <map>
