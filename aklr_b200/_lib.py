@@ -18,6 +18,7 @@ DTYPE_BF16, DTYPE_F32 = 0, 1
 VARIANT_WEIGHT_MAJOR, VARIANT_CTA_PAIRS, VARIANT_SEPARATE_PROLOGUE, VARIANT_FULL_ACTIVATION_BOXES = 1, 2, 4, 8
 VARIANT_BF16_ACTIVATIONS, VARIANT_MXFP4_ACTIVATIONS = 16, 32  # numerics modes of the MXFP4 entry points
 VARIANT_DEEP_PIPELINE = 64
+VARIANT_TILED_WEIGHTS = 128  # w1 / w2 in the tile-contiguous layout
 
 
 class AklrError(RuntimeError):
@@ -102,6 +103,7 @@ SIGNATURES = {
     "aklr_moe_align_noalloc_last_error": (c_char_p, []),
     "aklr_silu_mul_bf16": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_void_p]),
     "aklr_moe_add_gated_rows": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_void_p]),
+    "aklr_tile_weights_fp8": (c_int32, [c_void_p, c_void_p, c_int64, c_int32, c_int32, c_void_p]),
     "aklr_moe_shared_gate": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p]),
     "aklr_router_gemm_f32": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p]),
     "aklr_router_gemm_bf16": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p]),

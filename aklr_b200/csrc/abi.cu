@@ -34,6 +34,7 @@ std::atomic<long long> g_launches{0};
 bool force_weight_major(const aklr_moe_config& c) { return (c.variant & AKLR_VARIANT_WEIGHT_MAJOR) != 0; }
 bool use_cta_pairs(const aklr_moe_config& c) { return (c.variant & AKLR_VARIANT_CTA_PAIRS) != 0; }
 bool deep_pipeline(const aklr_moe_config& c) { return (c.variant & AKLR_VARIANT_DEEP_PIPELINE) != 0; }
+bool tiled_weights(const aklr_moe_config& c) { return (c.variant & AKLR_VARIANT_TILED_WEIGHTS) != 0; }
 bool small_activation_boxes(const aklr_moe_config& c) { return (c.variant & AKLR_VARIANT_FULL_ACTIVATION_BOXES) == 0; }
 bool bf16_activations(const aklr_moe_config& c) { return (c.variant & AKLR_VARIANT_BF16_ACTIVATIONS) != 0; }
 bool mxfp4_activations(const aklr_moe_config& c) { return (c.variant & AKLR_VARIANT_MXFP4_ACTIVATIONS) != 0; }
@@ -333,7 +334,8 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   ap.n_experts = experts;
   ap.n_experts_global = n_experts_global;
   ap.block_m = l.block_m;
-  const bool pairs = l.block_m == 128 && !force_weight_major(c) && use_cta_pairs(c) &&
+  const bool tiled = tiled_weights(c);  // [expert][row tile][K-block][128][128]: the maps below are over tiles
+  const bool pairs = l.block_m == 128 && !force_weight_major(c) && use_cta_pairs(c) && !tiled &&
                      grouped_gemm_is_token_major(true, l.block_m, c.inter) &&
                      grouped_gemm_is_token_major(false, l.block_m, c.hidden);
   int32_t* pair_table = block_expert + l.max_blocks;  // second half of the block table's space
@@ -395,7 +397,9 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   // 128-token blocks on 128 x 128 tiles, four partials in flight (both projections or neither)
   const bool deep = l.block_m == 128 && deep_pipeline(c) && !pairs && !force_weight_major(c) && c.inter % 128 == 0 &&
                     c.hidden % 128 == 0;
-  rc = make_map_u8(&g1.map_w, w1, static_cast<uint64_t>(experts) * 2 * c.inter, c.hidden, deep ? 64 : 128);
+  rc = tiled ? make_map_u8(&g1.map_w, w1, static_cast<uint64_t>(experts) * 2 * c.inter * (c.hidden / 128), 128, deep ? 64 : 128)
+             : make_map_u8(&g1.map_w, w1, static_cast<uint64_t>(experts) * 2 * c.inter, c.hidden, deep ? 64 : 128);
+  g1.w_tiled = tiled ? 1 : 0;
   if (rc) return rc;
   rc = make_map_u8(&g1.map_x, ws + l.xq, l.capacity, c.hidden, l.block_m);
   if (rc) return rc;
@@ -426,7 +430,9 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
 
   GroupedGemmParams g2{};
   const bool tm2 = grouped_gemm_is_token_major(false, l.block_m, c.hidden) && !force_weight_major(c);
-  rc = make_map_u8(&g2.map_w, w2, static_cast<uint64_t>(experts) * c.hidden, c.inter, tm2 && !pairs && !deep ? 256 : 128);
+  rc = tiled ? make_map_u8(&g2.map_w, w2, static_cast<uint64_t>(experts) * c.hidden * (c.inter / 128), 128, 128)
+             : make_map_u8(&g2.map_w, w2, static_cast<uint64_t>(experts) * c.hidden, c.inter, tm2 && !pairs && !deep ? 256 : 128);
+  g2.w_tiled = tiled ? 1 : 0;
   if (rc) return rc;
   rc = make_map_u8(&g2.map_x, ws + l.hq, l.capacity, c.inter, l.block_m);
   if (rc) return rc;
@@ -482,6 +488,7 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
                    const uint8_t* q_in = nullptr, const uint8_t* scales_in = nullptr, void* rows_out = nullptr,
                    int slot = -1, int q_in_stride = 0, int scales_in_stride = 0) {
   using namespace aklr;
+  if (tiled_weights(c)) return fail(AKLR_ERR_BAD_ARGUMENT, "the tile-contiguous weight layout is an FP8 layout: packed MXFP4 weights stay row-major");
   const int routes_per_token = c.topk + c.n_shared;
   const int routes = c.n_tokens * routes_per_token;
   const int experts = c.n_routed + c.n_shared;
@@ -1217,6 +1224,17 @@ int aklr_moe_add_gated_rows(const void* x, const void* shared_gate_weight, const
   rc = aklr::launch_add_gated_rows(x, shared_gate_weight, rows, out, n_tokens, hidden, static_cast<cudaStream_t>(stream));
   if (rc) return fail(rc, "gated shared rows: %s", aklr_status_string(rc));
   g_launches += n_tokens > 0;
+  return AKLR_OK;
+}
+
+int aklr_tile_weights_fp8(const void* src, void* dst, int64_t matrices, int32_t rows, int32_t cols, void* stream) {
+  if (!src || !dst) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
+  int rc = check_device();
+  if (rc) return rc;
+  rc = aklr::launch_tile_weights_fp8(src, dst, matrices, rows, cols, static_cast<cudaStream_t>(stream));
+  if (rc) return fail(rc, "tile-contiguous weight layout: %s (rows %d, cols %d, %lld matrices)", aklr_status_string(rc), rows, cols,
+                      static_cast<long long>(matrices));
+  g_launches += 1;
   return AKLR_OK;
 }
 

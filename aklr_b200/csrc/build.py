@@ -28,6 +28,7 @@ SOURCES = [
     "grouped_gemm_mx.cu",
     "combine.cu",
     "router_gemm.cu",
+    "weight_layout.cu",
     "ep.cu",
     "no_alloc.cu",
 ]

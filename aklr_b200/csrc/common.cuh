@@ -134,6 +134,19 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// Where a weight box starts in the TMA map: rows `row`.. of the flattened [experts * rows_per_expert, k] matrix at
+// K-block `kb`.  Row-major weights: (kb * 128, row).  Tile-contiguous weights: the map is [tiles * 128, 128] and the
+// box starts inside tile (row / 128) * (k / 128) + kb (a 64-row box may start at the tile's row 64).
+__device__ __forceinline__ void weight_box(bool tiled, int k_blocks, int row, int kb, int* x, int* y) {
+  if (tiled) {
+    *x = 0;
+    *y = (((row >> 7) * k_blocks + kb) << 7) + (row & 127);
+  } else {
+    *x = kb * 128;
+    *y = row;
+  }
+}
+
 // Ask the L2 to fetch a tile ahead of the load that will bring it into shared memory (no data moves to the SM).
 __device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int x, int y) {
   asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"

@@ -150,8 +150,13 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
           if (!got) { ok = false; break; }
           uint8_t* st = smem + s * L.stage_bytes;
           mbar_expect_tx(&full[s], L.stage_bytes);
-          tma_load_2d(st, &p.map_w, &full[s], kb * 128, w_row);
-          if (GATE_UP) tma_load_2d(st + kWTileBytes, &p.map_w, &full[s], kb * 128, w_row + p.out_dim);
+          int wx, wy;
+          weight_box(p.w_tiled != 0, KB, w_row, kb, &wx, &wy);
+          tma_load_2d(st, &p.map_w, &full[s], wx, wy);
+          if (GATE_UP) {
+            weight_box(p.w_tiled != 0, KB, w_row + p.out_dim, kb, &wx, &wy);
+            tma_load_2d(st + kWTileBytes, &p.map_w, &full[s], wx, wy);
+          }
           tma_load_2d(st + (GATE_UP ? 2 : 1) * kWTileBytes, &p.map_x, &full[s], kb * 128, b * BM);
           if (++s == S) { s = 0; ph ^= 1; }
         }

@@ -164,11 +164,12 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_deep_kernel(const __
               uint8_t* st = smem + s * kStageBytes;
               mbar_expect_tx(&full[s], kStageBytes);
               tma_load_2d(st, &p.map_x, &full[s], kb * 128, b * kBM);
-              if (GATE_UP) {  // boxes of 64 rows: one 128-row K-major operand, gate then up
-                tma_load_2d(st + kABytes, &p.map_w, &full[s], kb * 128, w_row);
-                tma_load_2d(st + kABytes + kBBytes / 2, &p.map_w, &full[s], kb * 128, w_row + p.out_dim);
-              } else {
-                tma_load_2d(st + kABytes, &p.map_w, &full[s], kb * 128, w_row);  // box of 128 rows
+              int wx, wy;
+              weight_box(p.w_tiled != 0, KB, w_row, kb, &wx, &wy);
+              tma_load_2d(st + kABytes, &p.map_w, &full[s], wx, wy);  // gate_up: a box of 64 rows; down: of 128
+              if (GATE_UP) {  // the up rows that match: together one 128-row K-major operand
+                weight_box(p.w_tiled != 0, KB, w_row + p.out_dim, kb, &wx, &wy);
+                tma_load_2d(st + kABytes + kBBytes / 2, &p.map_w, &full[s], wx, wy);
               }
               if (++s == S) { s = 0; ph ^= 1; }
             }

@@ -203,9 +203,16 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
           } else {
             mbar_expect_tx(&full[s], kStageBytes);
             tma_load_2d(st, &p.map_x, &full[s], kb * 128, b * kBM);
-            if (GATE_UP) {  // gate rows, then the matching up rows: one 256-row K-major operand
-              tma_load_2d(st + kABytes, &p.map_w, &full[s], kb * 128, w_row);
-              tma_load_2d(st + kABytes + kBBytes / 2, &p.map_w, &full[s], kb * 128, w_row + p.out_dim);
+            const bool tiled = p.w_tiled != 0;
+            int wx, wy;
+            if (GATE_UP || tiled) {
+              // gate rows, then the matching up rows: one 256-row K-major operand (tile-contiguous weights: the
+              // down projection's 256 rows are two tiles that do not follow one another in memory either)
+              const int second = w_row + (GATE_UP ? p.out_dim : 128);
+              weight_box(tiled, KB, w_row, kb, &wx, &wy);
+              tma_load_2d(st + kABytes, &p.map_w, &full[s], wx, wy);
+              weight_box(tiled, KB, second, kb, &wx, &wy);
+              tma_load_2d(st + kABytes + kBBytes / 2, &p.map_w, &full[s], wx, wy);
             } else {
               tma_load_2d(st + kABytes, &p.map_w, &full[s], kb * 128, w_row);  // box of 256 rows
             }
@@ -223,8 +230,12 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
               }
             }
             if (pk >= 0) {
-              tma_prefetch_l2_2d(&p.map_w, pk * 128, prow);
-              if (GATE_UP) tma_prefetch_l2_2d(&p.map_w, pk * 128, prow + p.out_dim);
+              weight_box(tiled, KB, prow, pk, &wx, &wy);
+              tma_prefetch_l2_2d(&p.map_w, wx, wy);
+              if (GATE_UP || tiled) {
+                weight_box(tiled, KB, prow + (GATE_UP ? p.out_dim : 128), pk, &wx, &wy);
+                tma_prefetch_l2_2d(&p.map_w, wx, wy);
+              }
             }
           }
           if (++s == S) { s = 0; ph ^= 1; }

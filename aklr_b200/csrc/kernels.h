@@ -99,6 +99,7 @@ struct GroupedGemmParams {
   int block_m;                 // tokens per block: 16, 32, 64 or 128
   int max_blocks;              // upper bound used to size the tile loop
   int stages;
+  int w_tiled;                 // weights in the tile-contiguous layout: [expert][row/128][k/128][128 rows][128 bytes]
 };
 int launch_grouped_gemm_gate_up(const GroupedGemmParams& p, int sm_count, cudaStream_t stream);
 int launch_grouped_gemm_down(const GroupedGemmParams& p, int sm_count, cudaStream_t stream);
@@ -113,6 +114,10 @@ int launch_grouped_gemm_prefill(const GroupedGemmParams& p, bool gate_up, bool p
 // 64-row box for gate_up and a 128-row box for down; out_dim a multiple of 128 for both
 int grouped_gemm_deep_pick_stages(bool gate_up);
 int launch_grouped_gemm_deep(const GroupedGemmParams& p, bool gate_up, int sm_count, cudaStream_t stream);
+// Tile-contiguous FP8 weights (a layout a checkpoint loader can convert to once): every 128-row x 128-byte tile
+// the TMA fetches is one contiguous 16 KB run of HBM instead of 128 row segments k bytes apart.  The map is then
+// over [tiles * 128 rows, 128 bytes] and a tile's box starts at row tile_index * 128.
+int launch_tile_weights_fp8(const void* src, void* dst, int64_t matrices, int rows, int cols, cudaStream_t stream);
 size_t grouped_gemm_smem_bytes(bool gate_up, int block_m, int k, int stages);
 int grouped_gemm_pick_stages(bool gate_up, int block_m, int k);
 

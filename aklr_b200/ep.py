@@ -42,6 +42,7 @@ from aklr_b200.moe import (
     _stream,
     fused_experts_fp8,
     fused_experts_mxfp4,
+    require_row_major,
     route,
 )
 
@@ -206,6 +207,7 @@ class ExpertParallelMoE:
     def __init__(self, routing: Routing, w1, w1_scale, w2, w2_scale, rank: int, world: int, kernels=None):
         self.routing = dataclasses.replace(routing, n_shared=0)
         self.n_shared = routing.n_shared
+        require_row_major(w1, w2)  # the rank's slices below are views: a tile-contiguous tensor cannot be sliced this way
         self.n_local = w1.shape[0] - self.n_shared
         if self.n_local < 1:
             raise ValueError("w1 must hold at least one routed expert before the shared ones")

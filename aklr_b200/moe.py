@@ -164,6 +164,20 @@ class Workspace:
         return self._view(self.layout.rows, n * self.cfg.hidden, torch.bfloat16).view(n, self.cfg.hidden)
 
 
+def _weights_variant(w1, w2) -> int:
+    """VARIANT_TILED_WEIGHTS when both weight tensors carry ``is_b200_tiled`` (aklr_b200.layouts), 0 when neither."""
+    tiled = [bool(getattr(w, "is_b200_tiled", False)) for w in (w1, w2)]
+    if tiled[0] != tiled[1]:
+        raise ValueError("w1 and w2 must be in the same layout: both row-major or both tile-contiguous")
+    return _lib.VARIANT_TILED_WEIGHTS if tiled[0] else 0
+
+
+def require_row_major(*weights) -> None:
+    """Paths without a tile-contiguous form (MXFP4 experts, expert parallelism) refuse such tensors."""
+    if any(getattr(w, "is_b200_tiled", False) for w in weights):
+        raise ValueError("tile-contiguous weights are served by the FP8 single-GPU entry points only")
+
+
 def _check_weights(hidden_states, w1, w1_scale, w2, w2_scale):
     e, two_i, h = w1.shape
     inter = two_i // 2
@@ -200,7 +214,7 @@ def fused_moe_fp8(
     n_tokens, n_routed = logits.shape
     if n_routed + routing.n_shared != e or hidden_states.shape[0] != n_tokens:
         raise ValueError("w1 must hold the routed experts followed by the shared ones")
-    cfg = _config(n_tokens, h, inter, n_routed, routing, logits, bias, block_m, variant=variant)
+    cfg = _config(n_tokens, h, inter, n_routed, routing, logits, bias, block_m, variant=variant | _weights_variant(w1, w2))
     ws = workspace or Workspace(cfg, device)
     if out is None:
         out = torch.empty_like(hidden_states)
@@ -246,7 +260,7 @@ def fused_experts_fp8(
         raise ValueError("topk_ids int32 and topk_weights float32 must share the shape [tokens, routes]")
     n_tokens, routes = topk_ids.shape
     n_global = 0 if expert_map is None else expert_map.numel()
-    cfg = _config(n_tokens, h, inter, e, Routing(topk=routes), None, None, block_m, n_global)
+    cfg = _config(n_tokens, h, inter, e, Routing(topk=routes), None, None, block_m, n_global, variant=_weights_variant(w1, w2))
     ws = Workspace(cfg, device)
     if out is None:
         out = torch.empty_like(hidden_states)
@@ -327,6 +341,7 @@ def fused_experts_mxfp4(
         ACTIVATIONS[activation], int(weight_in_stage1), float(swiglu_limit or 0.0), float(beta or 0.0),
         float(linear_beta or 0.0), _ptr(num_local_tokens),
     )
+    require_row_major(w1, w2)
     e, inter, h = _check_mx_weights(hidden_states, w1, w1_scale, w2, w2_scale)
     if topk_ids.dtype != torch.int32 or topk_weights.dtype != torch.float32 or topk_ids.shape != topk_weights.shape:
         raise ValueError("topk_ids int32 and topk_weights float32 must share the shape [tokens, routes]")
@@ -364,6 +379,7 @@ def fused_moe_mxfp4(
     """The whole MXFP4 layer from router logits (the routing of ``fused_moe_fp8``).  ``act_bits`` as in
     ``fused_experts_mxfp4``: 8 MXFP8 activations, 16 activations kept in bf16."""
     device = _need_cuda(hidden_states, logits, bias, w1, w1_scale, w2, w2_scale, out)
+    require_row_major(w1, w2)
     e, inter, h = _check_mx_weights(hidden_states, w1, w1_scale, w2, w2_scale)
     n_tokens, n_routed = logits.shape
     if n_routed + routing.n_shared != e or hidden_states.shape[0] != n_tokens:

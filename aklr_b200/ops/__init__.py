@@ -67,6 +67,12 @@ def _attr_name(value: Any) -> Any:
     return name.lower() if isinstance(name, str) else (value.lower() if isinstance(value, str) else value)
 
 
+def _layout(call: Mapping[str, Any]) -> str:
+    """The weights' layout variant, first element of a dispatch key (the reference keys its variants the same way,
+    aklr/plugins/sglang/models/deepseek_v2/contract.py:310-318)."""
+    return "b200_tiled" if getattr(call["w1"], "is_b200_tiled", False) else "row_major"
+
+
 def _fp8_weights_key(call: Mapping[str, Any], hidden: int, device) -> tuple | None:
     """(experts, inter) when w1/w2 and their 128 x 128 block scales are well formed, row-major."""
     w1, w2, s1, s2 = call["w1"], call["w2"], call["w1_scale"], call["w2_scale"]
@@ -76,6 +82,9 @@ def _fp8_weights_key(call: Mapping[str, Any], hidden: int, device) -> tuple | No
         return None
     # the aiter-shuffled layout (16 x 16 tiles) is another layout variant, not served here
     if getattr(w1, "is_shuffled", False) or getattr(w2, "is_shuffled", False):
+        return None
+    # row-major as the checkpoint stores them, or both tile-contiguous (aklr_b200.layouts.to_b200_tiled)
+    if bool(getattr(w1, "is_b200_tiled", False)) != bool(getattr(w2, "is_b200_tiled", False)):
         return None
     e, two_i, h = w1.shape
     inter = two_i // 2
@@ -124,7 +133,7 @@ def _deepseek_key(call):
         or not (1 <= topk <= min(31, topk_group * (n_routed // groups)))
     ):
         return None
-    return ("row_major", hidden, n_routed, weights[1], topk, groups, topk_group, call["renormalize"], float(factor))
+    return (_layout(call), hidden, n_routed, weights[1], topk, groups, topk_group, call["renormalize"], float(factor))
 
 
 def _layer_alloc(call, key):
@@ -294,7 +303,7 @@ def _qwen3_key(call):
     topk = call["topk"]
     if not isinstance(topk, int) or isinstance(topk, bool) or not (1 <= topk <= min(32, n_routed)):
         return None
-    return ("row_major", hidden, n_routed, weights[1], topk)
+    return (_layout(call), hidden, n_routed, weights[1], topk)
 
 
 def _qwen3_run(call, out):
@@ -362,7 +371,7 @@ def _minimax_key(call, mx: bool = False):
         return None
     if not (1 <= topk <= min(32, n_routed)) or not (0 <= offset and offset + weights[0] <= n_routed):
         return None
-    return ("row_major", hidden, n_routed, weights[0], weights[1], topk, offset)
+    return (_layout(call), hidden, n_routed, weights[0], weights[1], topk, offset)
 
 
 _EXPERT_MAPS: dict[tuple, torch.Tensor] = {}
@@ -503,7 +512,7 @@ def _qwen2_router_experts_key(call):
     topk = call["topk"]
     if common is None or not isinstance(topk, int) or isinstance(topk, bool) or not (1 <= topk <= min(31, common[2])):
         return None
-    return ("row_major", *common[1:], topk)
+    return (_layout(call), *common[1:], topk)
 
 
 def _qwen2_router_experts_run(call, out):
@@ -564,7 +573,7 @@ def _qwen2_experts_key(call):
         return None
     if wts.shape != ids.shape or wts.shape[0] != n_tokens or not (1 <= wts.shape[1] <= min(31, n_routed)):
         return None
-    return ("row_major", *common[1:], wts.shape[1])
+    return (_layout(call), *common[1:], wts.shape[1])
 
 
 def _qwen2_experts_run(call, out):
@@ -752,6 +761,8 @@ def _mx_weights_key(call: Mapping[str, Any], hidden: int, device) -> tuple | Non
     e8 = (torch.uint8,) + ((torch.float8_e8m0fnu,) if hasattr(torch, "float8_e8m0fnu") else ())
     if not (tensor_ok(w1, fp4, 3, device) and tensor_ok(w2, fp4, 3, device) and tensor_ok(s1, e8, 3, device) and tensor_ok(s2, e8, 3, device)):
         return None
+    if getattr(w1, "is_b200_tiled", False) or getattr(w2, "is_b200_tiled", False):
+        return None  # the tile-contiguous layout is an FP8 layout
     e, two_i, half_h = w1.shape
     inter = two_i // 2
     if half_h * 2 != hidden or hidden % 256 or inter % 128 or two_i % 256:
@@ -863,7 +874,7 @@ def _fused_moe_key(call):
             return None
         if any(isinstance(v, torch.Tensor) and overlaps(out, v) for k, v in call.items() if k != "out"):
             return None
-    return ("row_major", hidden, weights[0], weights[1], ids.shape[1], global_experts, mask is not None)
+    return (_layout(call), hidden, weights[0], weights[1], ids.shape[1], global_experts, mask is not None)
 
 
 def _fused_moe_alloc(call, key):

@@ -77,6 +77,10 @@ typedef struct aklr_moe_config {
 #define AKLR_VARIANT_SEPARATE_PROLOGUE 4      /* 1..8 tokens: routing and sort as two kernels, not one */
 #define AKLR_VARIANT_FULL_ACTIVATION_BOXES 8  /* MXFP4 GEMMs load all 128 activation rows of every block */
 #define AKLR_VARIANT_DEEP_PIPELINE 64         /* FP8 token-major GEMMs on 128 x 128 tiles with four partials in flight */
+/* w1 / w2 of the FP8 entry points are in the tile-contiguous layout aklr_tile_weights_fp8 writes (block scales are
+ * unchanged).  A layout variant of the weights, as the reference's `is_shuffled` is one of its own
+ * (aklr/plugins/sglang/models/deepseek_v2/contract.py:181-185, 310-318): results are bit-identical to row-major. */
+#define AKLR_VARIANT_TILED_WEIGHTS 128
 /* A numerics mode rather than a kernel choice (it also sizes the workspace, so set it before asking for the layout):
  * the MXFP4 expert entry points keep the activations in bf16 instead of rounding them to MXFP8 -- what the reference's
  * fused_moe does under gate_mode "interleave" and for gpt-oss swiglu below 256 rows (aklr/ops/fused_moe/
@@ -303,6 +307,13 @@ int aklr_moe_shared_gate(const void* x, const void* shared_gate_weight, const in
 int aklr_silu_mul_bf16(const void* gate_up, void* out, int32_t n_tokens, int32_t inter, void* stream);
 int aklr_moe_add_gated_rows(const void* x, const void* shared_gate_weight, const void* rows, void* out, int32_t n_tokens,
                             int32_t hidden, void* stream);
+
+/* Load-time converter, outside any layer call: `matrices` row-major FP8 matrices [rows, cols] (an expert tensor
+ * [E, rows, cols] is E of them) -> [matrix][rows/128][cols/128][128][128 bytes], every 128 x 128-byte tile one
+ * contiguous 16 KB run.  rows and cols multiples of 128; src and dst 16-byte aligned, not overlapping.  The
+ * reference's layout variants are converted the same way, by the engine at load time
+ * (`Preshuffle`, aklr/core/contract/semantics/_layouts.py:103-121). */
+int aklr_tile_weights_fp8(const void* src, void* dst, int64_t matrices, int32_t rows, int32_t cols, void* stream);
 
 /* logits float32 [T,E] = x (bf16 [T,H]) @ w (float32 [E,H])^T, nothing rounded: the gate of
  * `minimax_m2_fp8_moe` (aklr/plugins/sglang/models/minimax_m2/reference.py:43-50). */

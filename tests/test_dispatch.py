@@ -228,3 +228,20 @@ def test_mega_moe_declares_that_it_cannot_be_captured():
 
     assert ops.MEGA_MOE.capturable is False
     assert all(c.capturable for c in (ops.FUSED_MOE, ops.BIASED_GROUPED_TOPK))
+
+
+
+def test_tile_contiguous_layout_round_trips_on_the_host():
+    """from_b200_tiled undoes the layout [.., rows/128, cols/128, 128, 128] (the converter itself is a device kernel)."""
+    import torch
+
+    from aklr_b200 import layouts
+
+    w = torch.arange(2 * 256 * 384, dtype=torch.int64).remainder(251).to(torch.uint8).reshape(2, 256, 384)
+    tiled = w.reshape(2, 2, 128, 3, 128).permute(0, 1, 3, 2, 4).contiguous().reshape(2, 256, 384)
+    assert torch.equal(layouts.from_b200_tiled(tiled), w)
+    assert not layouts.is_b200_tiled(w)
+    import pytest
+
+    with pytest.raises(ValueError, match="CUDA"):
+        layouts.to_b200_tiled(w)

@@ -49,6 +49,23 @@ def test_deepseek_v2_fp8_moe_op(ops, golden):
     assert orc.gates_pass(gates), gates
 
 
+def test_ops_take_tile_contiguous_weights_by_their_attribute(ops):
+    """A loader converts the experts once (aklr_b200.layouts.to_b200_tiled); the op reads the tensors' attribute, keys the
+    call as another layout variant and returns the row-major call's output bit for bit.  One converted tensor
+    with one row-major one is outside the contract."""
+    from aklr_b200 import layouts
+
+    cfg, a = cases.ds_small_layer()
+    d = to_dev(a)
+    kw = dict(topk=cfg.topk, num_expert_group=cfg.num_expert_group, topk_group=cfg.topk_group, renormalize=True,
+              scoring_func="sigmoid")
+    plain = ops.deepseek_v2_fp8_moe(**d, **kw)
+    tiled = {**d, "w1": layouts.to_b200_tiled(d["w1"]), "w2": layouts.to_b200_tiled(d["w2"])}
+    out = ops.deepseek_v2_fp8_moe(**tiled, **kw)
+    assert isinstance(out, torch.Tensor) and torch.equal(out.cpu(), plain.cpu())
+    assert ops.deepseek_v2_fp8_moe(**{**tiled, "w2": d["w2"]}, **kw) is ops.FallbackReason.OUT_OF_CONTRACT
+
+
 def test_deepseek_v2_mxfp4_moe_op(ops, golden):
     """MXFP4 experts, ungrouped routing with a float32 bias, activations never quantised: against the reference's
     stored output (the kernels round the gated product to bf16, the reference does not: far inside the gates)."""

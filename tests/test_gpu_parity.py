@@ -615,3 +615,38 @@ def test_router_gemm_paths_round_like_the_oracle(n_tokens, hidden, experts):
     step = ref.abs().clamp_min(1e-2) * 2.0**-7
     assert ((got - ref).abs() <= step).all()
     assert (got == ref).float().mean() > 0.95
+
+
+def test_tile_contiguous_weights_give_the_row_major_results():
+    """The load-time converter against the torch statement of the layout, and the layer on tile-contiguous
+    weights against the same call on row-major ones, bit for bit: decode blocks (weight-major kernel), full
+    blocks (token-major kernel, whose down projection then takes its 256 rows as two tiles) and the 128 x 128-tile
+    variant (64-row boxes inside a tile)."""
+    from aklr_b200 import _lib, layouts
+    from aklr_b200.moe import fused_experts_fp8, fused_moe_fp8
+
+    d = dev()
+    cfg = wl.CONFIGS["deepseek_small"]
+    w1, s1, w2, s2 = (x.to(d) for x in wl.expert_weights(cfg, seed=11))
+    t1, t2 = layouts.to_b200_tiled(w1), layouts.to_b200_tiled(w2)
+    assert layouts.is_b200_tiled(t1) and t1.shape == w1.shape and t1.dtype == w1.dtype
+    e, rows, cols = w1.shape
+    expect = w1.view(torch.uint8).reshape(e, rows // 128, 128, cols // 128, 128).permute(0, 1, 3, 2, 4).contiguous()
+    assert torch.equal(t1.view(torch.uint8).reshape(expect.shape), expect)
+    assert torch.equal(layouts.from_b200_tiled(t1.view(torch.uint8)), w1.view(torch.uint8))
+    assert layouts.to_b200_tiled(t1) is t1
+    for n_tokens, variant in ((5, 0), (40, 0), (300, 0), (1500, 0), (1500, _lib.VARIANT_DEEP_PIPELINE)):
+        hidden, logits, bias = (x.to(d) for x in wl.router_inputs(cfg, n_tokens, seed=12 + n_tokens))
+        outs = []
+        for a, b in ((w1, w2), (t1, t2)):
+            out, ws = fused_moe_fp8(hidden, logits, bias, a, s1, b, s2, routing_of(cfg), return_workspace=True, variant=variant)
+            ws.check_status()
+            outs.append(out.cpu())
+        assert torch.equal(outs[0], outs[1]), (n_tokens, variant, ws.layout.block_m)
+    # routing given (the experts-only entry point), and a mixed pair is refused
+    ids = torch.stack([torch.randperm(cfg.n_experts)[:4] for _ in range(64)]).to(torch.int32).to(d)
+    wts = torch.rand(64, 4).to(d)
+    x = wl.router_inputs(cfg, 64, seed=3)[0].to(d)
+    assert torch.equal(fused_experts_fp8(x, ids, wts, t1, s1, t2, s2).cpu(), fused_experts_fp8(x, ids, wts, w1, s1, w2, s2).cpu())
+    with pytest.raises(ValueError, match="same layout"):
+        fused_experts_fp8(x, ids, wts, t1, s1, w2, s2)
