@@ -103,6 +103,7 @@ SIGNATURES = {
     "aklr_moe_align_noalloc_last_error": (c_char_p, []),
     "aklr_silu_mul_bf16": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_void_p]),
     "aklr_moe_add_gated_rows": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_void_p]),
+    "aklr_selftest_exact_divide": (c_int32, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "aklr_tile_weights_fp8": (c_int32, [c_void_p, c_void_p, c_int64, c_int32, c_int32, c_void_p]),
     "aklr_moe_shared_gate": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p]),
     "aklr_router_gemm_f32": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p]),

@@ -1227,6 +1227,16 @@ int aklr_moe_add_gated_rows(const void* x, const void* shared_gate_weight, const
   return AKLR_OK;
 }
 
+int aklr_selftest_exact_divide(const float* x, const float* scale, int64_t n, int32_t* mismatches, void* stream) {
+  if (!x || !scale || !mismatches || n < 0) return fail(AKLR_ERR_BAD_ARGUMENT, "bad argument");
+  int rc = check_device();
+  if (rc) return rc;
+  rc = aklr::launch_exact_divide_selftest(x, scale, n, mismatches, static_cast<cudaStream_t>(stream));
+  if (rc) return fail(rc, "division self-test launch failed");
+  g_launches += n > 0;
+  return AKLR_OK;
+}
+
 int aklr_tile_weights_fp8(const void* src, void* dst, int64_t matrices, int32_t rows, int32_t cols, void* stream) {
   if (!src || !dst) return fail(AKLR_ERR_BAD_ARGUMENT, "NULL argument");
   int rc = check_device();

@@ -21,8 +21,9 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
   const int64_t total = static_cast<int64_t>(p.n_tokens) * vec_per_row;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-    const int token = static_cast<int>(i / vec_per_row);
-    const int v = static_cast<int>(i - static_cast<int64_t>(token) * vec_per_row);
+    // 32-bit division (the total is far below 2^31): the 64-bit one is a subroutine
+    const int token = static_cast<int>(static_cast<uint32_t>(i) / static_cast<uint32_t>(vec_per_row));
+    const int v = static_cast<int>(static_cast<uint32_t>(i) - static_cast<uint32_t>(token) * static_cast<uint32_t>(vec_per_row));
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     const bool received = !p.num_local_tokens || token < __ldg(p.num_local_tokens);
     // Slots are summed in order, but their loads do not wait for one another: ids of a batch of
@@ -71,6 +72,7 @@ int launch_combine(const CombineParams& p, cudaStream_t stream) {
   if (p.hidden % 8 != 0) return AKLR_ERR_UNSUPPORTED_SHAPE;
   if (p.n_tokens == 0) return AKLR_OK;
   const int64_t total = static_cast<int64_t>(p.n_tokens) * (p.hidden / 8);
+  if (total >= (int64_t{1} << 31)) return AKLR_ERR_TOO_LARGE;
   const int64_t blocks = (total + 255) / 256;
   const int grid = static_cast<int>(blocks < 148 * 8 ? blocks : 148 * 8);
   return launch_kernel(combine_kernel, dim3(grid), dim3(256), 0, stream, 1, p) == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
@@ -174,7 +176,7 @@ __global__ void __launch_bounds__(256)
 silu_mul_bf16_kernel(const uint16_t* __restrict__ gate_up, uint16_t* __restrict__ out, int64_t n_vectors, int vec_per_row) {
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vectors; i += stride) {
-    const int64_t row = i / vec_per_row;
+    const int64_t row = static_cast<uint32_t>(i) / static_cast<uint32_t>(vec_per_row);  // n_vectors < 2^31: checked at launch
     const int64_t v = i - row * vec_per_row;
     const uint4 g = *reinterpret_cast<const uint4*>(gate_up + (row * 2 * vec_per_row + v) * 8);
     const uint4 u = *reinterpret_cast<const uint4*>(gate_up + (row * 2 * vec_per_row + vec_per_row + v) * 8);
@@ -233,6 +235,7 @@ int launch_silu_mul_bf16(const void* gate_up, void* out, int n_tokens, int inter
   if (n_tokens == 0) return AKLR_OK;
   const int vec_per_row = inter / 8;
   const int64_t n_vectors = static_cast<int64_t>(n_tokens) * vec_per_row;
+  if (n_vectors >= (int64_t{1} << 31)) return AKLR_ERR_TOO_LARGE;
   const int grid = static_cast<int>(std::min<int64_t>((n_vectors + 255) / 256, 148 * 8));
   silu_mul_bf16_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(gate_up), static_cast<uint16_t*>(out), n_vectors, vec_per_row);
   return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;

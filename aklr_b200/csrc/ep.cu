@@ -139,8 +139,8 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(EpCombineParams p) {
   const int64_t total = static_cast<int64_t>(p.n_tokens) * vec_per_row;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-    const int token = static_cast<int>(i / vec_per_row);
-    const int v = static_cast<int>(i - static_cast<int64_t>(token) * vec_per_row);
+    const int token = static_cast<int>(static_cast<uint32_t>(i) / static_cast<uint32_t>(vec_per_row));  // total < 2^31: checked at launch
+    const int v = static_cast<int>(static_cast<uint32_t>(i) - static_cast<uint32_t>(token) * static_cast<uint32_t>(vec_per_row));
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     auto add = [&](const void* base, size_t row) {
       const uint4 raw = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + row * p.hidden + v * 8);
@@ -171,6 +171,7 @@ int launch_ep_combine(const EpCombineParams& p, cudaStream_t stream) {
   if (p.hidden % 8 != 0) return AKLR_ERR_UNSUPPORTED_SHAPE;
   if (p.n_tokens == 0) return AKLR_OK;
   const int64_t total = static_cast<int64_t>(p.n_tokens) * (p.hidden / 8);
+  if (total >= (int64_t{1} << 31)) return AKLR_ERR_TOO_LARGE;
   const int64_t blocks = (total + 255) / 256;
   const int grid = static_cast<int>(blocks < 148 * 8 ? blocks : 148 * 8);
   ep_combine_kernel<<<grid, 256, 0, stream>>>(p);

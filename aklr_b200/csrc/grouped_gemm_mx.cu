@@ -621,8 +621,8 @@ __global__ void __launch_bounds__(256) gather_quant_mxfp8_kernel(MxQuantParams p
   const int64_t quads = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 2;
   const int KB = p.hidden >> 7;
   for (int64_t g = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 2; g < total; g += quads) {
-    const int row = static_cast<int>(g / groups_per_row);
-    const int grp = static_cast<int>(g - static_cast<int64_t>(row) * groups_per_row);
+    const int row = static_cast<int>(static_cast<uint32_t>(g) / static_cast<uint32_t>(groups_per_row));  // total < 2^31: checked at launch
+    const int grp = static_cast<int>(static_cast<uint32_t>(g) - static_cast<uint32_t>(row) * static_cast<uint32_t>(groups_per_row));
     const int rid = p.sorted_ids ? p.sorted_ids[row] : row;  // no table: quantise the rows in place order
     if (rid < 0) continue;
     const int token = rid / p.routes_per_token;
@@ -754,6 +754,7 @@ int launch_gather_quant_mxfp8(const MxQuantParams& p, cudaStream_t stream) {
     return launch_kernel(gather_rows_mxfp8_kernel, dim3(grid), dim3(256), 0, stream, 1, p) == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
   }
   const int64_t groups = static_cast<int64_t>(p.n_rows) * (p.hidden / 32);
+  if (groups >= (int64_t{1} << 31)) return AKLR_ERR_TOO_LARGE;
   const int64_t blocks = (groups * 4 + 255) / 256;
   const int grid = static_cast<int>(blocks < 148 * 16 ? blocks : 148 * 16);
   return launch_kernel(gather_quant_mxfp8_kernel, dim3(grid), dim3(256), 0, stream, 1, p) == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;

@@ -117,6 +117,7 @@ int launch_grouped_gemm_deep(const GroupedGemmParams& p, bool gate_up, int sm_co
 // Tile-contiguous FP8 weights (a layout a checkpoint loader can convert to once): every 128-row x 128-byte tile
 // the TMA fetches is one contiguous 16 KB run of HBM instead of 128 row segments k bytes apart.  The map is then
 // over [tiles * 128 rows, 128 bytes] and a tile's box starts at row tile_index * 128.
+int launch_exact_divide_selftest(const float* x, const float* scale, int64_t n, int32_t* mismatches, cudaStream_t stream);
 int launch_tile_weights_fp8(const void* src, void* dst, int64_t matrices, int rows, int cols, cudaStream_t stream);
 size_t grouped_gemm_smem_bytes(bool gate_up, int block_m, int k, int stages);
 int grouped_gemm_pick_stages(bool gate_up, int block_m, int k);

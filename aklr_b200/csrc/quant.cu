@@ -83,6 +83,7 @@ int launch_gather_quant_fp8(const GatherQuantParams& p, cudaStream_t stream) {
   if (p.hidden % 128 != 0) return AKLR_ERR_UNSUPPORTED_SHAPE;
   if (p.n_rows == 0) return AKLR_OK;
   const int64_t groups = static_cast<int64_t>(p.n_rows) * (p.hidden / 128);
+  if (groups >= (int64_t{1} << 31)) return AKLR_ERR_TOO_LARGE;
   const int64_t blocks = (groups * 16 + 255) / 256;
   const int grid = static_cast<int>(blocks < 148 * 16 ? blocks : 148 * 16);
   return launch_kernel(gather_quant_fp8_kernel, dim3(grid), dim3(256), 0, stream, 1, p) == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
@@ -96,22 +97,35 @@ per_group_quant_fp8_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__
   const int sub = threadIdx.x & 15;
   const uint32_t group_mask = 0xFFFFu << (threadIdx.x & 16);  // the lanes of this half-warp
   const int64_t half_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 4;
-  for (int64_t g = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4; g < total;
-       g += half_warps) {
-    const int row = static_cast<int>(g / groups_per_row);
-    const int grp = static_cast<int>(g - static_cast<int64_t>(row) * groups_per_row);
-    const size_t at = static_cast<size_t>(row) * hidden + grp * 128 + sub * 8;
-    float v[8];
-    unpack8(*reinterpret_cast<const uint4*>(x + at), v);
-    float m = amax8(v);
+  // kOpGroupsInFlight groups per half-warp and pass (more than one measured slower: occupancy hides the latency already)
+  for (int64_t g0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4; g0 < total;
+       g0 += half_warps * kOpGroupsInFlight) {
+    uint4 raw[kOpGroupsInFlight];
 #pragma unroll
-    for (int off = 8; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(group_mask, m, off, 16));
-    const float scale = __fmul_rn(fmaxf(m, 1e-10f), 1.0f / 448.0f);
-    const float recip = __fdiv_rn(1.0f, scale);
+    for (int u = 0; u < kOpGroupsInFlight; ++u) {
+      const int64_t g = g0 + u * half_warps;
+      if (g < total) raw[u] = *reinterpret_cast<const uint4*>(x + g * 128 + sub * 8);  // groups of a row follow one another
+    }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = fminf(fmaxf(__fmul_rn(v[i], recip), -448.0f), 448.0f);
-    *reinterpret_cast<uint2*>(q + at) = pack8_e4m3(v);
-    if (sub == 0) scales[static_cast<size_t>(grp) * rows + row] = scale;
+    for (int u = 0; u < kOpGroupsInFlight; ++u) {
+      const int64_t g = g0 + u * half_warps;
+      if (g >= total) continue;
+      float v[8];
+      unpack8(raw[u], v);
+      float m = amax8(v);
+#pragma unroll
+      for (int off = 8; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(group_mask, m, off, 16));
+      const float scale = __fmul_rn(fmaxf(m, 1e-10f), 1.0f / 448.0f);
+      const float recip = __fdiv_rn(1.0f, scale);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = fminf(fmaxf(__fmul_rn(v[i], recip), -448.0f), 448.0f);
+      *reinterpret_cast<uint2*>(q + g * 128 + sub * 8) = pack8_e4m3(v);
+      if (sub == 0) {
+        const uint32_t row = static_cast<uint32_t>(g) / static_cast<uint32_t>(groups_per_row);  // g < 2^31: checked at launch
+        const uint32_t grp = static_cast<uint32_t>(g) - row * static_cast<uint32_t>(groups_per_row);
+        scales[static_cast<size_t>(grp) * rows + row] = scale;
+      }
+    }
   }
 }
 
@@ -120,33 +134,46 @@ int launch_per_group_quant_fp8(const void* x, uint8_t* q, float* scales, int row
   if (hidden % 128 != 0) return AKLR_ERR_UNSUPPORTED_SHAPE;
   if (rows == 0) return AKLR_OK;
   const int64_t groups = static_cast<int64_t>(rows) * (hidden / 128);
+  if (groups >= (int64_t{1} << 31)) return AKLR_ERR_TOO_LARGE;
   const int64_t blocks = (groups * 16 + 255) / 256;
   const int grid = static_cast<int>(blocks < 148 * 16 ? blocks : 148 * 16);
   per_group_quant_fp8_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), q, scales, rows, hidden);
   return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
 }
 
-// Four lanes x 8 values per 1 x 32 group.
+// Four lanes x 8 values per 1 x 32 group.  The scale is a power of two, so dividing by it is multiplying by the
+// power of two that is its reciprocal: the same real number rounded the same way, without a division.
 __global__ void __launch_bounds__(256)
 per_group_quant_mxfp8_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ q,
                              uint8_t* __restrict__ scales, int64_t elements) {
   const int64_t slots = elements >> 3;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   const uint32_t group_mask = 0xFu << (threadIdx.x & 28);  // the four lanes of this group
-  // the four lanes of a group run the same number of iterations: slots is a multiple of 4
-  for (int64_t slot = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; slot < slots; slot += stride) {
-    float v[8];
-    unpack8(*reinterpret_cast<const uint4*>(x + slot * 8), v);
-    float m = amax8(v);
-    m = fmaxf(m, __shfl_xor_sync(group_mask, m, 2, 4));
-    m = fmaxf(m, __shfl_xor_sync(group_mask, m, 1, 4));
-    const uint32_t raw = __float_as_uint(__fmul_rn(fmaxf(m, 1e-10f), 1.0f / 448.0f));
-    const uint32_t exponent = (raw >> 23) + ((raw & 0x7FFFFFu) != 0u ? 1u : 0u);
-    const float scale = __uint_as_float(exponent << 23);
+  // the four lanes of a group run the same number of iterations: slots and the stride are multiples of 4
+  for (int64_t slot0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; slot0 < slots; slot0 += stride * kOpGroupsInFlight) {
+    uint4 raw[kOpGroupsInFlight];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = fminf(fmaxf(__fdiv_rn(v[i], scale), -448.0f), 448.0f);
-    *reinterpret_cast<uint2*>(q + slot * 8) = pack8_e4m3(v);
-    if ((slot & 3) == 0) scales[slot >> 2] = static_cast<uint8_t>(exponent);
+    for (int u = 0; u < kOpGroupsInFlight; ++u)
+      if (slot0 + u * stride < slots) raw[u] = *reinterpret_cast<const uint4*>(x + (slot0 + u * stride) * 8);
+#pragma unroll
+    for (int u = 0; u < kOpGroupsInFlight; ++u) {
+      const int64_t slot = slot0 + u * stride;
+      if (slot >= slots) continue;
+      float v[8];
+      unpack8(raw[u], v);
+      float m = amax8(v);
+      m = fmaxf(m, __shfl_xor_sync(group_mask, m, 2, 4));
+      m = fmaxf(m, __shfl_xor_sync(group_mask, m, 1, 4));
+      const uint32_t bits = __float_as_uint(__fmul_rn(fmaxf(m, 1e-10f), 1.0f / 448.0f));
+      const uint32_t exponent = (bits >> 23) + ((bits & 0x7FFFFFu) != 0u ? 1u : 0u);  // 2^(exponent-127), 94 .. 255 here
+      // 2^(127-exponent): a normal number down to exponent 253, below that two exact factors
+      const float r1 = __uint_as_float((exponent <= 253u ? 254u - exponent : 1u) << 23);
+      const float r2 = exponent <= 253u ? 1.0f : __uint_as_float((255u - exponent) << 23);  // 2^-1 or 2^-2 past 2^-126
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = fminf(fmaxf(__fmul_rn(__fmul_rn(v[i], r1), r2), -448.0f), 448.0f);
+      *reinterpret_cast<uint2*>(q + slot * 8) = pack8_e4m3(v);
+      if ((slot & 3) == 0) scales[slot >> 2] = static_cast<uint8_t>(exponent);
+    }
   }
 }
 
@@ -158,6 +185,25 @@ int launch_per_group_quant_mxfp8(const void* x, uint8_t* q, uint8_t* scales, int
   const int64_t blocks = (elements / 8 + 255) / 256;
   const int grid = static_cast<int>(blocks < 148 * 16 ? blocks : 148 * 16);
   per_group_quant_mxfp8_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), q, scales, elements);
+  return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
+}
+
+// Self-test of ExactDivider against the division it replaces: counts the pairs where they differ.
+__global__ void __launch_bounds__(256)
+exact_divide_selftest_kernel(const float* __restrict__ x, const float* __restrict__ scale, int64_t n, int32_t* mismatches) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  int bad = 0;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const ExactDivider divide(scale[i]);
+    bad += __float_as_uint(divide(x[i])) != __float_as_uint(__fdiv_rn(x[i], scale[i]));
+  }
+  if (bad) atomicAdd(mismatches, bad);
+}
+
+int launch_exact_divide_selftest(const float* x, const float* scale, int64_t n, int32_t* mismatches, cudaStream_t stream) {
+  if (n <= 0) return AKLR_OK;
+  const int64_t blocks = (n + 255) / 256;
+  exact_divide_selftest_kernel<<<static_cast<int>(blocks < 148 * 8 ? blocks : 148 * 8), 256, 0, stream>>>(x, scale, n, mismatches);
   return cudaGetLastError() == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
 }
 

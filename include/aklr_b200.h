@@ -308,6 +308,12 @@ int aklr_silu_mul_bf16(const void* gate_up, void* out, int32_t n_tokens, int32_t
 int aklr_moe_add_gated_rows(const void* x, const void* shared_gate_weight, const void* rows, void* out, int32_t n_tokens,
                             int32_t hidden, void* stream);
 
+/* Self-test: the activation quantiser divides by a group's scale through a reciprocal and one exact residual
+ * step instead of an IEEE division per value (the reference divides: `_fp8_input`,
+ * aklr/plugins/sglang/models/qwen3_moe/reference.py:44-54).  Adds to *mismatches (int32, device, zeroed by the
+ * caller) the number of pairs (x[i], scale[i]), float32 on the device, where the two differ in any bit. */
+int aklr_selftest_exact_divide(const float* x, const float* scale, int64_t n, int32_t* mismatches, void* stream);
+
 /* Load-time converter, outside any layer call: `matrices` row-major FP8 matrices [rows, cols] (an expert tensor
  * [E, rows, cols] is E of them) -> [matrix][rows/128][cols/128][128][128 bytes], every 128 x 128-byte tile one
  * contiguous 16 KB run.  rows and cols multiples of 128; src and dst 16-byte aligned, not overlapping.  The

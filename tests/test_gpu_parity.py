@@ -650,3 +650,34 @@ def test_tile_contiguous_weights_give_the_row_major_results():
     assert torch.equal(fused_experts_fp8(x, ids, wts, t1, s1, t2, s2).cpu(), fused_experts_fp8(x, ids, wts, w1, s1, w2, s2).cpu())
     with pytest.raises(ValueError, match="same layout"):
         fused_experts_fp8(x, ids, wts, t1, s1, w2, s2)
+
+
+def test_quantiser_division_shortcut_is_the_ieee_division():
+    """The layer's quantiser computes x / scale as q + (x - q*scale) * (1/scale) with q = x * (1/scale).  Against
+    __fdiv_rn over 64 M pairs: bf16 values of every magnitude over scales as the quantiser forms them (amax / 448),
+    scales with an all-ones significand, the smallest scale it can use (FLT_MIN) and very large ones -- no bit differs."""
+    import ctypes
+
+    from aklr_b200 import _lib
+
+    lib = _lib.load()
+    d = dev()
+    g = torch.Generator(device=d).manual_seed(77)
+    n = 1 << 24
+    total = 0
+    for kind in range(4):
+        amax = torch.randn(n, generator=g, device=d).abs() * torch.exp2(torch.randint(-40, 40, (n,), generator=g, device=d).float())
+        scale = (amax.to(torch.bfloat16).float() / 448.0).clamp_min(torch.finfo(torch.float32).tiny)
+        if kind == 1:  # all-ones significands
+            scale = (scale.view(torch.int32) | 0x7FFFFF).view(torch.float32)
+        elif kind == 2:  # the floor and its neighbourhood
+            scale = torch.where(torch.rand(n, generator=g, device=d) < 0.5, torch.full_like(scale, torch.finfo(torch.float32).tiny), scale * 2.0**-100).clamp_min(torch.finfo(torch.float32).tiny)
+        elif kind == 3:
+            scale = scale * 2.0**80
+        x = (torch.rand(n, generator=g, device=d) * 2 - 1) * scale * 448.0  # |x / scale| <= 448, as inside a group
+        x = x.to(torch.bfloat16).float()
+        bad = torch.zeros(1, dtype=torch.int32, device=d)
+        _lib.check(lib.aklr_selftest_exact_divide(x.data_ptr(), scale.data_ptr(), n, bad.data_ptr(), torch.cuda.current_stream().cuda_stream))
+        total += int(bad.item())
+        assert int(bad.item()) == 0, (kind, int(bad.item()))
+    assert total == 0
