@@ -301,13 +301,13 @@ def run_reference_arm(args, cfg):
 
 def workload_config(cfg, args):
     return {
-        "workload": f"deepseek_v3 fp8 fused-moe layer, {args.tokens} tokens per GPU per step",
+        "workload": f"{'deepseek_v3' if cfg.name.startswith('deepseek_v3') else cfg.name} fp8 fused-moe layer, {args.tokens} tokens per GPU per step",
         "hidden": cfg.hidden,
         "moe_intermediate": cfg.inter,
         "routed_experts": cfg.n_routed,
         "shared_experts": cfg.n_shared,
         "topk": cfg.topk,
-        "routing": "sigmoid + correction bias, 8 groups / top-4 groups / top-8, x2.5",
+        "routing": "sigmoid + correction bias, 8 groups / top-4 groups / top-8, x2.5" if cfg.scoring == "sigmoid" else f"softmax top-{cfg.topk}",
         "weights": "fp8 e4m3, 128x128 fp32 block scales, N(0,0.02)" + (", tile-contiguous layout" if getattr(args, "tiled_weights", False) else ""),
         "activations": "bf16 N(0,1), 1x128 fp8 groups",
         "tokens_per_gpu": args.tokens,
@@ -563,11 +563,15 @@ def main() -> None:
     ap.add_argument("--block-m", type=int, default=0, help="force the tokens-per-block of the grouped GEMMs")
     ap.add_argument("--variant", type=int, default=0, help="aklr_moe_config.variant bits for the headline leg")
     ap.add_argument("--format", default="fp8", choices=["fp8", "mxfp4"], help="mxfp4: only the MXFP4 record, as the line's value")
+    ap.add_argument("--model", default="deepseek_v3", choices=["deepseek_v3", "mixtral", "qwen3"],
+                    help="widths of the headline leg (profiling captures of the other configurations; with --headline-only)")
     ap.add_argument("--tiled-weights", action="store_true", help="expert weights in the tile-contiguous layout (aklr_b200.layouts)")
     ap.add_argument("--published", action="store_true", help="only the workloads the reference records timings for, one JSON object")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
-    cfg = wl.CONFIGS["deepseek_v3"]
+    cfg = wl.CONFIGS[args.model]
+    if args.model != "deepseek_v3" and not args.headline_only:
+        raise SystemExit("--model other than deepseek_v3 times the headline leg alone: add --headline-only")
     if args.routed_experts:
         import dataclasses
 
