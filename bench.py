@@ -128,6 +128,26 @@ class ClockSampler:
         }
 
 
+def bind_near_gpu(local_rank: int) -> str:
+    """Run this process on the CPUs the driver reports as closest to its GPU, BEFORE pinned host buffers are
+    allocated: with eight ranks on one box, buffers that land on the other socket halve the copy bandwidth of the
+    end-to-end leg.  Reads the GPU's CPU set through NVML and changes only this process's scheduler affinity."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByIndex(local_rank)
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+        cpus = {64 * w + b for w, word in enumerate(words) for b in range(64) if (word >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return "unchanged (the GPU's CPU set is outside this process's)"
+        os.sched_setaffinity(0, cpus)
+        return f"{len(cpus)} CPUs near GPU {local_rank}"
+    except Exception as e:  # noqa: BLE001 -- no NVML, no permission: the copies still work, only slower
+        return f"unchanged ({type(e).__name__})"
+
+
 def routing_of(cfg):
     from aklr_b200.moe import Routing
 
@@ -164,7 +184,9 @@ class CpuPath:
         from oracle import moe_oracle as orc
 
         self.cfg, self.orc = cfg, orc
-        self.cores = os.cpu_count() or 1
+        if hasattr(os, "sched_setaffinity"):  # the GPU legs may have narrowed this process to the CPUs near its GPU
+            os.sched_setaffinity(0, range(os.cpu_count() or 1))
+        self.cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
         torch.set_num_threads(self.cores)
         cache: dict = {}
         self.host = [HostExperts(cfg, SEED, i, cache) for i in range(4)]
@@ -588,6 +610,7 @@ def main() -> None:
         raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    args.cpu_affinity = bind_near_gpu(local_rank)
     if args.published:
         print(json.dumps(bench_published(device)))
         return
@@ -808,6 +831,7 @@ def bench_one_gpu(args, cfg, device, local_rank, lib) -> dict:
             "unit": UNIT,
             "ms_per_step": e2e_ms,
             "h2d_bytes_per_step": T * cfg.hidden * 2,
+            "cpu_affinity": args.cpu_affinity,
             "d2h_bytes_per_step": T * cfg.hidden * 2,
             "api": "aklr_b200.ops.deepseek_v2_fp8_moe (router GEMM included); copies double-buffered on their own streams",
             "clocks": e2e_sampler.stop(),
@@ -1102,6 +1126,7 @@ def bench_ep(args, cfg, rank, world, device, lib):
             "unit": UNIT,
             "ms_per_step": fp8["e2e_ms"],
             "h2d_bytes_per_step": tokens * cfg.hidden * 2,
+            "cpu_affinity": args.cpu_affinity,
             "d2h_bytes_per_step": tokens * cfg.hidden * 2,
             "api": "router GEMM + aklr_b200.ep.ExpertParallelMoE.forward per rank, from pinned host hidden states; copies on their own streams",
             "copy_only_ms_per_step": fp8["copy_only_ms"],
