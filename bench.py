@@ -47,7 +47,11 @@ FALLBACK_HBM_GBS = 6650.0
 STAGES = ["route", "sort", "quant", "gate_up", "down", "combine"]
 # token counts each configuration is quoted on
 SWEEP_TOKENS = {"deepseek_v3": (1, 64, 256, 16384), "mixtral": (1, 16, 64, 256, 1024, 4096), "qwen3": (1, 32, 256, 2048, 8192)}
-CPU_SAMPLE_TOKENS = 8  # tokens per step of the CPU legs: about 60 of the 257 experts, 2.6 GB of weights
+# Tokens per step of the CPU legs.  The sample is a slice of the workload BY EXPERTS: every one of its tokens is routed
+# (through the reference's own routing, by a correction bias that lifts eight routed experts of four groups) to the same
+# eight routed experts plus the shared one, so each of the nine experts decodes its weights once for 143 rows -- the
+# 4096-token batch's rows per expert (4096 x 9 / 257).  Time per token is then the full batch's, in seconds not hours.
+CPU_SAMPLE_TOKENS = 143
 
 
 def measured_peaks() -> tuple[float, float, str]:
@@ -227,11 +231,27 @@ class CpuPath:
         return self.orc.deepseek_v2_fp8_moe(hidden, self.router_w, bias, self.host[0], self.host[1], self.host[2], self.host[3], c.topk,
                                             c.num_expert_group, c.topk_group, c.renormalize, c.routed_scaling_factor)
 
+    def slice_bias(self, bias, step):
+        """The correction bias with eight routed experts (two in each of four groups, others every step) lifted far above
+        the sigmoid scores: the reference's grouped top-k then sends every token to exactly those."""
+        c = self.cfg
+        if c.scoring != "sigmoid" or c.num_expert_group < 4 or c.topk != 8:
+            return bias  # other routings: the sample's tokens spread over the experts as they fall
+        per_group = c.n_routed // c.num_expert_group
+        lifted = bias.clone().float()
+        step %= 4  # four sets of experts in turn: 36 experts (1.6 GB) in host memory however many steps run
+        for g in range(4):
+            group = (2 * g + step) % c.num_expert_group
+            for k in range(2):
+                lifted[group * per_group + (3 + 7 * step + 13 * k) % per_group] += 100.0
+        return lifted.to(bias.dtype)
+
     def time_steps(self, sample_tokens, steps, warmup):
         """(tokens/s, seconds in the timed steps): ``steps`` calls on ``sample_tokens`` tokens each."""
         batches = []
         for s in range(steps + warmup):
             hidden, _, bias = wl.router_inputs(self.cfg, sample_tokens, SEED + 1000 + s)
+            bias = self.slice_bias(bias, s)
             self.host[0].prefetch(self.experts_hit(hidden, bias))
             batches.append((hidden, bias))
         for hidden, bias in batches[:warmup]:
@@ -285,8 +305,9 @@ def cpu_record(cpu: CpuPath, value, elapsed, steps, sample) -> dict:
         "unit": UNIT,
         "cores": cpu.cores,
         "kind": cpu.kind,
-        "sample": f"{steps} steps of {sample} tokens of the workload ({elapsed:.1f} s timed), router GEMM included, "
-                  "expert weights already in host memory; every step decodes the ~60 experts its tokens hit",
+        "sample": f"{steps} steps of {sample} tokens ({elapsed:.1f} s timed), router GEMM and routing included, expert weights "
+                  "already in host memory; a slice of the batch by experts: the step's tokens all route to the same 8 routed "
+                  "experts + the shared one, so each expert decodes once for the full batch's ~143 rows per expert",
     }
 
 
@@ -882,7 +903,7 @@ def bench_one_gpu(args, cfg, device, local_rank, lib) -> dict:
 
     if not args.no_cpu_baseline:
         cpu = CpuPath(cfg)
-        cpu_steps = 3
+        cpu_steps = 12  # ~10 s of CPU work on sixteen cores
         value, elapsed = cpu.time_steps(CPU_SAMPLE_TOKENS, cpu_steps, 1)
         line["cpu_baseline"] = cpu_record(cpu, value, elapsed, cpu_steps, CPU_SAMPLE_TOKENS)
         line["cpu_baseline"]["full_batch_estimate"] = cpu.full_batch_estimate(T)
