@@ -46,7 +46,6 @@ constexpr int kSfaBytes = 512;              // 128 rows x 4 K-steps
 __host__ __device__ constexpr int stage_bytes(bool split) { return (split ? 2 : 1) * kABytes + kBBytes + 2048; }
 __host__ __device__ constexpr int stage_b_offset(bool split) { return (split ? 2 : 1) * kABytes; }
 constexpr int kSfLoOffset = kSfaBytes + 1024;  // the second term's activation scales inside the 2 KB scale area
-constexpr bool kTileResidentScales = false;  // staging variant for short reductions; measured slower, kept for reference
 constexpr int kSfaCol = 256, kSfbCol = 260, kSfaLoCol = 268;  // TMEM columns after the 256 accumulator columns
 
 struct MxLayout {
@@ -184,16 +183,11 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   griddep_launch();
-  // Down projection with a short reduction (k = 512, 1024, 1536 or 2048): the staging warps keep a
-  // whole tile's weight scales in registers (see there).
-  const int KB_ = p.k >> 7;
-  const bool tile_regs = kTileResidentScales && !GATE_UP && (KB_ & 3) == 0 && KB_ <= 16;
-
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
-      mbar_init(&sf_full[s], tile_regs ? 2 : 1);  // both staging warps, or the one that owns the K-block
+      mbar_init(&sf_full[s], 1);  // the staging warp that owns the K-block
     }
     mbar_init(acc_full, 1);
     mbar_init(acc_empty, kEpi / 32);
@@ -310,81 +304,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
     const int KS = p.k >> 5;  // scale bytes per weight row
     uint32_t it0 = 0;         // K-blocks before this tile
     bool ok = true;
-    if (tile_regs) {
-      // A tile's weight scales are 256 rows x KS (<= 64) contiguous bytes.  Fetching one 4-byte word
-      // per row and K-block re-reads every 32-byte sector of those rows eight times and was the
-      // bottleneck of the down projection (the MMA warp waited ~500 cycles per K-block for scales).
-      // Here the 64 staging lanes hold the tile in registers -- rows lane64 + 64 j, j < 4, as KB/4
-      // 16-byte pieces of 4 K-blocks each -- and every lane writes its four words per K-block.  A
-      // piece is reloaded for the NEXT tile right after its last K-block, a whole tile ahead of use.
-      const int lane64 = sw * 32 + lane;
-      const int P = KB >> 2;
-      uint4 reg[4][4];
-      auto tile_base = [&](int t) -> const uint8_t* {
-        const int b = t / tiles_per_block, j = t - b * tiles_per_block;
-        const int e = p.block_expert[b];
-        return p.w_scale + (static_cast<size_t>(e) * p.rows_per_expert + j * 256) * KS;
-      };
-      auto load_piece = [&](const uint8_t* wb, int pc) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          reg[j][pc] = __ldg(reinterpret_cast<const uint4*>(wb + static_cast<size_t>(lane64 + 64 * j) * KS) + pc);
-      };
-      int t = blockIdx.x;
-      if (t < total_tiles) {
-        const uint8_t* wb = tile_base(t);
-#pragma unroll
-        for (int pc = 0; pc < 4; ++pc)
-          if (pc < P) load_piece(wb, pc);
-      }
-      // activation scales (already in tcgen05.cp order in global memory): warp 0, four K-blocks ahead
-      uint4 aq[4];
-      int ta = blockIdx.x, kba = 0;
-      auto aq_load = [&](uint4& a) {
-        if (ta < total_tiles) {
-          const int ba = ta / tiles_per_block;
-          a = __ldg(reinterpret_cast<const uint4*>(p.x_scale + (static_cast<size_t>(ba) * KB + kba) * kSfaBytes) + lane);
-          if (++kba == KB) {
-            kba = 0;
-            ta += gridDim.x;
-          }
-        }
-      };
-      if (sw == 0) {
-#pragma unroll
-        for (int d = 0; d < 4; ++d) aq_load(aq[d]);
-      }
-      int s = 0;
-      uint32_t ph = 0;
-      for (; t < total_tiles && ok; t += gridDim.x) {
-        const int tn = t + static_cast<int>(gridDim.x);
-        const uint8_t* wb_next = tn < total_tiles ? tile_base(tn) : nullptr;
-#pragma unroll
-        for (int kb = 0; kb < 16; ++kb) {
-          if (kb < KB && ok) {
-            bool got;
-            got = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 25);
-            if (!got) ok = false;
-            uint8_t* sf = smem + s * kStageBytes + kOffSf;
-            if (sw == 0) *reinterpret_cast<uint4*>(sf + lane * 16) = aq[kb & 3];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {  // row lane64 + 64 j = lane + 32 q with q = sw + 2 j
-              const uint4 v = reg[j][kb >> 2];
-              const uint32_t word = (kb & 3) == 0 ? v.x : (kb & 3) == 1 ? v.y : (kb & 3) == 2 ? v.z : v.w;
-              const int q = sw + 2 * j;
-              *reinterpret_cast<uint32_t*>(sf + kSfaBytes + (q >> 2) * 512 + lane * 16 + (q & 3) * 4) = word;
-            }
-            fence_proxy_async_smem();  // tcgen05.cp reads these bytes through the async proxy
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sf_full[s]);
-            if (sw == 0) aq_load(aq[kb & 3]);
-            if ((kb & 3) == 3 && wb_next) load_piece(wb_next, kb >> 2);
-            if (++s == S) { s = 0; ph ^= 1; }
-          }
-        }
-      }
-    }
-    for (int t = blockIdx.x; !tile_regs && t < total_tiles && ok; t += gridDim.x, it0 += KB) {
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, it0 += KB) {
       const int b = t / tiles_per_block, j = t - b * tiles_per_block;
       const int e = p.block_expert[b];
       const uint8_t* wsf[8];
