@@ -2,13 +2,15 @@
 pipe, the TMA ring and the two together can do with nothing else in their way.  The kernels' own periods are read
 against these numbers.
 
-    python -m aklr_b200.csrc.probes            # builds the three programs under build/probes and runs them
+    python -m aklr_b200.csrc.probes            # builds the programs under build/probes and runs them
 
 * ``tma_ring``: persistent CTAs that only run the operand ring of the token-major kernel (48 KB x 4 stages, or
   32 KB x 6), stages recycled the moment they fill: bytes per second from L2 / HBM into shared memory.
 * ``mma_chain``: cycles per ``tcgen05.mma kind::f8f6f4`` (M 128, K 32) for N = 16 .. 256, with every MMA depending on
   the one before or rotating over 2 .. 8 accumulators.
 * ``mma_beside_tma``: the MMA stream of a K-block (two deep) alone, a TMA ring alone, and both at once.
+* ``mx_issue``: the MXFP4 kernel's issue stream alone: four block-scaled MMAs per K-block with 0 .. 4 ``tcgen05.cp`` of
+  scale factors in front of them.
 
 Every wait in them is bounded; they allocate at most 4 GB and run for a few seconds.
 """
@@ -22,7 +24,7 @@ import sys
 HERE = pathlib.Path(__file__).resolve().parent
 ROOT = HERE.parents[2]
 OUT = ROOT / "build" / "probes"
-PROGRAMS = ("tma_ring", "mma_chain", "mma_beside_tma")
+PROGRAMS = ("tma_ring", "mma_chain", "mma_beside_tma", "mx_issue")
 
 
 def build() -> list[pathlib.Path]:
