@@ -26,56 +26,51 @@ __global__ void __launch_bounds__(256) gather_quant_fp8_kernel(GatherQuantParams
 }
 
 // Rows already quantised elsewhere (each token once, or by the sender of an expert-parallel
-// dispatch): copy row rid's codes and scales into the expert-sorted table.  A CTA moves four rows
-// at a time, every thread with four independent 16-byte loads in flight.
-constexpr int kGatherRows = 4;
+// dispatch): copy row rid's codes and scales into the expert-sorted table.  One warp per destination row, no
+// block-wide barrier: a lane issues all of its 16-byte loads of the row (hidden / 512 of them, 14 at 7168) before
+// its first store, so a warp keeps a whole row in flight.
+constexpr int kGatherMaxVecPerLane = 16;  // hidden <= 8192 in one pass; wider rows take further passes
 
 __global__ void __launch_bounds__(256) gather_rows_fp8_kernel(GatherQuantParams p) {
-  __shared__ int src_s[kGatherRows];
   griddep_launch();
   griddep_wait();
+  const int lane = threadIdx.x & 31;
   const int vec_per_row = p.hidden >> 4;
   const int groups_per_row = p.hidden >> 7;
   const size_t q_pitch = p.q_in_stride ? p.q_in_stride : p.hidden;
   const size_t s_pitch = p.scales_in_stride ? p.scales_in_stride : groups_per_row * sizeof(float);
   const int n_rows = p.num_rows ? min(*p.num_rows, p.n_rows) : p.n_rows;
-  for (int row0 = blockIdx.x * kGatherRows; row0 < n_rows; row0 += gridDim.x * kGatherRows) {
-    if (threadIdx.x < kGatherRows) {
-      const int row = row0 + threadIdx.x;
-      const int rid = row < n_rows ? p.sorted_ids[row] : -1;
-      src_s[threadIdx.x] = rid < 0 ? -1 : rid / p.routes_per_token;
-    }
-    __syncthreads();
-    int src[kGatherRows];
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  for (int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < n_rows; row += warps) {
+    const int rid = p.sorted_ids[row];  // the same address for the whole warp: one broadcast load
+    if (rid < 0) continue;              // padding rows are never read back
+    const int src = rid / p.routes_per_token;
+    const uint4* from = reinterpret_cast<const uint4*>(p.q_in + static_cast<size_t>(src) * q_pitch);
+    uint4* to = reinterpret_cast<uint4*>(p.q + static_cast<size_t>(row) * p.hidden);
+    for (int v0 = 0; v0 < vec_per_row; v0 += 32 * kGatherMaxVecPerLane) {
+      uint4 val[kGatherMaxVecPerLane];
 #pragma unroll
-    for (int r = 0; r < kGatherRows; ++r) src[r] = src_s[r];
-    for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
-      uint4 val[kGatherRows];
+      for (int u = 0; u < kGatherMaxVecPerLane; ++u) {
+        const int v = v0 + u * 32 + lane;
+        if (v < vec_per_row) val[u] = __ldg(from + v);
+      }
 #pragma unroll
-      for (int r = 0; r < kGatherRows; ++r)
-        if (src[r] >= 0)
-          val[r] = __ldg(reinterpret_cast<const uint4*>(p.q_in + static_cast<size_t>(src[r]) * q_pitch) + v);
-#pragma unroll
-      for (int r = 0; r < kGatherRows; ++r)
-        if (src[r] >= 0)
-          reinterpret_cast<uint4*>(p.q + static_cast<size_t>(row0 + r) * p.hidden)[v] = val[r];
+      for (int u = 0; u < kGatherMaxVecPerLane; ++u) {
+        const int v = v0 + u * 32 + lane;
+        if (v < vec_per_row) to[v] = val[u];
+      }
     }
-    for (int i = threadIdx.x; i < kGatherRows * groups_per_row; i += blockDim.x) {
-      const int r = i / groups_per_row, grp = i - r * groups_per_row;
-      const int row = row0 + r;
-      if (src_s[r] >= 0)
-        p.scales[(static_cast<size_t>(row / p.block_m) * groups_per_row + grp) * p.block_m + row % p.block_m] =
-            __ldg(reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(p.scales_in) + static_cast<size_t>(src_s[r]) * s_pitch) + grp);
-    }
-    __syncthreads();
+    const float* scales_from = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(p.scales_in) + static_cast<size_t>(src) * s_pitch);
+    float* scales_to = p.scales + static_cast<size_t>(row / p.block_m) * groups_per_row * p.block_m + row % p.block_m;
+    for (int grp = lane; grp < groups_per_row; grp += 32) scales_to[static_cast<size_t>(grp) * p.block_m] = __ldg(scales_from + grp);
   }
 }
 
 int launch_gather_rows_fp8(const GatherQuantParams& p, cudaStream_t stream) {
   if (p.hidden % 128 != 0 || p.block_m < 1) return AKLR_ERR_UNSUPPORTED_SHAPE;
   if (p.n_rows == 0) return AKLR_OK;
-  const int64_t blocks = (static_cast<int64_t>(p.n_rows) + kGatherRows - 1) / kGatherRows;
-  const int grid = static_cast<int>(blocks < 148 * 32 ? blocks : 148 * 32);
+  const int64_t blocks = (static_cast<int64_t>(p.n_rows) + 7) / 8;  // eight warps = eight rows per CTA and pass
+  const int grid = static_cast<int>(blocks < 148 * 16 ? blocks : 148 * 16);
   return launch_kernel(gather_rows_fp8_kernel, dim3(grid), dim3(256), 0, stream, 1, p) == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
 }
 
