@@ -202,3 +202,67 @@ def test_experts_with_1_127_128_129_255_257_rows(block_m):
     assert orc.gates_pass(gates), gates
     worst = ((out.cpu().float() - orc.bf16_round(ref)).abs().amax(dim=1) / ref.abs().amax(dim=1).clamp_min(1e-30))
     assert float(worst.max()) <= 2e-2, (int(worst.argmax()), float(worst.max()))
+
+
+def _layer_against_oracle(cfg, hidden, logits, bias, seed, max_experts=5):
+    from aklr_b200.moe import fused_moe_fp8
+
+    d = dev()
+    w1, s1, w2, s2 = wl.expert_weights(cfg, seed=seed, device=d)
+    bias_d = None if bias is None else bias.to(d)
+    out, ws = fused_moe_fp8(hidden.to(d), logits.to(d), bias_d, w1, s1, w2, s2, routing_of(cfg), return_workspace=True)
+    ws.check_status()
+    ref_ids, ref_w = oracle_routing(cfg, logits, bias)
+    assert torch.equal(ws.topk_ids().cpu().long(), ref_ids)
+    counts = torch.bincount(ref_ids.flatten(), minlength=cfg.n_experts)
+    assert torch.equal(ws.counts().cpu().long(), counts)
+    # the sorted table: every expert's run holds exactly its routes, in ascending route order, padded with -1
+    sorted_ids = ws.sorted_ids().cpu().long()
+    live = sorted_ids[sorted_ids >= 0]
+    assert live.numel() == ref_ids.numel()
+    by_expert = ref_ids.flatten()[live]
+    assert torch.equal(by_expert, by_expert.sort(stable=True).values)  # experts ascend along the table
+    same = by_expert[1:] == by_expert[:-1]
+    assert bool((live[1:][same] > live[:-1][same]).all())  # and routes ascend inside an expert
+    lazy = [LazyExperts(t) for t in (w1, s1, w2, s2)]
+
+    def one_expert(tokens, e, weights):
+        ids = torch.full((tokens.numel(), 1), e, dtype=torch.long)
+        return orc.fp8_experts(hidden[tokens], ids, weights.reshape(-1, 1), *lazy)
+
+    def whole_token(tokens):
+        return orc.fp8_experts(hidden[tokens], ref_ids[tokens], ref_w[tokens], *lazy)
+
+    check_sampled(cfg, hidden, ref_ids, ref_w, out, ws.route_rows(), one_expert, whole_token, max_experts=max_experts)
+    return counts
+
+
+def test_largest_batch_the_ops_take():
+    """65 536 tokens (the contracts' upper bound) at Qwen3 widths: 524 288 routes through the three-pass sort (512
+    chunks), ids, counts and the sorted table bit for bit, outputs sampled by place in the runs."""
+    cfg = wl.CONFIGS["qwen3"]
+    hidden, logits, bias = wl.router_inputs(cfg, 65536, seed=71)
+    counts = _layer_against_oracle(cfg, hidden, logits, bias, seed=72, max_experts=4)
+    assert int(counts.sum()) == 65536 * cfg.topk
+
+
+def test_every_token_on_the_same_experts():
+    """Total imbalance: logits that send all 3000 tokens to the same eight experts (3000 rows each, 24 blocks) and
+    leave 120 experts empty; and the mirror case, one expert with a single row among busy ones."""
+    cfg = wl.CONFIGS["qwen3"]
+    n_tokens = 3000
+    hidden, logits, bias = wl.router_inputs(cfg, n_tokens, seed=73)
+    logits = (logits.float() * 0.1)
+    logits[:, [3, 17, 31, 45, 59, 73, 87, 101]] += 20.0
+    logits[5, 120] += 40.0  # one token also picks expert 120: a run of one row
+    logits = logits.to(torch.bfloat16)
+    counts = _layer_against_oracle(cfg, hidden, logits, bias, seed=74, max_experts=6)
+    assert int((counts > 0).sum()) == 9 and int(counts[120]) == 1 and int(counts.max()) == n_tokens
+
+
+def test_a_thousand_experts():
+    """1024 routed experts (the contracts' upper bound), top-8 softmax, 2000 tokens: most experts get 10-20 rows."""
+    cfg = wl.MoEConfig("wide", hidden=512, inter=256, n_routed=1024, topk=8)
+    hidden, logits, bias = wl.router_inputs(cfg, 2000, seed=75)
+    counts = _layer_against_oracle(cfg, hidden, logits, bias, seed=76, max_experts=4)
+    assert int((counts > 0).sum()) > 1000
