@@ -591,6 +591,39 @@ def bench_published(device) -> dict:
             "rows": rows}
 
 
+def bench_emulated_ep(args, cfg, device) -> dict:
+    """Expert parallelism with ``--emulate-ep`` ranks emulated in ONE process on one GPU (phase by phase, the
+    exchanges as device copies): the dispatch and combine kernels at the benchmark's sizes where a profiler can
+    see them (a multi-rank command is never run under one).  Times the whole emulated step; not a bench value."""
+    from aklr_b200.ep import ExpertParallelMoE, run_in_process
+
+    world, T = args.emulate_ep, args.tokens
+    routing = routing_of(cfg)
+    w1, s1, w2, s2 = wl.expert_weights(cfg, SEED, device)
+    bias = wl.router_inputs(cfg, 1, SEED + 1, device)[2]
+    n_local = cfg.n_routed // world
+    layers, inputs = [], []
+    for r in range(world):
+        mine = list(range(r * n_local, (r + 1) * n_local)) + list(range(cfg.n_routed, cfg.n_experts))
+        layers.append(ExpertParallelMoE(routing, w1[mine].contiguous(), s1[mine].contiguous(), w2[mine].contiguous(),
+                                        s2[mine].contiguous(), r, world))
+        hidden, logits, _ = wl.router_inputs(cfg, T, SEED + 10 + r, device)
+        inputs.append((hidden, logits, bias))
+    del w1, s1, w2, s2
+    torch.cuda.empty_cache()
+    for _ in range(args.warmup):
+        run_in_process(layers, inputs)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        run_in_process(layers, inputs)
+    stop.record()
+    torch.cuda.synchronize()
+    return {"emulated_ranks": world, "tokens_per_rank": T, "ms_per_emulated_step_all_ranks": start.elapsed_time(stop) / args.steps,
+            "note": "all ranks' phases one after the other on one GPU: for profiler captures of the dispatch / combine kernels"}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -608,6 +641,7 @@ def main() -> None:
     ap.add_argument("--format", default="fp8", choices=["fp8", "mxfp4"], help="mxfp4: only the MXFP4 record, as the line's value")
     ap.add_argument("--model", default="deepseek_v3", choices=["deepseek_v3", "mixtral", "qwen3"],
                     help="widths of the headline leg (profiling captures of the other configurations; with --headline-only)")
+    ap.add_argument("--emulate-ep", type=int, default=0, help="this many expert-parallel ranks emulated in one process on one GPU (profiling captures)")
     ap.add_argument("--tiled-weights", action="store_true", help="expert weights in the tile-contiguous layout (aklr_b200.layouts)")
     ap.add_argument("--published", action="store_true", help="only the workloads the reference records timings for, one JSON object")
     args = ap.parse_args()
@@ -634,6 +668,9 @@ def main() -> None:
     args.cpu_affinity = bind_near_gpu(local_rank)
     if args.published:
         print(json.dumps(bench_published(device)))
+        return
+    if args.emulate_ep:
+        print(json.dumps(bench_emulated_ep(args, cfg, device)))
         return
     saved_stdout = None
     if world > 1:
