@@ -15,8 +15,8 @@
 namespace aklr {
 
 __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   const int vec_per_row = p.hidden >> 3;  // 8 bf16 per 16-byte vector
   const int64_t total = static_cast<int64_t>(p.n_tokens) * vec_per_row;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;

@@ -104,7 +104,6 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  griddep_launch();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -127,7 +126,34 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr;
-  griddep_wait();  // everything below reads what earlier kernels of the call wrote
+  // The weight boxes of this CTA's first tile go on their way BEFORE the wait: weights are not written by any kernel,
+  // and the block table that says which expert's they are comes from the sort, which ran before the kernel before
+  // this one -- every kernel of the library signals its dependents only after its own wait, so whatever preceded
+  // the previous kernel is complete when this one starts.  The activation boxes of those stages follow the wait.
+  int early = 0;  // K-blocks of the first tile whose weight loads are already in flight (producer thread only)
+  if (warp == 0 && lane == 0) {
+    int nb0 = *p.num_blocks;
+    if (nb0 > p.max_blocks) nb0 = p.max_blocks;
+    const int tiles_per_block0 = p.out_dim >> 7;
+    if (static_cast<int>(blockIdx.x) < nb0 * tiles_per_block0) {
+      const int b = blockIdx.x / tiles_per_block0, j = blockIdx.x - b * tiles_per_block0;
+      const int w_row = p.block_expert[b] * p.rows_per_expert + j * 128;
+      early = KB < S ? KB : S;
+      for (int kb = 0; kb < early; ++kb) {
+        uint8_t* st = smem + kb * L.stage_bytes;
+        mbar_expect_tx(&full[kb], L.stage_bytes);  // the activation box's bytes too: it comes after the wait
+        int wx, wy;
+        weight_box(p.w_tiled != 0, KB, w_row, kb, &wx, &wy);
+        tma_load_2d(st, &p.map_w, &full[kb], wx, wy);
+        if (GATE_UP) {
+          weight_box(p.w_tiled != 0, KB, w_row + p.out_dim, kb, &wx, &wy);
+          tma_load_2d(st + kWTileBytes, &p.map_w, &full[kb], wx, wy);
+        }
+      }
+    }
+  }
+  griddep_wait();    // everything below reads what earlier kernels of the call wrote
+  griddep_launch();  // after the wait: a dependent that starts knows every kernel before this one is complete
   int nb = *p.num_blocks;
   if (nb > p.max_blocks) nb = p.max_blocks;
   const int tiles_per_block = p.out_dim >> 7;
@@ -145,17 +171,19 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
         const int e = p.block_expert[b];
         const int w_row = e * p.rows_per_expert + j * 128;
         for (int kb = 0; kb < KB; ++kb, ++it) {
-          bool got;
-          got = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1);
-          if (!got) { ok = false; break; }
           uint8_t* st = smem + s * L.stage_bytes;
-          mbar_expect_tx(&full[s], L.stage_bytes);
-          int wx, wy;
-          weight_box(p.w_tiled != 0, KB, w_row, kb, &wx, &wy);
-          tma_load_2d(st, &p.map_w, &full[s], wx, wy);
-          if (GATE_UP) {
-            weight_box(p.w_tiled != 0, KB, w_row + p.out_dim, kb, &wx, &wy);
-            tma_load_2d(st + kWTileBytes, &p.map_w, &full[s], wx, wy);
+          if (static_cast<int>(it) >= early) {  // else: stage free from the start, bytes announced and weights under way
+            bool got;
+            got = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1);
+            if (!got) { ok = false; break; }
+            mbar_expect_tx(&full[s], L.stage_bytes);
+            int wx, wy;
+            weight_box(p.w_tiled != 0, KB, w_row, kb, &wx, &wy);
+            tma_load_2d(st, &p.map_w, &full[s], wx, wy);
+            if (GATE_UP) {
+              weight_box(p.w_tiled != 0, KB, w_row + p.out_dim, kb, &wx, &wy);
+              tma_load_2d(st + kWTileBytes, &p.map_w, &full[s], wx, wy);
+            }
           }
           tma_load_2d(st + (GATE_UP ? 2 : 1) * kWTileBytes, &p.map_x, &full[s], kb * 128, b * BM);
           if (++s == S) { s = 0; ph ^= 1; }
@@ -400,11 +428,11 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
 }
 
 bool pdl_enabled() {
-  // Opt-in (AKLR_PDL=1): measured on B200 it changes nothing for T >= 16 and costs 8 us at T = 1
-  // under CUDA-graph replay, where launch gaps are already small.
+  // On unless AKLR_PDL=0: a kernel's set-up, and the weight-major GEMM's first weight loads, overlap the tail of the
+  // kernel before it (measured on B200 under CUDA-graph replay: one token 91.7 -> see the decode sweep).
   static const bool on = [] {
     const char* v = getenv("AKLR_PDL");
-    return v && v[0] == '1';
+    return !(v && v[0] == '0');
   }();
   return on;
 }

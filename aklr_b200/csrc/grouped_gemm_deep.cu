@@ -118,7 +118,6 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_deep_kernel(const __
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int worker = static_cast<int>(blockIdx.x), n_workers = static_cast<int>(gridDim.x);
-  griddep_launch();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -140,6 +139,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_deep_kernel(const __
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr;
   griddep_wait();  // everything below reads what earlier kernels of the call wrote
+  griddep_launch();  // after the wait: a dependent that starts knows every kernel before this one is complete
   int nb = p.num_blocks[0];
   if (nb > p.max_blocks) nb = p.max_blocks;
   const int tiles_per_block = p.out_dim >> 7;  // units of 128 channels

@@ -182,7 +182,6 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  griddep_launch();
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(&full[s], 1);
@@ -206,6 +205,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr;
   griddep_wait();  // everything below reads what earlier kernels of the call wrote
+  griddep_launch();  // after the wait: a dependent that starts knows every kernel before this one is complete
   int nb = *p.num_blocks;
   if (nb > p.max_blocks) nb = p.max_blocks;
   const int tiles_per_block = GATE_UP ? (p.out_dim >> 7) : (p.out_dim >> 8);
@@ -531,8 +531,8 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
 // Four lanes x 8 values per 1 x 32 group: rows
 // gathered through the sorted route table, e4m3 codes row-major, scale bytes in tcgen05.cp order.
 __global__ void __launch_bounds__(256) gather_quant_mxfp8_kernel(MxQuantParams p) {
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   const int groups_per_row = p.hidden >> 5;
   const int n_rows = p.num_rows ? min(*p.num_rows, p.n_rows) : p.n_rows;
   const int64_t total = static_cast<int64_t>(n_rows) * groups_per_row;
@@ -616,8 +616,8 @@ __global__ void __launch_bounds__(256) gather_quant_mxfp8_kernel(MxQuantParams p
 constexpr int kGatherRows = 4;
 __global__ void __launch_bounds__(256) gather_rows_mxfp8_kernel(MxQuantParams p) {
   __shared__ int src_s[kGatherRows];
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   const int vec_per_row = p.hidden >> 4;
   const int KB = p.hidden >> 7;
   const size_t q_pitch = p.q_in_stride ? p.q_in_stride : p.hidden;

@@ -131,7 +131,6 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
   // tiles are dealt to CTAs (or CTA pairs) round-robin
   const int worker = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
   const int n_workers = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
-  griddep_launch();
   // unit u -> this CTA's token block and whether it is a real one
   auto block_of = [&](int u, bool* live) -> int {
     if (!PAIR) { *live = true; return u; }
@@ -167,6 +166,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr;
   griddep_wait();  // everything below reads what earlier kernels of the call wrote
+  griddep_launch();  // after the wait: a dependent that starts knows every kernel before this one is complete
   int nb = PAIR ? p.num_blocks[2] : p.num_blocks[0];  // units: runs of <= 2 blocks, or blocks
   if (nb > p.max_blocks) nb = p.max_blocks;
   // gate_up: one tile per 128 intermediate channels (128 gate + 128 up rows); down: per 256 channels

@@ -19,8 +19,8 @@
 namespace aklr {
 
 __global__ void __launch_bounds__(256) gather_quant_fp8_kernel(GatherQuantParams p) {
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   gather_quant_fp8_groups(p, (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4,
                           (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 4);
 }
@@ -32,8 +32,8 @@ __global__ void __launch_bounds__(256) gather_quant_fp8_kernel(GatherQuantParams
 constexpr int kGatherMaxVecPerLane = 16;  // hidden <= 8192 in one pass; wider rows take further passes
 
 __global__ void __launch_bounds__(256) gather_rows_fp8_kernel(GatherQuantParams p) {
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   const int lane = threadIdx.x & 31;
   const int vec_per_row = p.hidden >> 4;
   const int groups_per_row = p.hidden >> 7;

@@ -44,8 +44,8 @@ __global__ void __launch_bounds__(256) route_kernel(RouteParams p) {
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const int token = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   if (token >= p.n_tokens) return;
   const int E = p.n_routed;
   const int ktot = p.topk + p.n_shared;
@@ -318,8 +318,8 @@ __device__ void route_by_counting(const RouteParams& p, int token, int e, int te
 
 __global__ void __launch_bounds__(1024) route_count_kernel(RouteParams p) {
   __shared__ RouteShared sh;
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   float s;
   uint32_t image;
   route_load(p, blockIdx.x, threadIdx.x, s, image);
@@ -381,8 +381,8 @@ __device__ __forceinline__ int local_expert(const AlignParams& p, int route) {
 // Pass 1: histogram of each 1024-route chunk -> chunk_hist[chunk][expert]
 __global__ void __launch_bounds__(kSortChunk) align_count_kernel(AlignParams p) {
   extern __shared__ int hist[];
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   for (int e = threadIdx.x; e < p.n_experts; e += blockDim.x) hist[e] = 0;
   __syncthreads();
   const int route = blockIdx.x * kSortChunk + threadIdx.x;
@@ -502,8 +502,8 @@ __device__ void place_chunk(const AlignParams& p, int route, int* cursor) {
 // Pass 2 (one CTA): per-expert totals, per-chunk offsets, block table.
 __global__ void __launch_bounds__(1024) align_scan_kernel(AlignParams p, int n_chunks) {
   extern __shared__ int sm[];
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   int* total = sm;                  // [n_experts]
   int* base = sm + p.n_experts;     // [n_experts]
   int* scratch = base + p.n_experts;  // [blockDim]
@@ -544,8 +544,8 @@ __global__ void __launch_bounds__(1024) align_scan_kernel(AlignParams p, int n_c
 // Pass 3: scatter each chunk
 __global__ void __launch_bounds__(kSortChunk) align_scatter_kernel(AlignParams p) {
   extern __shared__ int cursor[];
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   for (int e = threadIdx.x; e < p.n_experts; e += blockDim.x)
     cursor[e] = p.chunk_hist[static_cast<size_t>(blockIdx.x) * p.n_experts + e];
   __syncthreads();
@@ -574,8 +574,8 @@ __device__ void align_small_body(const AlignParams& p, int* sm) {
 
 __global__ void __launch_bounds__(kSortChunk) align_small_kernel(AlignParams p) {
   extern __shared__ int sm[];
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   align_small_body(p, sm);
 }
 
@@ -589,8 +589,8 @@ __global__ void __launch_bounds__(kSortChunk) decode_prologue_kernel(RouteParams
   extern __shared__ int sm[];
   using TeamShared = RouteSharedT<kDecodePrologueExperts, kDecodePrologueExperts>;
   __shared__ TeamShared sh[kPrologueTeams];
-  griddep_launch();
   griddep_wait();
+  griddep_launch();
   // Teams of 256 threads route tokens team, team + 4, ... side by side, each on its own named
   // barrier.  A team's loads for both of its tokens are issued before it counts (one memory round
   // trip), and the counting is a rolled loop: a decode call streams hundreds of MB through L2 between
