@@ -40,7 +40,10 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // Kernels of a call are launched with programmatic stream serialisation: a kernel's CTAs may be
 // scheduled while the previous kernel is still finishing, do their local set-up (barriers, TMEM,
 // descriptor prefetch) and then wait here until everything before them in the stream is complete
-// and visible.  Nothing produced by an earlier kernel may be read before griddep_wait().
+// and visible.  Nothing produced by the PREVIOUS kernel may be read before griddep_wait().  Every kernel
+// calls griddep_launch() only after its own griddep_wait(), so a kernel that has started also knows that
+// whatever ran before its predecessor is complete: the weight-major GEMM reads the sort's block table
+// (two kernels back) and starts its weight loads before it waits.
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

@@ -254,8 +254,8 @@ int32_t* host_visible_status(cudaStream_t stream);
 // Opt a kernel in to the full 227 KB of dynamic shared memory, once per (kernel, device).
 int ensure_max_dynamic_smem(const void* kernel);
 
-// Launch, with programmatic stream serialisation (see griddep_wait in common.cuh) when AKLR_PDL=1 is
-// in the environment (off by default: no measured gain).  ``cluster`` > 1 adds a cluster dimension.
+// Launch, with programmatic stream serialisation (see griddep_wait in common.cuh) unless AKLR_PDL=0 is in
+// the environment.  ``cluster`` > 1 adds a cluster dimension.
 bool pdl_enabled();
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
