@@ -451,8 +451,10 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   g2.block_m = l.block_m;
   g2.max_blocks = l.max_blocks;
   g2.pair_table = pairs ? pair_table : nullptr;
+  const bool wide2 = !tm2 && !deep && grouped_gemm_down_is_wide(l.block_m, c.hidden, l.max_blocks, sms);
+  g2.wide = wide2 ? 1 : 0;
   g2.stages = deep ? grouped_gemm_deep_pick_stages(false)
-              : tm2 ? grouped_gemm_prefill_pick_stages(false, pairs) : grouped_gemm_pick_stages(false, l.block_m, c.inter);
+              : tm2 ? grouped_gemm_prefill_pick_stages(false, pairs) : grouped_gemm_pick_stages(false, l.block_m, c.inter, wide2);
   if (g2.stages < 2) return fail(AKLR_ERR_UNSUPPORTED_SHAPE, "inter=%d needs more shared memory than one SM has", c.inter);
   rc = deep ? launch_grouped_gemm_deep(g2, false, sms, stream)
        : tm2 ? launch_grouped_gemm_prefill(g2, false, pairs, sms, stream) : launch_grouped_gemm_down(g2, sms, stream);

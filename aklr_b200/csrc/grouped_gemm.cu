@@ -38,11 +38,12 @@ struct GemmSmemLayout {
   int off_misc, off_rid, off_wmax, off_wscale, off_bars;
 };
 
-__host__ __device__ inline GemmSmemLayout gemm_layout(bool gate_up, int block_m, int k, int stages) {
+__host__ __device__ inline GemmSmemLayout gemm_layout(bool gate_up, int block_m, int k, int stages, bool wide = false) {
   GemmSmemLayout l;
   const int kb = k / 128;
-  l.stage_bytes = (gate_up ? 2 : 1) * kWTileBytes + block_m * 128;
-  const int scale_bytes = (gate_up ? 2 : 1) * kb * block_m * 4;  // combined scale table(s)
+  const int w_tiles = (gate_up || wide) ? 2 : 1;  // weight tiles per stage: gate + up, or two neighbouring down tiles
+  l.stage_bytes = w_tiles * kWTileBytes + block_m * 128;
+  const int scale_bytes = w_tiles * kb * block_m * 4;  // combined scale table(s)
   const int out_bytes = block_m * 128 * (gate_up ? 1 : 2);
   l.misc_bytes = ((scale_bytes > out_bytes ? scale_bytes : out_bytes) + 127) & ~127;
   l.off_misc = stages * l.stage_bytes;
@@ -54,13 +55,13 @@ __host__ __device__ inline GemmSmemLayout gemm_layout(bool gate_up, int block_m,
   return l;
 }
 
-size_t grouped_gemm_smem_bytes(bool gate_up, int block_m, int k, int stages) {
-  return static_cast<size_t>(gemm_layout(gate_up, block_m, k, stages).total_bytes) + 1024;  // alignment slack
+size_t grouped_gemm_smem_bytes(bool gate_up, int block_m, int k, int stages, bool wide) {
+  return static_cast<size_t>(gemm_layout(gate_up, block_m, k, stages, wide).total_bytes) + 1024;  // alignment slack
 }
 
-int grouped_gemm_pick_stages(bool gate_up, int block_m, int k) {
+int grouped_gemm_pick_stages(bool gate_up, int block_m, int k, bool wide) {
   for (int s = 8; s >= 2; --s)
-    if (grouped_gemm_smem_bytes(gate_up, block_m, k, s) <= 227 * 1024) return s;
+    if (grouped_gemm_smem_bytes(gate_up, block_m, k, s, wide) <= 227 * 1024) return s;
   return 0;
 }
 
@@ -78,12 +79,18 @@ __device__ __forceinline__ bool epi_bar_any(int flag) {
   return any != 0;
 }
 
-template <int BM, bool GATE_UP>
+// WIDE (down projection only): a tile is 256 output channels, two weight tiles per stage sharing the token tile as
+// gate and up do.  A decode block's K-block then moves 32 KB of weights instead of 16 KB per hand-off, which is what
+// lets the down projection stream at the rate of gate_up.
+template <int BM, bool GATE_UP, bool WIDE = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
+  static_assert(!(GATE_UP && WIDE), "wide tiles are for the down projection");
+  constexpr bool TWO = GATE_UP || WIDE;             // two weight tiles per stage and two accumulator tiles
+  constexpr int kTileShift = WIDE ? 8 : 7;          // output channels per tile: 256 or 128
   constexpr int NH = BM / 2;                        // columns per epilogue warp
   constexpr int CH = (NH >= 16 && !(GATE_UP && BM >= 64)) ? 16 : 8;  // columns per tcgen05.ld (register budget: 168 per thread)
-  constexpr int BUF_COLS = (GATE_UP ? 2 : 1) * BM;  // TMEM columns of one partial buffer
+  constexpr int BUF_COLS = (TWO ? 2 : 1) * BM;      // TMEM columns of one partial buffer
   constexpr int TMEM_COLS = 2 * BUF_COLS < 32 ? 32 : 2 * BUF_COLS;
   constexpr uint32_t IDESC = umma_idesc_e4m3(BM);
 
@@ -91,7 +98,7 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int KB = p.k >> 7;
   const int S = p.stages;
-  const GemmSmemLayout L = gemm_layout(GATE_UP, BM, p.k, S);
+  const GemmSmemLayout L = gemm_layout(GATE_UP, BM, p.k, S, WIDE);
   float* ftab = reinterpret_cast<float*>(smem + L.off_misc);  // [tiles][KB][BM] combined scales ...
   uint8_t* out_tile = smem + L.off_misc;                      // ... aliased by the output tile
   int* rid_s = reinterpret_cast<int*>(smem + L.off_rid);
@@ -134,10 +141,10 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
   if (warp == 0 && lane == 0) {
     int nb0 = *p.num_blocks;
     if (nb0 > p.max_blocks) nb0 = p.max_blocks;
-    const int tiles_per_block0 = p.out_dim >> 7;
+    const int tiles_per_block0 = p.out_dim >> kTileShift;
     if (static_cast<int>(blockIdx.x) < nb0 * tiles_per_block0) {
       const int b = blockIdx.x / tiles_per_block0, j = blockIdx.x - b * tiles_per_block0;
-      const int w_row = p.block_expert[b] * p.rows_per_expert + j * 128;
+      const int w_row = p.block_expert[b] * p.rows_per_expert + (j << kTileShift);
       early = KB < S ? KB : S;
       for (int kb = 0; kb < early; ++kb) {
         uint8_t* st = smem + kb * L.stage_bytes;
@@ -145,8 +152,8 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
         int wx, wy;
         weight_box(p.w_tiled != 0, KB, w_row, kb, &wx, &wy);
         tma_load_2d(st, &p.map_w, &full[kb], wx, wy);
-        if (GATE_UP) {
-          weight_box(p.w_tiled != 0, KB, w_row + p.out_dim, kb, &wx, &wy);
+        if (TWO) {
+          weight_box(p.w_tiled != 0, KB, w_row + (GATE_UP ? p.out_dim : 128), kb, &wx, &wy);
           tma_load_2d(st + kWTileBytes, &p.map_w, &full[kb], wx, wy);
         }
       }
@@ -156,7 +163,7 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
   griddep_launch();  // after the wait: a dependent that starts knows every kernel before this one is complete
   int nb = *p.num_blocks;
   if (nb > p.max_blocks) nb = p.max_blocks;
-  const int tiles_per_block = p.out_dim >> 7;
+  const int tiles_per_block = p.out_dim >> kTileShift;
   const int total_tiles = nb * tiles_per_block;
 
   if (warp == 0) {
@@ -169,7 +176,7 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const int b = t / tiles_per_block, j = t - b * tiles_per_block;
         const int e = p.block_expert[b];
-        const int w_row = e * p.rows_per_expert + j * 128;
+        const int w_row = e * p.rows_per_expert + (j << kTileShift);
         for (int kb = 0; kb < KB; ++kb, ++it) {
           uint8_t* st = smem + s * L.stage_bytes;
           if (static_cast<int>(it) >= early) {  // else: stage free from the start, bytes announced and weights under way
@@ -180,12 +187,12 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
             int wx, wy;
             weight_box(p.w_tiled != 0, KB, w_row, kb, &wx, &wy);
             tma_load_2d(st, &p.map_w, &full[s], wx, wy);
-            if (GATE_UP) {
-              weight_box(p.w_tiled != 0, KB, w_row + p.out_dim, kb, &wx, &wy);
+            if (TWO) {
+              weight_box(p.w_tiled != 0, KB, w_row + (GATE_UP ? p.out_dim : 128), kb, &wx, &wy);
               tma_load_2d(st + kWTileBytes, &p.map_w, &full[s], wx, wy);
             }
           }
-          tma_load_2d(st + (GATE_UP ? 2 : 1) * kWTileBytes, &p.map_x, &full[s], kb * 128, b * BM);
+          tma_load_2d(st + (TWO ? 2 : 1) * kWTileBytes, &p.map_x, &full[s], kb * 128, b * BM);
           if (++s == S) { s = 0; ph ^= 1; }
         }
       }
@@ -211,12 +218,12 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
           if (!got) { ok = false; break; }
           tc_fence_after_sync();
           const uint64_t da1 = da0 + (kWTileBytes >> 4);
-          const uint64_t db = da0 + (((GATE_UP ? 2 : 1) * kWTileBytes) >> 4);
+          const uint64_t db = da0 + (((TWO ? 2 : 1) * kWTileBytes) >> 4);
           const uint32_t d = tmem_base + buf * BUF_COLS;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {  // 32 K bytes per MMA: the descriptor start moves 32 B
             umma_f8f6f4(d, da0 + 2 * k, db + 2 * k, IDESC, k > 0);
-            if (GATE_UP) umma_f8f6f4(d + BM, da1 + 2 * k, db + 2 * k, IDESC, k > 0);
+            if (TWO) umma_f8f6f4(d + BM, da1 + 2 * k, db + 2 * k, IDESC, k > 0);
           }
           tc_commit(&empty[s]);
           da0 += stage_step;
@@ -235,7 +242,7 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
     const int chan = quarter * 32 + lane;    // output channel inside the tile = TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const int IB = p.out_dim >> 7;           // gate_up: 128-blocks of the intermediate size
-    constexpr int TILES = GATE_UP ? 2 : 1;
+    constexpr int TILES = TWO ? 2 : 1;
     constexpr int CPT = NH / CH;             // chunks per accumulator tile
     constexpr int NC = TILES * CPT;          // chunks per K-block
     uint32_t it = 0;
@@ -260,7 +267,9 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
       // during the previous tile of this CTA (``pre_*``): a tile of a short reduction (6..16 K-blocks)
       // would otherwise spend a third of its time waiting for these dependent global loads.
       {
-        const float* ws0 = p.w_scale + (static_cast<size_t>(e) * (p.rows_per_expert >> 7) + j) * KB;
+        // weight block scales of the tile's first 128 channels; the second set is gate_up's up rows, or the next 128 channels
+        const float* ws0 = p.w_scale + (static_cast<size_t>(e) * (p.rows_per_expert >> 7) + (WIDE ? 2 * j : j)) * KB;
+        const size_t second = static_cast<size_t>(GATE_UP ? IB : 1) * KB;
         const float* xs = p.x_scale + static_cast<size_t>(b) * KB * BM;  // [kb][n] of this block
         for (int base = et; base < BM * KB; base += kEpiThreads * kPreBatch) {
           float s[kPreBatch], w0[kPreBatch], w1[kPreBatch];
@@ -275,7 +284,7 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
               const int kb = in ? i / BM : 0;
               s[u] = in ? __ldg(xs + i) : 0.0f;
               w0[u] = __ldg(ws0 + kb);
-              w1[u] = GATE_UP ? __ldg(ws0 + static_cast<size_t>(IB) * KB + kb) : 0.0f;
+              w1[u] = TWO ? __ldg(ws0 + second + kb) : 0.0f;
             }
           }
 #pragma unroll
@@ -283,7 +292,7 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
             const int i = base + u * kEpiThreads;
             if (i < BM * KB) {
               ftab[i] = s[u] * w0[u];
-              if (GATE_UP) ftab[BM * KB + i] = s[u] * w1[u];
+              if (TWO) ftab[BM * KB + i] = s[u] * w1[u];
             }
           }
         }
@@ -300,7 +309,8 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
         if (have_pre) {
           const int bn = tn / tiles_per_block, jn = tn - bn * tiles_per_block;
           const int en = e_ahead;
-          const float* ws0 = p.w_scale + (static_cast<size_t>(en) * (p.rows_per_expert >> 7) + jn) * KB;
+          const float* ws0 = p.w_scale + (static_cast<size_t>(en) * (p.rows_per_expert >> 7) + (WIDE ? 2 * jn : jn)) * KB;
+          const size_t second = static_cast<size_t>(GATE_UP ? IB : 1) * KB;
           const float* xs = p.x_scale + static_cast<size_t>(bn) * KB * BM;
 #pragma unroll
           for (int u = 0; u < kPreBatch; ++u) {
@@ -309,7 +319,7 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
             const int kb = in ? i / BM : 0;
             pre_s[u] = in ? __ldg(xs + i) : 0.0f;
             pre_w0[u] = __ldg(ws0 + kb);
-            pre_w1[u] = GATE_UP ? __ldg(ws0 + static_cast<size_t>(IB) * KB + kb) : 0.0f;
+            pre_w1[u] = TWO ? __ldg(ws0 + second + kb) : 0.0f;
           }
           pre_rid = et < BM ? p.sorted_ids[bn * BM + et] : -1;
         }
@@ -397,18 +407,22 @@ grouped_gemm_kernel(const __grid_constant__ GroupedGemmParams p) {
       } else {
         __nv_bfloat16* out16 = reinterpret_cast<__nv_bfloat16*>(out_tile);
 #pragma unroll
-        for (int i = 0; i < NH; ++i) {
-          const int n = half * NH + i;
-          out16[n * 128 + chan] = __float2bfloat16_rn(acc[0][i] * colscale[n]);
-        }
-        epi_bar_sync();
-        for (int i = et; i < BM * 16; i += kEpiThreads) {  // 16 bytes per thread, 16 per row
-          const int n = i >> 4, seg = i & 15;
-          const int rid = rid_s[n];
-          if (rid >= 0 && !bad)
-            *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out_rows) +
-                                      (static_cast<size_t>(rid) * p.out_dim + j * 128) * 2 + seg * 16) =
-                *reinterpret_cast<const uint4*>(out_tile + n * 256 + seg * 16);
+        for (int a = 0; a < TILES; ++a) {  // one pass per 128 channels through the same staging tile
+          if (a > 0) epi_bar_sync();       // the pass before has been written out
+#pragma unroll
+          for (int i = 0; i < NH; ++i) {
+            const int n = half * NH + i;
+            out16[n * 128 + chan] = __float2bfloat16_rn(acc[a][i] * colscale[n]);
+          }
+          epi_bar_sync();
+          for (int i = et; i < BM * 16; i += kEpiThreads) {  // 16 bytes per thread, 16 per row
+            const int n = i >> 4, seg = i & 15;
+            const int rid = rid_s[n];
+            if (rid >= 0 && !bad)
+              *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out_rows) +
+                                        (static_cast<size_t>(rid) * p.out_dim + (j << kTileShift) + a * 128) * 2 + seg * 16) =
+                  *reinterpret_cast<const uint4*>(out_tile + n * 256 + seg * 16);
+          }
         }
       }
     }
@@ -452,18 +466,32 @@ int ensure_max_dynamic_smem(const void* kernel) {
   return AKLR_OK;
 }
 
+// The down projection of decode blocks (16 or 32 tokens) on 256-channel tiles: with 128-channel tiles a K-block hands
+// over 16 KB of weights, and the hand-offs, not HBM, set its pace (4.2 TB/s at one token where gate_up, whose
+// K-blocks carry 32 KB, reaches 5.8).
+// Not when so few blocks are in play that 256-channel tiles would leave SMs without one (two experts of Mixtral's
+// width at one token: 32 wide tiles for 148 SMs).
+bool grouped_gemm_down_is_wide(int block_m, int out_dim, int max_blocks, int sm_count) {
+  return (block_m == 16 || block_m == 32) && out_dim % 256 == 0 && static_cast<long long>(max_blocks) * (out_dim / 256) >= sm_count;
+}
+
 template <bool GATE_UP>
 static int launch_grouped(const GroupedGemmParams& p, int sm_count, cudaStream_t stream) {
   if (p.k % 128 != 0 || p.out_dim % 128 != 0 || p.max_blocks < 1) return AKLR_ERR_UNSUPPORTED_SHAPE;
   if (p.stages < 2) return AKLR_ERR_UNSUPPORTED_SHAPE;
-  const size_t smem = grouped_gemm_smem_bytes(GATE_UP, p.block_m, p.k, p.stages);
+  const bool wide = !GATE_UP && p.wide != 0;
+  if (wide && !((p.block_m == 16 || p.block_m == 32) && p.out_dim % 256 == 0)) return AKLR_ERR_UNSUPPORTED_SHAPE;
+  const size_t smem = grouped_gemm_smem_bytes(GATE_UP, p.block_m, p.k, p.stages, wide);
   if (smem > 227 * 1024) return AKLR_ERR_UNSUPPORTED_SHAPE;
-  const long long tiles = static_cast<long long>(p.max_blocks) * (p.out_dim / 128);
+  const long long tiles = static_cast<long long>(p.max_blocks) * (p.out_dim / (wide ? 256 : 128));
   const int grid = static_cast<int>(tiles < sm_count ? tiles : sm_count);
   auto run = [&](auto kernel) {
     if (ensure_max_dynamic_smem(reinterpret_cast<const void*>(kernel)) != AKLR_OK) return AKLR_ERR_CUDA;
     return launch_kernel(kernel, dim3(grid), dim3(kGemmThreads), smem, stream, 1, p) == cudaSuccess ? AKLR_OK : AKLR_ERR_CUDA;
   };
+  if constexpr (!GATE_UP) {
+    if (wide) return p.block_m == 16 ? run(grouped_gemm_kernel<16, false, true>) : run(grouped_gemm_kernel<32, false, true>);
+  }
   switch (p.block_m) {
     case 16: return run(grouped_gemm_kernel<16, GATE_UP>);
     case 32: return run(grouped_gemm_kernel<32, GATE_UP>);

@@ -100,6 +100,7 @@ struct GroupedGemmParams {
   int max_blocks;              // upper bound used to size the tile loop
   int stages;
   int w_tiled;                 // weights in the tile-contiguous layout: [expert][row/128][k/128][128 rows][128 bytes]
+  int wide;                    // weight-major down projection on 256-channel tiles (grouped_gemm_down_is_wide)
 };
 int launch_grouped_gemm_gate_up(const GroupedGemmParams& p, int sm_count, cudaStream_t stream);
 int launch_grouped_gemm_down(const GroupedGemmParams& p, int sm_count, cudaStream_t stream);
@@ -119,8 +120,9 @@ int launch_grouped_gemm_deep(const GroupedGemmParams& p, bool gate_up, int sm_co
 // over [tiles * 128 rows, 128 bytes] and a tile's box starts at row tile_index * 128.
 int launch_exact_divide_selftest(const float* x, const float* scale, int64_t n, int32_t* mismatches, cudaStream_t stream);
 int launch_tile_weights_fp8(const void* src, void* dst, int64_t matrices, int rows, int cols, cudaStream_t stream);
-size_t grouped_gemm_smem_bytes(bool gate_up, int block_m, int k, int stages);
-int grouped_gemm_pick_stages(bool gate_up, int block_m, int k);
+size_t grouped_gemm_smem_bytes(bool gate_up, int block_m, int k, int stages, bool wide = false);
+int grouped_gemm_pick_stages(bool gate_up, int block_m, int k, bool wide = false);
+bool grouped_gemm_down_is_wide(int block_m, int out_dim, int max_blocks, int sm_count);
 
 // ---- MXFP4 weights / MXFP8 activations (grouped_gemm_mx.cu), always 128-token blocks ----------
 struct MxQuantParams {

@@ -114,6 +114,8 @@ def check_sampled(cfg, hidden, ref_ids, ref_w, out, route_rows, one_expert, whol
 FP8_CASES = [
     ("deepseek_v3", 16384),
     ("deepseek_v3", 4096),
+    ("deepseek_v3", 1),  # nine blocks: the down projection runs on 64-channel tiles
+    ("deepseek_v3", 2),
     ("mixtral", 4096),
     ("qwen3", 1),
     ("qwen3", 32),
