@@ -25,8 +25,9 @@
 // period is 1100-1450.  No piece explains it: the hand-offs of the MMA <-> fold cycle each arrive late (512
 // TMEM columns hold exactly two N=256 partials, and a ring stage is held until the MMAs that read it are
 // done).  What helped: one commit per K-block and a lean MMA-issue loop, scales prefetched from global
-// memory two K-blocks ahead instead of staged per tile, register hand-over (setmaxnreg), weight tiles
-// prefetched into L2 ahead of the ring.  What did not: per-half hand-offs (two N=128 MMA groups; 20%
+// memory two K-blocks ahead instead of staged per tile, register hand-over (setmaxnreg).  What did not: weight
+// tiles prefetched into L2 ahead of the ring (+1-3% at 4096 tokens, -18% at 1024 where every tile's weights
+// come from HBM), per-half hand-offs (two N=128 MMA groups; 20%
 // slower), 128 x 128 tiles with four partials in flight (grouped_gemm_deep.cu; 40% slower), two MMA-issuing
 // threads, one polling lane per warp, issuing the next K-block's first batch early, 16 epilogue warps,
 // larger or single-buffered load batches, CTA pairs (below).  Persistent CTAs, TMA SWIZZLE_128B ring,
@@ -55,7 +56,6 @@ constexpr int kABytes = kBM * 128;       // token tile of one K-block
 constexpr int kBBytes = kBN * 128;       // weight tile of one K-block
 __host__ __device__ constexpr int stage_bytes(bool pair) { return kABytes + (pair ? kBBytes / 2 : kBBytes); }  // a CTA of a pair holds half the weight rows
 constexpr int kBatch = 32;                // TMEM columns one epilogue thread loads per round (as 4 x 8)
-constexpr int kPrefetchAhead = 8;         // K-blocks between a weight tile's L2 prefetch and its load
 
 struct PrefillLayout {
   int off_out, off_rid, off_wmax, off_bars, total;
@@ -215,27 +215,6 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
               tma_load_2d(st + kABytes + kBBytes / 2, &p.map_w, &full[s], wx, wy);
             } else {
               tma_load_2d(st + kABytes, &p.map_w, &full[s], kb * 128, w_row);  // box of 256 rows
-            }
-            // The ring holds four K-blocks, less than the latency of a weight tile that comes from HBM:
-            // ask the L2 for the weights kPrefetchAhead K-blocks further on (this tile's, then the next one's).
-            int pk = kb + kPrefetchAhead, prow = w_row;
-            if (pk >= KB) {
-              pk -= KB;
-              const int tn = t + n_workers;
-              if (tn < total_tiles && pk < KB) {
-                const int un = tn / tiles_per_block, jn = tn - un * tiles_per_block;
-                prow = p.block_expert[un] * p.rows_per_expert + (GATE_UP ? jn * 128 : jn * 256);
-              } else {
-                pk = -1;
-              }
-            }
-            if (pk >= 0) {
-              weight_box(tiled, KB, prow, pk, &wx, &wy);
-              tma_prefetch_l2_2d(&p.map_w, wx, wy);
-              if (GATE_UP || tiled) {
-                weight_box(tiled, KB, prow + (GATE_UP ? p.out_dim : 128), pk, &wx, &wy);
-                tma_prefetch_l2_2d(&p.map_w, wx, wy);
-              }
             }
           }
           if (++s == S) { s = 0; ph ^= 1; }
