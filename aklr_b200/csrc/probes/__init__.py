@@ -5,12 +5,15 @@ against these numbers.
     python -m aklr_b200.csrc.probes            # builds the programs under build/probes and runs them
 
 * ``tma_ring``: persistent CTAs that only run the operand ring of the token-major kernel (48 KB x 4 stages, or
-  32 KB x 6), stages recycled the moment they fill: bytes per second from L2 / HBM into shared memory.
+  32 KB x 6), stages recycled the moment they fill: bytes per second from L2 / HBM into shared memory; the same
+  with the MXFP4 kernel's packed e2m1 weight tiles, which the TMA unpacks on the way.
 * ``mma_chain``: cycles per ``tcgen05.mma kind::f8f6f4`` (M 128, K 32) for N = 16 .. 256, with every MMA depending on
   the one before or rotating over 2 .. 8 accumulators.
 * ``mma_beside_tma``: the MMA stream of a K-block (two deep) alone, a TMA ring alone, and both at once.
 * ``mx_issue``: the MXFP4 kernel's issue stream alone: four block-scaled MMAs per K-block with 0 .. 4 ``tcgen05.cp`` of
   scale factors in front of them.
+* ``mma_data``: the same N = 256 MMA stream on constant and on random operands, in cycles and in nanoseconds: the SM
+  clock the part holds while its tensor pipes are busy depends on the data.
 
 Every wait in them is bounded; they allocate at most 4 GB and run for a few seconds.
 """
@@ -24,7 +27,7 @@ import sys
 HERE = pathlib.Path(__file__).resolve().parent
 ROOT = HERE.parents[2]
 OUT = ROOT / "build" / "probes"
-PROGRAMS = ("tma_ring", "mma_chain", "mma_beside_tma", "mx_issue")
+PROGRAMS = ("tma_ring", "mma_chain", "mma_beside_tma", "mx_issue", "mma_data")
 
 
 def build() -> list[pathlib.Path]:

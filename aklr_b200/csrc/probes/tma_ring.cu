@@ -1,6 +1,7 @@
 // L2 -> shared memory delivery ceiling for the grouped GEMM's load pattern: persistent CTAs that only
 // run the TMA ring (no MMA, no fold).  Modes: tile shape (48 KB x 4 stages | 32 KB x 6 stages), weights
-// L2-resident or streamed from HBM.
+// L2-resident or streamed from HBM; and the MXFP4 kernel's weight loads, packed e2m1 in global memory that the TMA
+// unpacks to one byte per element in shared memory (16U4_ALIGN16B).
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <cstdio>
@@ -32,7 +33,7 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
 
 struct Params {
   CUtensorMap map_w, map_x;
-  int K, rows_per_expert, n_experts, blocks_per_expert, n_tile, stages, tiles_per_block, total_tiles, load_a;
+  int K, rows_per_expert, n_experts, blocks_per_expert, n_tile, stages, tiles_per_block, total_tiles, load_a, fp4;
   int* err;
 };
 
@@ -59,7 +60,8 @@ __global__ void __launch_bounds__(64, 1) probe(const __grid_constant__ Params p)
       for (int kb = 0; kb < KB; ++kb) {
         if (!mbar_wait(&empty[s], ph ^ 1, p.err)) return;
         uint8_t* st = smem + s * stage_bytes;
-        mbar_expect_tx(&full[s], a_bytes + p.n_tile * 128);
+        // an unpacking load counts the packed bytes that cross from global memory
+        mbar_expect_tx(&full[s], a_bytes + (p.fp4 ? p.n_tile * 64 : p.n_tile * 128));
         if (p.load_a) tma_load_2d(st, &p.map_x, &full[s], kb * 128, b * 128);
         for (int r = 0; r < p.n_tile; r += 128) tma_load_2d(st + 16384 + r * 128, &p.map_w, &full[s], kb * 128, w_row + r);
         if (++s == p.stages) { s = 0; ph ^= 1; }
@@ -81,12 +83,12 @@ typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void
                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-static void make_map(EncodeFn enc, CUtensorMap* m, void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+static void make_map(EncodeFn enc, CUtensorMap* m, void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, bool fp4 = false) {
   const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {cols};
+  const cuuint64_t strides[1] = {fp4 ? cols / 2 : cols};
   const cuuint32_t box[2] = {128, box_rows};
   const cuuint32_t elem[2] = {1, 1};
-  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  CUresult r = enc(m, fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) { printf("encode failed %d\n", (int)r); exit(1); }
 }
@@ -104,7 +106,7 @@ int main() {
   CHECK(cudaMalloc(&err, 4)); CHECK(cudaMemset(err, 0, 4));
   cudaEvent_t e0, e1; cudaEventCreate(&e0); cudaEventCreate(&e1);
   CHECK(cudaFuncSetAttribute(probe, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-  struct Mode { const char* name; int n_tile, stages, n_experts, blocks_per_expert, load_a; };
+  struct Mode { const char* name; int n_tile, stages, n_experts, blocks_per_expert, load_a, fp4; };
   const Mode modes[] = {
       {"48KB x4, weights from HBM (128 experts x 5 blocks)", 256, 4, 128, 5, 1},
       {"48KB x4, weights L2-resident (2 experts)", 256, 4, 2, 5, 1},
@@ -112,13 +114,17 @@ int main() {
       {"32KB x6, weights L2-resident (2 experts)", 128, 6, 2, 5, 1},
       {"B only 32KB x6 (stage 48KB), weights L2-resident", 256, 4, 2, 5, 0},
       {"B only, weights from HBM", 256, 4, 128, 5, 0},
+      {"fp4 unpacked by the TMA: A 16KB + B 16KB packed -> 32KB, x4, from HBM", 256, 4, 128, 5, 1, 1},
+      {"fp4 unpacked by the TMA: A + B, x4, L2-resident (2 experts)", 256, 4, 2, 5, 1, 1},
+      {"fp4 unpacked by the TMA: B only, x4, from HBM", 256, 4, 128, 5, 0, 1},
+      {"fp4 unpacked by the TMA: B only, x4, L2-resident", 256, 4, 2, 5, 0, 1},
   };
   for (const Mode& m : modes) {
     Params p{};
-    make_map(enc, &p.map_w, w, (uint64_t)128 * rows_per_expert, K, 128);
+    make_map(enc, &p.map_w, w, (uint64_t)128 * rows_per_expert, K, 128, m.fp4 != 0);
     make_map(enc, &p.map_x, x, (uint64_t)blocks * 128, K, 128);
     p.K = K; p.rows_per_expert = rows_per_expert; p.n_experts = m.n_experts; p.blocks_per_expert = m.blocks_per_expert;
-    p.n_tile = m.n_tile; p.stages = m.stages; p.tiles_per_block = rows_per_expert / m.n_tile; p.load_a = m.load_a;
+    p.n_tile = m.n_tile; p.stages = m.stages; p.tiles_per_block = rows_per_expert / m.n_tile; p.load_a = m.load_a; p.fp4 = m.fp4;
     p.total_tiles = blocks * p.tiles_per_block / 4;  // a quarter of the channel tiles: keeps a run ~10 ms
     p.tiles_per_block /= 4;
     p.err = err;
@@ -129,8 +135,10 @@ int main() {
       cudaEventRecord(e1);
       CHECK(cudaDeviceSynchronize());
       float ms; cudaEventElapsedTime(&ms, e0, e1);
+      // bytes written to shared memory (an unpacked fp4 tile is twice its size in global memory)
       const double bytes = (double)p.total_tiles * (K / 128) * ((m.load_a ? 16384 : 0) + m.n_tile * 128);
-      if (rep == 2) printf("%-58s %8.3f ms  %7.2f TB/s  (%.1f GB/s per SM)\n", m.name, ms, bytes / ms / 1e9, bytes / ms / 1e6 / 148);
+      const double stages = (double)p.total_tiles * (K / 128) / 148;
+      if (rep == 2) printf("%-72s %8.3f ms  %7.2f TB/s into shared memory (%.1f GB/s per SM, %.0f ns per stage)\n", m.name, ms, bytes / ms / 1e9, bytes / ms / 1e6 / 148, ms * 1e6 / stages);
     }
     int h = 0; CHECK(cudaMemcpy(&h, err, 4, cudaMemcpyDeviceToHost));
     if (h) { printf("a wait gave up\n"); return 1; }
