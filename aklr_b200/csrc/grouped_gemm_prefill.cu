@@ -295,6 +295,9 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
       wl_q[2] = KB > 1 ? __ldg(ws_lo + 1) : 0.0f;
       wh_q[2] = GATE_UP ? (KB > 1 ? __ldg(ws_hi + 1) : 0.0f) : wl_q[2];
       const int rid = live ? __ldg(p.sorted_ids + b * kBM + row) : -1;
+      // A block's routed rows come first, so an expert's last block often leaves whole quarters of the tile as
+      // padding: a warp without a routed row hands the partials back unread.
+      const bool warp_has_rows = __any_sync(0xFFFFFFFFu, rid >= 0);
       float route_w = 0.0f;
       // (the barrier inside epi_any above also means the previous tile's output pass is done with rid_s)
       if (!GATE_UP && cs == 0) rid_s[row] = rid;
@@ -342,6 +345,15 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
         if (++ring == S) { ring = 0; ring_ph ^= 1; }
         if (!got) bad = true;
         tc_fence_after_sync();
+        if (!warp_has_rows) {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) {
+            if (PAIR) mbar_arrive_cluster(tmem_empty0 + buf * 8);
+            else mbar_arrive(&tmem_empty[buf]);
+          }
+          continue;
+        }
         issue(buf, 0);
 #pragma unroll
         for (int bi = 0; bi < NB; ++bi) {
