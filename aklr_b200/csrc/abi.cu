@@ -366,6 +366,7 @@ int run_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l, co
   qp.scales_in = scales_in;
   qp.q_in_stride = q_in_stride;
   qp.scales_in_stride = scales_in_stride;
+  qp.zero_padding = l.block_m == 128;  // the token-major GEMM is where the padding rows' operands cost clock
   if (!q_in && routes_per_token > 1 && c.n_tokens >= kQuantOncePerTokenFrom) {
     // A token's routes all carry the same quantised row: quantise every token once, then copy.
     // The per-route output rows are not written before the down projection, so their space
@@ -536,6 +537,7 @@ int run_mx_experts(const aklr_moe_config& c, const aklr_moe_workspace_layout& l,
   if (split && fp4) return fail(AKLR_ERR_BAD_ARGUMENT, "activations are kept in bf16 or quantised to MXFP4, not both");
   if (fp4 && q_in) return fail(AKLR_ERR_BAD_ARGUMENT, "rows that arrive quantised are MXFP8");
   qp.act_fp4 = fp4;
+  qp.zero_padding = small_activation_boxes(c) && !split ? 2 : 1;
   const int64_t cap = l.capacity;
   uint8_t* xq_lo = ws + l.xq + align_up(cap * c.hidden, 1024);
   uint8_t* xs_lo = ws + l.xs + align_up(cap * (c.hidden / 128) * 4, 256);

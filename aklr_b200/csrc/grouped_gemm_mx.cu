@@ -106,6 +106,15 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// Whether the producer loads row `row` of the sorted table when blocks with at most 32 / 64 routed rows load only
+// those (a block's routed rows come first).
+__device__ __forceinline__ bool row_in_small_box(const int32_t* sorted_ids, int row) {
+  const int r = row & 127, b0 = row & ~127;
+  if (r < 32) return true;
+  if (sorted_ids[b0 + 32] < 0) return false;
+  return r < 64 || sorted_ids[b0 + 64] >= 0;
+}
+
 // ue8m0 exponent of the smallest power of two >= amax / 448 (frexp rule of the reference's _mxfp8):
 // returns the unbiased exponent in [-126, 127]; amax == 0 gives 0 (scale 1).
 __device__ __forceinline__ int mxfp8_exponent(float amax) {
@@ -200,6 +209,13 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
     tmem_alloc(tmem_ptr, 512);
     tmem_relinquish();
   }
+  // A block with few routed rows loads a 32- or 64-row box; the MMA still multiplies all 128 rows of the stage.
+  // Start them as zeros: in a decode batch, where every block is such a block, they stay zero, and what the tensor
+  // core draws -- and with it the clock the part holds -- depends on the operands.
+  for (int s = 0; s < S; ++s)
+    for (int i = threadIdx.x; i < kOffB / 16; i += kThreads)
+      reinterpret_cast<uint4*>(smem + s * kStageBytes)[i] = make_uint4(0u, 0u, 0u, 0u);
+  fence_proxy_async_smem();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -381,6 +397,12 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
         const float* weights = GATE_UP ? p.stage1_weights : p.topk_weights;
         wgt_s[et] = rid < 0 ? 0.0f : (weights ? weights[rid] : 1.0f);
       }
+      // gate_up: rows the down projection's producer will load (padding rows among them get zero codes)
+      int box_rows = kBM;
+      if (GATE_UP && !SPLIT && p.small_boxes) {
+        if (p.sorted_ids[b * kBM + 32] < 0) box_rows = 32;
+        else if (p.sorted_ids[b * kBM + 64] < 0) box_rows = 64;
+      }
       epi_sync();  // the epilogue reads other threads' entries
       // ---- epilogue: the whole K reduction is in TMEM ----
       {
@@ -457,6 +479,16 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_mx_kernel(const __gr
             for (int i = 0; i < 32; i += 4)
               packed[g * 8 + i / 4] = cvt_e4m3x2(acc[g * 32 + i] * inv, acc[g * 32 + i + 1] * inv) |
                                       (static_cast<uint32_t>(cvt_e4m3x2(acc[g * 32 + i + 2] * inv, acc[g * 32 + i + 3] * inv)) << 16);
+          }
+        }
+        if (rid < 0 && row < box_rows && !bad) {
+          uint8_t* dst = p.out_q + static_cast<size_t>(b * kBM + row) * p.out_dim + j * 128 + half * 64;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) *reinterpret_cast<uint4*>(dst + v * 16) = make_uint4(0u, 0u, 0u, 0u);
+          if (SPLIT) {
+            uint8_t* dst_lo = p.out_q_lo + static_cast<size_t>(b * kBM + row) * p.out_dim + j * 128 + half * 64;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) *reinterpret_cast<uint4*>(dst_lo + v * 16) = make_uint4(0u, 0u, 0u, 0u);
           }
         }
         if (rid >= 0 && !bad) {
@@ -544,7 +576,13 @@ __global__ void __launch_bounds__(256) gather_quant_mxfp8_kernel(MxQuantParams p
     const int row = static_cast<int>(static_cast<uint32_t>(g) / static_cast<uint32_t>(groups_per_row));  // total < 2^31: checked at launch
     const int grp = static_cast<int>(static_cast<uint32_t>(g) - static_cast<uint32_t>(row) * static_cast<uint32_t>(groups_per_row));
     const int rid = p.sorted_ids ? p.sorted_ids[row] : row;  // no table: quantise the rows in place order
-    if (rid < 0) continue;
+    if (rid < 0) {
+      if (p.zero_padding == 1 || (p.zero_padding == 2 && row_in_small_box(p.sorted_ids, row))) {
+        *reinterpret_cast<uint2*>(p.q + static_cast<size_t>(row) * p.hidden + grp * 32 + sub * 8) = make_uint2(0u, 0u);
+        if (p.q_lo) *reinterpret_cast<uint2*>(p.q_lo + static_cast<size_t>(row) * p.hidden + grp * 32 + sub * 8) = make_uint2(0u, 0u);
+      }
+      continue;
+    }
     const int token = rid / p.routes_per_token;
     if (p.q_in) {  // rows quantised by their sender: move codes and scale byte
       *reinterpret_cast<uint2*>(p.q + static_cast<size_t>(row) * p.hidden + grp * 32 + sub * 8) =
@@ -633,15 +671,22 @@ __global__ void __launch_bounds__(256) gather_rows_mxfp8_kernel(MxQuantParams p)
     int src[kGatherRows];
 #pragma unroll
     for (int r = 0; r < kGatherRows; ++r) src[r] = src_s[r];
+    bool zero[kGatherRows];  // a padding row that the GEMM's producer loads
+#pragma unroll
+    for (int r = 0; r < kGatherRows; ++r)
+      zero[r] = src[r] < 0 && row0 + r < n_rows &&
+                (p.zero_padding == 1 || (p.zero_padding == 2 && row_in_small_box(p.sorted_ids, row0 + r)));
     for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
       uint4 val[kGatherRows];
 #pragma unroll
-      for (int r = 0; r < kGatherRows; ++r)
+      for (int r = 0; r < kGatherRows; ++r) {
+        val[r] = make_uint4(0u, 0u, 0u, 0u);
         if (src[r] >= 0)
           val[r] = __ldg(reinterpret_cast<const uint4*>(p.q_in + static_cast<size_t>(src[r]) * q_pitch) + v);
+      }
 #pragma unroll
       for (int r = 0; r < kGatherRows; ++r)
-        if (src[r] >= 0) reinterpret_cast<uint4*>(p.q + static_cast<size_t>(row0 + r) * p.hidden)[v] = val[r];
+        if (src[r] >= 0 || zero[r]) reinterpret_cast<uint4*>(p.q + static_cast<size_t>(row0 + r) * p.hidden)[v] = val[r];
     }
     for (int i = threadIdx.x; i < kGatherRows * KB; i += blockDim.x) {
       const int r = i / KB, kb = i - r * KB;

@@ -399,8 +399,9 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
         for (int c = 0; c < kCS; ++c) m = fmaxf(m, wmax[c * kBM + row]);
         const float scale = fmaxf(__fdiv_rn(m, 448.0f), FLT_MIN);
         const float inv = __fdiv_rn(1.0f, scale);
-        if (rid >= 0 && !bad) {
-          if (cs == 0) p.out_scale[(static_cast<size_t>(b) * IB + j) * kBM + row] = scale;
+        if (live && !bad) {
+          // padding rows get zero codes: the down projection multiplies them too, and zero operands cost it least
+          if (cs == 0 && rid >= 0) p.out_scale[(static_cast<size_t>(b) * IB + j) * kBM + row] = scale;
           uint8_t* dst = p.out_q + static_cast<size_t>(b * kBM + row) * p.out_dim + j * 128 + cs * HC;
 #pragma unroll
           for (int v = 0; v < HC / 16; ++v) {
@@ -408,8 +409,9 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_prefill_kernel(const
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               const int i = v * 16 + q * 4;
-              w[q] = cvt_e4m3x2(acc[i] * inv, acc[i + 1] * inv) |
-                     (static_cast<uint32_t>(cvt_e4m3x2(acc[i + 2] * inv, acc[i + 3] * inv)) << 16);
+              w[q] = rid < 0 ? 0u
+                             : cvt_e4m3x2(acc[i] * inv, acc[i + 1] * inv) |
+                                   (static_cast<uint32_t>(cvt_e4m3x2(acc[i + 2] * inv, acc[i + 3] * inv)) << 16);
             }
             *reinterpret_cast<uint4*>(dst + v * 16) = make_uint4(w[0], w[1], w[2], w[3]);
           }

@@ -62,6 +62,7 @@ struct GatherQuantParams {
   float* scales;              // block_m == 0: [rows, hidden/128]; else [rows/block_m, hidden/128, block_m]
   int n_rows, hidden, routes_per_token, block_m;
   int q_in_stride, scales_in_stride;  // gather_rows only: bytes between source rows (0: dense)
+  int zero_padding;  // non-zero: padding rows of the table get zero codes (see gather_rows_fp8_kernel)
 };
 int launch_gather_quant_fp8(const GatherQuantParams& p, cudaStream_t stream);
 
@@ -145,6 +146,10 @@ struct MxQuantParams {
   // group's largest value in (3, 6], values round to the e2m1 grid (ties to the even code).  Every e2m1
   // value is also an e4m3 value, so the codes are stored as e4m3 bytes and the same MMAs consume them.
   int act_fp4;
+  // Padding rows of the table that the GEMM's producer loads get zero codes (they are multiplied although never
+  // read back, and zero operands cost the tensor core least): 0 off, 1 every padding row, 2 only those inside the
+  // 32- or 64-row box of a block with that few routed rows (MxGemmParams::small_boxes).
+  int zero_padding;
 };
 int launch_gather_quant_mxfp8(const MxQuantParams& p, cudaStream_t stream);
 

@@ -19,6 +19,8 @@ __global__ void __launch_bounds__(128, 1) probe(long long* out, int random_data,
       v = (i + 1) * 2654435761u + blockIdx.x * 40503u;
       v ^= v >> 15; v *= 2246822519u; v ^= v >> 13;
       v &= 0xBFBFBFBFu;
+      // modes 2, 3: the activation tile's rows from 64 / 32 on are zero (row r = bytes r * 128 .. of the first 16 KB)
+      if (random_data >= 2 && i * 4 < 16384 && i * 4 >= (random_data == 2 ? 64 : 32) * 128) v = 0u;
     }
     ((uint32_t*)smem)[i] = v;
   }
@@ -49,7 +51,7 @@ __global__ void __launch_bounds__(128, 1) probe(long long* out, int random_data,
 int main() {
   long long* d; cudaMalloc(&d, 148 * 2 * 8);
   cudaFuncSetAttribute(probe, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-  const int cfgs[][2] = {{0, 4096}, {1, 4096}, {0, 65536}, {1, 65536}, {0, 262144}, {1, 262144}, {0, 4096}};
+  const int cfgs[][2] = {{0, 4096}, {1, 4096}, {0, 65536}, {1, 65536}, {0, 262144}, {1, 262144}, {0, 4096}, {2, 65536}, {3, 65536}, {1, 65536}};
   for (auto& c : cfgs) {
     cudaMemset(d, 0, 148 * 2 * 8);
     probe<<<148, 128, 64 * 1024>>>(d, c[0], c[1]);
@@ -57,8 +59,8 @@ int main() {
     long long h[296]; cudaMemcpy(h, d, sizeof(h), cudaMemcpyDeviceToHost);
     double cyc = 0, ns = 0; for (int i = 0; i < 148; ++i) { cyc += h[2 * i]; ns += h[2 * i + 1]; }
     cyc /= 148.0 * c[1]; ns /= 148.0 * c[1];
-    printf("%-8s operands, %6d MMAs  %s  cycles per MMA %.1f   ns per MMA %.1f   -> SM clock %.0f MHz, %.2f PFLOP/s over the GPU\n",
-           c[0] ? "random" : "constant", c[1], cudaGetErrorString(e), cyc, ns, cyc / ns * 1e3,
+    printf("%-26s operands, %6d MMAs  %s  cycles per MMA %.1f   ns per MMA %.1f   -> SM clock %.0f MHz, %.2f PFLOP/s over the GPU\n",
+           c[0] == 0 ? "constant" : c[0] == 1 ? "random" : c[0] == 2 ? "random, A rows 64.. zero" : "random, A rows 32.. zero", c[1], cudaGetErrorString(e), cyc, ns, cyc / ns * 1e3,
            148.0 * 2 * 128 * 256 * 32 / ns / 1e6);
     fflush(stdout);
   }

@@ -43,7 +43,15 @@ __global__ void __launch_bounds__(256) gather_rows_fp8_kernel(GatherQuantParams 
   const int warps = (gridDim.x * blockDim.x) >> 5;
   for (int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < n_rows; row += warps) {
     const int rid = p.sorted_ids[row];  // the same address for the whole warp: one broadcast load
-    if (rid < 0) continue;              // padding rows are never read back
+    if (rid < 0) {
+      // Padding rows are never read back, but the tensor core multiplies them all the same, and what it draws
+      // depends on the operands: with zero rows in place of stale codes the part holds a higher clock under the
+      // token-major GEMM (an N = 256 MMA stream alone: 1600 MHz on random operands, 1740 with half the rows zero).
+      if (p.zero_padding)
+        for (int v = lane; v < vec_per_row; v += 32)
+          reinterpret_cast<uint4*>(p.q + static_cast<size_t>(row) * p.hidden)[v] = make_uint4(0u, 0u, 0u, 0u);
+      continue;
+    }
     const int src = rid / p.routes_per_token;
     const uint4* from = reinterpret_cast<const uint4*>(p.q_in + static_cast<size_t>(src) * q_pitch);
     uint4* to = reinterpret_cast<uint4*>(p.q + static_cast<size_t>(row) * p.hidden);

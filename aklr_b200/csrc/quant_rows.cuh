@@ -86,6 +86,8 @@ __device__ __forceinline__ void gather_quant_fp8_groups(const GatherQuantParams&
           token = rid < 0 ? -1 : rid / p.routes_per_token;
         }
         live[u] = token >= 0;  // padding rows are never read back
+        if (!live[u] && p.zero_padding)  // but multiplied: zero codes cost the tensor core least
+          *reinterpret_cast<uint2*>(p.q + static_cast<size_t>(row[u]) * p.hidden + grp[u] * 128 + sub * 8) = make_uint2(0u, 0u);
         if (live[u])
           raw[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.x) +
                                                    static_cast<size_t>(token) * p.hidden + grp[u] * 128 + sub * 8);
