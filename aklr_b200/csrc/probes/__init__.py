@@ -12,6 +12,8 @@ against these numbers.
 * ``mma_beside_tma``: the MMA stream of a K-block (two deep) alone, a TMA ring alone, and both at once.
 * ``mx_issue``: the MXFP4 kernel's issue stream alone: four block-scaled MMAs per K-block with 0 .. 4 ``tcgen05.cp`` of
   scale factors in front of them.
+* ``mma_burst``: bursts of 1 .. 12 MMAs from an idle pipe: what one ``tcgen05.mma`` costs its issuing thread and how far
+  the pipe lets the thread run ahead.
 * ``mma_data``: the same N = 256 MMA stream on constant and on random operands, in cycles and in nanoseconds: the SM
   clock the part holds while its tensor pipes are busy depends on the data.
 
@@ -27,7 +29,7 @@ import sys
 HERE = pathlib.Path(__file__).resolve().parent
 ROOT = HERE.parents[2]
 OUT = ROOT / "build" / "probes"
-PROGRAMS = ("tma_ring", "mma_chain", "mma_beside_tma", "mx_issue", "mma_data")
+PROGRAMS = ("tma_ring", "mma_chain", "mma_beside_tma", "mx_issue", "mma_burst", "mma_data")
 
 
 def build() -> list[pathlib.Path]:
