@@ -210,12 +210,14 @@ __global__ void wait_expiry_kernel(long long limit_cycles, int32_t* status, int3
 int pick_block_m(const aklr_moe_config& c) {
   if (c.block_m) return c.block_m;
   const double avg = static_cast<double>(c.n_tokens) * c.topk / (c.n_routed > 0 ? c.n_routed : 1);
-  // Measured on the DeepSeek-V3 layer: from ~24 rows per expert the token-major kernels on 128-token
+  // Measured on the DeepSeek-V3 layer: from ~28 rows per expert the token-major kernels on 128-token
   // blocks (mostly padding at that point) already beat the weight-major ones on smaller blocks --
-  // T=1024: 2.16 ms against 2.33 (block 64) and 2.69 (block 32); T=512 is a tie.
-  if (avg >= 24.0) return 128;
+  // T=1024 (32 rows per expert): 2.28-2.57 ms against 2.66 (block 32) and 2.60-2.67 (block 64); T=768 (24):
+  // 2.38-2.44 ms against 2.19-2.23 (block 32) and 2.54 (block 64).  Blocks of 64 lose to blocks of 32 at every
+  // count from 384 to 1536 tokens (their down projection has no 256-channel tiles), so they are never picked.
+  if (avg >= 28.0) return 128;
   int bm = 16;
-  while (bm < 64 && bm < avg * 1.5) bm *= 2;
+  while (bm < 32 && bm < avg * 1.5) bm *= 2;
   return bm;
 }
 
