@@ -60,6 +60,23 @@ def test_workspace_layout_is_ordered_and_sized(lib):
     assert lay.total_bytes >= lay.rows + 256 * 9 * 7168 * 2
 
 
+def test_automatic_block_size_follows_rows_per_expert(lib):
+    """Small blocks (weight-major kernels) up to 28 routes per routed expert, never 64; 128-token blocks above."""
+    from aklr_b200._lib import MoeConfig, WorkspaceLayout
+
+    def picked(tokens, n_routed=256, topk=8):
+        cfg = MoeConfig(n_tokens=tokens, hidden=7168, inter=2048, n_routed=n_routed, n_shared=1, topk=topk, scoring=1,
+                        num_expert_group=8, topk_group=4, renormalize=1, routed_scaling_factor=2.5)
+        lay = WorkspaceLayout()
+        assert lib.aklr_moe_fp8_workspace(ctypes.byref(cfg), ctypes.byref(lay)) == 0
+        return lay.block_m
+
+    assert [picked(t) for t in (1, 8, 256, 320)] == [16, 16, 16, 16]
+    assert [picked(t) for t in (352, 512, 704, 768, 895)] == [32, 32, 32, 32, 32]
+    assert [picked(t) for t in (896, 1024, 4096, 16384)] == [128, 128, 128, 128]
+    assert picked(64, n_routed=8, topk=2) == 32 and picked(128, n_routed=8, topk=2) == 128  # 16 and 32 routes per expert
+
+
 def test_bad_shapes_are_refused_with_a_message(lib):
     from aklr_b200._lib import MoeConfig, WorkspaceLayout
 
