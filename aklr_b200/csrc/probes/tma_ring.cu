@@ -34,11 +34,13 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
 struct Params {
   CUtensorMap map_w, map_x;
   int K, rows_per_expert, n_experts, blocks_per_expert, n_tile, stages, tiles_per_block, total_tiles, load_a, fp4;
+  int w_box;         // rows per weight box: 128 (two loads per 256-row tile) or 256 (one)
+  int two_producers; // 1: a thread of another warp issues the weight loads
   int* err;
 };
 
 // tile t -> (block b, channel tile j): block's expert = b / blocks_per_expert
-__global__ void __launch_bounds__(64, 1) probe(const __grid_constant__ Params p) {
+__global__ void __launch_bounds__(96, 1) probe(const __grid_constant__ Params p) {
   extern __shared__ uint8_t raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   const int a_bytes = p.load_a ? 16384 : 0;
@@ -51,7 +53,10 @@ __global__ void __launch_bounds__(64, 1) probe(const __grid_constant__ Params p)
   }
   __syncthreads();
   const int KB = p.K / 128;
-  if (threadIdx.x == 0) {
+  if (threadIdx.x == 0 || (p.two_producers && threadIdx.x == 64)) {
+    // one producer: barrier, activation box, weight boxes.  Two: thread 0 the barrier and the activation box,
+    // thread 64 the weight boxes (its bytes may land before the expectation is posted: the count goes negative).
+    const bool does_a = threadIdx.x == 0, does_w = !p.two_producers || threadIdx.x == 64;
     int s = 0; uint32_t ph = 0;
     for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
       const int b = t / p.tiles_per_block, j = t - b * p.tiles_per_block;
@@ -60,10 +65,13 @@ __global__ void __launch_bounds__(64, 1) probe(const __grid_constant__ Params p)
       for (int kb = 0; kb < KB; ++kb) {
         if (!mbar_wait(&empty[s], ph ^ 1, p.err)) return;
         uint8_t* st = smem + s * stage_bytes;
-        // an unpacking load counts the packed bytes that cross from global memory
-        mbar_expect_tx(&full[s], a_bytes + (p.fp4 ? p.n_tile * 64 : p.n_tile * 128));
-        if (p.load_a) tma_load_2d(st, &p.map_x, &full[s], kb * 128, b * 128);
-        for (int r = 0; r < p.n_tile; r += 128) tma_load_2d(st + 16384 + r * 128, &p.map_w, &full[s], kb * 128, w_row + r);
+        if (does_a) {
+          // an unpacking load counts the packed bytes that cross from global memory
+          mbar_expect_tx(&full[s], a_bytes + (p.fp4 ? p.n_tile * 64 : p.n_tile * 128));
+          if (p.load_a) tma_load_2d(st, &p.map_x, &full[s], kb * 128, b * 128);
+        }
+        if (does_w)
+          for (int r = 0; r < p.n_tile; r += p.w_box) tma_load_2d(st + 16384 + r * 128, &p.map_w, &full[s], kb * 128, w_row + r);
         if (++s == p.stages) { s = 0; ph ^= 1; }
       }
     }
@@ -106,7 +114,7 @@ int main() {
   CHECK(cudaMalloc(&err, 4)); CHECK(cudaMemset(err, 0, 4));
   cudaEvent_t e0, e1; cudaEventCreate(&e0); cudaEventCreate(&e1);
   CHECK(cudaFuncSetAttribute(probe, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-  struct Mode { const char* name; int n_tile, stages, n_experts, blocks_per_expert, load_a, fp4; };
+  struct Mode { const char* name; int n_tile, stages, n_experts, blocks_per_expert, load_a, fp4, w_box, two_producers; };
   const Mode modes[] = {
       {"48KB x4, weights from HBM (128 experts x 5 blocks)", 256, 4, 128, 5, 1},
       {"48KB x4, weights L2-resident (2 experts)", 256, 4, 2, 5, 1},
@@ -118,10 +126,15 @@ int main() {
       {"fp4 unpacked by the TMA: A + B, x4, L2-resident (2 experts)", 256, 4, 2, 5, 1, 1},
       {"fp4 unpacked by the TMA: B only, x4, from HBM", 256, 4, 128, 5, 0, 1},
       {"fp4 unpacked by the TMA: B only, x4, L2-resident", 256, 4, 2, 5, 0, 1},
+      {"48KB x4 L2-resident, weights as ONE 256-row box (2 loads per stage)", 256, 4, 2, 5, 1, 0, 256},
+      {"48KB x4 L2-resident, two producer threads (A | 2 weight boxes)", 256, 4, 2, 5, 1, 0, 128, 1},
+      {"48KB x4 L2-resident, two producer threads, one 256-row weight box", 256, 4, 2, 5, 1, 0, 256, 1},
+      {"48KB x4 from HBM, two producer threads, one 256-row weight box", 256, 4, 128, 5, 1, 0, 256, 1},
   };
   for (const Mode& m : modes) {
     Params p{};
-    make_map(enc, &p.map_w, w, (uint64_t)128 * rows_per_expert, K, 128, m.fp4 != 0);
+    make_map(enc, &p.map_w, w, (uint64_t)128 * rows_per_expert, K, m.w_box ? m.w_box : 128, m.fp4 != 0);
+    p.w_box = m.w_box ? m.w_box : 128; p.two_producers = m.two_producers;
     make_map(enc, &p.map_x, x, (uint64_t)blocks * 128, K, 128);
     p.K = K; p.rows_per_expert = rows_per_expert; p.n_experts = m.n_experts; p.blocks_per_expert = m.blocks_per_expert;
     p.n_tile = m.n_tile; p.stages = m.stages; p.tiles_per_block = rows_per_expert / m.n_tile; p.load_a = m.load_a; p.fp4 = m.fp4;
@@ -131,7 +144,7 @@ int main() {
     const size_t smem = (size_t)m.stages * (16384 + m.n_tile * 128) + 2 * m.stages * 8 + 1024;
     for (int rep = 0; rep < 3; ++rep) {
       cudaEventRecord(e0);
-      probe<<<148, 64, smem>>>(p);
+      probe<<<148, 96, smem>>>(p);
       cudaEventRecord(e1);
       CHECK(cudaDeviceSynchronize());
       float ms; cudaEventElapsedTime(&ms, e0, e1);
