@@ -225,16 +225,8 @@ class ExpertParallelMoE:
         k = self.kernels
         if routed is None and logits.shape[1] != self.n_local * self.world:
             raise ValueError(f"router has {logits.shape[1]} experts, the group holds {self.n_local * self.world}")
-        ids, weights = routed if routed is not None else k.route(logits, bias, self.routing)
-        self.routing = dataclasses.replace(self.routing, topk=ids.shape[1])
-        layout = RowLayout(hidden.shape[1], ids.shape[1], bool(getattr(k, "mx", False)))
-        plan = k.plan(ids, self.n_local, self.world)
-        packed = k.pack(hidden, ids, weights, plan, self.n_local, layout)
         shared_rows = shared_done = None
-        if self.shared is not None:
-            # Own tokens through the replicated shared experts, on a side stream that starts when the rows are
-            # packed: its persistent CTAs then fill the SMs while the counts and the rows are exchanged, instead of
-            # standing in the way of the routing and packing kernels that the exchange waits for.
+        if self.shared is not None:  # overlaps the dispatch: own tokens through the replicated shared experts
             if hidden.is_cuda:
                 if self._side is None:
                     self._side = k.side_stream(hidden.device)
@@ -246,6 +238,11 @@ class ExpertParallelMoE:
                 hidden.record_stream(self._side)
             else:
                 shared_rows = k.shared(hidden, *self.shared)
+        ids, weights = routed if routed is not None else k.route(logits, bias, self.routing)
+        self.routing = dataclasses.replace(self.routing, topk=ids.shape[1])
+        layout = RowLayout(hidden.shape[1], ids.shape[1], bool(getattr(k, "mx", False)))
+        plan = k.plan(ids, self.n_local, self.world)
+        packed = k.pack(hidden, ids, weights, plan, self.n_local, layout)
         return StepState(packed, plan[1], plan[2], shared_rows, shared_done, hidden.shape[0], layout)
 
     # ---- phase 2: on the rank that holds the experts ---------------------------------------------
