@@ -509,6 +509,37 @@ def test_cta_pair_kernels_match_the_single_cta_kernels(golden):
     assert torch.equal(outs[0], outs[1])
 
 
+def test_padding_rows_of_128_token_blocks_carry_zero_codes():
+    """The token-major GEMMs multiply a block's padding rows like any others; what they hold is never read back, but
+    the tensor core's draw depends on it, so the gather and the gate_up epilogue write zero codes there.  Routed rows
+    keep their codes (the output still passes against the same call on 16-token blocks, which has no such rows)."""
+    from aklr_b200.moe import fused_moe_fp8
+
+    cfg = wl.CONFIGS["deepseek_small"]
+    d = dev()
+    w1, s1, w2, s2 = (x.to(d) for x in wl.expert_weights(cfg, seed=5))
+    hidden, logits, bias = (x.to(d) for x in wl.router_inputs(cfg, 700, seed=9))
+    outs = {}
+    for bm in (128, 16):
+        # a call on other tokens first: the call under test then finds that call's codes where its padding falls
+        ws = None
+        for h, l in ((hidden.flip(0).contiguous(), logits.flip(0).contiguous()), (hidden, logits)):
+            out, ws = fused_moe_fp8(h, l, bias, w1, s1, w2, s2, routing_of(cfg), block_m=bm, return_workspace=True, workspace=ws)
+        ws.check_status()
+        outs[bm] = out.float().cpu()
+        if bm == 128:
+            ids = ws.sorted_ids().cpu()
+            padding = ids < 0
+            assert padding.any() and (~padding).any()
+            n = ids.numel()
+            for name, (codes, _) in (("activations", ws.xq()), ("gated product", ws.hq())):
+                as_bytes = codes[:n].view(torch.uint8).cpu()
+                assert int(as_bytes[padding].max()) == 0, name
+                assert int((as_bytes[~padding] != 0).sum()) > 0, name
+    gates = orc.output_gates(outs[128], outs[16])
+    assert orc.gates_pass(gates), gates
+
+
 def test_deep_pipeline_kernels_match_the_two_buffer_kernels(golden):
     """128 x 128 tiles with four partials in flight: per element the same float32 operations in the same order
     as the 128 x 256 kernels, so outputs are bit-identical -- on the golden layer, on a batch with several blocks
